@@ -1,0 +1,199 @@
+/*
+ * lsa_b200 - C ABI of the B200 (sm_100a) kernels for Latent Sparse Attention's selection-plus-attention path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - Every function returns 0 on success or a negative LSA_ERR_* code decided on the host before any launch.
+ *     lsa_error_string() names a code. Nothing here allocates, frees or synchronises unless its comment says so:
+ *     scratch memory is passed in by the caller and sized by the matching *_workspace_bytes() query.
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it.
+ *   - Conditions only the device can see (a truncated list, an id out of range) are counted in the int32 word
+ *     `status` (may be NULL): the kernel adds one per event and carries on with a safe value; it never traps.
+ *   - Strides are in ELEMENTS. bf16 data is passed as uint16_t bit patterns.
+ *   - "Reference" citations name files of the Prefrontal-AI/latent-sparse-attention project whose behaviour the
+ *     entry point reproduces.
+ */
+#ifndef LSA_B200_H
+#define LSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LSA_OK 0
+#define LSA_ERR_ARGUMENT (-1)    /* a size, stride or combination the kernels do not take */
+#define LSA_ERR_NULL (-2)        /* a required pointer is NULL */
+#define LSA_ERR_UNSUPPORTED (-3) /* a shape outside what this build was written for */
+#define LSA_ERR_WORKSPACE (-4)   /* the workspace passed in is smaller than *_workspace_bytes() asks */
+#define LSA_ERR_LAUNCH (-5)      /* the CUDA runtime refused a launch or an attribute */
+#define LSA_ERR_DEVICE (-6)      /* not an sm_100 device */
+
+#define LSA_PAD (-1)                  /* the only padding value an id list carries (src/lsa/constants.py:16-20) */
+#define LSA_EMPTY_KEY INT64_MIN       /* the packed key of no bucket (src/lsa/core/kernels/constants.py:29-37) */
+#define LSA_DTYPE_F32 0
+#define LSA_DTYPE_BF16 1
+
+const char *lsa_error_string(int code);
+/* ABI version of this library; bumped when a signature changes. */
+int lsa_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Index space: grouped-query head sum, learned map, row normalisation.
+ * Reference: regroup_partial / project_partial / project / rownorm (src/lsa/core/index_space.py:134-187,
+ * 378-419, 315-334); served form Projection.__call__ and KeyAndQueryProjection.index_queries / index_keys
+ * (src/lsa/sglang/index/layer_index.py:256-267, 331-355).
+ *
+ * out[s, :] = normalize( sum_kv  ( sum_{g<group} x[s, kv*group+g, off:off+dh_used] ) @ W[kv*dh_used:(kv+1)*dh_used, :] )
+ *   x        [rows, heads, *] of x_dtype with element strides (x_row_stride, x_head_stride)
+ *   group    query heads added per KV head (1 for keys); heads % group == 0
+ *   dh_off   first head dim read (the rotary prefix dropped), dh_used dims read per head
+ *   W        [heads/group*dh_used, d_idx] of w_dtype, row-major; NULL = identity (d_idx = heads/group*dh_used)
+ *   out_f32  [rows, d_idx] fp32 or NULL; out_bf16 [rows, d_idx] bf16 or NULL (at least one)
+ *   normalize 0 = leave the product as it is (the partial form), 1 = unit rows, a zero row stays zero
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group, int dh_off, int dh_used,
+                  int64_t x_row_stride, int64_t x_head_stride, const void *W, int w_dtype, int d_idx,
+                  int normalize, float *out_f32, uint16_t *out_bf16, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Pooling. Reference: pool_keys (src/lsa/core/ward.py:15-26).
+ * pools[p, :] = sum of index_keys[p*pool_size : (p+1)*pool_size, :] added in position order, fp32.
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_pool_keys(const void *index_keys, int key_dtype, int64_t n_pools, int pool_size, int d, float *pools,
+                  void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Capped Ward bucketing of every cluster block. Reference: ward_rounds (src/lsa/core/ward.py:29-90); GPU front
+ * door cluster_ward (src/lsa/core/kernels/ward.py:49-81).
+ *   pool_keys  [blocks, P, d] fp32, pool_sizes [blocks, P] fp32 (NULL = every pool holds uniform_pool_size)
+ *   labels     [blocks, P] int64 out - each pool's bucket, numbered by first pool
+ *   reached    [blocks] uint8 out - 1 where the block got down to bucket_count
+ *   rounds     [blocks] int32 out or NULL - merge rounds the block ran
+ * One CTA per block; P <= 4096, d <= 256, d % 4 == 0. Costs are fp32 in the reference's evaluation order, the
+ * Gram dot added in ascending dim order.
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_ward_merge(const float *pool_keys, const float *pool_sizes, float uniform_pool_size, int64_t blocks, int P,
+                   int d, int bucket_count, float bucket_cap, int max_rounds, int64_t *labels, uint8_t *reached,
+                   int32_t *rounds, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Bucket table from labels. Reference: build_buckets (src/lsa/core/reference.py:120-144), members_from_labels
+ * (src/lsa/core/ward.py:128-143), bucket_members_from_labels (src/lsa/core/kernels/triton/ward.py:551).
+ *   index_keys [>= blocks*P*pool_size, d] (key_dtype), labels [blocks, P] int64
+ *   members    [blocks*bucket_count, bucket_cap] int32 out, absolute positions ascending, -1 padded; position of
+ *              key t of block g is first_position + g*P*pool_size + t
+ *   sizes      [blocks*bucket_count] int32 out
+ *   key_sums   [blocks*bucket_count, d] fp32 out or NULL - the keys added one by one in position order
+ *   centroids  [blocks*bucket_count, d] fp32 out or NULL - key_sum / max(||key_sum||, 1e-30)
+ *   centroids_bf16 same, rounded to bf16, or NULL
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_bucket_table(const void *index_keys, int key_dtype, const int64_t *labels, int64_t blocks, int P,
+                     int pool_size, int d, int bucket_count, int bucket_cap, int64_t first_position,
+                     int32_t *members, int32_t *sizes, float *key_sums, float *centroids,
+                     uint16_t *centroids_bf16, int32_t *status, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Flat search, prefill form: score every visible bucket, keep the top_p packed keys of each row.
+ * Reference: read / _read_row (src/lsa/core/reference.py:228-265); served Selector.read_flat
+ * (src/lsa/sglang/index/selector.py:370-423), ScanSelect (src/lsa/core/kernels/scan_select.py:189-385), packed
+ * keys (src/lsa/core/kernels/triton/keys.py:18-88).
+ *   queries   [R, d] fp32; centroids [m, d] fp32
+ *   visible   [R] int32 - buckets the row sees (a prefix of the rows of centroids), clamped to m
+ *   row_top_p [R] int32 or NULL - a row's own top_p (an early budget), at most top_p
+ *   bucket_id_base  added to the row index of a centroid to give the id packed in the key
+ *   keys_out  [R, top_p] int64 - packed keys, best first, LSA_EMPTY_KEY after a row's count
+ *   picked_out [R, top_p] int32 or NULL - the ids of keys_out, -1 padded
+ * Scores are fp32 dots added in ascending dim order; a tie goes to the lower id.
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,
+                    const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                    int64_t *keys_out, int32_t *picked_out, void *stream);
+
+/* Flat search, decode form: few rows, many buckets. The buckets of a row are split over `splits` CTAs whose
+ * local top_p lists are merged by a second kernel. Reference: Selector.decode_flat
+ * (src/lsa/sglang/index/selector.py:603-660), scan_paged (src/lsa/core/kernels/triton/paged.py:61-101),
+ * DecodeSelect.listed (src/lsa/core/kernels/cutedsl/decode.py:1035-1068).
+ *   request_first [R] int64 - first row of centroids of each request (requests hold their buckets contiguously)
+ *   workspace  lsa_flat_select_decode_workspace_bytes(R, top_p, splits)
+ */
+size_t lsa_flat_select_decode_workspace_bytes(int64_t R, int top_p, int splits);
+int lsa_flat_select_decode(const float *queries, int64_t R, int d, const float *centroids,
+                           const int64_t *request_first, const int32_t *visible, int top_p, int splits,
+                           int64_t *keys_out, int32_t *picked_out, void *workspace, size_t workspace_bytes,
+                           void *stream);
+
+/* Global top_p of several candidate lists of packed keys (the lists every rank all-gathered, or a row's
+ * splits). keys_in [parts, R, top_p] int64; keys_out [R, top_p] best first; picked_out as above or NULL. */
+int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out,
+                         int32_t *picked_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Tree search, one beam step: score the candidate rows of a level (open node buckets first_open..made and the
+ * children carried from the level above), keep the best `keep`, a tie to the lower row.
+ * Reference: beam_pick / best (src/lsa/core/hierarchy.py:402-451); served Hierarchy.beam_search, pick_buckets
+ * (src/lsa/sglang/index/hierarchy.py:494-625, 765-854).
+ *   vectors   [N, d] fp32 - the level's node centroids (or the bucket centroids at level 0)
+ *   carried   [R, n_carried] int32 candidate rows, -1 = none; may be NULL with n_carried 0
+ *   open_first/open_end [R] int32 - the run of rows every query scores besides (open_end <= open_first = none)
+ *   children  [N, fanout] int64 or NULL. When given, kept_out is NULL and carried_out [R, keep*fanout] int32
+ *             receives the children of the kept rows (-1 padded), best row first.
+ *   kept_out  [R, keep] int32 (-1 padded), keys_out [R, keep] int64 or NULL
+ * One CTA per row.
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, int64_t N, const int32_t *carried,
+                  int n_carried, const int32_t *open_first, const int32_t *open_end, int keep,
+                  const int64_t *children, int fanout, int32_t *kept_out, int64_t *keys_out, int32_t *carried_out,
+                  void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Expansion: picked buckets -> the row's read list. Reference: expand_buckets
+ * (src/lsa/core/reference.py:268-289), budget_at (src/lsa/budget.py:60-74); served expand_in_order
+ * (src/lsa/core/kernels/expansion.py:16-58).
+ *   picked     [R, top_p] int32 bucket rows, best first, -1 = none
+ *   positions  [R] int64; members [m, bucket_cap] int32
+ *   row_top_p / row_top_k [R] int32 or NULL - a row's own budget
+ *   page_table [pages] int32 or NULL with page_size - when given every id is stored as the KV slot
+ *              page_table[id / page_size] * page_size + id % page_size instead of the position
+ *   owner_first/owner_end - only ids in [owner_first, owner_end) are written (a rank's share of the sequence);
+ *              the top_k cut still counts every id. Pass 0 and INT64_MAX for all.
+ *   selected   [R, top_k + window + sink] int32 out - expansion, window ascending, sinks ascending, -1 padded
+ *   lengths    [R] int32 out
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions, const int32_t *members,
+               int64_t m, int bucket_cap, const int32_t *row_top_p, const int32_t *row_top_k, int top_k,
+               int sink, int window, const int32_t *page_table, int page_size, int64_t owner_first,
+               int64_t owner_end, int32_t *selected, int32_t *lengths, int32_t *status, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Gather-sparse attention over each row's list, with the log-sum-exp of the scaled logits.
+ * Reference: topk_attention / keep_set (src/lsa/core/attention.py:15-146); served sparse_read, partial_read
+ * (src/lsa/sglang/models/qwen3_5/backend.py:427-460, 669-721).
+ *   q      [R, Hq, dh] bf16 (q_row_stride, q_head_stride); dh = 64 or 128; Hq/Hkv <= 16
+ *   k, v   [slots, Hkv, dh] bf16 (kv_row_stride, kv_head_stride), 16-byte aligned rows
+ *   ids    [R, list_stride] int32 - the first lengths[r] entries are read, each one once: KV rows (slots) the
+ *          caller guarantees causal and distinct, as lsa_expand writes them; an entry < 0 or >= slots is skipped
+ *   splits CTAs-per-(row, KV head) the list is divided over; > 1 needs the workspace and runs the merge kernel
+ *   out    [R, Hq, dh] bf16 (out_bf16) and/or fp32 (out_f32); lse [R, Hq] fp32 or NULL
+ * A row that reads nothing gives zeros and lse = -inf.
+ * --------------------------------------------------------------------------------------------------------- */
+size_t lsa_sparse_attend_workspace_bytes(int64_t R, int Hq, int dh, int splits);
+int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
+                      const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv, int64_t kv_row_stride,
+                      int64_t kv_head_stride, const int32_t *ids, int64_t list_stride, const int32_t *lengths,
+                      float scale, int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
+/* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
+ * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the
+ * reference calls at src/lsa/sglang/models/qwen3_5/backend.py:724-738.
+ *   parts [n_parts, rows, dh] fp32, lses [n_parts, rows] fp32; out_bf16/out_f32 [rows, dh]; lse_out [rows] or NULL */
+int lsa_lse_merge(const float *parts, const float *lses, int n_parts, int64_t rows, int dh, uint16_t *out_bf16,
+                  float *out_f32, float *lse_out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LSA_B200_H */

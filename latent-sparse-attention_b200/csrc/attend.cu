@@ -1,0 +1,398 @@
+// Gather-sparse attention: every query row attends over the KV rows its list names.
+//
+// A warp owns one (query row, KV head, split) item and streams the listed K/V rows through its own
+// shared-memory ring with asynchronous 16-byte copies (zero-filled for a list's ragged end), three tiles of 16
+// keys in flight. The head group's queries share each gathered row: with the KEYS as the M dimension of the
+// tensor-core tile (S^T = K Q^T, O^T = V^T P^T) a group of up to 8 query heads fills the N = 8 side of
+// mma.m16n8k16 instead of 5 of 16 M rows, which halves the instructions per key. Softmax is online in the log2
+// domain with fp32 statistics; the kernel emits the natural-log log-sum-exp so partial results over disjoint key
+// sets (splits of a list here, ranks of a sequence-sharded cache elsewhere) merge exactly.
+#include "common.cuh"
+
+namespace lsa {
+
+constexpr int kKeysPerTile = 16;
+constexpr int kStages = 3;
+
+struct AttendParams {
+  const uint16_t *q, *k, *v;
+  const int32_t *ids, *lengths;
+  uint16_t *out_bf16;
+  float *out_f32, *lse, *part_out, *part_lse;
+  int64_t R, slots, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride, list_stride;
+  int Hq, Hkv, group, splits;
+  float scale_log2;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                                  uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// DH: head dim (64 or 128). NT: 8-head tiles a group needs (1 or 2). W: warps a CTA.
+template <int DH, int NT, int W>
+__global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
+  constexpr int ROW_BYTES = DH * 2;
+  constexpr int CHUNKS = ROW_BYTES / 16;                  // 16-byte chunks a row
+  constexpr int TILE_BYTES = kKeysPerTile * ROW_BYTES;    // one of K or V
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  constexpr int WARP_BYTES = kStages * STAGE_BYTES + 16;  // + the stages' validity masks
+  constexpr int KSTEPS = DH / 16;
+  constexpr int ROWS_PER_PASS = 32 / CHUNKS;              // rows one pass of the warp's lanes covers
+  constexpr int PASSES = kKeysPerTile / ROWS_PER_PASS;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t item = (int64_t)blockIdx.x * W + warp;
+  if (item >= p.R * p.splits * p.Hkv) return;
+  const int h = (int)(item % p.Hkv);
+  const int64_t rs = item / p.Hkv;
+  const int split = (int)(rs % p.splits);
+  const int64_t r = rs / p.splits;
+
+  unsigned char *mine = smem_raw + (size_t)warp * WARP_BYTES;
+  const uint32_t smem_base = smem_u32(mine);
+  volatile uint32_t *masks = reinterpret_cast<volatile uint32_t *>(mine + kStages * STAGE_BYTES);
+
+  int64_t n_total = p.lengths ? p.lengths[r] : p.list_stride;
+  if (n_total > p.list_stride) n_total = p.list_stride;
+  if (n_total < 0) n_total = 0;
+  int64_t per = (n_total + p.splits - 1) / p.splits;
+  per = (per + kKeysPerTile - 1) / kKeysPerTile * kKeysPerTile;
+  const int64_t begin = (int64_t)split * per;
+  const int64_t end = begin + per < n_total ? begin + per : n_total;
+  const int n = end > begin ? (int)(end - begin) : 0;
+  const int tiles = (n + kKeysPerTile - 1) / kKeysPerTile;
+  const int32_t *list = p.ids + r * p.list_stride + begin;
+  const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride;
+  const uint16_t *v_head = p.v + (int64_t)h * p.kv_head_stride;
+
+  // Q^T fragments (the B operand of S^T = K Q^T): thread (g, t) holds head g's dims t*2, t*2+1 (+8) of each
+  // 16-dim step.
+  uint32_t qf[NT][KSTEPS][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int head = nt * 8 + g;
+    const uint16_t *qrow = p.q + r * p.q_row_stride + (int64_t)(h * p.group + head) * p.q_head_stride;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      if (head < p.group) {
+        qf[nt][ks][0] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + t * 2);
+        qf[nt][ks][1] = *reinterpret_cast<const uint32_t *>(qrow + ks * 16 + t * 2 + 8);
+      } else {
+        qf[nt][ks][0] = qf[nt][ks][1] = 0u;
+      }
+    }
+  }
+
+  float o[NT][DH / 16][4];
+  float m_run[NT][2], l_run[NT][2];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.0f;
+#pragma unroll
+    for (int mt = 0; mt < DH / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
+  }
+
+  auto issue = [&](int tile) {
+    if (tile < tiles) {
+      const int stage = tile % kStages;
+      const int e = tile * kKeysPerTile + (lane & 15);
+      int32_t id = e < n ? list[e] : -1;
+      const bool ok = id >= 0 && id < p.slots;
+      const uint32_t valid = __ballot_sync(0xffffffffu, ok) & 0xFFFFu;
+      if (lane == 0) masks[stage] = valid;
+      const uint32_t k_dst = smem_base + stage * STAGE_BYTES;
+      const int chunk = lane % CHUNKS;
+#pragma unroll
+      for (int pass = 0; pass < PASSES; ++pass) {
+        const int row = lane / CHUNKS + pass * ROWS_PER_PASS;
+        const int32_t row_id = __shfl_sync(0xffffffffu, id, row);
+        const bool row_ok = (valid >> row) & 1u;
+        const int64_t off = row_ok ? (int64_t)row_id * p.kv_row_stride + chunk * 8 : 0;
+        const uint32_t dst = k_dst + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+        cp_async_16(dst, k_head + off, row_ok ? 16 : 0);
+        cp_async_16(dst + TILE_BYTES, v_head + off, row_ok ? 16 : 0);
+      }
+    }
+    cp_async_commit();
+  };
+
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue(s);
+
+  for (int tile = 0; tile < tiles; ++tile) {
+    issue(tile + kStages - 1);
+    cp_async_wait<kStages - 1>();
+    __syncwarp();
+    const int stage = tile % kStages;
+    const uint32_t k_src = smem_base + stage * STAGE_BYTES, v_src = k_src + TILE_BYTES;
+    const uint32_t valid = masks[stage];
+
+    // S^T [16 keys x 8 heads] = K [16 x DH] . Q^T
+    float s[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    {
+      const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int chunk = ks * 2 + (lane >> 4);
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4(k_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), a0, a1, a2, a3);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+      }
+    }
+
+    const bool ok_lo = (valid >> g) & 1u, ok_hi = (valid >> (g + 8)) & 1u;
+    uint32_t pb[NT][2];
+    bool rescale = false;
+    float alpha[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float x[4];
+      x[0] = ok_lo ? s[nt][0] * p.scale_log2 : -INFINITY;
+      x[1] = ok_lo ? s[nt][1] * p.scale_log2 : -INFINITY;
+      x[2] = ok_hi ? s[nt][2] * p.scale_log2 : -INFINITY;
+      x[3] = ok_hi ? s[nt][3] * p.scale_log2 : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float mx = fmaxf(x[j], x[2 + j]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_run[nt][j], mx);
+        const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
+        alpha[nt][j] = exp2f(m_run[nt][j] - m_safe);
+        rescale = rescale || (m_new != m_run[nt][j]);
+        m_run[nt][j] = m_new;
+        x[j] = exp2f(x[j] - m_safe);
+        x[2 + j] = exp2f(x[2 + j] - m_safe);
+        l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + (x[j] + x[2 + j]);
+      }
+      pb[nt][0] = movmatrix_trans(pack_bf16x2(x[0], x[1]));
+      pb[nt][1] = movmatrix_trans(pack_bf16x2(x[2], x[3]));
+    }
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int mt = 0; mt < DH / 16; ++mt) {
+          o[nt][mt][0] *= alpha[nt][0];
+          o[nt][mt][1] *= alpha[nt][1];
+          o[nt][mt][2] *= alpha[nt][0];
+          o[nt][mt][3] *= alpha[nt][1];
+        }
+    }
+
+    // O^T [DH x 8 heads] += V^T [DH x 16 keys] . P^T
+    {
+      const int row = (lane & 7) + (lane >> 4) * 8;
+#pragma unroll
+      for (int mt = 0; mt < DH / 16; ++mt) {
+        const int chunk = mt * 2 + ((lane >> 3) & 1);
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4_trans(v_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), a0, a1, a2, a3);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][mt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+      }
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+
+  // Finish: the row sums live per thread; add them over the eight key lanes of each head.
+  constexpr float kLn2 = 0.6931471805599453f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      float l = l_run[nt][j];
+      l += __shfl_xor_sync(0xffffffffu, l, 4);
+      l += __shfl_xor_sync(0xffffffffu, l, 8);
+      l += __shfl_xor_sync(0xffffffffu, l, 16);
+      const int head = nt * 8 + t * 2 + j;
+      if (head >= p.group) continue;
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      const float lse = l > 0.0f ? (m_run[nt][j] + log2f(l)) * kLn2 : -INFINITY;
+      const int64_t out_row = r * p.Hq + h * p.group + head;
+      if (p.splits > 1) {
+        float *dst = p.part_out + ((int64_t)split * p.R * p.Hq + out_row) * DH;
+#pragma unroll
+        for (int mt = 0; mt < DH / 16; ++mt) {
+          dst[mt * 16 + g] = o[nt][mt][j] * inv;
+          dst[mt * 16 + g + 8] = o[nt][mt][2 + j] * inv;
+        }
+        if (g == 0) p.part_lse[(int64_t)split * p.R * p.Hq + out_row] = lse;
+      } else {
+#pragma unroll
+        for (int mt = 0; mt < DH / 16; ++mt) {
+          const float lo = o[nt][mt][j] * inv, hi = o[nt][mt][2 + j] * inv;
+          if (p.out_bf16) {
+            p.out_bf16[out_row * DH + mt * 16 + g] = float_to_bf16_bits(lo);
+            p.out_bf16[out_row * DH + mt * 16 + g + 8] = float_to_bf16_bits(hi);
+          }
+          if (p.out_f32) {
+            p.out_f32[out_row * DH + mt * 16 + g] = lo;
+            p.out_f32[out_row * DH + mt * 16 + g + 8] = hi;
+          }
+        }
+        if (g == 0 && p.lse) p.lse[out_row] = lse;
+      }
+    }
+  }
+}
+
+// out = sum_p exp(lse_p - lse) out_p over `n_parts` partial results; a warp a row.
+__global__ void lse_merge_kernel(const float *__restrict__ parts, const float *__restrict__ lses, int n_parts,
+                                 int64_t rows, int dh, uint16_t *__restrict__ out_bf16, float *__restrict__ out_f32,
+                                 float *__restrict__ lse_out) {
+  const int lane = lane_id();
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float m = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) m = fmaxf(m, lses[(int64_t)i * rows + row]);
+  float total = -INFINITY;
+  if (m > -INFINITY) {
+    float l = 0.0f;
+    for (int i = 0; i < n_parts; ++i) l += expf(lses[(int64_t)i * rows + row] - m);
+    total = m + logf(l);
+  }
+  for (int c = lane; c < dh; c += 32) {
+    float acc = 0.0f;
+    if (m > -INFINITY)
+      for (int i = 0; i < n_parts; ++i) {
+        const float w = expf(lses[(int64_t)i * rows + row] - total);
+        acc = fmaf(w, parts[((int64_t)i * rows + row) * dh + c], acc);
+      }
+    if (out_bf16) out_bf16[row * dh + c] = float_to_bf16_bits(acc);
+    if (out_f32) out_f32[row * dh + c] = acc;
+  }
+  if (lane == 0 && lse_out) lse_out[row] = total;
+}
+
+template <int DH, int NT, int W>
+static int launch_attend(const AttendParams &p, cudaStream_t s) {
+  constexpr int WARP_BYTES = kStages * 2 * kKeysPerTile * DH * 2 + 16;
+  const size_t smem = (size_t)W * WARP_BYTES;
+  if (cudaFuncSetAttribute(sparse_attend_kernel<DH, NT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  const int64_t items = p.R * p.splits * p.Hkv;
+  const int64_t grid = (items + W - 1) / W;
+  if (grid > INT32_MAX) return LSA_ERR_ARGUMENT;
+  sparse_attend_kernel<DH, NT, W><<<(unsigned)grid, W * 32, smem, s>>>(p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+}  // namespace lsa
+
+// ================================================================================================ C ABI
+
+LSA_API size_t lsa_sparse_attend_workspace_bytes(int64_t R, int Hq, int dh, int splits) {
+  if (R <= 0 || Hq <= 0 || dh <= 0 || splits <= 1) return 0;
+  return (size_t)splits * R * Hq * (dh + 1) * sizeof(float);
+}
+
+LSA_API int lsa_lse_merge(const float *parts, const float *lses, int n_parts, int64_t rows, int dh,
+                          uint16_t *out_bf16, float *out_f32, float *lse_out, void *stream) {
+  LSA_REQUIRE(parts && lses && (out_bf16 || out_f32), LSA_ERR_NULL);
+  LSA_REQUIRE(n_parts >= 1 && rows >= 0 && dh >= 1, LSA_ERR_ARGUMENT);
+  if (rows == 0) return LSA_OK;
+  const int warps = 8;
+  lsa::lse_merge_kernel<<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream>>>(
+      parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
+                              int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv,
+                              int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
+                              const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
+                              float *lse, void *workspace, size_t workspace_bytes, void *stream) {
+  LSA_REQUIRE(q && k && v && ids && (out_bf16 || out_f32), LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && slots >= 0 && list_stride >= 0 && splits >= 1,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(dh == 64 || dh == 128, LSA_ERR_UNSUPPORTED);
+  const int group = Hq / Hkv;
+  LSA_REQUIRE(group <= 16, LSA_ERR_UNSUPPORTED);
+  // 16-byte copies of K/V rows and 4-byte reads of Q need these alignments
+  LSA_REQUIRE(kv_row_stride % 8 == 0 && kv_head_stride % 8 == 0 && ((uintptr_t)k % 16) == 0 &&
+                  ((uintptr_t)v % 16) == 0,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(q_row_stride % 2 == 0 && q_head_stride % 2 == 0 && ((uintptr_t)q % 4) == 0, LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  lsa::AttendParams p;
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.ids = ids;
+  p.lengths = lengths;
+  p.out_bf16 = out_bf16;
+  p.out_f32 = out_f32;
+  p.lse = lse;
+  p.part_out = nullptr;
+  p.part_lse = nullptr;
+  p.R = R;
+  p.slots = slots;
+  p.q_row_stride = q_row_stride;
+  p.q_head_stride = q_head_stride;
+  p.kv_row_stride = kv_row_stride;
+  p.kv_head_stride = kv_head_stride;
+  p.list_stride = list_stride;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.group = group;
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (splits > 1) {
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= lsa_sparse_attend_workspace_bytes(R, Hq, dh, splits), LSA_ERR_WORKSPACE);
+    p.part_out = (float *)workspace;
+    p.part_lse = p.part_out + (size_t)splits * R * Hq * dh;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  int rc;
+  if (dh == 128)
+    rc = group <= 8 ? lsa::launch_attend<128, 1, 8>(p, s) : lsa::launch_attend<128, 2, 8>(p, s);
+  else
+    rc = group <= 8 ? lsa::launch_attend<64, 1, 8>(p, s) : lsa::launch_attend<64, 2, 8>(p, s);
+  if (rc != LSA_OK || splits == 1) return rc;
+  return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dh, out_bf16, out_f32, lse, stream);
+}

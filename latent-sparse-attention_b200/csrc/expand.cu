@@ -1,0 +1,117 @@
+// Expansion: a row's picked buckets become its read list - members best bucket first, then the window, then
+// the sinks. Pure integer work, one warp a row, ballot-compacted so the order is the table's order.
+#include "common.cuh"
+
+namespace lsa {
+
+constexpr int kExpandWarps = 8;
+
+struct ExpandParams {
+  const int32_t *picked;      // [R, top_p]
+  const int64_t *positions;   // [R]
+  const int32_t *members;     // [m, cap]
+  const int32_t *row_top_p;   // [R] or NULL
+  const int32_t *row_top_k;   // [R] or NULL
+  const int32_t *page_table;  // [pages] or NULL
+  int32_t *selected;          // [R, width]
+  int32_t *lengths;           // [R]
+  int32_t *status;
+  int64_t R, m, owner_first, owner_end;
+  int top_p, cap, top_k, sink, window, page_size, width;
+};
+
+__device__ __forceinline__ int32_t stored_id(const ExpandParams &p, int64_t id) {
+  if (!p.page_table) return (int32_t)id;
+  return p.page_table[id / p.page_size] * p.page_size + (int32_t)(id % p.page_size);
+}
+
+__global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams p) {
+  const int lane = lane_id();
+  const int64_t r = (int64_t)blockIdx.x * kExpandWarps + (threadIdx.x >> 5);
+  if (r >= p.R) return;
+  const int64_t pos = p.positions[r];
+  const int row_p = p.row_top_p ? min(p.row_top_p[r], p.top_p) : p.top_p;
+  const int row_k = p.row_top_k ? min(p.row_top_k[r], p.top_k) : p.top_k;
+  const int64_t window_start = max((int64_t)0, pos + 1 - p.window);
+  int32_t *out = p.selected + r * p.width;
+  const unsigned below = (1u << lane) - 1;
+  int counted = 0;  // ids that count toward top_k
+  int written = 0;  // ids this owner keeps
+  int bad = 0;
+  for (int i = 0; i < row_p && counted < row_k; ++i) {
+    const int32_t bucket = p.picked[r * p.top_p + i];
+    if (bucket < 0) continue;
+    if (bucket >= p.m) {
+      ++bad;
+      continue;
+    }
+    const int32_t *row = p.members + (int64_t)bucket * p.cap;
+    for (int base = 0; base < p.cap && counted < row_k; base += 32) {
+      const int32_t id = base + lane < p.cap ? row[base + lane] : LSA_PAD;
+      const bool counts = id >= p.sink && id < window_start;
+      const unsigned votes = __ballot_sync(0xffffffffu, counts);
+      const bool inside = counts && counted + __popc(votes & below) < row_k;
+      const bool mine = inside && id >= p.owner_first && id < p.owner_end;
+      const unsigned keeps = __ballot_sync(0xffffffffu, mine);
+      if (mine) out[written + __popc(keeps & below)] = stored_id(p, id);
+      written += __popc(keeps);
+      counted += __popc(votes);
+      // Members are stored first, padding after: a chunk that ends in padding ends the bucket.
+      if (__ballot_sync(0xffffffffu, id < 0) & 0x80000000u) break;
+    }
+  }
+  // The window, ascending, then the sinks.
+  const int64_t w_first = max(window_start, p.owner_first), w_end = min(pos + 1, p.owner_end);
+  for (int64_t t = w_first + lane; t < w_end; t += 32) out[written + (int)(t - w_first)] = stored_id(p, t);
+  if (w_end > w_first) written += (int)(w_end - w_first);
+  const int64_t sinks = min((int64_t)p.sink, min(window_start, pos + 1));
+  const int64_t s_first = max((int64_t)0, p.owner_first), s_end = min(sinks, p.owner_end);
+  for (int64_t t = s_first + lane; t < s_end; t += 32) out[written + (int)(t - s_first)] = stored_id(p, t);
+  if (s_end > s_first) written += (int)(s_end - s_first);
+  for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
+  if (lane == 0) {
+    p.lengths[r] = written;
+    if (bad && p.status) atomicAdd(p.status, bad);
+  }
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
+                       const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
+                       const int32_t *row_top_k, int top_k, int sink, int window, const int32_t *page_table,
+                       int page_size, int64_t owner_first, int64_t owner_end, int32_t *selected, int32_t *lengths,
+                       int32_t *status, void *stream) {
+  LSA_REQUIRE(picked && positions && selected && lengths, LSA_ERR_NULL);
+  LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && top_p >= 1 && m >= 0 && bucket_cap >= 1 && top_k >= 1 && sink >= 0 && window >= 1,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!page_table || page_size >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE((int64_t)top_k + window + sink < INT32_MAX, LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  lsa::ExpandParams p;
+  p.picked = picked;
+  p.positions = positions;
+  p.members = members;
+  p.row_top_p = row_top_p;
+  p.row_top_k = row_top_k;
+  p.page_table = page_table;
+  p.selected = selected;
+  p.lengths = lengths;
+  p.status = status;
+  p.R = R;
+  p.m = m;
+  p.owner_first = owner_first;
+  p.owner_end = owner_end;
+  p.top_p = top_p;
+  p.cap = bucket_cap;
+  p.top_k = top_k;
+  p.sink = sink;
+  p.window = window;
+  p.page_size = page_size;
+  p.width = top_k + window + sink;
+  const unsigned grid = (unsigned)((R + lsa::kExpandWarps - 1) / lsa::kExpandWarps);
+  lsa::expand_kernel<<<grid, lsa::kExpandWarps * 32, 0, (cudaStream_t)stream>>>(p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}

@@ -1,0 +1,139 @@
+// Index space: grouped-query head sum, learned linear map and row normalisation in one pass over the heads.
+//
+// out[s] = normalize( sum_kv (sum_{g < group} x[s, kv*group + g, off : off + dh_used]) @ W[kv*dh_used : (kv+1)*dh_used] )
+// with fp32 accumulation in ascending input-dim order. This is the exact-arithmetic form; rows are read once and
+// the head sum never reaches memory.
+#include "common.cuh"
+
+namespace lsa {
+
+constexpr int kMapThreads = 256;
+constexpr int kMapRows = 64;    // rows a CTA maps, two a thread
+constexpr int kMapSlice = 64;   // input dims staged at a time
+constexpr int kMapMaxCols = 16; // output dims a thread holds (d_idx <= 128)
+
+template <typename TX, typename TW>
+__global__ void __launch_bounds__(kMapThreads)
+    index_map_kernel(const TX *__restrict__ x, int64_t rows, int heads, int group, int dh_off, int dh_used,
+                     int64_t x_row_stride, int64_t x_head_stride, const TW *__restrict__ W, int d_idx, int normalize,
+                     float *__restrict__ out_f32, uint16_t *__restrict__ out_bf16) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float *xs = reinterpret_cast<float *>(smem_raw);       // [kMapRows][kMapSlice + 1]
+  float *ws = xs + kMapRows * (kMapSlice + 1);           // [kMapSlice][d_idx]
+  const int tid = threadIdx.x;
+  const int row_a = tid >> 3, row_b = row_a + 32, cg = tid & 7;
+  const int64_t row0 = (int64_t)blockIdx.x * kMapRows;
+  const int d_in = heads / group * dh_used;
+  const int cols = (d_idx + 7) / 8;
+  float acc_a[kMapMaxCols], acc_b[kMapMaxCols];
+#pragma unroll
+  for (int i = 0; i < kMapMaxCols; ++i) acc_a[i] = acc_b[i] = 0.0f;
+
+  for (int k0 = 0; k0 < d_in; k0 += kMapSlice) {
+    const int kn = min(kMapSlice, d_in - k0);
+    for (int e = tid; e < kMapRows * kMapSlice; e += kMapThreads) {
+      const int rr = e / kMapSlice, kk = e - rr * kMapSlice;
+      float sum = 0.0f;
+      const int64_t r = row0 + rr;
+      if (r < rows && kk < kn) {
+        const int k = k0 + kk, kv = k / dh_used, c = k - kv * dh_used;
+        const TX *src = x + r * x_row_stride + (int64_t)kv * group * x_head_stride + dh_off + c;
+        for (int g = 0; g < group; ++g) sum = __fadd_rn(sum, load_as_float<TX>(src, (int64_t)g * x_head_stride));
+      }
+      xs[rr * (kMapSlice + 1) + kk] = sum;
+    }
+    for (int e = tid; e < kMapSlice * d_idx; e += kMapThreads) {
+      const int kk = e / d_idx, j = e - kk * d_idx;
+      float w = 0.0f;
+      if (kk < kn) w = W ? load_as_float<TW>(W, (int64_t)(k0 + kk) * d_idx + j) : (k0 + kk == j ? 1.0f : 0.0f);
+      ws[e] = w;
+    }
+    __syncthreads();
+    for (int kk = 0; kk < kn; ++kk) {
+      const float xa = xs[row_a * (kMapSlice + 1) + kk], xb = xs[row_b * (kMapSlice + 1) + kk];
+      const float *wrow = ws + kk * d_idx + cg;
+#pragma unroll
+      for (int i = 0; i < kMapMaxCols; ++i) {
+        if (i < cols) {
+          const float w = (cg + 8 * i) < d_idx ? wrow[8 * i] : 0.0f;
+          acc_a[i] = fmaf(xa, w, acc_a[i]);
+          acc_b[i] = fmaf(xb, w, acc_b[i]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  float ss_a = 0.0f, ss_b = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMapMaxCols; ++i) {
+    ss_a = fmaf(acc_a[i], acc_a[i], ss_a);
+    ss_b = fmaf(acc_b[i], acc_b[i], ss_b);
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1) {
+    ss_a += __shfl_xor_sync(0xffffffffu, ss_a, o);
+    ss_b += __shfl_xor_sync(0xffffffffu, ss_b, o);
+  }
+  const float den_a = normalize ? fmaxf(sqrtf(ss_a), 1e-12f) : 1.0f;
+  const float den_b = normalize ? fmaxf(sqrtf(ss_b), 1e-12f) : 1.0f;
+#pragma unroll
+  for (int i = 0; i < kMapMaxCols; ++i) {
+    const int j = cg + 8 * i;
+    if (i >= cols || j >= d_idx) continue;
+    if (row0 + row_a < rows) {
+      const float v = acc_a[i] / den_a;
+      if (out_f32) out_f32[(row0 + row_a) * d_idx + j] = v;
+      if (out_bf16) out_bf16[(row0 + row_a) * d_idx + j] = float_to_bf16_bits(v);
+    }
+    if (row0 + row_b < rows) {
+      const float v = acc_b[i] / den_b;
+      if (out_f32) out_f32[(row0 + row_b) * d_idx + j] = v;
+      if (out_bf16) out_bf16[(row0 + row_b) * d_idx + j] = float_to_bf16_bits(v);
+    }
+  }
+}
+
+template <typename TX, typename TW>
+static int launch_index_map(const void *x, int64_t rows, int heads, int group, int dh_off, int dh_used,
+                            int64_t x_row_stride, int64_t x_head_stride, const void *W, int d_idx, int normalize,
+                            float *out_f32, uint16_t *out_bf16, cudaStream_t s) {
+  const size_t smem = sizeof(float) * ((size_t)kMapRows * (kMapSlice + 1) + (size_t)kMapSlice * d_idx);
+  if (cudaFuncSetAttribute(index_map_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  const unsigned grid = (unsigned)((rows + kMapRows - 1) / kMapRows);
+  index_map_kernel<TX, TW><<<grid, kMapThreads, smem, s>>>((const TX *)x, rows, heads, group, dh_off, dh_used,
+                                                            x_row_stride, x_head_stride, (const TW *)W, d_idx,
+                                                            normalize, out_f32, out_bf16);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group, int dh_off, int dh_used,
+                          int64_t x_row_stride, int64_t x_head_stride, const void *W, int w_dtype, int d_idx,
+                          int normalize, float *out_f32, uint16_t *out_bf16, void *stream) {
+  LSA_REQUIRE(x && (out_f32 || out_bf16), LSA_ERR_NULL);
+  LSA_REQUIRE(rows >= 0 && heads >= 1 && group >= 1 && heads % group == 0 && dh_off >= 0 && dh_used >= 1 &&
+                  d_idx >= 1,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(x_dtype == LSA_DTYPE_F32 || x_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(w_dtype == LSA_DTYPE_F32 || w_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(W || d_idx == heads / group * dh_used, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(d_idx <= 8 * lsa::kMapMaxCols, LSA_ERR_UNSUPPORTED);
+  if (rows == 0) return LSA_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (x_dtype == LSA_DTYPE_BF16 && w_dtype == LSA_DTYPE_BF16)
+    return lsa::launch_index_map<uint16_t, uint16_t>(x, rows, heads, group, dh_off, dh_used, x_row_stride,
+                                                     x_head_stride, W, d_idx, normalize, out_f32, out_bf16, s);
+  if (x_dtype == LSA_DTYPE_BF16)
+    return lsa::launch_index_map<uint16_t, float>(x, rows, heads, group, dh_off, dh_used, x_row_stride,
+                                                  x_head_stride, W, d_idx, normalize, out_f32, out_bf16, s);
+  if (w_dtype == LSA_DTYPE_BF16)
+    return lsa::launch_index_map<float, uint16_t>(x, rows, heads, group, dh_off, dh_used, x_row_stride,
+                                                  x_head_stride, W, d_idx, normalize, out_f32, out_bf16, s);
+  return lsa::launch_index_map<float, float>(x, rows, heads, group, dh_off, dh_used, x_row_stride, x_head_stride, W,
+                                             d_idx, normalize, out_f32, out_bf16, s);
+}

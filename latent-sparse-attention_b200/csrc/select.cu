@@ -1,0 +1,451 @@
+// Bucket search: score candidates with a fixed-order fp32 dot, keep each row's best as packed int64 keys.
+//
+// One kernel serves the flat prefill scan (eight rows a CTA share every centroid they load), the flat decode
+// scan (one row, its buckets split over CTAs, lists merged afterwards) and a beam step of the tree (one row,
+// carried children beside a run of open rows). Selection is exact: a streaming top-k over 64-bit keys whose low
+// word breaks a score tie toward the lower id, so the result does not depend on the order keys were produced in.
+#include "common.cuh"
+
+namespace lsa {
+
+constexpr int kSelThreads = 256;
+constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kHistBins = 256;
+
+// ---------------------------------------------------------------------------------------- warp-level top-k
+
+// The k-th greatest of buf[0..n) (n > k >= 1, keys distinct), found by eight 8-bit radix passes of one warp.
+// hist is 256 ints of warp-private shared memory.
+__device__ uint64_t warp_kth_greatest(const int64_t *buf, int n, int k, int *hist) {
+  const int lane = lane_id();
+  uint64_t prefix = 0, mask = 0;
+  int remaining = k;
+  for (int byte = 7; byte >= 0; --byte) {
+    const int shift = byte * 8;
+#pragma unroll
+    for (int i = 0; i < kHistBins / 32; ++i) hist[lane * (kHistBins / 32) + i] = 0;
+    __syncwarp();
+    for (int i = lane; i < n; i += 32) {
+      const uint64_t u = key_radix(buf[i]);
+      if ((u & mask) == prefix) atomicAdd(&hist[(int)((u >> shift) & 0xFF)], 1);
+    }
+    __syncwarp();
+    // Lane l owns bins 8l..8l+7; `above` counts the keys in bins over this lane's.
+    int own[kHistBins / 32];
+    int own_sum = 0;
+#pragma unroll
+    for (int i = 0; i < kHistBins / 32; ++i) {
+      own[i] = hist[lane * (kHistBins / 32) + i];
+      own_sum += own[i];
+    }
+    int above = own_sum;  // inclusive suffix sum over lanes, then made exclusive
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int other = __shfl_down_sync(0xffffffffu, above, o);
+      if (lane + o < 32) above += other;
+    }
+    above -= own_sum;
+    const bool here = above < remaining && above + own_sum >= remaining;
+    const unsigned who = __ballot_sync(0xffffffffu, here);
+    const int src = __ffs(who) - 1;
+    int digit = 0, next_remaining = remaining;
+    if (here) {
+      int seen = above;
+#pragma unroll
+      for (int i = kHistBins / 32 - 1; i >= 0; --i) {
+        if (seen < remaining && seen + own[i] >= remaining) {
+          digit = lane * (kHistBins / 32) + i;
+          next_remaining = remaining - seen;
+        }
+        seen += own[i];
+      }
+    }
+    digit = __shfl_sync(0xffffffffu, digit, src);
+    remaining = __shfl_sync(0xffffffffu, next_remaining, src);
+    prefix |= (uint64_t)digit << shift;
+    mask |= (uint64_t)0xFF << shift;
+    __syncwarp();
+  }
+  return prefix;
+}
+
+// Move the entries of buf[from..to) that pass `keep(key)` down to buf[out..), in order; returns the new end.
+template <typename Pred>
+__device__ int warp_compact(int64_t *buf, int from, int to, int out, Pred keep) {
+  const int lane = lane_id();
+  for (int base = from; base < to; base += 32) {
+    const int i = base + lane;
+    const int64_t key = i < to ? buf[i] : kEmptyKey;
+    const bool pass = i < to && keep(key);
+    const unsigned votes = __ballot_sync(0xffffffffu, pass);
+    __syncwarp();
+    if (pass) buf[out + __popc(votes & ((1u << lane) - 1))] = key;
+    out += __popc(votes);
+    __syncwarp();
+  }
+  return out;
+}
+
+// Sort buf[0..n) descending in place with one warp; buf has room for the next power of two of n.
+__device__ void warp_sort_descending(int64_t *buf, int n) {
+  const int lane = lane_id();
+  int size = 1;
+  while (size < n) size <<= 1;
+  for (int i = n + lane; i < size; i += 32) buf[i] = kEmptyKey;
+  __syncwarp();
+  for (int span = 2; span <= size; span <<= 1) {
+    for (int stride = span >> 1; stride > 0; stride >>= 1) {
+      for (int t = lane; t < (size >> 1); t += 32) {
+        const int i = ((t & ~(stride - 1)) << 1) | (t & (stride - 1));
+        const int j = i | stride;
+        const bool descending = (i & span) == 0;
+        const int64_t a = buf[i], b = buf[j];
+        if ((a < b) == descending) {
+          buf[i] = b;
+          buf[j] = a;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------- the kernel
+
+struct SelectParams {
+  const float *queries;         // [R, d]
+  const float *vectors;         // [N, d]
+  const int64_t *vector_base;   // [R] first row of `vectors` a row's ids are relative to, or NULL
+  const int32_t *run_first;     // [R] first id of the contiguous run a row scores, or NULL for 0
+  const int32_t *run_end;       // [R] end of that run
+  const int32_t *carried;       // [R, n_carried] explicit candidate ids (-1 = none) scored before the run, or NULL
+  const int32_t *row_keep;      // [R] a row's own keep (<= keep), or NULL
+  const int64_t *children;      // [N, fanout] or NULL
+  int64_t *keys_out;            // [splits, R, keep] or NULL
+  int32_t *ids_out;             // [splits, R, keep] or NULL
+  int32_t *carried_out;         // [R, keep * fanout] or NULL
+  int64_t R, N;
+  int d, n_carried, keep, fanout, id_base, chunk, run_limit;
+};
+
+// RB rows a CTA. Shared memory: queries [RB][d], per-row key buffers [RB][keep_pow2 + chunk], histograms.
+template <int RB>
+__global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int keep_room = 2;  // even, so the float4 reads of the queries behind the buffers stay 16-byte aligned
+  while (keep_room < p.keep) keep_room <<= 1;
+  const int row_room = keep_room + p.chunk;
+  int64_t *bufs = reinterpret_cast<int64_t *>(smem_raw);               // [RB][row_room]
+  float *qs = reinterpret_cast<float *>(bufs + (size_t)RB * row_room);  // [RB][d]
+  int *hists = reinterpret_cast<int *>(qs + RB * p.d);                  // [RB][256]
+  __shared__ int total_s[RB], first_s[RB], end_s[RB];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t row0 = (int64_t)blockIdx.x * RB;
+  const int splits = gridDim.y, split = blockIdx.y;
+
+  for (int e = tid; e < RB * p.d; e += kSelThreads) {
+    const int64_t r = row0 + e / p.d;
+    qs[e] = r < p.R ? p.queries[r * p.d + e % p.d] : 0.0f;
+  }
+  if (tid < RB) {
+    const int64_t r = row0 + tid;
+    int first = 0, end = 0;
+    if (r < p.R) {
+      first = p.run_first ? p.run_first[r] : 0;
+      end = p.run_end ? p.run_end[r] : 0;
+      if (end > p.run_limit) end = p.run_limit;
+      if (end < first) end = first;
+    }
+    first_s[tid] = first;
+    end_s[tid] = end;
+    total_s[tid] = r < p.R ? p.n_carried + (end - first) : 0;
+  }
+  __syncthreads();
+  int max_total = 0;
+#pragma unroll
+  for (int i = 0; i < RB; ++i) max_total = max(max_total, total_s[i]);
+  // This CTA's share of the candidate range, the same cut for every row it holds.
+  const int per_split = (max_total + splits - 1) / splits;
+  const int cand_begin = split * per_split;
+  const int cand_end = min(max_total, cand_begin + per_split);
+
+  // Per-row selection state, held by the row's warp.
+  int held = 0;                 // keys held at the front of the row's buffer
+  int64_t floor_key = kEmptyKey;  // a new key must beat this once the row holds its keep
+  const int64_t my_row = row0 + warp;
+  const int my_keep = (warp < RB && my_row < p.R) ? (p.row_keep ? min(p.row_keep[my_row], p.keep) : p.keep) : 0;
+
+  for (int chunk_base = cand_begin; chunk_base < cand_end; chunk_base += p.chunk) {
+    const int chunk_n = min(p.chunk, cand_end - chunk_base);
+    // ---- score: a thread a candidate, every row of the CTA against it
+    for (int t = tid; t < chunk_n; t += kSelThreads) {
+      const int c = chunk_base + t;
+      float acc[RB];
+      int64_t vec_row[RB];
+      int32_t ids[RB];
+      bool same = true;
+#pragma unroll
+      for (int i = 0; i < RB; ++i) {
+        const int64_t r = row0 + i;
+        int32_t id = -1;
+        if (r < p.R && c < total_s[i])
+          id = c < p.n_carried ? p.carried[r * p.n_carried + c] : first_s[i] + (c - p.n_carried);
+        ids[i] = id;
+        vec_row[i] = id >= 0 ? (p.vector_base ? p.vector_base[r] : 0) + id : -1;
+        if (vec_row[i] >= p.N) vec_row[i] = -1, ids[i] = -1;
+        acc[i] = 0.0f;
+        same = same && (vec_row[i] == vec_row[0] || vec_row[i] < 0 || vec_row[0] < 0);
+      }
+      if (RB > 1 && same) {
+        // Every row of the CTA scores the same vector: load it once.
+        int64_t row = -1;
+#pragma unroll
+        for (int i = 0; i < RB; ++i)
+          if (vec_row[i] >= 0) row = vec_row[i];
+        if (row >= 0) {
+          const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + row * p.d);
+          for (int k4 = 0; k4 < p.d / 4; ++k4) {
+            const float4 v = __ldg(v4 + k4);
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+              const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
+              acc[i] = fmaf(q.x, v.x, acc[i]);
+              acc[i] = fmaf(q.y, v.y, acc[i]);
+              acc[i] = fmaf(q.z, v.z, acc[i]);
+              acc[i] = fmaf(q.w, v.w, acc[i]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          if (vec_row[i] < 0) continue;
+          const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + vec_row[i] * p.d);
+          for (int k4 = 0; k4 < p.d / 4; ++k4) {
+            const float4 v = __ldg(v4 + k4);
+            const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
+            acc[i] = fmaf(q.x, v.x, acc[i]);
+            acc[i] = fmaf(q.y, v.y, acc[i]);
+            acc[i] = fmaf(q.z, v.z, acc[i]);
+            acc[i] = fmaf(q.w, v.w, acc[i]);
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < RB; ++i)
+        bufs[(size_t)i * row_room + keep_room + t] = ids[i] >= 0 ? pack_key(acc[i], ids[i] + p.id_base) : kEmptyKey;
+    }
+    __syncthreads();
+    // ---- select: the row's warp folds the chunk into what it holds
+    if (warp < RB && my_keep > 0) {
+      int64_t *buf = bufs + (size_t)warp * row_room;
+      const int64_t floor_now = floor_key;
+      // Survivors land right after the held keys; room is never short because held <= keep_room.
+      int n = warp_compact(buf, keep_room, keep_room + chunk_n, held,
+                           [floor_now](int64_t key) { return key > floor_now; });
+      if (n > my_keep) {
+        const uint64_t kth = warp_kth_greatest(buf, n, my_keep, hists + warp * kHistBins);
+        n = warp_compact(buf, 0, n, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+        floor_key = (int64_t)(kth ^ 0x8000000000000000ull);
+      }
+      held = n;
+    }
+    __syncthreads();
+  }
+
+  if (warp < RB && my_row < p.R) {
+    int64_t *buf = bufs + (size_t)warp * row_room;
+    warp_sort_descending(buf, held);
+    const int64_t out_row = ((int64_t)split * p.R + my_row) * p.keep;
+    for (int i = lane; i < p.keep; i += 32) {
+      const int64_t key = i < held ? buf[i] : kEmptyKey;
+      if (p.keys_out) p.keys_out[out_row + i] = key;
+      if (p.ids_out) p.ids_out[out_row + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+    }
+    if (p.carried_out) {
+      const int total = p.keep * p.fanout;
+      for (int e = lane; e < total; e += 32) {
+        const int i = e / p.fanout, c = e - i * p.fanout;
+        int32_t child = LSA_PAD;
+        if (i < held) child = (int32_t)p.children[(int64_t)(key_id(buf[i]) - p.id_base) * p.fanout + c];
+        p.carried_out[my_row * total + e] = child;
+      }
+    }
+  }
+}
+
+// Global top-k of `parts` lists of packed keys, a warp a row.
+__global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__restrict__ keys_in, int parts,
+                                                              int64_t R, int keep, int room,
+                                                              int64_t *__restrict__ keys_out,
+                                                              int32_t *__restrict__ ids_out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int64_t *buf = reinterpret_cast<int64_t *>(smem_raw);  // [room]
+  int *hist = reinterpret_cast<int *>(buf + room);        // [256]
+  const int lane = lane_id();
+  const int64_t r = blockIdx.x;
+  int n = 0;
+  for (int base = 0; base < parts * keep; base += 32) {
+    const int e = base + lane;
+    int64_t key = kEmptyKey;
+    if (e < parts * keep) key = keys_in[((int64_t)(e / keep) * R + r) * keep + e % keep];
+    const bool pass = key != kEmptyKey;
+    const unsigned votes = __ballot_sync(0xffffffffu, pass);
+    if (pass) buf[n + __popc(votes & ((1u << lane) - 1))] = key;
+    n += __popc(votes);
+  }
+  __syncwarp();
+  if (n > keep) {
+    const uint64_t kth = warp_kth_greatest(buf, n, keep, hist);
+    n = warp_compact(buf, 0, n, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+  }
+  warp_sort_descending(buf, n);
+  for (int i = lane; i < keep; i += 32) {
+    const int64_t key = i < n ? buf[i] : kEmptyKey;
+    keys_out[r * keep + i] = key;
+    if (ids_out) ids_out[r * keep + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+  }
+}
+
+static int pow2_at_least(int n) {
+  int v = 2;
+  while (v < n) v <<= 1;
+  return v;
+}
+
+// Chunk of candidates a pass scores: as many as shared memory holds beside the held keys, at most 2048.
+static int select_chunk(int rb, int keep, int d, size_t *smem_out) {
+  const size_t budget = 200 * 1024;
+  const size_t fixed = (size_t)rb * (pow2_at_least(keep) * 8 + d * 4 + kHistBins * 4);
+  int chunk = 2048;
+  while (chunk > 256 && fixed + (size_t)rb * chunk * 8 > budget) chunk -= 256;
+  if (fixed + (size_t)rb * chunk * 8 > budget) return 0;
+  *smem_out = fixed + (size_t)rb * chunk * 8;
+  return chunk;
+}
+
+template <int RB>
+static int launch_select(SelectParams p, int splits, cudaStream_t s) {
+  size_t smem = 0;
+  p.chunk = select_chunk(RB, p.keep, p.d, &smem);
+  if (p.chunk == 0) return LSA_ERR_UNSUPPORTED;
+  if (cudaFuncSetAttribute(select_kernel<RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  dim3 grid((unsigned)((p.R + RB - 1) / RB), (unsigned)splits);
+  select_kernel<RB><<<grid, kSelThreads, smem, s>>>(p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+}  // namespace lsa
+
+// ================================================================================================ C ABI
+
+LSA_API int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,
+                            const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                            int64_t *keys_out, int32_t *picked_out, void *stream) {
+  LSA_REQUIRE(queries && centroids && visible && (keys_out || picked_out), LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && m >= 0 && top_p >= 1 && m < INT32_MAX, LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  lsa::SelectParams p = {};
+  p.queries = queries;
+  p.vectors = centroids;
+  p.run_end = visible;
+  p.row_keep = row_top_p;
+  p.keys_out = keys_out;
+  p.ids_out = picked_out;
+  p.R = R;
+  p.N = m;
+  p.d = d;
+  p.keep = top_p;
+  p.id_base = bucket_id_base;
+  p.run_limit = (int)m;
+  return lsa::launch_select<8>(p, 1, (cudaStream_t)stream);
+}
+
+LSA_API size_t lsa_flat_select_decode_workspace_bytes(int64_t R, int top_p, int splits) {
+  if (R <= 0 || top_p <= 0 || splits <= 1) return 0;
+  return (size_t)R * top_p * splits * sizeof(int64_t);
+}
+
+LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out,
+                                 int32_t *picked_out, void *stream) {
+  LSA_REQUIRE(keys_in && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(parts >= 1 && R >= 0 && top_p >= 1, LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  const int room = lsa::pow2_at_least(parts * top_p);
+  const size_t smem = (size_t)room * 8 + lsa::kHistBins * 4;
+  LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
+  if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  lsa::merge_candidates_kernel<<<(unsigned)R, 32, smem, (cudaStream_t)stream>>>(keys_in, parts, R, top_p, room,
+                                                                                keys_out, picked_out);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+LSA_API int lsa_flat_select_decode(const float *queries, int64_t R, int d, const float *centroids,
+                                   const int64_t *request_first, const int32_t *visible, int top_p, int splits,
+                                   int64_t *keys_out, int32_t *picked_out, void *workspace, size_t workspace_bytes,
+                                   void *stream) {
+  LSA_REQUIRE(queries && centroids && visible && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && top_p >= 1 && splits >= 1 && splits <= 1024, LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  if (splits > 1) {
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= lsa_flat_select_decode_workspace_bytes(R, top_p, splits), LSA_ERR_WORKSPACE);
+  }
+  lsa::SelectParams p = {};
+  p.queries = queries;
+  p.vectors = centroids;
+  p.vector_base = request_first;
+  p.run_end = visible;
+  p.R = R;
+  p.N = INT64_MAX;
+  p.d = d;
+  p.keep = top_p;
+  p.run_limit = INT32_MAX;
+  if (splits == 1) {
+    p.keys_out = keys_out;
+    p.ids_out = picked_out;
+    return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+  }
+  p.keys_out = (int64_t *)workspace;
+  int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
+  if (rc != LSA_OK) return rc;
+  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+}
+
+LSA_API int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, int64_t N,
+                          const int32_t *carried, int n_carried, const int32_t *open_first,
+                          const int32_t *open_end, int keep, const int64_t *children, int fanout,
+                          int32_t *kept_out, int64_t *keys_out, int32_t *carried_out, void *stream) {
+  LSA_REQUIRE(queries && vectors, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && N >= 0 && N < INT32_MAX && keep >= 1 && n_carried >= 0,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(n_carried == 0 || carried, LSA_ERR_NULL);
+  LSA_REQUIRE((children != nullptr) == (carried_out != nullptr), LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!children || fanout >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(kept_out || keys_out || carried_out, LSA_ERR_NULL);
+  if (R == 0) return LSA_OK;
+  lsa::SelectParams p = {};
+  p.queries = queries;
+  p.vectors = vectors;
+  p.run_first = open_first;
+  p.run_end = open_end;
+  p.carried = carried;
+  p.children = children;
+  p.keys_out = keys_out;
+  p.ids_out = kept_out;
+  p.carried_out = carried_out;
+  p.R = R;
+  p.N = N;
+  p.d = d;
+  p.n_carried = n_carried;
+  p.keep = keep;
+  p.fanout = fanout;
+  p.run_limit = (int)N;
+  return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+}

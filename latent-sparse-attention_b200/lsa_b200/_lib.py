@@ -1,0 +1,104 @@
+"""ctypes binding of `liblsa_b200.so`, the C-ABI library of sm_100a kernels.
+
+There is no CPU path: if the library is missing or the tensors are not on a CUDA device, every call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
+ABI_VERSION = 1
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+PAD = -1
+EMPTY_KEY = -(2**63)
+INT64_MAX = 2**63 - 1
+
+_P, _I, _L, _F, _Z = c_void_p, c_int, c_int64, c_float, c_size_t
+
+# name -> (restype, argtypes); kept in the order of include/lsa_b200.h
+SIGNATURES = {
+    "lsa_error_string": (ctypes.c_char_p, [_I]),
+    "lsa_abi_version": (_I, []),
+    "lsa_index_map": (_I, [_P, _I, _L, _I, _I, _I, _I, _L, _L, _P, _I, _I, _I, _P, _P, _P]),
+    "lsa_pool_keys": (_I, [_P, _I, _L, _I, _I, _P, _P]),
+    "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P]),
+    "lsa_bucket_table": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),
+    "lsa_flat_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _I, c_int32, _P, _P, _P]),
+    "lsa_flat_select_decode_workspace_bytes": (_Z, [_L, _I, _I]),
+    "lsa_flat_select_decode": (_I, [_P, _L, _I, _P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
+    "lsa_merge_candidates": (_I, [_P, _I, _L, _I, _P, _P, _P]),
+    "lsa_beam_step": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P]),
+    "lsa_expand": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I, _P, _I, _L, _L, _P, _P, _P, _P]),
+    "lsa_sparse_attend_workspace_bytes": (_Z, [_L, _I, _I, _I]),
+    "lsa_sparse_attend": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _I, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P, _P,
+                               _Z, _P]),
+    "lsa_lse_merge": (_I, [_P, _P, _I, _L, _I, _P, _P, _P, _P]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the kernel library, or raise: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"lsa_b200: the CUDA kernel library {LIB_PATH} is not built - run "
+                "`python latent-sparse-attention_b200/build.py` (there is no CPU fallback)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        if lib.lsa_abi_version() != ABI_VERSION:
+            raise RuntimeError(f"lsa_b200: {LIB_PATH} has ABI {lib.lsa_abi_version()}, the binding wants {ABI_VERSION}")
+        _lib = lib
+    return _lib
+
+
+def ptr(tensor: torch.Tensor | None) -> int | None:
+    """Device address of a tensor (None passes NULL). Refuses anything that is not CUDA memory."""
+    if tensor is None:
+        return None
+    if not tensor.is_cuda:
+        raise RuntimeError("lsa_b200 kernels take CUDA tensors only - there is no CPU path")
+    return tensor.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(tensor: torch.Tensor) -> int:
+    if tensor.dtype == torch.float32:
+        return DTYPE_F32
+    if tensor.dtype == torch.bfloat16:
+        return DTYPE_BF16
+    raise ValueError(f"expected float32 or bfloat16 - got {tensor.dtype}")
+
+
+# Kernel launches made through this binding since import (a benchmark reads it before and after a step).
+LAUNCHES = 0
+
+
+def call(name: str, *args, launches: int = 1):
+    """Call an entry point that returns a status code; raise on a refusal."""
+    global LAUNCHES
+    code = getattr(load(), name)(*args)
+    LAUNCHES += launches
+    if code != 0:
+        reason = load().lsa_error_string(code).decode()
+        kind = ValueError if code in (-1, -2, -3, -4) else RuntimeError
+        raise kind(f"{name} refused the call: {reason} (code {code})")
+
+
+def query(name: str, *args) -> int:
+    """Call a size query."""
+    return int(getattr(load(), name)(*args))

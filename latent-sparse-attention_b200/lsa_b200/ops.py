@@ -1,0 +1,226 @@
+"""Tensor-level wrappers of the C-ABI kernels: they check shapes and dtypes, allocate outputs with torch, and
+launch on the current CUDA stream. Each names the reference function it stands in for.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from lsa_b200 import _lib
+from lsa_b200._lib import call, ptr, query, stream
+
+
+def _contig(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def index_map(x: torch.Tensor, index_map_weight: torch.Tensor | None, group: int = 1, dh_off: int = 0,
+              dh_used: int | None = None, normalize: bool = True, out_dtype: torch.dtype = torch.float32,
+              also_bf16: bool = False):
+    """Head sum, learned map and normalisation: x [rows, heads, dh] -> [rows, d_idx].
+
+    Stands in for `project(regroup(...))` (src/lsa/core/index_space.py:110-131, 405-419). `x` may be a strided
+    view whose last dim is contiguous.
+    """
+    if x.dim() != 3 or x.stride(2) != 1:
+        raise ValueError(f"x must be [rows, heads, dh] with a contiguous last dim - got {tuple(x.shape)}")
+    rows, heads, dh = x.shape
+    dh_used = dh - dh_off if dh_used is None else dh_used
+    if dh_off + dh_used > dh or heads % group:
+        raise ValueError("the head dims read must lie inside the head, and the heads must group evenly")
+    d_in = heads // group * dh_used
+    w = None
+    if index_map_weight is not None:
+        w = _contig(index_map_weight)
+        if w.dim() != 2 or w.shape[0] != d_in:
+            raise ValueError(f"rows have {d_in} dims and the map reads {w.shape[0] if w.dim() == 2 else w.shape}")
+    d_idx = w.shape[1] if w is not None else d_in
+    out_f32 = torch.empty(rows, d_idx, device=x.device, dtype=torch.float32) if out_dtype == torch.float32 else None
+    want_bf16 = also_bf16 or out_dtype == torch.bfloat16
+    out_bf16 = torch.empty(rows, d_idx, device=x.device, dtype=torch.bfloat16) if want_bf16 else None
+    call("lsa_index_map", ptr(x), _lib.dtype_code(x), rows, heads, group, dh_off, dh_used, x.stride(0), x.stride(1),
+         ptr(w), _lib.dtype_code(w) if w is not None else 0, d_idx, int(normalize), ptr(out_f32), ptr(out_bf16),
+         stream())
+    if out_dtype == torch.float32:
+        return (out_f32, out_bf16) if also_bf16 else out_f32
+    return out_bf16
+
+
+def pool_keys(index_keys: torch.Tensor, pool_size: int) -> torch.Tensor:
+    """`pool_keys` (src/lsa/core/ward.py:15-26): [..., T, d] -> [..., T / pool_size, d] fp32."""
+    keys = _contig(index_keys)
+    T, d = keys.shape[-2], keys.shape[-1]
+    if T % pool_size:
+        raise ValueError(f"{T} keys do not split into pools of {pool_size}")
+    out = torch.empty(*keys.shape[:-2], T // pool_size, d, device=keys.device, dtype=torch.float32)
+    call("lsa_pool_keys", ptr(keys), _lib.dtype_code(keys), out.numel() // d, pool_size, d, ptr(out), stream())
+    return out
+
+
+def ward_rounds(pools: torch.Tensor, pool_sizes: torch.Tensor | float, bucket_count: int, bucket_cap: float,
+                max_rounds: int = 256, return_rounds: bool = False):
+    """`ward_rounds` (src/lsa/core/ward.py:29-90): labels [G, P] int64 and whether each block reached its count."""
+    pools = _contig(pools)
+    if pools.dim() != 3 or pools.dtype != torch.float32:
+        raise ValueError(f"pool keys must be [G, P, index_dim] float32 - got {tuple(pools.shape)} {pools.dtype}")
+    G, P, d = pools.shape
+    sizes, uniform = None, 0.0
+    if isinstance(pool_sizes, torch.Tensor):
+        sizes = _contig(pool_sizes.to(torch.float32))
+        if sizes.shape != (G, P):
+            raise ValueError(f"pool sizes must be [{G}, {P}] - got {tuple(sizes.shape)}")
+    else:
+        uniform = float(pool_sizes)
+    labels = torch.empty(G, P, device=pools.device, dtype=torch.int64)
+    reached = torch.empty(G, device=pools.device, dtype=torch.uint8)
+    rounds = torch.empty(G, device=pools.device, dtype=torch.int32) if return_rounds else None
+    call("lsa_ward_merge", ptr(pools), ptr(sizes), uniform, G, P, d, bucket_count, float(bucket_cap), max_rounds,
+         ptr(labels), ptr(reached), ptr(rounds), stream())
+    if return_rounds:
+        return labels, reached.bool(), rounds
+    return labels, reached.bool()
+
+
+def bucket_table(index_keys: torch.Tensor, labels: torch.Tensor, pool_size: int, bucket_count: int,
+                 bucket_cap: int, first_position: int = 0, want_bf16: bool = False):
+    """Members, sizes, key sums and centroids of every block (src/lsa/core/reference.py:120-144)."""
+    keys, labels = _contig(index_keys), _contig(labels)
+    G, P = labels.shape
+    d = keys.shape[-1]
+    rows = G * bucket_count
+    members = torch.empty(rows, bucket_cap, device=keys.device, dtype=torch.int32)
+    sizes = torch.empty(rows, device=keys.device, dtype=torch.int32)
+    key_sums = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
+    centroids = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
+    centroids_bf16 = torch.empty(rows, d, device=keys.device, dtype=torch.bfloat16) if want_bf16 else None
+    status = torch.zeros(1, device=keys.device, dtype=torch.int32)
+    call("lsa_bucket_table", ptr(keys), _lib.dtype_code(keys), ptr(labels), G, P, pool_size, d, bucket_count,
+         bucket_cap, first_position, ptr(members), ptr(sizes), ptr(key_sums), ptr(centroids), ptr(centroids_bf16),
+         ptr(status), stream())
+    return members, sizes, key_sums, centroids, centroids_bf16, status
+
+
+def bucket_members(labels: torch.Tensor, pool_size: int, bucket_count: int, bucket_cap: int,
+                   first_position: int = 0):
+    """The member table alone (src/lsa/core/ward.py:128-143): (members [G*bucket_count, cap], sizes)."""
+    labels = _contig(labels)
+    G, P = labels.shape
+    members = torch.empty(G * bucket_count, bucket_cap, device=labels.device, dtype=torch.int32)
+    sizes = torch.empty(G * bucket_count, device=labels.device, dtype=torch.int32)
+    call("lsa_bucket_table", None, 0, ptr(labels), G, P, pool_size, 1, bucket_count, bucket_cap, first_position,
+         ptr(members), ptr(sizes), None, None, None, None, stream())
+    return members, sizes
+
+
+def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: torch.Tensor, top_p: int,
+                row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0):
+    """Top-p packed keys and bucket ids of every row (src/lsa/core/reference.py:228-265)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    call("lsa_flat_select", ptr(q), R, d, ptr(c), c.shape[0], ptr(_contig(visible.to(torch.int32))),
+         ptr(row_top_p), top_p, bucket_id_base, ptr(keys), ptr(picked), stream())
+    return keys, picked
+
+
+def flat_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, request_first: torch.Tensor | None,
+                       visible: torch.Tensor, top_p: int, splits: int = 1, workspace: torch.Tensor | None = None):
+    """Decode-form flat scan (src/lsa/sglang/index/selector.py:603-660): few rows, their buckets split over CTAs."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    need = query("lsa_flat_select_decode_workspace_bytes", R, top_p, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_flat_select_decode", ptr(q), R, d, ptr(c), ptr(request_first), ptr(_contig(visible.to(torch.int32))),
+         top_p, splits, ptr(keys), ptr(picked), ptr(workspace),
+         workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
+         launches=1 if splits == 1 else 2)
+    return keys, picked
+
+
+def merge_candidates(keys_in: torch.Tensor):
+    """Global top-p of [parts, R, top_p] packed keys: (keys [R, top_p], ids [R, top_p])."""
+    keys_in = _contig(keys_in)
+    parts, R, top_p = keys_in.shape
+    keys = torch.empty(R, top_p, device=keys_in.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=keys_in.device, dtype=torch.int32)
+    call("lsa_merge_candidates", ptr(keys_in), parts, R, top_p, ptr(keys), ptr(picked), stream())
+    return keys, picked
+
+
+def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch.Tensor | None,
+              open_first: torch.Tensor, open_end: torch.Tensor, keep: int, children: torch.Tensor | None = None):
+    """One level of the beam (src/lsa/core/hierarchy.py:402-451): kept rows, or their children when given."""
+    q, v = _contig(index_queries.float()), _contig(vectors.float())
+    R, d = q.shape
+    n_carried = 0 if carried is None else carried.shape[1]
+    carried = None if carried is None else _contig(carried.to(torch.int32))
+    kept = keys = carried_out = None
+    fanout = 0
+    if children is not None:
+        children = _contig(children)
+        fanout = children.shape[1]
+        carried_out = torch.empty(R, keep * fanout, device=q.device, dtype=torch.int32)
+    else:
+        kept = torch.empty(R, keep, device=q.device, dtype=torch.int32)
+        keys = torch.empty(R, keep, device=q.device, dtype=torch.int64)
+    call("lsa_beam_step", ptr(q), R, d, ptr(v), v.shape[0], ptr(carried), n_carried,
+         ptr(_contig(open_first.to(torch.int32))), ptr(_contig(open_end.to(torch.int32))), keep, ptr(children),
+         fanout, ptr(kept), ptr(keys), ptr(carried_out), stream())
+    return carried_out if children is not None else (kept, keys)
+
+
+def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor, top_k: int, sink: int, window: int,
+           row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
+           page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None):
+    """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status)."""
+    picked, members = _contig(picked), _contig(members)
+    R, top_p = picked.shape
+    width = top_k + window + sink
+    selected = torch.empty(R, width, device=picked.device, dtype=torch.int32)
+    lengths = torch.empty(R, device=picked.device, dtype=torch.int32)
+    status = torch.zeros(1, device=picked.device, dtype=torch.int32)
+    first, end = owner if owner is not None else (0, _lib.INT64_MAX)
+    call("lsa_expand", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
+         members.shape[0], members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(page_table),
+         page_size, first, end, ptr(selected), ptr(lengths), ptr(status), stream())
+    return selected, lengths, status
+
+
+def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.Tensor,
+                  lengths: torch.Tensor | None, scale: float, splits: int = 1, out_dtype=torch.bfloat16,
+                  workspace: torch.Tensor | None = None):
+    """Attention of q [R, Hq, dh] over the KV rows each list names; returns (out [R, Hq, dh], lse [R, Hq])."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("q, k and v must be bfloat16")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
+        raise ValueError("head dims must be contiguous and k, v must share their layout")
+    ids = _contig(ids)
+    R, Hq, dh = q.shape
+    slots, Hkv, _ = k.shape
+    out_bf16 = torch.empty(R, Hq, dh, device=q.device, dtype=torch.bfloat16) if out_dtype == torch.bfloat16 else None
+    out_f32 = torch.empty(R, Hq, dh, device=q.device, dtype=torch.float32) if out_dtype == torch.float32 else None
+    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32)
+    need = query("lsa_sparse_attend_workspace_bytes", R, Hq, dh, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_sparse_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, Hkv, k.stride(0),
+         k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits, ptr(out_bf16), ptr(out_f32),
+         ptr(lse), ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0,
+         stream(), launches=1 if splits == 1 else 2)
+    return (out_bf16 if out_bf16 is not None else out_f32), lse
+
+
+def lse_merge(parts: torch.Tensor, lses: torch.Tensor, out_dtype=torch.float32):
+    """Merge [n, rows..., dh] partial outputs by their [n, rows...] log-sum-exps."""
+    parts, lses = _contig(parts.float()), _contig(lses.float())
+    n, dh = parts.shape[0], parts.shape[-1]
+    rows = lses.numel() // n
+    out = torch.empty(parts.shape[1:], device=parts.device, dtype=out_dtype)
+    lse = torch.empty(lses.shape[1:], device=parts.device, dtype=torch.float32)
+    call("lsa_lse_merge", ptr(parts), ptr(lses), n, rows, dh, ptr(out) if out_dtype == torch.bfloat16 else None,
+         ptr(out) if out_dtype == torch.float32 else None, ptr(lse), stream())
+    return out, lse

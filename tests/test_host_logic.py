@@ -1,0 +1,85 @@
+"""Host-side logic that needs no GPU: budgets, design checks, validation errors, list composition, the probe."""
+
+import pytest
+import torch
+
+from lsa_b200 import core, probe
+from lsa_b200.budget import EarlyBudget, budget_at
+from lsa_b200.layer import FlatDesign
+
+
+def test_early_budget_is_validated_and_applied():
+    early = EarlyBudget(position=100, top_k=8, top_p=2)
+    assert budget_at(99, 64, 16, early) == (8, 2) and budget_at(100, 64, 16, early) == (64, 16)
+    assert budget_at(5, 64, 16, None) == (64, 16)
+    assert EarlyBudget.read({"position": 3, "top_k": 2, "top_p": 1}) == EarlyBudget(3, 2, 1)
+    assert EarlyBudget.read(None) is None
+    for bad in ({"position": 0, "top_k": 1, "top_p": 1}, {"position": True, "top_k": 1, "top_p": 1},
+                {"position": 1, "top_k": 1}, [1, 2, 3]):
+        with pytest.raises(ValueError):
+            EarlyBudget.read(bad)
+
+
+def test_design_sizes_must_nest():
+    FlatDesign(16, 32, 64, 1024, 64, 4096, 4, 1024)
+    for bad in [(3, 8, 16, 64), (4, 8, 16, 60), (4, 8, 15, 64), (0, 8, 16, 64)]:
+        with pytest.raises(ValueError):
+            core.check_sizes(*bad)
+    with pytest.raises(ValueError, match="cannot fill"):
+        FlatDesign(4, 8, 16, 64, top_p=2, top_k=64)
+
+
+def test_rows_that_are_not_unit_length_are_refused_before_any_kernel():
+    with pytest.raises(ValueError, match="unit rows"):
+        core.check_unit_rows("index_keys", torch.ones(4, 8))
+    with pytest.raises(ValueError, match="float32 or bfloat16"):
+        core.check_unit_rows("index_keys", torch.ones(4, 8, dtype=torch.float64))
+    with pytest.raises(ValueError, match="non-finite"):
+        core.check_unit_rows("index_keys", torch.full((2, 2), float("nan")))
+    with pytest.raises(ValueError, match=r"\[N, index_dim\]"):
+        core.check_unit_rows("index_keys", torch.ones(4))
+    core.check_unit_rows("index_keys", torch.nn.functional.normalize(torch.randn(5, 8), dim=-1).bfloat16())
+
+
+def test_rotary_layout_and_position_free_views():
+    q, k = torch.randn(2, 4, 3, 16), torch.randn(2, 2, 3, 16)
+    a, b = core.position_free(q, k, core.RotaryLayout("prefix", 4))
+    assert a.shape[-1] == 12 and torch.equal(b, k[..., 4:])
+    a, _ = core.position_free(q, k, core.RotaryLayout("suffix", 4))
+    assert torch.equal(a, q[..., :12])
+    assert core.position_free(q, k, core.RotaryLayout())[0] is q
+    with pytest.raises(ValueError):
+        core.RotaryLayout("prefix", 0)
+    with pytest.raises(ValueError, match="whole head"):
+        core.position_free(q, k, core.RotaryLayout("prefix", 16))
+
+
+def test_a_keep_set_list_is_the_union_with_every_key_once():
+    # tests/unit/core/test_attention.py:60-65 of the reference: keep-set {0,1,40,47,48,49,50} at position 50
+    selected = torch.tensor([[40, 49, 60, -1, 40]], dtype=torch.int32)
+    lists, lengths = core.compose_lists(selected, torch.tensor([50]), 4, 2)
+    assert lists[0, : int(lengths[0])].tolist() == [0, 1, 40, 47, 48, 49, 50]
+    assert (lists[0, int(lengths[0]):] == -1).all()
+    # padding selects nothing; no window and no sinks leaves only causal picks
+    lists, lengths = core.compose_lists(torch.tensor([[-1, 7, 2]], dtype=torch.int32), torch.tensor([5]), 0, 0)
+    assert lists[0, : int(lengths[0])].tolist() == [2]
+
+
+def test_regions_cost_nothing_until_a_recorder_listens():
+    seen = []
+
+    class Recorder:
+        def region(self, name):
+            import contextlib
+
+            seen.append(name)
+            return contextlib.nullcontext()
+
+    with probe.region("select"):
+        pass
+    assert not seen
+    probe.install(Recorder())
+    with probe.region("select"):
+        pass
+    probe.uninstall()
+    assert seen == ["select"]
