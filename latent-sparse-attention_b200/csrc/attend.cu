@@ -1,8 +1,7 @@
 // Gather-sparse attention: every query row attends over the KV rows its list names.
 //
 // A warp owns one (query row, KV head, split) item and streams the listed K/V rows through its own
-// shared-memory ring with asynchronous 16-byte copies (zero-filled for a list's ragged end), three tiles of 16
-// keys in flight. The head group's queries share each gathered row: with the KEYS as the M dimension of the
+// shared-memory ring with asynchronous 16-byte copies (zero-filled for a list's ragged end), 32 keys a stage. The head group's queries share each gathered row: with the KEYS as the M dimension of the
 // tensor-core tile (S^T = K Q^T, O^T = V^T P^T) a group of up to 8 query heads fills the N = 8 side of
 // mma.m16n8k16 instead of 5 of 16 M rows, which halves the instructions per key. Softmax is online in the log2
 // domain with fp32 statistics; the kernel emits the natural-log log-sum-exp so partial results over disjoint key
@@ -11,8 +10,7 @@
 
 namespace lsa {
 
-constexpr int kKeysPerTile = 16;
-constexpr int kStages = 3;
+constexpr int kKeysPerStage = 32;  // two 16-key MMA tiles, interleaved for instruction-level parallelism
 
 struct AttendParams {
   const uint16_t *q, *k, *v;
@@ -60,17 +58,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
-// DH: head dim (64 or 128). NT: 8-head tiles a group needs (1 or 2). W: warps a CTA.
-template <int DH, int NT, int W>
-__global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
+// DH: head dim (64 or 128). NT: 8-head tiles a group needs (1 or 2). W: warps a CTA. STAGES: ring depth.
+template <int DH, int NT, int W, int STAGES>
+__global__ void __launch_bounds__(W * 32, 1) sparse_attend_kernel(AttendParams p) {
   constexpr int ROW_BYTES = DH * 2;
-  constexpr int CHUNKS = ROW_BYTES / 16;                  // 16-byte chunks a row
-  constexpr int TILE_BYTES = kKeysPerTile * ROW_BYTES;    // one of K or V
+  constexpr int CHUNKS = ROW_BYTES / 16;                    // 16-byte chunks a row
+  constexpr int TILE_BYTES = kKeysPerStage * ROW_BYTES;     // one of K or V
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  constexpr int WARP_BYTES = kStages * STAGE_BYTES + 16;  // + the stages' validity masks
+  constexpr int WARP_BYTES = STAGES * STAGE_BYTES + 16;     // + the stages' validity masks
   constexpr int KSTEPS = DH / 16;
-  constexpr int ROWS_PER_PASS = 32 / CHUNKS;              // rows one pass of the warp's lanes covers
-  constexpr int PASSES = kKeysPerTile / ROWS_PER_PASS;
+  constexpr int ROWS_PER_PASS = 32 / CHUNKS;                // rows one pass of the warp's lanes covers
+  constexpr int PASSES = kKeysPerStage / ROWS_PER_PASS;
+  static_assert(STAGES >= 2 && STAGES <= 4, "ring depth");
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,17 +83,17 @@ __global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
 
   unsigned char *mine = smem_raw + (size_t)warp * WARP_BYTES;
   const uint32_t smem_base = smem_u32(mine);
-  volatile uint32_t *masks = reinterpret_cast<volatile uint32_t *>(mine + kStages * STAGE_BYTES);
+  volatile uint32_t *masks = reinterpret_cast<volatile uint32_t *>(mine + STAGES * STAGE_BYTES);
 
   int64_t n_total = p.lengths ? p.lengths[r] : p.list_stride;
   if (n_total > p.list_stride) n_total = p.list_stride;
   if (n_total < 0) n_total = 0;
   int64_t per = (n_total + p.splits - 1) / p.splits;
-  per = (per + kKeysPerTile - 1) / kKeysPerTile * kKeysPerTile;
+  per = (per + kKeysPerStage - 1) / kKeysPerStage * kKeysPerStage;
   const int64_t begin = (int64_t)split * per;
   const int64_t end = begin + per < n_total ? begin + per : n_total;
   const int n = end > begin ? (int)(end - begin) : 0;
-  const int tiles = (n + kKeysPerTile - 1) / kKeysPerTile;
+  const int iters = (n + kKeysPerStage - 1) / kKeysPerStage;
   const int32_t *list = p.ids + r * p.list_stride + begin;
   const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride;
   const uint16_t *v_head = p.v + (int64_t)h * p.kv_head_stride;
@@ -127,13 +126,16 @@ __global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
     for (int mt = 0; mt < DH / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
   }
 
-  auto issue = [&](int tile) {
-    if (tile < tiles) {
-      const int stage = tile % kStages;
-      const int e = tile * kKeysPerTile + (lane & 15);
-      int32_t id = e < n ? list[e] : -1;
-      const bool ok = id >= 0 && id < p.slots;
-      const uint32_t valid = __ballot_sync(0xffffffffu, ok) & 0xFFFFu;
+  // A lane's list entry of stage `it`; read a stage ahead of its use so the load never stalls the copies.
+  auto entry = [&](int it) -> int32_t {
+    const int e = it * kKeysPerStage + lane;
+    return e < n ? list[e] : -1;
+  };
+  // Start the copies of stage `it`, whose list entries the lanes hold in `id`.
+  auto issue = [&](int it, int32_t id) {
+    if (it < iters) {
+      const int stage = it % STAGES;
+      const uint32_t valid = __ballot_sync(0xffffffffu, id >= 0 && id < p.slots);
       if (lane == 0) masks[stage] = valid;
       const uint32_t k_dst = smem_base + stage * STAGE_BYTES;
       const int chunk = lane % CHUNKS;
@@ -152,46 +154,61 @@ __global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
   };
 
 #pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) issue(s);
+  for (int s = 0; s < STAGES - 1; ++s) issue(s, entry(s));
+  int32_t id_ahead = entry(STAGES - 1);
 
-  for (int tile = 0; tile < tiles; ++tile) {
-    issue(tile + kStages - 1);
-    cp_async_wait<kStages - 1>();
+  for (int it = 0; it < iters; ++it) {
+    cp_async_wait<STAGES - 2>();
     __syncwarp();
-    const int stage = tile % kStages;
+    issue(it + STAGES - 1, id_ahead);
+    id_ahead = entry(it + STAGES);
+    const int stage = it % STAGES;
     const uint32_t k_src = smem_base + stage * STAGE_BYTES, v_src = k_src + TILE_BYTES;
     const uint32_t valid = masks[stage];
 
-    // S^T [16 keys x 8 heads] = K [16 x DH] . Q^T
-    float s[NT][4];
+    // S^T [32 keys x 8 heads] = K [32 x DH] . Q^T, as two independent 16-key accumulations
+    float s0[NT][4], s1[NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    for (int nt = 0; nt < NT; ++nt) {
+      s0[nt][0] = s0[nt][1] = s0[nt][2] = s0[nt][3] = 0.0f;
+      s1[nt][0] = s1[nt][1] = s1[nt][2] = s1[nt][3] = 0.0f;
+    }
     {
       const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
         const int chunk = ks * 2 + (lane >> 4);
-        uint32_t a0, a1, a2, a3;
-        ldmatrix_x4(k_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), a0, a1, a2, a3);
+        const uint32_t addr = k_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        ldmatrix_x4(addr, a0, a1, a2, a3);
+        ldmatrix_x4(addr + 16 * ROW_BYTES, b0, b1, b2, b3);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma_bf16(s[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(s0[nt], a0, a1, a2, a3, qf[nt][ks][0], qf[nt][ks][1]);
+          mma_bf16(s1[nt], b0, b1, b2, b3, qf[nt][ks][0], qf[nt][ks][1]);
+        }
       }
     }
 
-    const bool ok_lo = (valid >> g) & 1u, ok_hi = (valid >> (g + 8)) & 1u;
-    uint32_t pb[NT][2];
+    const bool ok0 = (valid >> g) & 1u, ok1 = (valid >> (g + 8)) & 1u;
+    const bool ok2 = (valid >> (g + 16)) & 1u, ok3 = (valid >> (g + 24)) & 1u;
+    uint32_t pb[NT][4];
     bool rescale = false;
     float alpha[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      float x[4];
-      x[0] = ok_lo ? s[nt][0] * p.scale_log2 : -INFINITY;
-      x[1] = ok_lo ? s[nt][1] * p.scale_log2 : -INFINITY;
-      x[2] = ok_hi ? s[nt][2] * p.scale_log2 : -INFINITY;
-      x[3] = ok_hi ? s[nt][3] * p.scale_log2 : -INFINITY;
+      float x[8];
+      x[0] = ok0 ? s0[nt][0] * p.scale_log2 : -INFINITY;
+      x[1] = ok0 ? s0[nt][1] * p.scale_log2 : -INFINITY;
+      x[2] = ok1 ? s0[nt][2] * p.scale_log2 : -INFINITY;
+      x[3] = ok1 ? s0[nt][3] * p.scale_log2 : -INFINITY;
+      x[4] = ok2 ? s1[nt][0] * p.scale_log2 : -INFINITY;
+      x[5] = ok2 ? s1[nt][1] * p.scale_log2 : -INFINITY;
+      x[6] = ok3 ? s1[nt][2] * p.scale_log2 : -INFINITY;
+      x[7] = ok3 ? s1[nt][3] * p.scale_log2 : -INFINITY;
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        float mx = fmaxf(x[j], x[2 + j]);
+        float mx = fmaxf(fmaxf(x[j], x[2 + j]), fmaxf(x[4 + j], x[6 + j]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
@@ -202,10 +219,14 @@ __global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
         m_run[nt][j] = m_new;
         x[j] = exp2f(x[j] - m_safe);
         x[2 + j] = exp2f(x[2 + j] - m_safe);
-        l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + (x[j] + x[2 + j]);
+        x[4 + j] = exp2f(x[4 + j] - m_safe);
+        x[6 + j] = exp2f(x[6 + j] - m_safe);
+        l_run[nt][j] = l_run[nt][j] * alpha[nt][j] + ((x[j] + x[2 + j]) + (x[4 + j] + x[6 + j]));
       }
       pb[nt][0] = movmatrix_trans(pack_bf16x2(x[0], x[1]));
       pb[nt][1] = movmatrix_trans(pack_bf16x2(x[2], x[3]));
+      pb[nt][2] = movmatrix_trans(pack_bf16x2(x[4], x[5]));
+      pb[nt][3] = movmatrix_trans(pack_bf16x2(x[6], x[7]));
     }
     if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
@@ -219,16 +240,21 @@ __global__ void __launch_bounds__(W * 32) sparse_attend_kernel(AttendParams p) {
         }
     }
 
-    // O^T [DH x 8 heads] += V^T [DH x 16 keys] . P^T
+    // O^T [DH x 8 heads] += V^T [DH x 32 keys] . P^T
     {
       const int row = (lane & 7) + (lane >> 4) * 8;
 #pragma unroll
       for (int mt = 0; mt < DH / 16; ++mt) {
         const int chunk = mt * 2 + ((lane >> 3) & 1);
-        uint32_t a0, a1, a2, a3;
-        ldmatrix_x4_trans(v_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), a0, a1, a2, a3);
+        const uint32_t addr = v_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        ldmatrix_x4_trans(addr, a0, a1, a2, a3);
+        ldmatrix_x4_trans(addr + 16 * ROW_BYTES, b0, b1, b2, b3);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][mt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+        for (int nt = 0; nt < NT; ++nt) {
+          mma_bf16(o[nt][mt], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
+          mma_bf16(o[nt][mt], b0, b1, b2, b3, pb[nt][2], pb[nt][3]);
+        }
       }
     }
     __syncwarp();
@@ -305,17 +331,17 @@ __global__ void lse_merge_kernel(const float *__restrict__ parts, const float *_
   if (lane == 0 && lse_out) lse_out[row] = total;
 }
 
-template <int DH, int NT, int W>
+template <int DH, int NT, int W, int STAGES>
 static int launch_attend(const AttendParams &p, cudaStream_t s) {
-  constexpr int WARP_BYTES = kStages * 2 * kKeysPerTile * DH * 2 + 16;
+  constexpr int WARP_BYTES = STAGES * 2 * kKeysPerStage * DH * 2 + 16;
   const size_t smem = (size_t)W * WARP_BYTES;
-  if (cudaFuncSetAttribute(sparse_attend_kernel<DH, NT, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (cudaFuncSetAttribute(sparse_attend_kernel<DH, NT, W, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return LSA_ERR_LAUNCH;
   const int64_t items = p.R * p.splits * p.Hkv;
   const int64_t grid = (items + W - 1) / W;
   if (grid > INT32_MAX) return LSA_ERR_ARGUMENT;
-  sparse_attend_kernel<DH, NT, W><<<(unsigned)grid, W * 32, smem, s>>>(p);
+  sparse_attend_kernel<DH, NT, W, STAGES><<<(unsigned)grid, W * 32, smem, s>>>(p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -389,10 +415,11 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   }
   cudaStream_t s = (cudaStream_t)stream;
   int rc;
+  // Shared memory a warp: dh 128 -> 2 stages of 16 KB (7 warps fill an SM), dh 64 -> 3 stages of 8 KB (9 warps).
   if (dh == 128)
-    rc = group <= 8 ? lsa::launch_attend<128, 1, 8>(p, s) : lsa::launch_attend<128, 2, 8>(p, s);
+    rc = group <= 8 ? lsa::launch_attend<128, 1, 7, 2>(p, s) : lsa::launch_attend<128, 2, 7, 2>(p, s);
   else
-    rc = group <= 8 ? lsa::launch_attend<64, 1, 8>(p, s) : lsa::launch_attend<64, 2, 8>(p, s);
+    rc = group <= 8 ? lsa::launch_attend<64, 1, 9, 3>(p, s) : lsa::launch_attend<64, 2, 9, 3>(p, s);
   if (rc != LSA_OK || splits == 1) return rc;
   return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dh, out_bf16, out_f32, lse, stream);
 }
