@@ -30,6 +30,7 @@ extern "C" {
 #define LSA_ERR_WORKSPACE (-4)   /* the workspace passed in is smaller than *_workspace_bytes() asks */
 #define LSA_ERR_LAUNCH (-5)      /* the CUDA runtime refused a launch or an attribute */
 #define LSA_ERR_DEVICE (-6)      /* not an sm_100 device */
+#define LSA_ERR_STATIC_SCRATCH (-7) /* the call needs more scratch than the built-in static array holds */
 
 #define LSA_PAD (-1)                  /* the only padding value an id list carries (src/lsa/constants.py:16-20) */
 #define LSA_EMPTY_KEY INT64_MIN       /* the packed key of no bucket (src/lsa/core/kernels/constants.py:29-37) */
@@ -185,6 +186,28 @@ int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_ro
                       int64_t kv_head_stride, const int32_t *ids, int64_t list_stride, const int32_t *lengths,
                       float scale, int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
                       size_t workspace_bytes, void *stream);
+
+/* The same read for callers that cannot allocate device memory. This entry point has no counterpart in the
+ * reference; it exists for hosts where lsa_sparse_attend's caller-provided workspace is not an option: a serving
+ * engine that hands every free byte of the GPU to its KV pool at start-up and forbids later allocations, a
+ * plugin thread that is given raw pointers but no allocator, or a latency-critical decode loop that must not
+ * risk the implicit device synchronisation of an allocation. The scratch of a split read (the per-split partial
+ * outputs and log-sum-exps) lives in an 8 MiB static device array inside the library instead, which every GPU
+ * that loads the library holds until the process exits.
+ *   - Arguments are those of lsa_sparse_attend without the workspace. A call that needs more than
+ *     lsa_sparse_attend_static_scratch_bytes() - that is, splits * R * Hq * (dh + 1) * 4 bytes over 8 MiB -
+ *     returns LSA_ERR_STATIC_SCRATCH and launches nothing; lower `splits` or the rows a call.
+ *   - It calls no cudaMalloc, cudaFree or other allocating routine. The first call on each device resolves the
+ *     array's device address (with that device current); make that first call outside any stream capture.
+ *   - Every call on a device uses the same array and leaves its partial results in it. The kernels overwrite all
+ *     they later read, so nothing has to be cleared between calls, but two calls whose kernels overlap on the GPU
+ *     (different streams) race on it: serialise them. */
+size_t lsa_sparse_attend_static_scratch_bytes(void);
+int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
+                             int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv,
+                             int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
+                             const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
+                             float *lse, void *stream);
 
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the

@@ -423,3 +423,42 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   if (rc != LSA_OK || splits == 1) return rc;
   return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dh, out_bf16, out_f32, lse, stream);
 }
+
+// ================================================================================================ no-allocation entry
+
+// Scratch of lsa_sparse_attend_static: the partial outputs and log-sum-exps of a split read. It is part of the
+// library image, so every GPU that loads the library holds these bytes until the process exits.
+#define LSA_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char lsa_static_attend_scratch[LSA_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of the scratch array on each device, resolved on the first call made with that device current.
+void *static_scratch_address[kMaxDevices] = {};
+}  // namespace
+
+LSA_API size_t lsa_sparse_attend_static_scratch_bytes(void) { return LSA_STATIC_SCRATCH_BYTES; }
+
+LSA_API int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
+                                     int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots,
+                                     int Hkv, int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids,
+                                     int64_t list_stride, const int32_t *lengths, float scale, int splits,
+                                     uint16_t *out_bf16, float *out_f32, float *lse, void *stream) {
+  LSA_REQUIRE(R >= 0 && Hq >= 1 && dh >= 1 && splits >= 1, LSA_ERR_ARGUMENT);
+  const size_t need = lsa_sparse_attend_workspace_bytes(R, Hq, dh, splits);
+  if (need > LSA_STATIC_SCRATCH_BYTES) return LSA_ERR_STATIC_SCRATCH;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return LSA_ERR_DEVICE;
+  void *scratch = static_scratch_address[device];
+  if (scratch == nullptr) {
+    // In host code the array's name is only a handle: the kernels need the address it has on THIS device.
+    if (cudaGetSymbolAddress(&scratch, lsa_static_attend_scratch) != cudaSuccess || scratch == nullptr) {
+      (void)cudaGetLastError();
+      return LSA_ERR_LAUNCH;
+    }
+    static_scratch_address[device] = scratch;
+  }
+  return lsa_sparse_attend(q, R, Hq, dh, q_row_stride, q_head_stride, k, v, slots, Hkv, kv_row_stride, kv_head_stride,
+                           ids, list_stride, lengths, scale, splits, out_bf16, out_f32, lse, scratch,
+                           LSA_STATIC_SCRATCH_BYTES, stream);
+}

@@ -39,6 +39,9 @@ SIGNATURES = {
     "lsa_sparse_attend_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "lsa_sparse_attend": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _I, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P, _P,
                                _Z, _P]),
+    "lsa_sparse_attend_static_scratch_bytes": (_Z, []),
+    "lsa_sparse_attend_static": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _I, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P,
+                                      _P]),
     "lsa_lse_merge": (_I, [_P, _P, _I, _L, _I, _P, _P, _P, _P]),
 }
 
@@ -95,7 +98,7 @@ def call(name: str, *args, launches: int = 1):
     LAUNCHES += launches
     if code != 0:
         reason = load().lsa_error_string(code).decode()
-        kind = ValueError if code in (-1, -2, -3, -4) else RuntimeError
+        kind = ValueError if code in (-1, -2, -3, -4, -7) else RuntimeError
         raise kind(f"{name} refused the call: {reason} (code {code})")
 
 
