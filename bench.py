@@ -244,14 +244,17 @@ def run_ours(args, cfg: dict) -> dict:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms) / steps
 
+    out_d = torch.empty_like(q)
+    q_in, k_in, v_in = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
     def resident_step():
-        layer.prefill(q, k, v, chunk=cfg["chunk"])
+        layer.prefill(q, k, v, chunk=cfg["chunk"], out=out_d)
 
     def e2e_step():
-        qd = q_h.cuda(non_blocking=True)
-        kd = k_h.cuda(non_blocking=True)
-        vd = v_h.cuda(non_blocking=True)
-        out_h.copy_(layer.prefill(qd, kd, vd, chunk=cfg["chunk"]), non_blocking=True)
+        q_in.copy_(q_h, non_blocking=True)
+        k_in.copy_(k_h, non_blocking=True)
+        v_in.copy_(v_h, non_blocking=True)
+        out_h.copy_(layer.prefill(q_in, k_in, v_in, chunk=cfg["chunk"], out=out_d), non_blocking=True)
 
     for _ in range(args.warmup):
         resident_step()

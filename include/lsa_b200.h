@@ -59,6 +59,23 @@ int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group
                   int64_t x_row_stride, int64_t x_head_stride, const void *W, int w_dtype, int d_idx,
                   int normalize, float *out_f32, uint16_t *out_bf16, void *stream);
 
+/* The same map on the tensor cores (tcgen05 MMA, TMEM accumulator, TMA-fed operands) for the serving path, where
+ * heads and the map are bf16 (src/lsa/sglang/index/layer_index.py:298-300,344,355 does this product in bf16 too).
+ *   x    [rows, d_in] bf16 with x_row_stride elements between rows (a [rows, heads, dh] tensor with contiguous
+ *        heads IS such a matrix with d_in = heads*dh); base and row pitch 16-byte aligned
+ *   Wt   [d_idx, d_in] bf16, the map TRANSPOSED; for grouped queries the caller repeats a KV head's block of the
+ *        map under each query head of its group (the head sum then happens inside the product) and zeroes the
+ *        columns of dims the index does not read
+ *   d_idx 32, 64 or 128. status (may be NULL) is raised if a bounded on-chip wait gives up. */
+int lsa_index_map_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_row_stride, const uint16_t *Wt,
+                     int d_idx, int normalize, float *out_f32, uint16_t *out_bf16, int32_t *status, void *stream);
+
+/* out = gelu(x @ Wt^T) in bf16, the hidden layer of the BASELINE-only two-layer map (no counterpart in the
+ * reference, whose maps are one linear projection); the second layer is lsa_index_map_tc over `out`.
+ *   x [rows, d_in] bf16, Wt [d_out, d_in] bf16, out_bf16 [rows, d_out]; d_out a multiple of 128. */
+int lsa_gemm_gelu_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_row_stride, const uint16_t *Wt,
+                     int64_t d_out, uint16_t *out_bf16, int32_t *status, void *stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Pooling. Reference: pool_keys (src/lsa/core/ward.py:15-26).
  * pools[p, :] = sum of index_keys[p*pool_size : (p+1)*pool_size, :] added in position order, fp32.

@@ -27,6 +27,8 @@ SIGNATURES = {
     "lsa_error_string": (ctypes.c_char_p, [_I]),
     "lsa_abi_version": (_I, []),
     "lsa_index_map": (_I, [_P, _I, _L, _I, _I, _I, _I, _L, _L, _P, _I, _I, _I, _P, _P, _P]),
+    "lsa_index_map_tc": (_I, [_P, _L, _L, _L, _P, _I, _I, _P, _P, _P, _P]),
+    "lsa_gemm_gelu_tc": (_I, [_P, _L, _L, _L, _P, _L, _P, _P, _P]),
     "lsa_pool_keys": (_I, [_P, _I, _L, _I, _I, _P, _P]),
     "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P]),
     "lsa_bucket_table": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),

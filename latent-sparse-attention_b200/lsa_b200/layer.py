@@ -58,7 +58,8 @@ class FlatLayer:
     """Prefill and decode of one layer. `query_map` / `key_map` are [Hkv * (dh - rotary), index_dim]."""
 
     def __init__(self, design: FlatDesign, query_map: torch.Tensor, key_map: torch.Tensor, heads: int, kv_heads: int,
-                 head_dim: int, rotary: RotaryLayout = RotaryLayout(), scale: float | None = None):
+                 head_dim: int, rotary: RotaryLayout = RotaryLayout(), scale: float | None = None,
+                 tensor_cores: bool = True):
         if heads % kv_heads:
             raise ValueError(f"query heads must group evenly - {heads} does not divide by {kv_heads}")
         free = head_dim - rotary.dim
@@ -71,37 +72,82 @@ class FlatLayer:
         self.dh_off = rotary.dim if rotary.end == "prefix" else 0
         self.dh_used = free
         self.scale = head_dim ** -0.5 if scale is None else scale
+        self._buffers: dict = {}
+        # bf16 maps run on the tensor cores (the head sum folded into the product); fp32 maps keep the exact form
+        self.tensor_cores = tensor_cores and query_map.dtype == torch.bfloat16 and key_map.dtype == torch.bfloat16 \
+            and query_map.shape[1] in (32, 64, 128)
+        if self.tensor_cores:
+            self.query_map_t = ops.expand_map(self.query_map, heads, heads // kv_heads, head_dim, self.dh_off,
+                                              self.dh_used)
+            self.key_map_t = ops.expand_map(self.key_map, kv_heads, 1, head_dim, self.dh_off, self.dh_used)
+            self._map_status = torch.zeros(1, device=query_map.device, dtype=torch.int32)
+
+    # ---- buffers
+
+    def _buffer(self, name: str, shape: tuple, dtype: torch.dtype, device) -> torch.Tensor:
+        """A tensor that lives as long as the layer: a step allocates nothing once every shape has been seen."""
+        key = (name, tuple(shape), dtype, str(device))
+        held = self._buffers.get(key)
+        if held is None:
+            held = self._buffers[key] = torch.empty(shape, device=device, dtype=dtype)
+        return held
+
+    def _takes_tensor_cores(self, x: torch.Tensor) -> bool:
+        """Heads packed densely in bf16 with a 16-byte aligned row pitch: the layout a TMA descriptor can walk."""
+        return (self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) == x.shape[2]
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
     # ---- the stages
 
-    def index_queries(self, q: torch.Tensor) -> torch.Tensor:
+    def index_queries(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """q [T, Hq, dh] bf16 -> unit index queries [T, index_dim] fp32."""
+        if self._takes_tensor_cores(q):
+            return ops.index_map_tc(q, self.query_map_t, out=out, status=self._map_status)
         return ops.index_map(q, self.query_map, group=self.heads // self.kv_heads, dh_off=self.dh_off,
-                             dh_used=self.dh_used)
+                             dh_used=self.dh_used, out=out)
 
-    def index_keys(self, k: torch.Tensor) -> torch.Tensor:
+    def index_keys(self, k: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """k [T, Hkv, dh] bf16 -> unit index keys [T, index_dim] fp32."""
-        return ops.index_map(k, self.key_map, group=1, dh_off=self.dh_off, dh_used=self.dh_used)
+        if self._takes_tensor_cores(k):
+            return ops.index_map_tc(k, self.key_map_t, out=out, status=self._map_status)
+        return ops.index_map(k, self.key_map, group=1, dh_off=self.dh_off, dh_used=self.dh_used, out=out)
 
-    def build_index(self, k: torch.Tensor) -> FlatIndex:
-        """Index keys, then pools, Ward and the bucket table of every closed cluster block."""
-        d = self.design
+    def build_index(self, k: torch.Tensor, reuse_buffers: bool = False) -> FlatIndex:
+        """Index keys, then pools, Ward and the bucket table of every closed cluster block.
+
+        With `reuse_buffers` the index lives in the layer's own buffers and is overwritten by the next build.
+        """
+        d, dev = self.design, k.device
+        T, d_idx = k.shape[0], self.key_map.shape[1]
+        blocks = T // d.cluster_block_size
+        P, per_block = d.cluster_block_size // d.pool_size, d.block_bucket_count
+        rows = blocks * per_block
+        make = (lambda name, shape, dtype: self._buffer(name, shape, dtype, dev)) if reuse_buffers else \
+            (lambda name, shape, dtype: torch.empty(shape, device=dev, dtype=dtype))
         with probe.region("index map"):
-            keys = self.index_keys(k)
-        blocks = keys.shape[0] // d.cluster_block_size
+            keys = self.index_keys(k, out=make("index keys", (T, d_idx), torch.float32))
         with probe.region("pool"):
             pools = ops.pool_keys(keys[: blocks * d.cluster_block_size].view(blocks, d.cluster_block_size, -1),
-                                  d.pool_size)
+                                  d.pool_size, out=make("pools", (blocks, P, d_idx), torch.float32))
         with probe.region("ward"):
-            labels, _ = ops.ward_rounds(pools, float(d.pool_size), d.block_bucket_count, d.bucket_cap)
+            labels, _ = ops.ward_rounds(pools, float(d.pool_size), per_block, d.bucket_cap,
+                                        labels=make("labels", (blocks, P), torch.int64),
+                                        reached=make("reached", (blocks,), torch.uint8))
         with probe.region("bucket table"):
-            members, sizes, _, centroids, _, _ = ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count,
-                                                                 d.bucket_cap)
-        return FlatIndex(keys, Buckets(centroids, members, sizes, d.block_bucket_count, d.cluster_block_size))
+            status = make("table status", (1,), torch.int32)
+            status.zero_()
+            outs = (make("members", (rows, d.bucket_cap), torch.int32), make("sizes", (rows,), torch.int32),
+                    make("key sums", (rows, d_idx), torch.float32), make("centroids", (rows, d_idx), torch.float32),
+                    None, status)
+            members, sizes, _, centroids, _, _ = ops.bucket_table(keys, labels, d.pool_size, per_block, d.bucket_cap,
+                                                                 outs=outs)
+        return FlatIndex(keys, Buckets(centroids, members, sizes, per_block, d.cluster_block_size))
 
-    def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex):
+    def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
+               reuse_buffers: bool = False):
         """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`."""
-        d, b = self.design, index.buckets
+        d, b, dev = self.design, index.buckets, index_queries.device
+        R = index_queries.shape[0]
         positions = positions.to(torch.int64)
         visible = (positions // d.cluster_block_size * d.block_bucket_count).clamp_max(
             b.bucket_centroids.shape[0]).to(torch.int32)
@@ -110,34 +156,50 @@ class FlatLayer:
             early = positions < d.early_budget.position
             row_p = torch.where(early, d.early_budget.top_p, d.top_p).to(torch.int32)
             row_k = torch.where(early, d.early_budget.top_k, d.top_k).to(torch.int32)
+        keys = picked = outs = None
+        if reuse_buffers:
+            keys = self._buffer("keys", (R, d.top_p), torch.int64, dev)
+            picked = self._buffer("picked", (R, d.top_p), torch.int32, dev)
+            status = self._buffer("expand status", (1,), torch.int32, dev)
+            status.zero_()
+            outs = (self._buffer("lists", (R, d.list_width), torch.int32, dev),
+                    self._buffer("lengths", (R,), torch.int32, dev), status)
         with probe.region("select"):
-            _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p)
+            _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
+                                        picked=picked)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, positions, b.bucket_members, d.top_k, d.sink_size, d.window_size,
-                                           row_p, row_k)
+                                           row_p, row_k, outs=outs)
         return lists, lengths
 
     def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lists: torch.Tensor, lengths: torch.Tensor,
-               splits: int = 1):
+               splits: int = 1, out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
         with probe.region("attend"):
-            return ops.sparse_attend(q, k, v, lists, lengths, self.scale, splits=splits)
+            return ops.sparse_attend(q, k, v, lists, lengths, self.scale, splits=splits, out=out, lse=lse)
 
     # ---- the layer
 
     def prefill(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk: int = 8192,
-                return_index: bool = False):
-        """Causal prefill from position 0: q [T,Hq,dh], k/v [T,Hkv,dh] bf16 -> out [T,Hq,dh] bf16."""
-        T = q.shape[0]
-        index = self.build_index(k)
-        out = torch.empty_like(q)
+                return_index: bool = False, out: torch.Tensor | None = None):
+        """Causal prefill from position 0: q [T,Hq,dh], k/v [T,Hkv,dh] bf16 -> out [T,Hq,dh] bf16.
+
+        Every intermediate lives in buffers the layer keeps, so after the first call a step allocates nothing but
+        its output (pass `out` to avoid that too). With `return_index` the index is built in fresh tensors instead.
+        """
+        T, dev = q.shape[0], q.device
+        index = self.build_index(k, reuse_buffers=not return_index)
+        out = torch.empty_like(q) if out is None else out
+        d_idx = self.query_map.shape[1]
         for start in range(0, T, chunk):
             stop = min(T, start + chunk)
             rows = q[start:stop]
-            positions = torch.arange(start, stop, device=q.device)
+            positions = torch.arange(start, stop, device=dev)
             with probe.region("index map"):
-                index_queries = self.index_queries(rows)
-            lists, lengths = self.select(index_queries, positions, index)
-            out[start:stop], _ = self.attend(rows, k, v, lists, lengths)
+                index_queries = self.index_queries(rows, out=self._buffer("index queries", (stop - start, d_idx),
+                                                                          torch.float32, dev))
+            lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True)
+            self.attend(rows, k, v, lists, lengths, out=out[start:stop],
+                        lse=self._buffer("lse", (stop - start, self.heads), torch.float32, dev))
         return (out, index) if return_index else out
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,

@@ -16,7 +16,7 @@ def _contig(t: torch.Tensor) -> torch.Tensor:
 
 def index_map(x: torch.Tensor, index_map_weight: torch.Tensor | None, group: int = 1, dh_off: int = 0,
               dh_used: int | None = None, normalize: bool = True, out_dtype: torch.dtype = torch.float32,
-              also_bf16: bool = False):
+              also_bf16: bool = False, out: torch.Tensor | None = None):
     """Head sum, learned map and normalisation: x [rows, heads, dh] -> [rows, d_idx].
 
     Stands in for `project(regroup(...))` (src/lsa/core/index_space.py:110-131, 405-419). `x` may be a strided
@@ -35,7 +35,11 @@ def index_map(x: torch.Tensor, index_map_weight: torch.Tensor | None, group: int
         if w.dim() != 2 or w.shape[0] != d_in:
             raise ValueError(f"rows have {d_in} dims and the map reads {w.shape[0] if w.dim() == 2 else w.shape}")
     d_idx = w.shape[1] if w is not None else d_in
-    out_f32 = torch.empty(rows, d_idx, device=x.device, dtype=torch.float32) if out_dtype == torch.float32 else None
+    out_f32 = None
+    if out_dtype == torch.float32:
+        out_f32 = out if out is not None else torch.empty(rows, d_idx, device=x.device, dtype=torch.float32)
+        if out_f32.shape != (rows, d_idx) or out_f32.dtype != torch.float32 or not out_f32.is_contiguous():
+            raise ValueError(f"out must be a contiguous float32 [{rows}, {d_idx}]")
     want_bf16 = also_bf16 or out_dtype == torch.bfloat16
     out_bf16 = torch.empty(rows, d_idx, device=x.device, dtype=torch.bfloat16) if want_bf16 else None
     call("lsa_index_map", ptr(x), _lib.dtype_code(x), rows, heads, group, dh_off, dh_used, x.stride(0), x.stride(1),
@@ -46,19 +50,65 @@ def index_map(x: torch.Tensor, index_map_weight: torch.Tensor | None, group: int
     return out_bf16
 
 
-def pool_keys(index_keys: torch.Tensor, pool_size: int) -> torch.Tensor:
+def expand_map(index_map_weight: torch.Tensor, heads: int, group: int, head_dim: int, dh_off: int = 0,
+               dh_used: int | None = None) -> torch.Tensor:
+    """The map as `index_map_tc` reads it: transposed, a KV head's block repeated under every query head of its
+    group, zero columns for head dims the index drops. [Hkv*dh_used, d_idx] -> [d_idx, heads*head_dim] bf16."""
+    dh_used = head_dim - dh_off if dh_used is None else dh_used
+    kv_heads = heads // group
+    w = index_map_weight.float().view(kv_heads, dh_used, -1)
+    full = torch.zeros(heads, head_dim, w.shape[2], device=w.device, dtype=torch.float32)
+    full[:, dh_off:dh_off + dh_used] = w.repeat_interleave(group, dim=0)
+    return full.view(heads * head_dim, -1).t().contiguous().to(torch.bfloat16)
+
+
+def index_map_tc(x: torch.Tensor, weight_t: torch.Tensor, normalize: bool = True, out: torch.Tensor | None = None,
+                 out_bf16: torch.Tensor | None = None, status: torch.Tensor | None = None):
+    """normalize(x @ weight_t^T) on the tensor cores: x [rows, ...] bf16 flattened to [rows, d_in], weight_t
+    [d_idx, d_in] bf16 -> fp32 [rows, d_idx] (and/or bf16). Stands in for the serving path's bf16 map product
+    (src/lsa/sglang/index/layer_index.py:331-355)."""
+    if x.dtype != torch.bfloat16 or weight_t.dtype != torch.bfloat16:
+        raise ValueError("the tensor-core map takes bfloat16 rows and a bfloat16 map")
+    rows = x.shape[0]
+    d_in = x.numel() // max(rows, 1) if rows else weight_t.shape[1]
+    inner_ok = x.dim() == 2 or all(x.stride(i) == x.stride(i + 1) * x.shape[i + 1] for i in range(1, x.dim() - 1))
+    if x.stride(-1) != 1 or not inner_ok or weight_t.shape[1] != d_in or not weight_t.is_contiguous():
+        raise ValueError(f"rows must be contiguous past their first dim and hold {weight_t.shape[1]} dims")
+    d_idx = weight_t.shape[0]
+    if out is None and out_bf16 is None:
+        out = torch.empty(rows, d_idx, device=x.device, dtype=torch.float32)
+    call("lsa_index_map_tc", ptr(x), rows, d_in, x.stride(0), ptr(weight_t), d_idx, int(normalize), ptr(out),
+         ptr(out_bf16), ptr(status), stream())
+    return out if out is not None else out_bf16
+
+
+def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: torch.Tensor | None = None):
+    """The BASELINE-only two-layer map normalize(gelu(x @ W1) @ W2) on the tensor cores: x [rows, d_in] bf16,
+    w1_t [d_hidden, d_in], w2_t [d_idx, d_hidden] bf16 -> fp32 [rows, d_idx]. The hidden layer is held in bf16."""
+    rows, d_in = x.shape
+    d_hidden = w1_t.shape[0]
+    if hidden is None:
+        hidden = torch.empty(rows, d_hidden, device=x.device, dtype=torch.bfloat16)
+    call("lsa_gemm_gelu_tc", ptr(x), rows, d_in, x.stride(0), ptr(_contig(w1_t)), d_hidden, ptr(hidden), None,
+         stream())
+    return index_map_tc(hidden, _contig(w2_t))
+
+
+def pool_keys(index_keys: torch.Tensor, pool_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """`pool_keys` (src/lsa/core/ward.py:15-26): [..., T, d] -> [..., T / pool_size, d] fp32."""
     keys = _contig(index_keys)
     T, d = keys.shape[-2], keys.shape[-1]
     if T % pool_size:
         raise ValueError(f"{T} keys do not split into pools of {pool_size}")
-    out = torch.empty(*keys.shape[:-2], T // pool_size, d, device=keys.device, dtype=torch.float32)
+    if out is None:
+        out = torch.empty(*keys.shape[:-2], T // pool_size, d, device=keys.device, dtype=torch.float32)
     call("lsa_pool_keys", ptr(keys), _lib.dtype_code(keys), out.numel() // d, pool_size, d, ptr(out), stream())
     return out
 
 
 def ward_rounds(pools: torch.Tensor, pool_sizes: torch.Tensor | float, bucket_count: int, bucket_cap: float,
-                max_rounds: int = 256, return_rounds: bool = False):
+                max_rounds: int = 256, return_rounds: bool = False, labels: torch.Tensor | None = None,
+                reached: torch.Tensor | None = None):
     """`ward_rounds` (src/lsa/core/ward.py:29-90): labels [G, P] int64 and whether each block reached its count."""
     pools = _contig(pools)
     if pools.dim() != 3 or pools.dtype != torch.float32:
@@ -71,29 +121,34 @@ def ward_rounds(pools: torch.Tensor, pool_sizes: torch.Tensor | float, bucket_co
             raise ValueError(f"pool sizes must be [{G}, {P}] - got {tuple(sizes.shape)}")
     else:
         uniform = float(pool_sizes)
-    labels = torch.empty(G, P, device=pools.device, dtype=torch.int64)
-    reached = torch.empty(G, device=pools.device, dtype=torch.uint8)
+    labels = torch.empty(G, P, device=pools.device, dtype=torch.int64) if labels is None else labels
+    raw_reached = torch.empty(G, device=pools.device, dtype=torch.uint8) if reached is None else reached
     rounds = torch.empty(G, device=pools.device, dtype=torch.int32) if return_rounds else None
     call("lsa_ward_merge", ptr(pools), ptr(sizes), uniform, G, P, d, bucket_count, float(bucket_cap), max_rounds,
-         ptr(labels), ptr(reached), ptr(rounds), stream())
+         ptr(labels), ptr(raw_reached), ptr(rounds), stream())
+    if reached is not None:
+        return labels, raw_reached
     if return_rounds:
-        return labels, reached.bool(), rounds
-    return labels, reached.bool()
+        return labels, raw_reached.bool(), rounds
+    return labels, raw_reached.bool()
 
 
 def bucket_table(index_keys: torch.Tensor, labels: torch.Tensor, pool_size: int, bucket_count: int,
-                 bucket_cap: int, first_position: int = 0, want_bf16: bool = False):
+                 bucket_cap: int, first_position: int = 0, want_bf16: bool = False, outs: tuple | None = None):
     """Members, sizes, key sums and centroids of every block (src/lsa/core/reference.py:120-144)."""
     keys, labels = _contig(index_keys), _contig(labels)
     G, P = labels.shape
     d = keys.shape[-1]
     rows = G * bucket_count
-    members = torch.empty(rows, bucket_cap, device=keys.device, dtype=torch.int32)
-    sizes = torch.empty(rows, device=keys.device, dtype=torch.int32)
-    key_sums = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
-    centroids = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
-    centroids_bf16 = torch.empty(rows, d, device=keys.device, dtype=torch.bfloat16) if want_bf16 else None
-    status = torch.zeros(1, device=keys.device, dtype=torch.int32)
+    if outs is not None:
+        members, sizes, key_sums, centroids, centroids_bf16, status = outs
+    else:
+        members = torch.empty(rows, bucket_cap, device=keys.device, dtype=torch.int32)
+        sizes = torch.empty(rows, device=keys.device, dtype=torch.int32)
+        key_sums = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
+        centroids = torch.empty(rows, d, device=keys.device, dtype=torch.float32)
+        centroids_bf16 = torch.empty(rows, d, device=keys.device, dtype=torch.bfloat16) if want_bf16 else None
+        status = torch.zeros(1, device=keys.device, dtype=torch.int32)
     call("lsa_bucket_table", ptr(keys), _lib.dtype_code(keys), ptr(labels), G, P, pool_size, d, bucket_count,
          bucket_cap, first_position, ptr(members), ptr(sizes), ptr(key_sums), ptr(centroids), ptr(centroids_bf16),
          ptr(status), stream())
@@ -113,12 +168,13 @@ def bucket_members(labels: torch.Tensor, pool_size: int, bucket_count: int, buck
 
 
 def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: torch.Tensor, top_p: int,
-                row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0):
+                row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0, keys: torch.Tensor | None = None,
+                picked: torch.Tensor | None = None):
     """Top-p packed keys and bucket ids of every row (src/lsa/core/reference.py:228-265)."""
     q, c = _contig(index_queries.float()), _contig(centroids.float())
     R, d = q.shape
-    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
-    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64) if keys is None else keys
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32) if picked is None else picked
     call("lsa_flat_select", ptr(q), R, d, ptr(c), c.shape[0], ptr(_contig(visible.to(torch.int32))),
          ptr(row_top_p), top_p, bucket_id_base, ptr(keys), ptr(picked), stream())
     return keys, picked
@@ -175,14 +231,18 @@ def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch
 
 def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor, top_k: int, sink: int, window: int,
            row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
-           page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None):
+           page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None,
+           outs: tuple | None = None):
     """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status)."""
     picked, members = _contig(picked), _contig(members)
     R, top_p = picked.shape
     width = top_k + window + sink
-    selected = torch.empty(R, width, device=picked.device, dtype=torch.int32)
-    lengths = torch.empty(R, device=picked.device, dtype=torch.int32)
-    status = torch.zeros(1, device=picked.device, dtype=torch.int32)
+    if outs is not None:
+        selected, lengths, status = outs
+    else:
+        selected = torch.empty(R, width, device=picked.device, dtype=torch.int32)
+        lengths = torch.empty(R, device=picked.device, dtype=torch.int32)
+        status = torch.zeros(1, device=picked.device, dtype=torch.int32)
     first, end = owner if owner is not None else (0, _lib.INT64_MAX)
     call("lsa_expand", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
          members.shape[0], members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(page_table),
@@ -192,7 +252,8 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
 
 def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.Tensor,
                   lengths: torch.Tensor | None, scale: float, splits: int = 1, out_dtype=torch.bfloat16,
-                  workspace: torch.Tensor | None = None):
+                  workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                  lse: torch.Tensor | None = None):
     """Attention of q [R, Hq, dh] over the KV rows each list names; returns (out [R, Hq, dh], lse [R, Hq])."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("q, k and v must be bfloat16")
@@ -201,9 +262,15 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
     ids = _contig(ids)
     R, Hq, dh = q.shape
     slots, Hkv, _ = k.shape
-    out_bf16 = torch.empty(R, Hq, dh, device=q.device, dtype=torch.bfloat16) if out_dtype == torch.bfloat16 else None
-    out_f32 = torch.empty(R, Hq, dh, device=q.device, dtype=torch.float32) if out_dtype == torch.float32 else None
-    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32)
+    if out is not None:
+        if out.shape != (R, Hq, dh) or not out.is_contiguous() or out.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"out must be a contiguous bfloat16 or float32 [{R}, {Hq}, {dh}]")
+        out_dtype = out.dtype
+    else:
+        out = torch.empty(R, Hq, dh, device=q.device, dtype=out_dtype)
+    out_bf16 = out if out_dtype == torch.bfloat16 else None
+    out_f32 = out if out_dtype == torch.float32 else None
+    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32) if lse is None else lse
     need = query("lsa_sparse_attend_workspace_bytes", R, Hq, dh, splits)
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, device=q.device, dtype=torch.uint8)

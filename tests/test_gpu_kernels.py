@@ -38,6 +38,50 @@ def test_index_map_matches_the_oracle(ops, oracle, T, Hq, Hkv, dh, d_idx):
     np.testing.assert_allclose(got_q16.float().cpu().numpy(), want_q, rtol=0, atol=4e-3)
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,dh,d_idx,off", [(1000, 40, 8, 128, 64, 0), (333, 8, 2, 128, 32, 0),
+                                                     (4100, 16, 4, 64, 128, 16)])
+def test_tensor_core_map_matches_the_oracle(ops, oracle, T, Hq, Hkv, dh, d_idx, off):
+    q, k, _ = layer_inputs(T, Hq, Hkv, dh, 8, 5)
+    rng = np.random.default_rng(2)
+    used = dh - off
+    w = bf16_round(rng.standard_normal((Hkv * used, d_idx), dtype=np.float32) / np.sqrt(Hkv * used))
+    want_q = oracle.project(oracle.regroup_queries(q[:, :, off:], Hkv), w)
+    want_k = oracle.project(np.ascontiguousarray(k[:, :, off:]).reshape(T, -1), w)
+    W = cuda(w, torch.bfloat16)
+    wq_t = ops.expand_map(W, Hq, Hq // Hkv, dh, off)
+    wk_t = ops.expand_map(W, Hkv, 1, dh, off)
+    assert wq_t.shape == (d_idx, Hq * dh) and wk_t.shape == (d_idx, Hkv * dh)
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    got_q = ops.index_map_tc(cuda(q, torch.bfloat16), wq_t, status=status)
+    got_k = ops.index_map_tc(cuda(k, torch.bfloat16), wk_t, status=status)
+    assert int(status) == 0
+    np.testing.assert_allclose(got_q.cpu().numpy(), want_q, rtol=0, atol=3e-5)
+    np.testing.assert_allclose(got_k.cpu().numpy(), want_k, rtol=0, atol=3e-5)
+    # it agrees with the exact-order kernel to the same bound, and not normalising leaves the raw product
+    exact = ops.index_map(cuda(q, torch.bfloat16), W, group=Hq // Hkv, dh_off=off)
+    assert (exact - got_q).abs().max() <= 3e-5
+    raw = ops.index_map_tc(cuda(k, torch.bfloat16), wk_t, normalize=False)
+    want_raw = oracle.project(np.ascontiguousarray(k[:, :, off:]).reshape(T, -1), w, normalize=False)
+    np.testing.assert_allclose(raw.cpu().numpy(), want_raw, rtol=1e-4, atol=1e-4)
+
+
+def test_two_layer_map_matches_its_restatement(ops, oracle):
+    """BASELINE-only variant (no reference code): the oracle restatement is the only pin."""
+    from scipy.special import erf
+
+    rng = np.random.default_rng(3)
+    T, d_in, d_hidden, d_idx = 700, 128, 2048, 64
+    x = bf16_round(rng.standard_normal((T, d_in), dtype=np.float32))
+    w1 = bf16_round(rng.standard_normal((d_in, d_hidden), dtype=np.float32) / np.sqrt(d_in))
+    w2 = bf16_round(rng.standard_normal((d_hidden, d_idx), dtype=np.float32) / np.sqrt(d_hidden))
+    got = ops.mlp_map(cuda(x, torch.bfloat16), cuda(w1.T.copy(), torch.bfloat16), cuda(w2.T.copy(), torch.bfloat16))
+    # the kernel keeps the hidden layer in bf16: restate with that rounding, then against the pure fp32 form
+    pre = oracle.project(x, w1, normalize=False)
+    hidden = bf16_round(0.5 * pre * (1.0 + erf(pre * np.float32(0.7071067811865476))))
+    np.testing.assert_allclose(got.cpu().numpy(), oracle.project(hidden, w2), rtol=0, atol=2e-4)
+    np.testing.assert_allclose(got.cpu().numpy(), oracle.project_mlp(x, w1, w2), rtol=0, atol=3e-3)
+
+
 def test_index_map_identity_zero_rows_and_rotary_offsets(ops, oracle):
     g = golden("index_space")
     q, k = cuda(g["q"]), cuda(g["k"])
