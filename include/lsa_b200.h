@@ -90,12 +90,17 @@ int lsa_pool_keys(const void *index_keys, int key_dtype, int64_t n_pools, int po
  *   labels     [blocks, P] int64 out - each pool's bucket, numbered by first pool
  *   reached    [blocks] uint8 out - 1 where the block got down to bucket_count
  *   rounds     [blocks] int32 out or NULL - merge rounds the block ran
- * One CTA per block; P <= 4096, d <= 256, d % 4 == 0. Costs are fp32 in the reference's evaluation order, the
- * Gram dot added in ascending dim order.
+ * Blocks of up to 512 pools are merged by one CTA out of shared memory (d <= 256, d % 4 == 0) and need no
+ * workspace. Larger blocks (up to 4,096 pools, d 16, 32 or 64: the node-bucket pairings of the tree,
+ * src/lsa/core/hierarchy.py:73-98, cluster_node_buckets at src/lsa/core/kernels/ward.py:84-110) keep their state in
+ * the caller's workspace and run two launches a round for max_rounds rounds without a host read; a block that is
+ * finished returns at once. Costs are fp32 in the reference's evaluation order, the Gram dot added in ascending
+ * dim order, so labels equal a CPU replay in that order.
  * --------------------------------------------------------------------------------------------------------- */
+size_t lsa_ward_merge_workspace_bytes(int64_t blocks, int P, int d);
 int lsa_ward_merge(const float *pool_keys, const float *pool_sizes, float uniform_pool_size, int64_t blocks, int P,
                    int d, int bucket_count, float bucket_cap, int max_rounds, int64_t *labels, uint8_t *reached,
-                   int32_t *rounds, void *stream);
+                   int32_t *rounds, void *workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Bucket table from labels. Reference: build_buckets (src/lsa/core/reference.py:120-144), members_from_labels

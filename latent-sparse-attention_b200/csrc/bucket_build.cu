@@ -292,16 +292,39 @@ LSA_API int lsa_pool_keys(const void *index_keys, int key_dtype, int64_t n_pools
   return LSA_OK;
 }
 
+namespace lsa {
+size_t ward_large_workspace_bytes(int64_t G, int P, int d);
+int ward_large_run(const float *pool_keys, const float *pool_sizes, float uniform_size, int64_t G, int P, int d,
+                   int bucket_count, float bucket_cap, int max_rounds, int64_t *labels, uint8_t *reached,
+                   int32_t *rounds, void *workspace, cudaStream_t s);
+// Blocks up to this many pools (at 64 dims) are merged by one CTA out of shared memory.
+constexpr int kWardOneCtaPools = 512;
+}  // namespace lsa
+
+LSA_API size_t lsa_ward_merge_workspace_bytes(int64_t blocks, int P, int d) {
+  if (blocks <= 0 || P <= 0 || d <= 0) return 0;
+  if (P <= lsa::kWardOneCtaPools && lsa::ward_smem_bytes(P, d) <= 227 * 1024) return 0;
+  return lsa::ward_large_workspace_bytes(blocks, P, d);
+}
+
 LSA_API int lsa_ward_merge(const float *pool_keys, const float *pool_sizes, float uniform_pool_size, int64_t blocks,
                            int P, int d, int bucket_count, float bucket_cap, int max_rounds, int64_t *labels,
-                           uint8_t *reached, int32_t *rounds, void *stream) {
+                           uint8_t *reached, int32_t *rounds, void *workspace, size_t workspace_bytes,
+                           void *stream) {
   LSA_REQUIRE(pool_keys && labels && reached, LSA_ERR_NULL);
   LSA_REQUIRE(blocks >= 0 && P >= 1 && d >= 4 && d % 4 == 0 && bucket_count >= 1 && max_rounds >= 0,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(P <= 4096 && d <= 256, LSA_ERR_UNSUPPORTED);
   if (blocks == 0) return LSA_OK;
+  const size_t need = lsa_ward_merge_workspace_bytes(blocks, P, d);
+  if (need > 0) {
+    LSA_REQUIRE(d == 16 || d == 32 || d == 64, LSA_ERR_UNSUPPORTED);
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= need, LSA_ERR_WORKSPACE);
+    return lsa::ward_large_run(pool_keys, pool_sizes, uniform_pool_size, blocks, P, d, bucket_count, bucket_cap,
+                               max_rounds, labels, reached, rounds, workspace, (cudaStream_t)stream);
+  }
   const size_t smem = lsa::ward_smem_bytes(P, d);
-  LSA_REQUIRE(smem <= 227 * 1024, LSA_ERR_UNSUPPORTED);
   cudaStream_t s = (cudaStream_t)stream;
 #define LSA_WARD_LAUNCH(DD)                                                                                       \
   do {                                                                                                            \

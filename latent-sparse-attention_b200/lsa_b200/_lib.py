@@ -30,7 +30,8 @@ SIGNATURES = {
     "lsa_index_map_tc": (_I, [_P, _L, _L, _L, _P, _I, _I, _P, _P, _P, _P]),
     "lsa_gemm_gelu_tc": (_I, [_P, _L, _L, _L, _P, _L, _P, _P, _P]),
     "lsa_pool_keys": (_I, [_P, _I, _L, _I, _I, _P, _P]),
-    "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P]),
+    "lsa_ward_merge_workspace_bytes": (_Z, [_L, _I, _I]),
+    "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P, _Z, _P]),
     "lsa_bucket_table": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),
     "lsa_flat_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _I, c_int32, _P, _P, _P]),
     "lsa_flat_select_decode_workspace_bytes": (_Z, [_L, _I, _I]),

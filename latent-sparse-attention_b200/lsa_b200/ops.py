@@ -108,7 +108,7 @@ def pool_keys(index_keys: torch.Tensor, pool_size: int, out: torch.Tensor | None
 
 def ward_rounds(pools: torch.Tensor, pool_sizes: torch.Tensor | float, bucket_count: int, bucket_cap: float,
                 max_rounds: int = 256, return_rounds: bool = False, labels: torch.Tensor | None = None,
-                reached: torch.Tensor | None = None):
+                reached: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
     """`ward_rounds` (src/lsa/core/ward.py:29-90): labels [G, P] int64 and whether each block reached its count."""
     pools = _contig(pools)
     if pools.dim() != 3 or pools.dtype != torch.float32:
@@ -124,8 +124,12 @@ def ward_rounds(pools: torch.Tensor, pool_sizes: torch.Tensor | float, bucket_co
     labels = torch.empty(G, P, device=pools.device, dtype=torch.int64) if labels is None else labels
     raw_reached = torch.empty(G, device=pools.device, dtype=torch.uint8) if reached is None else reached
     rounds = torch.empty(G, device=pools.device, dtype=torch.int32) if return_rounds else None
+    need = query("lsa_ward_merge_workspace_bytes", G, P, d)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=pools.device, dtype=torch.uint8)
     call("lsa_ward_merge", ptr(pools), ptr(sizes), uniform, G, P, d, bucket_count, float(bucket_cap), max_rounds,
-         ptr(labels), ptr(raw_reached), ptr(rounds), stream())
+         ptr(labels), ptr(raw_reached), ptr(rounds), ptr(workspace) if need else None, need, stream(),
+         launches=1 if not need else 2 + 2 * max_rounds)
     if reached is not None:
         return labels, raw_reached
     if return_rounds:

@@ -126,6 +126,20 @@ def test_ward_labels_are_bit_exact(ops, oracle, G, P, d, pool, count, cap):
     assert torch.equal(got, got2)
 
 
+@pytest.mark.parametrize("G,P,d,count,cap,sizes", [(3, 1024, 64, 512, 2.0, 1.0), (2, 2048, 16, 1024, 2.0, 1.0),
+                                                     (2, 768, 64, 96, 64.0, 4.0), (1, 640, 32, 600, 2.0, 1.0)])
+def test_large_block_ward_is_bit_exact(ops, oracle, G, P, d, count, cap, sizes):
+    """Blocks past one CTA's shared memory: the multi-launch merge (the tree's pairings at a cap of two, and a
+    general cap), against the oracle label for label and round for round."""
+    keys = unit_rows(mixture(G * P, d, 40, 0.4, P + d)).reshape(G, P, d) * np.float32(3.0)
+    size_rows = np.full((G, P), sizes, dtype=np.float32)
+    want, want_reached, want_rounds = oracle.ward_rounds(keys, size_rows, count, cap, return_rounds=True)
+    got, reached, rounds = ops.ward_rounds(cuda(keys), sizes, count, cap, return_rounds=True)
+    assert np.array_equal(got.cpu().numpy(), want)
+    assert np.array_equal(reached.cpu().numpy(), want_reached)
+    assert np.array_equal(rounds.cpu().numpy(), want_rounds)
+
+
 def test_ward_golden_and_adversarial_cases(ops, oracle):
     g = golden("ward")
     for tag in "abcde":
