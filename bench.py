@@ -218,13 +218,18 @@ def run_ours(args, cfg: dict) -> dict:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     host = make_inputs(cfg, pin=True)
     q_h, k_h, v_h, wq, wk = host
-    layer = FlatLayer(design_of(cfg), wq.cuda(), wk.cuda(), cfg["heads"], cfg["kv_heads"], cfg["head_dim"])
+    base = FlatLayer(design_of(cfg), wq.cuda(), wk.cuda(), cfg["heads"], cfg["kv_heads"], cfg["head_dim"])
+    layer = base
     if world > 1:
-        from lsa_b200.parallel import ShardedFlatLayer
+        from lsa_b200.parallel import ShardedFlatLayer, owned_positions
 
-        layer = ShardedFlatLayer(layer, rank, world)
+        # queries are replicated; a rank holds only its own run of KV rows, on the host and on the device
+        layer = ShardedFlatLayer(base, rank, world)
+        lo, hi = owned_positions(cfg["tokens"], cfg["cluster_block_size"], rank, world)
+        k_h, v_h = k_h[lo:hi].clone().pin_memory(), v_h[lo:hi].clone().pin_memory()
     q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
-    out_h = torch.empty_like(q_h).pin_memory()
+    out_d = torch.empty(cfg["tokens"] // world, cfg["heads"], cfg["head_dim"], dtype=torch.bfloat16, device="cuda")
+    out_h = torch.empty(out_d.shape, dtype=torch.bfloat16).pin_memory()
 
     def barrier():
         if world > 1:
@@ -244,7 +249,6 @@ def run_ours(args, cfg: dict) -> dict:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms) / steps
 
-    out_d = torch.empty_like(q)
     q_in, k_in, v_in = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
     def resident_step():
@@ -258,17 +262,19 @@ def run_ours(args, cfg: dict) -> dict:
 
     for _ in range(args.warmup):
         resident_step()
-    # One more untimed pass counts the gathered keys the roofline figure needs, and keeps what the CPU baseline reads.
-    out, index = layer.prefill(q, k, v, chunk=cfg["chunk"], return_index=True)
-    gathered = 0
-    index_q = layer.index_queries(q)
-    for start in range(0, cfg["tokens"], cfg["chunk"]):
-        pos = torch.arange(start, min(cfg["tokens"], start + cfg["chunk"]), device="cuda")
-        _, lengths = layer.select(index_q[start:start + cfg["chunk"]], pos, index)
-        window_start = (pos + 1 - cfg["window_size"]).clamp_min(0)
-        fixed = (pos + 1 - window_start) + torch.minimum(window_start, torch.full_like(pos, cfg["sink_size"]))
-        gathered += int((lengths.to(torch.int64) - fixed).sum())
-    del out
+    gathered, index, index_q = None, None, None
+    if world == 1:
+        # One more untimed pass counts the gathered keys the roofline figure needs, and keeps what the CPU baseline
+        # reads.
+        _, index = base.prefill(q, k, v, chunk=cfg["chunk"], return_index=True)
+        gathered = 0
+        index_q = base.index_queries(q)
+        for start in range(0, cfg["tokens"], cfg["chunk"]):
+            pos = torch.arange(start, min(cfg["tokens"], start + cfg["chunk"]), device="cuda")
+            _, lengths = base.select(index_q[start:start + cfg["chunk"]], pos, index)
+            window_start = (pos + 1 - cfg["window_size"]).clamp_min(0)
+            fixed = (pos + 1 - window_start) + torch.minimum(window_start, torch.full_like(pos, cfg["sink_size"]))
+            gathered += int((lengths.to(torch.int64) - fixed).sum())
 
     recorder = probe.CudaEventRecorder()
     probe.install(recorder)
@@ -289,8 +295,10 @@ def run_ours(args, cfg: dict) -> dict:
         peak, peak_kind = json.load(open(peaks_path))["hbm_gbs"], "measured"
     else:
         peak, peak_kind = 6650.0, "fallback"
-    per_launch_bytes = attend_algorithmic_bytes(cfg, gathered) / max(1, attend_launches // args.steps)
-    achieved = per_launch_bytes / (attend_ms / max(1, attend_launches) * 1e-3) / 1e9 if attend_launches else None
+    per_launch_bytes = achieved = None
+    if gathered is not None and attend_launches:
+        per_launch_bytes = attend_algorithmic_bytes(cfg, gathered) / max(1, attend_launches // args.steps)
+        achieved = per_launch_bytes / (attend_ms / attend_launches * 1e-3) / 1e9
     result = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -302,8 +310,8 @@ def run_ours(args, cfg: dict) -> dict:
                    "l2": "inputs (1.9 GB of q, k, v per step) exceed the 126 MB L2",
                    "parallelism": "1 GPU" if world == 1 else f"sequence-sharded KV and index over {world} GPUs"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2,
-                "d2h_bytes_per_step": out_h.numel() * 2, "ms_per_step": e2e_ms},
+                "h2d_bytes_per_step": (q_h.numel() * world + (k_h.numel() + v_h.numel()) * world) * 2,
+                "d2h_bytes_per_step": out_h.numel() * world * 2, "ms_per_step": e2e_ms},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
         "roofline": {"kernel": "sparse_attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,

@@ -119,6 +119,15 @@ int lsa_bucket_table(const void *index_keys, int key_dtype, const int64_t *label
                      uint16_t *centroids_bf16, int32_t *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Sums of gathered rows, in a fixed order: out[r, :] = sum_c src[index[r, c] - index_base, :], added one by one in
+ * column order, an index < 0 ending the row. The key sums under buckets and node buckets that the tree build takes
+ * (src/lsa/core/hierarchy.py:134-136, 95-97, 157).
+ *   src [*, d] of src_dtype; index [rows, width] int32 or int64 (index_is_int64); out [rows, d] fp32
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_gather_sum(const void *src, int src_dtype, const void *index, int index_is_int64, int64_t rows, int width,
+                   int d, int64_t index_base, float *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Flat search, prefill form: score every visible bucket, keep the top_p packed keys of each row.
  * Reference: read / _read_row (src/lsa/core/reference.py:228-265); served Selector.read_flat
  * (src/lsa/sglang/index/selector.py:370-423), ScanSelect (src/lsa/core/kernels/scan_select.py:189-385), packed
@@ -195,16 +204,19 @@ int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *posit
  * Reference: topk_attention / keep_set (src/lsa/core/attention.py:15-146); served sparse_read, partial_read
  * (src/lsa/sglang/models/qwen3_5/backend.py:427-460, 669-721).
  *   q      [R, Hq, dh] bf16 (q_row_stride, q_head_stride); dh = 64 or 128; Hq/Hkv <= 16
- *   k, v   [slots, Hkv, dh] bf16 (kv_row_stride, kv_head_stride), 16-byte aligned rows
+ *   k, v   [slots, Hkv, dh] bf16 (kv_row_stride, kv_head_stride), 16-byte aligned rows; they hold the KV rows
+ *          first_slot .. first_slot + slots - 1 (a rank's share of a sequence-sharded cache; 0 for a whole one)
  *   ids    [R, list_stride] int32 - the first lengths[r] entries are read, each one once: KV rows (slots) the
- *          caller guarantees causal and distinct, as lsa_expand writes them; an entry < 0 or >= slots is skipped
+ *          caller guarantees causal and distinct, as lsa_expand writes them; an entry outside
+ *          [first_slot, first_slot + slots) is skipped
  *   splits CTAs-per-(row, KV head) the list is divided over; > 1 needs the workspace and runs the merge kernel
  *   out    [R, Hq, dh] bf16 (out_bf16) and/or fp32 (out_f32); lse [R, Hq] fp32 or NULL
  * A row that reads nothing gives zeros and lse = -inf.
  * --------------------------------------------------------------------------------------------------------- */
 size_t lsa_sparse_attend_workspace_bytes(int64_t R, int Hq, int dh, int splits);
 int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
-                      const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv, int64_t kv_row_stride,
+                      const uint16_t *k, const uint16_t *v, int64_t slots, int64_t first_slot, int Hkv,
+                      int64_t kv_row_stride,
                       int64_t kv_head_stride, const int32_t *ids, int64_t list_stride, const int32_t *lengths,
                       float scale, int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
                       size_t workspace_bytes, void *stream);
@@ -226,8 +238,9 @@ int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_ro
  *     (different streams) race on it: serialise them. */
 size_t lsa_sparse_attend_static_scratch_bytes(void);
 int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
-                             int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv,
-                             int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
+                             int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots,
+                             int64_t first_slot, int Hkv, int64_t kv_row_stride, int64_t kv_head_stride,
+                             const int32_t *ids, int64_t list_stride,
                              const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
                              float *lse, void *stream);
 

@@ -17,7 +17,7 @@ struct AttendParams {
   const int32_t *ids, *lengths;
   uint16_t *out_bf16;
   float *out_f32, *lse, *part_out, *part_lse;
-  int64_t R, slots, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride, list_stride;
+  int64_t R, slots, first_slot, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride, list_stride;
   int Hq, Hkv, group, splits;
   float scale_log2;
 };
@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(W * 32, 1) sparse_attend_kernel(AttendParams p
   auto issue = [&](int it, int32_t id) {
     if (it < iters) {
       const int stage = it % STAGES;
+      id -= (int32_t)p.first_slot;  // k and v point at the row of slot first_slot
       const uint32_t valid = __ballot_sync(0xffffffffu, id >= 0 && id < p.slots);
       if (lane == 0) masks[stage] = valid;
       const uint32_t k_dst = smem_base + stage * STAGE_BYTES;
@@ -368,12 +369,14 @@ LSA_API int lsa_lse_merge(const float *parts, const float *lses, int n_parts, in
 }
 
 LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
-                              int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv,
+                              int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int64_t first_slot,
+                              int Hkv,
                               int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
                               const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
                               float *lse, void *workspace, size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && k && v && ids && (out_bf16 || out_f32), LSA_ERR_NULL);
-  LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && slots >= 0 && list_stride >= 0 && splits >= 1,
+  LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && slots >= 0 && first_slot >= 0 &&
+                  first_slot + slots <= INT32_MAX && list_stride >= 0 && splits >= 1,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(dh == 64 || dh == 128, LSA_ERR_UNSUPPORTED);
   const int group = Hq / Hkv;
@@ -397,6 +400,7 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   p.part_lse = nullptr;
   p.R = R;
   p.slots = slots;
+  p.first_slot = first_slot;
   p.q_row_stride = q_row_stride;
   p.q_head_stride = q_head_stride;
   p.kv_row_stride = kv_row_stride;
@@ -441,7 +445,7 @@ LSA_API size_t lsa_sparse_attend_static_scratch_bytes(void) { return LSA_STATIC_
 
 LSA_API int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
                                      int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots,
-                                     int Hkv, int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids,
+                                     int64_t first_slot, int Hkv, int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids,
                                      int64_t list_stride, const int32_t *lengths, float scale, int splits,
                                      uint16_t *out_bf16, float *out_f32, float *lse, void *stream) {
   LSA_REQUIRE(R >= 0 && Hq >= 1 && dh >= 1 && splits >= 1, LSA_ERR_ARGUMENT);
@@ -458,7 +462,7 @@ LSA_API int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int d
     }
     static_scratch_address[device] = scratch;
   }
-  return lsa_sparse_attend(q, R, Hq, dh, q_row_stride, q_head_stride, k, v, slots, Hkv, kv_row_stride, kv_head_stride,
+  return lsa_sparse_attend(q, R, Hq, dh, q_row_stride, q_head_stride, k, v, slots, first_slot, Hkv, kv_row_stride, kv_head_stride,
                            ids, list_stride, lengths, scale, splits, out_bf16, out_f32, lse, scratch,
                            LSA_STATIC_SCRATCH_BYTES, stream);
 }

@@ -381,3 +381,57 @@ LSA_API int lsa_bucket_table(const void *index_keys, int key_dtype, const int64_
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
+
+// ================================================================================================ gathered sums
+
+namespace lsa {
+
+// out[r, :] = sum over c of src[index[r, c] - index_base, :], added one by one in column order; an index < 0 ends
+// the row. A thread a (row, dim): reads of a source row are coalesced across the dims.
+template <typename TS, typename TI>
+__global__ void gather_sum_kernel(const TS *__restrict__ src, const TI *__restrict__ index, int64_t rows, int width,
+                                  int d, int64_t index_base, float *__restrict__ out) {
+  const int64_t total = rows * d;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / d;
+    const int c = (int)(e - r * d);
+    float acc = 0.0f;
+    for (int j = 0; j < width; ++j) {
+      const int64_t id = (int64_t)index[r * width + j];
+      if (id < 0) break;
+      acc = __fadd_rn(acc, load_as_float<TS>(src, (id - index_base) * d + c));
+    }
+    out[e] = acc;
+  }
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_gather_sum(const void *src, int src_dtype, const void *index, int index_is_int64, int64_t rows,
+                           int width, int d, int64_t index_base, float *out, void *stream) {
+  LSA_REQUIRE(src && index && out, LSA_ERR_NULL);
+  LSA_REQUIRE(rows >= 0 && width >= 1 && d >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(src_dtype == LSA_DTYPE_F32 || src_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
+  if (rows == 0) return LSA_OK;
+  const int threads = 256;
+  const int64_t want = (rows * d + threads - 1) / threads;
+  const int grid = (int)(want < (int64_t)lsa::sm_count() * 16 ? want : (int64_t)lsa::sm_count() * 16);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (src_dtype == LSA_DTYPE_F32) {
+    if (index_is_int64)
+      lsa::gather_sum_kernel<float, int64_t><<<grid, threads, 0, s>>>((const float *)src, (const int64_t *)index, rows,
+                                                                      width, d, index_base, out);
+    else
+      lsa::gather_sum_kernel<float, int32_t><<<grid, threads, 0, s>>>((const float *)src, (const int32_t *)index, rows,
+                                                                      width, d, index_base, out);
+  } else {
+    if (index_is_int64)
+      lsa::gather_sum_kernel<uint16_t, int64_t><<<grid, threads, 0, s>>>((const uint16_t *)src, (const int64_t *)index,
+                                                                         rows, width, d, index_base, out);
+    else
+      lsa::gather_sum_kernel<uint16_t, int32_t><<<grid, threads, 0, s>>>((const uint16_t *)src, (const int32_t *)index,
+                                                                         rows, width, d, index_base, out);
+  }
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}

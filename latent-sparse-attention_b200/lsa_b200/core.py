@@ -307,3 +307,9 @@ def topk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, selected_k
                                    out_dtype=torch.float32)
         out[b] = res.to(q.dtype)
     return out
+
+
+# The hierarchy's half of the operator API lives in its own module; it is re-exported here so that
+# `from lsa_b200.core import build_hierarchy, read_hierarchy` reads as the reference's `lsa.core` does.
+from lsa_b200.hierarchy import (Hierarchy, build_hierarchy, growth_at, pair_into_node_buckets,  # noqa: E402,F401
+                                read_hierarchy, read_hierarchy_counted)

@@ -171,6 +171,18 @@ def bucket_members(labels: torch.Tensor, pool_size: int, bucket_count: int, buck
     return members, sizes
 
 
+def gather_sum(src: torch.Tensor, index: torch.Tensor, index_base: int = 0) -> torch.Tensor:
+    """out[r] = the rows src[index[r, c] - index_base] added one by one in column order (an index < 0 ends the row).
+    The key sums under buckets and node buckets (src/lsa/core/hierarchy.py:134-136, 157)."""
+    src, index = _contig(src), _contig(index)
+    if index.dtype not in (torch.int32, torch.int64) or index.dim() != 2:
+        raise ValueError("index must be an int32 or int64 matrix")
+    out = torch.empty(index.shape[0], src.shape[-1], device=src.device, dtype=torch.float32)
+    call("lsa_gather_sum", ptr(src), _lib.dtype_code(src), ptr(index), int(index.dtype == torch.int64),
+         index.shape[0], index.shape[1], src.shape[-1], index_base, ptr(out), stream())
+    return out
+
+
 def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: torch.Tensor, top_p: int,
                 row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0, keys: torch.Tensor | None = None,
                 picked: torch.Tensor | None = None):
@@ -257,8 +269,9 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
 def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.Tensor,
                   lengths: torch.Tensor | None, scale: float, splits: int = 1, out_dtype=torch.bfloat16,
                   workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
-                  lse: torch.Tensor | None = None):
-    """Attention of q [R, Hq, dh] over the KV rows each list names; returns (out [R, Hq, dh], lse [R, Hq])."""
+                  lse: torch.Tensor | None = None, first_slot: int = 0):
+    """Attention of q [R, Hq, dh] over the KV rows each list names; returns (out [R, Hq, dh], lse [R, Hq]).
+    `k`, `v` hold the KV rows from `first_slot` on (a rank's share of a sharded cache); other ids are skipped."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("q, k and v must be bfloat16")
     if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
@@ -278,7 +291,8 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
     need = query("lsa_sparse_attend_workspace_bytes", R, Hq, dh, splits)
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
-    call("lsa_sparse_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, Hkv, k.stride(0),
+    call("lsa_sparse_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, first_slot, Hkv,
+         k.stride(0),
          k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits, ptr(out_bf16), ptr(out_f32),
          ptr(lse), ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0,
          stream(), launches=1 if splits == 1 else 2)

@@ -1,0 +1,91 @@
+"""The tree on the GPU: node bucket levels and the beam read against the reference's golden vectors and the oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+from helpers import cuda, mixture, unit_rows
+
+pytestmark = pytest.mark.gpu
+
+
+def _golden_store():
+    from lsa_b200 import core
+
+    g = golden("hierarchy")
+    sizes = (g["members"] >= 0).sum(1).astype(np.int32)
+    buckets = core.Buckets(cuda(g["centroids"]), cuda(g["members"]), cuda(sizes), 8, 64)
+    return g, buckets
+
+
+def test_levels_match_the_reference():
+    from lsa_b200 import core
+
+    g, buckets = _golden_store()
+    tree = core.build_hierarchy(cuda(g["keys"]), buckets, 16, 4, 16)
+    assert [len(c) for c in tree.children] == [256, 64, 16, 4]
+    for level in range(4):
+        assert np.array_equal(tree.children[level].cpu().numpy(), g[f"children_{level}"])
+        np.testing.assert_allclose(tree.node_centroids[level].cpu().numpy(), g[f"node_centroids_{level}"], rtol=0,
+                                   atol=2e-6)
+    rows = [(closed, growth) for closed in (0, 64, 128, 512, 1024) for growth in (0, 64, 100)]
+    for (closed, growth), want in zip(rows, g["growth"]):
+        grown = core.growth_at(tree, closed, 64, growth)
+        assert [grown.covered_buckets, *grown.made, *grown.closed] == want.tolist()
+    with pytest.raises(ValueError, match="power of two"):
+        core.build_hierarchy(cuda(g["keys"]), buckets, 2, 3, 12)
+    with pytest.raises(ValueError, match="multiple"):
+        core.build_hierarchy(cuda(g["keys"]), buckets, 2, 4, 18)
+
+
+@pytest.mark.parametrize("tag,beam,start,growth", [("wide", 4096, None, 0), ("narrow", 2, None, 0),
+                                                   ("start", 3, 8, 0), ("wait", 2, None, 64)])
+def test_beam_read_matches_the_reference(tag, beam, start, growth):
+    from lsa_b200 import core
+
+    g, buckets = _golden_store()
+    levels = int(g["levels"])
+    tree = core.Hierarchy([cuda(g[f"node_centroids_{i}"]) for i in range(levels)],
+                          [cuda(g[f"children_{i}"]) for i in range(levels)], [], None, 4,
+                          tuple(g["block_sizes"].tolist()))
+    sel, lens, scored = core.read_hierarchy_counted(cuda(g["queries"]), cuda(g["positions"]), buckets, tree, beam,
+                                                    start, 16, 64, 4, 64, 512, growth)
+    assert np.array_equal(lens.cpu().numpy(), g[f"lengths_{tag}"])
+    assert np.array_equal(sel.cpu().numpy(), g[f"selected_{tag}"])
+    assert np.array_equal(scored.cpu().numpy(), g[f"scored_{tag}"])
+    with pytest.raises(ValueError, match="multiple of cluster_block_size"):
+        core.read_hierarchy(cuda(g["queries"]), cuda(g["positions"]), buckets, tree, beam, start, 16, 64, 4, 64, 500,
+                            growth)
+
+
+def test_a_tree_over_large_node_blocks_is_bit_exact_with_the_oracle(oracle):
+    """Node cluster blocks of 1,024 buckets (the multi-launch pairing), two levels, then a narrow beam."""
+    from lsa_b200 import core
+
+    T, d = 32768 + 300, 64
+    raw = mixture(T, d, 48, 0.35, 17)
+    keys = unit_rows(raw)
+    want_buckets = oracle.build_buckets(keys, 4, 16, 32, 512)
+    buckets = core.Buckets(cuda(want_buckets.bucket_centroids), cuda(want_buckets.bucket_members),
+                           cuda(want_buckets.bucket_sizes), 32, 512)
+    want = oracle.build_hierarchy(keys, want_buckets, 2, 8, (1024, 64))
+    tree = core.build_hierarchy(cuda(keys), buckets, 2, 8, (1024, 64))
+    assert [len(c) for c in tree.children] == [256, 32] == [len(c) for c in want.children]
+    for level in range(2):
+        assert np.array_equal(tree.children[level].cpu().numpy(), want.children[level])
+        np.testing.assert_allclose(tree.node_centroids[level].cpu().numpy(), want.node_centroids[level], rtol=0,
+                                   atol=1e-6)
+    rng = np.random.default_rng(3)
+    positions = np.sort(rng.integers(0, T, 40))
+    queries = unit_rows(raw[positions] + 0.4 * rng.standard_normal((40, d), dtype=np.float32))
+    # the read continues from the device's own node centroids, so the picks must be the oracle's
+    mine = oracle.Hierarchy([c.cpu().numpy() for c in tree.node_centroids], [c.cpu().numpy() for c in tree.children],
+                            8, (1024, 64))
+    for beam, start, growth in ((4, None, 0), ((6, 2), 16, 1024)):
+        want_sel, want_len, _, want_scored = oracle.read_hierarchy(queries, positions, want_buckets, mine, beam, start,
+                                                                   24, 256, 4, 512, 8192, growth, return_picked=True)
+        sel, lens, scored = core.read_hierarchy_counted(cuda(queries), cuda(positions), buckets, tree, beam, start, 24,
+                                                        256, 4, 512, 8192, growth)
+        assert np.array_equal(lens.cpu().numpy(), want_len) and np.array_equal(sel.cpu().numpy(), want_sel)
+        assert np.array_equal(scored.cpu().numpy(), want_scored)

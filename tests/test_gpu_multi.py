@@ -1,0 +1,63 @@
+"""The sequence-sharded layer on real GPUs over NCCL: every rank's rows of the output against the single-GPU layer.
+Needs two or more GPUs in the box; one process a GPU, spawned as children."""
+
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import PACKAGE_DIR, ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, result_dir):
+    for path in (ROOT, PACKAGE_DIR, os.path.join(ROOT, "tests")):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from helpers import bf16_round, cuda, layer_inputs
+        from lsa_b200.layer import FlatDesign, FlatLayer
+        from lsa_b200.parallel import ShardedFlatLayer, owned_positions
+
+        T, Hq, Hkv, dh, chunk = 8192, 40, 8, 128, 1024
+        design = FlatDesign(pool_size=16, bucket_size=32, bucket_cap=64, cluster_block_size=512, top_p=8, top_k=300,
+                            sink_size=4, window_size=512)
+        rng = np.random.default_rng(0)
+        w = bf16_round(rng.standard_normal((2, Hkv * dh, 64), dtype=np.float32) / np.sqrt(Hkv * dh))
+        layer = FlatLayer(design, cuda(w[0], torch.bfloat16), cuda(w[1], torch.bfloat16), Hq, Hkv, dh)
+        q, k, v = (cuda(a, torch.bfloat16) for a in layer_inputs(T, Hq, Hkv, dh, 32, 1))
+        want = layer.prefill(q, k, v, chunk=chunk)
+        lo, hi = owned_positions(T, design.cluster_block_size, rank, world)
+        sharded = ShardedFlatLayer(layer, rank, world)
+        got = sharded.prefill(q, k[lo:hi].contiguous(), v[lo:hi].contiguous(), chunk=chunk)
+        share = chunk // world
+        mine = torch.cat([want[c * chunk + rank * share: c * chunk + (rank + 1) * share] for c in range(T // chunk)])
+        err = (got.float() - mine.float()).abs()
+        assert got.shape == mine.shape
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_prefill_matches_the_single_gpu_layer(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two or more GPUs")
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]

@@ -33,7 +33,7 @@ def _static(q, k, v, ids, lengths, scale, splits):
     out = torch.empty(R, Hq, dh, device=q.device, dtype=torch.float32)
     lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32)
     call("lsa_sparse_attend_static", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), k.shape[0],
-         k.shape[1], k.stride(0), k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), scale, splits, None, ptr(out),
+         0, k.shape[1], k.stride(0), k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), scale, splits, None, ptr(out),
          ptr(lse), stream(), launches=2 if splits > 1 else 1)
     return out, lse
 
