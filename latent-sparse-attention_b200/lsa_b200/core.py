@@ -230,15 +230,10 @@ def build_buckets(index_keys: torch.Tensor, pool_size: int, bucket_size: int, bu
     return Buckets(centroids, members, sizes, per_block, cluster_block_size)
 
 
-def read(index_queries: torch.Tensor, positions: torch.Tensor, buckets: Buckets, top_p: int, top_k: int,
-         sink_size: int, window_size: int, shapes=None, deviations: float = 0.0,
-         early_budget: EarlyBudget | None = None):
-    """Select the keys each query reads: score, pick the top_p buckets, expand (reference.py:167-236).
-
-    Returns selected ids [Tq, top_k + window + sink] int32 (-1 padded; expansion, window, sinks) and lengths [Tq].
-    """
-    if shapes is not None:
-        raise NotImplementedError("bucket shapes are not built in lsa_b200")
+def check_read_arguments(index_queries, positions, buckets, top_p, top_k, sink_size, window_size,
+                         early_budget=None) -> None:
+    """The refusals of `read` (reference.py:209-224): unit rows of the buckets' dim, one non-negative integer
+    position a query, positive sizes, an early budget within the read's own."""
     check_unit_rows("index_queries", index_queries)
     if index_queries.shape[1] != buckets.bucket_centroids.shape[1]:
         raise ValueError(
@@ -252,6 +247,18 @@ def read(index_queries: torch.Tensor, positions: torch.Tensor, buckets: Buckets,
     if early_budget is not None and (early_budget.top_p > top_p or early_budget.top_k > top_k):
         raise ValueError(f"the early budget is at most top_p {top_p} and top_k {top_k} - "
                          f"got top_p {early_budget.top_p} and top_k {early_budget.top_k}")
+
+
+def read(index_queries: torch.Tensor, positions: torch.Tensor, buckets: Buckets, top_p: int, top_k: int,
+         sink_size: int, window_size: int, shapes=None, deviations: float = 0.0,
+         early_budget: EarlyBudget | None = None):
+    """Select the keys each query reads: score, pick the top_p buckets, expand (reference.py:167-236).
+
+    Returns selected ids [Tq, top_k + window + sink] int32 (-1 padded; expansion, window, sinks) and lengths [Tq].
+    """
+    if shapes is not None:
+        raise NotImplementedError("bucket shapes are not built in lsa_b200")
+    check_read_arguments(index_queries, positions, buckets, top_p, top_k, sink_size, window_size, early_budget)
     positions = positions.to(torch.int64)
     visible = (positions // buckets.cluster_block_size * buckets.block_bucket_count).clamp_max(
         buckets.bucket_centroids.shape[0]).to(torch.int32)

@@ -16,7 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from lsa_b200 import ops
-from lsa_b200.core import CLUSTER_ALGORITHMS, Buckets, check_unit_rows, read
+from lsa_b200.core import CLUSTER_ALGORITHMS, Buckets, check_read_arguments, check_unit_rows
 
 BUCKET_SCORES = ("centroid", "lse")
 
@@ -179,8 +179,7 @@ def read_hierarchy_counted(index_queries, positions, buckets, hierarchy, beam_wi
     Returns selected ids [Tq, top_k + window + sink] int32 (-1 padded), lengths [Tq] int32, and the vectors each
     row scored [Tq] int64.
     """
-    read(index_queries[:0], positions[:0], buckets, top_p, top_k, sink_size, window_size)  # the boundary's checks
-    check_unit_rows("index_queries", index_queries)
+    check_read_arguments(index_queries, positions, buckets, top_p, top_k, sink_size, window_size)
     if page_size % buckets.cluster_block_size:
         raise ValueError(f"page_size {page_size} must be a multiple of cluster_block_size {buckets.cluster_block_size}")
     if node_bucket_score not in BUCKET_SCORES or bucket_score not in BUCKET_SCORES:
