@@ -221,12 +221,11 @@ def run_ours(args, cfg: dict) -> dict:
     base = FlatLayer(design_of(cfg), wq.cuda(), wk.cuda(), cfg["heads"], cfg["kv_heads"], cfg["head_dim"])
     layer = base
     if world > 1:
-        from lsa_b200.parallel import ShardedFlatLayer, owned_positions
+        from lsa_b200.parallel import ShardedFlatLayer, deal
 
-        # queries are replicated; a rank holds only its own run of KV rows, on the host and on the device
+        # queries are replicated; a rank holds only its own share of the KV rows, on the host and on the device
         layer = ShardedFlatLayer(base, rank, world)
-        lo, hi = owned_positions(cfg["tokens"], cfg["cluster_block_size"], rank, world)
-        k_h, v_h = k_h[lo:hi].clone().pin_memory(), v_h[lo:hi].clone().pin_memory()
+        k_h, v_h = deal(k_h, rank, world).clone().pin_memory(), deal(v_h, rank, world).clone().pin_memory()
     q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
     out_d = torch.empty(cfg["tokens"] // world, cfg["heads"], cfg["head_dim"], dtype=torch.bfloat16, device="cuda")
     out_h = torch.empty(out_d.shape, dtype=torch.bfloat16).pin_memory()
@@ -308,7 +307,7 @@ def run_ours(args, cfg: dict) -> dict:
                    "top_p": cfg["top_p"], "top_k": cfg["top_k"], "window": cfg["window_size"],
                    "sink": cfg["sink_size"], "chunk": cfg["chunk"],
                    "l2": "inputs (1.9 GB of q, k, v per step) exceed the 126 MB L2",
-                   "parallelism": "1 GPU" if world == 1 else f"sequence-sharded KV and index over {world} GPUs"},
+                   "parallelism": "1 GPU" if world == 1 else f"KV rows and cluster blocks dealt round-robin over {world} GPUs (context parallel)"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": (q_h.numel() * world + (k_h.numel() + v_h.numel()) * world) * 2,
                 "d2h_bytes_per_step": out_h.numel() * world * 2, "ms_per_step": e2e_ms},

@@ -189,6 +189,9 @@ int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, 
  *   row_top_p / row_top_k [R] int32 or NULL - a row's own budget
  *   page_table [pages] int32 or NULL with page_size - when given every id is stored as the KV slot
  *              page_table[id / page_size] * page_size + id % page_size instead of the position
+ *   owner_granule/owner_world/owner_rank - with owner_world > 1 the cache is dealt out round-robin in granules of
+ *              owner_granule positions: only ids with (id / granule) % world == rank are written, and each is
+ *              stored as its row in that rank's own cache, id / (granule*world) * granule + id % granule
  *   owner_first/owner_end - only ids in [owner_first, owner_end) are written (a rank's share of the sequence);
  *              the top_k cut still counts every id. Pass 0 and INT64_MAX for all.
  *   selected   [R, top_k + window + sink] int32 out - expansion, window ascending, sinks ascending, -1 padded
@@ -197,7 +200,8 @@ int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, 
 int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions, const int32_t *members,
                int64_t m, int bucket_cap, const int32_t *row_top_p, const int32_t *row_top_k, int top_k,
                int sink, int window, const int32_t *page_table, int page_size, int64_t owner_first,
-               int64_t owner_end, int32_t *selected, int32_t *lengths, int32_t *status, void *stream);
+               int64_t owner_end, int owner_granule, int owner_world, int owner_rank, int32_t *selected,
+               int32_t *lengths, int32_t *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Gather-sparse attention over each row's list, with the log-sum-exp of the scaled logits.

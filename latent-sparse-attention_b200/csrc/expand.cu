@@ -17,12 +17,36 @@ struct ExpandParams {
   int32_t *lengths;           // [R]
   int32_t *status;
   int64_t R, m, owner_first, owner_end;
-  int top_p, cap, top_k, sink, window, page_size, width;
+  int top_p, cap, top_k, sink, window, page_size, width, granule, world, rank;
 };
 
+// Whether this caller keeps an id: inside its contiguous range and, when the cache is dealt out in granules of
+// positions round-robin over `world` ranks, in one of its granules.
+__device__ __forceinline__ bool owned(const ExpandParams &p, int64_t id) {
+  if (id < p.owner_first || id >= p.owner_end) return false;
+  return p.world <= 1 || (int)((id / p.granule) % p.world) == p.rank;
+}
+
+// What is written for an id: the position, its row in the rank's own cache when granules are dealt out, or its KV
+// slot through the page table.
 __device__ __forceinline__ int32_t stored_id(const ExpandParams &p, int64_t id) {
+  if (p.world > 1) id = id / ((int64_t)p.granule * p.world) * p.granule + id % p.granule;
   if (!p.page_table) return (int32_t)id;
   return p.page_table[id / p.page_size] * p.page_size + (int32_t)(id % p.page_size);
+}
+
+// Append the owned ids of [first, end) to out[written..], in order; returns the new count.
+__device__ __forceinline__ int append_run(const ExpandParams &p, int32_t *out, int written, int64_t first,
+                                          int64_t end, int lane) {
+  const unsigned below = (1u << lane) - 1;
+  for (int64_t base = first; base < end; base += 32) {
+    const int64_t t = base + lane;
+    const bool mine = t < end && owned(p, t);
+    const unsigned keeps = __ballot_sync(0xffffffffu, mine);
+    if (mine) out[written + __popc(keeps & below)] = stored_id(p, t);
+    written += __popc(keeps);
+  }
+  return written;
 }
 
 __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams p) {
@@ -51,7 +75,7 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
       const bool counts = id >= p.sink && id < window_start;
       const unsigned votes = __ballot_sync(0xffffffffu, counts);
       const bool inside = counts && counted + __popc(votes & below) < row_k;
-      const bool mine = inside && id >= p.owner_first && id < p.owner_end;
+      const bool mine = inside && owned(p, id);
       const unsigned keeps = __ballot_sync(0xffffffffu, mine);
       if (mine) out[written + __popc(keeps & below)] = stored_id(p, id);
       written += __popc(keeps);
@@ -61,13 +85,8 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
     }
   }
   // The window, ascending, then the sinks.
-  const int64_t w_first = max(window_start, p.owner_first), w_end = min(pos + 1, p.owner_end);
-  for (int64_t t = w_first + lane; t < w_end; t += 32) out[written + (int)(t - w_first)] = stored_id(p, t);
-  if (w_end > w_first) written += (int)(w_end - w_first);
-  const int64_t sinks = min((int64_t)p.sink, min(window_start, pos + 1));
-  const int64_t s_first = max((int64_t)0, p.owner_first), s_end = min(sinks, p.owner_end);
-  for (int64_t t = s_first + lane; t < s_end; t += 32) out[written + (int)(t - s_first)] = stored_id(p, t);
-  if (s_end > s_first) written += (int)(s_end - s_first);
+  written = append_run(p, out, written, window_start, pos + 1, lane);
+  written = append_run(p, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
   for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
   if (lane == 0) {
     p.lengths[r] = written;
@@ -80,13 +99,16 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
 LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
                        const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
                        const int32_t *row_top_k, int top_k, int sink, int window, const int32_t *page_table,
-                       int page_size, int64_t owner_first, int64_t owner_end, int32_t *selected, int32_t *lengths,
+                       int page_size, int64_t owner_first, int64_t owner_end, int owner_granule, int owner_world,
+                       int owner_rank, int32_t *selected, int32_t *lengths,
                        int32_t *status, void *stream) {
   LSA_REQUIRE(picked && positions && selected && lengths, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && top_p >= 1 && m >= 0 && bucket_cap >= 1 && top_k >= 1 && sink >= 0 && window >= 1,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(!page_table || page_size >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(owner_world <= 1 || (owner_granule >= 1 && owner_rank >= 0 && owner_rank < owner_world),
+              LSA_ERR_ARGUMENT);
   LSA_REQUIRE((int64_t)top_k + window + sink < INT32_MAX, LSA_ERR_ARGUMENT);
   if (R == 0) return LSA_OK;
   lsa::ExpandParams p;
@@ -103,6 +125,9 @@ LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_
   p.m = m;
   p.owner_first = owner_first;
   p.owner_end = owner_end;
+  p.granule = owner_granule;
+  p.world = owner_world;
+  p.rank = owner_rank;
   p.top_p = top_p;
   p.cap = bucket_cap;
   p.top_k = top_k;

@@ -248,7 +248,7 @@ def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch
 def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor, top_k: int, sink: int, window: int,
            row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
            page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None,
-           outs: tuple | None = None):
+           outs: tuple | None = None, dealt: tuple[int, int, int] | None = None):
     """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status)."""
     picked, members = _contig(picked), _contig(members)
     R, top_p = picked.shape
@@ -260,9 +260,11 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
         lengths = torch.empty(R, device=picked.device, dtype=torch.int32)
         status = torch.zeros(1, device=picked.device, dtype=torch.int32)
     first, end = owner if owner is not None else (0, _lib.INT64_MAX)
+    # dealt = (granule, world, rank): keep the ids of this rank's granules, stored as rows of its own cache
+    granule, world, rank = dealt if dealt is not None else (1, 1, 0)
     call("lsa_expand", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
          members.shape[0], members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(page_table),
-         page_size, first, end, ptr(selected), ptr(lengths), ptr(status), stream())
+         page_size, first, end, granule, world, rank, ptr(selected), ptr(lengths), ptr(status), stream())
     return selected, lengths, status
 
 

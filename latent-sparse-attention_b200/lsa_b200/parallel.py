@@ -1,20 +1,27 @@
-"""A flat layer over a sequence-sharded KV cache and index: one process a GPU, `torch.distributed` for the two
-small exchanges of a step.
+"""A flat layer over a sequence-sharded KV cache and index: one process a GPU, `torch.distributed` for the small
+exchanges of a step.
 
-Every rank owns a contiguous run of whole cluster blocks: their KV rows, index keys and bucket centroids. Queries
-are replicated. A step on rank r:
+What is split, and how:
 
-  1. scores its own centroids, keeps its local top-p as packed keys whose ids are GLOBAL bucket rows;
-  2. all-gathers the candidate lists `[world, R, top_p]` and cuts them to the global top-p with the single-GPU tie
-     rule (`lsa_merge_candidates`) - every rank ends with the same picks;
-  3. expands the picks against the replicated member table (integers, a few MB) but writes only the ids it owns; the
-     top-k cut counts every id, so the union over ranks is the single-GPU list;
-  4. attends over its own keys and merges: log-sum-exps are all-gathered, each partial output is weighted by
-     exp(lse_r - lse) and a reduce-scatter over query rows leaves rank r with its rows of the final output.
+  KV rows      dealt out round-robin in granules of `granule` positions (64): position p lives on rank
+               (p / granule) % world, at row p / (granule*world) * granule + p % granule of that rank's cache. A
+               query's window and the members of its buckets are runs of consecutive positions, so every rank
+               holds an even share of every query's keys - a causal prefill stays balanced from the first chunk on.
+  buckets      cluster blocks are dealt out round-robin too: rank r clusters and scores blocks r, r + world, ...
+  index keys   each rank maps the keys it holds; one all-gather puts all index keys (64 floats a token) on every
+               rank, which is what clustering a whole block needs.
+  member table integers, a few MB: all-gathered once after the build, so every rank can expand any pick.
+  queries      replicated.
 
-The reference replicates the whole index and interleaves KV slots over ranks instead
-(`src/lsa/sglang/context_parallel.py:1-24`, `src/lsa/sglang/models/qwen3_5/backend.py:621-781`); the merged
-selection and output are the same single-GPU result either way. Nothing here reads a peer's memory from a kernel.
+A step on rank r: score its own centroids -> local top-p as packed keys with GLOBAL bucket ids -> all-gather the
+candidates and cut them to the global top-p with the single-GPU tie rule (`lsa_merge_candidates`), so every rank
+holds the same picks -> expand them, writing only the rows this rank holds (the top-k cut counts every id) -> attend
+over its own rows -> all-gather the log-sum-exps, weight the partial output by exp(lse_r - lse), reduce-scatter over
+query rows. The union of the ranks' lists is the single-GPU list and the merged output the single-GPU output.
+
+The reference replicates the whole index and interleaves single KV slots over ranks
+(`src/lsa/sglang/context_parallel.py:1-24`, `src/lsa/sglang/models/qwen3_5/backend.py:621-781`). No kernel here reads
+a peer's memory; gathered data lands in local memory through the collective first.
 """
 
 from __future__ import annotations
@@ -23,8 +30,9 @@ import torch
 import torch.distributed as dist
 
 from lsa_b200 import ops, probe
-from lsa_b200.core import Buckets
-from lsa_b200.layer import FlatIndex, FlatLayer
+from lsa_b200.layer import FlatLayer
+
+GRANULE = 64  # positions a rank holds in a row before the next rank's turn
 
 
 def shard_blocks(blocks: int, world: int) -> list:
@@ -39,13 +47,29 @@ def shard_blocks(blocks: int, world: int) -> list:
 
 
 def owned_positions(tokens: int, cluster_block_size: int, rank: int, world: int) -> tuple:
-    """The positions [first, end) rank owns: its run of whole blocks; the open tail block goes to the last rank."""
+    """The positions [first, end) of a CONTIGUOUS split by whole blocks; the open tail block goes to the last rank."""
     blocks = tokens // cluster_block_size
     first, end = shard_blocks(blocks, world)[rank]
     lo, hi = first * cluster_block_size, end * cluster_block_size
     if rank == world - 1:
         hi = tokens
     return lo, hi
+
+
+def deal(rows: torch.Tensor, rank: int, world: int, granule: int = GRANULE) -> torch.Tensor:
+    """A rank's share of [T, ...] rows dealt out round-robin in granules: [T / world, ...]."""
+    T = rows.shape[0]
+    if T % (granule * world):
+        raise ValueError(f"{T} rows do not deal out in granules of {granule} over {world} ranks")
+    return rows.view(T // (granule * world), world, granule, *rows.shape[1:])[:, rank].reshape(
+        T // world, *rows.shape[1:])
+
+
+def undeal(every: torch.Tensor, granule: int = GRANULE) -> torch.Tensor:
+    """The inverse for all ranks' shares at once: [world, T / world, ...] -> [T, ...] in position order."""
+    world, share = every.shape[0], every.shape[1]
+    return every.view(world, share // granule, granule, *every.shape[2:]).transpose(0, 1).reshape(
+        world * share, *every.shape[2:])
 
 
 def _all_gather(out: torch.Tensor, piece: torch.Tensor, group=None) -> None:
@@ -56,20 +80,33 @@ def _all_gather(out: torch.Tensor, piece: torch.Tensor, group=None) -> None:
         dist.all_gather(list(out.unbind(0)), piece.contiguous(), group=group)
 
 
+def gather_pieces(piece: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather one equal-shaped tensor a rank into [world, ...]."""
+    out = torch.empty(dist.get_world_size(group), *piece.shape, dtype=piece.dtype, device=piece.device)
+    _all_gather(out, piece, group)
+    return out
+
+
 def gather_candidates(keys: torch.Tensor, group=None) -> torch.Tensor:
     """All-gather every rank's packed candidate keys [R, top_p] int64 into [world, R, top_p]."""
-    world = dist.get_world_size(group)
-    out = torch.empty(world, *keys.shape, dtype=keys.dtype, device=keys.device)
-    _all_gather(out, keys, group)
-    return out
+    return gather_pieces(keys, group)
+
+
+def globalise_keys(keys: torch.Tensor, per_block: int, rank: int, world: int) -> torch.Tensor:
+    """Packed keys over a rank's OWN bucket rows -> the same keys over global bucket rows, when cluster blocks are
+    dealt out round-robin: local row l is global row (l / per_block * world + rank) * per_block + l % per_block.
+    The map is increasing, so a tie broken toward the lower local row is broken toward the lower global row."""
+    empty = keys == torch.iinfo(torch.int64).min
+    local = 0x7FFFFFFF - (keys & 0xFFFFFFFF)
+    wide = (local // per_block * world + rank) * per_block + local % per_block
+    out = (keys & ~0xFFFFFFFF) | (0x7FFFFFFF - wide)
+    return torch.where(empty, keys, out)
 
 
 def merge_weight(lse: torch.Tensor, group=None) -> tuple:
     """This rank's weight exp(lse - LSE) of every (row, head), and the merged LSE, from an all-gather of the
     log-sum-exps. A row nobody read gives weight 0 and LSE -inf."""
-    world = dist.get_world_size(group)
-    every = torch.empty(world, *lse.shape, dtype=lse.dtype, device=lse.device)
-    _all_gather(every, lse, group)
+    every = gather_pieces(lse, group)
     total = torch.logsumexp(every, dim=0)
     weight = torch.exp(lse - total)
     return torch.where(torch.isfinite(total), weight, torch.zeros_like(weight)), total
@@ -94,75 +131,80 @@ def reduce_rows(weighted: torch.Tensor, group=None) -> torch.Tensor:
 
 
 class ShardedFlatLayer:
-    """`FlatLayer.prefill` over a cache whose keys, values and buckets are split by sequence across ranks."""
+    """`FlatLayer.prefill` over a cache whose keys, values and buckets are dealt out across ranks."""
 
-    def __init__(self, layer: FlatLayer, rank: int, world: int, group=None):
-        self.layer, self.rank, self.world, self.group = layer, rank, world, group
+    def __init__(self, layer: FlatLayer, rank: int, world: int, group=None, granule: int = GRANULE):
+        self.layer, self.rank, self.world, self.group, self.granule = layer, rank, world, group, granule
         self.design = layer.design
 
-    def build_index(self, k_shard: torch.Tensor, tokens: int) -> tuple:
-        """Index this rank's blocks and gather the integer tables: (local FlatIndex with global ids, global members).
-
-        `k_shard` holds the rank's own KV rows [hi - lo, Hkv, dh].
-        """
-        d = self.design
-        lo, hi = owned_positions(tokens, d.cluster_block_size, self.rank, self.world)
-        local = self.layer.build_index(k_shard[: hi - lo], reuse_buffers=False)
-        members = local.buckets.bucket_members
-        members = torch.where(members >= 0, members + lo, members)
+    def build_index(self, k_share: torch.Tensor, tokens: int):
+        """From this rank's dealt keys [tokens / world, Hkv, dh]: its own centroids, the global member table, and
+        every index key."""
+        d, layer, world, rank = self.design, self.layer, self.world, self.rank
         blocks = tokens // d.cluster_block_size
-        counts = [(end - first) * d.block_bucket_count for first, end in shard_blocks(blocks, self.world)]
-        # ranks may hold one block more or less: gather equal-sized (padded) tables, then drop the padding
-        widest = max(counts)
-        padded = torch.full((widest, d.bucket_cap), -1, dtype=torch.int32, device=members.device)
-        padded[: members.shape[0]] = members
-        gathered = torch.empty(self.world, widest, d.bucket_cap, dtype=torch.int32, device=members.device)
+        if tokens % d.cluster_block_size or blocks % world:
+            raise ValueError(f"{tokens} tokens must be whole cluster blocks of {d.cluster_block_size}, a multiple of "
+                             f"{world} of them")
+        with probe.region("index map"):
+            own_keys = layer.index_keys(k_share)
+        with probe.region("gather index keys"):
+            index_keys = undeal(gather_pieces(own_keys, self.group), self.granule)
+        # this rank's blocks: r, r + world, ...
+        mine = index_keys.view(blocks // world, world, d.cluster_block_size, -1)[:, rank].contiguous()
+        per_block, block = d.block_bucket_count, d.cluster_block_size
+        with probe.region("pool"):
+            pools = ops.pool_keys(mine, d.pool_size)
+        with probe.region("ward"):
+            labels, _ = ops.ward_rounds(pools, float(d.pool_size), per_block, d.bucket_cap)
+        with probe.region("bucket table"):
+            members, _, _, centroids, _, _ = ops.bucket_table(mine.view(-1, mine.shape[-1]), labels, d.pool_size,
+                                                              per_block, d.bucket_cap)
+            # positions inside this rank's run of blocks -> positions in the sequence
+            members = torch.where(members >= 0, members // block * (world * block) + rank * block + members % block,
+                                  members)
         with probe.region("gather members"):
-            _all_gather(gathered, padded, self.group)
-        every_member = torch.cat([gathered[r, :n] for r, n in enumerate(counts)])
-        bucket_base = sum(counts[: self.rank])
-        index = FlatIndex(local.index_keys, Buckets(local.buckets.bucket_centroids, members,
-                                                    local.buckets.bucket_sizes, d.block_bucket_count,
-                                                    d.cluster_block_size))
-        return index, every_member, bucket_base, (lo, hi)
+            every = gather_pieces(members, self.group)  # [world, blocks / world * per_block, cap]
+            table = every.view(world, blocks // world, per_block, d.bucket_cap).transpose(0, 1).reshape(
+                blocks * per_block, d.bucket_cap)
+        return centroids, table, index_keys
 
-    def prefill(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk: int = 8192,
+    def prefill(self, q: torch.Tensor, k_share: torch.Tensor, v_share: torch.Tensor, chunk: int = 8192,
                 out: torch.Tensor | None = None):
-        """Causal prefill of replicated queries q [T, Hq, dh] over this rank's share of k, v (passed whole or as the
-        shard's rows). Returns this rank's rows of the output, [T / world / ..] chunk by chunk: out[c] holds rows
-        [c*chunk + rank*chunk/world, ...) of chunk c; shape [T // world, Hq, dh] bf16.
+        """Causal prefill of replicated queries q [T, Hq, dh] over this rank's dealt share of the cache
+        (`deal(k, rank, world)`, `deal(v, rank, world)`). Returns this rank's rows of the output, chunk by chunk:
+        rows [c*chunk + rank*chunk/world, c*chunk + (rank+1)*chunk/world) of every chunk c, [T / world, Hq, dh].
         """
-        layer, d = self.layer, self.design
+        layer, d, world, rank = self.layer, self.design, self.world, self.rank
         T = q.shape[0]
-        lo, hi = owned_positions(T, d.cluster_block_size, self.rank, self.world)
-        k_shard = k[lo:hi] if k.shape[0] == T else k
-        v_shard = v[lo:hi] if v.shape[0] == T else v
-        index, members, bucket_base, _ = self.build_index(k_shard, T)
-        centroids = index.buckets.bucket_centroids
-        if T % chunk or chunk % self.world:
-            raise ValueError(f"{T} tokens must split into chunks of {chunk} rows, and a chunk over {self.world} ranks")
-        share = chunk // self.world
-        out = torch.empty(T // self.world, q.shape[1], q.shape[2], dtype=q.dtype, device=q.device) if out is None \
-            else out
+        if T % chunk or chunk % world:
+            raise ValueError(f"{T} tokens must split into chunks of {chunk} rows, and a chunk over {world} ranks")
+        centroids, members, _ = self.build_index(k_share, T)
+        per_block = d.block_bucket_count
+        share = chunk // world
+        if out is None:
+            out = torch.empty(T // world, q.shape[1], q.shape[2], dtype=q.dtype, device=q.device)
         for c, start in enumerate(range(0, T, chunk)):
             rows = q[start:start + chunk]
             positions = torch.arange(start, start + chunk, device=q.device)
             with probe.region("index map"):
                 index_queries = layer.index_queries(rows)
-            visible = (positions // d.cluster_block_size * d.block_bucket_count - bucket_base).clamp(
-                0, centroids.shape[0]).to(torch.int32)
+            # closed blocks b < n with b % world == rank: ceil((n - rank) / world) of this rank's blocks are visible
+            closed = positions // d.cluster_block_size
+            visible = (((closed - rank + world - 1) // world).clamp_min(0) * per_block).clamp_max(
+                centroids.shape[0]).to(torch.int32)
             with probe.region("select"):
-                keys, _ = ops.flat_select(index_queries, centroids, visible, d.top_p, bucket_id_base=bucket_base)
+                keys, _ = ops.flat_select(index_queries, centroids, visible, d.top_p)
+                keys = globalise_keys(keys, per_block, rank, world)
             with probe.region("exchange candidates"):
                 every = gather_candidates(keys, self.group)
             with probe.region("select"):
                 _, picked = ops.merge_candidates(every)
             with probe.region("expand"):
                 lists, lengths, _ = ops.expand(picked, positions, members, d.top_k, d.sink_size, d.window_size,
-                                               owner=(lo, hi))
+                                               dealt=(self.granule, world, rank))
             with probe.region("attend"):
-                partial, lse = ops.sparse_attend(rows, k_shard, v_shard, lists, lengths, layer.scale,
-                                                 out_dtype=torch.float32, first_slot=lo)
+                partial, lse = ops.sparse_attend(rows, k_share, v_share, lists, lengths, layer.scale,
+                                                 out_dtype=torch.float32)
             with probe.region("merge partials"):
                 weight, _ = merge_weight(lse, self.group)
                 partial *= weight[..., None]

@@ -327,6 +327,16 @@ def test_expansion_with_slots_owners_and_bad_ids(ops, oracle):
     for a, b, w in zip(lo.cpu().numpy(), hi.cpu().numpy(), want_sel):
         assert sorted(a[a >= 0].tolist() + b[b >= 0].tolist()) == sorted(w[w >= 0].tolist())
         assert (a[a >= 0] < 2048).all() and (b[b >= 0] >= 2048).all()
+    # four ranks that hold the cache dealt out in granules of 64 positions: each writes rows of its own share
+    seen = [[] for _ in want_sel]
+    for rank in range(4):
+        part, lens_r, _ = ops.expand(cuda(picked), pos, mem, 700, 4, 512, dealt=(64, 4, rank))
+        for r, row in enumerate(part.cpu().numpy()):
+            local = row[row >= 0]
+            assert len(local) == int(lens_r[r])
+            seen[r] += (local // 64 * 256 + rank * 64 + local % 64).tolist()
+    for got, w in zip(seen, want_sel):
+        assert sorted(got) == sorted(w[w >= 0].tolist())
     # a pick past the table is counted in the status word and skipped
     bad = picked.copy()
     bad[0, 0] = 10**6

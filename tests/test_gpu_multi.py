@@ -32,7 +32,7 @@ def _rank_main(rank, world, port, result_dir):
     try:
         from helpers import bf16_round, cuda, layer_inputs
         from lsa_b200.layer import FlatDesign, FlatLayer
-        from lsa_b200.parallel import ShardedFlatLayer, owned_positions
+        from lsa_b200.parallel import ShardedFlatLayer, deal
 
         T, Hq, Hkv, dh, chunk = 8192, 40, 8, 128, 1024
         design = FlatDesign(pool_size=16, bucket_size=32, bucket_cap=64, cluster_block_size=512, top_p=8, top_k=300,
@@ -42,9 +42,8 @@ def _rank_main(rank, world, port, result_dir):
         layer = FlatLayer(design, cuda(w[0], torch.bfloat16), cuda(w[1], torch.bfloat16), Hq, Hkv, dh)
         q, k, v = (cuda(a, torch.bfloat16) for a in layer_inputs(T, Hq, Hkv, dh, 32, 1))
         want = layer.prefill(q, k, v, chunk=chunk)
-        lo, hi = owned_positions(T, design.cluster_block_size, rank, world)
         sharded = ShardedFlatLayer(layer, rank, world)
-        got = sharded.prefill(q, k[lo:hi].contiguous(), v[lo:hi].contiguous(), chunk=chunk)
+        got = sharded.prefill(q, deal(k, rank, world).contiguous(), deal(v, rank, world).contiguous(), chunk=chunk)
         share = chunk // world
         mine = torch.cat([want[c * chunk + rank * share: c * chunk + (rank + 1) * share] for c in range(T // chunk)])
         err = (got.float() - mine.float()).abs()
