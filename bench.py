@@ -193,13 +193,21 @@ def host_threads() -> int:
 
 
 def attend_algorithmic_bytes(cfg: dict, gathered_total: int) -> float:
-    """Algorithmic bytes of a step's attention: gathered K/V rows per query, the band once per 128-query tile,
-    the sinks per tile, Q in and O out, and the log-sum-exp."""
+    """Algorithmic bytes of a step's gather attention: the K/V rows each query gathers (its selected keys; the
+    window and the sinks are the band kernel's), Q in, the band's partial result in (fp32 output and log-sum-exp),
+    and O out."""
+    T, Hq, Hkv, dh = cfg["tokens"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    row = Hkv * dh * 2 * 2
+    return gathered_total * row + T * Hq * dh * (2 + 4 + 2) + T * Hq * 4
+
+
+def band_algorithmic_bytes(cfg: dict) -> float:
+    """Algorithmic bytes of a step's band attention: the band's K/V once per 128-query tile, the sinks, Q in and
+    the fp32 partial result out."""
     T, Hq, Hkv, dh = cfg["tokens"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
     row = Hkv * dh * 2 * 2
     tiles = (T + 127) // 128
-    return (gathered_total * row + tiles * (cfg["window_size"] + 128 + cfg["sink_size"]) * row + T * Hq * dh * 2 * 2
-            + T * Hq * 4)
+    return tiles * (cfg["window_size"] + 128 + cfg["sink_size"]) * row + T * Hq * dh * (2 + 4) + T * Hq * 4
 
 
 def run_ours(args, cfg: dict) -> dict:

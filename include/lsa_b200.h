@@ -34,6 +34,8 @@ extern "C" {
 
 #define LSA_PAD (-1)                  /* the only padding value an id list carries (src/lsa/constants.py:16-20) */
 #define LSA_EMPTY_KEY INT64_MIN       /* the packed key of no bucket (src/lsa/core/kernels/constants.py:29-37) */
+/* lsa_expand flag: leave the window and the sinks out of the list (a dense band kernel reads them instead) */
+#define LSA_EXPAND_NO_LOCAL 1
 #define LSA_DTYPE_F32 0
 #define LSA_DTYPE_BF16 1
 
@@ -157,6 +159,17 @@ int lsa_flat_select_decode(const float *queries, int64_t R, int d, const float *
                            int64_t *keys_out, int32_t *picked_out, void *workspace, size_t workspace_bytes,
                            void *stream);
 
+/* The same scan through page tables, as a serving cache holds its buckets: request r's logical bucket i is row
+ * i % page_rows of page pages[r, i / page_rows] of `centroids` (-1 = no page: skipped); ids in the keys are the
+ * LOGICAL bucket ids. Reference: scan_paged (src/lsa/core/kernels/triton/paged.py:61-101), DecodeSelect.listed
+ * (src/lsa/core/kernels/cutedsl/decode.py:1035-1068).
+ *   centroids [rows, d] fp32; pages [R, max_pages] int32; counts [R] int32 visible buckets of each request
+ *   workspace as lsa_flat_select_decode_workspace_bytes(R, top_p, splits) */
+int lsa_flat_select_paged(const float *queries, int64_t R, int d, const float *centroids, int64_t rows,
+                          const int32_t *pages, int max_pages, int page_rows, const int32_t *counts, int top_p,
+                          int splits, int64_t *keys_out, int32_t *picked_out, void *workspace,
+                          size_t workspace_bytes, void *stream);
+
 /* Global top_p of several candidate lists of packed keys (the lists every rank all-gathered, or a row's
  * splits). keys_in [parts, R, top_p] int64; keys_out [R, top_p] best first; picked_out as above or NULL. */
 int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out,
@@ -194,14 +207,15 @@ int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, 
  *              stored as its row in that rank's own cache, id / (granule*world) * granule + id % granule
  *   owner_first/owner_end - only ids in [owner_first, owner_end) are written (a rank's share of the sequence);
  *              the top_k cut still counts every id. Pass 0 and INT64_MAX for all.
+ *   flags      0, or LSA_EXPAND_NO_LOCAL to write the expansion alone (the cut and the window filter stay)
  *   selected   [R, top_k + window + sink] int32 out - expansion, window ascending, sinks ascending, -1 padded
  *   lengths    [R] int32 out
  * --------------------------------------------------------------------------------------------------------- */
 int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions, const int32_t *members,
                int64_t m, int bucket_cap, const int32_t *row_top_p, const int32_t *row_top_k, int top_k,
                int sink, int window, const int32_t *page_table, int page_size, int64_t owner_first,
-               int64_t owner_end, int owner_granule, int owner_world, int owner_rank, int32_t *selected,
-               int32_t *lengths, int32_t *status, void *stream);
+               int64_t owner_end, int owner_granule, int owner_world, int owner_rank, int flags,
+               int32_t *selected, int32_t *lengths, int32_t *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Gather-sparse attention over each row's list, with the log-sum-exp of the scaled logits.
@@ -213,6 +227,8 @@ int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *posit
  *   ids    [R, list_stride] int32 - the first lengths[r] entries are read, each one once: KV rows (slots) the
  *          caller guarantees causal and distinct, as lsa_expand writes them; an entry outside
  *          [first_slot, first_slot + slots) is skipped
+ *   init_out / init_lse  [R, Hq, dh] / [R, Hq] fp32 or both NULL - a partial read over OTHER keys (the dense band
+ *          of lsa_band_attend) the read starts from, as one more term of the online softmax
  *   splits CTAs-per-(row, KV head) the list is divided over; > 1 needs the workspace and runs the merge kernel
  *   out    [R, Hq, dh] bf16 (out_bf16) and/or fp32 (out_f32); lse [R, Hq] fp32 or NULL
  * A row that reads nothing gives zeros and lse = -inf.
@@ -220,10 +236,10 @@ int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *posit
 size_t lsa_sparse_attend_workspace_bytes(int64_t R, int Hq, int dh, int splits);
 int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
                       const uint16_t *k, const uint16_t *v, int64_t slots, int64_t first_slot, int Hkv,
-                      int64_t kv_row_stride,
-                      int64_t kv_head_stride, const int32_t *ids, int64_t list_stride, const int32_t *lengths,
-                      float scale, int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
-                      size_t workspace_bytes, void *stream);
+                      int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
+                      const int32_t *lengths, const float *init_out, const float *init_lse, float scale, int splits,
+                      uint16_t *out_bf16, float *out_f32, float *lse, void *workspace, size_t workspace_bytes,
+                      void *stream);
 
 /* The same read for callers that cannot allocate device memory. This entry point has no counterpart in the
  * reference; it exists for hosts where lsa_sparse_attend's caller-provided workspace is not an option: a serving
@@ -247,6 +263,17 @@ int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64
                              const int32_t *ids, int64_t list_stride,
                              const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
                              float *lse, void *stream);
+
+/* The local part of a prefill's read as dense banded attention: rows are consecutive positions (row i sits at
+ * first_position + i, KV row p holds position p) and each attends to its window [pos + 1 - window, pos] and its
+ * sinks [0, min(sink, window start)). One pass over the band's K/V serves 16 query rows and a whole head group.
+ * The result is partial - normalised fp32 output and log-sum-exp - and is meant as lsa_sparse_attend's
+ * init_out / init_lse, whose lists then hold only the selected keys (lsa_expand with LSA_EXPAND_NO_LOCAL).
+ * Reference: the window and sink terms of keep_set (src/lsa/core/attention.py:49-58). sink <= 64. */
+int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
+                    const uint16_t *k, const uint16_t *v, int64_t n_keys, int Hkv, int64_t kv_row_stride,
+                    int64_t kv_head_stride, int64_t first_position, int window, int sink, float scale, float *out_f32,
+                    float *lse, void *stream);
 
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the

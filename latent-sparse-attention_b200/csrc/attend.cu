@@ -17,6 +17,7 @@ struct AttendParams {
   const int32_t *ids, *lengths;
   uint16_t *out_bf16;
   float *out_f32, *lse, *part_out, *part_lse;
+  const float *init_out, *init_lse;  // a partial read to start from ([R,Hq,dh], [R,Hq]), or NULL
   int64_t R, slots, first_slot, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride, list_stride;
   int Hq, Hkv, group, splits;
   float scale_log2;
@@ -124,6 +125,29 @@ __global__ void __launch_bounds__(W * 32, 1) sparse_attend_kernel(AttendParams p
     l_run[nt][0] = l_run[nt][1] = 0.0f;
 #pragma unroll
     for (int mt = 0; mt < DH / 16; ++mt) o[nt][mt][0] = o[nt][mt][1] = o[nt][mt][2] = o[nt][mt][3] = 0.0f;
+  }
+
+  // Start from a partial read over other keys (the dense band of the window): it enters as one more term of the
+  // online softmax, weight exp(lse) and value its normalised output. Only the first split carries it.
+  if (p.init_out && split == 0) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int head = nt * 8 + t * 2 + j;
+        if (head >= p.group) continue;
+        const int64_t out_row = r * p.Hq + h * p.group + head;
+        const float lse0 = p.init_lse[out_row];
+        if (lse0 == -INFINITY) continue;
+        m_run[nt][j] = lse0 * 1.4426950408889634f;
+        l_run[nt][j] = g == 0 ? 1.0f : 0.0f;
+        const float *src = p.init_out + out_row * DH;
+#pragma unroll
+        for (int mt = 0; mt < DH / 16; ++mt) {
+          o[nt][mt][j] = src[mt * 16 + g];
+          o[nt][mt][2 + j] = src[mt * 16 + g + 8];
+        }
+      }
   }
 
   // A lane's list entry of stage `it`; read a stage ahead of its use so the load never stalls the copies.
@@ -372,9 +396,11 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
                               int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t slots, int64_t first_slot,
                               int Hkv,
                               int64_t kv_row_stride, int64_t kv_head_stride, const int32_t *ids, int64_t list_stride,
-                              const int32_t *lengths, float scale, int splits, uint16_t *out_bf16, float *out_f32,
-                              float *lse, void *workspace, size_t workspace_bytes, void *stream) {
+                              const int32_t *lengths, const float *init_out, const float *init_lse, float scale,
+                              int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
+                              size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && k && v && ids && (out_bf16 || out_f32), LSA_ERR_NULL);
+  LSA_REQUIRE((init_out == nullptr) == (init_lse == nullptr), LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && slots >= 0 && first_slot >= 0 &&
                   first_slot + slots <= INT32_MAX && list_stride >= 0 && splits >= 1,
               LSA_ERR_ARGUMENT);
@@ -396,6 +422,8 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   p.out_bf16 = out_bf16;
   p.out_f32 = out_f32;
   p.lse = lse;
+  p.init_out = init_out;
+  p.init_lse = init_lse;
   p.part_out = nullptr;
   p.part_lse = nullptr;
   p.R = R;
@@ -463,6 +491,6 @@ LSA_API int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int d
     static_scratch_address[device] = scratch;
   }
   return lsa_sparse_attend(q, R, Hq, dh, q_row_stride, q_head_stride, k, v, slots, first_slot, Hkv, kv_row_stride, kv_head_stride,
-                           ids, list_stride, lengths, scale, splits, out_bf16, out_f32, lse, scratch,
+                           ids, list_stride, lengths, nullptr, nullptr, scale, splits, out_bf16, out_f32, lse, scratch,
                            LSA_STATIC_SCRATCH_BYTES, stream);
 }

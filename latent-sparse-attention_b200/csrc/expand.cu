@@ -17,7 +17,7 @@ struct ExpandParams {
   int32_t *lengths;           // [R]
   int32_t *status;
   int64_t R, m, owner_first, owner_end;
-  int top_p, cap, top_k, sink, window, page_size, width, granule, world, rank;
+  int top_p, cap, top_k, sink, window, page_size, width, granule, world, rank, flags;
 };
 
 // Whether this caller keeps an id: inside its contiguous range and, when the cache is dealt out in granules of
@@ -85,8 +85,10 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
     }
   }
   // The window, ascending, then the sinks.
-  written = append_run(p, out, written, window_start, pos + 1, lane);
-  written = append_run(p, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
+  if (!(p.flags & LSA_EXPAND_NO_LOCAL)) {
+    written = append_run(p, out, written, window_start, pos + 1, lane);
+    written = append_run(p, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
+  }
   for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
   if (lane == 0) {
     p.lengths[r] = written;
@@ -100,7 +102,7 @@ LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_
                        const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
                        const int32_t *row_top_k, int top_k, int sink, int window, const int32_t *page_table,
                        int page_size, int64_t owner_first, int64_t owner_end, int owner_granule, int owner_world,
-                       int owner_rank, int32_t *selected, int32_t *lengths,
+                       int owner_rank, int flags, int32_t *selected, int32_t *lengths,
                        int32_t *status, void *stream) {
   LSA_REQUIRE(picked && positions && selected && lengths, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
@@ -128,6 +130,7 @@ LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_
   p.granule = owner_granule;
   p.world = owner_world;
   p.rank = owner_rank;
+  p.flags = flags;
   p.top_p = top_p;
   p.cap = bucket_cap;
   p.top_k = top_k;

@@ -125,7 +125,8 @@ struct SelectParams {
   int32_t *ids_out;             // [splits, R, keep] or NULL
   int32_t *carried_out;         // [R, keep * fanout] or NULL
   int64_t R, N;
-  int d, n_carried, keep, fanout, id_base, chunk, run_limit;
+  const int32_t *pages;         // [R, max_pages] page of every page_rows ids of a row (-1 = none), or NULL
+  int d, n_carried, keep, fanout, id_base, chunk, run_limit, max_pages, page_rows;
 };
 
 // RB rows a CTA. Shared memory: queries [RB][d], per-row key buffers [RB][keep_pow2 + chunk], histograms.
@@ -193,6 +194,12 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
           id = c < p.n_carried ? p.carried[r * p.n_carried + c] : first_s[i] + (c - p.n_carried);
         ids[i] = id;
         vec_row[i] = id >= 0 ? (p.vector_base ? p.vector_base[r] : 0) + id : -1;
+        if (p.pages && id >= 0) {
+          // a request's logical bucket id sits at row id % page_rows of its page id / page_rows
+          const int page = id / p.page_rows < p.max_pages ? p.pages[r * p.max_pages + id / p.page_rows] : -1;
+          vec_row[i] = page >= 0 ? (int64_t)page * p.page_rows + id % p.page_rows : -1;
+          if (page < 0) ids[i] = -1;
+        }
         if (vec_row[i] >= p.N) vec_row[i] = -1, ids[i] = -1;
         acc[i] = 0.0f;
         same = same && (vec_row[i] == vec_row[0] || vec_row[i] < 0 || vec_row[0] < 0);
@@ -448,4 +455,40 @@ LSA_API int lsa_beam_step(const float *queries, int64_t R, int d, const float *v
   p.fanout = fanout;
   p.run_limit = (int)N;
   return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+}
+
+LSA_API int lsa_flat_select_paged(const float *queries, int64_t R, int d, const float *centroids, int64_t rows,
+                                  const int32_t *pages, int max_pages, int page_rows, const int32_t *counts,
+                                  int top_p, int splits, int64_t *keys_out, int32_t *picked_out, void *workspace,
+                                  size_t workspace_bytes, void *stream) {
+  LSA_REQUIRE(queries && centroids && pages && counts && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && rows >= 0 && max_pages >= 1 && page_rows >= 1 && top_p >= 1 &&
+                  splits >= 1 && splits <= 1024,
+              LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  if (splits > 1) {
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= lsa_flat_select_decode_workspace_bytes(R, top_p, splits), LSA_ERR_WORKSPACE);
+  }
+  lsa::SelectParams p = {};
+  p.queries = queries;
+  p.vectors = centroids;
+  p.run_end = counts;
+  p.pages = pages;
+  p.max_pages = max_pages;
+  p.page_rows = page_rows;
+  p.R = R;
+  p.N = rows;
+  p.d = d;
+  p.keep = top_p;
+  p.run_limit = INT32_MAX;
+  if (splits == 1) {
+    p.keys_out = keys_out;
+    p.ids_out = picked_out;
+    return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+  }
+  p.keys_out = (int64_t *)workspace;
+  int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
+  if (rc != LSA_OK) return rc;
+  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
 }

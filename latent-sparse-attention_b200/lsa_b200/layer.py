@@ -144,8 +144,9 @@ class FlatLayer:
         return FlatIndex(keys, Buckets(centroids, members, sizes, per_block, d.cluster_block_size))
 
     def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
-               reuse_buffers: bool = False):
-        """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`."""
+               reuse_buffers: bool = False, local: bool = True):
+        """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`; with
+        `local=False` the lists hold the expansion alone (a band kernel reads the window and the sinks)."""
         d, b, dev = self.design, index.buckets, index_queries.device
         R = index_queries.shape[0]
         positions = positions.to(torch.int64)
@@ -169,18 +170,27 @@ class FlatLayer:
                                         picked=picked)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, positions, b.bucket_members, d.top_k, d.sink_size, d.window_size,
-                                           row_p, row_k, outs=outs)
+                                           row_p, row_k, outs=outs, local=local)
         return lists, lengths
 
     def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lists: torch.Tensor, lengths: torch.Tensor,
-               splits: int = 1, out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
+               splits: int = 1, out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+               init: tuple | None = None):
         with probe.region("attend"):
-            return ops.sparse_attend(q, k, v, lists, lengths, self.scale, splits=splits, out=out, lse=lse)
+            return ops.sparse_attend(q, k, v, lists, lengths, self.scale, splits=splits, out=out, lse=lse, init=init)
+
+    def band(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_position: int):
+        """The window and sinks of consecutive rows as one dense banded read: a partial (out fp32, lse)."""
+        R, dev = q.shape[0], q.device
+        with probe.region("band"):
+            return ops.band_attend(q, k, v, first_position, self.design.window_size, self.design.sink_size, self.scale,
+                                   out=self._buffer("band out", (R, self.heads, self.head_dim), torch.float32, dev),
+                                   lse=self._buffer("band lse", (R, self.heads), torch.float32, dev))
 
     # ---- the layer
 
     def prefill(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk: int = 8192,
-                return_index: bool = False, out: torch.Tensor | None = None):
+                return_index: bool = False, out: torch.Tensor | None = None, band: bool = True):
         """Causal prefill from position 0: q [T,Hq,dh], k/v [T,Hkv,dh] bf16 -> out [T,Hq,dh] bf16.
 
         Every intermediate lives in buffers the layer keeps, so after the first call a step allocates nothing but
@@ -197,9 +207,13 @@ class FlatLayer:
             with probe.region("index map"):
                 index_queries = self.index_queries(rows, out=self._buffer("index queries", (stop - start, d_idx),
                                                                           torch.float32, dev))
-            lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True)
+            # The window and the sinks are the same keys for neighbouring rows: one dense band serves them, and the
+            # gather starts from its partial result and reads the selected keys alone.
+            banded = band and self.design.sink_size <= 64 and k.shape[0] >= stop
+            init = self.band(rows, k, v, start) if banded else None
+            lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
             self.attend(rows, k, v, lists, lengths, out=out[start:stop],
-                        lse=self._buffer("lse", (stop - start, self.heads), torch.float32, dev))
+                        lse=self._buffer("lse", (stop - start, self.heads), torch.float32, dev), init=init)
         return (out, index) if return_index else out
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,

@@ -213,6 +213,26 @@ def flat_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, req
     return keys, picked
 
 
+def flat_select_paged(index_queries: torch.Tensor, centroids: torch.Tensor, pages: torch.Tensor,
+                      counts: torch.Tensor, page_rows: int, top_p: int, splits: int = 1,
+                      workspace: torch.Tensor | None = None):
+    """The decode scan through each request's page table (src/lsa/core/kernels/triton/paged.py:61-101): logical
+    bucket i of request r is row i % page_rows of page pages[r, i // page_rows]. Returns (keys, logical ids)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    pages = _contig(pages.to(torch.int32))
+    R, d = q.shape
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    need = query("lsa_flat_select_decode_workspace_bytes", R, top_p, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_flat_select_paged", ptr(q), R, d, ptr(c), c.shape[0], ptr(pages), pages.shape[1], page_rows,
+         ptr(_contig(counts.to(torch.int32))), top_p, splits, ptr(keys), ptr(picked), ptr(workspace),
+         workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
+         launches=1 if splits == 1 else 2)
+    return keys, picked
+
+
 def merge_candidates(keys_in: torch.Tensor):
     """Global top-p of [parts, R, top_p] packed keys: (keys [R, top_p], ids [R, top_p])."""
     keys_in = _contig(keys_in)
@@ -248,7 +268,7 @@ def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch
 def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor, top_k: int, sink: int, window: int,
            row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
            page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None,
-           outs: tuple | None = None, dealt: tuple[int, int, int] | None = None):
+           outs: tuple | None = None, dealt: tuple[int, int, int] | None = None, local: bool = True):
     """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status)."""
     picked, members = _contig(picked), _contig(members)
     R, top_p = picked.shape
@@ -264,14 +284,14 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
     granule, world, rank = dealt if dealt is not None else (1, 1, 0)
     call("lsa_expand", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
          members.shape[0], members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(page_table),
-         page_size, first, end, granule, world, rank, ptr(selected), ptr(lengths), ptr(status), stream())
+         page_size, first, end, granule, world, rank, 0 if local else 1, ptr(selected), ptr(lengths), ptr(status), stream())
     return selected, lengths, status
 
 
 def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.Tensor,
                   lengths: torch.Tensor | None, scale: float, splits: int = 1, out_dtype=torch.bfloat16,
                   workspace: torch.Tensor | None = None, out: torch.Tensor | None = None,
-                  lse: torch.Tensor | None = None, first_slot: int = 0):
+                  lse: torch.Tensor | None = None, first_slot: int = 0, init: tuple | None = None):
     """Attention of q [R, Hq, dh] over the KV rows each list names; returns (out [R, Hq, dh], lse [R, Hq]).
     `k`, `v` hold the KV rows from `first_slot` on (a rank's share of a sharded cache); other ids are skipped."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
@@ -295,10 +315,28 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
         workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
     call("lsa_sparse_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, first_slot, Hkv,
          k.stride(0),
-         k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits, ptr(out_bf16), ptr(out_f32),
+         k.stride(1), ptr(ids), ids.shape[1], ptr(lengths), ptr(init[0]) if init else None,
+         ptr(init[1]) if init else None, float(scale), splits, ptr(out_bf16), ptr(out_f32),
          ptr(lse), ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0,
          stream(), launches=1 if splits == 1 else 2)
     return (out_bf16 if out_bf16 is not None else out_f32), lse
+
+
+def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_position: int, window: int, sink: int,
+                scale: float, out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
+    """The window and sinks of consecutive query rows as dense banded attention: q [R, Hq, dh] at positions
+    first_position.., k/v [n_keys, Hkv, dh] by position. Returns the PARTIAL read (out fp32 [R, Hq, dh], lse [R, Hq])
+    that `sparse_attend(..., init=(out, lse))` extends with the selected keys."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("q, k and v must be bfloat16")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
+        raise ValueError("head dims must be contiguous and k, v must share their layout")
+    R, Hq, dh = q.shape
+    out = torch.empty(R, Hq, dh, device=q.device, dtype=torch.float32) if out is None else out
+    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32) if lse is None else lse
+    call("lsa_band_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), k.shape[0], k.shape[1],
+         k.stride(0), k.stride(1), first_position, window, sink, float(scale), ptr(out), ptr(lse), stream())
+    return out, lse
 
 
 def lse_merge(parts: torch.Tensor, lses: torch.Tensor, out_dtype=torch.float32):

@@ -380,6 +380,40 @@ def test_sparse_attention_within_bf16_tolerance(ops, oracle, T, Hq, Hkv, dh, R, 
     assert np.abs(out16.float().cpu().numpy() - want).max() <= 2e-2
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,dh,window,sink,first,R", [(3000, 40, 8, 128, 1024, 4, 1500, 700),
+                                                             (700, 8, 2, 128, 512, 4, 0, 700),
+                                                             (2000, 16, 1, 64, 300, 0, 90, 333),
+                                                             (2500, 8, 8, 64, 64, 7, 1000, 61)])
+def test_band_attention_and_its_hand_over_to_the_gather(ops, oracle, T, Hq, Hkv, dh, window, sink, first, R):
+    q, k, v = layer_inputs(T, Hq, Hkv, dh, 16, T + window)
+    rows = np.arange(first, first + R)
+    scale = dh ** -0.5
+    empty = np.full((R, 1), -1, dtype=np.int32)
+    want, want_lse = oracle.sparse_attend(q[rows], k, v, empty, rows, window, sink, scale)
+    Q, K, V = cuda(q[rows], torch.bfloat16), cuda(k, torch.bfloat16), cuda(v, torch.bfloat16)
+    out, lse = ops.band_attend(Q, K, V, first, window, sink, scale)
+    err = np.abs(out.cpu().numpy() - want)
+    assert err.max() <= 2e-2 and err.mean() <= 2e-3, (err.max(), err.mean())
+    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=0, atol=2e-3)
+    # the gather continues from the band's partial result over keys outside the window and the sinks
+    rng = np.random.default_rng(1)
+    ids = np.full((R, 200), -1, dtype=np.int32)
+    lens = np.zeros(R, dtype=np.int32)
+    for i, pos in enumerate(rows):
+        lo, hi = sink, max(sink, pos + 1 - window)
+        n = min(200, hi - lo)
+        if n > 0:
+            ids[i, :n] = rng.choice(np.arange(lo, hi), n, replace=False)
+        lens[i] = max(n, 0)
+    whole, whole_lse = oracle.sparse_attend(q[rows], k, v, ids, rows, window, sink, scale, lengths=lens)
+    for splits in (1, 3):
+        got, got_lse = ops.sparse_attend(Q, K, V, cuda(ids), cuda(lens), scale, splits=splits, out_dtype=torch.float32,
+                                         init=(out, lse))
+        err = np.abs(got.cpu().numpy() - whole)
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3, (splits, err.max(), err.mean())
+        np.testing.assert_allclose(got_lse.cpu().numpy(), whole_lse, rtol=0, atol=2e-3)
+
+
 def test_attention_skips_bad_ids_and_merges_partials(ops, oracle):
     q, k, v, rows, ids, lens = _attend_case(2000, 8, 2, 128, 12, 400, 4)
     scale = 128 ** -0.5
