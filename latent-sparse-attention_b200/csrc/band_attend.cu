@@ -137,19 +137,33 @@ __global__ void band_attend_kernel(BandParams p) {
         band_mma(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
       }
     }
-    // mask: a key counts for a row if it is inside the row's window (and causal), or one of its sinks
+    // mask: a key counts for a row if it is inside the row's window (and causal), or one of its sinks. A tile that
+    // lies inside every row's window (all but the band's two ends) needs none.
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool inside = tile >= 0 && key0 >= max((int64_t)0, pos_last + 1 - p.window) && key0 + kBandKeys - 1 <= pos0 &&
+                        key0 + kBandKeys <= p.n_keys && pos0 + kBandRows <= p.first_position + p.R;
+    if (inside) {
 #pragma unroll
-    for (int n = 0; n < kBandKeys / 8; ++n) {
+      for (int n = 0; n < kBandKeys / 8; ++n) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int64_t key = key0 + n * 8 + t * 2 + (j & 1);
-        const int64_t pos = (j & 2) ? pos_b : pos_a;
-        const int64_t start = max((int64_t)0, pos + 1 - p.window);
-        const bool ok = pos < p.first_position + p.R && key < p.n_keys &&
-                        ((tile >= 0 && key >= start && key <= pos) || key < min((int64_t)p.sink, start));
-        s[n][j] = ok ? s[n][j] * p.scale_log2 : -INFINITY;
-        mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
+        for (int j = 0; j < 4; ++j) {
+          s[n][j] *= p.scale_log2;
+          mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < kBandKeys / 8; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int64_t key = key0 + n * 8 + t * 2 + (j & 1);
+          const int64_t pos = (j & 2) ? pos_b : pos_a;
+          const int64_t start = max((int64_t)0, pos + 1 - p.window);
+          const bool ok = pos < p.first_position + p.R && key < p.n_keys &&
+                          ((tile >= 0 && key >= start && key <= pos) || key < min((int64_t)p.sink, start));
+          s[n][j] = ok ? s[n][j] * p.scale_log2 : -INFINITY;
+          mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
+        }
       }
     }
     float alpha[2];
@@ -256,13 +270,19 @@ LSA_API int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_
   const int threads = (group < 8 ? group : 8) * 32;
   cudaStream_t s = (cudaStream_t)stream;
   if (dh == 128) {
+    // 64 KB of tiles a CTA: ask for the largest shared-memory carve-out so that two or three CTAs share an SM
     if (cudaFuncSetAttribute(lsa::band_attend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(lsa::band_attend_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared) != cudaSuccess)
       return LSA_ERR_LAUNCH;
     lsa::band_attend_kernel<128><<<grid, threads, smem, s>>>(p);
   } else {
+    // 64 KB of tiles a CTA: ask for the largest shared-memory carve-out so that two or three CTAs share an SM
     if (cudaFuncSetAttribute(lsa::band_attend_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-        cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(lsa::band_attend_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared) != cudaSuccess)
       return LSA_ERR_LAUNCH;
     lsa::band_attend_kernel<64><<<grid, threads, smem, s>>>(p);
   }

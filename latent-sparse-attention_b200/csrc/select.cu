@@ -345,6 +345,123 @@ static int launch_select(SelectParams p, int splits, cudaStream_t s) {
   return LSA_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------- flat prefill scan
+
+// The prefill form of the flat scan: row r scores the first visible[r] centroids, so every row of a CTA scores the
+// SAME centroid for a candidate and it is loaded once for all of them. 16 rows and 16 warps a CTA: all 512 threads
+// score a chunk (a thread a centroid, 16 dots), then each warp folds the chunk into its own row's held keys.
+constexpr int kFlatRows = 16;
+constexpr int kFlatThreads = kFlatRows * 32;
+
+struct FlatParams {
+  const float *queries, *centroids;
+  const int32_t *visible, *row_keep;
+  int64_t *keys_out;
+  int32_t *ids_out;
+  int64_t R, m;
+  int d, keep, id_base, chunk;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kFlatThreads) flat_select_kernel(FlatParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int keep_room = 2;
+  while (keep_room < p.keep) keep_room <<= 1;
+  const int row_room = keep_room + p.chunk;
+  int64_t *bufs = reinterpret_cast<int64_t *>(smem_raw);                     // [16][row_room]
+  float *qs = reinterpret_cast<float *>(bufs + (size_t)kFlatRows * row_room);  // [16][D]
+  int *hists = reinterpret_cast<int *>(qs + kFlatRows * D);                    // [16][256]
+  __shared__ int visible_s[kFlatRows];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t row0 = (int64_t)blockIdx.x * kFlatRows;
+  for (int e = tid; e < kFlatRows * D; e += kFlatThreads) {
+    const int64_t r = row0 + e / D;
+    qs[e] = r < p.R ? p.queries[r * D + e % D] : 0.0f;
+  }
+  if (tid < kFlatRows) {
+    const int64_t r = row0 + tid;
+    int v = r < p.R ? p.visible[r] : 0;
+    visible_s[tid] = v < 0 ? 0 : (v > p.m ? (int)p.m : v);
+  }
+  __syncthreads();
+  int widest = 0;
+#pragma unroll
+  for (int i = 0; i < kFlatRows; ++i) widest = max(widest, visible_s[i]);
+
+  int held = 0;
+  int64_t floor_key = kEmptyKey;
+  const int64_t my_row = row0 + warp;
+  const int my_visible = visible_s[warp];
+  const int my_keep = my_row < p.R ? (p.row_keep ? min(p.row_keep[my_row], p.keep) : p.keep) : 0;
+
+  for (int base = 0; base < widest; base += p.chunk) {
+    const int n = min(p.chunk, widest - base);
+    for (int c = tid; c < n; c += kFlatThreads) {
+      float acc[kFlatRows];
+#pragma unroll
+      for (int i = 0; i < kFlatRows; ++i) acc[i] = 0.0f;
+      const float4 *v4 = reinterpret_cast<const float4 *>(p.centroids + (int64_t)(base + c) * D);
+#pragma unroll 4
+      for (int k4 = 0; k4 < D / 4; ++k4) {
+        const float4 v = __ldg(v4 + k4);
+#pragma unroll
+        for (int i = 0; i < kFlatRows; ++i) {
+          const float4 q = *reinterpret_cast<const float4 *>(qs + i * D + k4 * 4);
+          acc[i] = fmaf(q.x, v.x, acc[i]);
+          acc[i] = fmaf(q.y, v.y, acc[i]);
+          acc[i] = fmaf(q.z, v.z, acc[i]);
+          acc[i] = fmaf(q.w, v.w, acc[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kFlatRows; ++i)
+        bufs[(size_t)i * row_room + keep_room + c] =
+            base + c < visible_s[i] ? pack_key(acc[i], base + c + p.id_base) : kEmptyKey;
+    }
+    __syncthreads();
+    if (my_keep > 0 && base < my_visible) {
+      int64_t *buf = bufs + (size_t)warp * row_room;
+      const int64_t floor_now = floor_key;
+      int count = warp_compact(buf, keep_room, keep_room + min(n, my_visible - base), held,
+                               [floor_now](int64_t key) { return key > floor_now; });
+      if (count > my_keep) {
+        const uint64_t kth = warp_kth_greatest(buf, count, my_keep, hists + warp * kHistBins);
+        count = warp_compact(buf, 0, count, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+        floor_key = (int64_t)(kth ^ 0x8000000000000000ull);
+      }
+      held = count;
+    }
+    __syncthreads();
+  }
+  if (my_row < p.R) {
+    int64_t *buf = bufs + (size_t)warp * row_room;
+    warp_sort_descending(buf, held);
+    for (int i = lane; i < p.keep; i += 32) {
+      const int64_t key = i < held ? buf[i] : kEmptyKey;
+      if (p.keys_out) p.keys_out[my_row * p.keep + i] = key;
+      if (p.ids_out) p.ids_out[my_row * p.keep + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+    }
+  }
+}
+
+template <int D>
+static int launch_flat(FlatParams p, cudaStream_t s) {
+  int keep_room = 2;
+  while (keep_room < p.keep) keep_room <<= 1;
+  const size_t fixed = (size_t)kFlatRows * (keep_room * 8 + D * 4 + kHistBins * 4);
+  p.chunk = 1024;
+  while (p.chunk > 256 && fixed + (size_t)kFlatRows * p.chunk * 8 > 200 * 1024) p.chunk -= 256;
+  const size_t smem = fixed + (size_t)kFlatRows * p.chunk * 8;
+  if (smem > 200 * 1024) return LSA_ERR_UNSUPPORTED;
+  if (cudaFuncSetAttribute(flat_select_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  flat_select_kernel<D><<<(unsigned)((p.R + kFlatRows - 1) / kFlatRows), kFlatThreads, smem, s>>>(p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
 }  // namespace lsa
 
 // ================================================================================================ C ABI
@@ -355,6 +472,21 @@ LSA_API int lsa_flat_select(const float *queries, int64_t R, int d, const float 
   LSA_REQUIRE(queries && centroids && visible && (keys_out || picked_out), LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && m >= 0 && top_p >= 1 && m < INT32_MAX, LSA_ERR_ARGUMENT);
   if (R == 0) return LSA_OK;
+  if ((d == 64 || d == 32) && top_p <= 512) {
+    lsa::FlatParams f = {};
+    f.queries = queries;
+    f.centroids = centroids;
+    f.visible = visible;
+    f.row_keep = row_top_p;
+    f.keys_out = keys_out;
+    f.ids_out = picked_out;
+    f.R = R;
+    f.m = m;
+    f.d = d;
+    f.keep = top_p;
+    f.id_base = bucket_id_base;
+    return d == 64 ? lsa::launch_flat<64>(f, (cudaStream_t)stream) : lsa::launch_flat<32>(f, (cudaStream_t)stream);
+  }
   lsa::SelectParams p = {};
   p.queries = queries;
   p.vectors = centroids;
