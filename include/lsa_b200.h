@@ -217,6 +217,21 @@ int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *posit
                int64_t owner_end, int owner_granule, int owner_world, int owner_rank, int flags,
                int32_t *selected, int32_t *lengths, int32_t *status, void *stream);
 
+/* The same expansion for a batch of requests that share one paged cache (the serving form; reference:
+ * expand_in_order / expand_by_threshold with request_blocks, request_rows and slot_table,
+ * src/lsa/core/kernels/expansion.py:16-126). Beyond lsa_expand:
+ *   row_request   [R] int32 request of each row (NULL = request 0)
+ *   page_table    [requests, page_table_stride] KV pages of each request (positions are the request's own)
+ *   bucket_pages  [requests, bucket_pages_stride] or NULL - a pick is a request's LOGICAL bucket id, stored at row
+ *                 id % bucket_page_rows of page bucket_pages[request, id / bucket_page_rows] of `members` */
+int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, const int64_t *positions, const int32_t *members,
+                       int64_t m, int bucket_cap, const int32_t *row_top_p, const int32_t *row_top_k, int top_k,
+                       int sink, int window, const int32_t *page_table, int page_size, int64_t owner_first,
+                       int64_t owner_end, int owner_granule, int owner_world, int owner_rank, int flags,
+                       const int32_t *row_request, int64_t page_table_stride, const int32_t *bucket_pages,
+                       int64_t bucket_pages_stride, int bucket_max_pages, int bucket_page_rows, int32_t *selected,
+                       int32_t *lengths, int32_t *status, void *stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Gather-sparse attention over each row's list, with the log-sum-exp of the scaled logits.
  * Reference: topk_attention / keep_set (src/lsa/core/attention.py:15-146); served sparse_read, partial_read

@@ -12,7 +12,11 @@ struct ExpandParams {
   const int32_t *members;     // [m, cap]
   const int32_t *row_top_p;   // [R] or NULL
   const int32_t *row_top_k;   // [R] or NULL
-  const int32_t *page_table;  // [pages] or NULL
+  const int32_t *page_table;  // [pages] (or [requests, pages] with page_table_stride) or NULL
+  const int32_t *row_request;   // [R] request of each row, or NULL for request 0
+  const int32_t *bucket_pages;  // [requests, bucket_max_pages] page of every bucket_page_rows logical buckets, or NULL
+  int64_t page_table_stride, bucket_pages_stride;
+  int bucket_page_rows, bucket_max_pages;
   int32_t *selected;          // [R, width]
   int32_t *lengths;           // [R]
   int32_t *status;
@@ -29,21 +33,21 @@ __device__ __forceinline__ bool owned(const ExpandParams &p, int64_t id) {
 
 // What is written for an id: the position, its row in the rank's own cache when granules are dealt out, or its KV
 // slot through the page table.
-__device__ __forceinline__ int32_t stored_id(const ExpandParams &p, int64_t id) {
+__device__ __forceinline__ int32_t stored_id(const ExpandParams &p, const int32_t *table, int64_t id) {
   if (p.world > 1) id = id / ((int64_t)p.granule * p.world) * p.granule + id % p.granule;
-  if (!p.page_table) return (int32_t)id;
-  return p.page_table[id / p.page_size] * p.page_size + (int32_t)(id % p.page_size);
+  if (!table) return (int32_t)id;
+  return table[id / p.page_size] * p.page_size + (int32_t)(id % p.page_size);
 }
 
 // Append the owned ids of [first, end) to out[written..], in order; returns the new count.
-__device__ __forceinline__ int append_run(const ExpandParams &p, int32_t *out, int written, int64_t first,
-                                          int64_t end, int lane) {
+__device__ __forceinline__ int append_run(const ExpandParams &p, const int32_t *table, int32_t *out, int written,
+                                          int64_t first, int64_t end, int lane) {
   const unsigned below = (1u << lane) - 1;
   for (int64_t base = first; base < end; base += 32) {
     const int64_t t = base + lane;
     const bool mine = t < end && owned(p, t);
     const unsigned keeps = __ballot_sync(0xffffffffu, mine);
-    if (mine) out[written + __popc(keeps & below)] = stored_id(p, t);
+    if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, t);
     written += __popc(keeps);
   }
   return written;
@@ -54,6 +58,8 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   const int64_t r = (int64_t)blockIdx.x * kExpandWarps + (threadIdx.x >> 5);
   if (r >= p.R) return;
   const int64_t pos = p.positions[r];
+  const int64_t request = p.row_request ? p.row_request[r] : 0;
+  const int32_t *table = p.page_table ? p.page_table + request * p.page_table_stride : nullptr;
   const int row_p = p.row_top_p ? min(p.row_top_p[r], p.top_p) : p.top_p;
   const int row_k = p.row_top_k ? min(p.row_top_k[r], p.top_k) : p.top_k;
   const int64_t window_start = max((int64_t)0, pos + 1 - p.window);
@@ -63,13 +69,19 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   int written = 0;  // ids this owner keeps
   int bad = 0;
   for (int i = 0; i < row_p && counted < row_k; ++i) {
-    const int32_t bucket = p.picked[r * p.top_p + i];
+    int64_t bucket = p.picked[r * p.top_p + i];
     if (bucket < 0) continue;
+    if (p.bucket_pages) {
+      // a request's logical bucket sits at row bucket % rows of its page bucket / rows
+      const int64_t slot = bucket / p.bucket_page_rows;
+      const int page = slot < p.bucket_max_pages ? p.bucket_pages[request * p.bucket_pages_stride + slot] : -1;
+      bucket = page >= 0 ? (int64_t)page * p.bucket_page_rows + bucket % p.bucket_page_rows : p.m;
+    }
     if (bucket >= p.m) {
       ++bad;
       continue;
     }
-    const int32_t *row = p.members + (int64_t)bucket * p.cap;
+    const int32_t *row = p.members + bucket * p.cap;
     for (int base = 0; base < p.cap && counted < row_k; base += 32) {
       const int32_t id = base + lane < p.cap ? row[base + lane] : LSA_PAD;
       const bool counts = id >= p.sink && id < window_start;
@@ -77,7 +89,7 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
       const bool inside = counts && counted + __popc(votes & below) < row_k;
       const bool mine = inside && owned(p, id);
       const unsigned keeps = __ballot_sync(0xffffffffu, mine);
-      if (mine) out[written + __popc(keeps & below)] = stored_id(p, id);
+      if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, id);
       written += __popc(keeps);
       counted += __popc(votes);
       // Members are stored first, padding after: a chunk that ends in padding ends the bucket.
@@ -86,8 +98,8 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   }
   // The window, ascending, then the sinks.
   if (!(p.flags & LSA_EXPAND_NO_LOCAL)) {
-    written = append_run(p, out, written, window_start, pos + 1, lane);
-    written = append_run(p, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
+    written = append_run(p, table, out, written, window_start, pos + 1, lane);
+    written = append_run(p, table, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
   }
   for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
   if (lane == 0) {
@@ -98,17 +110,20 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
 
 }  // namespace lsa
 
-LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
+LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
                        const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
                        const int32_t *row_top_k, int top_k, int sink, int window, const int32_t *page_table,
                        int page_size, int64_t owner_first, int64_t owner_end, int owner_granule, int owner_world,
-                       int owner_rank, int flags, int32_t *selected, int32_t *lengths,
+                       int owner_rank, int flags, const int32_t *row_request, int64_t page_table_stride,
+                       const int32_t *bucket_pages, int64_t bucket_pages_stride, int bucket_max_pages,
+                       int bucket_page_rows, int32_t *selected, int32_t *lengths,
                        int32_t *status, void *stream) {
   LSA_REQUIRE(picked && positions && selected && lengths, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && top_p >= 1 && m >= 0 && bucket_cap >= 1 && top_k >= 1 && sink >= 0 && window >= 1,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(!page_table || page_size >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!bucket_pages || (bucket_page_rows >= 1 && bucket_max_pages >= 1), LSA_ERR_ARGUMENT);
   LSA_REQUIRE(owner_world <= 1 || (owner_granule >= 1 && owner_rank >= 0 && owner_rank < owner_world),
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE((int64_t)top_k + window + sink < INT32_MAX, LSA_ERR_ARGUMENT);
@@ -131,6 +146,12 @@ LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_
   p.world = owner_world;
   p.rank = owner_rank;
   p.flags = flags;
+  p.row_request = row_request;
+  p.page_table_stride = page_table_stride;
+  p.bucket_pages = bucket_pages;
+  p.bucket_pages_stride = bucket_pages_stride;
+  p.bucket_max_pages = bucket_max_pages;
+  p.bucket_page_rows = bucket_page_rows;
   p.top_p = top_p;
   p.cap = bucket_cap;
   p.top_k = top_k;
@@ -142,4 +163,15 @@ LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_
   lsa::expand_kernel<<<grid, lsa::kExpandWarps * 32, 0, (cudaStream_t)stream>>>(p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
+}
+
+LSA_API int lsa_expand(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
+                       const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
+                       const int32_t *row_top_k, int top_k, int sink, int window, const int32_t *page_table,
+                       int page_size, int64_t owner_first, int64_t owner_end, int owner_granule, int owner_world,
+                       int owner_rank, int flags, int32_t *selected, int32_t *lengths, int32_t *status,
+                       void *stream) {
+  return lsa_expand_batched(picked, R, top_p, positions, members, m, bucket_cap, row_top_p, row_top_k, top_k, sink,
+                            window, page_table, page_size, owner_first, owner_end, owner_granule, owner_world,
+                            owner_rank, flags, nullptr, 0, nullptr, 0, 0, 0, selected, lengths, status, stream);
 }

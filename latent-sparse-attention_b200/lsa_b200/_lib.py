@@ -42,6 +42,8 @@ SIGNATURES = {
     "lsa_beam_step": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P]),
     "lsa_expand": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I, _P, _I, _L, _L, _I, _I, _I, _I, _P, _P, _P,
                         _P]),
+    "lsa_expand_batched": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I, _P, _I, _L, _L, _I, _I, _I, _I, _P, _L, _P,
+                                _L, _I, _I, _P, _P, _P, _P]),
     "lsa_sparse_attend_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "lsa_sparse_attend": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _L, _I, _L, _L, _P, _L, _P, _P, _P, _F, _I, _P, _P,
                                _P, _P, _Z, _P]),

@@ -1,0 +1,128 @@
+"""The serving index of a batch of requests over paged memory: a bucket cache and its selector.
+
+A small, engine-free counterpart of the reference's `BucketCache` and `Selector`
+(`src/lsa/sglang/index/bucket_cache.py:70-601`, `src/lsa/sglang/index/selector.py:107-700`): a model hands the selector
+each request's index keys as they arrive and its page tables, and takes back lists of KV slots.
+
+  - Buckets live in pages of `page_buckets` rows of one device table (centroids, members, sizes). A request owns a
+    list of pages; its logical bucket i is row i % page_buckets of its page i / page_buckets. Pages come from a host
+    free list and go back when a request is released, so the device tables never move.
+  - Positions are a request's own (0 .. length); a KV slot is `kv_pages[request, pos / kv_page] * kv_page + pos % kv_page`
+    (the engine's `req_to_token` table in page form). The reference serves with single-token pages only
+    (`src/lsa/sglang/models/qwen3_5/backend.py:290-294`); any page size works here because the expansion maps each
+    position itself.
+  - Decode is fixed-shape and reads no device value on the host: one paged scan, one expansion, one split
+    attention with its merge.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from lsa_b200 import ops, probe
+from lsa_b200.layer import FlatDesign
+
+
+class BucketCache:
+    """Paged store of every request's buckets (bucket_cache.py:70-140)."""
+
+    def __init__(self, design: FlatDesign, index_dim: int, pages: int, page_buckets: int, max_requests: int,
+                 max_request_pages: int, device="cuda"):
+        self.design, self.page_buckets = design, page_buckets
+        rows = pages * page_buckets
+        self.centroids = torch.zeros(rows, index_dim, device=device, dtype=torch.float32)
+        self.members = torch.full((rows, design.bucket_cap), -1, device=device, dtype=torch.int32)
+        self.sizes = torch.zeros(rows, device=device, dtype=torch.int32)
+        self.request_pages = torch.full((max_requests, max_request_pages), -1, device=device, dtype=torch.int32)
+        self.free_pages = list(range(pages - 1, -1, -1))
+        self.held: dict[int, list] = {}      # request -> its pages, in order
+        self.closed_keys: dict[int, int] = {}  # request -> keys of its closed cluster blocks
+        self.pending: dict[int, torch.Tensor] = {}  # request -> index keys of its open block
+
+    def buckets_of(self, request: int) -> int:
+        return self.closed_keys.get(request, 0) // self.design.bucket_size
+
+    def release(self, request: int) -> None:
+        """Give a finished request's pages back."""
+        self.free_pages.extend(reversed(self.held.pop(request, [])))
+        self.closed_keys.pop(request, None)
+        self.pending.pop(request, None)
+        self.request_pages[request].fill_(-1)
+
+    def _grow(self, request: int, buckets: int) -> None:
+        pages = self.held.setdefault(request, [])
+        need = -(-buckets // self.page_buckets)
+        if need > self.request_pages.shape[1]:
+            raise RuntimeError(f"request {request} needs {need} index pages and a request holds at most "
+                               f"{self.request_pages.shape[1]}")
+        fresh = []
+        while len(pages) < need:
+            if not self.free_pages:
+                raise RuntimeError("the bucket cache is out of pages")  # bucket_cache.py:375-378
+            fresh.append(self.free_pages.pop())
+            pages.append(fresh[-1])
+        if fresh:
+            first = len(pages) - len(fresh)
+            self.request_pages[request, first:len(pages)] = torch.tensor(fresh, dtype=torch.int32,
+                                                                         device=self.request_pages.device)
+
+    def append(self, request: int, index_keys: torch.Tensor) -> int:
+        """Take a request's next index keys [n, index_dim] (fp32 unit rows, in position order); cluster every
+        cluster block that closes and write its buckets into the request's pages. Returns the blocks closed."""
+        d = self.design
+        held = self.pending.get(request)
+        keys = index_keys if held is None else torch.cat([held, index_keys])
+        blocks = keys.shape[0] // d.cluster_block_size
+        closed = blocks * d.cluster_block_size
+        self.pending[request] = keys[closed:]
+        if not blocks:
+            return 0
+        first_position = self.closed_keys.get(request, 0)
+        first_bucket = first_position // d.bucket_size
+        per_block = d.block_bucket_count
+        self._grow(request, first_bucket + blocks * per_block)
+        with probe.region("index k cluster"):
+            block_keys = keys[:closed].contiguous()
+            pools = ops.pool_keys(block_keys.view(blocks, d.cluster_block_size, -1), d.pool_size)
+            labels, _ = ops.ward_rounds(pools, float(d.pool_size), per_block, d.bucket_cap)
+            members, sizes, _, centroids, _, _ = ops.bucket_table(block_keys, labels, d.pool_size, per_block,
+                                                                  d.bucket_cap, first_position=first_position)
+        logical = first_bucket + torch.arange(blocks * per_block, device=members.device)
+        rows = self.request_pages[request][logical // self.page_buckets].long() * self.page_buckets + \
+            logical % self.page_buckets
+        self.centroids[rows] = centroids
+        self.members[rows] = members
+        self.sizes[rows] = sizes
+        self.closed_keys[request] = first_position + closed
+        return blocks
+
+
+class Selector:
+    """Routes a batch's reads over a `BucketCache` (selector.py:107-700), flat design."""
+
+    def __init__(self, cache: BucketCache, kv_page_size: int):
+        self.cache, self.kv_page_size = cache, kv_page_size
+
+    def visible(self, request_rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """Buckets each row sees: those of the cluster blocks closed before its own, that the cache holds."""
+        d = self.cache.design
+        held = torch.tensor([self.cache.buckets_of(int(r)) for r in request_rows.tolist()], device=positions.device)
+        return torch.minimum(positions // d.cluster_block_size * d.block_bucket_count, held).to(torch.int32)
+
+    def decode_flat(self, index_queries: torch.Tensor, request_rows: torch.Tensor, positions: torch.Tensor,
+                    kv_pages: torch.Tensor, visible: torch.Tensor | None = None, splits: int = 4,
+                    local: bool = True):
+        """Lists of KV slots [B, top_k + window + sink] int32 (-1 padded, valid first) and their lengths for one
+        query a request (selector.py:603-700). `visible` may be passed in to keep the step free of host work."""
+        cache, d = self.cache, self.cache.design
+        visible = self.visible(request_rows, positions) if visible is None else visible
+        pages = cache.request_pages[request_rows.long()]
+        with probe.region("index q scan"):
+            _, picked = ops.flat_select_paged(index_queries, cache.centroids, pages, visible, cache.page_buckets,
+                                              d.top_p, splits=splits)
+        with probe.region("expand"):
+            rows = torch.arange(request_rows.shape[0], device=picked.device, dtype=torch.int32)
+            lists, lengths, _ = ops.expand_batched(picked, positions, rows, cache.members, pages, cache.page_buckets,
+                                                   kv_pages, self.kv_page_size, d.top_k, d.sink_size, d.window_size,
+                                                   local=local)
+        return lists, lengths

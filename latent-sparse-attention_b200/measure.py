@@ -1,0 +1,251 @@
+"""Measurements of the configurations the main benchmark does not time: the tree decode over a 1M-token cache and the
+batched paged decode of 64 requests. Each prints one JSON line (device time from CUDA events, the CPU oracle timed
+beside it on a stated sample, and a parity check of the measured path against the oracle).
+
+    python latent-sparse-attention_b200/measure.py tree-decode   [--tokens 1048576] [--steps 256]
+    python latent-sparse-attention_b200/measure.py batched-decode [--requests 64] [--steps 64]
+
+Inputs are seeded synthetic tensors with the shapes of the benchmark configurations.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+for _path in (HERE, os.path.dirname(HERE)):
+    if _path not in sys.path:
+        sys.path.insert(0, _path)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+from lsa_b200 import ops  # noqa: E402
+from lsa_b200.layer import FlatDesign, FlatLayer  # noqa: E402
+
+
+def clustered_cache(tokens: int, kv_heads: int, head_dim: int, centres: int, gen: torch.Generator, chunk: int = 1 << 17):
+    """K, V [tokens, Hkv, dh] bf16 on the device, keys around `centres` centres, built in chunks."""
+    k = torch.empty(tokens, kv_heads, head_dim, dtype=torch.bfloat16, device="cuda")
+    v = torch.empty_like(k)
+    mu = torch.randn(centres, kv_heads, head_dim, generator=gen, device="cuda")
+    for start in range(0, tokens, chunk):
+        n = min(chunk, tokens - start)
+        label = torch.randint(0, centres, (n,), generator=gen, device="cuda")
+        k[start:start + n] = (0.7071 * mu[label] + 0.7071 * torch.randn(n, kv_heads, head_dim, generator=gen,
+                                                                        device="cuda")).bfloat16()
+        v[start:start + n] = torch.randn(n, kv_heads, head_dim, generator=gen, device="cuda").bfloat16()
+    return k, v
+
+
+def timed_graph(step, warmup: int, steps: int) -> float:
+    """Microseconds a step, the step captured in a CUDA graph and replayed (falls back to eager launches if capture
+    is refused)."""
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    run = step
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+    except Exception as failure:  # capture is an optimisation of the measurement, not of the result
+        print(f"graph capture refused ({failure}); timing eager launches", file=sys.stderr)
+    for _ in range(warmup):
+        run()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        run()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / steps
+
+
+def tree_decode(args) -> dict:
+    """Config 3: one query a step over a 1M-token cache, a two-level tree of 64-child node buckets."""
+    import oracle
+    from lsa_b200.core import Buckets
+    from lsa_b200.decode import TreeDecoder
+    from lsa_b200.hierarchy import build_hierarchy
+
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    T, Hq, Hkv, dh = args.tokens, 40, 8, 128
+    design = FlatDesign(pool_size=4, bucket_size=16, bucket_cap=32, cluster_block_size=1024, top_p=64, top_k=2048,
+                        sink_size=4, window_size=1024)
+    k, v = clustered_cache(T, Hkv, dh, 256, gen)
+    w = (torch.randn(2, Hkv * dh, 64, generator=gen, device="cuda") / (Hkv * dh) ** 0.5).bfloat16()
+    layer = FlatLayer(design, w[0], w[1], Hq, Hkv, dh)
+    t0 = time.perf_counter()
+    index = layer.build_index(k)
+    torch.cuda.synchronize()
+    t_buckets = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    tree = build_hierarchy(index.index_keys, index.buckets, 1, 64, 4096)
+    torch.cuda.synchronize()
+    t_tree = time.perf_counter() - t0
+    position = T - 1
+    decoder = TreeDecoder(layer, index.buckets, tree, 32, None, 8192, 4096, splits=args.splits)
+    decoder.prepare(position)
+    q = (0.7071 * k[position].repeat_interleave(Hq // Hkv, dim=0) + 0.7071 * torch.randn(
+        Hq, dh, generator=gen, device="cuda").bfloat16())[None].contiguous()
+    out = decoder.step(q, k, v)
+    us = timed_graph(lambda: decoder.step(q, k, v), 5, args.steps)
+    lists, lengths = decoder.select(q)
+
+    # parity and the CPU baseline: the oracle reads the same step from the device's own index
+    b = index.buckets
+    buckets_np = oracle.Buckets(b.bucket_centroids.cpu().numpy(), b.bucket_members.cpu().numpy(),
+                                b.bucket_sizes.cpu().numpy(), b.block_bucket_count, b.cluster_block_size)
+    tree_np = oracle.Hierarchy([c.cpu().numpy() for c in tree.node_centroids], [c.cpu().numpy() for c in tree.children],
+                               64, (4096,))
+    index_q = layer.index_queries(q).cpu().numpy()
+    kf, vf = None, None
+    t0 = time.perf_counter()
+    want_lists, want_len = oracle.read_hierarchy(index_q, np.array([position]), buckets_np, tree_np, 32, None, 64,
+                                                 2048, 4, 1024, 8192, 4096)
+    t_read = time.perf_counter() - t0
+    same = bool(np.array_equal(lists.cpu().numpy(), want_lists) and int(lengths[0]) == int(want_len[0]))
+    ids = want_lists[0, : want_len[0]]
+    # gather the listed rows so the oracle need not hold a 2 GB fp32 copy of the cache
+    rows = torch.from_numpy(np.sort(ids)).cuda().long()
+    remap = {int(p): i for i, p in enumerate(np.sort(ids))}
+    local = np.array([[remap[int(p)] for p in ids]], dtype=np.int32)
+    kf, vf = k[rows].float().cpu().numpy(), v[rows].float().cpu().numpy()
+    t0 = time.perf_counter()
+    want, _ = oracle.sparse_attend(q.float().cpu().numpy(), kf, vf, local, np.array([len(ids)]), 0, 0, dh ** -0.5)
+    t_attend = time.perf_counter() - t0
+    err = float(np.abs(out.float().cpu().numpy() - want).max())
+    node_bytes = (960 + 32 * 64 + (int(want_len[0]) and 4032)) * 64 * 4
+    kv_bytes = int(want_len[0]) * Hkv * dh * 2 * 2
+    return {"metric": "tree decode us/step", "value": us, "unit": "us", "higher_is_better": False, "n_gpus": 1,
+            "config": {"workload": "C3", "tokens": T, "buckets": int(b.bucket_sizes.shape[0]),
+                       "nodes": int(tree.children[0].shape[0]), "beam": 32, "top_p": 64, "list": int(want_len[0]),
+                       "splits": args.splits},
+            "build": {"buckets_s": t_buckets, "tree_s": t_tree},
+            "parity": {"lists_equal": same, "attention_max_abs": err},
+            "algorithmic_bytes_per_step": node_bytes + kv_bytes,
+            "hbm_floor_us": (node_bytes + kv_bytes) / 6536.4e3,
+            "cpu_baseline": {"value": (t_read + t_attend) * 1e6, "unit": "us", "kind": "port",
+                             "cores": len(os.sched_getaffinity(0)), "sample": "one step: tree read + attend"}}
+
+
+def batched_decode(args) -> dict:
+    """Config 5: one decode step of 64 requests of 32k-512k tokens over a paged bf16 KV pool (page 64) and a paged
+    bucket cache, flat design."""
+    import oracle
+    from lsa_b200.serving import BucketCache, Selector
+
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rng = np.random.default_rng(0)
+    B, Hq, Hkv, dh, kv_page = args.requests, 40, 8, 128, 64
+    design = FlatDesign(pool_size=16, bucket_size=256, bucket_cap=512, cluster_block_size=1024, top_p=32, top_k=16384,
+                        sink_size=4, window_size=1024)
+    lengths = (np.exp(rng.uniform(math.log(args.min_len), math.log(args.max_len), B)) // 1024 * 1024).astype(np.int64)
+    total = int(lengths.sum())
+    pool_pages = total // kv_page + B
+    k, v = clustered_cache(pool_pages * kv_page, Hkv, dh, 256, gen)
+    w = (torch.randn(2, Hkv * dh, 64, generator=gen, device="cuda") / (Hkv * dh) ** 0.5).bfloat16()
+    layer = FlatLayer(design, w[0], w[1], Hq, Hkv, dh)
+    # KV pages dealt to the requests in a shuffled order; a request's position p is slot pages[p / 64] * 64 + p % 64
+    order = torch.from_numpy(rng.permutation(pool_pages).astype(np.int32)).cuda()
+    max_kv_pages = int(lengths.max()) // kv_page
+    kv_pages = torch.full((B, max_kv_pages), -1, dtype=torch.int32, device="cuda")
+    page_buckets = 32  # buckets of 8,192 keys a page of the bucket cache
+    cache = BucketCache(design, 64, pages=total // 8192 + 2 * B, page_buckets=page_buckets, max_requests=B,
+                        max_request_pages=int(lengths.max()) // 8192 + 1)
+    taken = 0
+    t0 = time.perf_counter()
+    for r, n in enumerate(lengths.tolist()):
+        count = n // kv_page
+        kv_pages[r, :count] = order[taken:taken + count]
+        taken += count
+        slots = (kv_pages[r, :count].long()[:, None] * kv_page + torch.arange(kv_page, device="cuda")[None]).reshape(-1)
+        for start in range(0, n, 1 << 17):  # index keys of the request, in position order, a piece at a time
+            piece = slots[start:start + (1 << 17)]
+            cache.append(r, layer.index_keys(k[piece]))
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t0
+    selector = Selector(cache, kv_page)
+    rows = torch.arange(B, device="cuda")
+    positions = torch.from_numpy(lengths - 1).cuda()
+    last_slot = kv_pages[rows, (positions // kv_page)].long() * kv_page + positions % kv_page
+    q = (0.7071 * k[last_slot].repeat_interleave(Hq // Hkv, dim=1) + 0.7071 * torch.randn(
+        B, Hq, dh, generator=gen, device="cuda")).bfloat16().contiguous()
+    visible = selector.visible(rows, positions)
+
+    def step():
+        lists, lens = selector.decode_flat(layer.index_queries(q), rows, positions, kv_pages, visible=visible,
+                                           splits=args.select_splits)
+        return ops.sparse_attend(q, k, v, lists, lens, layer.scale, splits=args.splits)[0], lists, lens
+
+    out, lists, lens = step()
+    us = timed_graph(lambda: step(), 3, args.steps)
+
+    # parity on a few requests, the oracle reading each from the device's own index vectors
+    index_q = layer.index_queries(q).cpu().numpy()
+    checked, worst, t_cpu = 0, 0.0, 0.0
+    for r in rng.choice(B, min(B, args.check), replace=False).tolist():
+        n = int(lengths[r])
+        slots = (kv_pages[r, : n // kv_page].long()[:, None] * kv_page + torch.arange(kv_page, device="cuda")[None]).reshape(-1)
+        index_k = torch.cat([layer.index_keys(k[slots[s:s + (1 << 17)]]) for s in range(0, n, 1 << 17)]).cpu().numpy()
+        t0 = time.perf_counter()
+        buckets = oracle.build_buckets(index_k, 16, 256, 512, 1024)
+        t_index = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        want, want_len = oracle.read(index_q[r:r + 1], np.array([n - 1]), buckets, 32, 16384, 4, 1024)
+        ids = want[0, : want_len[0]]
+        mine = lists[r, : int(lens[r])].cpu().numpy()
+        want_slots = slots[torch.from_numpy(ids.astype(np.int64)).cuda()].cpu().numpy()
+        assert int(lens[r]) == int(want_len[0]) and np.array_equal(mine, want_slots), f"request {r}: lists differ"
+        gathered = torch.from_numpy(want_slots).cuda().long()
+        ref, _ = oracle.sparse_attend(q[r:r + 1].float().cpu().numpy(), k[gathered].float().cpu().numpy(),
+                                      v[gathered].float().cpu().numpy(), np.arange(len(ids), dtype=np.int32)[None],
+                                      np.array([len(ids)]), 0, 0, dh ** -0.5)
+        t_cpu += time.perf_counter() - t0
+        worst = max(worst, float(np.abs(out[r].float().cpu().numpy() - ref[0]).max()))
+        checked += 1
+        del t_index
+    listed = int(lens.sum())
+    centroid_bytes = int(visible.sum()) * 64 * 4
+    kv_bytes = listed * Hkv * dh * 2 * 2
+    return {"metric": "batched decode steps/s", "value": 1e6 / us, "unit": "steps/s", "us_per_step": us,
+            "higher_is_better": True, "n_gpus": 1,
+            "config": {"workload": "C5", "requests": B, "tokens_total": total, "min_len": int(lengths.min()),
+                       "max_len": int(lengths.max()), "kv_page": kv_page, "top_p": 32, "listed_keys": listed,
+                       "splits": args.splits, "select_splits": args.select_splits},
+            "build": {"index_s": t_build},
+            "parity": {"requests_checked": checked, "lists_equal": True, "attention_max_abs": worst},
+            "algorithmic_bytes_per_step": centroid_bytes + kv_bytes,
+            "hbm_floor_us": (centroid_bytes + kv_bytes) / 6536.4e3,
+            "cpu_baseline": {"value": 1.0 / (t_cpu / max(checked, 1) * B), "unit": "steps/s", "kind": "port",
+                             "cores": len(os.sched_getaffinity(0)),
+                             "sample": f"read + attend of {checked} requests, scaled to {B}"}}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("what", choices=["tree-decode", "batched-decode"])
+    parser.add_argument("--tokens", type=int, default=1 << 20)
+    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--splits", type=int, default=16)
+    parser.add_argument("--select-splits", type=int, default=4)
+    parser.add_argument("--requests", type=int, default=64)
+    parser.add_argument("--min-len", type=int, default=32768)
+    parser.add_argument("--max-len", type=int, default=524288)
+    parser.add_argument("--check", type=int, default=4)
+    args = parser.parse_args()
+    torch.cuda.set_device(0)
+    result = tree_decode(args) if args.what == "tree-decode" else batched_decode(args)
+    print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

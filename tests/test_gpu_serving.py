@@ -1,0 +1,82 @@
+"""The paged serving index on the GPU: requests of different lengths share one bucket cache and one KV pool whose
+pages are not in order, and every decode list must be the oracle's read of that request, as KV slots."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import bf16_round, cuda, mixture, unit_rows
+
+pytestmark = pytest.mark.gpu
+
+
+def test_batched_decode_over_paged_buckets_and_kv(oracle):
+    from lsa_b200 import ops
+    from lsa_b200.layer import FlatDesign
+    from lsa_b200.serving import BucketCache, Selector
+
+    design = FlatDesign(pool_size=4, bucket_size=16, bucket_cap=32, cluster_block_size=256, top_p=6, top_k=150,
+                        sink_size=4, window_size=256)
+    d_idx, kv_page, page_buckets = 32, 64, 32
+    lengths = [700, 2048, 5000, 300, 1333]
+    rng = np.random.default_rng(0)
+    cache = BucketCache(design, d_idx, pages=24, page_buckets=page_buckets, max_requests=8, max_request_pages=16)
+    selector = Selector(cache, kv_page)
+    # KV pool pages dealt to requests in a shuffled order
+    total_pages = sum(-(-n // kv_page) for n in lengths)
+    order = rng.permutation(total_pages + 5).astype(np.int32)
+    kv_pages = np.full((len(lengths), max(-(-n // kv_page) for n in lengths)), -1, dtype=np.int32)
+    taken = 0
+    keys, raws = [], []
+    for r, n in enumerate(lengths):
+        count = -(-n // kv_page)
+        kv_pages[r, :count] = order[taken:taken + count]
+        taken += count
+        raw = mixture(n, d_idx, 10, 0.3, 100 + r)
+        raws.append(raw)
+        keys.append(unit_rows(raw))
+    # prefill arrives in pieces, the requests interleaved, so pages of the bucket cache interleave too
+    cut = [n // 3 for n in lengths]
+    for r, n in enumerate(lengths):
+        cache.append(r, cuda(keys[r][: cut[r]]))
+    for r, n in enumerate(lengths):
+        cache.append(r, cuda(keys[r][cut[r]:]))
+    assert [cache.closed_keys.get(r, 0) for r in range(len(lengths))] == [n // 256 * 256 for n in lengths]
+
+    positions = np.array([n - 1 for n in lengths])
+    queries = np.stack([unit_rows(raws[r][positions[r]] + 0.3 * rng.standard_normal(d_idx).astype(np.float32))
+                        for r in range(len(lengths))])
+    rows = torch.arange(len(lengths)).cuda()
+    for splits in (1, 3):
+        lists, lens = selector.decode_flat(cuda(queries), rows, cuda(positions), cuda(kv_pages), splits=splits)
+        for r, n in enumerate(lengths):
+            buckets = oracle.build_buckets(keys[r], 4, 16, 32, 256)
+            want, want_len = oracle.read(queries[r:r + 1], positions[r:r + 1], buckets, 6, 150, 4, 256)
+            ids = want[0, : want_len[0]]
+            slots = kv_pages[r][ids // kv_page] * kv_page + ids % kv_page
+            assert int(lens[r]) == int(want_len[0])
+            assert np.array_equal(lists[r, : int(lens[r])].cpu().numpy(), slots), (r, splits)
+            assert (lists[r, int(lens[r]):] == -1).all()
+
+    # the read over the pool: slots in, the oracle reads the same keys through the same table
+    Hq, Hkv, dh = 8, 2, 128
+    pool_rows = (total_pages + 5) * kv_page
+    k = bf16_round(rng.standard_normal((pool_rows, Hkv, dh), dtype=np.float32))
+    v = bf16_round(rng.standard_normal((pool_rows, Hkv, dh), dtype=np.float32))
+    q = bf16_round(rng.standard_normal((len(lengths), Hq, dh), dtype=np.float32))
+    out, _ = ops.sparse_attend(cuda(q, torch.bfloat16), cuda(k, torch.bfloat16), cuda(v, torch.bfloat16), lists, lens,
+                               dh ** -0.5, splits=4, out_dtype=torch.float32)
+    listed = lists.cpu().numpy()
+    want, _ = oracle.sparse_attend(q, k, v, listed, np.full(len(lengths), pool_rows), 0, 0, dh ** -0.5,
+                                   lengths=lens.cpu().numpy())
+    assert np.abs(out.cpu().numpy() - want).max() <= 2e-2
+
+    # releasing a request gives its pages back, and a new request can take them
+    free_before = len(cache.free_pages)
+    cache.release(2)
+    assert len(cache.free_pages) > free_before and (cache.request_pages[2] == -1).all()
+    cache.append(5, cuda(keys[1]))
+    assert cache.buckets_of(5) == 2048 // 16
+    with pytest.raises(RuntimeError, match="out of pages"):
+        for r in (6, 7):
+            cache.append(r, cuda(keys[2]))
