@@ -193,6 +193,15 @@ int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, 
                   const int64_t *children, int fanout, int32_t *kept_out, int64_t *keys_out, int32_t *carried_out,
                   void *stream);
 
+/* The same step with a row's candidates split over `splits` CTAs and merged by a second launch - the decode form,
+ * where one query would otherwise keep one CTA busy. workspace: lsa_beam_step_workspace_bytes(R, keep, splits). */
+size_t lsa_beam_step_workspace_bytes(int64_t R, int keep, int splits);
+int lsa_beam_step_split(const float *queries, int64_t R, int d, const float *vectors, int64_t N,
+                        const int32_t *carried, int n_carried, const int32_t *open_first, const int32_t *open_end,
+                        int keep, const int64_t *children, int fanout, int splits, int32_t *kept_out,
+                        int64_t *keys_out, int32_t *carried_out, void *workspace, size_t workspace_bytes,
+                        void *stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Expansion: picked buckets -> the row's read list. Reference: expand_buckets
  * (src/lsa/core/reference.py:268-289), budget_at (src/lsa/budget.py:60-74); served expand_in_order

@@ -286,7 +286,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
 __global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__restrict__ keys_in, int parts,
                                                               int64_t R, int keep, int room,
                                                               int64_t *__restrict__ keys_out,
-                                                              int32_t *__restrict__ ids_out) {
+                                                              int32_t *__restrict__ ids_out,
+                                                              const int64_t *__restrict__ children, int fanout,
+                                                              int32_t *__restrict__ carried_out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int64_t *buf = reinterpret_cast<int64_t *>(smem_raw);  // [room]
   int *hist = reinterpret_cast<int *>(buf + room);        // [256]
@@ -310,8 +312,15 @@ __global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__r
   warp_sort_descending(buf, n);
   for (int i = lane; i < keep; i += 32) {
     const int64_t key = i < n ? buf[i] : kEmptyKey;
-    keys_out[r * keep + i] = key;
+    if (keys_out) keys_out[r * keep + i] = key;
     if (ids_out) ids_out[r * keep + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+  }
+  if (carried_out) {  // the children of the kept rows, best row first
+    __syncwarp();
+    for (int e = lane; e < keep * fanout; e += 32) {
+      const int i = e / fanout, c = e - i * fanout;
+      carried_out[r * keep * fanout + e] = i < n ? (int32_t)children[(int64_t)key_id(buf[i]) * fanout + c] : LSA_PAD;
+    }
   }
 }
 
@@ -510,7 +519,7 @@ LSA_API size_t lsa_flat_select_decode_workspace_bytes(int64_t R, int top_p, int 
 
 LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out,
                                  int32_t *picked_out, void *stream) {
-  LSA_REQUIRE(keys_in && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(keys_in && (keys_out || picked_out), LSA_ERR_NULL);
   LSA_REQUIRE(parts >= 1 && R >= 0 && top_p >= 1, LSA_ERR_ARGUMENT);
   if (R == 0) return LSA_OK;
   const int room = lsa::pow2_at_least(parts * top_p);
@@ -520,7 +529,8 @@ LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, i
       cudaSuccess)
     return LSA_ERR_LAUNCH;
   lsa::merge_candidates_kernel<<<(unsigned)R, 32, smem, (cudaStream_t)stream>>>(keys_in, parts, R, top_p, room,
-                                                                                keys_out, picked_out);
+                                                                                keys_out, picked_out, nullptr, 0,
+                                                                                nullptr);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -623,4 +633,53 @@ LSA_API int lsa_flat_select_paged(const float *queries, int64_t R, int d, const 
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
   return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+}
+
+LSA_API size_t lsa_beam_step_workspace_bytes(int64_t R, int keep, int splits) {
+  return lsa_flat_select_decode_workspace_bytes(R, keep, splits);
+}
+
+LSA_API int lsa_beam_step_split(const float *queries, int64_t R, int d, const float *vectors, int64_t N,
+                                const int32_t *carried, int n_carried, const int32_t *open_first,
+                                const int32_t *open_end, int keep, const int64_t *children, int fanout, int splits,
+                                int32_t *kept_out, int64_t *keys_out, int32_t *carried_out, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+  if (splits <= 1)
+    return lsa_beam_step(queries, R, d, vectors, N, carried, n_carried, open_first, open_end, keep, children, fanout,
+                         kept_out, keys_out, carried_out, stream);
+  LSA_REQUIRE(queries && vectors && workspace, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && d >= 4 && d % 4 == 0 && N >= 0 && N < INT32_MAX && keep >= 1 && n_carried >= 0 &&
+                  splits <= 1024,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(n_carried == 0 || carried, LSA_ERR_NULL);
+  LSA_REQUIRE((children != nullptr) == (carried_out != nullptr), LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!children || fanout >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(kept_out || keys_out || carried_out, LSA_ERR_NULL);
+  LSA_REQUIRE(workspace_bytes >= lsa_beam_step_workspace_bytes(R, keep, splits), LSA_ERR_WORKSPACE);
+  if (R == 0) return LSA_OK;
+  lsa::SelectParams p = {};
+  p.queries = queries;
+  p.vectors = vectors;
+  p.run_first = open_first;
+  p.run_end = open_end;
+  p.carried = carried;
+  p.keys_out = (int64_t *)workspace;
+  p.R = R;
+  p.N = N;
+  p.d = d;
+  p.n_carried = n_carried;
+  p.keep = keep;
+  p.run_limit = (int)N;
+  int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
+  if (rc != LSA_OK) return rc;
+  const int room = lsa::pow2_at_least(splits * keep);
+  const size_t smem = (size_t)room * 8 + lsa::kHistBins * 4;
+  LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
+  if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  lsa::merge_candidates_kernel<<<(unsigned)R, 32, smem, (cudaStream_t)stream>>>(
+      (const int64_t *)workspace, splits, R, keep, room, keys_out, kept_out, children, fanout, carried_out);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
 }

@@ -40,6 +40,8 @@ SIGNATURES = {
     "lsa_flat_select_paged": (_I, [_P, _L, _I, _P, _L, _P, _I, _I, _P, _I, _I, _P, _P, _P, _Z, _P]),
     "lsa_merge_candidates": (_I, [_P, _I, _L, _I, _P, _P, _P]),
     "lsa_beam_step": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P]),
+    "lsa_beam_step_workspace_bytes": (_Z, [_L, _I, _I]),
+    "lsa_beam_step_split": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "lsa_expand": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I, _P, _I, _L, _L, _I, _I, _I, _I, _P, _P, _P,
                         _P]),
     "lsa_expand_batched": (_I, [_P, _L, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I, _P, _I, _L, _L, _I, _I, _I, _I, _P, _L, _P,

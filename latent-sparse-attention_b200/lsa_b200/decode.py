@@ -19,10 +19,11 @@ from lsa_b200.layer import FlatLayer
 
 class TreeDecoder:
     def __init__(self, layer: FlatLayer, buckets: Buckets, hierarchy: Hierarchy, beam_width, start_nodes: int | None,
-                 page_size: int, growth_buckets: int, splits: int = 16):
+                 page_size: int, growth_buckets: int, splits: int = 16, select_splits: int = 16):
         self.layer, self.buckets, self.hierarchy = layer, buckets, hierarchy
         self.beam_widths = per_level(beam_width, len(hierarchy.node_cluster_block_sizes))
         self.start_nodes, self.page_size, self.growth_buckets, self.splits = start_nodes, page_size, growth_buckets, splits
+        self.select_splits = select_splits
         self.plan = None
 
     def prepare(self, position: int) -> None:
@@ -45,9 +46,11 @@ class TreeDecoder:
             for level in range(plan["start"], 0, -1):
                 first, end = plan["runs"][level]
                 carried = ops.beam_step(index_query, self.hierarchy.node_centroids[level - 1], carried, first, end,
-                                        self.beam_widths[level - 1], children=self.hierarchy.children[level - 1])
+                                        self.beam_widths[level - 1], children=self.hierarchy.children[level - 1],
+                                        splits=self.select_splits)
             first, end = plan["runs"][0]
-            picked, _ = ops.beam_step(index_query, self.buckets.bucket_centroids, carried, first, end, d.top_p)
+            picked, _ = ops.beam_step(index_query, self.buckets.bucket_centroids, carried, first, end, d.top_p,
+                                      splits=self.select_splits)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, plan["positions"], self.buckets.bucket_members, d.top_k, d.sink_size,
                                            d.window_size)

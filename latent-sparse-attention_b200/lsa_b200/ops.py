@@ -244,7 +244,8 @@ def merge_candidates(keys_in: torch.Tensor):
 
 
 def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch.Tensor | None,
-              open_first: torch.Tensor, open_end: torch.Tensor, keep: int, children: torch.Tensor | None = None):
+              open_first: torch.Tensor, open_end: torch.Tensor, keep: int, children: torch.Tensor | None = None,
+              splits: int = 1, workspace: torch.Tensor | None = None):
     """One level of the beam (src/lsa/core/hierarchy.py:402-451): kept rows, or their children when given."""
     q, v = _contig(index_queries.float()), _contig(vectors.float())
     R, d = q.shape
@@ -259,9 +260,13 @@ def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch
     else:
         kept = torch.empty(R, keep, device=q.device, dtype=torch.int32)
         keys = torch.empty(R, keep, device=q.device, dtype=torch.int64)
-    call("lsa_beam_step", ptr(q), R, d, ptr(v), v.shape[0], ptr(carried), n_carried,
+    need = query("lsa_beam_step_workspace_bytes", R, keep, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_beam_step_split", ptr(q), R, d, ptr(v), v.shape[0], ptr(carried), n_carried,
          ptr(_contig(open_first.to(torch.int32))), ptr(_contig(open_end.to(torch.int32))), keep, ptr(children),
-         fanout, ptr(kept), ptr(keys), ptr(carried_out), stream())
+         fanout, splits, ptr(kept), ptr(keys), ptr(carried_out), ptr(workspace) if need else None, need, stream(),
+         launches=1 if splits <= 1 else 2)
     return carried_out if children is not None else (kept, keys)
 
 

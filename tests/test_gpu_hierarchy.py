@@ -89,3 +89,26 @@ def test_a_tree_over_large_node_blocks_is_bit_exact_with_the_oracle(oracle):
                                                         256, 4, 512, 8192, growth)
         assert np.array_equal(lens.cpu().numpy(), want_len) and np.array_equal(sel.cpu().numpy(), want_sel)
         assert np.array_equal(scored.cpu().numpy(), want_scored)
+
+
+def test_a_beam_step_split_over_ctas_keeps_what_one_cta_keeps():
+    from lsa_b200 import ops
+
+    g, buckets = _golden_store()
+    q = cuda(g["queries"])
+    R = q.shape[0]
+    nodes, kids = cuda(g["node_centroids_0"]), cuda(g["children_0"])
+    zero = torch.zeros(R, dtype=torch.int32).cuda()
+    end = torch.full((R,), nodes.shape[0], dtype=torch.int32).cuda()
+    want_kept, want_keys = ops.beam_step(q, nodes, None, zero, end, 5)
+    want_carried = ops.beam_step(q, nodes, None, zero, end, 5, children=kids)
+    for splits in (2, 7, 16):
+        kept, keys = ops.beam_step(q, nodes, None, zero, end, 5, splits=splits)
+        assert torch.equal(kept, want_kept) and torch.equal(keys, want_keys)
+        carried = ops.beam_step(q, nodes, None, zero, end, 5, children=kids, splits=splits)
+        assert torch.equal(carried, want_carried)
+        first = torch.full((R,), 900, dtype=torch.int32).cuda()
+        last = torch.full((R,), 1024, dtype=torch.int32).cuda()
+        a, _ = ops.beam_step(q, buckets.bucket_centroids, want_carried, first, last, 16)
+        b, _ = ops.beam_step(q, buckets.bucket_centroids, want_carried, first, last, 16, splits=splits)
+        assert torch.equal(a, b)

@@ -1,0 +1,186 @@
+"""The SGLang plugin surface without SGLang (as the reference tests it, tests/integ/sglang/test_plugin.py:1-7 and
+tests/unit/sglang/test_qwen3_5.py:1-9): settings parsing, hook registration against a fake registry, the call
+routing of `select_and_read` with fake backend objects; on a GPU, that a read attends over exactly the slots a list
+names and that a decode group's partial reads merge to the whole."""
+
+import enum
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from lsa_b200.sglang import backend, plugin, settings
+
+
+class FakeRegistry:
+    class HookType(enum.Enum):
+        BEFORE = 1
+        AFTER = 2
+        AROUND = 3
+        REPLACE = 4
+
+    def __init__(self):
+        self.hooks, self.applied = [], 0
+
+    def register(self, target, hook, kind):
+        self.hooks.append((target, hook, kind))
+
+    def apply_hooks(self):
+        self.applied += 1
+
+
+def test_settings_block_is_parsed_and_unknown_keys_are_refused():
+    design = settings.parse({"indexer": {"window_size": 1024, "top_p": 64, "top_k": 4096, "pool_size": 16,
+                                         "bucket_size": 32, "bucket_cap": 64},
+                             "serving": {"projections": "maps.safetensors"}})
+    assert design.width == 4096 + 1024 + 4 and design.early_width is None
+    flat = design.indexer.flat_design()
+    assert (flat.cluster_block_size, flat.block_bucket_count) == (1024, 32)
+    assert settings.parse({}).indexer.top_p == 1024  # the reference's defaults
+    early = settings.parse({"indexer": {"early_budget": {"position": 4096, "top_k": 512, "top_p": 64}}})
+    assert early.early_width == 512 + 512 + 4
+    for bad in ({"indexer": {"windows": 3}}, {"serving": {"kernels": "triton"}}, {"extra": 1},
+                {"indexer": {"bucket_cap": 8}}, {"indexer": {"window_size": 500}}, {"indexer": {"top_level": 1}},
+                {"serving": {"decode": "descend"}}, {"indexer": {"top_p": 4096}},
+                {"indexer": {"top_p": 2, "top_k": 4096}}, []):
+        with pytest.raises(ValueError):
+            settings.parse(bad)
+
+
+def test_every_target_is_resolved_before_any_hook_is_registered(monkeypatch):
+    design = settings.parse({"serving": {"projections": "maps.safetensors"}})
+    registry = FakeRegistry()
+    # sglang is not installed: nothing resolves, so nothing may be registered
+    with pytest.raises(RuntimeError, match="no longer resolve"):
+        plugin.enable_lsa(design, registry=registry)
+    assert not registry.hooks and not registry.applied
+    with pytest.raises(RuntimeError, match="no serving.projections"):
+        plugin.enable_lsa(settings.parse({}), registry=registry)
+    # against targets that do resolve the whole table goes in, then the hooks are applied once
+    fake = types.ModuleType("fake_engine")
+
+    class Attention:
+        def __init__(self): ...
+        def init_forward_metadata(self, forward_batch): ...
+        def init_forward_metadata_out_graph(self, forward_batch): ...
+        def forward_extend(self, q, k, v, layer, forward_batch, save_kv_cache=True): ...
+        def forward_decode(self, q, k, v, layer, forward_batch, save_kv_cache=True): ...
+
+    fake.Attention = Attention
+    monkeypatch.setitem(__import__("sys").modules, "fake_engine", fake)
+    targets = tuple(f"fake_engine.Attention.{m}" for m in plugin.GROUPED_QUERY_METHODS)
+    monkeypatch.setattr(plugin, "ENABLED", {})
+    assert plugin.enable_lsa(design, registry=registry, targets=targets) == 5
+    kinds = {target.rpartition(".")[2]: kind for target, _, kind in registry.hooks}
+    assert kinds["forward_extend"] == kinds["forward_decode"] == FakeRegistry.HookType.AROUND
+    assert kinds["__init__"] == FakeRegistry.HookType.AFTER and registry.applied == 1
+    assert plugin.ENABLED["design"] is design
+
+
+def test_the_standing_hook_enables_a_design_only_when_a_config_names_one(monkeypatch):
+    registry = FakeRegistry()
+    plugin.register(registry=registry)
+    assert [(t, h.__name__) for t, h, _ in registry.hooks] == [(plugin.MODEL_CONFIG, "configure")]
+    monkeypatch.setattr(plugin, "ENABLED", {})
+    plugin.configure(None, types.SimpleNamespace(hf_config=types.SimpleNamespace()), registry=registry)  # no block
+    assert "design" not in plugin.ENABLED
+    with pytest.raises(RuntimeError):  # a block is found and enabling it needs an engine that is not here
+        config = types.SimpleNamespace(hf_config=types.SimpleNamespace(lsa={"serving": {"projections": "m"}}))
+        plugin.configure(None, config, registry=registry)
+    with pytest.raises(RuntimeError, match="cannot read its settings"):
+        plugin.register()
+
+
+def test_select_and_read_hands_unserved_calls_back_untouched():
+    calls = []
+
+    def forward_decode(self, q, k, v, layer, forward_batch, save_kv_cache=True):
+        calls.append((q, save_kv_cache))
+        return "original"
+
+    engine = types.SimpleNamespace()  # no indexers: not an LSA layer
+    layer = types.SimpleNamespace(layer_id=3)
+    assert backend.select_and_read(forward_decode, engine, 1, 2, 3, layer, None) == "original"
+    engine.lsa_indexers = {3: object()}
+    assert backend.select_and_read(forward_decode, engine, 1, None, None, layer, None, save_kv_cache=False) == "original"
+    assert calls == [(1, True), (1, False)]
+    mode = types.SimpleNamespace(is_extend=lambda: False, is_target_verify=lambda: True)
+    with pytest.raises(NotImplementedError, match="speculative"):
+        backend.select_and_read(forward_decode, engine, 1, 2, 3, layer, types.SimpleNamespace(forward_mode=mode))
+
+
+def test_lists_split_over_a_decode_group_hold_every_slot_once():
+    lists = torch.tensor([[5, 2, 9, 4, -1, -1], [7, -1, -1, -1, -1, -1]], dtype=torch.int32)
+    assert backend.list_lengths(lists).tolist() == [4, 1]
+    seen = [[], []]
+    for rank in range(3):
+        rows, counts = backend.owned_lists(lists, backend.Shard(rank, 3))
+        for r in range(2):
+            held = rows[r, : int(counts[r])]
+            assert (rows[r, int(counts[r]):] == -1).all()
+            seen[r] += (held * 3 + rank).tolist()
+    assert sorted(seen[0]) == [2, 4, 5, 9] and seen[1] == [7]
+
+
+class _Pool:
+    def __init__(self, k, v):
+        self.k, self.v, self.saved = k, v, []
+
+    def get_key_buffer(self, layer_id):
+        return self.k
+
+    def get_value_buffer(self, layer_id):
+        return self.v
+
+    def set_kv_buffer(self, layer, loc, k, v):
+        self.saved.append(loc)
+        self.k[loc.long()] = k
+        self.v[loc.long()] = v
+
+
+@pytest.mark.gpu
+def test_a_read_attends_over_exactly_the_slots_a_list_names(oracle):
+    from helpers import bf16_round, cuda
+
+    rng = np.random.default_rng(0)
+    slots, Hq, Hkv, dh, T, width = 3000, 8, 2, 128, 6, 700
+    k = bf16_round(rng.standard_normal((slots, Hkv, dh), dtype=np.float32))
+    v = bf16_round(rng.standard_normal((slots, Hkv, dh), dtype=np.float32))
+    q = bf16_round(rng.standard_normal((T, Hq, dh), dtype=np.float32))
+    lists = np.full((T, width), -1, dtype=np.int32)
+    for r in range(T):
+        n = int(rng.integers(1, width))
+        lists[r, :n] = rng.choice(slots - 10, n, replace=False)
+    pool = _Pool(cuda(k, torch.bfloat16), cuda(v, torch.bfloat16))
+    engine = types.SimpleNamespace(token_to_kv_pool=pool)
+    layer = types.SimpleNamespace(layer_id=0, tp_q_head_num=Hq, tp_k_head_num=Hkv, head_dim=dh, scaling=dh ** -0.5)
+    want, _ = oracle.sparse_attend(q, k, v, lists, np.full(T, slots), 0, 0, dh ** -0.5)
+    out = backend.sparse_read(engine, cuda(q, torch.bfloat16).view(T, Hq * dh), layer, cuda(lists))
+    assert out.shape == (T, Hq * dh)
+    assert np.abs(out.float().cpu().numpy().reshape(T, Hq, dh) - want).max() <= 2e-2
+    # a decode group of two: each rank's pool holds every other slot, partial reads merged by hand
+    parts, lses = [], []
+    for rank in range(2):
+        shard = backend.Shard(rank, 2)
+        mine = types.SimpleNamespace(token_to_kv_pool=_Pool(pool.k[rank::2].contiguous(), pool.v[rank::2].contiguous()))
+        rows, counts = backend.owned_lists(cuda(lists), shard)
+        part, lse = backend.partial_read(mine, cuda(q, torch.bfloat16), layer, rows, counts)
+        parts.append(part)
+        lses.append(lse)
+    from lsa_b200 import ops
+    merged, _ = ops.lse_merge(torch.stack(parts), torch.stack(lses))
+    assert np.abs(merged.cpu().numpy() - want).max() <= 2e-2
+    # the full hook: save this step's keys, select, read
+    step_k, step_v = cuda(k[-T:], torch.bfloat16), cuda(v[-T:], torch.bfloat16)
+    indexer = types.SimpleNamespace(shard=backend.Shard(), select=lambda q_, k_, fb: cuda(lists))
+    engine.lsa_indexers = {0: indexer}
+    batch = types.SimpleNamespace(forward_mode=types.SimpleNamespace(is_extend=lambda: False),
+                                  out_cache_loc=torch.arange(slots - T, slots).cuda())
+
+    def forward_decode(self, q, k, v, layer, forward_batch, save_kv_cache=True):
+        raise AssertionError("a served layer must not reach the engine's own attention")
+
+    got = backend.select_and_read(forward_decode, engine, cuda(q, torch.bfloat16).view(T, Hq * dh), step_k, step_v, layer,
+                                  batch)
+    assert len(pool.saved) == 1 and np.abs(got.float().cpu().numpy().reshape(T, Hq, dh) - want).max() <= 2e-2
