@@ -68,34 +68,50 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   int counted = 0;  // ids that count toward top_k
   int written = 0;  // ids this owner keeps
   int bad = 0;
-  for (int i = 0; i < row_p && counted < row_k; ++i) {
-    int64_t bucket = p.picked[r * p.top_p + i];
-    if (bucket < 0) continue;
-    if (p.bucket_pages) {
-      // a request's logical bucket sits at row bucket % rows of its page bucket / rows
-      const int64_t slot = bucket / p.bucket_page_rows;
-      const int page = slot < p.bucket_max_pages ? p.bucket_pages[request * p.bucket_pages_stride + slot] : -1;
-      bucket = page >= 0 ? (int64_t)page * p.bucket_page_rows + bucket % p.bucket_page_rows : p.m;
+  // The picks are read 32 at a time, a lane a pick (so no load waits on the one before), and a bucket's member
+  // chunks four at a time: the loads of a group are in flight together, only the counting is in order.
+  const int chunks = (p.cap + 31) / 32;
+  for (int i0 = 0; i0 < row_p && counted < row_k; i0 += 32) {
+    int64_t my_bucket = -1;
+    if (i0 + lane < row_p) {
+      my_bucket = p.picked[r * p.top_p + i0 + lane];
+      if (my_bucket >= 0 && p.bucket_pages) {
+        // a request's logical bucket sits at row bucket % rows of its page bucket / rows
+        const int64_t slot = my_bucket / p.bucket_page_rows;
+        const int page = slot < p.bucket_max_pages ? p.bucket_pages[request * p.bucket_pages_stride + slot] : -1;
+        my_bucket = page >= 0 ? (int64_t)page * p.bucket_page_rows + my_bucket % p.bucket_page_rows : p.m;
+      }
+      if (my_bucket >= p.m) {
+        my_bucket = -1;
+        ++bad;
+      }
     }
-    if (bucket >= p.m) {
-      ++bad;
-      continue;
-    }
-    const int32_t *row = p.members + bucket * p.cap;
-    for (int base = 0; base < p.cap && counted < row_k; base += 32) {
-      const int32_t id = base + lane < p.cap ? row[base + lane] : LSA_PAD;
-      const bool counts = id >= p.sink && id < window_start;
-      const unsigned votes = __ballot_sync(0xffffffffu, counts);
-      const bool inside = counts && counted + __popc(votes & below) < row_k;
-      const bool mine = inside && owned(p, id);
-      const unsigned keeps = __ballot_sync(0xffffffffu, mine);
-      if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, id);
-      written += __popc(keeps);
-      counted += __popc(votes);
-      // Members are stored first, padding after: a chunk that ends in padding ends the bucket.
-      if (__ballot_sync(0xffffffffu, id < 0) & 0x80000000u) break;
+    const int picks = min(32, row_p - i0);
+    const int segments = picks * chunks;
+    for (int s0 = 0; s0 < segments && counted < row_k; s0 += 4) {
+      int32_t ids[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int seg = s0 + j;
+        const int pick = seg / chunks, at = (seg - pick * chunks) * 32 + lane;
+        const int64_t bucket = __shfl_sync(0xffffffffu, my_bucket, pick & 31);
+        ids[j] = seg < segments && bucket >= 0 && at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int32_t id = ids[j];
+        const bool counts = id >= p.sink && id < window_start;
+        const unsigned votes = __ballot_sync(0xffffffffu, counts);
+        const bool inside = counts && counted + __popc(votes & below) < row_k;
+        const bool mine = inside && owned(p, id);
+        const unsigned keeps = __ballot_sync(0xffffffffu, mine);
+        if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, id);
+        written += __popc(keeps);
+        counted += __popc(votes);
+      }
     }
   }
+  bad = warp_sum_int(bad);
   // The window, ascending, then the sinks.
   if (!(p.flags & LSA_EXPAND_NO_LOCAL)) {
     written = append_run(p, table, out, written, window_start, pos + 1, lane);

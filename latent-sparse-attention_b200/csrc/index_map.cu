@@ -94,10 +94,74 @@ __global__ void __launch_bounds__(kMapThreads)
   }
 }
 
+// A few rows (a decode step): one CTA a row, its threads splitting the input dims, so the map of a single query
+// is not one thread block walking the whole contraction alone.
+constexpr int kRowThreads = 256;
+
+template <typename TX, typename TW, int COLS>
+__global__ void __launch_bounds__(kRowThreads)
+    index_map_rows_kernel(const TX *__restrict__ x, int heads, int group, int dh_off, int dh_used, int64_t x_row_stride,
+                          int64_t x_head_stride, const TW *__restrict__ W, int d_idx, int normalize,
+                          float *__restrict__ out_f32, uint16_t *__restrict__ out_bf16) {
+  __shared__ float partial[kRowThreads / 32][COLS];
+  __shared__ float total[COLS];
+  __shared__ float norm_s;
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int d_in = heads / group * dh_used;
+  float acc[COLS];
+#pragma unroll
+  for (int j = 0; j < COLS; ++j) acc[j] = 0.0f;
+  for (int k = tid; k < d_in; k += kRowThreads) {
+    const int kv = k / dh_used, c = k - kv * dh_used;
+    const TX *src = x + row * x_row_stride + (int64_t)kv * group * x_head_stride + dh_off + c;
+    float xs = 0.0f;
+    for (int g = 0; g < group; ++g) xs = __fadd_rn(xs, load_as_float<TX>(src, (int64_t)g * x_head_stride));
+#pragma unroll
+    for (int j = 0; j < COLS; ++j)
+      if (j < d_idx) acc[j] = fmaf(xs, W ? load_as_float<TW>(W, (int64_t)k * d_idx + j) : (k == j ? 1.0f : 0.0f), acc[j]);
+  }
+#pragma unroll
+  for (int j = 0; j < COLS; ++j) {
+    const float v = warp_sum(acc[j]);
+    if (lane == 0) partial[warp][j] = v;
+  }
+  __syncthreads();
+  if (tid < COLS) {
+    float v = 0.0f;
+    for (int w = 0; w < kRowThreads / 32; ++w) v += partial[w][tid];
+    total[tid] = tid < d_idx ? v : 0.0f;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float ss = 0.0f;
+    for (int j = 0; j < d_idx; ++j) ss = fmaf(total[j], total[j], ss);
+    norm_s = normalize ? fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+  }
+  __syncthreads();
+  if (tid < d_idx) {
+    const float v = total[tid] / norm_s;
+    if (out_f32) out_f32[row * d_idx + tid] = v;
+    if (out_bf16) out_bf16[row * d_idx + tid] = float_to_bf16_bits(v);
+  }
+}
+
 template <typename TX, typename TW>
 static int launch_index_map(const void *x, int64_t rows, int heads, int group, int dh_off, int dh_used,
                             int64_t x_row_stride, int64_t x_head_stride, const void *W, int d_idx, int normalize,
                             float *out_f32, uint16_t *out_bf16, cudaStream_t s) {
+  if (rows <= 32 && d_idx <= 128) {
+    if (d_idx <= 64)
+      index_map_rows_kernel<TX, TW, 64><<<(unsigned)rows, kRowThreads, 0, s>>>(
+          (const TX *)x, heads, group, dh_off, dh_used, x_row_stride, x_head_stride, (const TW *)W, d_idx, normalize,
+          out_f32, out_bf16);
+    else
+      index_map_rows_kernel<TX, TW, 128><<<(unsigned)rows, kRowThreads, 0, s>>>(
+          (const TX *)x, heads, group, dh_off, dh_used, x_row_stride, x_head_stride, (const TW *)W, d_idx, normalize,
+          out_f32, out_bf16);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
   const size_t smem = sizeof(float) * ((size_t)kMapRows * (kMapSlice + 1) + (size_t)kMapSlice * d_idx);
   if (cudaFuncSetAttribute(index_map_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)

@@ -14,7 +14,8 @@ constexpr int kHistBins = 256;
 
 // ---------------------------------------------------------------------------------------- warp-level top-k
 
-// The k-th greatest of buf[0..n) (n > k >= 1, keys distinct), found by eight 8-bit radix passes of one warp.
+// A threshold t with exactly k keys of buf[0..n) at or above it (n > k >= 1, keys distinct): 8-bit radix passes of
+// one warp, most significant byte first, stopped as soon as the chosen bin holds exactly the keys still wanted.
 // hist is 256 ints of warp-private shared memory.
 __device__ uint64_t warp_kth_greatest(const int64_t *buf, int n, int k, int *hist) {
   const int lane = lane_id();
@@ -64,7 +65,10 @@ __device__ uint64_t warp_kth_greatest(const int64_t *buf, int n, int k, int *his
     remaining = __shfl_sync(0xffffffffu, next_remaining, src);
     prefix |= (uint64_t)digit << shift;
     mask |= (uint64_t)0xFF << shift;
+    // Every key of the chosen bin is wanted: the prefix with zero low bits already separates the k greatest keys.
+    const int in_bin = __shfl_sync(0xffffffffu, hist[digit], 0);
     __syncwarp();
+    if (in_bin == remaining) break;
   }
   return prefix;
 }

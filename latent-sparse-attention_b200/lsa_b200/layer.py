@@ -94,7 +94,9 @@ class FlatLayer:
 
     def _takes_tensor_cores(self, x: torch.Tensor) -> bool:
         """Heads packed densely in bf16 with a 16-byte aligned row pitch: the layout a TMA descriptor can walk."""
-        return (self.tensor_cores and x.dtype == torch.bfloat16 and x.stride(2) == 1 and x.stride(1) == x.shape[2]
+        # (a handful of rows - a decode step - goes to the kernel that splits one row's contraction over a CTA)
+        return (self.tensor_cores and x.shape[0] > 32 and x.dtype == torch.bfloat16 and x.stride(2) == 1
+                and x.stride(1) == x.shape[2]
                 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0)
 
     # ---- the stages

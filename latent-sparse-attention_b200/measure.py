@@ -99,6 +99,13 @@ def tree_decode(args) -> dict:
     out = decoder.step(q, k, v)
     us = timed_graph(lambda: decoder.step(q, k, v), 5, args.steps)
     lists, lengths = decoder.select(q)
+    from lsa_b200 import probe
+    recorder = probe.CudaEventRecorder()
+    probe.install(recorder)
+    for _ in range(20):
+        decoder.step(q, k, v)
+    stages = {name: total * 1e3 / 20 for name, (total, _) in recorder.totals_ms().items()}
+    probe.uninstall()
 
     # parity and the CPU baseline: the oracle reads the same step from the device's own index
     b = index.buckets
@@ -129,7 +136,7 @@ def tree_decode(args) -> dict:
             "config": {"workload": "C3", "tokens": T, "buckets": int(b.bucket_sizes.shape[0]),
                        "nodes": int(tree.children[0].shape[0]), "beam": 32, "top_p": 64, "list": int(want_len[0]),
                        "splits": args.splits},
-            "build": {"buckets_s": t_buckets, "tree_s": t_tree},
+            "build": {"buckets_s": t_buckets, "tree_s": t_tree}, "stages_us_eager": stages,
             "parity": {"lists_equal": same, "attention_max_abs": err},
             "algorithmic_bytes_per_step": node_bytes + kv_bytes,
             "hbm_floor_us": (node_bytes + kv_bytes) / 6536.4e3,
