@@ -56,6 +56,9 @@ int lsa_abi_version(void);
  *   W        [heads/group*dh_used, d_idx] of w_dtype, row-major; NULL = identity (d_idx = heads/group*dh_used)
  *   out_f32  [rows, d_idx] fp32 or NULL; out_bf16 [rows, d_idx] bf16 or NULL (at least one)
  *   normalize 0 = leave the product as it is (the partial form), 1 = unit rows, a zero row stays zero
+ * A map wider than 128 output dims (the 512-dim latent space of an MLA layer, regroup_latent at
+ * src/lsa/core/index_space.py:271-312) is written in slices and normalised in place by a second launch, so it
+ * needs out_f32 when normalize is set.
  * --------------------------------------------------------------------------------------------------------- */
 int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group, int dh_off, int dh_used,
                   int64_t x_row_stride, int64_t x_head_stride, const void *W, int w_dtype, int d_idx,
@@ -119,6 +122,16 @@ int lsa_bucket_table(const void *index_keys, int key_dtype, const int64_t *label
                      int pool_size, int d, int bucket_count, int bucket_cap, int64_t first_position,
                      int32_t *members, int32_t *sizes, float *key_sums, float *centroids,
                      uint16_t *centroids_bf16, int32_t *status, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Update step of the BASELINE-only k-means bucketing (the reference has no k-means: its buckets are Ward's). The
+ * assignment step is lsa_flat_select with top_p = 1 over the centroids (first maximum = lower id on a tie); this
+ * replaces every non-empty cluster's centroid by the normalised sum of its pools, added in pool order.
+ *   pools [n, d] fp32; order [n] int64 - the pools cluster by cluster, ascending inside a cluster;
+ *   offsets [k + 1] int64 - cluster j's run of `order`; centroids [k, d] fp32 in and out
+ * --------------------------------------------------------------------------------------------------------- */
+int lsa_kmeans_update(const float *pools, const int64_t *order, const int64_t *offsets, int k, int d,
+                      float *centroids, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Sums of gathered rows, in a fixed order: out[r, :] = sum_c src[index[r, c] - index_base, :], added one by one in
@@ -298,6 +311,26 @@ int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_
                     const uint16_t *k, const uint16_t *v, int64_t n_keys, int Hkv, int64_t kv_row_stride,
                     int64_t kv_head_stride, int64_t first_position, int window, int sink, float scale, float *out_f32,
                     float *lse, void *stream);
+
+/* Gather-sparse attention over a shared latent cache (the MLA form): all Hq heads of a row attend over the SAME
+ * listed latent rows; a key is the whole row (dk dims, rope part last), a value its first dv dims, and q holds the
+ * absorbed queries (the key up-projection folded into them), so no per-head key is ever materialised.
+ * Reference: topk_attention with one KV head (src/lsa/core/attention.py:65-146); the served form is FlashMLA's
+ * sparse kernel behind src/lsa/sglang/plugin.py:525-598 and the indexer of
+ * src/lsa/sglang/models/glm5_next/indexer.py:83-316.
+ *   q       [R, Hq, dk] bf16, element strides (q_row_stride, q_head_stride), 16-byte aligned rows
+ *   latent  [slots, dk] bf16 with latent_row_stride elements between rows
+ *   ids     [R, list_stride] int32, the first lengths[r] entries read (all when lengths is NULL); ids outside
+ *           [0, slots) are skipped. Lists hold each key once and only causal keys (lsa_expand writes such lists).
+ *   out     [R, Hq, dv] bf16 and/or fp32; lse [R, Hq] natural-log log-sum-exp (-inf for an empty list)
+ *   splits  CTAs a row's list is divided over; > 1 needs lsa_latent_attend_workspace_bytes() of workspace
+ * dk = 576, dv = 512 in this build. */
+size_t lsa_latent_attend_workspace_bytes(int64_t R, int Hq, int dv, int splits);
+int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int64_t q_row_stride,
+                      int64_t q_head_stride, const uint16_t *latent, int64_t slots, int64_t latent_row_stride,
+                      const int32_t *ids, int64_t list_stride, const int32_t *lengths, float scale, int splits,
+                      uint16_t *out_bf16, float *out_f32, float *lse, void *workspace, size_t workspace_bytes,
+                      void *stream);
 
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the

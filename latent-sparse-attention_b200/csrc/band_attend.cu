@@ -7,6 +7,7 @@
 // and log-sum-exp per (row, head), which lsa_sparse_attend takes as its starting state and extends with the
 // gathered keys.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace lsa {
 
@@ -20,32 +21,6 @@ struct BandParams {
   int Hq, Hkv, group, window, sink;
   float scale_log2;
 };
-
-__device__ __forceinline__ void band_cp_async_16(uint32_t dst, const void *src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void band_ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void band_ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
-                                                       uint32_t &r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void band_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t band_pack(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t *>(&h);
-}
 
 // grid (ceil(R / 16), Hkv, ceil(group / 8)); blockDim = min(group, 8) * 32. Row i of the call sits at position first_position + i and KV
 // row p holds position p.
@@ -81,8 +56,8 @@ __global__ void band_attend_kernel(BandParams p) {
       const bool ok = key < p.n_keys && (tile >= 0 || row < p.sink);
       const int64_t off = ok ? key * p.kv_row_stride + chunk * 8 : 0;
       const uint32_t dst = dst0 + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4);
-      band_cp_async_16(dst, k_head + off, ok ? 16 : 0);
-      band_cp_async_16(dst + TILE_BYTES, v_head + off, ok ? 16 : 0);
+      cp_async_16(dst, k_head + off, ok ? 16 : 0);
+      cp_async_16(dst + TILE_BYTES, v_head + off, ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -132,9 +107,9 @@ __global__ void band_attend_kernel(BandParams p) {
         const int row = np * 16 + (lane & 7) + (lane >> 4) * 8;
         const int chunk = ks * 2 + ((lane >> 3) & 1);
         uint32_t b0, b1, b2, b3;
-        band_ldmatrix_x4(k_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
-        band_mma(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-        band_mma(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+        ldmatrix_x4(k_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16(s[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        mma_bf16(s[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
       }
     }
     // mask: a key counts for a row if it is inside the row's window (and causal), or one of its sinks. A tile that
@@ -196,16 +171,16 @@ __global__ void band_attend_kernel(BandParams p) {
     // O [16 rows x DH] += P [16 x 64] V [64 x DH]
 #pragma unroll
     for (int kk = 0; kk < kBandKeys / 16; ++kk) {
-      const uint32_t a0 = band_pack(s[2 * kk][0], s[2 * kk][1]), a1 = band_pack(s[2 * kk][2], s[2 * kk][3]);
-      const uint32_t a2 = band_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = band_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      const uint32_t a0 = pack_bf16x2(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16x2(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16x2(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16x2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
       for (int np = 0; np < DH / 16; ++np) {
         const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int chunk = np * 2 + (lane >> 4);
         uint32_t b0, b1, b2, b3;
-        band_ldmatrix_x4_trans(v_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
-        band_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
-        band_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+        ldmatrix_x4_trans(v_src + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
+        mma_bf16(o[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
     }
     __syncthreads();

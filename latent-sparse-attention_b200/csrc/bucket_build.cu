@@ -435,3 +435,45 @@ LSA_API int lsa_gather_sum(const void *src, int src_dtype, const void *index, in
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
+
+// ================================================================================================ k-means update
+
+namespace lsa {
+
+// Update step of the BASELINE-only k-means bucketing: cluster j's new centroid is the normalised sum of the pools
+// assigned to it, added one by one in pool order (`order` lists the pools cluster by cluster, ascending within a
+// cluster; `offsets[j] .. offsets[j + 1]` is cluster j's run). An empty cluster, or one whose sum is zero, keeps its
+// centroid. One CTA a cluster; the norm is a single thread's fma chain so that it equals a CPU replay.
+__global__ void kmeans_update_kernel(const float *__restrict__ pools, const int64_t *__restrict__ order,
+                                     const int64_t *__restrict__ offsets, int d, float *__restrict__ centroids) {
+  extern __shared__ float sum[];  // [d]
+  __shared__ float norm_s;
+  const int64_t j = blockIdx.x;
+  const int64_t first = offsets[j], end = offsets[j + 1];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int64_t i = first; i < end; ++i) acc = __fadd_rn(acc, pools[order[i] * d + c]);
+    sum[c] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float ss = 0.0f;
+    for (int c = 0; c < d; ++c) ss = fmaf(sum[c], sum[c], ss);
+    norm_s = ss > 0.0f ? sqrtf(ss) : 0.0f;
+  }
+  __syncthreads();
+  if (norm_s > 0.0f)
+    for (int c = threadIdx.x; c < d; c += blockDim.x) centroids[j * d + c] = __fdiv_rn(sum[c], norm_s);
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_kmeans_update(const float *pools, const int64_t *order, const int64_t *offsets, int k, int d,
+                              float *centroids, void *stream) {
+  LSA_REQUIRE(pools && order && offsets && centroids, LSA_ERR_NULL);
+  LSA_REQUIRE(k >= 1 && d >= 1 && d <= 4096, LSA_ERR_ARGUMENT);
+  lsa::kmeans_update_kernel<<<(unsigned)k, 64, (size_t)d * sizeof(float), (cudaStream_t)stream>>>(pools, order,
+                                                                                                 offsets, d, centroids);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}

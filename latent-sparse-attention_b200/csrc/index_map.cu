@@ -10,7 +10,8 @@ namespace lsa {
 constexpr int kMapThreads = 256;
 constexpr int kMapRows = 64;    // rows a CTA maps, two a thread
 constexpr int kMapSlice = 64;   // input dims staged at a time
-constexpr int kMapMaxCols = 16; // output dims a thread holds (d_idx <= 128)
+constexpr int kMapMaxCols = 16; // output dims a thread holds: a CTA writes a slice of up to 128 output dims
+constexpr int kMapColSlice = 8 * kMapMaxCols;
 
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(kMapThreads)
@@ -24,7 +25,9 @@ __global__ void __launch_bounds__(kMapThreads)
   const int row_a = tid >> 3, row_b = row_a + 32, cg = tid & 7;
   const int64_t row0 = (int64_t)blockIdx.x * kMapRows;
   const int d_in = heads / group * dh_used;
-  const int cols = (d_idx + 7) / 8;
+  // blockIdx.y picks the slice of output dims; a map wider than one slice is normalised by a second kernel
+  const int col0 = blockIdx.y * kMapColSlice, width = min(kMapColSlice, d_idx - col0);
+  const int cols = (width + 7) / 8;
   float acc_a[kMapMaxCols], acc_b[kMapMaxCols];
 #pragma unroll
   for (int i = 0; i < kMapMaxCols; ++i) acc_a[i] = acc_b[i] = 0.0f;
@@ -42,8 +45,8 @@ __global__ void __launch_bounds__(kMapThreads)
       }
       xs[rr * (kMapSlice + 1) + kk] = sum;
     }
-    for (int e = tid; e < kMapSlice * d_idx; e += kMapThreads) {
-      const int kk = e / d_idx, j = e - kk * d_idx;
+    for (int e = tid; e < kMapSlice * width; e += kMapThreads) {
+      const int kk = e / width, j = col0 + e - kk * width;
       float w = 0.0f;
       if (kk < kn) w = W ? load_as_float<TW>(W, (int64_t)(k0 + kk) * d_idx + j) : (k0 + kk == j ? 1.0f : 0.0f);
       ws[e] = w;
@@ -51,11 +54,11 @@ __global__ void __launch_bounds__(kMapThreads)
     __syncthreads();
     for (int kk = 0; kk < kn; ++kk) {
       const float xa = xs[row_a * (kMapSlice + 1) + kk], xb = xs[row_b * (kMapSlice + 1) + kk];
-      const float *wrow = ws + kk * d_idx + cg;
+      const float *wrow = ws + kk * width + cg;
 #pragma unroll
       for (int i = 0; i < kMapMaxCols; ++i) {
         if (i < cols) {
-          const float w = (cg + 8 * i) < d_idx ? wrow[8 * i] : 0.0f;
+          const float w = (cg + 8 * i) < width ? wrow[8 * i] : 0.0f;
           acc_a[i] = fmaf(xa, w, acc_a[i]);
           acc_b[i] = fmaf(xb, w, acc_b[i]);
         }
@@ -79,8 +82,8 @@ __global__ void __launch_bounds__(kMapThreads)
   const float den_b = normalize ? fmaxf(sqrtf(ss_b), 1e-12f) : 1.0f;
 #pragma unroll
   for (int i = 0; i < kMapMaxCols; ++i) {
-    const int j = cg + 8 * i;
-    if (i >= cols || j >= d_idx) continue;
+    const int j = col0 + cg + 8 * i;
+    if (i >= cols || cg + 8 * i >= width) continue;
     if (row0 + row_a < rows) {
       const float v = acc_a[i] / den_a;
       if (out_f32) out_f32[(row0 + row_a) * d_idx + j] = v;
@@ -146,6 +149,24 @@ __global__ void __launch_bounds__(kRowThreads)
   }
 }
 
+// Unit rows in place, a warp a row: the second pass of a map wider than one slice.
+__global__ void __launch_bounds__(256)
+    rownorm_kernel(float *__restrict__ rows, int64_t n, int d, uint16_t *__restrict__ out_bf16) {
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= n) return;
+  float *r = rows + row * d;
+  float ss = 0.0f;
+  for (int j = lane; j < d; j += 32) ss = fmaf(r[j], r[j], ss);
+  ss = warp_sum(ss);
+  const float den = fmaxf(sqrtf(ss), 1e-12f);
+  for (int j = lane; j < d; j += 32) {
+    const float v = r[j] / den;
+    r[j] = v;
+    if (out_bf16) out_bf16[row * d + j] = float_to_bf16_bits(v);
+  }
+}
+
 template <typename TX, typename TW>
 static int launch_index_map(const void *x, int64_t rows, int heads, int group, int dh_off, int dh_used,
                             int64_t x_row_stride, int64_t x_head_stride, const void *W, int d_idx, int normalize,
@@ -162,15 +183,22 @@ static int launch_index_map(const void *x, int64_t rows, int heads, int group, i
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
-  const size_t smem = sizeof(float) * ((size_t)kMapRows * (kMapSlice + 1) + (size_t)kMapSlice * d_idx);
+  const int slices = (d_idx + kMapColSlice - 1) / kMapColSlice;
+  const size_t smem =
+      sizeof(float) * ((size_t)kMapRows * (kMapSlice + 1) + (size_t)kMapSlice * min(d_idx, kMapColSlice));
   if (cudaFuncSetAttribute(index_map_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  const unsigned grid = (unsigned)((rows + kMapRows - 1) / kMapRows);
-  index_map_kernel<TX, TW><<<grid, kMapThreads, smem, s>>>((const TX *)x, rows, heads, group, dh_off, dh_used,
-                                                            x_row_stride, x_head_stride, (const TW *)W, d_idx,
-                                                            normalize, out_f32, out_bf16);
+  const dim3 grid((unsigned)((rows + kMapRows - 1) / kMapRows), (unsigned)slices);
+  // One slice: the CTA holds whole rows and normalises them itself. More: fp32 rows first, then unit rows in place.
+  index_map_kernel<TX, TW><<<grid, kMapThreads, smem, s>>>(
+      (const TX *)x, rows, heads, group, dh_off, dh_used, x_row_stride, x_head_stride, (const TW *)W, d_idx,
+      slices == 1 ? normalize : 0, out_f32, slices == 1 || !normalize ? out_bf16 : nullptr);
   LSA_LAUNCH_CHECK();
+  if (slices > 1 && normalize) {
+    rownorm_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(out_f32, rows, d_idx, out_bf16);
+    LSA_LAUNCH_CHECK();
+  }
   return LSA_OK;
 }
 
@@ -186,7 +214,8 @@ LSA_API int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, i
   LSA_REQUIRE(x_dtype == LSA_DTYPE_F32 || x_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
   LSA_REQUIRE(w_dtype == LSA_DTYPE_F32 || w_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
   LSA_REQUIRE(W || d_idx == heads / group * dh_used, LSA_ERR_ARGUMENT);
-  LSA_REQUIRE(d_idx <= 8 * lsa::kMapMaxCols, LSA_ERR_UNSUPPORTED);
+  // a map wider than one slice of output dims is normalised in place in its fp32 output
+  LSA_REQUIRE(d_idx <= lsa::kMapColSlice || !normalize || out_f32, LSA_ERR_UNSUPPORTED);
   if (rows == 0) return LSA_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (x_dtype == LSA_DTYPE_BF16 && w_dtype == LSA_DTYPE_BF16)

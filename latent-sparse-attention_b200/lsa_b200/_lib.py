@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -33,6 +33,7 @@ SIGNATURES = {
     "lsa_ward_merge_workspace_bytes": (_Z, [_L, _I, _I]),
     "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P, _Z, _P]),
     "lsa_bucket_table": (_I, [_P, _I, _P, _L, _I, _I, _I, _I, _I, _L, _P, _P, _P, _P, _P, _P, _P]),
+    "lsa_kmeans_update": (_I, [_P, _P, _P, _I, _I, _P, _P]),
     "lsa_gather_sum": (_I, [_P, _I, _P, _I, _L, _I, _I, _L, _P, _P]),
     "lsa_flat_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _I, c_int32, _P, _P, _P]),
     "lsa_flat_select_decode_workspace_bytes": (_Z, [_L, _I, _I]),
@@ -53,6 +54,8 @@ SIGNATURES = {
     "lsa_sparse_attend_static_scratch_bytes": (_Z, []),
     "lsa_sparse_attend_static": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _L, _I, _L, _L, _P, _L, _P, _F, _I, _P, _P,
                                       _P, _P]),
+    "lsa_latent_attend_workspace_bytes": (_Z, [_L, _I, _I, _I]),
+    "lsa_latent_attend": (_I, [_P, _L, _I, _I, _I, _L, _L, _P, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P, _P, _Z, _P]),
     "lsa_lse_merge": (_I, [_P, _P, _I, _L, _I, _P, _P, _P, _P]),
 }
 

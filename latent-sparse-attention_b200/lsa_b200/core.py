@@ -135,6 +135,72 @@ class LearnedProjection:
         return int(self.key_projection.shape[1])
 
 
+@dataclass(frozen=True)
+class LatentMetric:
+    """An MLA layer's key maps [Hq, dh, r] and the lower Cholesky factor [r, r] fp32 of the metric they impose on the
+    latent, `L L^T = sum_h W_h^T W_h` (index_space.py:190-268). `L^T latent` has the lengths and angles the
+    concatenated per-head keys have, so a selection made on it is the one made on them, at r dims."""
+
+    key_maps: torch.Tensor
+    metric_factor: torch.Tensor
+
+    def __post_init__(self) -> None:
+        if self.key_maps.ndim != 3:
+            raise ValueError(f"key_maps must be [Hq, dh, r] - got {tuple(self.key_maps.shape)}")
+        rank = self.key_maps.shape[2]
+        if self.metric_factor.shape != (rank, rank):
+            raise ValueError(f"metric_factor must be [{rank}, {rank}] to match the key maps - "
+                             f"got {tuple(self.metric_factor.shape)}")
+
+    @property
+    def dim(self) -> int:
+        return int(self.key_maps.shape[2])
+
+    @classmethod
+    def from_key_maps(cls, key_maps: torch.Tensor) -> "LatentMetric":
+        """Factor the metric in fp64 (a layer's one-time setup; the factorisation is torch's).
+
+        Raises:
+            ValueError: `key_maps` is not `[Hq, dh, r]`, or the maps do not span the latent.
+        """
+        if key_maps.ndim != 3:
+            raise ValueError(f"key_maps must be [Hq, dh, r] - got {tuple(key_maps.shape)}")
+        metric = torch.einsum("hdr,hde->re", key_maps.double(), key_maps.double())
+        factored = torch.linalg.cholesky_ex(metric)
+        if int(factored.info) != 0:
+            raise ValueError(f"the key maps do not span the {key_maps.shape[2]}-dim latent - "
+                             "the metric they impose on it is singular and cannot be factored")
+        return cls(key_maps, factored.L.float())
+
+    def maps(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """The two linear maps `regroup_latent` amounts to, fp32 from fp64: queries [Hq*dh] -> r through `W L^-T`
+        (every head's key map pulled onto the query side, then `L^-1`), latents r -> r through `L`."""
+        wide = self.key_maps.double().reshape(-1, self.dim)
+        query_map = torch.linalg.solve_triangular(self.metric_factor.double(), wide.t(), upper=False).t()
+        return query_map.float().contiguous(), self.metric_factor.float().contiguous()
+
+
+def regroup_latent(q: torch.Tensor, latent: torch.Tensor, metric: LatentMetric):
+    """q [B,Hq,Tq,dh], latent [B,Tk,r] -> unit rows [B,Tq,r] and [B,Tk,r] fp32 (index_space.py:271-312), the keys
+    never expanded: both sides are one pass of the index map kernel, the triangular solve folded into the query map.
+
+    Raises:
+        ValueError: `q` or `latent` does not match the key maps.
+    """
+    head_count, head_dim, rank = metric.key_maps.shape
+    if q.ndim != 4 or q.shape[1] != head_count or q.shape[3] != head_dim:
+        raise ValueError(f"q must be [B, {head_count}, Tq, {head_dim}] to match the key maps - got {tuple(q.shape)}")
+    if latent.ndim != 3 or latent.shape[2] != rank:
+        raise ValueError(f"latent must be [B, Tk, {rank}] to match the key maps - got {tuple(latent.shape)}")
+    query_map, key_map = metric.maps()
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    queries = [ops.index_map(q[b].transpose(0, 1), query_map) for b in range(q.shape[0])]
+    keys = ops.index_map(latent.reshape(-1, 1, rank), key_map).reshape(latent.shape)
+    index_queries = torch.stack(queries) if queries else q.new_zeros(0, q.shape[2], rank, dtype=torch.float32)
+    return index_queries, keys
+
+
 # --------------------------------------------------------------------------------------------- Ward
 
 

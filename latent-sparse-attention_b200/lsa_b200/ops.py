@@ -183,6 +183,28 @@ def gather_sum(src: torch.Tensor, index: torch.Tensor, index_base: int = 0) -> t
     return out
 
 
+def kmeans(pools: torch.Tensor, init_centroids: torch.Tensor, iters: int):
+    """BASELINE-only k-means bucketing (no counterpart in the reference): `iters` Lloyd iterations over pool keys
+    [n, d] from `init_centroids` [k, d]; returns (centroids [k, d] fp32, assignment [n] int32). Assignment is the
+    exact fixed-order argmax of pool . centroid (a tie to the lower cluster)."""
+    pools = _contig(pools.float())
+    centroids = _contig(init_centroids.float()).clone()
+    n, d = pools.shape
+    k = centroids.shape[0]
+    every = torch.full((n,), k, device=pools.device, dtype=torch.int32)
+    assign = None
+    for it in range(iters + 1):
+        _, picked = flat_select(pools, centroids, every, 1)
+        assign = picked[:, 0]
+        if it == iters:
+            break
+        order = torch.argsort(assign, stable=True)
+        offsets = torch.zeros(k + 1, device=pools.device, dtype=torch.int64)
+        offsets[1:] = torch.cumsum(torch.bincount(assign, minlength=k), 0)
+        call("lsa_kmeans_update", ptr(pools), ptr(order), ptr(offsets), k, d, ptr(centroids), stream())
+    return centroids, assign
+
+
 def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: torch.Tensor, top_p: int,
                 row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0, keys: torch.Tensor | None = None,
                 picked: torch.Tensor | None = None):
@@ -348,6 +370,30 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
          ptr(lse), ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0,
          stream(), launches=1 if splits == 1 else 2)
     return (out_bf16 if out_bf16 is not None else out_f32), lse
+
+
+def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, lengths: torch.Tensor | None,
+                  scale: float, value_dim: int = 512, splits: int = 1, out_dtype=torch.bfloat16,
+                  workspace: torch.Tensor | None = None):
+    """The MLA read: absorbed queries q [R, Hq, dk] bf16 over the latent rows [slots, dk] bf16 each list names, a
+    value being a row's first `value_dim` dims. Returns (out [R, Hq, value_dim], lse [R, Hq])."""
+    if q.dtype != torch.bfloat16 or latent.dtype != torch.bfloat16:
+        raise ValueError("q and latent must be bfloat16")
+    if q.dim() != 3 or latent.dim() != 2 or q.stride(2) != 1 or latent.stride(1) != 1 or q.shape[2] != latent.shape[1]:
+        raise ValueError(f"q must be [R, Hq, dk] and latent [slots, dk] - got {tuple(q.shape)} and {tuple(latent.shape)}")
+    ids = _contig(ids)
+    R, Hq, dk = q.shape
+    out = torch.empty(R, Hq, value_dim, device=q.device, dtype=out_dtype)
+    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32)
+    need = query("lsa_latent_attend_workspace_bytes", R, Hq, value_dim, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_latent_attend", ptr(q), R, Hq, dk, value_dim, q.stride(0), q.stride(1), ptr(latent), latent.shape[0],
+         latent.stride(0), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits,
+         ptr(out) if out_dtype == torch.bfloat16 else None, ptr(out) if out_dtype == torch.float32 else None, ptr(lse),
+         ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
+         launches=1 if splits == 1 else 2)
+    return out, lse
 
 
 def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_position: int, window: int, sink: int,

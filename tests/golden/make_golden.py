@@ -62,6 +62,20 @@ def main(src):
     save("index_space", q=q[0].transpose(0, 1), k=k[0].transpose(0, 1), index_queries=iq[0], index_keys=ik[0],
          w=w, projected_queries=project(iq[0], w), projected_keys=project(ik[0], w))
 
+    # ---- the MLA index space: latent keys under the metric their key maps impose (test_index_space.py:169-232)
+    from lsa.core import LatentMetric, regroup_latent
+    gen = torch.Generator().manual_seed(4)
+    ql = torch.randn(1, 8, 40, 16, generator=gen)
+    latent = torch.randn(1, 40, 12, generator=gen)
+    latent[0, 5] = 0
+    key_maps = torch.randn(8, 16, 12, generator=gen) / 4
+    metric = LatentMetric.from_key_maps(key_maps)
+    lq, lk = regroup_latent(ql, latent, metric)
+    wide_q, wide_k = regroup(ql, torch.einsum("btr,hdr->bhtd", latent, key_maps))
+    save("latent_space", q=ql[0].transpose(0, 1), latent=latent[0], key_maps=key_maps,
+         metric_factor=metric.metric_factor, index_queries=lq[0], index_keys=lk[0],
+         wide_scores=wide_q[0] @ wide_k[0].T)
+
     # ---- packed keys (src/lsa/core/kernels/triton/keys.py)
     scores = torch.tensor([0.0, -0.0, 1.5, -1.5, 1e-30, -1e-30, 3.0e38, -3.0e38, 0.25, 0.25])
     ids = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 9, 8], dtype=torch.int32)

@@ -163,6 +163,18 @@ def test_ward_golden_and_adversarial_cases(ops, oracle):
     assert not reached.any() and torch.equal(labels.cpu(), torch.arange(16).expand(2, 16))
 
 
+def test_kmeans_bucketing_matches_its_restatement(ops, oracle):
+    """BASELINE-only variant (no reference code): config 1's shapes - 1,024 pools, 256 centres, 32 dims, 10 rounds."""
+    keys = unit_rows(mixture(16384, 32, 64, 0.3, 8))
+    pools = oracle.pool_keys(keys[None], 16)[0]
+    rng = np.random.default_rng(0)
+    init = unit_rows(pools[rng.permutation(len(pools))[:256]])
+    want_centroids, want_assign = oracle.kmeans(pools, init, 10)
+    centroids, assign = ops.kmeans(cuda(pools), cuda(init), 10)
+    assert np.array_equal(assign.cpu().numpy(), want_assign)
+    assert np.array_equal(centroids.cpu().numpy().view(np.int32), want_centroids.view(np.int32))
+
+
 def test_bucket_table_is_bit_exact(ops, oracle):
     for name, (pool, bucket, cap, block) in {"flat_small": (4, 8, 16, 64), "flat_c1like": (16, 64, 128, 512)}.items():
         g = golden(name)

@@ -1,0 +1,151 @@
+"""The MLA form of the path: the latent index space (`regroup_latent`, `LatentMetric`,
+src/lsa/core/index_space.py:190-312) and gather attention over a shared latent cache (`topk_attention` with one KV
+head whose values are the first 512 dims of the key, src/lsa/core/attention.py:65-146)."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+from helpers import bf16_round, cuda, mixture
+
+pytestmark = pytest.mark.gpu
+
+
+def test_latent_regroup_matches_the_reference_vectors():
+    from lsa_b200 import core
+
+    g = golden("latent_space")
+    metric = core.LatentMetric.from_key_maps(cuda(g["key_maps"]))
+    assert metric.dim == 12
+    assert np.abs(metric.metric_factor.cpu().numpy() - g["metric_factor"]).max() <= 2e-6
+    q = cuda(g["q"]).transpose(0, 1)[None]  # [1, Hq, T, dh]
+    iq, ik = core.regroup_latent(q, cuda(g["latent"])[None], metric)
+    assert iq.shape == (1, 40, 12) and ik.shape == (1, 40, 12)
+    assert np.abs(iq[0].cpu().numpy() - g["index_queries"]).max() <= 5e-6
+    assert np.abs(ik[0].cpu().numpy() - g["index_keys"]).max() <= 5e-6
+    assert not ik[0, 5].any()
+
+    degenerate = cuda(g["key_maps"]).clone()
+    degenerate[..., -1] = 0
+    with pytest.raises(ValueError, match="do not span"):
+        core.LatentMetric.from_key_maps(degenerate)
+    with pytest.raises(ValueError, match=r"\[Hq, dh, r\]"):
+        core.LatentMetric.from_key_maps(torch.randn(16, 12, device="cuda"))
+    with pytest.raises(ValueError, match="metric_factor must be"):
+        core.LatentMetric(key_maps=cuda(g["key_maps"]), metric_factor=torch.eye(13, device="cuda"))
+    with pytest.raises(ValueError, match="to match the key maps"):
+        core.regroup_latent(q[:, :4], cuda(g["latent"])[None], metric)
+    with pytest.raises(ValueError, match="to match the key maps"):
+        core.regroup_latent(q, cuda(g["latent"])[None, :, :8], metric)
+
+
+def test_latent_regroup_at_the_served_width(oracle):
+    """r = 512, 16 heads of 64 dims: the map is wider than one slice of output dims, so the second-pass
+    normalisation runs. Both sides against the oracle's fixed-order product."""
+    from lsa_b200 import core
+
+    rng = np.random.default_rng(0)
+    heads, dh, r, tokens = 16, 64, 512, 300
+    key_maps = (rng.standard_normal((heads, dh, r)) / dh ** 0.5).astype(np.float32)
+    q = rng.standard_normal((tokens, heads, dh)).astype(np.float32)
+    latent = mixture(tokens, r, 8, 0.3, 1)
+    latent[17] = 0
+    factor = oracle.latent_metric_factor(key_maps)
+    want_q, want_k = oracle.regroup_latent(q, latent, key_maps, factor)
+    metric = core.LatentMetric.from_key_maps(cuda(key_maps))
+    assert np.abs(metric.metric_factor.cpu().numpy() - factor).max() <= 1e-5
+    iq, ik = core.regroup_latent(cuda(q).transpose(0, 1)[None], cuda(latent)[None], metric)
+    assert np.abs(iq[0].cpu().numpy() - want_q).max() <= 2e-5
+    assert np.abs(ik[0].cpu().numpy() - want_k).max() <= 2e-5
+    assert not ik[0, 17].any()
+    norms = ik[0].norm(dim=-1).cpu().numpy()
+    assert np.abs(np.delete(norms, 17) - 1).max() <= 1e-5
+
+
+def _latent_case(seed, rows, heads, slots, width, ragged=True):
+    rng = np.random.default_rng(seed)
+    latent = bf16_round(np.concatenate([mixture(slots, 512, 16, 0.5, seed), rng.standard_normal((slots, 64),
+                                                                                                 dtype=np.float32)], 1))
+    q = bf16_round(0.3 * rng.standard_normal((rows, heads, 576), dtype=np.float32))
+    ids = np.full((rows, width), -1, dtype=np.int32)
+    lengths = np.zeros(rows, dtype=np.int32)
+    for r in range(rows):
+        n = int(rng.integers(0, width + 1)) if ragged else width
+        if r == 0:
+            n = 0  # an empty list: zeros and a log-sum-exp of minus infinity
+        if r == 1:
+            n = min(width, 33)  # one key past a tile
+        ids[r, :n] = rng.choice(slots, n, replace=False)
+        lengths[r] = n
+    return q, latent, ids, lengths
+
+
+@pytest.mark.parametrize("heads,splits", [(64, 1), (64, 4), (16, 1), (128, 3)])
+def test_latent_attend_matches_the_oracle(oracle, heads, splits):
+    from lsa_b200 import ops
+
+    rows, slots, width = 12, 3000, 700
+    q, latent, ids, lengths = _latent_case(heads + splits, rows, heads, slots, width)
+    scale = 576 ** -0.5
+    out, lse = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths), scale,
+                                 splits=splits, out_dtype=torch.float32)
+    want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
+                                          np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    got, got_lse = out.cpu().numpy(), lse.cpu().numpy()
+    assert not got[0].any() and np.isneginf(got_lse[0]).all()
+    gap = np.abs(got - want[:, :, :512])
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (gap.max(), gap.mean())
+    held = lengths > 0
+    assert np.abs(got_lse[held] - want_lse[held]).max() <= 2e-2
+
+    # bf16 output, ids outside the cache skipped, lengths left out (the -1 padding is skipped like any bad id)
+    ids_bad = ids.copy()
+    ids_bad[2, : lengths[2] // 2] = slots + 5
+    out16, _ = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids_bad), None, scale,
+                                 splits=splits)
+    keep = ids.copy()
+    keep[2, : lengths[2] // 2] = -1
+    want2, _ = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], keep,
+                                    np.full(rows, slots, dtype=np.int64), 0, 0, scale)
+    assert np.abs(out16.float().cpu().numpy() - want2[:, :, :512]).max() <= 3e-2
+
+
+def test_latent_layer_end_to_end(oracle):
+    """Index space -> buckets -> read -> attention for an MLA layer, against the oracle stage by stage."""
+    from lsa_b200 import core, ops
+
+    rng = np.random.default_rng(7)
+    heads, dh, r, tokens = 16, 64, 512, 2048
+    key_maps = (rng.standard_normal((heads, dh, r)) / dh ** 0.5).astype(np.float32)
+    latent_nope = bf16_round(mixture(tokens, r, 12, 0.3, 3))
+    rope = bf16_round(rng.standard_normal((tokens, 64), dtype=np.float32))
+    # pre-index queries whose absorbed form points at their own latent
+    q_heads = bf16_round(np.einsum("tr,hdr->thd", latent_nope + 0.3 * rng.standard_normal((tokens, r), dtype=np.float32),
+                                   key_maps))
+    factor = oracle.latent_metric_factor(key_maps)
+    want_q, want_k = oracle.regroup_latent(q_heads, latent_nope, key_maps, factor)
+    metric = core.LatentMetric.from_key_maps(cuda(key_maps))
+    iq, ik = core.regroup_latent(cuda(q_heads).transpose(0, 1)[None], cuda(latent_nope)[None], metric)
+    assert np.abs(ik[0].cpu().numpy() - want_k).max() <= 2e-5
+
+    # buckets and lists from the oracle's keys on both sides, so the integer stages compare bit for bit
+    buckets = core.build_buckets(cuda(want_k), 4, 16, 32, 256)
+    want_buckets = oracle.build_buckets(want_k, 4, 16, 32, 256)
+    assert np.array_equal(buckets.bucket_members.cpu().numpy(), want_buckets.bucket_members)
+    positions = np.arange(tokens - 64, tokens)
+    lists, lens = core.read(cuda(want_q[positions]), cuda(positions), buckets, 8, 200, 4, 256)
+    want_lists, want_lens = oracle.read(want_q[positions], positions, want_buckets, 8, 200, 4, 256)
+    assert np.array_equal(lists.cpu().numpy(), want_lists) and np.array_equal(lens.cpu().numpy(), want_lens)
+
+    # the read: absorbed queries (W_h^T q_h, rope part appended) over the latent cache
+    absorbed = np.einsum("thd,hdr->thr", q_heads[positions], key_maps)
+    q_full = bf16_round(np.concatenate([absorbed, rng.standard_normal((64, heads, 64), dtype=np.float32)], 2))
+    cache = np.concatenate([latent_nope, rope], 1)
+    scale = (dh + 64) ** -0.5
+    out, _ = ops.latent_attend(cuda(q_full, torch.bfloat16), cuda(cache, torch.bfloat16), lists, lens, scale, splits=2,
+                               out_dtype=torch.float32)
+    want, _ = oracle.sparse_attend(q_full, cache[:, None, :], cache[:, None, :], want_lists, positions, 0, 0, scale,
+                                   lengths=want_lens)
+    gap = np.abs(out.cpu().numpy() - want[:, :, :512])
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (gap.max(), gap.mean())

@@ -38,6 +38,26 @@ def test_regroup_and_project_match_the_reference(oracle):
         oracle.project(iq[:, :8], g["w"])
 
 
+def test_latent_regroup_matches_the_reference(oracle):
+    """The MLA index space (src/lsa/core/index_space.py:240-312): the factor, both sides' unit rows, and the property
+    the reference's own test checks - the latent scores rank keys as the expanded keys' scores do."""
+    g = golden("latent_space")
+    factor = oracle.latent_metric_factor(g["key_maps"])
+    assert np.abs(factor - g["metric_factor"]).max() <= 2e-6
+    iq, ik = oracle.regroup_latent(g["q"], g["latent"], g["key_maps"], factor)
+    assert np.abs(iq - g["index_queries"]).max() <= 5e-6
+    assert np.abs(ik - g["index_keys"]).max() <= 5e-6
+    assert not ik[5].any()  # a zero latent stays zero
+    narrow = iq @ ik.T
+    held = np.ones(40, dtype=bool)
+    held[5] = False
+    assert np.array_equal(np.argsort(narrow[:, held], axis=1), np.argsort(g["wide_scores"][:, held], axis=1))
+    degenerate = g["key_maps"].copy()
+    degenerate[..., -1] = 0
+    with pytest.raises(ValueError, match="do not span"):
+        oracle.latent_metric_factor(degenerate)
+
+
 def test_pooling_matches_the_reference(oracle):
     g = golden("ward")
     np.testing.assert_allclose(oracle.pool_keys(g["c_keys"], 16), g["c_pools"], rtol=0, atol=1e-6)
