@@ -39,9 +39,10 @@ C2 = dict(workload="C2", tokens=131072, heads=40, kv_heads=8, head_dim=128, inde
           bucket_size=32, bucket_cap=64, cluster_block_size=1024, top_p=64, top_k=4096, sink_size=4,
           window_size=1024, chunk=8192, centres=256, seed=0)
 
-# DRAM bytes of one sparse_attend launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture
-# summarised in profiles/; None until a capture of this workload's launch exists.
-ATTEND_DRAM_TRAFFIC_PER_LAUNCH = None
+# DRAM bytes per algorithmic byte of a sparse_attend launch, from the ncu capture summarised in profiles/
+# (dram__bytes_read.sum + dram__bytes_write.sum = 35.75 GB for a launch of about 68 GB at 49,152 tokens; traffic
+# grows with the ids a launch gathers). The traffic reported is this ratio times the launch's algorithmic bytes.
+ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.52
 
 
 def small(cfg: dict, tokens: int) -> dict:
@@ -323,7 +324,7 @@ def run_ours(args, cfg: dict) -> dict:
         "clocks": clocks.summary(),
         "roofline": {"kernel": "sparse_attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                     "traffic": ATTEND_DRAM_TRAFFIC_PER_LAUNCH, "algorithmic_bytes_per_launch": per_launch_bytes,
+                     "traffic": ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE * per_launch_bytes, "algorithmic_bytes_per_launch": per_launch_bytes,
                      "launches_per_step": attend_launches // args.steps,
                      "ms_per_launch": attend_ms / max(1, attend_launches)},
         "stages_ms_per_step": {name: total / args.steps for name, (total, _) in sorted(stage_ms.items())},

@@ -95,8 +95,8 @@ int lsa_pool_keys(const void *index_keys, int key_dtype, int64_t n_pools, int po
  *   labels     [blocks, P] int64 out - each pool's bucket, numbered by first pool
  *   reached    [blocks] uint8 out - 1 where the block got down to bucket_count
  *   rounds     [blocks] int32 out or NULL - merge rounds the block ran
- * Blocks of up to 512 pools are merged by one CTA out of shared memory (d <= 256, d % 4 == 0) and need no
- * workspace. Larger blocks (up to 4,096 pools, d 16, 32 or 64: the node-bucket pairings of the tree,
+ * Blocks of up to 512 pools are merged by one CTA out of shared memory (d % 4 == 0, d <= 1024, the block's
+ * P * (d + 4) floats within 227 KB: 64 pools of the 512-dim latent space fit) and need no workspace. Larger blocks (up to 4,096 pools, d 16, 32 or 64: the node-bucket pairings of the tree,
  * src/lsa/core/hierarchy.py:73-98, cluster_node_buckets at src/lsa/core/kernels/ward.py:84-110) keep their state in
  * the caller's workspace and run two launches a round for max_rounds rounds without a host read; a block that is
  * finished returns at once. Costs are fp32 in the reference's evaluation order, the Gram dot added in ascending

@@ -314,7 +314,7 @@ LSA_API int lsa_ward_merge(const float *pool_keys, const float *pool_sizes, floa
   LSA_REQUIRE(pool_keys && labels && reached, LSA_ERR_NULL);
   LSA_REQUIRE(blocks >= 0 && P >= 1 && d >= 4 && d % 4 == 0 && bucket_count >= 1 && max_rounds >= 0,
               LSA_ERR_ARGUMENT);
-  LSA_REQUIRE(P <= 4096 && d <= 256, LSA_ERR_UNSUPPORTED);
+  LSA_REQUIRE(P <= 4096 && d <= 1024, LSA_ERR_UNSUPPORTED);
   if (blocks == 0) return LSA_OK;
   const size_t need = lsa_ward_merge_workspace_bytes(blocks, P, d);
   if (need > 0) {
