@@ -39,10 +39,11 @@ C2 = dict(workload="C2", tokens=131072, heads=40, kv_heads=8, head_dim=128, inde
           bucket_size=32, bucket_cap=64, cluster_block_size=1024, top_p=64, top_k=4096, sink_size=4,
           window_size=1024, chunk=8192, centres=256, seed=0)
 
-# DRAM bytes per algorithmic byte of a sparse_attend launch, from the ncu capture summarised in profiles/
-# (dram__bytes_read.sum + dram__bytes_write.sum = 35.75 GB for a launch of about 68 GB at 49,152 tokens; traffic
-# grows with the ids a launch gathers). The traffic reported is this ratio times the launch's algorithmic bytes.
-ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.52
+# DRAM bytes per algorithmic byte of a sparse_attend launch, from a one-pass ncu capture of the 16 launches of a
+# full-size step (dram__bytes_read.sum + dram__bytes_write.sum: 0.3 GB for the first chunk up to 55.9 GB for the
+# last, 37.2 GB on average, against 66.4 GB of algorithmic bytes; summarised in profiles/). The traffic reported is
+# this ratio times the launch's algorithmic bytes.
+ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.561
 
 
 def small(cfg: dict, tokens: int) -> dict:

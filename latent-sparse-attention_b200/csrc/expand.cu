@@ -124,6 +124,101 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   }
 }
 
+// A few rows with long lists (a decode step): a whole CTA a row. The warps count every pick's ids at once, one warp
+// scans the counts into write offsets, and the warps write their picks' ids in place - the list is the same as the
+// one-warp kernel's, id for id. Only for callers that keep every id (no owner range, no dealt granules), so the ids
+// that count toward top_k are the ids written.
+constexpr int kWideThreads = 1024;
+constexpr int kWideMaxPicks = 1024;
+
+__global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams p) {
+  __shared__ int64_t bucket_s[kWideMaxPicks];
+  __shared__ int count_s[kWideMaxPicks];
+  __shared__ int start_s[kWideMaxPicks + 1];
+  __shared__ int bad_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = kWideThreads / 32;
+  const int64_t r = blockIdx.x;
+  const int64_t pos = p.positions[r];
+  const int64_t request = p.row_request ? p.row_request[r] : 0;
+  const int32_t *table = p.page_table ? p.page_table + request * p.page_table_stride : nullptr;
+  const int row_p = p.row_top_p ? min(p.row_top_p[r], p.top_p) : p.top_p;
+  const int row_k = p.row_top_k ? min(p.row_top_k[r], p.top_k) : p.top_k;
+  const int64_t window_start = max((int64_t)0, pos + 1 - p.window);
+  int32_t *out = p.selected + r * p.width;
+  const unsigned below = (1u << lane) - 1;
+  if (tid == 0) bad_s = 0;
+  __syncthreads();
+  for (int i = tid; i < row_p; i += kWideThreads) {
+    int64_t bucket = p.picked[r * p.top_p + i];
+    if (bucket >= 0 && p.bucket_pages) {
+      const int64_t slot = bucket / p.bucket_page_rows;
+      const int page = slot < p.bucket_max_pages ? p.bucket_pages[request * p.bucket_pages_stride + slot] : -1;
+      bucket = page >= 0 ? (int64_t)page * p.bucket_page_rows + bucket % p.bucket_page_rows : p.m;
+    }
+    if (bucket >= p.m) {
+      bucket = -1;
+      atomicAdd(&bad_s, 1);
+    }
+    bucket_s[i] = bucket;
+  }
+  __syncthreads();
+  for (int pick = warp; pick < row_p; pick += kWarps) {
+    const int64_t bucket = bucket_s[pick];
+    int n = 0;
+    if (bucket >= 0)
+      for (int at0 = 0; at0 < p.cap; at0 += 32) {
+        const int32_t id = at0 + lane < p.cap ? p.members[bucket * p.cap + at0 + lane] : LSA_PAD;
+        n += __popc(__ballot_sync(0xffffffffu, id >= p.sink && id < window_start));
+      }
+    if (lane == 0) count_s[pick] = n;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < row_p; base += 32) {
+      const int v = base + lane < row_p ? count_s[base + lane] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (base + lane < row_p) start_s[base + lane] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) start_s[row_p] = carry;
+  }
+  __syncthreads();
+  for (int pick = warp; pick < row_p; pick += kWarps) {
+    const int64_t bucket = bucket_s[pick];
+    int written = start_s[pick];
+    if (bucket < 0) continue;
+    for (int at0 = 0; at0 < p.cap && written < row_k; at0 += 32) {
+      const int32_t id = at0 + lane < p.cap ? p.members[bucket * p.cap + at0 + lane] : LSA_PAD;
+      const bool counts = id >= p.sink && id < window_start;
+      const unsigned votes = __ballot_sync(0xffffffffu, counts);
+      const int at = written + __popc(votes & below);
+      if (counts && at < row_k) out[at] = stored_id(p, table, id);
+      written += __popc(votes);
+    }
+  }
+  int total = min(start_s[row_p], row_k);
+  if (!(p.flags & LSA_EXPAND_NO_LOCAL)) {
+    const int in_window = (int)(pos + 1 - window_start);
+    for (int i = tid; i < in_window; i += kWideThreads) out[total + i] = stored_id(p, table, window_start + i);
+    total += in_window;
+    const int sinks = (int)min((int64_t)p.sink, min(window_start, pos + 1));
+    for (int i = tid; i < sinks; i += kWideThreads) out[total + i] = stored_id(p, table, i);
+    total += sinks;
+  }
+  for (int j = total + tid; j < p.width; j += kWideThreads) out[j] = LSA_PAD;
+  if (tid == 0) {
+    p.lengths[r] = total;
+    if (bad_s && p.status) atomicAdd(p.status, bad_s);
+  }
+}
+
 }  // namespace lsa
 
 LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
@@ -175,6 +270,13 @@ LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, cons
   p.window = window;
   p.page_size = page_size;
   p.width = top_k + window + sink;
+  const bool keeps_all = owner_world <= 1 && owner_first <= 0 && owner_end == INT64_MAX;
+  if (R <= 64 && keeps_all && top_p <= lsa::kWideMaxPicks && (int64_t)top_p * bucket_cap >= 4096) {
+    // a decode step's long lists: one CTA a row
+    lsa::expand_wide_kernel<<<(unsigned)R, lsa::kWideThreads, 0, (cudaStream_t)stream>>>(p);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
   const unsigned grid = (unsigned)((R + lsa::kExpandWarps - 1) / lsa::kExpandWarps);
   lsa::expand_kernel<<<grid, lsa::kExpandWarps * 32, 0, (cudaStream_t)stream>>>(p);
   LSA_LAUNCH_CHECK();

@@ -82,7 +82,8 @@ def index_map_tc(x: torch.Tensor, weight_t: torch.Tensor, normalize: bool = True
     return out if out is not None else out_bf16
 
 
-def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: torch.Tensor | None = None):
+def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: torch.Tensor | None = None,
+            out: torch.Tensor | None = None):
     """The BASELINE-only two-layer map normalize(gelu(x @ W1) @ W2) on the tensor cores: x [rows, d_in] bf16,
     w1_t [d_hidden, d_in], w2_t [d_idx, d_hidden] bf16 -> fp32 [rows, d_idx]. The hidden layer is held in bf16."""
     rows, d_in = x.shape
@@ -91,7 +92,7 @@ def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: tor
         hidden = torch.empty(rows, d_hidden, device=x.device, dtype=torch.bfloat16)
     call("lsa_gemm_gelu_tc", ptr(x), rows, d_in, x.stride(0), ptr(_contig(w1_t)), d_hidden, ptr(hidden), None,
          stream())
-    return index_map_tc(hidden, _contig(w2_t))
+    return index_map_tc(hidden, _contig(w2_t), out=out)
 
 
 def pool_keys(index_keys: torch.Tensor, pool_size: int, out: torch.Tensor | None = None) -> torch.Tensor:

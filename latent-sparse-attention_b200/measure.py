@@ -1,9 +1,10 @@
-"""Measurements of the configurations the main benchmark does not time: the tree decode over a 1M-token cache and the
-batched paged decode of 64 requests. Each prints one JSON line (device time from CUDA events, the CPU oracle timed
+"""Measurements of the configurations the main benchmark does not time: the tree decode over a 1M-token cache, the
+batched paged decode of 64 requests, and the flat design over an MLA-style latent cache. Each prints one JSON line (device time from CUDA events, the CPU oracle timed
 beside it on a stated sample, and a parity check of the measured path against the oracle).
 
     python latent-sparse-attention_b200/measure.py tree-decode   [--tokens 1048576] [--steps 256]
     python latent-sparse-attention_b200/measure.py batched-decode [--requests 64] [--steps 64]
+    python latent-sparse-attention_b200/measure.py latent-layer   [--tokens 10485760] [--chunk 8192] [--splits 148]
 
 Inputs are seeded synthetic tensors with the shapes of the benchmark configurations.
 """
@@ -237,9 +238,145 @@ def batched_decode(args) -> dict:
                              "sample": f"read + attend of {checked} requests, scaled to {B}"}}
 
 
+def latent_layer(args) -> dict:
+    """Config 4: the flat design over an MLA-style layer - 64 query heads over a shared latent of 512 + 64 rope dims,
+    two-layer maps 576 -> 2048 -> 64, keys pooled by 64 into buckets of 640 (cap 1,280, 8 a cluster block), the top
+    128 buckets plus 4 sinks and a 5,120-key window; one prefill chunk of 8,192 queries at the end of the context,
+    then decode steps at the last position."""
+    import oracle
+    from lsa_b200 import core
+
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    T, Hq, dk, dv, d_idx, hidden_dim = args.tokens, 64, 576, 512, 64, 2048
+    chunk = min(args.chunk, T)
+    top_p, cap = 128, 1280
+    top_k = top_p * cap
+    sink, window = 4, 5120
+    # the latent cache: a clustered 512-dim part (256 centres) and N(0,1) rope dims, built a piece at a time
+    cache = torch.empty(T, dk, dtype=torch.bfloat16, device="cuda")
+    mu = torch.randn(256, dv, generator=gen, device="cuda")
+    for start in range(0, T, 1 << 18):
+        n = min(1 << 18, T - start)
+        label = torch.randint(0, 256, (n,), generator=gen, device="cuda")
+        cache[start:start + n, :dv] = (0.7071 * mu[label] + 0.7071 * torch.randn(n, dv, generator=gen,
+                                                                                 device="cuda")).bfloat16()
+        cache[start:start + n, dv:] = torch.randn(n, dk - dv, generator=gen, device="cuda").bfloat16()
+    w1 = [(torch.randn(hidden_dim, dk, generator=gen, device="cuda") / dk ** 0.5).bfloat16() for _ in range(2)]
+    w2 = [(torch.randn(d_idx, hidden_dim, generator=gen, device="cuda") / hidden_dim ** 0.5).bfloat16() for _ in range(2)]
+    # absorbed queries of the chunk: every head points at its token's latent, plus noise
+    positions = torch.arange(T - chunk, T, device="cuda")
+    q = (0.7071 * cache[T - chunk:, None, :].float() + 0.7071 * torch.randn(chunk, Hq, dk, generator=gen,
+                                                                            device="cuda")).bfloat16().contiguous()
+    scale = (128 + 64) ** -0.5 / 4  # keeps the logits of unit-variance 576-dim vectors in a softmax's working range
+
+    start_ev, stop_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        start_ev.record()
+        result = fn()
+        stop_ev.record()
+        torch.cuda.synchronize()
+        return result, start_ev.elapsed_time(stop_ev)
+
+    def key_map():
+        index_keys = torch.empty(T, d_idx, dtype=torch.float32, device="cuda")
+        piece = 1 << 19
+        hidden = torch.empty(min(piece, T), hidden_dim, dtype=torch.bfloat16, device="cuda")
+        for start in range(0, T, piece):
+            n = min(piece, T - start)
+            ops.mlp_map(cache[start:start + n], w1[1], w2[1], hidden=hidden[:n], out=index_keys[start:start + n])
+        return index_keys
+
+    def query_map(rows):
+        summed = ops.index_map(rows, None, group=Hq, normalize=False, out_dtype=torch.bfloat16)
+        return ops.mlp_map(summed, w1[0], w2[0])
+
+    index_keys, ms_key_map = timed(key_map)
+    buckets, ms_buckets = timed(lambda: core.build_buckets(index_keys, 64, 640, cap, 5120))
+
+    def prefill():
+        index_q = query_map(q)
+        lists, lens = core.read(index_q, positions, buckets, top_p, top_k, sink, window)
+        out, _ = ops.latent_attend(q, cache, lists, lens, scale)
+        return index_q, lists, lens, out
+
+    prefill()  # warm-up
+    (index_q, lists, lens, out), ms_prefill = timed(prefill)
+    _, ms_attend = timed(lambda: ops.latent_attend(q, cache, lists, lens, scale))
+
+    # decode at the last position
+    q1, pos1 = q[-1:].contiguous(), positions[-1:]
+    visible1 = torch.full((1,), (T - 1) // 5120 * 8, dtype=torch.int32, device="cuda")
+
+    from lsa_b200 import probe
+
+    def decode():
+        with probe.region("index map"):
+            index_q1 = query_map(q1)
+        with probe.region("select"):
+            _, picked = ops.flat_select_decode(index_q1, buckets.bucket_centroids, None, visible1, top_p,
+                                               splits=args.select_splits)
+        with probe.region("expand"):
+            l1, n1, _ = ops.expand(picked, pos1, buckets.bucket_members, top_k, sink, window)
+        with probe.region("attend"):
+            return ops.latent_attend(q1, cache, l1, n1, scale, splits=args.splits)[0], l1, n1
+
+    out1, l1, n1 = decode()
+    us_decode = timed_graph(lambda: decode(), 3, args.steps)
+    recorder = probe.CudaEventRecorder()
+    probe.install(recorder)
+    for _ in range(20):
+        decode()
+    decode_stages = {name: total * 1e3 / 20 for name, (total, _) in recorder.totals_ms().items()}
+    probe.uninstall()
+
+    # parity on sample rows of the chunk and the decode row, the oracle reading the device's own index vectors
+    b_np = oracle.Buckets(buckets.bucket_centroids.cpu().numpy(), buckets.bucket_members.cpu().numpy(),
+                          buckets.bucket_sizes.cpu().numpy(), buckets.block_bucket_count, buckets.cluster_block_size)
+    rows = sorted({0, chunk - 1} | set(np.random.default_rng(0).choice(chunk, min(args.check, chunk), replace=False).tolist()))
+    iq_np, pos_np = index_q.cpu().numpy(), positions.cpu().numpy()
+    t0 = time.perf_counter()
+    want_lists, want_lens = oracle.read(iq_np[rows], pos_np[rows], b_np, top_p, top_k, sink, window)
+    t_read = time.perf_counter() - t0
+    same = all(int(lens[r]) == int(want_lens[i]) and np.array_equal(lists[r, : int(lens[r])].cpu().numpy(),
+                                                                  want_lists[i, : want_lens[i]])
+               for i, r in enumerate(rows))
+    same = same and np.array_equal(l1[0, : int(n1[0])].cpu().numpy(), want_lists[-1, : want_lens[-1]])
+    worst, t_attend = 0.0, 0.0
+    for i, r in list(enumerate(rows))[-2:]:
+        ids = np.sort(want_lists[i, : want_lens[i]])
+        gathered = cache[torch.from_numpy(ids.astype(np.int64)).cuda()].float().cpu().numpy()
+        t0 = time.perf_counter()
+        ref, _ = oracle.sparse_attend(q[r:r + 1].float().cpu().numpy(), gathered[:, None, :], gathered[:, None, :],
+                                      np.arange(len(ids), dtype=np.int32)[None], np.array([len(ids)]), 0, 0, scale)
+        t_attend += time.perf_counter() - t0
+        worst = max(worst, float(np.abs(out[r].float().cpu().numpy() - ref[0, :, :dv]).max()))
+        if r == chunk - 1:
+            worst = max(worst, float(np.abs(out1[0].float().cpu().numpy() - ref[0, :, :dv]).max()))
+    gathered_total = int(lens.sum())
+    flops = 2.0 * gathered_total * Hq * (dk + dv)
+    cpu_row_s = t_read / len(rows) + t_attend / 2
+    return {"metric": "MLA flat prefill tokens/s", "value": chunk / (ms_prefill * 1e-3), "unit": "tokens/s",
+            "higher_is_better": True, "n_gpus": 1, "decode_us_per_step": us_decode,
+            "config": {"workload": "C4", "tokens": T, "chunk": chunk, "heads": Hq, "latent": dk, "value_dim": dv,
+                       "buckets": int(buckets.bucket_sizes.shape[0]), "top_p": top_p, "window": window,
+                       "keys_listed_per_row": gathered_total / chunk, "decode_splits": args.splits},
+            "build_ms": {"key_map": ms_key_map, "buckets": ms_buckets},
+            "stages_ms": {"prefill_chunk": ms_prefill, "attend": ms_attend}, "decode_stages_us_eager": decode_stages,
+            "attend": {"tflops": flops / (ms_attend * 1e-3) / 1e12, "gathered_GBps": gathered_total * dk * 2 / (
+                ms_attend * 1e-3) / 1e9},
+            "parity": {"rows_checked": len(rows), "lists_equal": bool(same), "attention_max_abs": worst},
+            "hbm_floor_decode_us": (int(n1[0]) * dk * 2 + int(visible1[0]) * d_idx * 4) / 6536.4e3,
+            "cpu_baseline": {"value": 1.0 / cpu_row_s, "unit": "tokens/s", "kind": "port",
+                             "cores": len(os.sched_getaffinity(0)),
+                             "sample": f"read of {len(rows)} rows and attend of 2 rows, per-row times summed"}}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("what", choices=["tree-decode", "batched-decode"])
+    parser.add_argument("what", choices=["tree-decode", "batched-decode", "latent-layer"])
+    parser.add_argument("--chunk", type=int, default=8192)
     parser.add_argument("--tokens", type=int, default=1 << 20)
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--splits", type=int, default=16)
@@ -250,7 +387,7 @@ def main() -> None:
     parser.add_argument("--check", type=int, default=4)
     args = parser.parse_args()
     torch.cuda.set_device(0)
-    result = tree_decode(args) if args.what == "tree-decode" else batched_decode(args)
+    result = {"tree-decode": tree_decode, "batched-decode": batched_decode, "latent-layer": latent_layer}[args.what](args)
     print(json.dumps(result))
 
 

@@ -356,6 +356,48 @@ def test_expansion_with_slots_owners_and_bad_ids(ops, oracle):
     assert int(status) == 1
 
 
+def test_expansion_of_a_few_rows_with_long_lists(ops, oracle):
+    """Up to 64 rows whose picks hold over a thousand ids go through the CTA-a-row kernel; its lists are the
+    one-warp kernel's and the oracle's, id for id - cut at top_k, under per-row budgets, through a page table."""
+    g = golden("flat_c1like")
+    buckets = oracle.Buckets(g["centroids"], g["members"], g["sizes"], 8, 512)
+    rows = slice(40, 88)
+    positions = g["positions"][rows]
+    _, _, picked, _ = oracle.read(g["queries"][rows], positions, buckets, 16, 700, 4, 512, return_picked=True)
+    pos, mem = cuda(positions), cuda(g["members"])
+    for top_k in (700, 150, 4000):
+        want_sel, want_len = oracle.expand(picked, positions, g["members"], top_k, 4, 512)
+        sel, lens, _ = ops.expand(cuda(picked), pos, mem, top_k, 4, 512)
+        assert np.array_equal(sel.cpu().numpy(), want_sel) and np.array_equal(lens.cpu().numpy(), want_len), top_k
+    # the early budget of the first rows
+    cut = int(positions[20])
+    want_sel, want_len = oracle.expand(picked, positions, g["members"], 700, 4, 512, early_budget=(cut, 90, 5))
+    early = positions < cut
+    row_p = cuda(np.where(early, 5, 16).astype(np.int32))
+    row_k = cuda(np.where(early, 90, 700).astype(np.int32))
+    sel, lens, _ = ops.expand(cuda(picked), pos, mem, 700, 4, 512, row_p, row_k)
+    assert np.array_equal(sel.cpu().numpy(), want_sel) and np.array_equal(lens.cpu().numpy(), want_len)
+    # KV slots through a page table, the window and sinks left out, a pick past the table
+    pages = np.random.default_rng(3).permutation(70).astype(np.int32)
+    want_sel, want_len = oracle.expand(picked, positions, g["members"], 700, 4, 512)
+    sel, lens, _ = ops.expand(cuda(picked), pos, mem, 700, 4, 512, page_table=cuda(pages), page_size=64)
+    mapped = np.where(want_sel >= 0, pages[np.maximum(want_sel, 0) // 64] * 64 + np.maximum(want_sel, 0) % 64, -1)
+    assert np.array_equal(sel.cpu().numpy(), mapped) and np.array_equal(lens.cpu().numpy(), want_len)
+    bare, bare_len, _ = ops.expand(cuda(picked), pos, mem, 700, 4, 512, local=False)
+    for r in range(len(positions)):
+        n = int(bare_len[r])
+        assert np.array_equal(bare[r, :n].cpu().numpy(), want_sel[r, :n]) and (bare[r, n:] == -1).all()
+        assert n == int(want_len[r]) - min(512, int(positions[r]) + 1) - min(4, max(0, int(positions[r]) + 1 - 512))
+    bad = picked.copy()
+    bad[3, 1] = 10**6
+    sel, _, status = ops.expand(cuda(bad), pos, mem, 700, 4, 512)
+    assert int(status) == 1
+    keep = np.delete(bad[3], 1)[None]
+    want_row, _ = oracle.expand(np.concatenate([keep, np.full((1, 1), -1, np.int32)], 1), positions[3:4],
+                                g["members"], 700, 4, 512)
+    assert np.array_equal(sel[3].cpu().numpy(), want_row[0])
+
+
 # ------------------------------------------------------------------------------------------------ attention
 
 
