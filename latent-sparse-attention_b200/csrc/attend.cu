@@ -321,6 +321,64 @@ __global__ void lse_merge_kernel(const float *__restrict__ parts, const float *_
   if (lane == 0 && lse_out) lse_out[row] = total;
 }
 
+// The same merge for many parts or wide rows (a decode row split over a hundred CTAs): a CTA of 128 threads a row.
+// The parts' weights are computed once into shared memory, 256 parts at a time; a thread owns dims tid, tid + 128,
+// ... and adds the parts in order, so an output element sees the same sequence of fused multiply-adds either way.
+constexpr int kMergeWideDims = 8;  // dims a thread holds: rows of up to 1,024 dims
+
+__global__ void __launch_bounds__(128)
+    lse_merge_wide_kernel(const float *__restrict__ parts, const float *__restrict__ lses, int n_parts, int64_t rows,
+                          int dh, uint16_t *__restrict__ out_bf16, float *__restrict__ out_f32,
+                          float *__restrict__ lse_out) {
+  __shared__ float w_s[256];
+  __shared__ float red_s[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  float m = -INFINITY;
+  for (int i = tid; i < n_parts; i += 128) m = fmaxf(m, lses[(int64_t)i * rows + row]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) red_s[warp] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+  __syncthreads();
+  float total = -INFINITY;
+  if (m > -INFINITY) {
+    float l = 0.0f;
+    for (int i = tid; i < n_parts; i += 128) l += expf(lses[(int64_t)i * rows + row] - m);
+    l = warp_sum(l);
+    if (lane == 0) red_s[warp] = l;
+    __syncthreads();
+    total = m + logf(red_s[0] + red_s[1] + red_s[2] + red_s[3]);
+  }
+  float acc[kMergeWideDims];
+#pragma unroll
+  for (int j = 0; j < kMergeWideDims; ++j) acc[j] = 0.0f;
+  for (int i0 = 0; i0 < n_parts; i0 += 256) {
+    const int n = min(256, n_parts - i0);
+    __syncthreads();
+    for (int i = tid; i < n; i += 128)
+      w_s[i] = m > -INFINITY ? expf(lses[(int64_t)(i0 + i) * rows + row] - total) : 0.0f;
+    __syncthreads();
+    const float *src = parts + ((int64_t)i0 * rows + row) * dh;
+#pragma unroll 4
+    for (int i = 0; i < n; ++i, src += rows * dh) {
+      const float w = w_s[i];
+#pragma unroll
+      for (int j = 0; j < kMergeWideDims; ++j)
+        if (tid + 128 * j < dh) acc[j] = fmaf(w, src[tid + 128 * j], acc[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMergeWideDims; ++j) {
+    const int c = tid + 128 * j;
+    if (c >= dh) continue;
+    if (out_bf16) out_bf16[row * dh + c] = float_to_bf16_bits(acc[j]);
+    if (out_f32) out_f32[row * dh + c] = acc[j];
+  }
+  if (tid == 0 && lse_out) lse_out[row] = total;
+}
+
 template <int DH, int NT, int W, int STAGES>
 static int launch_attend(const AttendParams &p, cudaStream_t s) {
   constexpr int WARP_BYTES = STAGES * 2 * kKeysPerStage * DH * 2 + 16;
@@ -350,6 +408,12 @@ LSA_API int lsa_lse_merge(const float *parts, const float *lses, int n_parts, in
   LSA_REQUIRE(parts && lses && (out_bf16 || out_f32), LSA_ERR_NULL);
   LSA_REQUIRE(n_parts >= 1 && rows >= 0 && dh >= 1, LSA_ERR_ARGUMENT);
   if (rows == 0) return LSA_OK;
+  if ((n_parts >= 16 || dh >= 256) && dh <= 128 * lsa::kMergeWideDims) {
+    lsa::lse_merge_wide_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, lses, n_parts, rows, dh,
+                                                                                  out_bf16, out_f32, lse_out);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
   const int warps = 8;
   lsa::lse_merge_kernel<<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream>>>(
       parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);

@@ -167,9 +167,15 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
     const int64_t bucket = bucket_s[pick];
     int n = 0;
     if (bucket >= 0)
-      for (int at0 = 0; at0 < p.cap; at0 += 32) {
-        const int32_t id = at0 + lane < p.cap ? p.members[bucket * p.cap + at0 + lane] : LSA_PAD;
-        n += __popc(__ballot_sync(0xffffffffu, id >= p.sink && id < window_start));
+      for (int at0 = 0; at0 < p.cap; at0 += 128) {  // four loads in flight
+        int32_t ids[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int at = at0 + 32 * j + lane;
+          ids[j] = at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) n += __popc(__ballot_sync(0xffffffffu, ids[j] >= p.sink && ids[j] < window_start));
       }
     if (lane == 0) count_s[pick] = n;
   }
@@ -194,13 +200,21 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
     const int64_t bucket = bucket_s[pick];
     int written = start_s[pick];
     if (bucket < 0) continue;
-    for (int at0 = 0; at0 < p.cap && written < row_k; at0 += 32) {
-      const int32_t id = at0 + lane < p.cap ? p.members[bucket * p.cap + at0 + lane] : LSA_PAD;
-      const bool counts = id >= p.sink && id < window_start;
-      const unsigned votes = __ballot_sync(0xffffffffu, counts);
-      const int at = written + __popc(votes & below);
-      if (counts && at < row_k) out[at] = stored_id(p, table, id);
-      written += __popc(votes);
+    for (int at0 = 0; at0 < p.cap && written < row_k; at0 += 128) {
+      int32_t ids[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int at = at0 + 32 * j + lane;
+        ids[j] = at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool counts = ids[j] >= p.sink && ids[j] < window_start;
+        const unsigned votes = __ballot_sync(0xffffffffu, counts);
+        const int at = written + __popc(votes & below);
+        if (counts && at < row_k) out[at] = stored_id(p, table, ids[j]);
+        written += __popc(votes);
+      }
     }
   }
   int total = min(start_s[row_p], row_k);

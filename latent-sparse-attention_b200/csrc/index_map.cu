@@ -167,10 +167,35 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The head sum alone (no map, no normalisation): out[r, kv*dh_used + c] = sum_g x[r, kv*group + g, off + c], added in
+// head order - what the identity map computes, without walking a contraction.
+template <typename TX>
+__global__ void __launch_bounds__(256)
+    head_sum_kernel(const TX *__restrict__ x, int64_t rows, int d_in, int group, int dh_off, int dh_used,
+                    int64_t x_row_stride, int64_t x_head_stride, float *__restrict__ out_f32,
+                    uint16_t *__restrict__ out_bf16) {
+  const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= rows * d_in) return;
+  const int64_t r = e / d_in;
+  const int k = (int)(e - r * d_in), kv = k / dh_used, c = k - kv * dh_used;
+  const TX *src = x + r * x_row_stride + (int64_t)kv * group * x_head_stride + dh_off + c;
+  float sum = 0.0f;
+  for (int g = 0; g < group; ++g) sum = __fadd_rn(sum, load_as_float<TX>(src, (int64_t)g * x_head_stride));
+  if (out_f32) out_f32[e] = sum;
+  if (out_bf16) out_bf16[e] = float_to_bf16_bits(sum);
+}
+
 template <typename TX, typename TW>
 static int launch_index_map(const void *x, int64_t rows, int heads, int group, int dh_off, int dh_used,
                             int64_t x_row_stride, int64_t x_head_stride, const void *W, int d_idx, int normalize,
                             float *out_f32, uint16_t *out_bf16, cudaStream_t s) {
+  if (!W && !normalize) {
+    const int64_t total = rows * d_idx;
+    head_sum_kernel<TX><<<(unsigned)((total + 255) / 256), 256, 0, s>>>(
+        (const TX *)x, rows, d_idx, group, dh_off, dh_used, x_row_stride, x_head_stride, out_f32, out_bf16);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
   if (rows <= 32 && d_idx <= 128) {
     if (d_idx <= 64)
       index_map_rows_kernel<TX, TW, 64><<<(unsigned)rows, kRowThreads, 0, s>>>(
