@@ -325,7 +325,8 @@ def run_ours(args, cfg: dict) -> dict:
         "clocks": clocks.summary(),
         "roofline": {"kernel": "sparse_attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                     "traffic": ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE * per_launch_bytes, "algorithmic_bytes_per_launch": per_launch_bytes,
+                     "traffic": ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE * per_launch_bytes if per_launch_bytes else None,
+                     "algorithmic_bytes_per_launch": per_launch_bytes,
                      "launches_per_step": attend_launches // args.steps,
                      "ms_per_launch": attend_ms / max(1, attend_launches)},
         "stages_ms_per_step": {name: total / args.steps for name, (total, _) in sorted(stage_ms.items())},

@@ -332,6 +332,32 @@ int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int6
                       uint16_t *out_bf16, float *out_f32, float *lse, void *workspace, size_t workspace_bytes,
                       void *stream);
 
+/* Bucket-major attention of a prefill chunk: expansion and gather attention in one call, the loop over buckets
+ * outside the loop over rows. The result is lsa_expand (LSA_EXPAND_NO_LOCAL) followed by lsa_sparse_attend with
+ * init_out / init_lse: every row attends over the members of its picked buckets that lie in
+ * [sink, position + 1 - window), best bucket first and cut at top_k, merged with the partial read it starts from
+ * (lsa_band_attend's window and sinks). A chunk's rows pick the same few thousand buckets a hundred times over:
+ * here a bucket's K/V rows are read once per 128 (row, pick) pairs instead of once per pair.
+ * Reference: expand_buckets + topk_attention (src/lsa/core/reference.py:268-289, src/lsa/core/attention.py:65-146).
+ *   picked   [R, top_p] int32 bucket ids, best first, -1 = none (lsa_flat_select's picked_out)
+ *   members  [m, bucket_cap] int32, ASCENDING within a bucket and -1 padded at the end (as lsa_bucket_table writes
+ *            them); bucket_cap <= 64
+ *   row_top_p / row_top_k [R] or NULL: a row's own budgets (the early budget)
+ *   init_out [R, Hq, dh] fp32 + init_lse [R, Hq], or both NULL
+ *   out_bf16 [R, Hq, dh]; lse_out [R, Hq] or NULL
+ *   workspace: lsa_bucket_attend_workspace_bytes(); it holds a bf16 partial output per (row, pick, head), which is
+ *            what trades the gather's repeated reads for one write and one read
+ * dh = 128 and Hq / Hkv <= 8 in this build; other shapes return LSA_ERR_UNSUPPORTED and the caller uses
+ * lsa_expand + lsa_sparse_attend. */
+size_t lsa_bucket_attend_workspace_bytes(int64_t R, int top_p, int Hq, int dh, int64_t m);
+int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
+                      const uint16_t *k, const uint16_t *v, int64_t slots, int Hkv, int64_t kv_row_stride,
+                      int64_t kv_head_stride, const int32_t *picked, int top_p, const int64_t *positions,
+                      const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
+                      const int32_t *row_top_k, int top_k, int sink, int window, const float *init_out,
+                      const float *init_lse, float scale, uint16_t *out_bf16, float *lse_out, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the
  * reference calls at src/lsa/sglang/models/qwen3_5/backend.py:724-738.

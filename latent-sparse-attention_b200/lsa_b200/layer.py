@@ -11,7 +11,7 @@ from dataclasses import dataclass
 
 import torch
 
-from lsa_b200 import ops, probe
+from lsa_b200 import _lib, ops, probe
 from lsa_b200.budget import EarlyBudget
 from lsa_b200.core import Buckets, RotaryLayout, check_sizes
 
@@ -145,10 +145,10 @@ class FlatLayer:
                                                                  outs=outs)
         return FlatIndex(keys, Buckets(centroids, members, sizes, per_block, d.cluster_block_size))
 
-    def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
-               reuse_buffers: bool = False, local: bool = True):
-        """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`; with
-        `local=False` the lists hold the expansion alone (a band kernel reads the window and the sinks)."""
+    def pick(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
+             reuse_buffers: bool = False):
+        """The top-p buckets of every row, best first: (picked [R, top_p] int32, positions int64, and the rows' own
+        budgets under an early budget, else None)."""
         d, b, dev = self.design, index.buckets, index_queries.device
         R = index_queries.shape[0]
         positions = positions.to(torch.int64)
@@ -159,17 +159,28 @@ class FlatLayer:
             early = positions < d.early_budget.position
             row_p = torch.where(early, d.early_budget.top_p, d.top_p).to(torch.int32)
             row_k = torch.where(early, d.early_budget.top_k, d.top_k).to(torch.int32)
-        keys = picked = outs = None
+        keys = picked = None
         if reuse_buffers:
             keys = self._buffer("keys", (R, d.top_p), torch.int64, dev)
             picked = self._buffer("picked", (R, d.top_p), torch.int32, dev)
+        with probe.region("select"):
+            _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
+                                        picked=picked)
+        return picked, positions, row_p, row_k
+
+    def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
+               reuse_buffers: bool = False, local: bool = True):
+        """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`; with
+        `local=False` the lists hold the expansion alone (a band kernel reads the window and the sinks)."""
+        d, b, dev = self.design, index.buckets, index_queries.device
+        R = index_queries.shape[0]
+        picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers)
+        outs = None
+        if reuse_buffers:
             status = self._buffer("expand status", (1,), torch.int32, dev)
             status.zero_()
             outs = (self._buffer("lists", (R, d.list_width), torch.int32, dev),
                     self._buffer("lengths", (R,), torch.int32, dev), status)
-        with probe.region("select"):
-            _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
-                                        picked=picked)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, positions, b.bucket_members, d.top_k, d.sink_size, d.window_size,
                                            row_p, row_k, outs=outs, local=local)
@@ -192,11 +203,14 @@ class FlatLayer:
     # ---- the layer
 
     def prefill(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, chunk: int = 8192,
-                return_index: bool = False, out: torch.Tensor | None = None, band: bool = True):
+                return_index: bool = False, out: torch.Tensor | None = None, band: bool = True,
+                bucket_major: bool = True):
         """Causal prefill from position 0: q [T,Hq,dh], k/v [T,Hkv,dh] bf16 -> out [T,Hq,dh] bf16.
 
         Every intermediate lives in buffers the layer keeps, so after the first call a step allocates nothing but
         its output (pass `out` to avoid that too). With `return_index` the index is built in fresh tensors instead.
+        `band` reads the window and the sinks as dense tiles; `bucket_major` reads the selected keys bucket by bucket
+        where the shapes allow (both off: every row gathers its whole list).
         """
         T, dev = q.shape[0], q.device
         index = self.build_index(k, reuse_buffers=not return_index)
@@ -213,9 +227,22 @@ class FlatLayer:
             # gather starts from its partial result and reads the selected keys alone.
             banded = band and self.design.sink_size <= 64 and k.shape[0] >= stop
             init = self.band(rows, k, v, start) if banded else None
+            lse = self._buffer("lse", (stop - start, self.heads), torch.float32, dev)
+            # (without the band the window and the sinks are in the lists, which only the gather path reads)
+            if banded and bucket_major and ops.bucket_attend_supported(rows, k, self.design.bucket_cap):
+                # The rows of a chunk pick the same buckets over and over: read each bucket's keys once per 64
+                # (row, pick) pairs instead of once per pair.
+                picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True)
+                need = _lib.query("lsa_bucket_attend_workspace_bytes", stop - start, self.design.top_p, self.heads,
+                                  self.head_dim, index.buckets.bucket_members.shape[0])
+                with probe.region("attend"):
+                    ops.bucket_attend(rows, k, v, picked, positions, index.buckets.bucket_members, self.design.top_k,
+                                      self.design.sink_size, self.design.window_size, self.scale, init=init,
+                                      row_top_p=row_p, row_top_k=row_k, out=out[start:stop], lse=lse,
+                                      workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
+                continue
             lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
-            self.attend(rows, k, v, lists, lengths, out=out[start:stop],
-                        lse=self._buffer("lse", (stop - start, self.heads), torch.float32, dev), init=init)
+            self.attend(rows, k, v, lists, lengths, out=out[start:stop], lse=lse, init=init)
         return (out, index) if return_index else out
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,

@@ -397,6 +397,42 @@ def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, leng
     return out, lse
 
 
+def bucket_attend_supported(q: torch.Tensor, k: torch.Tensor, bucket_cap: int) -> bool:
+    """Whether `bucket_attend` takes these shapes (else: `expand` + `sparse_attend`)."""
+    return q.shape[2] == 128 and bucket_cap <= 64 and q.shape[1] % k.shape[1] == 0 and q.shape[1] // k.shape[1] <= 8
+
+
+def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: torch.Tensor, positions: torch.Tensor,
+                  members: torch.Tensor, top_k: int, sink: int, window: int, scale: float, init: tuple | None = None,
+                  row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+                  workspace: torch.Tensor | None = None):
+    """Expansion and attention of a prefill chunk bucket by bucket: q [R, Hq, dh] bf16 over the members of each row's
+    picked buckets (picked [R, top_p], members ascending in a bucket) inside [sink, position + 1 - window), cut at
+    top_k, merged with the partial read `init` = (out fp32, lse). Returns (out [R, Hq, dh] bf16, lse [R, Hq])."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise ValueError("q, k and v must be bfloat16")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
+        raise ValueError("head dims must be contiguous and k, v must share their layout")
+    picked, members = _contig(picked), _contig(members)
+    R, Hq, dh = q.shape
+    slots, Hkv, _ = k.shape
+    top_p = picked.shape[1]
+    out = torch.empty(R, Hq, dh, device=q.device, dtype=torch.bfloat16) if out is None else out
+    if out.shape != (R, Hq, dh) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous bfloat16 [{R}, {Hq}, {dh}]")
+    lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32) if lse is None else lse
+    need = query("lsa_bucket_attend_workspace_bytes", R, top_p, Hq, dh, members.shape[0])
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
+    call("lsa_bucket_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, Hkv, k.stride(0),
+         k.stride(1), ptr(picked), top_p, ptr(_contig(positions.to(torch.int64))), ptr(members), members.shape[0],
+         members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(init[0]) if init else None,
+         ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), ptr(workspace),
+         workspace.numel() * workspace.element_size(), stream(), launches=5)
+    return out, lse
+
+
 def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_position: int, window: int, sink: int,
                 scale: float, out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
     """The window and sinks of consecutive query rows as dense banded attention: q [R, Hq, dh] at positions

@@ -1,0 +1,79 @@
+"""Bucket-major attention of a prefill chunk (`lsa_bucket_attend`): the same read as expansion + gather attention
+(`expand_buckets` then `topk_attention`, src/lsa/core/reference.py:268-289, src/lsa/core/attention.py:65-146), with
+the loop over buckets outside the loop over rows. Held to the oracle's read and to the gather path."""
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import cuda, layer_inputs, mixture, unit_rows
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(oracle, seed=5):
+    T, Hq, Hkv, dh, d = 3072, 10, 2, 128, 32
+    q, k, v = layer_inputs(T, Hq, Hkv, dh, 16, seed)
+    raw = mixture(T, d, 24, 0.3, seed + 1)
+    buckets = oracle.build_buckets(unit_rows(raw), 4, 16, 32, 256)
+    first, rows = 1500, 600
+    positions = np.arange(first, first + rows)
+    rng = np.random.default_rng(seed + 2)
+    index_q = unit_rows(raw[positions] + 0.3 * rng.standard_normal((rows, d)).astype(np.float32))
+    return q, k, v, buckets, positions, index_q, first
+
+
+def _close(got, want, what):
+    gap = np.abs(got - want)
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (what, gap.max(), gap.mean())
+
+
+@pytest.mark.parametrize("top_p,top_k", [(12, 400), (12, 150), (3, 400)])
+def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p, top_k):
+    from lsa_b200 import ops
+
+    q, k, v, buckets, positions, index_q, first = _case(oracle)
+    sink, window, scale = 4, 128, 128 ** -0.5
+    want_lists, want_len, picked, _ = oracle.read(index_q, positions, buckets, top_p, top_k, sink, window,
+                                                  return_picked=True)
+    Q, K, V = (cuda(a, torch.bfloat16) for a in (q, k, v))
+    rows = Q[first:first + len(positions)]
+    pos, mem, pk = cuda(positions), cuda(buckets.bucket_members), cuda(picked)
+    band = ops.band_attend(rows, K, V, first, window, sink, scale)
+    out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, init=band)
+    want, want_lse = oracle.sparse_attend(q[positions], k, v, want_lists, positions, 0, 0, scale, lengths=want_len)
+    _close(out.float().cpu().numpy(), want, "oracle")
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
+    lists, lens, _ = ops.expand(pk, pos, mem, top_k, sink, window, local=False)
+    gathered, _ = ops.sparse_attend(rows, K, V, lists, lens, scale, init=band)
+    _close(out.float().cpu().numpy(), gathered.float().cpu().numpy(), "gather path")
+
+
+def test_bucket_major_read_alone_under_row_budgets_and_missing_picks(oracle):
+    from lsa_b200 import ops
+
+    q, k, v, buckets, positions, index_q, first = _case(oracle, seed=11)
+    sink, window, scale, top_p, top_k = 4, 128, 128 ** -0.5, 12, 400
+    _, _, picked, _ = oracle.read(index_q, positions, buckets, top_p, top_k, sink, window, return_picked=True)
+    picked = picked.copy()
+    picked[::7, 2] = -1       # a hole in a row's picks
+    picked[5] = -1            # a row that picked nothing
+    early = positions < first + 200
+    row_p = np.where(early, 5, top_p).astype(np.int32)
+    row_k = np.where(early, 90, top_k).astype(np.int32)
+    Q, K, V = (cuda(a, torch.bfloat16) for a in (q, k, v))
+    rows = Q[first:first + len(positions)]
+    pos, mem, pk = cuda(positions), cuda(buckets.bucket_members), cuda(picked)
+    # no band: the read is over the expansion alone, which the one-warp expansion lists for the oracle
+    lists, lens, _ = ops.expand(pk, pos, mem, top_k, sink, window, cuda(row_p), cuda(row_k), local=False)
+    want, want_lse = oracle.sparse_attend(q[positions], k, v, lists.cpu().numpy(), positions, 0, 0, scale,
+                                          lengths=lens.cpu().numpy())
+    out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, row_top_p=cuda(row_p),
+                                 row_top_k=cuda(row_k))
+    _close(out.float().cpu().numpy(), want, "oracle")
+    got_lse = lse.cpu().numpy()
+    assert int(lens[5]) == 0 and not out[5].any() and np.isneginf(got_lse[5]).all()
+    held = lens.cpu().numpy() > 0
+    assert np.abs(got_lse[held] - want_lse[held]).max() <= 2e-2
+    # cut lists: some row's running count must have stopped inside a bucket for the budget to have been exercised
+    assert (lens.cpu().numpy()[early] == 90).any()
