@@ -44,6 +44,9 @@ C2 = dict(workload="C2", tokens=131072, heads=40, kv_heads=8, head_dim=128, inde
 # last, 37.2 GB on average, against 66.4 GB of algorithmic bytes; summarised in profiles/). The traffic reported is
 # this ratio times the launch's algorithmic bytes.
 ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.561
+# DRAM bytes of one bucket-major attend call (the six kernels of a chunk), from an ncu capture summarised in
+# profiles/; None until a capture of this workload exists.
+BUCKET_DRAM_TRAFFIC_PER_CALL = None
 
 
 def small(cfg: dict, tokens: int) -> dict:
@@ -203,6 +206,15 @@ def attend_algorithmic_bytes(cfg: dict, gathered_total: int) -> float:
     return gathered_total * row + T * Hq * dh * (2 + 4 + 2) + T * Hq * 4
 
 
+def bucket_attend_algorithmic_bytes(cfg: dict, pairs: int) -> float:
+    """Algorithmic bytes of a step's bucket-major attention (starts, invert, attend, merge): per (row, pick) pair and
+    query head one query vector in, one bf16 partial output and one log-sum-exp out of the attend pass and back
+    into the merge; per row the band's fp32 partial in and the bf16 output out. A bucket's K/V rows are read once
+    per 128 pairs and do not show at this scale."""
+    T, Hq, dh = cfg["tokens"], cfg["heads"], cfg["head_dim"]
+    return pairs * Hq * (3 * dh * 2 + 2 * 4) + T * Hq * ((dh + 1) * 4 + dh * 2)
+
+
 def band_algorithmic_bytes(cfg: dict) -> float:
     """Algorithmic bytes of a step's band attention: the band's K/V once per 128-query tile, the sinks, Q in and
     the fp32 partial result out."""
@@ -276,10 +288,11 @@ def run_ours(args, cfg: dict) -> dict:
         # One more untimed pass counts the gathered keys the roofline figure needs, and keeps what the CPU baseline
         # reads.
         _, index = base.prefill(q, k, v, chunk=cfg["chunk"], return_index=True)
-        gathered = 0
+        gathered = pairs = 0
         index_q = base.index_queries(q)
         for start in range(0, cfg["tokens"], cfg["chunk"]):
             pos = torch.arange(start, min(cfg["tokens"], start + cfg["chunk"]), device="cuda")
+            pairs += int((base.pick(index_q[start:start + cfg["chunk"]], pos, index)[0] >= 0).sum())
             _, lengths = base.select(index_q[start:start + cfg["chunk"]], pos, index)
             window_start = (pos + 1 - cfg["window_size"]).clamp_min(0)
             fixed = (pos + 1 - window_start) + torch.minimum(window_start, torch.full_like(pos, cfg["sink_size"]))
@@ -304,10 +317,14 @@ def run_ours(args, cfg: dict) -> dict:
         peak, peak_kind = json.load(open(peaks_path))["hbm_gbs"], "measured"
     else:
         peak, peak_kind = 6650.0, "fallback"
-    per_launch_bytes = achieved = None
+    per_launch_bytes = achieved = useful_tflops = None
+    bucket_major = world == 1  # the single-GPU prefill reads the selected keys bucket by bucket
     if gathered is not None and attend_launches:
-        per_launch_bytes = attend_algorithmic_bytes(cfg, gathered) / max(1, attend_launches // args.steps)
+        stage_bytes = bucket_attend_algorithmic_bytes(cfg, pairs) if bucket_major else \
+            attend_algorithmic_bytes(cfg, gathered)
+        per_launch_bytes = stage_bytes / max(1, attend_launches // args.steps)
         achieved = per_launch_bytes / (attend_ms / attend_launches * 1e-3) / 1e9
+        useful_tflops = 4.0 * gathered * cfg["heads"] * cfg["head_dim"] / (attend_ms / args.steps * 1e-3) / 1e12
     result = {
         "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
@@ -323,10 +340,14 @@ def run_ours(args, cfg: dict) -> dict:
                 "d2h_bytes_per_step": out_h.numel() * world * 2, "ms_per_step": e2e_ms},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
-        "roofline": {"kernel": "sparse_attend_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+        "roofline": {"kernel": "bucket-major attend (bucket_starts, scan, scatter, segments, bucket_attend, "
+                               "bucket_merge: one call a chunk)" if bucket_major else "sparse_attend_kernel",
+                     "bound": "hbm", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                     "traffic": ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE * per_launch_bytes if per_launch_bytes else None,
+                     "traffic": (BUCKET_DRAM_TRAFFIC_PER_CALL if bucket_major else
+                                 ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE * per_launch_bytes) if per_launch_bytes else None,
                      "algorithmic_bytes_per_launch": per_launch_bytes,
+                     "useful_tflops": useful_tflops,
                      "launches_per_step": attend_launches // args.steps,
                      "ms_per_launch": attend_ms / max(1, attend_launches)},
         "stages_ms_per_step": {name: total / args.steps for name, (total, _) in sorted(stage_ms.items())},

@@ -14,36 +14,11 @@
 //
 // A pair's keys are its bucket's members inside [sink, window_start(row)), cut where the row's running count
 // reaches its top-k: with members ascending (as lsa_bucket_table writes them) that is an index range of the bucket.
+#include "bucket_attend.cuh"
 #include "common.cuh"
 #include "mma.cuh"
 
 namespace lsa {
-
-constexpr int kBktKeys = 64;     // members a bucket may hold here (the tile of keys a CTA stages)
-constexpr int kBktSegment = 128;  // (row, pick) pairs a CTA runs through its bucket
-constexpr int kBktTile = 16;     // query rows a warp multiplies at once
-
-struct BucketParams {
-  const uint16_t *q, *k, *v;
-  const int32_t *picked, *members, *row_top_p, *row_top_k;
-  const int64_t *positions;
-  const float *init_out, *init_lse;
-  uint16_t *out_bf16;
-  float *lse_out;
-  // workspace
-  int32_t *starts;         // [R, top_p] selected ids of the row before this pick, -1 = the pick adds nothing
-  int32_t *counts;         // [m + 1] pairs of each bucket
-  int32_t *offsets;        // [m + 1] exclusive scan of counts
-  int32_t *seg_offsets;    // [m + 1] exclusive scan of ceil(counts / segment)
-  int32_t *cursors;        // [m]
-  int32_t *order;          // [R * top_p] pair ids grouped by bucket
-  int4 *segments;          // [segment bound] bucket, first pair in `order`, pairs: what a CTA of the attend pass runs
-  uint16_t *part_out;      // [R * top_p, Hq, dh] bf16
-  float *part_lse;         // [R * top_p, Hq]
-  int64_t R, m, slots, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride;
-  int top_p, cap, top_k, sink, window, Hq, Hkv, group;
-  float scale_log2;
-};
 
 // ---------------------------------------------------------------------------------------------- starts
 
@@ -284,31 +259,43 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
         mma_bf16(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
     }
-    // softmax over the pair's key range
+    // softmax over the pair's key range. Most key tiles lie inside every row's range and need no masks: the tile
+    // is inside when it starts at or after the warp's greatest range start and ends by its least range end.
+    const int lo_max = __reduce_max_sync(0xffffffffu, max(lo_key[0], lo_key[1]));
+    const int hi_min = __reduce_min_sync(0xffffffffu, min(hi_key[0], hi_key[1]));
     float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.0f, 0.0f};
 #pragma unroll
-    for (int nt = 0; nt < kBktKeys / 8; ++nt)
+    for (int nt = 0; nt < kBktKeys / 8; ++nt) {
+      if (nt * 8 >= key_steps * 16) continue;
+      if (nt * 8 < lo_max || nt * 8 + 8 > hi_min) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int key = nt * 8 + 2 * t + (c & 1), j = c >> 1;
-        const bool ok = key >= lo_key[j] && key < hi_key[j];
-        s[nt][c] = ok ? s[nt][c] * p.scale_log2 : -INFINITY;
-        m_row[j] = fmaxf(m_row[j], s[nt][c]);
+        for (int c = 0; c < 4; ++c) {
+          const int key = nt * 8 + 2 * t + (c & 1), j = c >> 1;
+          if (key < lo_key[j] || key >= hi_key[j]) s[nt][c] = -INFINITY;
+        }
       }
+      m_row[0] = fmaxf(m_row[0], fmaxf(s[nt][0], s[nt][1]));
+      m_row[1] = fmaxf(m_row[1], fmaxf(s[nt][2], s[nt][3]));
+    }
+    float m_off[2];  // the row maximum in the log2 domain, what the exponent subtracts (0 for a row with no key)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       m_row[j] = fmaxf(m_row[j], __shfl_xor_sync(0xffffffffu, m_row[j], 1));
       m_row[j] = fmaxf(m_row[j], __shfl_xor_sync(0xffffffffu, m_row[j], 2));
+      m_row[j] *= p.scale_log2;  // the scale is positive: the maximum of the raw products is the maximum
+      m_off[j] = m_row[j] == -INFINITY ? 0.0f : m_row[j];
     }
     uint32_t pa[kBktKeys / 16][4];
 #pragma unroll
     for (int nt = 0; nt < kBktKeys / 8; ++nt) {
-      float e[4];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int j = c >> 1;
-        e[c] = m_row[j] == -INFINITY ? 0.0f : exp2f(s[nt][c] - m_row[j]);
-        l_row[j] += e[c];
+      float e[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      if (nt * 8 < key_steps * 16) {
+        e[0] = exp2f(fmaf(s[nt][0], p.scale_log2, -m_off[0]));
+        e[1] = exp2f(fmaf(s[nt][1], p.scale_log2, -m_off[0]));
+        e[2] = exp2f(fmaf(s[nt][2], p.scale_log2, -m_off[1]));
+        e[3] = exp2f(fmaf(s[nt][3], p.scale_log2, -m_off[1]));
+        l_row[0] += e[0] + e[1];
+        l_row[1] += e[2] + e[3];
       }
       // the accumulator of key tiles 2k, 2k + 1 is the A fragment of 16-key step k
       pa[nt >> 1][(nt & 1) * 2] = pack_bf16x2(e[0], e[1]);
@@ -477,13 +464,13 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
                               const int64_t *positions, const int32_t *members, int64_t m, int bucket_cap,
                               const int32_t *row_top_p, const int32_t *row_top_k, int top_k, int sink, int window,
                               const float *init_out, const float *init_lse, float scale, uint16_t *out_bf16,
-                              float *lse_out, void *workspace, size_t workspace_bytes, void *stream) {
+                              float *lse_out, int flags, void *workspace, size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && k && v && picked && positions && out_bf16 && workspace, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
   LSA_REQUIRE((init_out == nullptr) == (init_lse == nullptr), LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && slots >= 0 && slots <= INT32_MAX && top_p >= 1 &&
                   m >= 0 && m < INT32_MAX && bucket_cap >= 1 && top_k >= 1 && sink >= 0 && window >= 1 &&
-                  R * top_p < INT32_MAX,
+                  R * top_p < INT32_MAX && scale > 0.0f,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(dh == 128 && bucket_cap <= lsa::kBktKeys && Hq / Hkv <= 8, LSA_ERR_UNSUPPORTED);
   LSA_REQUIRE(kv_row_stride % 8 == 0 && kv_head_stride % 8 == 0 && ((uintptr_t)k % 16) == 0 &&
@@ -528,13 +515,18 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
     lsa::bucket_segments_kernel<<<(unsigned)((m + 255) / 256), 256, 0, s>>>(p);
     LSA_LAUNCH_CHECK();
     const int64_t bound = lsa::segment_bound(R, top_p, m);
-    const size_t smem = 2 * (size_t)lsa::kBktKeys * dh * 2 + 2 * (size_t)p.group * lsa::kBktTile * dh * 2;
-    if (cudaFuncSetAttribute(lsa::bucket_attend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-      return LSA_ERR_LAUNCH;
-    const dim3 grid((unsigned)bound, (unsigned)Hkv);
-    lsa::bucket_attend_kernel<128><<<grid, p.group * 32, smem, s>>>(p);
-    LSA_LAUNCH_CHECK();
+    if (flags & LSA_BUCKET_WARP_MMA) {
+      const size_t smem = 2 * (size_t)lsa::kBktKeys * dh * 2 + 2 * (size_t)p.group * lsa::kBktTile * dh * 2;
+      if (cudaFuncSetAttribute(lsa::bucket_attend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem) != cudaSuccess)
+        return LSA_ERR_LAUNCH;
+      const dim3 grid((unsigned)bound, (unsigned)Hkv);
+      lsa::bucket_attend_kernel<128><<<grid, p.group * 32, smem, s>>>(p);
+      LSA_LAUNCH_CHECK();
+    } else {
+      const int rc = lsa::launch_bucket_attend_tc(p, bound, s);
+      if (rc != LSA_OK) return rc;
+    }
   }
   lsa::bucket_merge_kernel<128><<<(unsigned)((R * Hq + 7) / 8), 256, 0, s>>>(p);
   LSA_LAUNCH_CHECK();

@@ -13,13 +13,13 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "umma.cuh"
 
 namespace lsa {
 
 constexpr int kTileM = 128;
 constexpr int kTileK = 64;  // bf16 elements: one 128-byte swizzle atom a row
 constexpr int kGemmThreads = 192;
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 enum GemmEpilogue { kEpilogueRownorm = 0, kEpilogueGelu = 1, kEpiloguePlain = 2 };
 
@@ -31,74 +31,6 @@ struct GemmParams {
   int k_blocks;
   int normalize;
 };
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Wait for the phase with the given parity; false when the limit runs out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-
-// Shared-memory matrix descriptor of a K-major bf16 tile written by TMA with the 128-byte swizzle: rows of 128
-// bytes, groups of 8 rows 1,024 bytes apart; bits 46-47 carry the descriptor version of this architecture, bits
-// 61-63 the swizzle mode.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t desc = (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  desc |= (uint64_t)1 << 16;            // leading byte offset, unused by swizzled K-major layouts
-  desc |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset: 8 rows x 128 bytes
-  desc |= (uint64_t)1 << 46;            // version
-  desc |= (uint64_t)2 << 61;            // 128-byte swizzle
-  return desc;
-}
-
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-}
 
 template <int N_TILE, int STAGES, int EPILOGUE>
 __global__ void __launch_bounds__(kGemmThreads)

@@ -73,6 +73,10 @@ class FlatLayer:
         self.dh_used = free
         self.scale = head_dim ** -0.5 if scale is None else scale
         self._buffers: dict = {}
+        # The bucket-major attend pass has two forms. With the pairs of a segment as the 128 rows of tcgen05 products
+        # (S and O in tensor memory) a CTA walks its heads through a chain of dependent hand-overs and measures
+        # slower (7.8 ms a chunk of config 2) than the warp-level tiles of 16 rows (3.9 ms), so those are the default.
+        self.bucket_tensor_memory = False
         # bf16 maps run on the tensor cores (the head sum folded into the product); fp32 maps keep the exact form
         self.tensor_cores = tensor_cores and query_map.dtype == torch.bfloat16 and key_map.dtype == torch.bfloat16 \
             and query_map.shape[1] in (32, 64, 128)
@@ -239,6 +243,7 @@ class FlatLayer:
                     ops.bucket_attend(rows, k, v, picked, positions, index.buckets.bucket_members, self.design.top_k,
                                       self.design.sink_size, self.design.window_size, self.scale, init=init,
                                       row_top_p=row_p, row_top_k=row_k, out=out[start:stop], lse=lse,
+                                      warp_mma=not self.bucket_tensor_memory,
                                       workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
                 continue
             lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)

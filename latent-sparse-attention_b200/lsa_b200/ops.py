@@ -406,10 +406,11 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
                   members: torch.Tensor, top_k: int, sink: int, window: int, scale: float, init: tuple | None = None,
                   row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
                   out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-                  workspace: torch.Tensor | None = None):
+                  workspace: torch.Tensor | None = None, warp_mma: bool = False):
     """Expansion and attention of a prefill chunk bucket by bucket: q [R, Hq, dh] bf16 over the members of each row's
     picked buckets (picked [R, top_p], members ascending in a bucket) inside [sink, position + 1 - window), cut at
-    top_k, merged with the partial read `init` = (out fp32, lse). Returns (out [R, Hq, dh] bf16, lse [R, Hq])."""
+    top_k, merged with the partial read `init` = (out fp32, lse). Returns (out [R, Hq, dh] bf16, lse [R, Hq]).
+    The products run on tcgen05 with tensor-memory accumulators; `warp_mma` takes the warp-level MMA kernel."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("q, k and v must be bfloat16")
     if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
@@ -428,8 +429,8 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
     call("lsa_bucket_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, Hkv, k.stride(0),
          k.stride(1), ptr(picked), top_p, ptr(_contig(positions.to(torch.int64))), ptr(members), members.shape[0],
          members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(init[0]) if init else None,
-         ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), ptr(workspace),
-         workspace.numel() * workspace.element_size(), stream(), launches=5)
+         ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), 1 if warp_mma else 0, ptr(workspace),
+         workspace.numel() * workspace.element_size(), stream(), launches=6)
     return out, lse
 
 

@@ -28,8 +28,9 @@ def _close(got, want, what):
     assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (what, gap.max(), gap.mean())
 
 
+@pytest.mark.parametrize("warp_mma", [False, True])
 @pytest.mark.parametrize("top_p,top_k", [(12, 400), (12, 150), (3, 400)])
-def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p, top_k):
+def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p, top_k, warp_mma):
     from lsa_b200 import ops
 
     q, k, v, buckets, positions, index_q, first = _case(oracle)
@@ -40,7 +41,7 @@ def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p,
     rows = Q[first:first + len(positions)]
     pos, mem, pk = cuda(positions), cuda(buckets.bucket_members), cuda(picked)
     band = ops.band_attend(rows, K, V, first, window, sink, scale)
-    out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, init=band)
+    out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, init=band, warp_mma=warp_mma)
     want, want_lse = oracle.sparse_attend(q[positions], k, v, want_lists, positions, 0, 0, scale, lengths=want_len)
     _close(out.float().cpu().numpy(), want, "oracle")
     assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
@@ -49,7 +50,8 @@ def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p,
     _close(out.float().cpu().numpy(), gathered.float().cpu().numpy(), "gather path")
 
 
-def test_bucket_major_read_alone_under_row_budgets_and_missing_picks(oracle):
+@pytest.mark.parametrize("warp_mma", [False, True])
+def test_bucket_major_read_alone_under_row_budgets_and_missing_picks(oracle, warp_mma):
     from lsa_b200 import ops
 
     q, k, v, buckets, positions, index_q, first = _case(oracle, seed=11)
@@ -69,7 +71,7 @@ def test_bucket_major_read_alone_under_row_budgets_and_missing_picks(oracle):
     want, want_lse = oracle.sparse_attend(q[positions], k, v, lists.cpu().numpy(), positions, 0, 0, scale,
                                           lengths=lens.cpu().numpy())
     out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, row_top_p=cuda(row_p),
-                                 row_top_k=cuda(row_k))
+                                 row_top_k=cuda(row_k), warp_mma=warp_mma)
     _close(out.float().cpu().numpy(), want, "oracle")
     got_lse = lse.cpu().numpy()
     assert int(lens[5]) == 0 and not out[5].any() and np.isneginf(got_lse[5]).all()
