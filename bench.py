@@ -44,9 +44,10 @@ C2 = dict(workload="C2", tokens=131072, heads=40, kv_heads=8, head_dim=128, inde
 # last, 37.2 GB on average, against 66.4 GB of algorithmic bytes; summarised in profiles/). The traffic reported is
 # this ratio times the launch's algorithmic bytes.
 ATTEND_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 0.561
-# DRAM bytes of one bucket-major attend call (the six kernels of a chunk), from an ncu capture summarised in
-# profiles/; None until a capture of this workload exists.
-BUCKET_DRAM_TRAFFIC_PER_CALL = None
+# DRAM bytes of one bucket-major attend call (the six kernels of a chunk): dram__bytes_read.sum +
+# dram__bytes_write.sum over the 96 launches of a full-size step in a one-pass ncu capture, 189.7 GB, a sixteenth of
+# it a call (the attend pass writes 5.4 GB of partials, the merge reads them back; summarised in profiles/).
+BUCKET_DRAM_TRAFFIC_PER_CALL = 11.85e9
 
 
 def small(cfg: dict, tokens: int) -> dict:
