@@ -285,26 +285,31 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
       m_row[j] *= p.scale_log2;  // the scale is positive: the maximum of the raw products is the maximum
       m_off[j] = m_row[j] == -INFINITY ? 0.0f : m_row[j];
     }
-    uint32_t pa[kBktKeys / 16][4];
 #pragma unroll
     for (int nt = 0; nt < kBktKeys / 8; ++nt) {
-      float e[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      if (nt * 8 < key_steps * 16) {
-        e[0] = exp2f(fmaf(s[nt][0], p.scale_log2, -m_off[0]));
-        e[1] = exp2f(fmaf(s[nt][1], p.scale_log2, -m_off[0]));
-        e[2] = exp2f(fmaf(s[nt][2], p.scale_log2, -m_off[1]));
-        e[3] = exp2f(fmaf(s[nt][3], p.scale_log2, -m_off[1]));
-        l_row[0] += e[0] + e[1];
-        l_row[1] += e[2] + e[3];
-      }
-      // the accumulator of key tiles 2k, 2k + 1 is the A fragment of 16-key step k
-      pa[nt >> 1][(nt & 1) * 2] = pack_bf16x2(e[0], e[1]);
-      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(e[2], e[3]);
+      if (nt * 8 >= key_steps * 16) continue;
+      s[nt][0] = exp2f(fmaf(s[nt][0], p.scale_log2, -m_off[0]));
+      s[nt][1] = exp2f(fmaf(s[nt][1], p.scale_log2, -m_off[0]));
+      s[nt][2] = exp2f(fmaf(s[nt][2], p.scale_log2, -m_off[1]));
+      s[nt][3] = exp2f(fmaf(s[nt][3], p.scale_log2, -m_off[1]));
+      l_row[0] += s[nt][0] + s[nt][1];
+      l_row[1] += s[nt][2] + s[nt][3];
     }
+    float inv[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       l_row[j] += __shfl_xor_sync(0xffffffffu, l_row[j], 1);
       l_row[j] += __shfl_xor_sync(0xffffffffu, l_row[j], 2);
+      inv[j] = l_row[j] > 0.0f ? 1.0f / l_row[j] : 0.0f;
+    }
+    // P is normalised before it is rounded to bf16 (a row's sum is known by now), so O needs no scaling afterwards.
+    // The accumulator of key tiles 2k, 2k + 1 is the A fragment of 16-key step k.
+    uint32_t pa[kBktKeys / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < kBktKeys / 8; ++nt) {
+      const bool live = nt * 8 < key_steps * 16;
+      pa[nt >> 1][(nt & 1) * 2] = live ? pack_bf16x2(s[nt][0] * inv[0], s[nt][1] * inv[0]) : 0u;
+      pa[nt >> 1][(nt & 1) * 2 + 1] = live ? pack_bf16x2(s[nt][2] * inv[1], s[nt][3] * inv[1]) : 0u;
     }
     // O [16 rows x DH] = P V
     float o[DH / 8][4];
@@ -326,7 +331,6 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
     for (int j = 0; j < 2; ++j) {
       if (pair_of[j] < 0) continue;
       const int64_t slot = (int64_t)pair_of[j] * p.Hq + head;
-      const float inv = l_row[j] > 0.0f ? 1.0f / l_row[j] : 0.0f;
       if (t == 0)
         p.part_lse[slot] = l_row[j] > 0.0f ? (m_row[j] + log2f(l_row[j])) * 0.6931471805599453f : -INFINITY;
       // staged in the tile's query buffer (the products are done with it), so the rows leave in whole 16-byte pieces
@@ -335,7 +339,7 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
       for (int nt = 0; nt < DH / 8; ++nt) {
         const uint32_t at = row * ROW_BYTES + ((nt ^ (row & 7)) << 4) + 4 * t;
         asm volatile("st.shared.b32 [%0], %1;" ::"r"(q_tile + at),
-                     "r"(pack_bf16x2(o[nt][2 * j] * inv, o[nt][2 * j + 1] * inv)));
+                     "r"(pack_bf16x2(o[nt][2 * j], o[nt][2 * j + 1])));
       }
     }
     __syncwarp();
