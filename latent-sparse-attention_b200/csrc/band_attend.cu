@@ -121,10 +121,7 @@ __global__ void band_attend_kernel(BandParams p) {
 #pragma unroll
       for (int n = 0; n < kBandKeys / 8; ++n) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          s[n][j] *= p.scale_log2;
-          mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
-        }
+        for (int j = 0; j < 4; ++j) mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
       }
     } else {
 #pragma unroll
@@ -136,7 +133,7 @@ __global__ void band_attend_kernel(BandParams p) {
           const int64_t start = max((int64_t)0, pos + 1 - p.window);
           const bool ok = pos < p.first_position + p.R && key < p.n_keys &&
                           ((tile >= 0 && key >= start && key <= pos) || key < min((int64_t)p.sink, start));
-          s[n][j] = ok ? s[n][j] * p.scale_log2 : -INFINITY;
+          s[n][j] = ok ? s[n][j] : -INFINITY;
           mx[j >> 1] = fmaxf(mx[j >> 1], s[n][j]);
         }
       }
@@ -146,7 +143,8 @@ __global__ void band_attend_kernel(BandParams p) {
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m_run[r], mx[r]);
+      // the products are raw: the scale is positive, so it is applied to the maximum and inside the exponent
+      const float m_new = fmaxf(m_run[r], mx[r] * p.scale_log2);
       const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
       alpha[r] = exp2f(m_run[r] - m_safe);
       m_run[r] = m_new;
@@ -157,16 +155,19 @@ __global__ void band_attend_kernel(BandParams p) {
     for (int n = 0; n < kBandKeys / 8; ++n) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        s[n][j] = exp2f(s[n][j] - mx[j >> 1]);
+        s[n][j] = exp2f(fmaf(s[n][j], p.scale_log2, -mx[j >> 1]));
         l_run[j >> 1] += s[n][j];
       }
     }
+    // (once a row has met its largest keys the maximum stops moving and the rescale is a multiply by one)
+    if (__any_sync(0xffffffffu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
 #pragma unroll
-    for (int n = 0; n < DH / 8; ++n) {
-      o[n][0] *= alpha[0];
-      o[n][1] *= alpha[0];
-      o[n][2] *= alpha[1];
-      o[n][3] *= alpha[1];
+      for (int n = 0; n < DH / 8; ++n) {
+        o[n][0] *= alpha[0];
+        o[n][1] *= alpha[0];
+        o[n][2] *= alpha[1];
+        o[n][3] *= alpha[1];
+      }
     }
     // O [16 rows x DH] += P [16 x 64] V [64 x DH]
 #pragma unroll
@@ -213,6 +214,7 @@ LSA_API int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_
   LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && n_keys >= 0 && first_position >= 0 && window >= 0 &&
                   sink >= 0,
               LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(scale > 0.0f, LSA_ERR_ARGUMENT);  // the row maximum is taken before the scale is applied
   LSA_REQUIRE(dh == 64 || dh == 128, LSA_ERR_UNSUPPORTED);
   const int group = Hq / Hkv;
   LSA_REQUIRE(group <= 16 && sink <= lsa::kBandKeys, LSA_ERR_UNSUPPORTED);
