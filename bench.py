@@ -246,9 +246,13 @@ def run_ours(args, cfg: dict) -> dict:
     if world > 1:
         from lsa_b200.parallel import ShardedFlatLayer, deal
 
-        # queries are replicated; a rank holds only its own share of the KV rows, on the host and on the device
+        # a rank holds only its own share of the KV rows, on the host and on the device; the queries are split by
+        # rows (every rank reads the gathered cache for its own rows) or replicated (context parallel: every rank
+        # reads the keys it stores for all rows and the partial outputs are merged)
         layer = ShardedFlatLayer(base, rank, world)
         k_h, v_h = deal(k_h, rank, world).clone().pin_memory(), deal(v_h, rank, world).clone().pin_memory()
+        if args.parallel == "rows":
+            q_h = layer.rows_of(q_h, cfg["chunk"]).clone().pin_memory()
     q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
     out_d = torch.empty(cfg["tokens"] // world, cfg["heads"], cfg["head_dim"], dtype=torch.bfloat16, device="cuda")
     out_h = torch.empty(out_d.shape, dtype=torch.bfloat16).pin_memory()
@@ -273,14 +277,21 @@ def run_ours(args, cfg: dict) -> dict:
 
     q_in, k_in, v_in = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
+    by_rows = world > 1 and args.parallel == "rows"
+
+    def prefill(q_, k_, v_):
+        if by_rows:
+            return layer.prefill_by_rows(q_, k_, v_, cfg["tokens"], chunk=cfg["chunk"], out=out_d)
+        return layer.prefill(q_, k_, v_, chunk=cfg["chunk"], out=out_d)
+
     def resident_step():
-        layer.prefill(q, k, v, chunk=cfg["chunk"], out=out_d)
+        prefill(q, k, v)
 
     def e2e_step():
         q_in.copy_(q_h, non_blocking=True)
         k_in.copy_(k_h, non_blocking=True)
         v_in.copy_(v_h, non_blocking=True)
-        out_h.copy_(layer.prefill(q_in, k_in, v_in, chunk=cfg["chunk"], out=out_d), non_blocking=True)
+        out_h.copy_(prefill(q_in, k_in, v_in), non_blocking=True)
 
     for _ in range(args.warmup):
         resident_step()
@@ -319,7 +330,7 @@ def run_ours(args, cfg: dict) -> dict:
     else:
         peak, peak_kind = 6650.0, "fallback"
     per_launch_bytes = achieved = useful_tflops = None
-    bucket_major = world == 1  # the single-GPU prefill reads the selected keys bucket by bucket
+    bucket_major = world == 1 or by_rows  # these prefills read the selected keys bucket by bucket
     if gathered is not None and attend_launches:
         stage_bytes = bucket_attend_algorithmic_bytes(cfg, pairs) if bucket_major else \
             attend_algorithmic_bytes(cfg, gathered)
@@ -335,7 +346,10 @@ def run_ours(args, cfg: dict) -> dict:
                    "top_p": cfg["top_p"], "top_k": cfg["top_k"], "window": cfg["window_size"],
                    "sink": cfg["sink_size"], "chunk": cfg["chunk"],
                    "l2": "inputs (1.9 GB of q, k, v per step) exceed the 126 MB L2",
-                   "parallelism": "1 GPU" if world == 1 else f"KV rows and cluster blocks dealt round-robin over {world} GPUs (context parallel)"},
+                   "parallelism": "1 GPU" if world == 1 else (
+                       f"KV rows and cluster blocks dealt round-robin over {world} GPUs; " + (
+                           "the cache all-gathered once a step, query rows split over the ranks" if by_rows else
+                           "every rank reads the keys it stores, partial outputs merged (context parallel)"))},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": (q_h.numel() * world + (k_h.numel() + v_h.numel()) * world) * 2,
                 "d2h_bytes_per_step": out_h.numel() * world * 2, "ms_per_step": e2e_ms},
@@ -406,6 +420,9 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=None, help="a smaller context of the same workload (profiling)")
+    parser.add_argument("--parallel", default="rows", choices=["rows", "context"],
+                        help="at N > 1: split the query rows over the ranks (the cache is all-gathered once a step), "
+                             "or keep every rank on the keys it stores and merge partial outputs")
     args = parser.parse_args()
     cfg = dict(C2)
     if args.tokens:

@@ -306,11 +306,17 @@ int lsa_sparse_attend_static(const uint16_t *q, int64_t R, int Hq, int dh, int64
  * sinks [0, min(sink, window start)). One pass over the band's K/V serves 16 query rows and a whole head group.
  * The result is partial - normalised fp32 output and log-sum-exp - and is meant as lsa_sparse_attend's
  * init_out / init_lse, whose lists then hold only the selected keys (lsa_expand with LSA_EXPAND_NO_LOCAL).
- * Reference: the window and sink terms of keep_set (src/lsa/core/attention.py:49-58). sink <= 64. */
+ * Reference: the window and sink terms of keep_set (src/lsa/core/attention.py:49-58). sink <= 64.
+ *   flags  0: heads of 128 dims packed densely and at least 128 rows go to the tensor-memory form - 128 rows of one
+ *          head a CTA, both products on tcgen05 (the rows as M), K/V tiles streamed by tensor-map copies, the band
+ *          walked twice (row maxima, then the sums) so the accumulator in tensor memory is never rescaled;
+ *          LSA_BAND_WARP_MMA: always the warp-level form
+ *   status (may be NULL) is raised if a bounded on-chip wait of the tensor-memory form gives up */
+#define LSA_BAND_WARP_MMA 1
 int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride, int64_t q_head_stride,
                     const uint16_t *k, const uint16_t *v, int64_t n_keys, int Hkv, int64_t kv_row_stride,
                     int64_t kv_head_stride, int64_t first_position, int window, int sink, float scale, float *out_f32,
-                    float *lse, void *stream);
+                    float *lse, int flags, int32_t *status, void *stream);
 
 /* Gather-sparse attention over a shared latent cache (the MLA form): all Hq heads of a row attend over the SAME
  * listed latent rows; a key is the whole row (dk dims, rope part last), a value its first dv dims, and q holds the

@@ -204,12 +204,18 @@ __global__ void band_attend_kernel(BandParams p) {
   }
 }
 
+int launch_band_attend_tc(const uint16_t *q, int64_t R, int Hq, int64_t q_row_stride, const uint16_t *k,
+                          const uint16_t *v, int64_t n_keys, int Hkv, int64_t kv_row_stride, int64_t first_position,
+                          int window, int sink, float scale, float *out, float *lse, int32_t *status,
+                          cudaStream_t stream);
+
 }  // namespace lsa
 
 LSA_API int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_stride,
                             int64_t q_head_stride, const uint16_t *k, const uint16_t *v, int64_t n_keys, int Hkv,
                             int64_t kv_row_stride, int64_t kv_head_stride, int64_t first_position, int window,
-                            int sink, float scale, float *out_f32, float *lse, void *stream) {
+                            int sink, float scale, float *out_f32, float *lse, int flags, int32_t *status,
+                            void *stream) {
   LSA_REQUIRE(q && k && v && out_f32 && lse, LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && Hq >= 1 && Hkv >= 1 && Hq % Hkv == 0 && n_keys >= 0 && first_position >= 0 && window >= 0 &&
                   sink >= 0,
@@ -223,6 +229,13 @@ LSA_API int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_
                   ((uintptr_t)q % 4) == 0,
               LSA_ERR_ARGUMENT);
   if (R == 0) return LSA_OK;
+  // The tensor-memory form: a head's 128 rows a CTA, operands fetched through tensor maps. It wants heads of 128
+  // dims packed densely (a row of heads is a row of the map) and 16-byte aligned rows; a chunk shorter than a tile
+  // of rows gains nothing from it.
+  const bool dense = q_head_stride == dh && kv_head_stride == dh && q_row_stride % 8 == 0 && ((uintptr_t)q % 16) == 0;
+  if (!(flags & LSA_BAND_WARP_MMA) && dh == 128 && dense && R >= 128 && n_keys < INT32_MAX)
+    return lsa::launch_band_attend_tc(q, R, Hq, q_row_stride, k, v, n_keys, Hkv, kv_row_stride, first_position,
+                                      window, sink, scale, out_f32, lse, status, (cudaStream_t)stream);
   lsa::BandParams p;
   p.q = q;
   p.k = k;

@@ -1,0 +1,292 @@
+// The window and the sinks of a prefill as dense banded attention on the fifth-generation tensor cores.
+//
+// A CTA owns 128 consecutive query rows of ONE query head and walks the band of keys they see - from the first row's
+// window start to the last row, in tiles of 64 keys, plus a tile for the sinks. The rows are the M = 128 side of both
+// products, so a row of S and of O lives in one lane of tensor memory and the thread that owns the row does its
+// softmax alone. The band is walked TWICE: the first walk only takes every row's maximum, the second computes
+// P = exp2(S - max) and accumulates O = sum P V in tensor memory without ever rescaling it (the second product costs
+// half a walk more of tensor-core time, which this path has to spare, and saves the read-modify-write of O).
+//
+//   warp 0      one lane streams the key and value tiles with tensor-map copies (128-byte swizzle) through a ring
+//   warp 1      tensor-memory allocation; one lane issues the MMAs: S = Q K^T (both K-major) into one of two S
+//               buffers, O += P V with V read as stored (an MN-major operand)
+//   warps 2-5   thread = row: S out of tensor memory, masks on the band's edge tiles only, maximum (walk one) or
+//               P in bf16 into the consumed key tile's slot (walk two), then the normalised fp32 output
+//
+// Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's abort flag and the status word, the
+// roles drain, the tensor memory is freed and the CTA leaves.
+#include "common.cuh"
+#include "mma.cuh"
+#include "umma.cuh"
+
+namespace lsa {
+
+constexpr int kBtRows = 128;
+constexpr int kBtKeys = 64;
+constexpr int kBtThreads = 192;
+constexpr int kBtStages = 2;
+constexpr int kBtPlane = kBtKeys * 128;             // 64 keys x 64 dims of bf16
+constexpr int kBtQPlane = kBtRows * 128;            // 128 rows x 64 dims
+constexpr int kBtStage = 4 * kBtPlane;              // K (2 planes; P lands here once S is done) and V (2 planes)
+constexpr int kBtSmem = 2 * kBtQPlane + kBtStages * kBtStage + 1024;
+constexpr int kBtTmemCols = 256;                    // S buffers in columns 0-63 and 64-127, O in 128-255
+
+struct BandTcParams {
+  float *out, *lse;
+  int32_t *status;
+  int64_t R, n_keys, first_position;
+  int Hq, group, window, sink;
+  float scale_log2;
+};
+
+__global__ void __launch_bounds__(kBtThreads, 2)
+    band_attend_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                          const __grid_constant__ CUtensorMap map_v, BandTcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // full / empty: a ring stage's tiles have landed / may be overwritten; s_ready / s_free: an S buffer holds a
+  // product / has been read; p_ready: a stage holds P; q_full, o_done: once each.
+  __shared__ __align__(8) uint64_t bars[5 * 2 + 2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_s;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_s = base, ring = base + 2 * kBtQPlane;
+  auto bar = [&](int kind, int i) { return smem_u32(&bars[kind * 2 + i]); };
+  enum { kFull = 0, kEmpty = 1, kSReady = 2, kSFree = 3, kPReady = 4 };
+  const uint32_t q_full = smem_u32(&bars[10]), o_done = smem_u32(&bars[11]);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row0 = (int64_t)blockIdx.x * kBtRows;
+  const int head = blockIdx.y, kv_head = head / p.group;
+  const int64_t pos0 = p.first_position + row0;
+  const int64_t pos_last = min(pos0 + kBtRows - 1, p.first_position + p.R - 1);
+  const int64_t band_first = max((int64_t)0, pos0 + 1 - p.window) / kBtKeys * kBtKeys;
+  const int band_tiles = (int)((pos_last - band_first) / kBtKeys) + 1;
+  const bool has_sinks = p.sink > 0 && band_first > 0;
+  const int tiles = band_tiles + (has_sinks ? 1 : 0);  // tile 0 is the sinks when there are any
+  auto key0_of = [&](int tile) {
+    return has_sinks ? (tile == 0 ? (int64_t)0 : band_first + (int64_t)(tile - 1) * kBtKeys)
+                     : band_first + (int64_t)tile * kBtKeys;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kFull, i), 1);
+      mbar_init(bar(kEmpty, i), 1);
+      mbar_init(bar(kSReady, i), 1);
+      mbar_init(bar(kSFree, i), 128);
+      mbar_init(bar(kPReady, i), 128);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(o_done, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"(kBtTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // the query tile once, then the ring: keys alone on the first walk, keys and values on the second
+      mbar_expect_tx(q_full, 2 * kBtQPlane);
+      tma_load_2d(q_s, &map_q, q_full, head * 128, (int)row0);
+      tma_load_2d(q_s + kBtQPlane, &map_q, q_full, head * 128 + 64, (int)row0);
+      uint32_t phase[2] = {0, 0};
+      for (int n = 0; n < 2 * tiles && !abort_s; ++n) {
+        const int stage = n & 1, tile = n % tiles;
+        const bool second = n >= tiles;
+        if (n >= kBtStages) {
+          if (!mbar_wait(bar(kEmpty, stage), phase[stage])) {
+            abort_s = 1;
+            break;
+          }
+          phase[stage] ^= 1;
+        }
+        const uint32_t dst = ring + stage * kBtStage;
+        const int y = (int)key0_of(tile), x = kv_head * 128;
+        mbar_expect_tx(bar(kFull, stage), second ? 4 * kBtPlane : 2 * kBtPlane);
+        tma_load_2d(dst, &map_k, bar(kFull, stage), x, y);
+        tma_load_2d(dst + kBtPlane, &map_k, bar(kFull, stage), x + 64, y);
+        if (second) {
+          tma_load_2d(dst + 2 * kBtPlane, &map_v, bar(kFull, stage), x, y);
+          tma_load_2d(dst + 3 * kBtPlane, &map_v, bar(kFull, stage), x + 64, y);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(kBtKeys), idesc_o = umma_idesc(128, true);
+      uint32_t full_phase[2] = {0, 0}, free_phase[2] = {0, 0}, p_phase[2] = {0, 0};
+      bool ok = mbar_wait(q_full, 0);
+      // the second product of tile n, once the workers have written its P
+      auto second_product = [&](int n) {
+        const int stage = n & 1;
+        if (!mbar_wait(bar(kPReady, stage), p_phase[stage])) return false;
+        p_phase[stage] ^= 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t p_tile = ring + stage * kBtStage, v_tile = p_tile + 2 * kBtPlane;
+#pragma unroll
+        for (int k = 0; k < kBtKeys / 16; ++k)
+          umma_bf16(tmem_base + 128, smem_desc_sw128(p_tile) + 2 * k, smem_desc_mn_sw128(v_tile + k * 2048, kBtPlane),
+                    idesc_o, (n > tiles || k > 0) ? 1u : 0u);
+        umma_commit(bar(kEmpty, stage));
+        return true;
+      };
+      for (int n = 0; n < 2 * tiles && ok && !abort_s; ++n) {
+        const int stage = n & 1;
+        const bool second = n >= tiles;
+        ok = mbar_wait(bar(kFull, stage), full_phase[stage]);
+        if (!ok) break;
+        full_phase[stage] ^= 1;
+        if (n >= 2) {
+          ok = mbar_wait(bar(kSFree, stage), free_phase[stage]);
+          if (!ok) break;
+          free_phase[stage] ^= 1;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t k_tile = ring + stage * kBtStage;
+#pragma unroll
+        for (int plane = 0; plane < 2; ++plane)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + stage * 64, smem_desc_sw128(q_s + plane * kBtQPlane) + 2 * k,
+                      smem_desc_sw128(k_tile + plane * kBtPlane) + 2 * k, idesc_s, (plane | k) != 0);
+        umma_commit(bar(kSReady, stage));
+        if (!second) umma_commit(bar(kEmpty, stage));  // on the first walk the keys are all a stage holds
+        if (second && n > tiles) ok = second_product(n - 1);
+      }
+      if (ok && !abort_s) ok = second_product(2 * tiles - 1);
+      if (!ok) abort_s = 1;
+      umma_commit(o_done);
+    }
+  } else {
+    // Workers: TMEM lane 32 * (warp % 4) + lane is this thread's row.
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const int64_t pos = pos0 + row;
+    const bool live = row0 + row < p.R;
+    const int64_t start = max((int64_t)0, pos + 1 - p.window);
+    const int64_t sink_end = min((int64_t)p.sink, start);
+    uint32_t ready_phase[2] = {0, 0};
+    float m_row = -INFINITY, l_row = 0.0f;
+    bool go = true;
+    for (int n = 0; n < 2 * tiles && go; ++n) {
+      const int stage = n & 1, tile = n % tiles;
+      const bool second = n >= tiles;
+      go = __all_sync(0xffffffffu, mbar_wait(bar(kSReady, stage), ready_phase[stage]) && !abort_s);
+      if (!go) break;
+      ready_phase[stage] ^= 1;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t r0[32], r1[32];
+      tmem_load_32(lane_addr + stage * 64, r0);
+      tmem_load_32(lane_addr + stage * 64 + 32, r1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kSFree, stage)) : "memory");
+      const int64_t key0 = key0_of(tile);
+      const bool is_sinks = has_sinks && tile == 0;
+      // a tile inside every row's window, below every row's position and inside the cache needs no masks
+      const bool inside = !is_sinks && key0 >= max((int64_t)0, pos_last + 1 - p.window) && key0 + kBtKeys - 1 <= pos0 &&
+                          key0 + kBtKeys <= p.n_keys && pos0 + kBtRows <= p.first_position + p.R;
+      float s[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float raw = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
+        if (inside) {
+          s[c] = raw;
+        } else {
+          const int64_t key = key0 + c;
+          // (a band that starts at key 0 holds the sinks of its rows itself: keys below a row's window start)
+          const bool ok = live && key < p.n_keys &&
+                          (is_sinks ? key < sink_end : ((key >= start && key <= pos) || key < sink_end));
+          s[c] = ok ? raw : -INFINITY;
+        }
+      }
+      if (!second) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) m_row = fmaxf(m_row, s[c]);
+      } else {
+        if (n == tiles) m_row = m_row == -INFINITY ? 0.0f : m_row * p.scale_log2;  // the offset of every exponent
+        const uint32_t p_row = ring + stage * kBtStage + row * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float e0 = exp2f(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, -m_row));
+            const float e1 = exp2f(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, -m_row));
+            l_row += e0 + e1;
+            w[j] = pack_bf16x2(e0, e1);
+          }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)), "r"(w[0]),
+                       "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kPReady, stage)) : "memory");
+      }
+    }
+    go = __all_sync(0xffffffffu, go && mbar_wait(o_done, 0) && !abort_s);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (go) {
+      const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+      const int64_t out_row = (row0 + row) * p.Hq + head;
+#pragma unroll
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t r[32];
+        tmem_load_32(lane_addr + 128 + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
+          float4 *dst = reinterpret_cast<float4 *>(p.out + out_row * 128 + c0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            dst[i] = make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
+                                 __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+        }
+      }
+      if (live) p.lse[out_row] = l_row > 0.0f ? (m_row + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
+    } else {
+      abort_s = 1;
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBtTmemCols));
+  }
+  if (threadIdx.x == 0 && abort_s && p.status) atomicAdd(p.status, 1);
+}
+
+// Launches the tensor-core band kernel; the caller has checked dh == 128 and the alignments a tensor map needs.
+int launch_band_attend_tc(const uint16_t *q, int64_t R, int Hq, int64_t q_row_stride, const uint16_t *k,
+                          const uint16_t *v, int64_t n_keys, int Hkv, int64_t kv_row_stride, int64_t first_position,
+                          int window, int sink, float scale, float *out, float *lse, int32_t *status,
+                          cudaStream_t stream) {
+  CUtensorMap map_q, map_k, map_v;
+  int rc = make_map(&map_q, q, R, (int64_t)Hq * 128, q_row_stride, kBtRows);
+  if (rc != LSA_OK) return rc;
+  rc = make_map(&map_k, k, n_keys, (int64_t)Hkv * 128, kv_row_stride, kBtKeys);
+  if (rc != LSA_OK) return rc;
+  rc = make_map(&map_v, v, n_keys, (int64_t)Hkv * 128, kv_row_stride, kBtKeys);
+  if (rc != LSA_OK) return rc;
+  BandTcParams p = {};
+  p.out = out, p.lse = lse, p.status = status;
+  p.R = R, p.n_keys = n_keys, p.first_position = first_position;
+  p.Hq = Hq, p.group = Hq / Hkv, p.window = window, p.sink = sink;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  if (cudaFuncSetAttribute(band_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBtSmem) != cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  const dim3 grid((unsigned)((R + kBtRows - 1) / kBtRows), (unsigned)Hq);
+  band_attend_tc_kernel<<<grid, kBtThreads, kBtSmem, stream>>>(map_q, map_k, map_v, p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+}  // namespace lsa

@@ -172,36 +172,6 @@ __global__ void __launch_bounds__(kGemmThreads)
 
 // ------------------------------------------------------------------------------------------------ host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void *sym = nullptr;
-    cudaDriverEntryPointQueryResult query;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query) == cudaSuccess &&
-        query == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-
-// A [rows, cols] bf16 matrix with `ld` elements between rows, read in boxes of [box_rows, 64] with the 128-byte swizzle.
-static int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (!encode) return LSA_ERR_LAUNCH;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elem,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return rc == CUDA_SUCCESS ? LSA_OK : LSA_ERR_ARGUMENT;
-}
-
 template <int N_TILE, int EPILOGUE>
 static int launch_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *B, int64_t N, int64_t ldb,
                        GemmParams p, cudaStream_t s) {

@@ -216,39 +216,46 @@ class FlatLayer:
         `band` reads the window and the sinks as dense tiles; `bucket_major` reads the selected keys bucket by bucket
         where the shapes allow (both off: every row gathers its whole list).
         """
-        T, dev = q.shape[0], q.device
+        T = q.shape[0]
         index = self.build_index(k, reuse_buffers=not return_index)
         out = torch.empty_like(q) if out is None else out
-        d_idx = self.query_map.shape[1]
         for start in range(0, T, chunk):
             stop = min(T, start + chunk)
-            rows = q[start:stop]
-            positions = torch.arange(start, stop, device=dev)
-            with probe.region("index map"):
-                index_queries = self.index_queries(rows, out=self._buffer("index queries", (stop - start, d_idx),
-                                                                          torch.float32, dev))
-            # The window and the sinks are the same keys for neighbouring rows: one dense band serves them, and the
-            # gather starts from its partial result and reads the selected keys alone.
-            banded = band and self.design.sink_size <= 64 and k.shape[0] >= stop
-            init = self.band(rows, k, v, start) if banded else None
-            lse = self._buffer("lse", (stop - start, self.heads), torch.float32, dev)
-            # (without the band the window and the sinks are in the lists, which only the gather path reads)
-            if banded and bucket_major and ops.bucket_attend_supported(rows, k, self.design.bucket_cap):
-                # The rows of a chunk pick the same buckets over and over: read each bucket's keys once per 64
-                # (row, pick) pairs instead of once per pair.
-                picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True)
-                need = _lib.query("lsa_bucket_attend_workspace_bytes", stop - start, self.design.top_p, self.heads,
-                                  self.head_dim, index.buckets.bucket_members.shape[0])
-                with probe.region("attend"):
-                    ops.bucket_attend(rows, k, v, picked, positions, index.buckets.bucket_members, self.design.top_k,
-                                      self.design.sink_size, self.design.window_size, self.scale, init=init,
-                                      row_top_p=row_p, row_top_k=row_k, out=out[start:stop], lse=lse,
-                                      warp_mma=not self.bucket_tensor_memory,
-                                      workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
-                continue
-            lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
-            self.attend(rows, k, v, lists, lengths, out=out[start:stop], lse=lse, init=init)
+            self.prefill_rows(q[start:stop], start, k, v, index, out[start:stop], band, bucket_major)
         return (out, index) if return_index else out
+
+    def prefill_rows(self, rows: torch.Tensor, start: int, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,
+                     out: torch.Tensor, band: bool = True, bucket_major: bool = True) -> torch.Tensor:
+        """The read of consecutive query rows [n, Hq, dh] at positions start.. over a cache whose index is built,
+        into `out` [n, Hq, dh] bf16 - one chunk of a prefill, or one rank's rows of a chunk."""
+        n, dev = rows.shape[0], rows.device
+        stop = start + n
+        positions = torch.arange(start, stop, device=dev)
+        with probe.region("index map"):
+            index_queries = self.index_queries(rows, out=self._buffer("index queries", (n, self.query_map.shape[1]),
+                                                                      torch.float32, dev))
+        # The window and the sinks are the same keys for neighbouring rows: one dense band serves them, and the
+        # read of the selected keys starts from its partial result.
+        banded = band and self.design.sink_size <= 64 and k.shape[0] >= stop
+        init = self.band(rows, k, v, start) if banded else None
+        lse = self._buffer("lse", (n, self.heads), torch.float32, dev)
+        # (without the band the window and the sinks are in the lists, which only the gather path reads)
+        if banded and bucket_major and ops.bucket_attend_supported(rows, k, self.design.bucket_cap):
+            # The rows of a chunk pick the same buckets over and over: read each bucket's keys once per 128
+            # (row, pick) pairs instead of once per pair.
+            picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True)
+            need = _lib.query("lsa_bucket_attend_workspace_bytes", n, self.design.top_p, self.heads, self.head_dim,
+                              index.buckets.bucket_members.shape[0])
+            with probe.region("attend"):
+                ops.bucket_attend(rows, k, v, picked, positions, index.buckets.bucket_members, self.design.top_k,
+                                  self.design.sink_size, self.design.window_size, self.scale, init=init,
+                                  row_top_p=row_p, row_top_k=row_k, out=out, lse=lse,
+                                  warp_mma=not self.bucket_tensor_memory,
+                                  workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
+            return out
+        lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
+        self.attend(rows, k, v, lists, lengths, out=out, lse=lse, init=init)
+        return out
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,
                splits: int = 8):

@@ -435,10 +435,12 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
 
 
 def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_position: int, window: int, sink: int,
-                scale: float, out: torch.Tensor | None = None, lse: torch.Tensor | None = None):
+                scale: float, out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
+                warp_mma: bool = False, status: torch.Tensor | None = None):
     """The window and sinks of consecutive query rows as dense banded attention: q [R, Hq, dh] at positions
     first_position.., k/v [n_keys, Hkv, dh] by position. Returns the PARTIAL read (out fp32 [R, Hq, dh], lse [R, Hq])
-    that `sparse_attend(..., init=(out, lse))` extends with the selected keys."""
+    that `sparse_attend(..., init=(out, lse))` extends with the selected keys. Dense heads of 128 dims and 128 rows
+    or more run on tcgen05 with tensor-memory accumulators unless `warp_mma` asks for the warp-level kernel."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         raise ValueError("q, k and v must be bfloat16")
     if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or k.stride() != v.stride():
@@ -447,7 +449,8 @@ def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_positio
     out = torch.empty(R, Hq, dh, device=q.device, dtype=torch.float32) if out is None else out
     lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32) if lse is None else lse
     call("lsa_band_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), k.shape[0], k.shape[1],
-         k.stride(0), k.stride(1), first_position, window, sink, float(scale), ptr(out), ptr(lse), stream())
+         k.stride(0), k.stride(1), first_position, window, sink, float(scale), ptr(out), ptr(lse),
+         1 if warp_mma else 0, ptr(status), stream())
     return out, lse
 
 

@@ -168,11 +168,54 @@ class ShardedFlatLayer:
                 blocks * per_block, d.bucket_cap)
         return centroids, table, index_keys
 
+    def rows_of(self, q: torch.Tensor, chunk: int) -> torch.Tensor:
+        """This rank's query rows of q [T, ...]: rows [c*chunk + rank*chunk/world, c*chunk + (rank+1)*chunk/world)
+        of every chunk c, [T / world, ...] - the rows whose output `prefill` leaves on this rank."""
+        share = chunk // self.world
+        return q.view(q.shape[0] // chunk, self.world, share, *q.shape[1:])[:, self.rank].reshape(
+            q.shape[0] // self.world, *q.shape[1:])
+
+    def prefill_by_rows(self, q: torch.Tensor, k_share: torch.Tensor, v_share: torch.Tensor, tokens: int,
+                        chunk: int = 8192, out: torch.Tensor | None = None):
+        """Causal prefill with the QUERY ROWS split over the ranks: the cache stays dealt out for storage, but a
+        prefill reads almost all of it from every row, so the shares are all-gathered once (K, V and the index - the
+        one exchange of the step) and every rank then runs the single-GPU read - dense band, bucket-major expansion -
+        over its own rows of every chunk. No partial outputs cross ranks and nothing is merged.
+
+        q holds this rank's rows (`rows_of`), [tokens / world, Hq, dh], or all rows [tokens, Hq, dh]; the result is
+        this rank's rows, as `prefill` returns them.
+        """
+        layer, d, world, rank = self.layer, self.design, self.world, self.rank
+        if tokens % chunk or chunk % world:
+            raise ValueError(f"{tokens} tokens must split into chunks of {chunk} rows, and a chunk over {world} ranks")
+        from lsa_b200.core import Buckets
+        from lsa_b200.layer import FlatIndex
+
+        if q.shape[0] == tokens:
+            q = self.rows_of(q, chunk)
+        own_centroids, members, index_keys = self.build_index(k_share, tokens)
+        blocks, per_block = tokens // d.cluster_block_size, d.block_bucket_count
+        with probe.region("gather cache"):
+            centroids = gather_pieces(own_centroids, self.group).view(world, blocks // world, per_block, -1).transpose(
+                0, 1).reshape(blocks * per_block, -1)
+            k = undeal(gather_pieces(k_share, self.group), self.granule)
+            v = undeal(gather_pieces(v_share, self.group), self.granule)
+        index = FlatIndex(index_keys, Buckets(centroids, members, (members >= 0).sum(1, dtype=torch.int32), per_block,
+                                              d.cluster_block_size))
+        share = chunk // world
+        if out is None:
+            out = torch.empty(tokens // world, q.shape[1], q.shape[2], dtype=q.dtype, device=q.device)
+        for c, start in enumerate(range(0, tokens, chunk)):
+            layer.prefill_rows(q[c * share:(c + 1) * share], start + rank * share, k, v, index,
+                               out[c * share:(c + 1) * share])
+        return out
+
     def prefill(self, q: torch.Tensor, k_share: torch.Tensor, v_share: torch.Tensor, chunk: int = 8192,
                 out: torch.Tensor | None = None):
         """Causal prefill of replicated queries q [T, Hq, dh] over this rank's dealt share of the cache
-        (`deal(k, rank, world)`, `deal(v, rank, world)`). Returns this rank's rows of the output, chunk by chunk:
-        rows [c*chunk + rank*chunk/world, c*chunk + (rank+1)*chunk/world) of every chunk c, [T / world, Hq, dh].
+        (`deal(k, rank, world)`, `deal(v, rank, world)`), every rank reading only the keys it stores and the partial
+        outputs merged by their log-sum-exps (context parallel). Returns this rank's rows of the output, chunk by
+        chunk: rows [c*chunk + rank*chunk/world, c*chunk + (rank+1)*chunk/world) of every chunk c, [T / world, Hq, dh].
         """
         layer, d, world, rank = self.layer, self.design, self.world, self.rank
         T = q.shape[0]

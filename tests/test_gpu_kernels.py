@@ -445,10 +445,14 @@ def test_band_attention_and_its_hand_over_to_the_gather(ops, oracle, T, Hq, Hkv,
     empty = np.full((R, 1), -1, dtype=np.int32)
     want, want_lse = oracle.sparse_attend(q[rows], k, v, empty, rows, window, sink, scale)
     Q, K, V = cuda(q[rows], torch.bfloat16), cuda(k, torch.bfloat16), cuda(v, torch.bfloat16)
-    out, lse = ops.band_attend(Q, K, V, first, window, sink, scale)
-    err = np.abs(out.cpu().numpy() - want)
-    assert err.max() <= 2e-2 and err.mean() <= 2e-3, (err.max(), err.mean())
-    np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=0, atol=2e-3)
+    # both forms: tensor memory (dense heads of 128 dims, 128 rows or more) and warp-level tiles
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for warp_mma in (True, False):
+        out, lse = ops.band_attend(Q, K, V, first, window, sink, scale, warp_mma=warp_mma, status=status)
+        err = np.abs(out.cpu().numpy() - want)
+        assert err.max() <= 2e-2 and err.mean() <= 2e-3, (warp_mma, err.max(), err.mean())
+        np.testing.assert_allclose(lse.cpu().numpy(), want_lse, rtol=0, atol=2e-3)
+    assert int(status) == 0
     # the gather continues from the band's partial result over keys outside the window and the sinks
     rng = np.random.default_rng(1)
     ids = np.full((R, 200), -1, dtype=np.int32)

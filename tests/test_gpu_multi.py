@@ -49,6 +49,13 @@ def _rank_main(rank, world, port, result_dir):
         err = (got.float() - mine.float()).abs()
         assert got.shape == mine.shape
         assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+        # the query rows split over the ranks instead: the same rows from the gathered cache, all queries or its own
+        for rows in (q, sharded.rows_of(q, chunk).contiguous()):
+            split = sharded.prefill_by_rows(rows, deal(k, rank, world).contiguous(), deal(v, rank, world).contiguous(),
+                                            T, chunk=chunk)
+            err = (split.float() - mine.float()).abs()
+            assert split.shape == mine.shape
+            assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
