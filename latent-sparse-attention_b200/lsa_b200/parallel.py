@@ -19,6 +19,11 @@ holds the same picks -> expand them, writing only the rows this rank holds (the 
 over its own rows -> all-gather the log-sum-exps, weight the partial output by exp(lse_r - lse), reduce-scatter over
 query rows. The union of the ranks' lists is the single-GPU list and the merged output the single-GPU output.
 
+That is `prefill`, the context-parallel form, and the only way to split a decode step. A prefill reads almost the
+whole cache from every row, so `prefill_by_rows` splits the QUERY ROWS instead: the shares of K, V and the index are
+all-gathered once a step and every rank runs the single-GPU read (dense band, bucket-major expansion) over its own
+rows of every chunk; nothing is merged.
+
 The reference replicates the whole index and interleaves single KV slots over ranks
 (`src/lsa/sglang/context_parallel.py:1-24`, `src/lsa/sglang/models/qwen3_5/backend.py:621-781`). No kernel here reads
 a peer's memory; gathered data lands in local memory through the collective first.
