@@ -353,6 +353,9 @@ int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int6
  *   out_bf16 [R, Hq, dh]; lse_out [R, Hq] or NULL
  *   workspace: lsa_bucket_attend_workspace_bytes(); it holds a bf16 partial output per (row, pick, head), which is
  *            what trades the gather's repeated reads for one write and one read
+ *   init_ready_event  a cudaEvent_t (as void*) or NULL: when init_out / init_lse are written on ANOTHER stream (the
+ *            band kernel running beside this call's first passes) the event recorded after that work; only the
+ *            merge pass waits for it
  *   flags    0: the two products of a (bucket, head) run on tcgen05 with the pairs as the M = 128 rows, S and O in
  *            tensor memory; LSA_BUCKET_WARP_MMA: the same pass on warp-level mma.sync tiles of 16 rows
  * dh = 128 and Hq / Hkv <= 8 in this build; other shapes return LSA_ERR_UNSUPPORTED and the caller uses
@@ -365,7 +368,7 @@ int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_ro
                       const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
                       const int32_t *row_top_k, int top_k, int sink, int window, const float *init_out,
                       const float *init_lse, float scale, uint16_t *out_bf16, float *lse_out, int flags,
-                      void *workspace, size_t workspace_bytes, void *stream);
+                      void *init_ready_event, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the

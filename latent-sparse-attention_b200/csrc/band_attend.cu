@@ -146,7 +146,7 @@ __global__ void band_attend_kernel(BandParams p) {
       // the products are raw: the scale is positive, so it is applied to the maximum and inside the exponent
       const float m_new = fmaxf(m_run[r], mx[r] * p.scale_log2);
       const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[r] = exp2f(m_run[r] - m_safe);
+      alpha[r] = fast_exp2(m_run[r] - m_safe);
       m_run[r] = m_new;
       mx[r] = m_safe;
       l_run[r] *= alpha[r];
@@ -155,7 +155,7 @@ __global__ void band_attend_kernel(BandParams p) {
     for (int n = 0; n < kBandKeys / 8; ++n) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        s[n][j] = exp2f(fmaf(s[n][j], p.scale_log2, -mx[j >> 1]));
+        s[n][j] = fast_exp2(fmaf(s[n][j], p.scale_log2, -mx[j >> 1]));
         l_run[j >> 1] += s[n][j];
       }
     }

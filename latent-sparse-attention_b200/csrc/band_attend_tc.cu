@@ -219,8 +219,8 @@ __global__ void __launch_bounds__(kBtThreads, 2)
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float e0 = exp2f(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, -m_row));
-            const float e1 = exp2f(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, -m_row));
+            const float e0 = fast_exp2(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, -m_row));
+            const float e1 = fast_exp2(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, -m_row));
             l_row += e0 + e1;
             w[j] = pack_bf16x2(e0, e1);
           }

@@ -288,10 +288,10 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
 #pragma unroll
     for (int nt = 0; nt < kBktKeys / 8; ++nt) {
       if (nt * 8 >= key_steps * 16) continue;
-      s[nt][0] = exp2f(fmaf(s[nt][0], p.scale_log2, -m_off[0]));
-      s[nt][1] = exp2f(fmaf(s[nt][1], p.scale_log2, -m_off[0]));
-      s[nt][2] = exp2f(fmaf(s[nt][2], p.scale_log2, -m_off[1]));
-      s[nt][3] = exp2f(fmaf(s[nt][3], p.scale_log2, -m_off[1]));
+      s[nt][0] = fast_exp2(fmaf(s[nt][0], p.scale_log2, -m_off[0]));
+      s[nt][1] = fast_exp2(fmaf(s[nt][1], p.scale_log2, -m_off[0]));
+      s[nt][2] = fast_exp2(fmaf(s[nt][2], p.scale_log2, -m_off[1]));
+      s[nt][3] = fast_exp2(fmaf(s[nt][3], p.scale_log2, -m_off[1]));
       l_row[0] += s[nt][0] + s[nt][1];
       l_row[1] += s[nt][2] + s[nt][3];
     }
@@ -468,7 +468,8 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
                               const int64_t *positions, const int32_t *members, int64_t m, int bucket_cap,
                               const int32_t *row_top_p, const int32_t *row_top_k, int top_k, int sink, int window,
                               const float *init_out, const float *init_lse, float scale, uint16_t *out_bf16,
-                              float *lse_out, int flags, void *workspace, size_t workspace_bytes, void *stream) {
+                              float *lse_out, int flags, void *init_ready_event, void *workspace,
+                              size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && k && v && picked && positions && out_bf16 && workspace, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
   LSA_REQUIRE((init_out == nullptr) == (init_lse == nullptr), LSA_ERR_NULL);
@@ -532,6 +533,9 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
       if (rc != LSA_OK) return rc;
     }
   }
+  // init_out / init_lse may be the work of another stream (the dense band running beside the passes above): only
+  // the merge reads them, so only the merge waits.
+  if (init_ready_event && cudaStreamWaitEvent(s, (cudaEvent_t)init_ready_event, 0) != cudaSuccess) return LSA_ERR_LAUNCH;
   lsa::bucket_merge_kernel<128><<<(unsigned)((R * Hq + 7) / 8), 256, 0, s>>>(p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;

@@ -172,8 +172,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float e0 = m_row == -INFINITY ? 0.0f : exp2f(s[c8 * 8 + 2 * j] - m_row);
-            const float e1 = m_row == -INFINITY ? 0.0f : exp2f(s[c8 * 8 + 2 * j + 1] - m_row);
+            const float e0 = m_row == -INFINITY ? 0.0f : fast_exp2(s[c8 * 8 + 2 * j] - m_row);
+            const float e1 = m_row == -INFINITY ? 0.0f : fast_exp2(s[c8 * 8 + 2 * j + 1] - m_row);
             l_row += e0 + e1;
             w[j] = pack_bf16x2(e0, e1);
           }

@@ -77,6 +77,7 @@ class FlatLayer:
         # (S and O in tensor memory) a CTA walks its heads through a chain of dependent hand-overs and measures
         # slower (7.8 ms a chunk of config 2) than the warp-level tiles of 16 rows (3.9 ms), so those are the default.
         self.bucket_tensor_memory = False
+        self._band_stream = self._band_done = None  # the side stream the band runs on beside the bucket-major read
         # bf16 maps run on the tensor cores (the head sum folded into the product); fp32 maps keep the exact form
         self.tensor_cores = tensor_cores and query_map.dtype == torch.bfloat16 and key_map.dtype == torch.bfloat16 \
             and query_map.shape[1] in (32, 64, 128)
@@ -237,10 +238,18 @@ class FlatLayer:
         # The window and the sinks are the same keys for neighbouring rows: one dense band serves them, and the
         # read of the selected keys starts from its partial result.
         banded = band and self.design.sink_size <= 64 and k.shape[0] >= stop
-        init = self.band(rows, k, v, start) if banded else None
         lse = self._buffer("lse", (n, self.heads), torch.float32, dev)
         # (without the band the window and the sinks are in the lists, which only the gather path reads)
         if banded and bucket_major and ops.bucket_attend_supported(rows, k, self.design.bucket_cap):
+            # The band and the read of the selected keys meet only in the merge, and one waits on the tensor pipe
+            # while the other is bound by instruction issue: the band runs on a stream of its own beside them.
+            main = torch.cuda.current_stream(dev)
+            if self._band_stream is None:
+                self._band_stream, self._band_done = torch.cuda.Stream(dev), torch.cuda.Event()
+            self._band_stream.wait_stream(main)  # the inputs are ready; the last chunk's merge has read the buffers
+            with torch.cuda.stream(self._band_stream):
+                init = self.band(rows, k, v, start)
+                self._band_done.record(self._band_stream)
             # The rows of a chunk pick the same buckets over and over: read each bucket's keys once per 128
             # (row, pick) pairs instead of once per pair.
             picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True)
@@ -250,9 +259,10 @@ class FlatLayer:
                 ops.bucket_attend(rows, k, v, picked, positions, index.buckets.bucket_members, self.design.top_k,
                                   self.design.sink_size, self.design.window_size, self.scale, init=init,
                                   row_top_p=row_p, row_top_k=row_k, out=out, lse=lse,
-                                  warp_mma=not self.bucket_tensor_memory,
+                                  warp_mma=not self.bucket_tensor_memory, init_ready=self._band_done,
                                   workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
             return out
+        init = self.band(rows, k, v, start) if banded else None
         lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
         self.attend(rows, k, v, lists, lengths, out=out, lse=lse, init=init)
         return out

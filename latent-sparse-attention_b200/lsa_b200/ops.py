@@ -406,7 +406,8 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
                   members: torch.Tensor, top_k: int, sink: int, window: int, scale: float, init: tuple | None = None,
                   row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
                   out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
-                  workspace: torch.Tensor | None = None, warp_mma: bool = False):
+                  workspace: torch.Tensor | None = None, warp_mma: bool = False,
+                  init_ready: torch.cuda.Event | None = None):
     """Expansion and attention of a prefill chunk bucket by bucket: q [R, Hq, dh] bf16 over the members of each row's
     picked buckets (picked [R, top_p], members ascending in a bucket) inside [sink, position + 1 - window), cut at
     top_k, merged with the partial read `init` = (out fp32, lse). Returns (out [R, Hq, dh] bf16, lse [R, Hq]).
@@ -429,7 +430,8 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
     call("lsa_bucket_attend", ptr(q), R, Hq, dh, q.stride(0), q.stride(1), ptr(k), ptr(v), slots, Hkv, k.stride(0),
          k.stride(1), ptr(picked), top_p, ptr(_contig(positions.to(torch.int64))), ptr(members), members.shape[0],
          members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(init[0]) if init else None,
-         ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), 1 if warp_mma else 0, ptr(workspace),
+         ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), 1 if warp_mma else 0,
+         init_ready.cuda_event if init_ready is not None else None, ptr(workspace),
          workspace.numel() * workspace.element_size(), stream(), launches=6)
     return out, lse
 
