@@ -252,7 +252,7 @@ def run_ours(args, cfg: dict) -> dict:
         layer = ShardedFlatLayer(base, rank, world)
         k_h, v_h = deal(k_h, rank, world).clone().pin_memory(), deal(v_h, rank, world).clone().pin_memory()
         if args.parallel == "rows":
-            q_h = layer.rows_of(q_h, cfg["chunk"]).clone().pin_memory()
+            q_h = layer.rows_of(q_h, cfg["chunk"] * world).clone().pin_memory()
     q, k, v = q_h.cuda(), k_h.cuda(), v_h.cuda()
     out_d = torch.empty(cfg["tokens"] // world, cfg["heads"], cfg["head_dim"], dtype=torch.bfloat16, device="cuda")
     out_h = torch.empty(out_d.shape, dtype=torch.bfloat16).pin_memory()
@@ -281,13 +281,18 @@ def run_ours(args, cfg: dict) -> dict:
 
     def prefill(q_, k_, v_):
         if by_rows:
-            return layer.prefill_by_rows(q_, k_, v_, cfg["tokens"], chunk=cfg["chunk"], out=out_d)
+            # the ranks take a chunk of 8,192 rows each, side by side
+            return layer.prefill_by_rows(q_, k_, v_, cfg["tokens"], chunk=cfg["chunk"] * world, out=out_d)
         return layer.prefill(q_, k_, v_, chunk=cfg["chunk"], out=out_d)
 
     def resident_step():
         prefill(q, k, v)
 
     def e2e_step():
+        if world == 1:
+            # the layer's own call for host-resident inputs: copies in and out overlapped with the chunks' work
+            base.prefill_from_host(q_h, k_h, v_h, out_h, chunk=cfg["chunk"])
+            return
         q_in.copy_(q_h, non_blocking=True)
         k_in.copy_(k_h, non_blocking=True)
         v_in.copy_(v_h, non_blocking=True)

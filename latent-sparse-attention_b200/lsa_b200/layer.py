@@ -78,6 +78,8 @@ class FlatLayer:
         # slower (7.8 ms a chunk of config 2) than the warp-level tiles of 16 rows (3.9 ms), so those are the default.
         self.bucket_tensor_memory = False
         self._band_stream = self._band_done = None  # the side stream the band runs on beside the bucket-major read
+        self._copy_in = self._copy_out = None       # the copy streams of `prefill_from_host`
+        self._copy_events: list = []
         # bf16 maps run on the tensor cores (the head sum folded into the product); fp32 maps keep the exact form
         self.tensor_cores = tensor_cores and query_map.dtype == torch.bfloat16 and key_map.dtype == torch.bfloat16 \
             and query_map.shape[1] in (32, 64, 128)
@@ -224,6 +226,46 @@ class FlatLayer:
             stop = min(T, start + chunk)
             self.prefill_rows(q[start:stop], start, k, v, index, out[start:stop], band, bucket_major)
         return (out, index) if return_index else out
+
+    def prefill_from_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
+                          out_host: torch.Tensor, chunk: int = 8192) -> torch.Tensor:
+        """`prefill` for inputs and an output that live in PINNED host memory, the copies overlapped with the work:
+        K and V cross first (the index needs them), the query chunks follow on a copy stream while earlier chunks
+        are read, and every chunk's output leaves on a second copy stream as soon as its merge is done. On return
+        the current stream has waited for the last output copy; synchronise it before reading `out_host`."""
+        dev = self.query_map.device
+        T = q_host.shape[0]
+        main = torch.cuda.current_stream(dev)
+        if self._copy_in is None:
+            self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        chunks = [(start, min(T, start + chunk)) for start in range(0, T, chunk)]
+        while len(self._copy_events) < 2 * len(chunks) + 1:
+            self._copy_events.append(torch.cuda.Event())
+        kv_ready, arrived, done = self._copy_events[0], self._copy_events[1::2], self._copy_events[2::2]
+        q = self._buffer("q from host", tuple(q_host.shape), q_host.dtype, dev)
+        k = self._buffer("k from host", tuple(k_host.shape), k_host.dtype, dev)
+        v = self._buffer("v from host", tuple(v_host.shape), v_host.dtype, dev)
+        out = self._buffer("out to host", tuple(q_host.shape), torch.bfloat16, dev)
+        self._copy_in.wait_stream(main)   # the last call's reads of these buffers are over
+        self._copy_out.wait_stream(main)
+        with torch.cuda.stream(self._copy_in):
+            k.copy_(k_host, non_blocking=True)
+            v.copy_(v_host, non_blocking=True)
+            kv_ready.record(self._copy_in)
+            for c, (start, stop) in enumerate(chunks):
+                q[start:stop].copy_(q_host[start:stop], non_blocking=True)
+                arrived[c].record(self._copy_in)
+        main.wait_event(kv_ready)
+        index = self.build_index(k, reuse_buffers=True)
+        for c, (start, stop) in enumerate(chunks):
+            main.wait_event(arrived[c])
+            self.prefill_rows(q[start:stop], start, k, v, index, out[start:stop])
+            done[c].record(main)
+            with torch.cuda.stream(self._copy_out):
+                self._copy_out.wait_event(done[c])
+                out_host[start:stop].copy_(out[start:stop], non_blocking=True)
+        main.wait_stream(self._copy_out)
+        return out_host
 
     def prefill_rows(self, rows: torch.Tensor, start: int, k: torch.Tensor, v: torch.Tensor, index: FlatIndex,
                      out: torch.Tensor, band: bool = True, bucket_major: bool = True) -> torch.Tensor:

@@ -2,7 +2,7 @@
 
 Run where the reference is mounted (it is imported in place, never copied):
 
-    python tests/golden/make_golden.py /root/reference/src
+    python tests/golden/make_golden.py <checkout of the reference>/src
 
 Each `.npz` holds the inputs and what the reference returned for them, so the tests need neither the reference
 nor torch's random streams. The constructions follow the reference's own unit tests
@@ -211,4 +211,6 @@ def main(src):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference>/src")
+    main(sys.argv[1])

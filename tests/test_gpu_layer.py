@@ -78,3 +78,20 @@ def test_a_decode_step_matches_its_prefill_row(oracle):
     for splits in (1, 4):
         step = layer.decode(Q[rows], rows, K, V, index, splits=splits)
         assert (step.float() - out[rows].float()).abs().max() <= 1e-2
+
+
+def test_prefill_from_pinned_host_memory_is_the_resident_prefill():
+    from lsa_b200.layer import FlatDesign
+
+    design = FlatDesign(pool_size=16, bucket_size=32, bucket_cap=64, cluster_block_size=1024, top_p=16, top_k=1024,
+                        sink_size=4, window_size=1024)
+    T, Hq, Hkv, dh = 6144 + 300, 40, 8, 128
+    layer, _ = _layer(Hq, Hkv, dh, 64, design, 9)
+    q, k, v = (torch.from_numpy(a).bfloat16().pin_memory() for a in layer_inputs(T, Hq, Hkv, dh, 32, 10))
+    want = layer.prefill(q.cuda(), k.cuda(), v.cuda(), chunk=2048)
+    out = torch.empty(T, Hq, dh, dtype=torch.bfloat16).pin_memory()
+    for _ in range(2):  # the second call reuses the buffers, streams and events of the first
+        out.zero_()
+        layer.prefill_from_host(q, k, v, out, chunk=2048)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(out, want.cpu())
