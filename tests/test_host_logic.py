@@ -83,3 +83,27 @@ def test_regions_cost_nothing_until_a_recorder_listens():
         pass
     probe.uninstall()
     assert seen == ["select"]
+
+
+def test_the_rows_a_rank_keeps_partition_every_chunk():
+    from types import SimpleNamespace
+
+    from lsa_b200.parallel import ShardedFlatLayer, deal, undeal
+
+    tokens, chunk, world = 4096, 1024, 4
+    rows = torch.arange(tokens)[:, None].expand(tokens, 3)
+    kept = []
+    for rank in range(world):
+        sharded = ShardedFlatLayer(SimpleNamespace(design=None), rank, world)
+        mine = sharded.rows_of(rows, chunk)
+        assert mine.shape == (tokens // world, 3)
+        share = chunk // world
+        want = torch.cat([torch.arange(c * chunk + rank * share, c * chunk + (rank + 1) * share)
+                          for c in range(tokens // chunk)])
+        assert torch.equal(mine[:, 0], want)
+        kept.append(mine[:, 0])
+    assert torch.equal(torch.cat(kept).sort().values, torch.arange(tokens))
+    # the dealt cache and its inverse: granules of 64 positions round-robin over the ranks
+    dealt = torch.stack([deal(rows, rank, world) for rank in range(world)])
+    assert dealt[1, :64, 0].tolist() == list(range(64, 128)) and dealt[1, 64, 0] == 64 + 64 * world
+    assert torch.equal(undeal(dealt), rows)
