@@ -90,6 +90,84 @@ __device__ int warp_compact(int64_t *buf, int from, int to, int out, Pred keep) 
   return out;
 }
 
+// The same threshold found by a whole CTA of kSelThreads threads (a decode row has the CTA to itself): every
+// thread counts into one shared histogram, warp 0 picks the bin, the pick is broadcast through shared memory.
+__device__ uint64_t block_kth_greatest(const int64_t *buf, int n, int k, int *hist, int *pick) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint64_t prefix = 0, mask = 0;
+  int remaining = k;
+  for (int byte = 7; byte >= 0; --byte) {
+    const int shift = byte * 8;
+    hist[tid] = 0;  // kSelThreads == kHistBins
+    __syncthreads();
+    for (int i = tid; i < n; i += kSelThreads) {
+      const uint64_t u = key_radix(buf[i]);
+      if ((u & mask) == prefix) atomicAdd(&hist[(int)((u >> shift) & 0xFF)], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int own[kHistBins / 32];
+      int own_sum = 0;
+#pragma unroll
+      for (int i = 0; i < kHistBins / 32; ++i) {
+        own[i] = hist[lane * (kHistBins / 32) + i];
+        own_sum += own[i];
+      }
+      int above = own_sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int other = __shfl_down_sync(0xffffffffu, above, o);
+        if (lane + o < 32) above += other;
+      }
+      above -= own_sum;
+      if (above < remaining && above + own_sum >= remaining) {
+        int seen = above;
+#pragma unroll
+        for (int i = kHistBins / 32 - 1; i >= 0; --i) {
+          if (seen < remaining && seen + own[i] >= remaining) {
+            pick[0] = lane * (kHistBins / 32) + i;  // the digit
+            pick[1] = remaining - seen;              // keys still wanted inside its bin
+            pick[2] = own[i];                        // keys in the bin
+          }
+          seen += own[i];
+        }
+      }
+    }
+    __syncthreads();
+    const int digit = pick[0];
+    remaining = pick[1];
+    const int in_bin = pick[2];
+    prefix |= (uint64_t)digit << shift;
+    mask |= (uint64_t)0xFF << shift;
+    __syncthreads();  // the pick and the histogram are read before the next pass rewrites them
+    if (in_bin == remaining) break;
+  }
+  return prefix;
+}
+
+// Keep the entries of buf[from..to) that pass `keep(key)` at buf[out..), in any order, with the whole CTA; returns
+// the new end. Every thread first takes its entries into registers, so the source and the target may overlap.
+constexpr int kBlockCompactPerThread = 12;  // up to 3,072 entries
+template <typename Pred>
+__device__ int block_compact(int64_t *buf, int from, int to, int out, int *counter, Pred keep) {
+  int64_t mine[kBlockCompactPerThread];
+#pragma unroll
+  for (int i = 0; i < kBlockCompactPerThread; ++i) {
+    const int at = from + (int)threadIdx.x + i * kSelThreads;
+    mine[i] = at < to ? buf[at] : kEmptyKey;
+    if (at >= to || !keep(mine[i])) mine[i] = kEmptyKey;
+  }
+  if (threadIdx.x == 0) *counter = out;
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kBlockCompactPerThread; ++i)
+    if (mine[i] != kEmptyKey) buf[atomicAdd(counter, 1)] = mine[i];
+  __syncthreads();
+  const int end = *counter;
+  __syncthreads();
+  return end;
+}
+
 // Sort buf[0..n) descending in place with one warp; buf has room for the next power of two of n.
 __device__ void warp_sort_descending(int64_t *buf, int n) {
   const int lane = lane_id();
@@ -180,6 +258,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   int64_t floor_key = kEmptyKey;  // a new key must beat this once the row holds its keep
   const int64_t my_row = row0 + warp;
   const int my_keep = (warp < RB && my_row < p.R) ? (p.row_keep ? min(p.row_keep[my_row], p.keep) : p.keep) : 0;
+  // (a single row: every thread of the CTA carries the row's state, which stays the same in all of them)
+  const int my_keep_all = (RB == 1 && row0 < p.R) ? (p.row_keep ? min(p.row_keep[row0], p.keep) : p.keep) : 0;
+  __shared__ int block_counter, block_pick[3];
 
   for (int chunk_base = cand_begin; chunk_base < cand_end; chunk_base += p.chunk) {
     const int chunk_n = min(p.chunk, cand_end - chunk_base);
@@ -248,6 +329,24 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
         bufs[(size_t)i * row_room + keep_room + t] = ids[i] >= 0 ? pack_key(acc[i], ids[i] + p.id_base) : kEmptyKey;
     }
     __syncthreads();
+    // ---- select: a row that has the CTA to itself is folded by all of its threads (the keys are distinct and the
+    // final sort orders them, so the order they are kept in does not matter)
+    if (RB == 1 && row_room <= kBlockCompactPerThread * kSelThreads) {
+      if (my_keep_all > 0) {
+        int64_t *buf = bufs;
+        const int64_t floor_now = floor_key;
+        int n = block_compact(buf, keep_room, keep_room + chunk_n, held, &block_counter,
+                              [floor_now](int64_t key) { return key > floor_now; });
+        if (n > my_keep_all) {
+          const uint64_t kth = block_kth_greatest(buf, n, my_keep_all, hists, block_pick);
+          n = block_compact(buf, 0, n, 0, &block_counter, [kth](int64_t key) { return key_radix(key) >= kth; });
+          floor_key = (int64_t)(kth ^ 0x8000000000000000ull);
+        }
+        held = n;
+      }
+      __syncthreads();
+      continue;
+    }
     // ---- select: the row's warp folds the chunk into what it holds
     if (warp < RB && my_keep > 0) {
       int64_t *buf = bufs + (size_t)warp * row_room;
@@ -287,7 +386,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
 }
 
 // Global top-k of `parts` lists of packed keys, a warp a row.
-__global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__restrict__ keys_in, int parts,
+__global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int64_t *__restrict__ keys_in, int parts,
                                                               int64_t R, int keep, int room,
                                                               int64_t *__restrict__ keys_out,
                                                               int32_t *__restrict__ ids_out,
@@ -299,19 +398,34 @@ __global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__r
   const int lane = lane_id();
   const int64_t r = blockIdx.x;
   int n = 0;
-  for (int base = 0; base < parts * keep; base += 32) {
-    const int e = base + lane;
-    int64_t key = kEmptyKey;
-    if (e < parts * keep) key = keys_in[((int64_t)(e / keep) * R + r) * keep + e % keep];
-    const bool pass = key != kEmptyKey;
-    const unsigned votes = __ballot_sync(0xffffffffu, pass);
-    if (pass) buf[n + __popc(votes & ((1u << lane) - 1))] = key;
-    n += __popc(votes);
-  }
-  __syncwarp();
-  if (n > keep) {
-    const uint64_t kth = warp_kth_greatest(buf, n, keep, hist);
-    n = warp_compact(buf, 0, n, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+  if (blockDim.x == kSelThreads) {
+    // many candidates (a row split over dozens of CTAs): the whole CTA cuts them to `keep`, warp 0 sorts and writes
+    __shared__ int counter, pick[3];
+    const int total = parts * keep;
+    for (int e = threadIdx.x; e < total; e += kSelThreads)
+      buf[e] = keys_in[((int64_t)(e / keep) * R + r) * keep + e % keep];
+    __syncthreads();
+    n = block_compact(buf, 0, total, 0, &counter, [](int64_t key) { return key != kEmptyKey; });
+    if (n > keep) {
+      const uint64_t kth = block_kth_greatest(buf, n, keep, hist, pick);
+      n = block_compact(buf, 0, n, 0, &counter, [kth](int64_t key) { return key_radix(key) >= kth; });
+    }
+    if (threadIdx.x >= 32) return;
+  } else {
+    for (int base = 0; base < parts * keep; base += 32) {
+      const int e = base + lane;
+      int64_t key = kEmptyKey;
+      if (e < parts * keep) key = keys_in[((int64_t)(e / keep) * R + r) * keep + e % keep];
+      const bool pass = key != kEmptyKey;
+      const unsigned votes = __ballot_sync(0xffffffffu, pass);
+      if (pass) buf[n + __popc(votes & ((1u << lane) - 1))] = key;
+      n += __popc(votes);
+    }
+    __syncwarp();
+    if (n > keep) {
+      const uint64_t kth = warp_kth_greatest(buf, n, keep, hist);
+      n = warp_compact(buf, 0, n, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+    }
   }
   warp_sort_descending(buf, n);
   for (int i = lane; i < keep; i += 32) {
@@ -326,6 +440,12 @@ __global__ void __launch_bounds__(32) merge_candidates_kernel(const int64_t *__r
       carried_out[r * keep * fanout + e] = i < n ? (int32_t)children[(int64_t)key_id(buf[i]) * fanout + c] : LSA_PAD;
     }
   }
+}
+
+// Threads of a candidate merge: a warp for a few hundred candidates, the whole CTA for what its registers can hold.
+static int merge_threads(int parts, int keep) {
+  const int64_t total = (int64_t)parts * keep;
+  return total > 256 && total <= kBlockCompactPerThread * kSelThreads ? kSelThreads : 32;
 }
 
 static int pow2_at_least(int n) {
@@ -532,7 +652,7 @@ LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, i
   if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  lsa::merge_candidates_kernel<<<(unsigned)R, 32, smem, (cudaStream_t)stream>>>(keys_in, parts, R, top_p, room,
+  lsa::merge_candidates_kernel<<<(unsigned)R, lsa::merge_threads(parts, top_p), smem, (cudaStream_t)stream>>>(keys_in, parts, R, top_p, room,
                                                                                 keys_out, picked_out, nullptr, 0,
                                                                                 nullptr);
   LSA_LAUNCH_CHECK();
@@ -682,7 +802,7 @@ LSA_API int lsa_beam_step_split(const float *queries, int64_t R, int d, const fl
   if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  lsa::merge_candidates_kernel<<<(unsigned)R, 32, smem, (cudaStream_t)stream>>>(
+  lsa::merge_candidates_kernel<<<(unsigned)R, lsa::merge_threads(splits, keep), smem, (cudaStream_t)stream>>>(
       (const int64_t *)workspace, splits, R, keep, room, keys_out, kept_out, children, fanout, carried_out);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
