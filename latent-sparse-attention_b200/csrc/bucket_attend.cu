@@ -132,8 +132,10 @@ __global__ void __launch_bounds__(256) bucket_segments_kernel(BucketParams p) {
 // ---------------------------------------------------------------------------------------------- attend
 
 // grid (segment bound, Hkv); blockDim = group * 32: warp w serves query head h * group + w.
+// Occupancy decides this kernel. At 96 registers and one query buffer a warp, four CTAs of five warps share an SM
+// (66 ms a step of 16 chunks); at 128 registers and two buffers three did (71 ms); uncapped, one did (125 ms).
 template <int DH>
-__global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
+__global__ void __maxnreg__(96) bucket_attend_kernel(BucketParams p) {
   constexpr int ROW_BYTES = DH * 2;
   constexpr int CHUNKS = ROW_BYTES / 16;
   constexpr int KV_BYTES = kBktKeys * ROW_BYTES;   // one of K or V
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
   // The bucket's keys and values of this KV head, staged once (rows of ids outside the cache are zero-filled and
   // never valid: a pair's range only holds ids the starts pass counted).
   const uint32_t k_s = smem_u32(smem_raw), v_s = k_s + KV_BYTES;
-  const uint32_t q_s = v_s + KV_BYTES + warp * 2 * Q_BYTES;  // two tiles a warp: the next one loads under this one
+  const uint32_t q_s = v_s + KV_BYTES + warp * Q_BYTES;  // a tile a warp: four CTAs share an SM instead of three
   {
     const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride, *v_head = p.v + (int64_t)h * p.kv_head_stride;
     for (int e = tid; e < kBktKeys * CHUNKS; e += blockDim.x) {
@@ -193,7 +195,7 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
   // Start the copies of a tile's 16 query rows of this warp's head.
   auto issue_q = [&](int tile) {
     if (tile < tiles) {
-      const uint32_t dst0 = q_s + (tile & 1) * Q_BYTES;
+      const uint32_t dst0 = q_s;
       for (int e = lane; e < kBktTile * CHUNKS; e += 32) {
         const int row = e / CHUNKS, chunk = e - row * CHUNKS;
         const bool ok = pairs_s[tile * kBktTile + row] >= 0;
@@ -222,11 +224,11 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
     hi_s[i] = pairs_s[i] >= 0 ? min(members_below(until_s[i]), below_sink + allow_s[i]) : 0;
 
   for (int tile = 0; tile < tiles; ++tile) {
-    __syncwarp();  // the warp is done with the tile before last, whose buffer the next copies fill
-    issue_q(tile + 1);
-    cp_async_wait<1>();
+    __syncwarp();  // the warp has sent the last tile's outputs, which were staged in this buffer
+    if (tile > 0) issue_q(tile);
+    cp_async_wait<0>();
     if (tile == 0) __syncthreads(); else __syncwarp();  // the first wait also covers the bucket's K/V and the ranges
-    const uint32_t q_tile = q_s + (tile & 1) * Q_BYTES;
+    const uint32_t q_tile = q_s;
 
     // the key range of rows g and g + 8 of the tile
     int lo_key[2], hi_key[2];
@@ -311,36 +313,42 @@ __global__ void __launch_bounds__(256, 2) bucket_attend_kernel(BucketParams p) {
       pa[nt >> 1][(nt & 1) * 2] = live ? pack_bf16x2(s[nt][0] * inv[0], s[nt][1] * inv[0]) : 0u;
       pa[nt >> 1][(nt & 1) * 2 + 1] = live ? pack_bf16x2(s[nt][2] * inv[1], s[nt][3] * inv[1]) : 0u;
     }
-    // O [16 rows x DH] = P V
-    float o[DH / 8][4];
+    // O [16 rows x DH] = P V, one half of the head dim at a time: 32 accumulators live instead of 64. Each half is
+    // staged in the tile's query buffer (the first product is done with it), so the rows leave in 16-byte pieces.
 #pragma unroll
-    for (int nt = 0; nt < DH / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+    for (int half = 0; half < 2; ++half) {
+      float o[DH / 16][4];
 #pragma unroll
-    for (int ks = 0; ks < kBktKeys / 16; ++ks) {
-      if (ks >= key_steps) continue;
+      for (int nt = 0; nt < DH / 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
 #pragma unroll
-      for (int np = 0; np < DH / 16; ++np) {
-        const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), chunk = np * 2 + (lane >> 4);
-        uint32_t b0, b1, b2, b3;
-        ldmatrix_x4_trans(v_s + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
-        mma_bf16(o[2 * np], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
-        mma_bf16(o[2 * np + 1], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b2, b3);
+      for (int ks = 0; ks < kBktKeys / 16; ++ks) {
+        if (ks >= key_steps) continue;
+#pragma unroll
+        for (int np = 0; np < DH / 32; ++np) {
+          const int row = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+          const int chunk = (half * (DH / 32) + np) * 2 + (lane >> 4);
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(v_s + row * ROW_BYTES + ((chunk ^ (row & 7)) << 4), b0, b1, b2, b3);
+          mma_bf16(o[2 * np], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b0, b1);
+          mma_bf16(o[2 * np + 1], pa[ks][0], pa[ks][1], pa[ks][2], pa[ks][3], b2, b3);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (pair_of[j] < 0) continue;
+        const int row = g + 8 * j;
+#pragma unroll
+        for (int nt = 0; nt < DH / 16; ++nt) {
+          const uint32_t at = row * ROW_BYTES + (((half * (DH / 16) + nt) ^ (row & 7)) << 4) + 4 * t;
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(q_tile + at), "r"(pack_bf16x2(o[nt][2 * j], o[nt][2 * j + 1])));
+        }
       }
     }
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      if (pair_of[j] < 0) continue;
-      const int64_t slot = (int64_t)pair_of[j] * p.Hq + head;
-      if (t == 0)
-        p.part_lse[slot] = l_row[j] > 0.0f ? (m_row[j] + log2f(l_row[j])) * 0.6931471805599453f : -INFINITY;
-      // staged in the tile's query buffer (the products are done with it), so the rows leave in whole 16-byte pieces
-      const int row = g + 8 * j;
-#pragma unroll
-      for (int nt = 0; nt < DH / 8; ++nt) {
-        const uint32_t at = row * ROW_BYTES + ((nt ^ (row & 7)) << 4) + 4 * t;
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(q_tile + at),
-                     "r"(pack_bf16x2(o[nt][2 * j], o[nt][2 * j + 1])));
-      }
+      if (pair_of[j] < 0 || t != 0) continue;
+      p.part_lse[(int64_t)pair_of[j] * p.Hq + head] =
+          l_row[j] > 0.0f ? (m_row[j] + log2f(l_row[j])) * 0.6931471805599453f : -INFINITY;
     }
     __syncwarp();
     for (int e = lane; e < kBktTile * CHUNKS; e += 32) {
@@ -521,7 +529,7 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
     LSA_LAUNCH_CHECK();
     const int64_t bound = lsa::segment_bound(R, top_p, m);
     if (flags & LSA_BUCKET_WARP_MMA) {
-      const size_t smem = 2 * (size_t)lsa::kBktKeys * dh * 2 + 2 * (size_t)p.group * lsa::kBktTile * dh * 2;
+      const size_t smem = 2 * (size_t)lsa::kBktKeys * dh * 2 + (size_t)p.group * lsa::kBktTile * dh * 2;
       if (cudaFuncSetAttribute(lsa::bucket_attend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)smem) != cudaSuccess)
         return LSA_ERR_LAUNCH;
