@@ -242,6 +242,7 @@ def run_ours(args, cfg: dict) -> dict:
     host = make_inputs(cfg, pin=True)
     q_h, k_h, v_h, wq, wk = host
     base = FlatLayer(design_of(cfg), wq.cuda(), wk.cuda(), cfg["heads"], cfg["kv_heads"], cfg["head_dim"])
+    base.bucket_tensor_memory = args.bucket_kernel == "tensor-memory"
     layer = base
     if world > 1:
         from lsa_b200.parallel import ShardedFlatLayer, deal
@@ -349,7 +350,7 @@ def run_ours(args, cfg: dict) -> dict:
         "config": {"workload": cfg["workload"], "tokens": tokens, "heads": cfg["heads"], "kv_heads": cfg["kv_heads"],
                    "head_dim": cfg["head_dim"], "index_dim": cfg["index_dim"], "buckets": tokens // cfg["bucket_size"],
                    "top_p": cfg["top_p"], "top_k": cfg["top_k"], "window": cfg["window_size"],
-                   "sink": cfg["sink_size"], "chunk": cfg["chunk"],
+                   "sink": cfg["sink_size"], "chunk": cfg["chunk"], "bucket_kernel": args.bucket_kernel,
                    "l2": "inputs (1.9 GB of q, k, v per step) exceed the 126 MB L2",
                    "parallelism": "1 GPU" if world == 1 else (
                        f"KV rows and cluster blocks dealt round-robin over {world} GPUs; " + (
@@ -425,6 +426,8 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=None, help="a smaller context of the same workload (profiling)")
+    parser.add_argument("--bucket-kernel", default="warp", choices=["warp", "tensor-memory"],
+                        help="the form of the bucket-major attend pass: warp-level MMA tiles or tcgen05 tiles in tensor memory")
     parser.add_argument("--parallel", default="rows", choices=["rows", "context"],
                         help="at N > 1: split the query rows over the ranks (the cache is all-gathered once a step), "
                              "or keep every rank on the keys it stores and merge partial outputs")

@@ -1,48 +1,73 @@
 // The attend pass of the bucket-major attention on the fifth-generation tensor cores.
 //
-// A CTA owns (bucket, KV head, segment of up to 128 (row, pick) pairs) and takes the query heads of the KV head's
-// group one after the other. The pairs are the M = 128 rows of both products, so a row of S and of O lives in one
-// lane of tensor memory and the thread that owns the row does its softmax without talking to anyone:
+// A CTA owns (bucket, KV head, segment of up to 128 (row, pick) pairs). The M = 128 rows of a tile are (pair, query
+// head of the KV head's group) couples, the heads of a pair next to one another, so a ragged segment of n pairs
+// costs ceil(n * group / 128) tiles and not `group` of them. A row of S and of O lives in one lane of tensor memory
+// and the thread that owns the row does its softmax without talking to anyone:
 //
-//   S [128 x keys]  = Q_head [128 x 128] . K^T      tcgen05.mma, A = the pairs' query rows, B = the bucket's keys,
+//   S [128 x keys]  = Q [128 x 128] . K^T           tcgen05.mma, A = the tile's query rows, B = the bucket's keys,
 //                                                   both K-major planes of 64 dims with the 128-byte swizzle
-//   P               = exp2(S - rowmax) on the row's key range, bf16, written back to shared memory
+//   P               = exp2(S - rowmax) / rowsum on the row's key range, bf16, written back to shared memory
 //   O [128 x 128]   = P [128 x keys] . V            A = P (K-major), B = the bucket's values AS STORED
 //                                                   ([key][dim] planes: an MN-major operand)
 //
 //   warp 0          tensor-memory allocation; one lane issues the MMAs
-//   warps 1-4       thread = row: asynchronous copy of its query row (the next head's while this head computes),
-//                   softmax, normalised bf16 partial output and log-sum-exp
+//   warps 1-8       workers. Together they gather the query rows of the tile after next (a row of 256 bytes a half
+//                   warp) and send the finished tile's rows out in the same shape. For the softmax and the unloading
+//                   of O a row has TWO threads, one in warp 1 + q and one in warp 5 + q (both may read the tensor-
+//                   memory lanes of quarter q): they take alternate groups of 8 keys of S, swap their maxima and
+//                   sums through shared memory, and take a half of O's columns each. The row's instruction stream
+//                   is what bounds this kernel, so it is cut in two.
+//
+// The tiles of a CTA overlap: the tensor cores multiply S of tile i + 1 while the workers unload O of tile i, and
+// the query rows of tile i + 2 are on their way by then. Two CTAs share an SM and fill one another's waits.
 //
 // Shared-memory operands are written by ordinary and asynchronous copies (the generic proxy), so a proxy fence stands
 // before every hand-over to the tensor cores. Every wait on an mbarrier is bounded; a wait that gives up raises the
-// CTA's abort flag, the CTA skips its remaining work, frees its tensor memory and leaves.
+// CTA's abort flag, the CTA skips its remaining work (but none of its barriers), frees its tensor memory and leaves.
 #include "bucket_attend.cuh"
 #include "mma.cuh"
 #include "umma.cuh"
 
 namespace lsa {
 
-constexpr int kTcThreads = 160;
-constexpr int kTcRows = 128;                    // pairs a CTA holds: kBktSegment
+constexpr int kTcThreads = 288;
+constexpr int kTcWorkers = 256;
+constexpr int kTcRows = 128;                    // rows of a tile
 constexpr int kTcPlane = 64 * 128;              // a plane of 64 rows x 128 bytes (keys or values, 64 dims)
 constexpr int kTcQPlane = kTcRows * 128;        // a plane of the query tile or of P
 constexpr int kTcKOff = 0;                      // K: 2 planes
 constexpr int kTcVOff = 2 * kTcPlane;           // V: 2 planes
 constexpr int kTcQOff = 4 * kTcPlane;           // Q: 2 buffers of 2 planes
-// P takes the first plane of the head's own query buffer: the first product is over when P is written
+// P takes the first plane of the tile's own query buffer (the first product is over when P is written), and the
+// finished rows of O are staged in the whole of it (the second product is over by then).
 constexpr int kTcSmem = kTcQOff + 4 * kTcQPlane + 1024;  // + room to align the base to 1,024 bytes
 constexpr int kTcTmemCols = 256;                // S in columns 0-63, O in 64-191
 static_assert(kBktSegment == kTcRows && kBktKeys == 64, "the tile shapes of the tensor-core attend pass");
 
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTcWorkers) : "memory"); }
+// the two warps of a quarter of the rows
+__device__ __forceinline__ void quarter_sync(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory"); }
+
 
 template <int DH>
 __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketParams p) {
   static_assert(DH == 128, "two planes of 64 dims");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int32_t ids_s[kBktKeys];
-  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int32_t pairs_s[kBktSegment];   // the segment's pairs, -1 past its end
+  __shared__ int32_t qrows_s[kBktSegment];   // their query rows
+  __shared__ int32_t hi_s[kBktSegment];      // end of their index range of the bucket's members
+  // of the rows of a tile (a ring of three tiles): where the query row starts in q (-1 past the end), which slot of
+  // the partial outputs it fills, and the end of its key range
+  __shared__ int64_t src_s[3][kTcRows], dst_s[3][kTcRows];
+  __shared__ int32_t end_s[3][kTcRows];
+  __shared__ float swap_max_s[2][kTcRows], swap_sum_s[2][kTcRows];
+  __shared__ __align__(8) uint64_t bars[3];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
 
@@ -53,10 +78,14 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   const int4 info = p.segments[seg];
   const int64_t bucket = info.x;
   const int first = info.y, n_pairs = info.z;
+  const int n_rows = n_pairs * p.group;
+  const int n_tiles = (n_rows + kTcRows - 1) / kTcRows;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_s = smem_u32(&bars[0]), bar_o = smem_u32(&bars[1]);
+  // bar_w: the workers tell the MMA lane that operands are in place; bar_s / bar_o: a product has finished
+  const uint32_t bar_w = smem_u32(&bars[0]), bar_s = smem_u32(&bars[1]), bar_o = smem_u32(&bars[2]);
 
   if (tid == 0) {
+    mbar_init(bar_w, kTcWorkers);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     abort_s = 0;
@@ -73,159 +102,236 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
 
-  // The bucket's keys and values of this KV head: chunk c of member j goes to plane c / 8, row j, 16-byte slot
-  // (c % 8) ^ (j % 8) - the layout a tensor-map copy with the 128-byte swizzle would write.
+  // members of the bucket: the ids before the first pad
+  int n_members;
   {
-    const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride, *v_head = p.v + (int64_t)h * p.kv_head_stride;
-    for (int e = tid; e < kBktKeys * 16; e += kTcThreads) {
-      const int row = e >> 4, chunk = e & 15;
-      const int32_t id = ids_s[row];
-      const bool ok = id >= 0 && id < p.slots;
-      const int64_t off = ok ? (int64_t)id * p.kv_row_stride + chunk * 8 : 0;
-      const uint32_t dst = (chunk >> 3) * kTcPlane + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-      cp_async_16(base + kTcKOff + dst, k_head + off, ok ? 16 : 0);
-      cp_async_16(base + kTcVOff + dst, v_head + off, ok ? 16 : 0);
-    }
+    const unsigned low = __ballot_sync(0xffffffffu, ids_s[lane] >= 0),
+                   high = __ballot_sync(0xffffffffu, ids_s[lane + 32] >= 0);
+    n_members = low != 0xffffffffu ? __ffs(~low) - 1 : (high != 0xffffffffu ? 32 + __ffs(~high) - 1 : 64);
+    n_members = min(n_members, p.cap);
   }
-  int n_members = 0;
-  while (n_members < p.cap && n_members < kBktKeys && ids_s[n_members] >= 0) ++n_members;
-  auto members_below = [&](int64_t bound) {
-    int lo = 0, hi = n_members;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (ids_s[mid] < bound) lo = mid + 1; else hi = mid;
-    }
-    return lo;
-  };
   const int n_keys = max(16, (n_members + 15) & ~15);  // the N of S and the K of O: whole 16-key steps
 
-  // A worker thread is a row: TMEM lane 32 * (warp % 4) + lane is what its warp may read.
-  const bool worker = warp >= 1;
-  const int row = (warp & 3) * 32 + lane;
-  int32_t pair = -1;
-  int64_t q_row = 0;
-  int lo_key = 0, hi_key = 0;
-  if (worker && row < n_pairs) {
-    pair = p.order[first + row];
-    q_row = pair / p.top_p;
-    const int64_t pos = p.positions[q_row];
-    const int row_k = p.row_top_k ? min(p.row_top_k[q_row], p.top_k) : p.top_k;
-    lo_key = members_below(p.sink);
-    hi_key = min(members_below(max((int64_t)0, pos + 1 - p.window)), lo_key + row_k - p.starts[pair]);
-  }
-  // Start the copy of this row's query vector of head `hq` into buffer hq % 2 (zero-filled past the segment).
-  auto issue_q = [&](int hq) {
-    if (worker && hq < p.group) {
-      const uint16_t *src = p.q + q_row * p.q_row_stride + (int64_t)(h * p.group + hq) * p.q_head_stride;
-      const uint32_t dst0 = base + kTcQOff + (hq & 1) * 2 * kTcQPlane + row * 128;
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------ the MMA lane
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc(n_keys), idesc_o = umma_idesc(DH, true);
+      for (int k = 0; k <= n_tiles; ++k) {
+        if (abort_s || !mbar_wait(bar_w, k & 1)) {
+          abort_s = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (k >= 1) {  // O of tile k - 1 = P V: 16 keys are 32 bytes along P's rows, 16 rows (2,048 bytes) down V's planes
+          const uint32_t p_buf = base + kTcQOff + ((k - 1) & 1) * 2 * kTcQPlane;
+          for (int s = 0; s < n_keys / 16; ++s)
+            umma_bf16(tmem_base + 64, smem_desc_sw128(p_buf) + 2 * s,
+                      smem_desc_mn_sw128(base + kTcVOff + s * 2048, kTcPlane), idesc_o, s != 0);
+          umma_commit(bar_o);
+        }
+        if (k < n_tiles) {  // S of tile k = Q K^T: 16 dims are 32 bytes further inside the swizzle atom
+          const uint32_t q_buf = base + kTcQOff + (k & 1) * 2 * kTcQPlane;
 #pragma unroll
-      for (int chunk = 0; chunk < 16; ++chunk)
-        cp_async_16(dst0 + (chunk >> 3) * kTcQPlane + (((chunk & 7) ^ (row & 7)) << 4), src + chunk * 8,
-                    pair >= 0 ? 16 : 0);
+          for (int plane = 0; plane < 2; ++plane)
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+              umma_bf16(tmem_base, smem_desc_sw128(q_buf + plane * kTcQPlane) + 2 * s,
+                        smem_desc_sw128(base + kTcKOff + plane * kTcPlane) + 2 * s, idesc_s, (plane | s) != 0);
+          umma_commit(bar_s);
+        }
+      }
     }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------------------------------ the workers
+    const int w = tid - 32;                    // the thread's place in the shared copies
+    const int quarter = warp & 3;              // the 32 tensor-memory lanes this warp may read
+    const int half = (warp - 1) >> 2;          // which of the row's two threads
+    const int row = quarter * 32 + lane;       // the tile row (= tensor-memory lane)
+    auto members_below = [&](int64_t bound) {
+      int lo = 0, hi = n_members;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (ids_s[mid] < bound) lo = mid + 1; else hi = mid;
+      }
+      return lo;
+    };
+    const int lo_key = members_below(p.sink);
+    // The bucket's keys and values of this KV head: chunk c of member j goes to plane c / 8, row j, 16-byte slot
+    // (c % 8) ^ (j % 8) - the layout a tensor-map copy with the 128-byte swizzle would write.
+    {
+      const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride, *v_head = p.v + (int64_t)h * p.kv_head_stride;
+#pragma unroll
+      for (int e = w; e < kBktKeys * 16; e += kTcWorkers) {
+        const int r = e >> 4, chunk = e & 15;
+        const int32_t id = ids_s[r];
+        const bool ok = id >= 0 && id < p.slots;
+        const int64_t off = ok ? (int64_t)id * p.kv_row_stride + chunk * 8 : 0;
+        const uint32_t dst = (chunk >> 3) * kTcPlane + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+        cp_async_16(base + kTcKOff + dst, k_head + off, ok ? 16 : 0);
+        cp_async_16(base + kTcVOff + dst, v_head + off, ok ? 16 : 0);
+      }
+    }
+    if (w < kBktSegment) {
+      int32_t pair = -1, q_row = 0, hi = 0;
+      if (w < n_pairs) {
+        pair = p.order[first + w];
+        q_row = pair / p.top_p;
+        const int64_t pos = p.positions[q_row];
+        const int row_k = p.row_top_k ? min(p.row_top_k[q_row], p.top_k) : p.top_k;
+        hi = min(members_below(max((int64_t)0, pos + 1 - p.window)), lo_key + row_k - p.starts[pair]);
+      }
+      pairs_s[w] = pair, qrows_s[w] = q_row, hi_s[w] = hi;
+    }
+    auto list_rows = [&](int tile) {
+      if (w >= kTcRows) return;
+      const int flat = tile * kTcRows + w;
+      const bool ok = flat < n_rows;
+      const int pl = ok ? flat / p.group : 0;
+      const int head = h * p.group + (flat - pl * p.group);
+      src_s[tile % 3][w] = ok ? (int64_t)qrows_s[pl] * p.q_row_stride + (int64_t)head * p.q_head_stride : -1;
+      dst_s[tile % 3][w] = ok ? (int64_t)pairs_s[pl] * p.Hq + head : -1;
+      end_s[tile % 3][w] = ok ? hi_s[pl] : 0;
+    };
+    // The query rows of a tile: half a warp copies a row of 256 bytes, in the layout of the keys.
+    auto gather_q = [&](int tile) {
+      const uint32_t buf = base + kTcQOff + (tile & 1) * 2 * kTcQPlane;
+#pragma unroll
+      for (int j = 0; j < kTcRows * 16 / kTcWorkers; ++j) {
+        const int e = j * kTcWorkers + w;
+        const int r = e >> 4, chunk = e & 15;
+        const int64_t from = src_s[tile % 3][r];
+        cp_async_16(buf + (chunk >> 3) * kTcQPlane + r * 128 + (((chunk & 7) ^ (r & 7)) << 4),
+                    p.q + (from >= 0 ? from + chunk * 8 : 0), from >= 0 ? 16 : 0);
+      }
+    };
+    workers_sync();  // the segment's pairs are written
+    list_rows(0);
+    if (n_tiles > 1) list_rows(1);
+    workers_sync();  // and the first tiles' rows
+    gather_q(0);
     cp_async_commit();
-  };
-  issue_q(0);  // (the group also closes the K/V copies above)
-
-  for (int hq = 0; hq < p.group; ++hq) {
-    const uint32_t parity = hq & 1;
-    issue_q(hq + 1);
+    if (n_tiles > 1) gather_q(1);
+    cp_async_commit();
     cp_async_wait<1>();
     proxy_fence();
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // K, V and this head's queries are in shared memory; the last head's reads of S and O are over
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0 && !abort_s) {
-      const uint32_t q_buf = base + kTcQOff + (hq & 1) * 2 * kTcQPlane;
-      const uint32_t idesc = umma_idesc(n_keys);
-#pragma unroll
-      for (int plane = 0; plane < 2; ++plane)
-#pragma unroll
-        for (int k = 0; k < 4; ++k)  // 16 dims = 32 bytes further inside the swizzle atom a step
-          umma_bf16(tmem_base, smem_desc_sw128(q_buf + plane * kTcQPlane) + 2 * k,
-                    smem_desc_sw128(base + kTcKOff + plane * kTcPlane) + 2 * k, idesc, (plane | k) != 0);
-      umma_commit(bar_s);
-    }
-    float m_row = -INFINITY, l_row = 0.0f;
-    if (worker) {
-      // (one decision a warp: the tensor-memory loads below are warp-wide instructions)
-      const bool go = __all_sync(0xffffffffu, mbar_wait(bar_s, parity) && !abort_s);
+    mbar_arrive(bar_w);  // K, V and the first tile's queries are in place
+
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    for (int tile = 0; tile < n_tiles; ++tile) {
+      const uint32_t parity = tile & 1;
+      const uint32_t buf = base + kTcQOff + parity * 2 * kTcQPlane;
+      const int hi_key = end_s[tile % 3][row];
+      const int64_t slot = dst_s[tile % 3][row];
+      // ---- softmax of the row: P, bf16 and already divided by the row's sum, is the A operand of the second product.
+      // This thread has the groups of 8 keys 2 j + half. (One decision a warp on the wait: the tensor-memory loads
+      // are warp-wide instructions.)
+      bool go = __all_sync(0xffffffffu, !abort_s && mbar_wait(bar_s, parity));
       if (!go) abort_s = 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (go) {
-        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        uint32_t r0[32], r1[32];
-        tmem_load_32(lane_addr, r0);
-        if (n_keys > 32) tmem_load_32(lane_addr + 32, r1);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        float s[64];
+      uint32_t sv[4][8];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const float raw = c < 32 ? __uint_as_float(r0[c]) : (n_keys > 32 ? __uint_as_float(r1[c - 32]) : 0.0f);
-          s[c] = (c >= lo_key && c < hi_key) ? raw * p.scale_log2 : -INFINITY;
-          m_row = fmaxf(m_row, s[c]);
-        }
-        // P, bf16, as the K-major A operand of the second product: 16-byte slot (c / 8) ^ (row % 8) of the row
-        const uint32_t p_row = base + kTcQOff + (hq & 1) * 2 * kTcQPlane + row * 128;
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint32_t w[4];
+        for (int c = 0; c < 8; ++c) sv[j][c] = 0u;
+        if (go && (2 * j + half) * 8 < n_keys) tmem_load_8(lane_addr + (2 * j + half) * 8, sv[j]);
+      }
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      float mx = -INFINITY;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float e0 = m_row == -INFINITY ? 0.0f : fast_exp2(s[c8 * 8 + 2 * j] - m_row);
-            const float e1 = m_row == -INFINITY ? 0.0f : fast_exp2(s[c8 * 8 + 2 * j + 1] - m_row);
-            l_row += e0 + e1;
-            w[j] = pack_bf16x2(e0, e1);
-          }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)), "r"(w[0]),
-                       "r"(w[1]), "r"(w[2]), "r"(w[3])
-                       : "memory");
+      for (int j = 0; j < 4; ++j) {
+        const int c0 = (2 * j + half) * 8;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c0 + c >= lo_key && c0 + c < hi_key) mx = fmaxf(mx, __uint_as_float(sv[j][c]));
+      }
+      swap_max_s[half][row] = mx;
+      quarter_sync(quarter);
+      mx = fmaxf(mx, swap_max_s[half ^ 1][row]);
+      const float m_row = mx * p.scale_log2;
+      float l_row = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c0 = (2 * j + half) * 8;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const float e = (c0 + c >= lo_key && c0 + c < hi_key)
+                              ? fast_exp2(fmaf(__uint_as_float(sv[j][c]), p.scale_log2, -m_row))
+                              : 0.0f;
+          l_row += e;
+          sv[j][c] = __float_as_uint(e);
         }
       }
-    }
-    proxy_fence();
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // P is in shared memory and S has been read
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0 && !abort_s) {
-      const uint32_t idesc = umma_idesc(DH, true);
-      for (int k = 0; k < n_keys / 16; ++k)  // 16 keys: 32 bytes along P's rows, 16 rows (2,048 bytes) down V's planes
-        umma_bf16(tmem_base + 64, smem_desc_sw128(base + kTcQOff + (hq & 1) * 2 * kTcQPlane) + 2 * k,
-                  smem_desc_mn_sw128(base + kTcVOff + k * 2048, kTcPlane), idesc, k != 0);
-      umma_commit(bar_o);
-    }
-    if (worker) {
-      const bool go = __all_sync(0xffffffffu, mbar_wait(bar_o, parity) && !abort_s);
+      swap_sum_s[half][row] = l_row;
+      quarter_sync(quarter);
+      l_row += swap_sum_s[half ^ 1][row];
+      const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
+      const uint32_t p_row = buf + row * 128;  // 16-byte slot (c / 8) ^ (row % 8) of the row
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c8 = 2 * j + half;
+        if (c8 * 8 >= n_keys) continue;
+        uint32_t v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          v[i] = pack_bf16x2(__uint_as_float(sv[j][2 * i]) * inv, __uint_as_float(sv[j][2 * i + 1]) * inv);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)), "r"(v[0]),
+                     "r"(v[1]), "r"(v[2]), "r"(v[3])
+                     : "memory");
+      }
+      if (go && half == 0 && slot >= 0)
+        p.part_lse[slot] = l_row > 0.0f ? (m_row + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
+      cp_async_wait<0>();  // the next tile's queries (sent a tile ago) have landed too
+      proxy_fence();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(bar_w);
+      // ---- O of the tile: out of tensor memory into the tile's (spent) query buffer, this thread's half of the
+      // columns, then out in whole rows
+      go = __all_sync(0xffffffffu, !abort_s && mbar_wait(bar_o, parity));
       if (!go) abort_s = 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (go) {
-        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + 64;
-        const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
-        const int64_t slot = (int64_t)pair * p.Hq + h * p.group + hq;
 #pragma unroll
-        for (int c0 = 0; c0 < DH; c0 += 32) {
+        for (int c0 = 0; c0 < DH / 2; c0 += 32) {
           uint32_t r[32];
-          tmem_load_32(lane_addr + c0, r);
+          tmem_load_32(lane_addr + 64 + half * (DH / 2) + c0, r);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (pair >= 0) {
-            uint4 *dst = reinterpret_cast<uint4 *>(p.part_out + slot * DH + c0);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 piece;
-              piece.x = pack_bf16x2(__uint_as_float(r[8 * i]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-              piece.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-              piece.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-              piece.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
-              dst[i] = piece;
-            }
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t a = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
+            const uint32_t b = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            const uint32_t c = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+            const uint32_t d = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            const int chunk = (half * (DH / 2) + c0) / 8 + i;
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + row * 256 + ((chunk ^ (row & 7)) << 4)),
+                         "r"(a), "r"(b), "r"(c), "r"(d)
+                         : "memory");
           }
         }
-        if (pair >= 0)
-          p.part_lse[slot] = l_row > 0.0f ? (m_row + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      workers_sync();  // the tile's rows are staged
+      if (go) {
+#pragma unroll
+        for (int j = 0; j < kTcRows * 16 / kTcWorkers; ++j) {
+          const int e = j * kTcWorkers + w;
+          const int r = e >> 4, chunk = e & 15;
+          const int64_t to = dst_s[tile % 3][r];
+          if (to < 0) continue;
+          uint4 piece;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(piece.x), "=r"(piece.y), "=r"(piece.z), "=r"(piece.w)
+                       : "r"(buf + r * 256 + ((chunk ^ (r & 7)) << 4)));
+          *reinterpret_cast<uint4 *>(p.part_out + to * DH + chunk * 8) = piece;
+        }
+      }
+      if (tile + 2 < n_tiles) list_rows(tile + 2);
+      workers_sync();  // the buffer has been read out, and the rows of the tile after next are listed
+      if (tile + 2 < n_tiles) gather_q(tile + 2);
+      cp_async_commit();
     }
+    cp_async_wait<0>();
   }
-  cp_async_wait<0>();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {

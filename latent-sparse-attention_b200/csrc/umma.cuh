@@ -61,6 +61,12 @@ __device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) 
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_load_8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+
 // Shared-memory matrix descriptor of a K-major bf16 tile written by TMA with the 128-byte swizzle: rows of 128
 // bytes, groups of 8 rows 1,024 bytes apart; bits 46-47 carry the descriptor version of this architecture, bits
 // 61-63 the swizzle mode.
