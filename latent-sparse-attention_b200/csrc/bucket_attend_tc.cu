@@ -11,13 +11,12 @@
 //   O [128 x 128]   = P [128 x keys] . V            A = P (K-major), B = the bucket's values AS STORED
 //                                                   ([key][dim] planes: an MN-major operand)
 //
-//   warp 0          tensor-memory allocation; one lane issues the MMAs
-//   warps 1-8       workers. Together they gather the query rows of the tile after next (a row of 256 bytes a half
-//                   warp) and send the finished tile's rows out in the same shape. For the softmax and the unloading
-//                   of O a row has TWO threads, one in warp 1 + q and one in warp 5 + q (both may read the tensor-
-//                   memory lanes of quarter q): they take alternate groups of 8 keys of S, swap their maxima and
-//                   sums through shared memory, and take a half of O's columns each. The row's instruction stream
-//                   is what bounds this kernel, so it is cut in two.
+// Eight warps. Together they gather the query rows of the tile after next (a row of 256 bytes a half warp) and send
+// the finished tile's rows out in the same shape. For the softmax and the unloading of O a row has TWO threads, one
+// in warp q and one in warp 4 + q (both may read the tensor-memory lanes of quarter q): they take alternate groups
+// of 8 keys of S, swap their maxima and sums through shared memory, and take a half of O's columns each. The row's instruction stream is what bounds this kernel, so it
+// is cut in two. A lane of warp 0 also issues the MMAs, at the points where the warp would wait for their results
+// anyway: a ninth warp for that would cost every thread 32 registers (five warps on a scheduler instead of four).
 //
 // The tiles of a CTA overlap: the tensor cores multiply S of tile i + 1 while the workers unload O of tile i, and
 // the query rows of tile i + 2 are on their way by then. Two CTAs share an SM and fill one another's waits.
@@ -31,8 +30,7 @@
 
 namespace lsa {
 
-constexpr int kTcThreads = 288;
-constexpr int kTcWorkers = 256;
+constexpr int kTcThreads = 256;
 constexpr int kTcRows = 128;                    // rows of a tile
 constexpr int kTcPlane = 64 * 128;              // a plane of 64 rows x 128 bytes (keys or values, 64 dims)
 constexpr int kTcQPlane = kTcRows * 128;        // a plane of the query tile or of P
@@ -49,7 +47,6 @@ __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTcWorkers) : "memory"); }
 // the two warps of a quarter of the rows
 __device__ __forceinline__ void quarter_sync(int quarter) { asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory"); }
 
@@ -85,7 +82,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   const uint32_t bar_w = smem_u32(&bars[0]), bar_s = smem_u32(&bars[1]), bar_o = smem_u32(&bars[2]);
 
   if (tid == 0) {
-    mbar_init(bar_w, kTcWorkers);
+    mbar_init(bar_w, kTcThreads);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     abort_s = 0;
@@ -112,41 +109,37 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   }
   const int n_keys = max(16, (n_members + 15) & ~15);  // the N of S and the K of O: whole 16-key steps
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------------------------------ the MMA lane
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc(n_keys), idesc_o = umma_idesc(DH, true);
-      for (int k = 0; k <= n_tiles; ++k) {
-        if (abort_s || !mbar_wait(bar_w, k & 1)) {
-          abort_s = 1;
-          break;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (k >= 1) {  // O of tile k - 1 = P V: 16 keys are 32 bytes along P's rows, 16 rows (2,048 bytes) down V's planes
-          const uint32_t p_buf = base + kTcQOff + ((k - 1) & 1) * 2 * kTcQPlane;
-          for (int s = 0; s < n_keys / 16; ++s)
-            umma_bf16(tmem_base + 64, smem_desc_sw128(p_buf) + 2 * s,
-                      smem_desc_mn_sw128(base + kTcVOff + s * 2048, kTcPlane), idesc_o, s != 0);
-          umma_commit(bar_o);
-        }
-        if (k < n_tiles) {  // S of tile k = Q K^T: 16 dims are 32 bytes further inside the swizzle atom
-          const uint32_t q_buf = base + kTcQOff + (k & 1) * 2 * kTcQPlane;
-#pragma unroll
-          for (int plane = 0; plane < 2; ++plane)
-#pragma unroll
-            for (int s = 0; s < 4; ++s)
-              umma_bf16(tmem_base, smem_desc_sw128(q_buf + plane * kTcQPlane) + 2 * s,
-                        smem_desc_sw128(base + kTcKOff + plane * kTcPlane) + 2 * s, idesc_s, (plane | s) != 0);
-          umma_commit(bar_s);
-        }
-      }
+  // Step k of the MMAs (warp 0; the whole warp waits so that its lanes stay together, lane 0 issues): once the k-th
+  // hand-over of the threads is complete, O of tile k - 1 and S of tile k.
+  auto issue_products = [&](int k) {
+    if (!__all_sync(0xffffffffu, !abort_s && mbar_wait(bar_w, k & 1))) {
+      abort_s = 1;
+      return;
     }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------------------------------------ the workers
-    const int w = tid - 32;                    // the thread's place in the shared copies
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (lane != 0) return;
+    if (k >= 1) {  // O = P V: 16 keys are 32 bytes along P's rows, 16 rows (2,048 bytes) down V's planes
+      const uint32_t p_buf = base + kTcQOff + ((k - 1) & 1) * 2 * kTcQPlane;
+      for (int s = 0; s < n_keys / 16; ++s)
+        umma_bf16(tmem_base + 64, smem_desc_sw128(p_buf) + 2 * s, smem_desc_mn_sw128(base + kTcVOff + s * 2048, kTcPlane),
+                  umma_idesc(DH, true), s != 0);
+      umma_commit(bar_o);
+    }
+    if (k < n_tiles) {  // S = Q K^T: 16 dims are 32 bytes further inside the swizzle atom
+      const uint32_t q_buf = base + kTcQOff + (k & 1) * 2 * kTcQPlane;
+#pragma unroll
+      for (int plane = 0; plane < 2; ++plane)
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          umma_bf16(tmem_base, smem_desc_sw128(q_buf + plane * kTcQPlane) + 2 * s,
+                    smem_desc_sw128(base + kTcKOff + plane * kTcPlane) + 2 * s, umma_idesc(n_keys), (plane | s) != 0);
+      umma_commit(bar_s);
+    }
+  };
+  {
+    const int w = tid;                         // the thread's place in the shared copies
     const int quarter = warp & 3;              // the 32 tensor-memory lanes this warp may read
-    const int half = (warp - 1) >> 2;          // which of the row's two threads
+    const int half = warp >> 2;                // which of the row's two threads
     const int row = quarter * 32 + lane;       // the tile row (= tensor-memory lane)
     auto members_below = [&](int64_t bound) {
       int lo = 0, hi = n_members;
@@ -161,8 +154,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     // (c % 8) ^ (j % 8) - the layout a tensor-map copy with the 128-byte swizzle would write.
     {
       const uint16_t *k_head = p.k + (int64_t)h * p.kv_head_stride, *v_head = p.v + (int64_t)h * p.kv_head_stride;
-#pragma unroll
-      for (int e = w; e < kBktKeys * 16; e += kTcWorkers) {
+#pragma unroll 2
+      for (int e = w; e < kBktKeys * 16; e += kTcThreads) {
         const int r = e >> 4, chunk = e & 15;
         const int32_t id = ids_s[r];
         const bool ok = id >= 0 && id < p.slots;
@@ -196,19 +189,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     // The query rows of a tile: half a warp copies a row of 256 bytes, in the layout of the keys.
     auto gather_q = [&](int tile) {
       const uint32_t buf = base + kTcQOff + (tile & 1) * 2 * kTcQPlane;
-#pragma unroll
-      for (int j = 0; j < kTcRows * 16 / kTcWorkers; ++j) {
-        const int e = j * kTcWorkers + w;
+#pragma unroll 4
+      for (int j = 0; j < kTcRows * 16 / kTcThreads; ++j) {
+        const int e = j * kTcThreads + w;
         const int r = e >> 4, chunk = e & 15;
         const int64_t from = src_s[tile % 3][r];
         cp_async_16(buf + (chunk >> 3) * kTcQPlane + r * 128 + (((chunk & 7) ^ (r & 7)) << 4),
                     p.q + (from >= 0 ? from + chunk * 8 : 0), from >= 0 ? 16 : 0);
       }
     };
-    workers_sync();  // the segment's pairs are written
+    __syncthreads();  // the segment's pairs are written
     list_rows(0);
     if (n_tiles > 1) list_rows(1);
-    workers_sync();  // and the first tiles' rows
+    __syncthreads();  // and the first tiles' rows
     gather_q(0);
     cp_async_commit();
     if (n_tiles > 1) gather_q(1);
@@ -216,6 +209,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     cp_async_wait<1>();
     proxy_fence();
     mbar_arrive(bar_w);  // K, V and the first tile's queries are in place
+    if (warp == 0) issue_products(0);
 
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     for (int tile = 0; tile < n_tiles; ++tile) {
@@ -229,39 +223,62 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       bool go = __all_sync(0xffffffffu, !abort_s && mbar_wait(bar_s, parity));
       if (!go) abort_s = 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // A group of 8 keys that lies inside the key range of every row of the warp needs no masks: most do.
       uint32_t sv[4][8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c) sv[j][c] = 0u;
-        if (go && (2 * j + half) * 8 < n_keys) tmem_load_8(lane_addr + (2 * j + half) * 8, sv[j]);
-      }
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      float mx = -INFINITY;
+      bool active[4], whole[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c0 = (2 * j + half) * 8;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          if (c0 + c >= lo_key && c0 + c < hi_key) mx = fmaxf(mx, __uint_as_float(sv[j][c]));
+        active[j] = c0 < n_keys;
+        whole[j] = __all_sync(0xffffffffu, c0 >= lo_key && c0 + 8 <= hi_key);
+        if (go && active[j]) tmem_load_8(lane_addr + c0, sv[j]);
       }
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      // (four running maxima, and four running sums below: one chain of 32 dependent operations is what a thread
+      // with few warps beside it waits on)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c0 = (2 * j + half) * 8;
+        if (!active[j]) continue;
+        if (whole[j]) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[j][c]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            if (c0 + c >= lo_key && c0 + c < hi_key) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[j][c]));
+        }
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       swap_max_s[half][row] = mx;
       quarter_sync(quarter);
       mx = fmaxf(mx, swap_max_s[half ^ 1][row]);
       const float m_row = mx * p.scale_log2;
-      float l_row = 0.0f;
+      float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c0 = (2 * j + half) * 8;
+        if (!active[j]) continue;
+        if (whole[j]) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const float e = (c0 + c >= lo_key && c0 + c < hi_key)
-                              ? fast_exp2(fmaf(__uint_as_float(sv[j][c]), p.scale_log2, -m_row))
-                              : 0.0f;
-          l_row += e;
-          sv[j][c] = __float_as_uint(e);
+          for (int c = 0; c < 8; ++c) {
+            const float e = fast_exp2(fmaf(__uint_as_float(sv[j][c]), p.scale_log2, -m_row));
+            l4[c & 3] += e;
+            sv[j][c] = __float_as_uint(e);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float e = (c0 + c >= lo_key && c0 + c < hi_key)
+                                ? fast_exp2(fmaf(__uint_as_float(sv[j][c]), p.scale_log2, -m_row))
+                                : 0.0f;
+            l4[c & 3] += e;
+            sv[j][c] = __float_as_uint(e);
+          }
         }
       }
+      float l_row = (l4[0] + l4[1]) + (l4[2] + l4[3]);
       swap_sum_s[half][row] = l_row;
       quarter_sync(quarter);
       l_row += swap_sum_s[half ^ 1][row];
@@ -270,7 +287,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c8 = 2 * j + half;
-        if (c8 * 8 >= n_keys) continue;
+        if (!active[j]) continue;
         uint32_t v[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i)
@@ -285,36 +302,37 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       proxy_fence();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(bar_w);
+      if (warp == 0) issue_products(tile + 1);
       // ---- O of the tile: out of tensor memory into the tile's (spent) query buffer, this thread's half of the
       // columns, then out in whole rows
       go = __all_sync(0xffffffffu, !abort_s && mbar_wait(bar_o, parity));
       if (!go) abort_s = 1;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (go) {
+        uint32_t r[2][32];
+        tmem_load_32(lane_addr + 64 + half * (DH / 2), r[0]);
+        tmem_load_32(lane_addr + 64 + half * (DH / 2) + 32, r[1]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int c0 = 0; c0 < DH / 2; c0 += 32) {
-          uint32_t r[32];
-          tmem_load_32(lane_addr + 64 + half * (DH / 2) + c0, r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint32_t a = pack_bf16x2(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
-            const uint32_t b = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-            const uint32_t c = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-            const uint32_t d = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-            const int chunk = (half * (DH / 2) + c0) / 8 + i;
+            const uint32_t a = pack_bf16x2(__uint_as_float(r[c][8 * i]), __uint_as_float(r[c][8 * i + 1]));
+            const uint32_t b = pack_bf16x2(__uint_as_float(r[c][8 * i + 2]), __uint_as_float(r[c][8 * i + 3]));
+            const uint32_t d = pack_bf16x2(__uint_as_float(r[c][8 * i + 4]), __uint_as_float(r[c][8 * i + 5]));
+            const uint32_t f = pack_bf16x2(__uint_as_float(r[c][8 * i + 6]), __uint_as_float(r[c][8 * i + 7]));
+            const int chunk = half * (DH / 16) + c * 4 + i;
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + row * 256 + ((chunk ^ (row & 7)) << 4)),
-                         "r"(a), "r"(b), "r"(c), "r"(d)
+                         "r"(a), "r"(b), "r"(d), "r"(f)
                          : "memory");
           }
-        }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      workers_sync();  // the tile's rows are staged
+      __syncthreads();  // the tile's rows are staged
       if (go) {
-#pragma unroll
-        for (int j = 0; j < kTcRows * 16 / kTcWorkers; ++j) {
-          const int e = j * kTcWorkers + w;
+#pragma unroll 4
+        for (int j = 0; j < kTcRows * 16 / kTcThreads; ++j) {
+          const int e = j * kTcThreads + w;
           const int r = e >> 4, chunk = e & 15;
           const int64_t to = dst_s[tile % 3][r];
           if (to < 0) continue;
@@ -326,7 +344,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
         }
       }
       if (tile + 2 < n_tiles) list_rows(tile + 2);
-      workers_sync();  // the buffer has been read out, and the rows of the tile after next are listed
+      __syncthreads();  // the buffer has been read out, and the rows of the tile after next are listed
       if (tile + 2 < n_tiles) gather_q(tile + 2);
       cp_async_commit();
     }
