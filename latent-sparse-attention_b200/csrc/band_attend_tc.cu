@@ -10,8 +10,9 @@
 //   warp 0      one lane streams the key and value tiles with tensor-map copies (128-byte swizzle) through a ring
 //   warp 1      tensor-memory allocation; one lane issues the MMAs: S = Q K^T (both K-major) into one of two S
 //               buffers, O += P V with V read as stored (an MN-major operand)
-//   warps 2-5   thread = row: S out of tensor memory, masks on the band's edge tiles only, maximum (walk one) or
-//               P in bf16 into the consumed key tile's slot (walk two), then the normalised fp32 output
+//   warps 2-9   two threads a row (32 of a tile's 64 keys each): S out of tensor memory, masks on the band's edge
+//               tiles only, maximum (walk one) or P in bf16 into the consumed key tile's slot (walk two), then the
+//               normalised fp32 output
 //
 // Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's abort flag and the status word, the
 // roles drain, the tensor memory is freed and the CTA leaves.
@@ -23,8 +24,9 @@ namespace lsa {
 
 constexpr int kBtRows = 128;
 constexpr int kBtKeys = 64;
-constexpr int kBtThreads = 192;
-constexpr int kBtStages = 2;
+constexpr int kBtThreads = 320;                      // the copy warp, the MMA warp and eight worker warps
+constexpr int kBtWorkers = 256;
+constexpr int kBtStages = 6;                        // the ring of key/value tiles: deep enough to hide a tensor-map copy
 constexpr int kBtPlane = kBtKeys * 128;             // 64 keys x 64 dims of bf16
 constexpr int kBtQPlane = kBtRows * 128;            // 128 rows x 64 dims
 constexpr int kBtStage = 4 * kBtPlane;              // K (2 planes; P lands here once S is done) and V (2 planes)
@@ -39,20 +41,23 @@ struct BandTcParams {
   float scale_log2;
 };
 
-__global__ void __launch_bounds__(kBtThreads, 2)
+__global__ void __launch_bounds__(kBtThreads, 1)
     band_attend_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, BandTcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // full / empty: a ring stage's tiles have landed / may be overwritten; s_ready / s_free: an S buffer holds a
   // product / has been read; p_ready: a stage holds P; q_full, o_done: once each.
-  __shared__ __align__(8) uint64_t bars[5 * 2 + 2];
+  __shared__ __align__(8) uint64_t bars[3 * kBtStages + 2 * 2 + 2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
+  __shared__ float swap_s[2][kBtRows];  // where the two threads of a row leave their maximum, then their sum
+  auto workers_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kBtWorkers) : "memory"); };
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_s = base, ring = base + 2 * kBtQPlane;
-  auto bar = [&](int kind, int i) { return smem_u32(&bars[kind * 2 + i]); };
-  enum { kFull = 0, kEmpty = 1, kSReady = 2, kSFree = 3, kPReady = 4 };
-  const uint32_t q_full = smem_u32(&bars[10]), o_done = smem_u32(&bars[11]);
+  // (kFull, kEmpty, kPReady: one a ring stage; kSReady, kSFree: one an S buffer)
+  enum { kFull = 0, kEmpty = kBtStages, kPReady = 2 * kBtStages, kSReady = 3 * kBtStages, kSFree = 3 * kBtStages + 2 };
+  auto bar = [&](int kind, int i) { return smem_u32(&bars[kind + i]); };
+  const uint32_t q_full = smem_u32(&bars[3 * kBtStages + 4]), o_done = smem_u32(&bars[3 * kBtStages + 5]);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row0 = (int64_t)blockIdx.x * kBtRows;
@@ -69,12 +74,14 @@ __global__ void __launch_bounds__(kBtThreads, 2)
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kBtStages; ++i) {
       mbar_init(bar(kFull, i), 1);
       mbar_init(bar(kEmpty, i), 1);
+      mbar_init(bar(kPReady, i), kBtWorkers);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kSReady, i), 1);
-      mbar_init(bar(kSFree, i), 128);
-      mbar_init(bar(kPReady, i), 128);
+      mbar_init(bar(kSFree, i), kBtWorkers);
     }
     mbar_init(q_full, 1);
     mbar_init(o_done, 1);
@@ -97,16 +104,16 @@ __global__ void __launch_bounds__(kBtThreads, 2)
       mbar_expect_tx(q_full, 2 * kBtQPlane);
       tma_load_2d(q_s, &map_q, q_full, head * 128, (int)row0);
       tma_load_2d(q_s + kBtQPlane, &map_q, q_full, head * 128 + 64, (int)row0);
-      uint32_t phase[2] = {0, 0};
+      uint32_t phases = 0;  // a parity bit a stage
       for (int n = 0; n < 2 * tiles && !abort_s; ++n) {
-        const int stage = n & 1, tile = n % tiles;
+        const int stage = n % kBtStages, tile = n % tiles;
         const bool second = n >= tiles;
         if (n >= kBtStages) {
-          if (!mbar_wait(bar(kEmpty, stage), phase[stage])) {
+          if (!mbar_wait(bar(kEmpty, stage), (phases >> stage) & 1)) {
             abort_s = 1;
             break;
           }
-          phase[stage] ^= 1;
+          phases ^= 1u << stage;
         }
         const uint32_t dst = ring + stage * kBtStage;
         const int y = (int)key0_of(tile), x = kv_head * 128;
@@ -122,13 +129,13 @@ __global__ void __launch_bounds__(kBtThreads, 2)
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc(kBtKeys), idesc_o = umma_idesc(128, true);
-      uint32_t full_phase[2] = {0, 0}, free_phase[2] = {0, 0}, p_phase[2] = {0, 0};
+      uint32_t full_phases = 0, free_phases = 0, p_phases = 0;  // a parity bit a stage (or S buffer)
       bool ok = mbar_wait(q_full, 0);
       // the second product of tile n, once the workers have written its P
       auto second_product = [&](int n) {
-        const int stage = n & 1;
-        if (!mbar_wait(bar(kPReady, stage), p_phase[stage])) return false;
-        p_phase[stage] ^= 1;
+        const int stage = n % kBtStages;
+        if (!mbar_wait(bar(kPReady, stage), (p_phases >> stage) & 1)) return false;
+        p_phases ^= 1u << stage;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t p_tile = ring + stage * kBtStage, v_tile = p_tile + 2 * kBtPlane;
 #pragma unroll
@@ -139,15 +146,15 @@ __global__ void __launch_bounds__(kBtThreads, 2)
         return true;
       };
       for (int n = 0; n < 2 * tiles && ok && !abort_s; ++n) {
-        const int stage = n & 1;
+        const int stage = n % kBtStages, sbuf = n & 1;
         const bool second = n >= tiles;
-        ok = mbar_wait(bar(kFull, stage), full_phase[stage]);
+        ok = mbar_wait(bar(kFull, stage), (full_phases >> stage) & 1);
         if (!ok) break;
-        full_phase[stage] ^= 1;
+        full_phases ^= 1u << stage;
         if (n >= 2) {
-          ok = mbar_wait(bar(kSFree, stage), free_phase[stage]);
+          ok = mbar_wait(bar(kSFree, sbuf), (free_phases >> sbuf) & 1);
           if (!ok) break;
-          free_phase[stage] ^= 1;
+          free_phases ^= 1u << sbuf;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_tile = ring + stage * kBtStage;
@@ -155,9 +162,9 @@ __global__ void __launch_bounds__(kBtThreads, 2)
         for (int plane = 0; plane < 2; ++plane)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + stage * 64, smem_desc_sw128(q_s + plane * kBtQPlane) + 2 * k,
+            umma_bf16(tmem_base + sbuf * 64, smem_desc_sw128(q_s + plane * kBtQPlane) + 2 * k,
                       smem_desc_sw128(k_tile + plane * kBtPlane) + 2 * k, idesc_s, (plane | k) != 0);
-        umma_commit(bar(kSReady, stage));
+        umma_commit(bar(kSReady, sbuf));
         if (!second) umma_commit(bar(kEmpty, stage));  // on the first walk the keys are all a stage holds
         if (second && n > tiles) ok = second_product(n - 1);
       }
@@ -166,79 +173,96 @@ __global__ void __launch_bounds__(kBtThreads, 2)
       umma_commit(o_done);
     }
   } else {
-    // Workers: TMEM lane 32 * (warp % 4) + lane is this thread's row.
+    // Workers: TMEM lane 32 * (warp % 4) + lane is this thread's row, and a row has two threads (warps w and w + 4):
+    // each takes 32 of a tile's 64 keys and 64 of O's 128 columns. Their maxima and sums meet once a walk, not once
+    // a tile. (With one thread a row a step ran some 800 dependent instructions on a scheduler that had nothing
+    // else to issue: that, not the tensor pipe or the copies, set the pace.)
+    const int half = (warp - 2) >> 2;
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const int64_t pos = pos0 + row;
     const bool live = row0 + row < p.R;
     const int64_t start = max((int64_t)0, pos + 1 - p.window);
     const int64_t sink_end = min((int64_t)p.sink, start);
-    uint32_t ready_phase[2] = {0, 0};
-    float m_row = -INFINITY, l_row = 0.0f;
+    // a tile inside every row's window, below every row's position and inside the cache needs no masks
+    const int64_t inside_from = max((int64_t)0, pos_last + 1 - p.window);
+    const bool rows_whole = pos0 + kBtRows <= p.first_position + p.R;
+    uint32_t ready_phases = 0;
+    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float m_row = 0.0f;
     bool go = true;
-    for (int n = 0; n < 2 * tiles && go; ++n) {
-      const int stage = n & 1, tile = n % tiles;
+    for (int n = 0; n < 2 * tiles; ++n) {  // (a warp that gave up still walks on: it owes the others two barriers)
+      const int stage = n % kBtStages, sbuf = n & 1, tile = n % tiles;
       const bool second = n >= tiles;
-      go = __all_sync(0xffffffffu, mbar_wait(bar(kSReady, stage), ready_phase[stage]) && !abort_s);
-      if (!go) break;
-      ready_phase[stage] ^= 1;
+      if (n == tiles) {  // between the walks: the row's maximum is the larger of its two threads'
+        float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        swap_s[half][row] = m;
+        workers_sync();
+        m = fmaxf(m, swap_s[half ^ 1][row]);
+        m_row = m == -INFINITY ? 0.0f : m * p.scale_log2;  // the offset of every exponent
+        workers_sync();
+      }
+      go = go && __all_sync(0xffffffffu, mbar_wait(bar(kSReady, sbuf), (ready_phases >> sbuf) & 1) && !abort_s);
+      if (!go) continue;
+      ready_phases ^= 1u << sbuf;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t r0[32], r1[32];
-      tmem_load_32(lane_addr + stage * 64, r0);
-      tmem_load_32(lane_addr + stage * 64 + 32, r1);
+      uint32_t sv[32];
+      tmem_load_32(lane_addr + sbuf * 64 + half * 32, sv);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kSFree, stage)) : "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kSFree, sbuf)) : "memory");
       const int64_t key0 = key0_of(tile);
       const bool is_sinks = has_sinks && tile == 0;
-      // a tile inside every row's window, below every row's position and inside the cache needs no masks
-      const bool inside = !is_sinks && key0 >= max((int64_t)0, pos_last + 1 - p.window) && key0 + kBtKeys - 1 <= pos0 &&
-                          key0 + kBtKeys <= p.n_keys && pos0 + kBtRows <= p.first_position + p.R;
-      float s[64];
+      const bool inside = !is_sinks && rows_whole && key0 >= inside_from && key0 + kBtKeys - 1 <= pos0 &&
+                          key0 + kBtKeys <= p.n_keys;
+      if (!inside) {
+        // the row's bounds as columns of this thread's half of the tile
+        const int64_t col0 = key0 + half * 32;
+        auto rel = [&](int64_t key) { return (int)max((int64_t)-1, min((int64_t)64, key - col0)); };
+        const int end = live ? rel(p.n_keys) : 0;                   // columns at or past it are outside the cache
+        const int sinks = rel(sink_end);                             // columns below it are the row's sinks
+        const int from = is_sinks ? 64 : rel(start), to = is_sinks ? -1 : rel(pos);  // the window: from <= c <= to
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float raw = __uint_as_float(c < 32 ? r0[c] : r1[c - 32]);
-        if (inside) {
-          s[c] = raw;
-        } else {
-          const int64_t key = key0 + c;
-          // (a band that starts at key 0 holds the sinks of its rows itself: keys below a row's window start)
-          const bool ok = live && key < p.n_keys &&
-                          (is_sinks ? key < sink_end : ((key >= start && key <= pos) || key < sink_end));
-          s[c] = ok ? raw : -INFINITY;
+        for (int c = 0; c < 32; ++c) {
+          const bool ok = c < end && ((c >= from && c <= to) || c < sinks);
+          if (!ok) sv[c] = 0xff800000u;  // -inf
         }
       }
       if (!second) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) m_row = fmaxf(m_row, s[c]);
+        for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[c]));
       } else {
-        if (n == tiles) m_row = m_row == -INFINITY ? 0.0f : m_row * p.scale_log2;  // the offset of every exponent
         const uint32_t p_row = ring + stage * kBtStage + row * 128;
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
+        for (int c8 = 0; c8 < 4; ++c8) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float e0 = fast_exp2(fmaf(s[c8 * 8 + 2 * j], p.scale_log2, -m_row));
-            const float e1 = fast_exp2(fmaf(s[c8 * 8 + 2 * j + 1], p.scale_log2, -m_row));
-            l_row += e0 + e1;
+            const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j]), p.scale_log2, -m_row));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c8 * 8 + 2 * j + 1]), p.scale_log2, -m_row));
+            l4[j] += e0 + e1;
             w[j] = pack_bf16x2(e0, e1);
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)), "r"(w[0]),
-                       "r"(w[1]), "r"(w[2]), "r"(w[3])
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((half * 4 + c8) ^ (row & 7)) << 4)),
+                       "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kPReady, stage)) : "memory");
       }
     }
+    // the row's sum is the sum of its two threads'
+    float l_row = (l4[0] + l4[1]) + (l4[2] + l4[3]);
+    swap_s[half][row] = l_row;
+    workers_sync();
+    l_row += swap_s[half ^ 1][row];
     go = __all_sync(0xffffffffu, go && mbar_wait(o_done, 0) && !abort_s);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (go) {
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
       const int64_t out_row = (row0 + row) * p.Hq + head;
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
         uint32_t r[32];
         tmem_load_32(lane_addr + 128 + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -250,7 +274,7 @@ __global__ void __launch_bounds__(kBtThreads, 2)
                                  __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
         }
       }
-      if (live) p.lse[out_row] = l_row > 0.0f ? (m_row + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
+      if (live && half == 0) p.lse[out_row] = l_row > 0.0f ? (m_row + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
     } else {
       abort_s = 1;
     }
