@@ -1,7 +1,7 @@
 // The window and the sinks of a prefill as dense banded attention on the fifth-generation tensor cores.
 //
 // A CTA owns 128 consecutive query rows of ONE query head and walks the band of keys they see - from the first row's
-// window start to the last row, in tiles of 64 keys, plus a tile for the sinks. The rows are the M = 128 side of both
+// window start to the last row, in tiles of 128 keys, plus a tile for the sinks. The rows are the M = 128 side of both
 // products, so a row of S and of O lives in one lane of tensor memory and the thread that owns the row does its
 // softmax alone. The band is walked TWICE: the first walk only takes every row's maximum, the second computes
 // P = exp2(S - max) and accumulates O = sum P V in tensor memory without ever rescaling it (the second product costs
@@ -10,7 +10,7 @@
 //   warp 0      one lane streams the key and value tiles with tensor-map copies (128-byte swizzle) through a ring
 //   warp 1      tensor-memory allocation; one lane issues the MMAs: S = Q K^T (both K-major) into one of two S
 //               buffers, O += P V with V read as stored (an MN-major operand)
-//   warps 2-9   two threads a row (32 of a tile's 64 keys each): S out of tensor memory, masks on the band's edge
+//   warps 2-9   two threads a row (64 of a tile's 128 keys each): S out of tensor memory, masks on the band's edge
 //               tiles only, maximum (walk one) or P in bf16 into the consumed key tile's slot (walk two), then the
 //               normalised fp32 output
 //
@@ -23,15 +23,16 @@
 namespace lsa {
 
 constexpr int kBtRows = 128;
-constexpr int kBtKeys = 64;
+constexpr int kBtKeys = 128;                        // keys a tile: two planes of 64 for P, N = 128 for S
 constexpr int kBtThreads = 320;                      // the copy warp, the MMA warp and eight worker warps
 constexpr int kBtWorkers = 256;
-constexpr int kBtStages = 6;                        // the ring of key/value tiles: deep enough to hide a tensor-map copy
-constexpr int kBtPlane = kBtKeys * 128;             // 64 keys x 64 dims of bf16
+constexpr int kBtStages = 3;                        // the ring of key/value tiles: deep enough to hide a tensor-map copy
+constexpr int kBtPlane = kBtKeys * 128;             // 128 keys x 64 dims of bf16
 constexpr int kBtQPlane = kBtRows * 128;            // 128 rows x 64 dims
 constexpr int kBtStage = 4 * kBtPlane;              // K (2 planes; P lands here once S is done) and V (2 planes)
 constexpr int kBtSmem = 2 * kBtQPlane + kBtStages * kBtStage + 1024;
-constexpr int kBtTmemCols = 256;                    // S buffers in columns 0-63 and 64-127, O in 128-255
+constexpr int kBtTmemCols = 512;                    // S buffers in columns 0-127 and 128-255, O in 256-383
+constexpr int kBtOCol = 256;
 
 struct BandTcParams {
   float *out, *lse;
@@ -139,9 +140,9 @@ __global__ void __launch_bounds__(kBtThreads, 1)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t p_tile = ring + stage * kBtStage, v_tile = p_tile + 2 * kBtPlane;
 #pragma unroll
-        for (int k = 0; k < kBtKeys / 16; ++k)
-          umma_bf16(tmem_base + 128, smem_desc_sw128(p_tile) + 2 * k, smem_desc_mn_sw128(v_tile + k * 2048, kBtPlane),
-                    idesc_o, (n > tiles || k > 0) ? 1u : 0u);
+        for (int k = 0; k < kBtKeys / 16; ++k)  // P: two planes of 64 keys; V: 16 keys are 2,048 bytes down a plane
+          umma_bf16(tmem_base + kBtOCol, smem_desc_sw128(p_tile + (k >> 2) * kBtQPlane) + 2 * (k & 3),
+                    smem_desc_mn_sw128(v_tile + k * 2048, kBtPlane), idesc_o, (n > tiles || k > 0) ? 1u : 0u);
         umma_commit(bar(kEmpty, stage));
         return true;
       };
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(kBtThreads, 1)
         for (int plane = 0; plane < 2; ++plane)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_base + sbuf * 64, smem_desc_sw128(q_s + plane * kBtQPlane) + 2 * k,
+            umma_bf16(tmem_base + sbuf * kBtKeys, smem_desc_sw128(q_s + plane * kBtQPlane) + 2 * k,
                       smem_desc_sw128(k_tile + plane * kBtPlane) + 2 * k, idesc_s, (plane | k) != 0);
         umma_commit(bar(kSReady, sbuf));
         if (!second) umma_commit(bar(kEmpty, stage));  // on the first walk the keys are all a stage holds
@@ -174,7 +175,7 @@ __global__ void __launch_bounds__(kBtThreads, 1)
     }
   } else {
     // Workers: TMEM lane 32 * (warp % 4) + lane is this thread's row, and a row has two threads (warps w and w + 4):
-    // each takes 32 of a tile's 64 keys and 64 of O's 128 columns. Their maxima and sums meet once a walk, not once
+    // each takes 64 of a tile's 128 keys and 64 of O's 128 columns. Their maxima and sums meet once a walk, not once
     // a tile. (With one thread a row a step ran some 800 dependent instructions on a scheduler that had nothing
     // else to issue: that, not the tensor pipe or the copies, set the pace.)
     const int half = (warp - 2) >> 2;
@@ -206,8 +207,9 @@ __global__ void __launch_bounds__(kBtThreads, 1)
       if (!go) continue;
       ready_phases ^= 1u << sbuf;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t sv[32];
-      tmem_load_32(lane_addr + sbuf * 64 + half * 32, sv);
+      uint32_t sv[64];
+      tmem_load_32(lane_addr + sbuf * kBtKeys + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_load_32(lane_addr + sbuf * kBtKeys + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar(kSFree, sbuf)) : "memory");
@@ -217,24 +219,24 @@ __global__ void __launch_bounds__(kBtThreads, 1)
                           key0 + kBtKeys <= p.n_keys;
       if (!inside) {
         // the row's bounds as columns of this thread's half of the tile
-        const int64_t col0 = key0 + half * 32;
+        const int64_t col0 = key0 + half * 64;
         auto rel = [&](int64_t key) { return (int)max((int64_t)-1, min((int64_t)64, key - col0)); };
         const int end = live ? rel(p.n_keys) : 0;                   // columns at or past it are outside the cache
         const int sinks = rel(sink_end);                             // columns below it are the row's sinks
         const int from = is_sinks ? 64 : rel(start), to = is_sinks ? -1 : rel(pos);  // the window: from <= c <= to
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 64; ++c) {
           const bool ok = c < end && ((c >= from && c <= to) || c < sinks);
           if (!ok) sv[c] = 0xff800000u;  // -inf
         }
       }
       if (!second) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[c]));
+        for (int c = 0; c < 64; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sv[c]));
       } else {
-        const uint32_t p_row = ring + stage * kBtStage + row * 128;
+        const uint32_t p_row = ring + stage * kBtStage + half * kBtQPlane + row * 128;  // the plane of this half's keys
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
+        for (int c8 = 0; c8 < 8; ++c8) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -243,7 +245,7 @@ __global__ void __launch_bounds__(kBtThreads, 1)
             l4[j] += e0 + e1;
             w[j] = pack_bf16x2(e0, e1);
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((half * 4 + c8) ^ (row & 7)) << 4)),
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c8 ^ (row & 7)) << 4)),
                        "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
         }
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(kBtThreads, 1)
 #pragma unroll
       for (int c0 = half * 64; c0 < half * 64 + 64; c0 += 32) {
         uint32_t r[32];
-        tmem_load_32(lane_addr + 128 + c0, r);
+        tmem_load_32(lane_addr + kBtOCol + c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (live) {
           float4 *dst = reinterpret_cast<float4 *>(p.out + out_row * 128 + c0);
