@@ -224,10 +224,11 @@ __global__ void __launch_bounds__(kBtThreads, 1)
         const int end = live ? rel(p.n_keys) : 0;                   // columns at or past it are outside the cache
         const int sinks = rel(sink_end);                             // columns below it are the row's sinks
         const int from = is_sinks ? 64 : rel(start), to = is_sinks ? -1 : rel(pos);  // the window: from <= c <= to
+        // (bitwise, not short-circuit, logic and a select: branches here diverge lane by lane, 64 times a tile)
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
-          const bool ok = c < end && ((c >= from && c <= to) || c < sinks);
-          if (!ok) sv[c] = 0xff800000u;  // -inf
+          const bool ok = (c < end) & (((c >= from) & (c <= to)) | (c < sinks));
+          sv[c] = ok ? sv[c] : 0xff800000u;  // -inf
         }
       }
       if (!second) {

@@ -246,15 +246,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
           for (int c = 0; c < 8; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[j][c]));
         } else {
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            if (c0 + c >= lo_key && c0 + c < hi_key) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[j][c]));
+          for (int c = 0; c < 8; ++c) {  // (bitwise logic and selects: branches here would diverge lane by lane)
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key);
+            mx4[c & 3] = fmaxf(mx4[c & 3], ok ? __uint_as_float(sv[j][c]) : -INFINITY);
+          }
         }
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       swap_max_s[half][row] = mx;
       quarter_sync(quarter);
       mx = fmaxf(mx, swap_max_s[half ^ 1][row]);
-      const float m_row = mx * p.scale_log2;
+      const float m_row = mx == -INFINITY ? 0.0f : mx * p.scale_log2;  // (finite, so that a masked key gives exp2(-inf) = 0)
       float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -270,9 +272,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
         } else {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const float e = (c0 + c >= lo_key && c0 + c < hi_key)
-                                ? fast_exp2(fmaf(__uint_as_float(sv[j][c]), p.scale_log2, -m_row))
-                                : 0.0f;
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key);
+            const float e = fast_exp2(fmaf(ok ? __uint_as_float(sv[j][c]) : -INFINITY, p.scale_log2, -m_row));
             l4[c & 3] += e;
             sv[j][c] = __float_as_uint(e);
           }
