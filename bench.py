@@ -426,7 +426,7 @@ def main() -> None:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--tokens", type=int, default=None, help="a smaller context of the same workload (profiling)")
-    parser.add_argument("--bucket-kernel", default="warp", choices=["warp", "tensor-memory"],
+    parser.add_argument("--bucket-kernel", default="tensor-memory", choices=["warp", "tensor-memory"],
                         help="the form of the bucket-major attend pass: warp-level MMA tiles or tcgen05 tiles in tensor memory")
     parser.add_argument("--parallel", default="rows", choices=["rows", "context"],
                         help="at N > 1: split the query rows over the ranks (the cache is all-gathered once a step), "

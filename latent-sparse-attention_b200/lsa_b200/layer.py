@@ -73,10 +73,9 @@ class FlatLayer:
         self.dh_used = free
         self.scale = head_dim ** -0.5 if scale is None else scale
         self._buffers: dict = {}
-        # The bucket-major attend pass has two forms. With the pairs of a segment as the 128 rows of tcgen05 products
-        # (S and O in tensor memory) a CTA walks its heads through a chain of dependent hand-overs and measures
-        # slower (7.8 ms a chunk of config 2) than the warp-level tiles of 16 rows (3.9 ms), so those are the default.
-        self.bucket_tensor_memory = False
+        # The bucket-major attend pass has two forms: (pair, head) rows as the M = 128 side of tcgen05 products with S
+        # and O in tensor memory (the default: 63.5 ms a step of config 2), or warp-level MMA tiles of 16 rows (66.4 ms).
+        self.bucket_tensor_memory = True
         self._band_stream = self._band_done = None  # the side stream the band runs on beside the bucket-major read
         self._copy_in = self._copy_out = None       # the copy streams of `prefill_from_host`
         self._copy_events: list = []
