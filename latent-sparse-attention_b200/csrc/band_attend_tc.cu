@@ -224,11 +224,22 @@ __global__ void __launch_bounds__(kBtThreads, 1)
         const int end = live ? rel(p.n_keys) : 0;                   // columns at or past it are outside the cache
         const int sinks = rel(sink_end);                             // columns below it are the row's sinks
         const int from = is_sinks ? 64 : rel(start), to = is_sinks ? -1 : rel(pos);  // the window: from <= c <= to
-        // (bitwise, not short-circuit, logic and a select: branches here diverge lane by lane, 64 times a tile)
+        // The row's valid columns as a 64-bit word. A group of 8 columns that every row of the warp sees whole is
+        // left alone, and one that none sees is cleared; the others take a bit test and a select a column (no
+        // branches on a lane's own bounds: they would diverge lane by lane, 64 times a tile).
+        auto below = [](int x) { return x >= 64 ? ~0ull : (x <= 0 ? 0ull : (1ull << x) - 1ull); };
+        const unsigned long long valid = ((below(to + 1) & ~below(from)) | below(sinks)) & below(end);
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const bool ok = (c < end) & (((c >= from) & (c <= to)) | (c < sinks));
-          sv[c] = ok ? sv[c] : 0xff800000u;  // -inf
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t bits = (uint32_t)(valid >> (8 * g)) & 0xffu;
+          if (__all_sync(0xffffffffu, bits == 0xffu)) continue;
+          if (__all_sync(0xffffffffu, bits == 0u)) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) sv[8 * g + c] = 0xff800000u;  // -inf
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) sv[8 * g + c] = (bits & (1u << c)) ? sv[8 * g + c] : 0xff800000u;
+          }
         }
       }
       if (!second) {
