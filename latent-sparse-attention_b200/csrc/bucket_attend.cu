@@ -53,7 +53,10 @@ __global__ void __launch_bounds__(256) bucket_starts_kernel(BucketParams p) {
     }
     const int before = running + incl - mine;
     const bool adds = bucket >= 0 && mine > 0 && before < row_k;
-    if (i < p.top_p) p.starts[r * p.top_p + i] = adds ? before : -1;
+    if (i < p.top_p) {
+      p.starts[r * p.top_p + i] = adds ? before : -1;
+      p.takes[r * p.top_p + i] = adds ? min(mine, row_k - before) : 0;  // members ascend: the counted ids are a run
+    }
     if (adds) atomicAdd(&p.counts[bucket], 1);
     running += __shfl_sync(0xffffffffu, incl, 31);
   }
@@ -117,7 +120,9 @@ __global__ void __launch_bounds__(256) bucket_scatter_kernel(BucketParams p) {
   if (pair >= p.R * p.top_p) return;
   if (p.starts[pair] < 0) return;
   const int32_t bucket = p.picked[pair];
-  p.order[atomicAdd(&p.cursors[bucket], 1)] = (int32_t)pair;
+  const int at = atomicAdd(&p.cursors[bucket], 1);
+  p.order[at] = (int32_t)pair;
+  p.order_takes[at] = p.takes[pair];
 }
 
 // A thread a bucket writes the table of its segments, so a CTA of the attend pass finds its work with one load.
@@ -434,7 +439,7 @@ __global__ void __launch_bounds__(256) bucket_merge_kernel(BucketParams p) {
 }
 
 struct BucketWorkspace {
-  size_t starts, counts, offsets, seg_offsets, cursors, order, segments, part_out, part_lse, total;
+  size_t starts, counts, offsets, seg_offsets, cursors, order, takes, order_takes, segments, part_out, part_lse, total;
 };
 
 // Every bucket with pairs has at most one ragged segment: segments <= pairs / segment + buckets with pairs.
@@ -454,6 +459,8 @@ static BucketWorkspace bucket_workspace(int64_t R, int top_p, int Hq, int dh, in
   w.seg_offsets = at, at += up((size_t)(m + 1) * 4);
   w.cursors = at, at += up((size_t)(m + 1) * 4);
   w.order = at, at += up(pairs * 4);
+  w.takes = at, at += up(pairs * 4);
+  w.order_takes = at, at += up(pairs * 4);
   w.segments = at, at += up((size_t)segment_bound(R, top_p, m) * 16);
   w.part_out = at, at += up(pairs * Hq * dh * 2);
   w.part_lse = at, at += up(pairs * Hq * 4);
@@ -506,6 +513,8 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   p.seg_offsets = reinterpret_cast<int32_t *>(base + w.seg_offsets);
   p.cursors = reinterpret_cast<int32_t *>(base + w.cursors);
   p.order = reinterpret_cast<int32_t *>(base + w.order);
+  p.takes = reinterpret_cast<int32_t *>(base + w.takes);
+  p.order_takes = reinterpret_cast<int32_t *>(base + w.order_takes);
   p.segments = reinterpret_cast<int4 *>(base + w.segments);
   p.part_out = reinterpret_cast<uint16_t *>(base + w.part_out);
   p.part_lse = reinterpret_cast<float *>(base + w.part_lse);

@@ -23,6 +23,8 @@ struct BucketParams {
   int32_t *seg_offsets;    // [m + 1] exclusive scan of ceil(counts / segment)
   int32_t *cursors;        // [m]
   int32_t *order;          // [R * top_p] pair ids grouped by bucket
+  int32_t *takes;          // [R * top_p] keys of its bucket a pair reads (0 = none), by pair
+  int32_t *order_takes;    // [R * top_p] the same beside `order`, so a CTA fetches both with one round of loads
   int4 *segments;          // [segment bound] bucket, first pair in `order`, pairs: what a CTA of the attend pass runs
   uint16_t *part_out;      // [R * top_p, Hq, dh] bf16
   float *part_lse;         // [R * top_p, Hq]

@@ -167,12 +167,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     }
     if (w < kBktSegment) {
       int32_t pair = -1, q_row = 0, hi = 0;
-      if (w < n_pairs) {
+      if (w < n_pairs) {  // (the starts pass has counted the keys a pair takes: its run of members starts at the sinks' end)
         pair = p.order[first + w];
+        hi = lo_key + p.order_takes[first + w];
         q_row = pair / p.top_p;
-        const int64_t pos = p.positions[q_row];
-        const int row_k = p.row_top_k ? min(p.row_top_k[q_row], p.top_k) : p.top_k;
-        hi = min(members_below(max((int64_t)0, pos + 1 - p.window)), lo_key + row_k - p.starts[pair]);
       }
       pairs_s[w] = pair, qrows_s[w] = q_row, hi_s[w] = hi;
     }

@@ -11,8 +11,8 @@ from helpers import cuda, layer_inputs, mixture, unit_rows
 pytestmark = pytest.mark.gpu
 
 
-def _case(oracle, seed=5):
-    T, Hq, Hkv, dh, d = 3072, 10, 2, 128, 32
+def _case(oracle, seed=5, Hq=10, Hkv=2):
+    T, dh, d = 3072, 128, 32
     q, k, v = layer_inputs(T, Hq, Hkv, dh, 16, seed)
     raw = mixture(T, d, 24, 0.3, seed + 1)
     buckets = oracle.build_buckets(unit_rows(raw), 4, 16, 32, 256)
@@ -48,6 +48,27 @@ def test_bucket_major_read_matches_the_oracle_and_the_gather_path(oracle, top_p,
     lists, lens, _ = ops.expand(pk, pos, mem, top_k, sink, window, local=False)
     gathered, _ = ops.sparse_attend(rows, K, V, lists, lens, scale, init=band)
     _close(out.float().cpu().numpy(), gathered.float().cpu().numpy(), "gather path")
+
+
+@pytest.mark.parametrize("warp_mma", [False, True])
+@pytest.mark.parametrize("Hq,Hkv", [(2, 2), (6, 2), (8, 2), (7, 1), (8, 1)])
+def test_bucket_major_read_over_head_groups(oracle, Hq, Hkv, warp_mma):
+    """Groups of 1, 3, 4, 7 and 8 query heads a KV head: a tile of the tcgen05 pass holds (pair, head) rows, so the
+    group decides where a pair's rows sit and which tile they fall in."""
+    from lsa_b200 import ops
+
+    q, k, v, buckets, positions, index_q, first = _case(oracle, seed=7, Hq=Hq, Hkv=Hkv)
+    sink, window, scale, top_p, top_k = 4, 128, 128 ** -0.5, 12, 300
+    want_lists, want_len, picked, _ = oracle.read(index_q, positions, buckets, top_p, top_k, sink, window,
+                                                  return_picked=True)
+    Q, K, V = (cuda(a, torch.bfloat16) for a in (q, k, v))
+    rows = Q[first:first + len(positions)]
+    pos, mem, pk = cuda(positions), cuda(buckets.bucket_members), cuda(picked)
+    band = ops.band_attend(rows, K, V, first, window, sink, scale)
+    out, lse = ops.bucket_attend(rows, K, V, pk, pos, mem, top_k, sink, window, scale, init=band, warp_mma=warp_mma)
+    want, want_lse = oracle.sparse_attend(q[positions], k, v, want_lists, positions, 0, 0, scale, lengths=want_len)
+    _close(out.float().cpu().numpy(), want, "oracle")
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
 
 
 @pytest.mark.parametrize("warp_mma", [False, True])
