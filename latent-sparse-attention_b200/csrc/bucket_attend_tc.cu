@@ -174,23 +174,26 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       }
       pairs_s[w] = pair, qrows_s[w] = q_row, hi_s[w] = hi;
     }
+    // Rows come in, are listed and go out a QUARTER at a time: the two warps that share the tensor-memory lanes of 32
+    // rows also copy those rows, so the only barriers inside a tile are between those two warps.
+    const int w64 = half * 32 + lane;  // the thread's place among the 64 of its quarter
     auto list_rows = [&](int tile) {
-      if (w >= kTcRows) return;
-      const int flat = tile * kTcRows + w;
+      if (half != 0) return;
+      const int flat = tile * kTcRows + row;
       const bool ok = flat < n_rows;
       const int pl = ok ? flat / p.group : 0;
       const int head = h * p.group + (flat - pl * p.group);
-      src_s[tile % 3][w] = ok ? (int64_t)qrows_s[pl] * p.q_row_stride + (int64_t)head * p.q_head_stride : -1;
-      dst_s[tile % 3][w] = ok ? (int64_t)pairs_s[pl] * p.Hq + head : -1;
-      end_s[tile % 3][w] = ok ? hi_s[pl] : 0;
+      src_s[tile % 3][row] = ok ? (int64_t)qrows_s[pl] * p.q_row_stride + (int64_t)head * p.q_head_stride : -1;
+      dst_s[tile % 3][row] = ok ? (int64_t)pairs_s[pl] * p.Hq + head : -1;
+      end_s[tile % 3][row] = ok ? hi_s[pl] : 0;
     };
     // The query rows of a tile: half a warp copies a row of 256 bytes, in the layout of the keys.
     auto gather_q = [&](int tile) {
       const uint32_t buf = base + kTcQOff + (tile & 1) * 2 * kTcQPlane;
 #pragma unroll 4
-      for (int j = 0; j < kTcRows * 16 / kTcThreads; ++j) {
-        const int e = j * kTcThreads + w;
-        const int r = e >> 4, chunk = e & 15;
+      for (int j = 0; j < 32 * 16 / 64; ++j) {
+        const int e = j * 64 + w64;
+        const int r = quarter * 32 + (e >> 4), chunk = e & 15;
         const int64_t from = src_s[tile % 3][r];
         cp_async_16(buf + (chunk >> 3) * kTcQPlane + r * 128 + (((chunk & 7) ^ (r & 7)) << 4),
                     p.q + (from >= 0 ? from + chunk * 8 : 0), from >= 0 ? 16 : 0);
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     __syncthreads();  // the segment's pairs are written
     list_rows(0);
     if (n_tiles > 1) list_rows(1);
-    __syncthreads();  // and the first tiles' rows
+    quarter_sync(quarter);  // and the first tiles' rows of this quarter
     gather_q(0);
     cp_async_commit();
     if (n_tiles > 1) gather_q(1);
@@ -320,30 +323,32 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
             const uint32_t b = pack_bf16x2(__uint_as_float(r[c][8 * i + 2]), __uint_as_float(r[c][8 * i + 3]));
             const uint32_t d = pack_bf16x2(__uint_as_float(r[c][8 * i + 4]), __uint_as_float(r[c][8 * i + 5]));
             const uint32_t f = pack_bf16x2(__uint_as_float(r[c][8 * i + 6]), __uint_as_float(r[c][8 * i + 7]));
-            const int chunk = half * (DH / 16) + c * 4 + i;
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + row * 256 + ((chunk ^ (row & 7)) << 4)),
+            // (the thread's half of the columns is a plane of the buffer, laid out as the query rows were: a quarter's
+            // rows stay inside the bytes that the quarter itself fills again)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + half * kTcQPlane + row * 128 +
+                                                                           (((c * 4 + i) ^ (row & 7)) << 4)),
                          "r"(a), "r"(b), "r"(d), "r"(f)
                          : "memory");
           }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();  // the tile's rows are staged
+      quarter_sync(quarter);  // the quarter's rows are staged
       if (go) {
 #pragma unroll 4
-        for (int j = 0; j < kTcRows * 16 / kTcThreads; ++j) {
-          const int e = j * kTcThreads + w;
-          const int r = e >> 4, chunk = e & 15;
+        for (int j = 0; j < 32 * 16 / 64; ++j) {
+          const int e = j * 64 + w64;
+          const int r = quarter * 32 + (e >> 4), chunk = e & 15;
           const int64_t to = dst_s[tile % 3][r];
           if (to < 0) continue;
           uint4 piece;
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(piece.x), "=r"(piece.y), "=r"(piece.z), "=r"(piece.w)
-                       : "r"(buf + r * 256 + ((chunk ^ (r & 7)) << 4)));
+                       : "r"(buf + (chunk >> 3) * kTcQPlane + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)));
           *reinterpret_cast<uint4 *>(p.part_out + to * DH + chunk * 8) = piece;
         }
       }
       if (tile + 2 < n_tiles) list_rows(tile + 2);
-      __syncthreads();  // the buffer has been read out, and the rows of the tile after next are listed
+      quarter_sync(quarter);  // the quarter's rows have been read out, and those of the tile after next are listed
       if (tile + 2 < n_tiles) gather_q(tile + 2);
       cp_async_commit();
     }
