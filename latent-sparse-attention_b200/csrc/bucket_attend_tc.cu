@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   __shared__ int32_t ids_s[kBktKeys];
   __shared__ int32_t pairs_s[kBktSegment];   // the segment's pairs, -1 past its end
   __shared__ int32_t qrows_s[kBktSegment];   // their query rows
-  __shared__ int32_t hi_s[kBktSegment];      // end of their index range of the bucket's members
+  __shared__ int32_t hi_s[kBktSegment];      // members of the bucket they read
   // of the rows of a tile (a ring of three tiles): where the query row starts in q (-1 past the end), which slot of
   // the partial outputs it fills, and the end of its key range
   __shared__ int64_t src_s[3][kTcRows], dst_s[3][kTcRows];
@@ -94,6 +94,16 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   for (int i = tid; i < kBktKeys; i += kTcThreads) ids_s[i] = i < p.cap ? p.members[bucket * p.cap + i] : LSA_PAD;
+  // The segment's pairs, fetched beside the member ids (one round of loads for both). The starts pass has counted the
+  // keys a pair takes; its run of members starts where the sinks end, which is added once the ids are in.
+  if (tid < kBktSegment) {
+    int32_t pair = -1, take = 0;
+    if (tid < n_pairs) {
+      pair = p.order[first + tid];
+      take = p.order_takes[first + tid];
+    }
+    pairs_s[tid] = pair, qrows_s[tid] = pair >= 0 ? pair / p.top_p : 0, hi_s[tid] = take;
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -165,15 +175,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
         cp_async_16(base + kTcVOff + dst, v_head + off, ok ? 16 : 0);
       }
     }
-    if (w < kBktSegment) {
-      int32_t pair = -1, q_row = 0, hi = 0;
-      if (w < n_pairs) {  // (the starts pass has counted the keys a pair takes: its run of members starts at the sinks' end)
-        pair = p.order[first + w];
-        hi = lo_key + p.order_takes[first + w];
-        q_row = pair / p.top_p;
-      }
-      pairs_s[w] = pair, qrows_s[w] = q_row, hi_s[w] = hi;
-    }
     // Rows come in, are listed and go out a QUARTER at a time: the two warps that share the tensor-memory lanes of 32
     // rows also copy those rows, so the only barriers inside a tile are between those two warps.
     const int w64 = half * 32 + lane;  // the thread's place among the 64 of its quarter
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       const int head = h * p.group + (flat - pl * p.group);
       src_s[tile % 3][row] = ok ? (int64_t)qrows_s[pl] * p.q_row_stride + (int64_t)head * p.q_head_stride : -1;
       dst_s[tile % 3][row] = ok ? (int64_t)pairs_s[pl] * p.Hq + head : -1;
-      end_s[tile % 3][row] = ok ? hi_s[pl] : 0;
+      end_s[tile % 3][row] = ok ? lo_key + hi_s[pl] : 0;
     };
     // The query rows of a tile: half a warp copies a row of 256 bytes, in the layout of the keys.
     auto gather_q = [&](int tile) {
@@ -199,7 +200,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
                     p.q + (from >= 0 ? from + chunk * 8 : 0), from >= 0 ? 16 : 0);
       }
     };
-    __syncthreads();  // the segment's pairs are written
     list_rows(0);
     if (n_tiles > 1) list_rows(1);
     quarter_sync(quarter);  // and the first tiles' rows of this quarter
