@@ -39,9 +39,16 @@ __global__ void __launch_bounds__(256) bucket_starts_kernel(BucketParams p) {
     int mine = 0;
     if (bucket >= 0) {
       const int32_t *row = p.members + bucket * p.cap;
-      for (int j = 0; j < p.cap; ++j) {
-        const int32_t id = row[j];
-        mine += (id >= p.sink && id < window_start) ? 1 : 0;
+      auto counts = [&](int32_t id) { return (id >= p.sink && id < window_start) ? 1 : 0; };
+      if ((p.cap & 3) == 0 && (reinterpret_cast<uintptr_t>(p.members) & 15) == 0) {
+        const int4 *row4 = reinterpret_cast<const int4 *>(row);
+#pragma unroll 4
+        for (int j = 0; j < p.cap / 4; ++j) {
+          const int4 ids = row4[j];
+          mine += counts(ids.x) + counts(ids.y) + counts(ids.z) + counts(ids.w);
+        }
+      } else {
+        for (int j = 0; j < p.cap; ++j) mine += counts(row[j]);
       }
     }
     // exclusive scan of the counts over the 32 picks
