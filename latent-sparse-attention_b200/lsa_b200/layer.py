@@ -125,31 +125,55 @@ class FlatLayer:
 
         With `reuse_buffers` the index lives in the layer's own buffers and is overwritten by the next build.
         """
-        d, dev = self.design, k.device
-        T, d_idx = k.shape[0], self.key_map.shape[1]
+        bufs = self._index_buffers(k.shape[0], k.device, reuse_buffers)
+        self._build_blocks(k, 0, bufs)
+        return self._index_of(bufs)
+
+    def _index_buffers(self, T: int, dev, reuse_buffers: bool) -> dict:
+        """The tensors an index over T keys lives in (the layer's own buffers, or fresh ones)."""
+        d, d_idx = self.design, self.key_map.shape[1]
         blocks = T // d.cluster_block_size
-        P, per_block = d.cluster_block_size // d.pool_size, d.block_bucket_count
-        rows = blocks * per_block
+        P, rows = d.cluster_block_size // d.pool_size, blocks * d.block_bucket_count
         make = (lambda name, shape, dtype: self._buffer(name, shape, dtype, dev)) if reuse_buffers else \
             (lambda name, shape, dtype: torch.empty(shape, device=dev, dtype=dtype))
+        bufs = {"keys": make("index keys", (T, d_idx), torch.float32),
+                "pools": make("pools", (blocks, P, d_idx), torch.float32),
+                "labels": make("labels", (blocks, P), torch.int64), "reached": make("reached", (blocks,), torch.uint8),
+                "status": make("table status", (1,), torch.int32),
+                "members": make("members", (rows, d.bucket_cap), torch.int32), "sizes": make("sizes", (rows,), torch.int32),
+                "key sums": make("key sums", (rows, d_idx), torch.float32),
+                "centroids": make("centroids", (rows, d_idx), torch.float32)}
+        bufs["status"].zero_()
+        return bufs
+
+    def _index_of(self, bufs: dict) -> FlatIndex:
+        d = self.design
+        return FlatIndex(bufs["keys"], Buckets(bufs["centroids"], bufs["members"], bufs["sizes"], d.block_bucket_count,
+                                               d.cluster_block_size))
+
+    def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
+        """Index keys of k [n, Hkv, dh] = the keys at positions first.., and the pools, Ward labels and bucket table of
+        the cluster blocks they close (first is a multiple of the block size): blocks are independent, so an index
+        can be built as its keys arrive."""
+        d = self.design
+        n = k.shape[0]
+        b0, nb = first // d.cluster_block_size, n // d.cluster_block_size
+        r0, r1 = b0 * d.block_bucket_count, (b0 + nb) * d.block_bucket_count
         with probe.region("index map"):
-            keys = self.index_keys(k, out=make("index keys", (T, d_idx), torch.float32))
+            keys = self.index_keys(k, out=bufs["keys"][first:first + n])
+        if nb == 0:
+            return
         with probe.region("pool"):
-            pools = ops.pool_keys(keys[: blocks * d.cluster_block_size].view(blocks, d.cluster_block_size, -1),
-                                  d.pool_size, out=make("pools", (blocks, P, d_idx), torch.float32))
+            pools = ops.pool_keys(keys[: nb * d.cluster_block_size].view(nb, d.cluster_block_size, -1), d.pool_size,
+                                  out=bufs["pools"][b0:b0 + nb])
         with probe.region("ward"):
-            labels, _ = ops.ward_rounds(pools, float(d.pool_size), per_block, d.bucket_cap,
-                                        labels=make("labels", (blocks, P), torch.int64),
-                                        reached=make("reached", (blocks,), torch.uint8))
+            labels, _ = ops.ward_rounds(pools, float(d.pool_size), d.block_bucket_count, d.bucket_cap,
+                                        labels=bufs["labels"][b0:b0 + nb], reached=bufs["reached"][b0:b0 + nb])
         with probe.region("bucket table"):
-            status = make("table status", (1,), torch.int32)
-            status.zero_()
-            outs = (make("members", (rows, d.bucket_cap), torch.int32), make("sizes", (rows,), torch.int32),
-                    make("key sums", (rows, d_idx), torch.float32), make("centroids", (rows, d_idx), torch.float32),
-                    None, status)
-            members, sizes, _, centroids, _, _ = ops.bucket_table(keys, labels, d.pool_size, per_block, d.bucket_cap,
-                                                                 outs=outs)
-        return FlatIndex(keys, Buckets(centroids, members, sizes, per_block, d.cluster_block_size))
+            outs = (bufs["members"][r0:r1], bufs["sizes"][r0:r1], bufs["key sums"][r0:r1], bufs["centroids"][r0:r1],
+                    None, bufs["status"])
+            ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count, d.bucket_cap, first_position=first,
+                             outs=outs)
 
     def pick(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
              reuse_buffers: bool = False):
@@ -228,19 +252,23 @@ class FlatLayer:
 
     def prefill_from_host(self, q_host: torch.Tensor, k_host: torch.Tensor, v_host: torch.Tensor,
                           out_host: torch.Tensor, chunk: int = 8192) -> torch.Tensor:
-        """`prefill` for inputs and an output that live in PINNED host memory, the copies overlapped with the work:
-        K and V cross first (the index needs them), the query chunks follow on a copy stream while earlier chunks
-        are read, and every chunk's output leaves on a second copy stream as soon as its merge is done. On return
-        the current stream has waited for the last output copy; synchronise it before reading `out_host`."""
+        """`prefill` for inputs and an output that live in PINNED host memory, the copies overlapped with the work.
+        A causal chunk needs the keys and values up to its own end and the buckets of the cluster blocks before its
+        rows, and blocks are clustered independently: so K, V and Q cross chunk by chunk on a copy stream, each
+        chunk's blocks are indexed when its keys have arrived, and every chunk's output leaves on a second copy
+        stream as soon as its merge is done. (`chunk` must hold whole cluster blocks.) On return the current stream
+        has waited for the last output copy; synchronise it before reading `out_host`."""
         dev = self.query_map.device
         T = q_host.shape[0]
+        if chunk % self.design.cluster_block_size or chunk % 128:
+            raise ValueError("a chunk must hold whole cluster blocks (and whole tiles of 128 keys)")
         main = torch.cuda.current_stream(dev)
         if self._copy_in is None:
             self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         chunks = [(start, min(T, start + chunk)) for start in range(0, T, chunk)]
         while len(self._copy_events) < 2 * len(chunks) + 1:
             self._copy_events.append(torch.cuda.Event())
-        kv_ready, arrived, done = self._copy_events[0], self._copy_events[1::2], self._copy_events[2::2]
+        arrived, done = self._copy_events[1::2], self._copy_events[2::2]
         q = self._buffer("q from host", tuple(q_host.shape), q_host.dtype, dev)
         k = self._buffer("k from host", tuple(k_host.shape), k_host.dtype, dev)
         v = self._buffer("v from host", tuple(v_host.shape), v_host.dtype, dev)
@@ -248,17 +276,18 @@ class FlatLayer:
         self._copy_in.wait_stream(main)   # the last call's reads of these buffers are over
         self._copy_out.wait_stream(main)
         with torch.cuda.stream(self._copy_in):
-            k.copy_(k_host, non_blocking=True)
-            v.copy_(v_host, non_blocking=True)
-            kv_ready.record(self._copy_in)
             for c, (start, stop) in enumerate(chunks):
+                k[start:stop].copy_(k_host[start:stop], non_blocking=True)
+                v[start:stop].copy_(v_host[start:stop], non_blocking=True)
                 q[start:stop].copy_(q_host[start:stop], non_blocking=True)
                 arrived[c].record(self._copy_in)
-        main.wait_event(kv_ready)
-        index = self.build_index(k, reuse_buffers=True)
+        bufs = self._index_buffers(T, dev, reuse_buffers=True)
+        index = self._index_of(bufs)
         for c, (start, stop) in enumerate(chunks):
             main.wait_event(arrived[c])
-            self.prefill_rows(q[start:stop], start, k, v, index, out[start:stop])
+            self._build_blocks(k[start:stop], start, bufs)
+            # (the cache as far as it has arrived: no kernel is handed rows that are still on their way)
+            self.prefill_rows(q[start:stop], start, k[:stop], v[:stop], index, out[start:stop])
             done[c].record(main)
             with torch.cuda.stream(self._copy_out):
                 self._copy_out.wait_event(done[c])
