@@ -227,34 +227,56 @@ class ShardedFlatLayer:
         if T % chunk or chunk % world:
             raise ValueError(f"{T} tokens must split into chunks of {chunk} rows, and a chunk over {world} ranks")
         centroids, members, _ = self.build_index(k_share, T)
-        per_block = d.block_bucket_count
         share = chunk // world
         if out is None:
             out = torch.empty(T // world, q.shape[1], q.shape[2], dtype=q.dtype, device=q.device)
         for c, start in enumerate(range(0, T, chunk)):
             rows = q[start:start + chunk]
             positions = torch.arange(start, start + chunk, device=q.device)
-            with probe.region("index map"):
-                index_queries = layer.index_queries(rows)
-            # closed blocks b < n with b % world == rank: ceil((n - rank) / world) of this rank's blocks are visible
-            closed = positions // d.cluster_block_size
-            visible = (((closed - rank + world - 1) // world).clamp_min(0) * per_block).clamp_max(
-                centroids.shape[0]).to(torch.int32)
-            with probe.region("select"):
-                keys, _ = ops.flat_select(index_queries, centroids, visible, d.top_p)
-                keys = globalise_keys(keys, per_block, rank, world)
-            with probe.region("exchange candidates"):
-                every = gather_candidates(keys, self.group)
-            with probe.region("select"):
-                _, picked = ops.merge_candidates(every)
-            with probe.region("expand"):
-                lists, lengths, _ = ops.expand(picked, positions, members, d.top_k, d.sink_size, d.window_size,
-                                               dealt=(self.granule, world, rank))
-            with probe.region("attend"):
-                partial, lse = ops.sparse_attend(rows, k_share, v_share, lists, lengths, layer.scale,
-                                                 out_dtype=torch.float32)
+            partial, lse = self._read_rows(rows, positions, centroids, members, k_share, v_share)
             with probe.region("merge partials"):
                 weight, _ = merge_weight(lse, self.group)
                 partial *= weight[..., None]
                 out[c * share:(c + 1) * share] = reduce_rows(partial, self.group).to(out.dtype)
         return out
+
+    def _read_rows(self, rows: torch.Tensor, positions: torch.Tensor, centroids: torch.Tensor, members: torch.Tensor,
+                   k_share: torch.Tensor, v_share: torch.Tensor, splits: int = 1) -> tuple:
+        """This rank's part of the read of replicated query rows: the buckets are picked together (every rank scores
+        the centroids of the blocks it clustered, the candidates are all-gathered and cut), then the rank expands and
+        attends over the ids it stores. Returns its partial output (fp32) and log-sum-exp per (row, head)."""
+        layer, d, world, rank = self.layer, self.design, self.world, self.rank
+        per_block = d.block_bucket_count
+        with probe.region("index map"):
+            index_queries = layer.index_queries(rows)
+        # closed blocks b < n with b % world == rank: ceil((n - rank) / world) of this rank's blocks are visible
+        closed = positions // d.cluster_block_size
+        visible = (((closed - rank + world - 1) // world).clamp_min(0) * per_block).clamp_max(
+            centroids.shape[0]).to(torch.int32)
+        with probe.region("select"):
+            keys, _ = ops.flat_select(index_queries, centroids, visible, d.top_p)
+            keys = globalise_keys(keys, per_block, rank, world)
+        with probe.region("exchange candidates"):
+            every = gather_candidates(keys, self.group)
+        with probe.region("select"):
+            _, picked = ops.merge_candidates(every)
+        with probe.region("expand"):
+            lists, lengths, _ = ops.expand(picked, positions, members, d.top_k, d.sink_size, d.window_size,
+                                           dealt=(self.granule, world, rank))
+        with probe.region("attend"):
+            return ops.sparse_attend(rows, k_share, v_share, lists, lengths, layer.scale, splits=splits,
+                                     out_dtype=torch.float32)
+
+    def decode(self, q: torch.Tensor, positions: torch.Tensor, k_share: torch.Tensor, v_share: torch.Tensor,
+               index: tuple, splits: int = 8) -> torch.Tensor:
+        """One step for replicated rows q [R, Hq, dh] at `positions` over the dealt cache (`index` = what
+        `build_index` returned): every rank reads the keys it stores and the partial outputs are merged by their
+        log-sum-exps with one all-reduce, so every rank returns the whole [R, Hq, dh] bf16 output. A decode step has
+        too few rows to split: context parallel is its only split."""
+        centroids, members, _ = index
+        partial, lse = self._read_rows(q, positions.to(torch.int64), centroids, members, k_share, v_share, splits)
+        with probe.region("merge partials"):
+            weight, _ = merge_weight(lse, self.group)
+            partial *= weight[..., None]
+            dist.all_reduce(partial, group=self.group)
+        return partial.to(q.dtype)

@@ -56,6 +56,16 @@ def _rank_main(rank, world, port, result_dir):
             err = (split.float() - mine.float()).abs()
             assert split.shape == mine.shape
             assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+        # a decode step over the dealt cache: replicated rows, every rank returns the whole output
+        k_share, v_share = deal(k, rank, world).contiguous(), deal(v, rank, world).contiguous()
+        index = sharded.build_index(k_share, T)
+        _, single = layer.prefill(q, k, v, chunk=chunk, return_index=True)
+        rows = torch.tensor([5, 511, 512, 4000, T - 1], device="cuda")
+        for splits in (1, 4):
+            step = sharded.decode(q[rows], rows, k_share, v_share, index, splits=splits)
+            alone = layer.decode(q[rows], rows, k, v, single, splits=splits)
+            err = (step.float() - alone.float()).abs()
+            assert step.shape == alone.shape and err.max().item() <= 2e-2, err.max().item()
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
