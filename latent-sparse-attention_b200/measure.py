@@ -5,6 +5,8 @@ beside it on a stated sample, and a parity check of the measured path against th
     python latent-sparse-attention_b200/measure.py tree-decode   [--tokens 1048576] [--steps 256]
     python latent-sparse-attention_b200/measure.py batched-decode [--requests 64] [--steps 64]
     python latent-sparse-attention_b200/measure.py latent-layer   [--tokens 10485760] [--chunk 8192] [--splits 148]
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        latent-sparse-attention_b200/measure.py sharded-decode [--tokens 1048576] [--steps 256]
 
 Inputs are seeded synthetic tensors with the shapes of the benchmark configurations.
 """
@@ -373,9 +375,66 @@ def latent_layer(args) -> dict:
                              "sample": f"read of {len(rows)} rows and attend of 2 rows, per-row times summed"}}
 
 
+def sharded_decode(args) -> dict:
+    """One decode row of the flat design (config 2's index parameters) over a cache dealt across the ranks of a
+    torchrun launch (`ShardedFlatLayer.decode`: every rank scores the centroids of its blocks, the candidates are
+    all-gathered and cut, each rank reads the keys it stores, the partial outputs merge with one all-reduce).
+    Eager launches (the step holds NCCL calls), device time from CUDA events, max over ranks; at one rank the
+    single-GPU step is timed beside it and the outputs are compared."""
+    import torch.distributed as dist
+
+    from lsa_b200.parallel import ShardedFlatLayer, deal
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    heads, kv_heads, dh = 40, 8, 128
+    design = FlatDesign(pool_size=16, bucket_size=32, bucket_cap=64, cluster_block_size=1024, top_p=64, top_k=4096,
+                        sink_size=4, window_size=1024)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    k, v = clustered_cache(args.tokens, kv_heads, dh, 256, gen)
+    maps = torch.randn(2, kv_heads * dh, 64, generator=gen, device="cuda") / math.sqrt(kv_heads * dh)
+    layer = FlatLayer(design, maps[0].bfloat16(), maps[1].bfloat16(), heads, kv_heads, dh)
+    sharded = ShardedFlatLayer(layer, rank, world)
+    k_share, v_share = deal(k, rank, world).contiguous(), deal(v, rank, world).contiguous()
+    index = sharded.build_index(k_share, args.tokens)
+    position = torch.tensor([args.tokens - 1], device="cuda")
+    q = (k[-1:].repeat_interleave(heads // kv_heads, dim=1).float() +
+         0.5 * torch.randn(1, heads, dh, generator=gen, device="cuda")).bfloat16()
+    single = layer.build_index(k) if world == 1 else None
+    del k, v
+
+    def timed(step) -> float:
+        for _ in range(8):
+            step()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dist.barrier()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        torch.cuda.synchronize()
+        us = torch.tensor([start.elapsed_time(stop) * 1e3 / args.steps], device="cuda")
+        dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        return float(us)
+
+    us = timed(lambda: sharded.decode(q, position, k_share, v_share, index, splits=args.splits))
+    result = {"metric": "flat decode us/step over a dealt cache", "value": us, "unit": "us", "n_gpus": world,
+              "steps": args.steps, "config": {"workload": "C2 index parameters, one row at the end of the context",
+                                              "tokens": args.tokens, "splits": args.splits}}
+    if world == 1:
+        out = sharded.decode(q, position, k_share, v_share, index, splits=args.splits)
+        alone = layer.decode(q, position, k_share, v_share, single, splits=args.splits)
+        result["single_gpu_us"] = timed(lambda: layer.decode(q, position, k_share, v_share, single, splits=args.splits))
+        result["gap_to_single_gpu_step"] = float((out.float() - alone.float()).abs().max())
+    dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
-    parser.add_argument("what", choices=["tree-decode", "batched-decode", "latent-layer"])
+    parser.add_argument("what", choices=["tree-decode", "batched-decode", "latent-layer", "sharded-decode"])
     parser.add_argument("--chunk", type=int, default=8192)
     parser.add_argument("--tokens", type=int, default=1 << 20)
     parser.add_argument("--steps", type=int, default=256)
@@ -386,6 +445,11 @@ def main() -> None:
     parser.add_argument("--max-len", type=int, default=524288)
     parser.add_argument("--check", type=int, default=4)
     args = parser.parse_args()
+    if args.what == "sharded-decode":  # under torchrun, one rank a GPU
+        result = sharded_decode(args)
+        if result:
+            print(json.dumps(result))
+        return
     torch.cuda.set_device(0)
     result = {"tree-decode": tree_decode, "batched-decode": batched_decode, "latent-layer": latent_layer}[args.what](args)
     print(json.dumps(result))
