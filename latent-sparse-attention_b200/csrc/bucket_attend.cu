@@ -6,7 +6,7 @@
 //   starts    a warp a row walks the row's picks in order and records, for each, how many selected ids came before
 //             it (the top-k cut needs that) - or -1 when the pick adds nothing
 //   invert    the (row, pick) pairs are grouped by bucket: histogram, scan, scatter
-//   attend    a CTA owns (bucket, KV head, segment of 128 pairs): the bucket's K/V rows are staged ONCE in shared
+//   attend    a CTA owns (bucket, KV head, segment of 128 or 256 pairs): the bucket's K/V rows are staged ONCE in shared
 //             memory, each warp takes one query head of the group and runs its pairs through them in tiles of 16
 //             query rows (queries as the M side of mma.m16n8k16), writing a normalised bf16 partial output and a
 //             log-sum-exp per (pair, head)
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(1024) bucket_scan_kernel(BucketParams p) {
   for (int64_t base = 0; base < p.m; base += 1024) {
     const int64_t b = base + tid;
     const int c = b < p.m ? p.counts[b] : 0;
-    const int s = (c + kBktSegment - 1) / kBktSegment;
+    const int s = (c + p.segment - 1) / p.segment;
     int ic = c, is = s;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -137,8 +137,8 @@ __global__ void __launch_bounds__(256) bucket_segments_kernel(BucketParams p) {
   const int64_t b = (int64_t)blockIdx.x * 256 + threadIdx.x;
   if (b >= p.m) return;
   const int count = p.counts[b], first = p.offsets[b], at = p.seg_offsets[b];
-  for (int s = 0; s * kBktSegment < count; ++s)
-    p.segments[at + s] = make_int4((int)b, first + s * kBktSegment, min(kBktSegment, count - s * kBktSegment), 0);
+  for (int s = 0; s * p.segment < count; ++s)
+    p.segments[at + s] = make_int4((int)b, first + s * p.segment, min(p.segment, count - s * p.segment), 0);
 }
 
 // ---------------------------------------------------------------------------------------------- attend
@@ -530,6 +530,8 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   p.kv_row_stride = kv_row_stride, p.kv_head_stride = kv_head_stride;
   p.top_p = top_p, p.cap = bucket_cap, p.top_k = top_k, p.sink = sink, p.window = window;
   p.Hq = Hq, p.Hkv = Hkv, p.group = Hq / Hkv;
+  const bool tensor_memory = !(flags & LSA_BUCKET_WARP_MMA) && R * top_p * Hq < INT32_MAX;
+  p.segment = tensor_memory ? lsa::kBktSegmentTc : lsa::kBktSegment;
   p.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   if (cudaMemsetAsync(p.counts, 0, (size_t)(m + 1) * 4, s) != cudaSuccess) return LSA_ERR_LAUNCH;
@@ -544,7 +546,7 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
     lsa::bucket_segments_kernel<<<(unsigned)((m + 255) / 256), 256, 0, s>>>(p);
     LSA_LAUNCH_CHECK();
     const int64_t bound = lsa::segment_bound(R, top_p, m);
-    if (flags & LSA_BUCKET_WARP_MMA) {
+    if (!tensor_memory) {
       const size_t smem = 2 * (size_t)lsa::kBktKeys * dh * 2 + (size_t)p.group * lsa::kBktTile * dh * 2;
       if (cudaFuncSetAttribute(lsa::bucket_attend_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)smem) != cudaSuccess)

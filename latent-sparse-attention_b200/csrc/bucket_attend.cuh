@@ -6,7 +6,8 @@
 namespace lsa {
 
 constexpr int kBktKeys = 64;     // members a bucket may hold here (the tile of keys a CTA stages)
-constexpr int kBktSegment = 128;  // (row, pick) pairs a CTA runs through its bucket
+constexpr int kBktSegment = 128;  // (row, pick) pairs a CTA of the warp-level pass runs through its bucket
+constexpr int kBktSegmentTc = 256;  // and of the tcgen05 pass: twice the tiles for one staging of the bucket
 constexpr int kBktTile = 16;     // query rows a warp multiplies at once
 
 struct BucketParams {
@@ -30,6 +31,7 @@ struct BucketParams {
   float *part_lse;         // [R * top_p, Hq]
   int64_t R, m, slots, q_row_stride, q_head_stride, kv_row_stride, kv_head_stride;
   int top_p, cap, top_k, sink, window, Hq, Hkv, group;
+  int segment;             // pairs a segment, at most: kBktSegment or kBktSegmentTc
   float scale_log2;
 };
 

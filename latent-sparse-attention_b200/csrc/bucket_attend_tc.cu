@@ -1,6 +1,6 @@
 // The attend pass of the bucket-major attention on the fifth-generation tensor cores.
 //
-// A CTA owns (bucket, KV head, segment of up to 128 (row, pick) pairs). The M = 128 rows of a tile are (pair, query
+// A CTA owns (bucket, KV head, segment of up to 256 (row, pick) pairs). The M = 128 rows of a tile are (pair, query
 // head of the KV head's group) couples, the heads of a pair next to one another, so a ragged segment of n pairs
 // costs ceil(n * group / 128) tiles and not `group` of them. A row of S and of O lives in one lane of tensor memory
 // and the thread that owns the row does its softmax without talking to anyone:
@@ -41,7 +41,7 @@ constexpr int kTcQOff = 4 * kTcPlane;           // Q: 2 buffers of 2 planes
 // finished rows of O are staged in the whole of it (the second product is over by then).
 constexpr int kTcSmem = kTcQOff + 4 * kTcQPlane + 1024;  // + room to align the base to 1,024 bytes
 constexpr int kTcTmemCols = 256;                // S in columns 0-63, O in 64-191
-static_assert(kBktSegment == kTcRows && kBktKeys == 64, "the tile shapes of the tensor-core attend pass");
+static_assert(kBktSegmentTc == kTcThreads && kBktKeys == 64, "a thread a pair of the segment; 64 keys a bucket");
 
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -56,12 +56,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   static_assert(DH == 128, "two planes of 64 dims");
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ int32_t ids_s[kBktKeys];
-  __shared__ int32_t pairs_s[kBktSegment];   // the segment's pairs, -1 past its end
-  __shared__ int32_t qrows_s[kBktSegment];   // their query rows
-  __shared__ int32_t hi_s[kBktSegment];      // members of the bucket they read
+  __shared__ int32_t pairs_s[kBktSegmentTc];   // the segment's pairs, -1 past its end
+  __shared__ int32_t qrows_s[kBktSegmentTc];   // their query rows
+  __shared__ int32_t hi_s[kBktSegmentTc];      // members of the bucket they read
   // of the rows of a tile (a ring of three tiles): where the query row starts in q (-1 past the end), which slot of
   // the partial outputs it fills, and the end of its key range
-  __shared__ int64_t src_s[3][kTcRows], dst_s[3][kTcRows];
+  __shared__ int64_t src_s[3][kTcRows];
+  __shared__ int32_t dst_s[3][kTcRows];  // (the caller has checked that the slots fit 31 bits)
   __shared__ int32_t end_s[3][kTcRows];
   __shared__ float swap_max_s[2][kTcRows], swap_sum_s[2][kTcRows];
   __shared__ __align__(8) uint64_t bars[3];
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   for (int i = tid; i < kBktKeys; i += kTcThreads) ids_s[i] = i < p.cap ? p.members[bucket * p.cap + i] : LSA_PAD;
   // The segment's pairs, fetched beside the member ids (one round of loads for both). The starts pass has counted the
   // keys a pair takes; its run of members starts where the sinks end, which is added once the ids are in.
-  if (tid < kBktSegment) {
+  if (tid < kBktSegmentTc) {
     int32_t pair = -1, take = 0;
     if (tid < n_pairs) {
       pair = p.order[first + tid];
@@ -185,7 +186,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       const int pl = ok ? flat / p.group : 0;
       const int head = h * p.group + (flat - pl * p.group);
       src_s[tile % 3][row] = ok ? (int64_t)qrows_s[pl] * p.q_row_stride + (int64_t)head * p.q_head_stride : -1;
-      dst_s[tile % 3][row] = ok ? (int64_t)pairs_s[pl] * p.Hq + head : -1;
+      dst_s[tile % 3][row] = ok ? pairs_s[pl] * p.Hq + head : -1;
       end_s[tile % 3][row] = ok ? lo_key + hi_s[pl] : 0;
     };
     // The query rows of a tile: half a warp copies a row of 256 bytes, in the layout of the keys.
