@@ -8,8 +8,8 @@
 // half a walk more of tensor-core time, which this path has to spare, and saves the read-modify-write of O).
 //
 //   warp 0      one lane streams the key and value tiles with tensor-map copies (128-byte swizzle) through a ring
-//   warp 1      tensor-memory allocation; one lane issues the MMAs: S = Q K^T (both K-major) into one of two S
-//               buffers, O += P V with V read as stored (an MN-major operand)
+//   warp 1      tensor-memory allocation; one lane issues S = Q K^T (both K-major) into one of two S buffers
+//   warp 10     one lane issues O += P V with V read as stored (an MN-major operand)
 //   warps 2-9   two threads a row (64 of a tile's 128 keys each): S out of tensor memory, masks on the band's edge
 //               tiles only, maximum (walk one) or P in bf16 into the consumed key tile's slot (walk two), then the
 //               normalised fp32 output
@@ -24,7 +24,7 @@ namespace lsa {
 
 constexpr int kBtRows = 128;
 constexpr int kBtKeys = 128;                        // keys a tile: two planes of 64 for P, N = 128 for S
-constexpr int kBtThreads = 320;                      // the copy warp, the MMA warp and eight worker warps
+constexpr int kBtThreads = 352;                      // the copy warp, two MMA warps and eight worker warps
 constexpr int kBtWorkers = 256;
 constexpr int kBtStages = 3;                        // the ring of key/value tiles: deep enough to hide a tensor-map copy
 constexpr int kBtPlane = kBtKeys * 128;             // 128 keys x 64 dims of bf16
@@ -129,23 +129,9 @@ __global__ void __launch_bounds__(kBtThreads, 1)
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc(kBtKeys), idesc_o = umma_idesc(128, true);
-      uint32_t full_phases = 0, free_phases = 0, p_phases = 0;  // a parity bit a stage (or S buffer)
+      const uint32_t idesc_s = umma_idesc(kBtKeys);
+      uint32_t full_phases = 0, free_phases = 0;  // a parity bit a stage (or S buffer)
       bool ok = mbar_wait(q_full, 0);
-      // the second product of tile n, once the workers have written its P
-      auto second_product = [&](int n) {
-        const int stage = n % kBtStages;
-        if (!mbar_wait(bar(kPReady, stage), (p_phases >> stage) & 1)) return false;
-        p_phases ^= 1u << stage;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t p_tile = ring + stage * kBtStage, v_tile = p_tile + 2 * kBtPlane;
-#pragma unroll
-        for (int k = 0; k < kBtKeys / 16; ++k)  // P: two planes of 64 keys; V: 16 keys are 2,048 bytes down a plane
-          umma_bf16(tmem_base + kBtOCol, smem_desc_sw128(p_tile + (k >> 2) * kBtQPlane) + 2 * (k & 3),
-                    smem_desc_mn_sw128(v_tile + k * 2048, kBtPlane), idesc_o, (n > tiles || k > 0) ? 1u : 0u);
-        umma_commit(bar(kEmpty, stage));
-        return true;
-      };
       for (int n = 0; n < 2 * tiles && ok && !abort_s; ++n) {
         const int stage = n % kBtStages, sbuf = n & 1;
         const bool second = n >= tiles;
@@ -167,9 +153,30 @@ __global__ void __launch_bounds__(kBtThreads, 1)
                       smem_desc_sw128(k_tile + plane * kBtPlane) + 2 * k, idesc_s, (plane | k) != 0);
         umma_commit(bar(kSReady, sbuf));
         if (!second) umma_commit(bar(kEmpty, stage));  // on the first walk the keys are all a stage holds
-        if (second && n > tiles) ok = second_product(n - 1);
       }
-      if (ok && !abort_s) ok = second_product(2 * tiles - 1);
+      if (!ok) abort_s = 1;
+    }
+  } else if (warp == kBtThreads / 32 - 1) {
+    // The second products have an issuing lane of their own: O += P V of tile n once the workers have written its P.
+    // (One lane for both products waited for P of tile n - 1 before it could issue S of tile n + 1.) P exists only
+    // after S of the tile was read, so the stage's keys are spent too when this product has run.
+    if (lane == 0) {
+      const uint32_t idesc_o = umma_idesc(128, true);
+      uint32_t p_phases = 0;
+      bool ok = true;
+      for (int n = tiles; n < 2 * tiles && ok && !abort_s; ++n) {
+        const int stage = n % kBtStages;
+        ok = mbar_wait(bar(kPReady, stage), (p_phases >> stage) & 1);
+        if (!ok) break;
+        p_phases ^= 1u << stage;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t p_tile = ring + stage * kBtStage, v_tile = p_tile + 2 * kBtPlane;
+#pragma unroll
+        for (int k = 0; k < kBtKeys / 16; ++k)  // P: two planes of 64 keys; V: 16 keys are 2,048 bytes down a plane
+          umma_bf16(tmem_base + kBtOCol, smem_desc_sw128(p_tile + (k >> 2) * kBtQPlane) + 2 * (k & 3),
+                    smem_desc_mn_sw128(v_tile + k * 2048, kBtPlane), idesc_o, (n > tiles || k > 0) ? 1u : 0u);
+        umma_commit(bar(kEmpty, stage));
+      }
       if (!ok) abort_s = 1;
       umma_commit(o_done);
     }
