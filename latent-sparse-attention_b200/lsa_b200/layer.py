@@ -77,7 +77,7 @@ class FlatLayer:
         # and O in tensor memory (the default: 63.5 ms a step of config 2), or warp-level MMA tiles of 16 rows (66.4 ms).
         self.bucket_tensor_memory = True
         self._band_stream = self._band_done = None  # the side stream the band runs on beside the bucket-major read
-        self._copy_in = self._copy_out = None       # the copy streams of `prefill_from_host`
+        self._copy_in = self._copy_out = self._index_stream = None  # the side streams of `prefill_from_host`
         self._copy_events: list = []
         # bf16 maps run on the tensor cores (the head sum folded into the product); fp32 maps keep the exact form
         self.tensor_cores = tensor_cores and query_map.dtype == torch.bfloat16 and key_map.dtype == torch.bfloat16 \
@@ -255,7 +255,8 @@ class FlatLayer:
         """`prefill` for inputs and an output that live in PINNED host memory, the copies overlapped with the work.
         A causal chunk needs the keys and values up to its own end and the buckets of the cluster blocks before its
         rows, and blocks are clustered independently: so K, V and Q cross chunk by chunk on a copy stream, each
-        chunk's blocks are indexed when its keys have arrived, and every chunk's output leaves on a second copy
+        chunk's blocks are indexed when its keys have arrived (on a stream of its own: a handful of small launches
+        that would otherwise stand between two chunks' reads), and every chunk's output leaves on a second copy
         stream as soon as its merge is done. (`chunk` must hold whole cluster blocks.) On return the current stream
         has waited for the last output copy; synchronise it before reading `out_host`."""
         dev = self.query_map.device
@@ -264,11 +265,11 @@ class FlatLayer:
             raise ValueError("a chunk must hold whole cluster blocks (and whole tiles of 128 keys)")
         main = torch.cuda.current_stream(dev)
         if self._copy_in is None:
-            self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+            self._copy_in, self._copy_out, self._index_stream = (torch.cuda.Stream(dev) for _ in range(3))
         chunks = [(start, min(T, start + chunk)) for start in range(0, T, chunk)]
-        while len(self._copy_events) < 2 * len(chunks) + 1:
+        while len(self._copy_events) < 3 * len(chunks):
             self._copy_events.append(torch.cuda.Event())
-        arrived, done = self._copy_events[1::2], self._copy_events[2::2]
+        arrived, done, built = self._copy_events[0::3], self._copy_events[1::3], self._copy_events[2::3]
         q = self._buffer("q from host", tuple(q_host.shape), q_host.dtype, dev)
         k = self._buffer("k from host", tuple(k_host.shape), k_host.dtype, dev)
         v = self._buffer("v from host", tuple(v_host.shape), v_host.dtype, dev)
@@ -283,9 +284,14 @@ class FlatLayer:
                 arrived[c].record(self._copy_in)
         bufs = self._index_buffers(T, dev, reuse_buffers=True)
         index = self._index_of(bufs)
+        self._index_stream.wait_stream(main)
+        with torch.cuda.stream(self._index_stream):
+            for c, (start, stop) in enumerate(chunks):
+                self._index_stream.wait_event(arrived[c])
+                self._build_blocks(k[start:stop], start, bufs)
+                built[c].record(self._index_stream)
         for c, (start, stop) in enumerate(chunks):
-            main.wait_event(arrived[c])
-            self._build_blocks(k[start:stop], start, bufs)
+            main.wait_event(built[c])  # (the chunk's keys, values and queries have arrived, and its blocks are indexed)
             # (the cache as far as it has arrived: no kernel is handed rows that are still on their way)
             self.prefill_rows(q[start:stop], start, k[:stop], v[:stop], index, out[start:stop])
             done[c].record(main)
