@@ -330,13 +330,18 @@ int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_
  *           [0, slots) are skipped. Lists hold each key once and only causal keys (lsa_expand writes such lists).
  *   out     [R, Hq, dv] bf16 and/or fp32; lse [R, Hq] natural-log log-sum-exp (-inf for an empty list)
  *   splits  CTAs a row's list is divided over; > 1 needs lsa_latent_attend_workspace_bytes() of workspace
+ *   flags   0: both products run on tcgen05 with a block of 64 heads as the M side, S and O in tensor memory;
+ *           LSA_LATENT_WARP_MMA: the same read on warp-level mma.sync tiles
+ *   status  (may be NULL) raised if a bounded on-chip wait of the tensor-memory form gives up: the output of a
+ *           call that raised it is void
  * dk = 576, dv = 512 in this build. */
+#define LSA_LATENT_WARP_MMA 1
 size_t lsa_latent_attend_workspace_bytes(int64_t R, int Hq, int dv, int splits);
 int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int64_t q_row_stride,
                       int64_t q_head_stride, const uint16_t *latent, int64_t slots, int64_t latent_row_stride,
                       const int32_t *ids, int64_t list_stride, const int32_t *lengths, float scale, int splits,
-                      uint16_t *out_bf16, float *out_f32, float *lse, void *workspace, size_t workspace_bytes,
-                      void *stream);
+                      uint16_t *out_bf16, float *out_f32, float *lse, int flags, int32_t *status, void *workspace,
+                      size_t workspace_bytes, void *stream);
 
 /* Bucket-major attention of a prefill chunk: expansion and gather attention in one call, the loop over buckets
  * outside the loop over rows. The result is lsa_expand (LSA_EXPAND_NO_LOCAL) followed by lsa_sparse_attend with
@@ -356,6 +361,8 @@ int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int6
  *   init_ready_event  a cudaEvent_t (as void*) or NULL: when init_out / init_lse are written on ANOTHER stream (the
  *            band kernel running beside this call's first passes) the event recorded after that work; only the
  *            merge pass waits for it
+ *   status   (may be NULL) raised if a bounded on-chip wait of the tensor-memory pass gives up: the output of a call
+ *            that raised it is void
  *   flags    0: the two products of a (bucket, head) run on tcgen05 with the pairs as the M = 128 rows, S and O in
  *            tensor memory; LSA_BUCKET_WARP_MMA: the same pass on warp-level mma.sync tiles of 16 rows
  * dh = 128 and Hq / Hkv <= 8 in this build; other shapes return LSA_ERR_UNSUPPORTED and the caller uses
@@ -368,7 +375,8 @@ int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_ro
                       const int32_t *members, int64_t m, int bucket_cap, const int32_t *row_top_p,
                       const int32_t *row_top_k, int top_k, int sink, int window, const float *init_out,
                       const float *init_lse, float scale, uint16_t *out_bf16, float *lse_out, int flags,
-                      void *init_ready_event, void *workspace, size_t workspace_bytes, void *stream);
+                      void *init_ready_event, int32_t *status, void *workspace, size_t workspace_bytes,
+                      void *stream);
 
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the

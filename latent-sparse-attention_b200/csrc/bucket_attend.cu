@@ -231,6 +231,9 @@ __global__ void __maxnreg__(96) bucket_attend_kernel(BucketParams p) {
     return lo;
   };
   const int below_sink = members_below(p.sink);
+  // members that name a row of the cache handed in (the others are staged as zeros and masked out of the softmax)
+  const uint64_t valid_word = (uint64_t)__ballot_sync(0xffffffffu, ids_s[lane] >= 0 && ids_s[lane] < p.slots) |
+                              ((uint64_t)__ballot_sync(0xffffffffu, ids_s[lane + 32] >= 0 && ids_s[lane + 32] < p.slots) << 32);
   const int key_steps = (n_members + 15) >> 4;  // 16-key steps that hold members; the rest of the tile is padding
   for (int i = tid; i < kBktSegment; i += blockDim.x)
     hi_s[i] = pairs_s[i] >= 0 ? min(members_below(until_s[i]), below_sink + allow_s[i]) : 0;
@@ -281,11 +284,11 @@ __global__ void __maxnreg__(96) bucket_attend_kernel(BucketParams p) {
 #pragma unroll
     for (int nt = 0; nt < kBktKeys / 8; ++nt) {
       if (nt * 8 >= key_steps * 16) continue;
-      if (nt * 8 < lo_max || nt * 8 + 8 > hi_min) {
+      if (nt * 8 < lo_max || nt * 8 + 8 > hi_min || ((valid_word >> (nt * 8)) & 0xFFu) != 0xFFu) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int key = nt * 8 + 2 * t + (c & 1), j = c >> 1;
-          if (key < lo_key[j] || key >= hi_key[j]) s[nt][c] = -INFINITY;
+          if (key < lo_key[j] || key >= hi_key[j] || !((valid_word >> key) & 1u)) s[nt][c] = -INFINITY;
         }
       }
       m_row[0] = fmaxf(m_row[0], fmaxf(s[nt][0], s[nt][1]));
@@ -490,8 +493,8 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
                               const int64_t *positions, const int32_t *members, int64_t m, int bucket_cap,
                               const int32_t *row_top_p, const int32_t *row_top_k, int top_k, int sink, int window,
                               const float *init_out, const float *init_lse, float scale, uint16_t *out_bf16,
-                              float *lse_out, int flags, void *init_ready_event, void *workspace,
-                              size_t workspace_bytes, void *stream) {
+                              float *lse_out, int flags, void *init_ready_event, int32_t *status,
+                              void *workspace, size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && k && v && picked && positions && out_bf16 && workspace, LSA_ERR_NULL);
   LSA_REQUIRE(m == 0 || members, LSA_ERR_NULL);
   LSA_REQUIRE((init_out == nullptr) == (init_lse == nullptr), LSA_ERR_NULL);
@@ -513,7 +516,7 @@ LSA_API int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   p.picked = picked, p.members = members, p.row_top_p = row_top_p, p.row_top_k = row_top_k;
   p.positions = positions;
   p.init_out = init_out, p.init_lse = init_lse;
-  p.out_bf16 = out_bf16, p.lse_out = lse_out;
+  p.out_bf16 = out_bf16, p.lse_out = lse_out, p.status = status;
   p.starts = reinterpret_cast<int32_t *>(base + w.starts);
   p.counts = reinterpret_cast<int32_t *>(base + w.counts);
   p.offsets = reinterpret_cast<int32_t *>(base + w.offsets);

@@ -17,6 +17,7 @@ struct BucketParams {
   const float *init_out, *init_lse;
   uint16_t *out_bf16;
   float *lse_out;
+  int32_t *status;          // raised when a bounded on-chip wait of the tensor-memory pass gives up, or NULL
   // workspace
   int32_t *starts;         // [R, top_p] selected ids of the row before this pick, -1 = the pick adds nothing
   int32_t *counts;         // [m + 1] pairs of each bucket

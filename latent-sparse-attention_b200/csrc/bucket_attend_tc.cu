@@ -118,6 +118,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     n_members = low != 0xffffffffu ? __ffs(~low) - 1 : (high != 0xffffffffu ? 32 + __ffs(~high) - 1 : 64);
     n_members = min(n_members, p.cap);
   }
+  // members that name a row of the cache handed in: a key outside it is staged as zeros and masked out of the softmax,
+  // as the row-by-row read skips such ids
+  const uint64_t valid_word = (uint64_t)__ballot_sync(0xffffffffu, ids_s[lane] >= 0 && ids_s[lane] < p.slots) |
+                              ((uint64_t)__ballot_sync(0xffffffffu, ids_s[lane + 32] >= 0 && ids_s[lane + 32] < p.slots) << 32);
   const int n_keys = max(16, (n_members + 15) & ~15);  // the N of S and the K of O: whole 16-key steps
 
   // Step k of the MMAs (warp 0; the whole warp waits so that its lanes stay together, lane 0 issues): once the k-th
@@ -232,7 +236,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       for (int j = 0; j < 4; ++j) {
         const int c0 = (2 * j + half) * 8;
         active[j] = c0 < n_keys;
-        whole[j] = __all_sync(0xffffffffu, c0 >= lo_key && c0 + 8 <= hi_key);
+        whole[j] = __all_sync(0xffffffffu, c0 >= lo_key && c0 + 8 <= hi_key) && ((valid_word >> c0) & 0xFFu) == 0xFFu;
         if (go && active[j]) tmem_load_8(lane_addr + c0, sv[j]);
       }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -249,7 +253,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
         } else {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {  // (bitwise logic and selects: branches here would diverge lane by lane)
-            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key);
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((valid_word >> (c0 + c)) & 1u);
             mx4[c & 3] = fmaxf(mx4[c & 3], ok ? __uint_as_float(sv[j][c]) : -INFINITY);
           }
         }
@@ -274,7 +278,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
         } else {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key);
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((valid_word >> (c0 + c)) & 1u);
             const float e = fast_exp2(fmaf(ok ? __uint_as_float(sv[j][c]) : -INFINITY, p.scale_log2, -m_row));
             l4[c & 3] += e;
             sv[j][c] = __float_as_uint(e);
@@ -361,6 +365,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTcTmemCols));
   }
+  // A CTA that gave up leaves stale partials behind: the status word tells the host that the call's output is void.
+  if (tid == 0 && abort_s && p.status) atomicAdd(p.status, 1);
 }
 
 int launch_bucket_attend_tc(const BucketParams &p, int64_t segment_bound, cudaStream_t stream) {

@@ -13,26 +13,15 @@
 //                same staged rows read transposed
 //
 // The natural-log log-sum-exp is emitted, so splits of a list and ranks of a sharded cache merge exactly.
-#include "common.cuh"
+#include "latent_attend.cuh"
 #include "mma.cuh"
 
 namespace lsa {
 
-constexpr int kLatHeads = 64;
 constexpr int kLatTile = 32;
 constexpr int kLatStages = 3;
 constexpr int kLatThreads = 256;
 constexpr int kLatPPitch = 80;  // bytes a row of P: 32 keys bf16 + 16 of padding
-
-struct LatentParams {
-  const uint16_t *q, *latent;
-  const int32_t *ids, *lengths;
-  uint16_t *out_bf16;
-  float *out_f32, *lse, *part_out, *part_lse;
-  int64_t R, slots, q_row_stride, q_head_stride, latent_row_stride, list_stride;
-  int Hq, splits;
-  float scale_log2;
-};
 
 template <int DK, int DV>
 struct LatentLayout {
@@ -272,8 +261,8 @@ LSA_API size_t lsa_latent_attend_workspace_bytes(int64_t R, int Hq, int dv, int 
 LSA_API int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int64_t q_row_stride,
                               int64_t q_head_stride, const uint16_t *latent, int64_t slots, int64_t latent_row_stride,
                               const int32_t *ids, int64_t list_stride, const int32_t *lengths, float scale,
-                              int splits, uint16_t *out_bf16, float *out_f32, float *lse, void *workspace,
-                              size_t workspace_bytes, void *stream) {
+                              int splits, uint16_t *out_bf16, float *out_f32, float *lse, int flags,
+                              int32_t *status, void *workspace, size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && latent && ids && lse && (out_bf16 || out_f32), LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && Hq >= 1 && slots >= 0 && slots <= INT32_MAX && list_stride >= 0 && splits >= 1 &&
                   latent_row_stride >= dk,
@@ -302,19 +291,25 @@ LSA_API int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int 
   p.Hq = Hq;
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
   if (splits > 1) {
     const size_t need = lsa_latent_attend_workspace_bytes(R, Hq, dv, splits);
     LSA_REQUIRE(workspace && workspace_bytes >= need, LSA_ERR_WORKSPACE);
     p.part_out = reinterpret_cast<float *>(workspace);
     p.part_lse = p.part_out + (size_t)splits * R * Hq * dv;
   }
-  using L = lsa::LatentLayout<576, 512>;
-  auto kernel = lsa::latent_attend_kernel<576, 512>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
-    return LSA_ERR_LAUNCH;
-  const dim3 grid((unsigned)(R * splits), (unsigned)((Hq + lsa::kLatHeads - 1) / lsa::kLatHeads));
-  kernel<<<grid, lsa::kLatThreads, L::TOTAL, (cudaStream_t)stream>>>(p);
-  LSA_LAUNCH_CHECK();
+  if (!(flags & LSA_LATENT_WARP_MMA)) {
+    const int rc = lsa::launch_latent_attend_tc(p, (cudaStream_t)stream);
+    if (rc != LSA_OK) return rc;
+  } else {
+    using L = lsa::LatentLayout<576, 512>;
+    auto kernel = lsa::latent_attend_kernel<576, 512>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return LSA_ERR_LAUNCH;
+    const dim3 grid((unsigned)(R * splits), (unsigned)((Hq + lsa::kLatHeads - 1) / lsa::kLatHeads));
+    kernel<<<grid, lsa::kLatThreads, L::TOTAL, (cudaStream_t)stream>>>(p);
+    LSA_LAUNCH_CHECK();
+  }
   if (splits == 1) return LSA_OK;
   return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dv, out_bf16, out_f32, lse, stream);
 }

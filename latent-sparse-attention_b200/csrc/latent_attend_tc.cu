@@ -1,0 +1,406 @@
+// Gather-sparse attention over a shared latent (the MLA form) on the fifth-generation tensor cores.
+//
+// A CTA owns a (query row, split of its list, block of 64 heads) item. All heads of a row read the SAME listed latent
+// rows, so the heads are the M = 64 side of both products and a gathered row serves 64 heads:
+//
+//   S [64 heads x 64 keys]  = Q [64 x 576] . K^T      tcgen05.mma, A = the row's heads, B = a tile of gathered
+//                                                     latent rows, both K-major planes of 64 dims (128-byte swizzle)
+//   P                       = exp2(S - m), bf16       a thread a head; m is the running row maximum, refreshed only
+//                                                     when it grows by more than 2^8 (so O is rescaled rarely)
+//   O [64 x 512]           += P [64 x 64] . V         A = P (K-major), B = the SAME staged rows read as an MN-major
+//                                                     operand: a value is the first 512 dims of its latent row
+//
+// An M = 64 accumulator fills lanes 0-15 of each 32-lane quarter of tensor memory, and a second one may sit in lanes
+// 16-31: O's first 256 value dims live in the lower half-quarters of columns 0-255 and its last 256 in the upper ones,
+// S has two buffers in the lower half-quarters of columns 256-319 and 320-383. M = 64 because the shared memory of
+// an SM holds the 64 heads' queries (72 KB) beside two stages of 64 gathered rows (72 KB each) and no more.
+//
+//   warps 0-3   a thread a head (lanes 0-15 of a warp; lanes 16-31 own the upper half of O): S out of tensor memory,
+//               masks, P into shared memory, the rare rescale of O, the normalised output
+//   warp 4      tensor-memory allocation; one lane issues the products
+//   warps 5-8   the gather: 16-byte asynchronous copies of the listed latent rows into the swizzled planes
+//
+// The products of tile i + 1 are issued before P of tile i is needed, so the tensor cores multiply S of the next tile
+// while the softmax of this one runs. Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's
+// abort flag and the status word, the roles drain, the tensor memory is freed and the CTA leaves.
+#include "latent_attend.cuh"
+#include "mma.cuh"
+#include "umma.cuh"
+
+namespace lsa {
+
+constexpr int kLtThreads = 288;
+constexpr int kLtKeys = 64;                         // gathered rows a tile
+constexpr int kLtPlanes = 9;                        // 576 dims = 9 planes of 64
+constexpr int kLtPlane = 64 * 128;                  // 64 rows x 64 dims of bf16
+constexpr int kLtStage = kLtPlanes * kLtPlane;      // a tile of gathered rows (and the queries: the same shape)
+constexpr int kLtStages = 2;
+constexpr int kLtKOff = kLtStage;                   // queries first, then the ring
+constexpr int kLtPOff = kLtKOff + kLtStages * kLtStage;
+constexpr int kLtSmem = kLtPOff + kLtPlane + 1024;  // + room to align the base to 1,024 bytes
+constexpr int kLtTmemCols = 512;
+constexpr int kLtSCol = 256;                        // S buffers at columns 256 and 320
+constexpr int kLtChunks = 72;                       // 16-byte chunks a latent row
+constexpr float kLtRescale = 8.0f;                  // the running maximum is refreshed when it grows by 2^8
+
+__device__ __forceinline__ void lt_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void lt_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+// Instruction descriptor of an M = 64 product: bf16 x bf16 -> fp32, N = n, A K-major, B K-major or MN-major.
+__host__ __device__ constexpr uint32_t lt_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(64 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // k_full / k_empty: a ring stage's rows have landed / may be overwritten; s_full / s_empty: an S buffer holds a
+  // product / has been read; p_full: P is in place (and O rescaled); pv_done: the second product of a tile is over;
+  // drained: every product issued has completed.
+  __shared__ __align__(8) uint64_t bars[2 * kLtStages + 2 * 2 + 3];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ volatile int abort_s;
+  __shared__ int32_t ids_s[kLtStages][kLtKeys];
+  __shared__ uint32_t masks_s[kLtStages][2];  // which rows of a staged tile hold a listed key of the cache
+  enum { kFull = 0, kEmpty = kLtStages, kSFull = 2 * kLtStages, kSEmpty = 2 * kLtStages + 2 };
+  auto bar = [&](int kind, int i) { return smem_u32(&bars[kind + i]); };
+  const uint32_t p_full = smem_u32(&bars[2 * kLtStages + 4]), pv_done = smem_u32(&bars[2 * kLtStages + 5]),
+                 drained = smem_u32(&bars[2 * kLtStages + 6]);
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = (int)(blockIdx.x % p.splits);
+  const int64_t r = blockIdx.x / p.splits;
+  const int head0 = blockIdx.y * kLatHeads;
+  const bool partial = p.splits > 1;
+
+  int64_t n_total = p.lengths ? p.lengths[r] : p.list_stride;
+  if (n_total > p.list_stride) n_total = p.list_stride;
+  if (n_total < 0) n_total = 0;
+  int64_t per = (n_total + p.splits - 1) / p.splits;
+  per = (per + kLtKeys - 1) / kLtKeys * kLtKeys;
+  const int64_t begin = (int64_t)split * per;
+  const int64_t end = begin + per < n_total ? begin + per : n_total;
+  const int n = end > begin ? (int)(end - begin) : 0;
+  const int n_tiles = (n + kLtKeys - 1) / kLtKeys;
+  const int32_t *list = p.ids + r * p.list_stride + begin;
+
+  // the thread's head and its half of the value dims (threads of the worker warps)
+  const int half = lane >> 4;
+  const int row = (warp & 3) * 16 + (lane & 15);
+  const int64_t out_row = (partial ? (int64_t)split * p.R + r : r) * p.Hq + head0 + row;
+  const bool row_ok = warp < 4 && head0 + row < p.Hq;
+
+  if (n_tiles == 0) {  // nothing listed for this item: an empty partial
+    if (row_ok) {
+      if (half == 0) (partial ? p.part_lse : p.lse)[out_row] = -INFINITY;
+      for (int c = 0; c < 256; ++c) {
+        const int64_t at = out_row * 512 + half * 256 + c;
+        if (partial) {
+          p.part_out[at] = 0.0f;
+        } else {
+          if (p.out_f32) p.out_f32[at] = 0.0f;
+          if (p.out_bf16) p.out_bf16[at] = 0;
+        }
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int i = 0; i < kLtStages; ++i) {
+      mbar_init(bar(kFull, i), 128);
+      mbar_init(bar(kEmpty, i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(kSFull, i), 1);
+      mbar_init(bar(kSEmpty, i), 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    mbar_init(drained, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"(kLtTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_s;
+
+  // A wait that every lane of the warp takes together; false (and the abort flag) when it gives up or the CTA has
+  // already given up elsewhere.
+  auto wait = [&](uint32_t b, uint32_t parity) {
+    const bool ok = __all_sync(0xffffffffu, !abort_s && mbar_wait(b, parity));
+    if (!ok) abort_s = 1;
+    return ok;
+  };
+
+  if (warp >= 5) {
+    // ------------------------------------------------------------------------------------------ the gather
+    const int ptid = tid - 5 * 32;
+    // the row's query heads: they join the first tile's copies
+    for (int e = ptid; e < kLatHeads * kLtChunks; e += 128) {
+      const int qr = e / kLtChunks, c = e - qr * kLtChunks;
+      const bool ok = head0 + qr < p.Hq;
+      const uint16_t *src = ok ? p.q + r * p.q_row_stride + (int64_t)(head0 + qr) * p.q_head_stride + c * 8 : p.q;
+      cp_async_16(base + (c >> 3) * kLtPlane + qr * 128 + (((c & 7) ^ (qr & 7)) << 4), src, ok ? 16 : 0);
+    }
+    int32_t id_next = ptid < kLtKeys && ptid < n ? list[ptid] : -1;
+    bool alive = true;
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      const int stage = j & 1;
+      if (j >= kLtStages) alive = wait(bar(kEmpty, stage), ((j >> 1) - 1) & 1);
+      if (!alive) break;
+      if (ptid < kLtKeys) {
+        const bool ok = id_next >= 0 && id_next < p.slots;
+        ids_s[stage][ptid] = ok ? id_next : -1;
+        const uint32_t valid = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) masks_s[stage][ptid >> 5] = valid;
+        const int at = (j + 1) * kLtKeys + ptid;
+        id_next = at < n ? list[at] : -1;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the gather warps: the tile's ids are listed
+      const uint32_t dst0 = base + kLtKOff + stage * kLtStage;
+#pragma unroll 4
+      for (int i = 0; i < kLtKeys * kLtChunks / 128; ++i) {
+        const int e = ptid + i * 128;
+        const int kr = e / kLtChunks, c = e - kr * kLtChunks;
+        const int32_t id = ids_s[stage][kr];
+        const uint16_t *src = p.latent + (id >= 0 ? (int64_t)id * p.latent_row_stride + c * 8 : 0);
+        cp_async_16(dst0 + (c >> 3) * kLtPlane + kr * 128 + (((c & 7) ^ (kr & 7)) << 4), src, id >= 0 ? 16 : 0);
+      }
+      cp_async_commit();
+      if (j >= 1) {  // tile j - 1 has landed while tile j is on its way
+        cp_async_wait<1>();
+        lt_proxy_fence();
+        lt_arrive(bar(kFull, (j - 1) & 1));
+      }
+    }
+    cp_async_wait<0>();
+    if (alive) {
+      lt_proxy_fence();
+      lt_arrive(bar(kFull, (n_tiles - 1) & 1));
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------------------------------ the products
+    auto second_product = [&](int t) {  // O += P V of tile t, then its stage and P are free
+      if (lane != 0) return;
+      const uint32_t v_s = base + kLtKOff + (t & 1) * kLtStage;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int ks = 0; ks < kLtKeys / 16; ++ks)
+          umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
+                    smem_desc_mn_sw128(v_s + h * 4 * kLtPlane + ks * 2048, kLtPlane), lt_idesc(256, true),
+                    (t | ks) != 0);
+      umma_commit(bar(kEmpty, t & 1));
+      umma_commit(pv_done);
+    };
+    bool alive = true;
+    for (int i = 0; i < n_tiles && alive; ++i) {
+      const int sb = i & 1;
+      alive = wait(bar(kFull, sb), (i >> 1) & 1);
+      if (alive && i >= 2) alive = wait(bar(kSEmpty, sb), ((i >> 1) - 1) & 1);
+      if (!alive) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (lane == 0) {
+        const uint32_t k_s = base + kLtKOff + sb * kLtStage;
+#pragma unroll
+        for (int plane = 0; plane < kLtPlanes; ++plane)
+#pragma unroll
+          for (int s = 0; s < 4; ++s)
+            umma_bf16(tmem_base + kLtSCol + sb * kLtKeys, smem_desc_sw128(base + plane * kLtPlane) + 2 * s,
+                      smem_desc_sw128(k_s + plane * kLtPlane) + 2 * s, lt_idesc(kLtKeys, false), (plane | s) != 0);
+        umma_commit(bar(kSFull, sb));
+      }
+      __syncwarp();
+      if (i >= 1) {
+        alive = wait(p_full, (i - 1) & 1);
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        second_product(i - 1);
+        __syncwarp();
+      }
+    }
+    if (alive) alive = wait(p_full, (n_tiles - 1) & 1);
+    if (alive) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      second_product(n_tiles - 1);
+      __syncwarp();
+    }
+    // whatever was issued completes before the tensor memory is given back
+    if (lane == 0) umma_commit(drained);
+    __syncwarp();
+    (void)__all_sync(0xffffffffu, mbar_wait(drained, 0));
+  } else {
+    // ------------------------------------------------------------------------------------------ softmax and output
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t p_row = base + kLtPOff + row * 128;
+    float m_used = 0.0f, l_run = 0.0f;
+    bool alive = true;
+    for (int i = 0; i < n_tiles && alive; ++i) {
+      const int sb = i & 1;
+      // (the stage's own barrier too: it is what publishes the tile's validity masks)
+      alive = wait(bar(kFull, sb), (i >> 1) & 1) && wait(bar(kSFull, sb), (i >> 1) & 1);
+      if (!alive) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t sv[2][32];
+      tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys, sv[0]);
+      tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys + 32, sv[1]);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      lt_arrive(bar(kSEmpty, sb));
+      const uint32_t valid0 = masks_s[sb][0], valid1 = masks_s[sb][1];
+      const bool whole = (valid0 & valid1) == 0xffffffffu;
+      // the tile's maximum of the row (raw products: the scale is positive)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (whole) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[0][c]));
+          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[1][c]));
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          mx4[c & 3] = fmaxf(mx4[c & 3], (valid0 >> c) & 1u ? __uint_as_float(sv[0][c]) : -INFINITY);
+          mx4[c & 3] = fmaxf(mx4[c & 3], (valid1 >> c) & 1u ? __uint_as_float(sv[1][c]) : -INFINITY);
+        }
+      }
+      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      // The maximum the exponents subtract is refreshed only when the tile's exceeds it by 2^8: P stays below 2^8,
+      // and O, which would have to be rescaled in tensor memory, almost never is.
+      float alpha = 1.0f;
+      if (i == 0) {
+        m_used = m_tile == -INFINITY ? 0.0f : m_tile;
+      } else if (m_tile > m_used + kLtRescale) {
+        alpha = fast_exp2(m_used - m_tile);
+        m_used = m_tile;
+      }
+      // (lanes 16-31 hold the upper half of the same head's O: they take the head's factor from lane & 15)
+      alpha = __shfl_sync(0xffffffffu, alpha, lane & 15);
+      m_used = __shfl_sync(0xffffffffu, m_used, lane & 15);
+      const bool rescale = i > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
+      if (i > 0) {  // the last tile's second product is over: O is at rest and P may be overwritten
+        alive = wait(pv_done, (i - 1) & 1);
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      if (rescale) {
+#pragma unroll 1
+        for (int c = 0; c < 256; c += 32) {
+          uint32_t o[32];
+          tmem_load_32(lane_addr + c, o);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+          tmem_store_32(lane_addr + c, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+      l_run *= alpha;
+      float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int w = 0; w < 2; ++w) {
+        const uint32_t valid = w ? valid1 : valid0;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          float e[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float s = __uint_as_float(sv[w][c8 * 8 + c]);
+            const bool ok = whole || ((valid >> (c8 * 8 + c)) & 1u);
+            e[c] = fast_exp2(fmaf(ok ? s : -INFINITY, p.scale_log2, -m_used));
+            l4[c & 3] += e[c];
+          }
+          if (half == 0)  // 16-byte slot (keys / 8) ^ (row % 8) of the head's row of P
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((w * 4 + c8) ^ (row & 7)) << 4)),
+                         "r"(pack_bf16x2(e[0], e[1])), "r"(pack_bf16x2(e[2], e[3])), "r"(pack_bf16x2(e[4], e[5])),
+                         "r"(pack_bf16x2(e[6], e[7]))
+                         : "memory");
+        }
+      }
+      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      lt_proxy_fence();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      lt_arrive(p_full);
+    }
+    if (alive) alive = wait(pv_done, (n_tiles - 1) & 1);
+    if (alive) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      l_run = __shfl_sync(0xffffffffu, l_run, lane & 15);
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      if (row_ok && half == 0)
+        (partial ? p.part_lse : p.lse)[out_row] =
+            l_run > 0.0f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 256; c += 32) {
+        uint32_t o[32];
+        tmem_load_32(lane_addr + c, o);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (!row_ok) continue;
+        const int64_t at = out_row * 512 + half * 256 + c;
+        if (partial) {
+#pragma unroll
+          for (int k = 0; k < 32; k += 4)
+            *reinterpret_cast<float4 *>(p.part_out + at + k) =
+                make_float4(__uint_as_float(o[k]) * inv, __uint_as_float(o[k + 1]) * inv,
+                            __uint_as_float(o[k + 2]) * inv, __uint_as_float(o[k + 3]) * inv);
+        } else {
+          if (p.out_f32) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 4)
+              *reinterpret_cast<float4 *>(p.out_f32 + at + k) =
+                  make_float4(__uint_as_float(o[k]) * inv, __uint_as_float(o[k + 1]) * inv,
+                              __uint_as_float(o[k + 2]) * inv, __uint_as_float(o[k + 3]) * inv);
+          }
+          if (p.out_bf16) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 8)
+              *reinterpret_cast<uint4 *>(p.out_bf16 + at + k) =
+                  make_uint4(pack_bf16x2(__uint_as_float(o[k]) * inv, __uint_as_float(o[k + 1]) * inv),
+                             pack_bf16x2(__uint_as_float(o[k + 2]) * inv, __uint_as_float(o[k + 3]) * inv),
+                             pack_bf16x2(__uint_as_float(o[k + 4]) * inv, __uint_as_float(o[k + 5]) * inv),
+                             pack_bf16x2(__uint_as_float(o[k + 6]) * inv, __uint_as_float(o[k + 7]) * inv));
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kLtTmemCols));
+  }
+  if (tid == 0 && abort_s && p.status) atomicAdd(p.status, 1);
+}
+
+int launch_latent_attend_tc(const LatentParams &p, cudaStream_t stream) {
+  if (cudaFuncSetAttribute(latent_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLtSmem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  const dim3 grid((unsigned)(p.R * p.splits), (unsigned)((p.Hq + kLatHeads - 1) / kLatHeads));
+  latent_attend_tc_kernel<<<grid, kLtThreads, kLtSmem, stream>>>(p);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
+}  // namespace lsa

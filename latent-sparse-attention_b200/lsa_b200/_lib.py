@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -55,10 +55,11 @@ SIGNATURES = {
     "lsa_sparse_attend_static": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _L, _I, _L, _L, _P, _L, _P, _F, _I, _P, _P,
                                       _P, _P]),
     "lsa_latent_attend_workspace_bytes": (_Z, [_L, _I, _I, _I]),
-    "lsa_latent_attend": (_I, [_P, _L, _I, _I, _I, _L, _L, _P, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P, _P, _Z, _P]),
+    "lsa_latent_attend": (_I, [_P, _L, _I, _I, _I, _L, _L, _P, _L, _L, _P, _L, _P, _F, _I, _P, _P, _P, _I, _P, _P, _Z,
+                               _P]),
     "lsa_bucket_attend_workspace_bytes": (_Z, [_L, _I, _I, _I, _L]),
     "lsa_bucket_attend": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _I, _L, _L, _P, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I,
-                               _P, _P, _F, _P, _P, _I, _P, _P, _Z, _P]),
+                               _P, _P, _F, _P, _P, _I, _P, _P, _P, _Z, _P]),
     "lsa_lse_merge": (_I, [_P, _P, _I, _L, _I, _P, _P, _P, _P]),
 }
 
@@ -83,13 +84,24 @@ def load() -> ctypes.CDLL:
     return _lib
 
 
-def ptr(tensor: torch.Tensor | None) -> int | None:
+class Address(int):
+    """A device address that keeps its tensor alive: a tensor converted inline in an argument list
+    (`ptr(x.to(torch.int32))`) must outlive the launch it is passed to, or the caching allocator may hand its block
+    to the next conversion of the same call."""
+
+    def __new__(cls, tensor: torch.Tensor):
+        self = super().__new__(cls, tensor.data_ptr())
+        self.tensor = tensor
+        return self
+
+
+def ptr(tensor: torch.Tensor | None) -> Address | None:
     """Device address of a tensor (None passes NULL). Refuses anything that is not CUDA memory."""
     if tensor is None:
         return None
     if not tensor.is_cuda:
         raise RuntimeError("lsa_b200 kernels take CUDA tensors only - there is no CPU path")
-    return tensor.data_ptr()
+    return Address(tensor)
 
 
 def stream() -> int:

@@ -73,8 +73,14 @@ class FlatLayer:
         self.dh_used = free
         self.scale = head_dim ** -0.5 if scale is None else scale
         self._buffers: dict = {}
+        # What the kernels report from the device, read by `check()`: bounded waits of the map kernels that gave up,
+        # buckets over their cap in the table, bad picks in the expansion, bounded waits of the attention kernels.
+        self.status = torch.zeros(4, device=query_map.device, dtype=torch.int32)
+        self._map_status, self._table_status = self.status[0:1], self.status[1:2]
+        self._expand_status, self._attend_status = self.status[2:3], self.status[3:4]
+        self._reached: list = []  # per index build: whether each cluster block merged down to its bucket count
         # The bucket-major attend pass has two forms: (pair, head) rows as the M = 128 side of tcgen05 products with S
-        # and O in tensor memory (the default: 63.5 ms a step of config 2), or warp-level MMA tiles of 16 rows (66.4 ms).
+        # and O in tensor memory (the default), or warp-level MMA tiles of 16 rows.
         self.bucket_tensor_memory = True
         self._band_stream = self._band_done = None  # the side stream the band runs on beside the bucket-major read
         self._copy_in = self._copy_out = self._index_stream = None  # the side streams of `prefill_from_host`
@@ -86,7 +92,25 @@ class FlatLayer:
             self.query_map_t = ops.expand_map(self.query_map, heads, heads // kv_heads, head_dim, self.dh_off,
                                               self.dh_used)
             self.key_map_t = ops.expand_map(self.key_map, kv_heads, 1, head_dim, self.dh_off, self.dh_used)
-            self._map_status = torch.zeros(1, device=query_map.device, dtype=torch.int32)
+
+    def check(self) -> None:
+        """The deferred checks of everything launched since the last call: ONE host synchronisation, so a hot path
+        calls it once a prefill (or once a benchmark) rather than after every kernel. Raises `ValueError` when a
+        cluster block stopped short of its bucket count or a bucket overflowed its cap (what `core.build_buckets`
+        raises at once, src/lsa/core/reference.py:131, ward.py:118-122) and `RuntimeError` when a bounded on-chip
+        wait gave up, in which case the outputs since the last check are void."""
+        counts = self.status.tolist()
+        short = sum(int((~r.bool()).sum()) for r in self._reached)
+        self.status.zero_()
+        self._reached.clear()
+        if short or counts[1]:
+            raise ValueError(f"{short} cluster blocks stopped short of {self.design.block_bucket_count} buckets under "
+                             f"the cap {self.design.bucket_cap}; {counts[1]} buckets overflowed it")
+        if counts[2]:
+            raise ValueError(f"{counts[2]} picked bucket ids lay outside the member table")
+        if counts[0] or counts[3]:
+            raise RuntimeError(f"bounded on-chip waits gave up ({counts[0]} in the index map, {counts[3]} in the "
+                               "attention kernels): the outputs since the last check are void")
 
     # ---- buffers
 
@@ -139,11 +163,10 @@ class FlatLayer:
         bufs = {"keys": make("index keys", (T, d_idx), torch.float32),
                 "pools": make("pools", (blocks, P, d_idx), torch.float32),
                 "labels": make("labels", (blocks, P), torch.int64), "reached": make("reached", (blocks,), torch.uint8),
-                "status": make("table status", (1,), torch.int32),
+                "status": self._table_status,
                 "members": make("members", (rows, d.bucket_cap), torch.int32), "sizes": make("sizes", (rows,), torch.int32),
                 "key sums": make("key sums", (rows, d_idx), torch.float32),
                 "centroids": make("centroids", (rows, d_idx), torch.float32)}
-        bufs["status"].zero_()
         return bufs
 
     def _index_of(self, bufs: dict) -> FlatIndex:
@@ -169,6 +192,8 @@ class FlatLayer:
         with probe.region("ward"):
             labels, _ = ops.ward_rounds(pools, float(d.pool_size), d.block_bucket_count, d.bucket_cap,
                                         labels=bufs["labels"][b0:b0 + nb], reached=bufs["reached"][b0:b0 + nb])
+            if len(self._reached) < 64:  # (views of the index buffers; `check()` reads and drops them)
+                self._reached.append(bufs["reached"][b0:b0 + nb])
         with probe.region("bucket table"):
             outs = (bufs["members"][r0:r1], bufs["sizes"][r0:r1], bufs["key sums"][r0:r1], bufs["centroids"][r0:r1],
                     None, bufs["status"])
@@ -207,10 +232,8 @@ class FlatLayer:
         picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers)
         outs = None
         if reuse_buffers:
-            status = self._buffer("expand status", (1,), torch.int32, dev)
-            status.zero_()
             outs = (self._buffer("lists", (R, d.list_width), torch.int32, dev),
-                    self._buffer("lengths", (R,), torch.int32, dev), status)
+                    self._buffer("lengths", (R,), torch.int32, dev), self._expand_status)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, positions, b.bucket_members, d.top_k, d.sink_size, d.window_size,
                                            row_p, row_k, outs=outs, local=local)
@@ -228,7 +251,8 @@ class FlatLayer:
         with probe.region("band"):
             return ops.band_attend(q, k, v, first_position, self.design.window_size, self.design.sink_size, self.scale,
                                    out=self._buffer("band out", (R, self.heads, self.head_dim), torch.float32, dev),
-                                   lse=self._buffer("band lse", (R, self.heads), torch.float32, dev))
+                                   lse=self._buffer("band lse", (R, self.heads), torch.float32, dev),
+                                   status=self._attend_status)
 
     # ---- the layer
 
@@ -336,6 +360,7 @@ class FlatLayer:
                                   self.design.sink_size, self.design.window_size, self.scale, init=init,
                                   row_top_p=row_p, row_top_k=row_k, out=out, lse=lse,
                                   warp_mma=not self.bucket_tensor_memory, init_ready=self._band_done,
+                                  status=self._attend_status,
                                   workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
             return out
         init = self.band(rows, k, v, start) if banded else None

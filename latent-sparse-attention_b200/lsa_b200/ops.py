@@ -375,16 +375,22 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
 
 def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, lengths: torch.Tensor | None,
                   scale: float, value_dim: int = 512, splits: int = 1, out_dtype=torch.bfloat16,
-                  workspace: torch.Tensor | None = None):
+                  workspace: torch.Tensor | None = None, warp_mma: bool = False,
+                  status: torch.Tensor | None = None, out: torch.Tensor | None = None):
     """The MLA read: absorbed queries q [R, Hq, dk] bf16 over the latent rows [slots, dk] bf16 each list names, a
-    value being a row's first `value_dim` dims. Returns (out [R, Hq, value_dim], lse [R, Hq])."""
+    value being a row's first `value_dim` dims. Returns (out [R, Hq, value_dim], lse [R, Hq]). The products run
+    on tcgen05 with tensor-memory accumulators; `warp_mma` takes the warp-level MMA kernel."""
     if q.dtype != torch.bfloat16 or latent.dtype != torch.bfloat16:
         raise ValueError("q and latent must be bfloat16")
     if q.dim() != 3 or latent.dim() != 2 or q.stride(2) != 1 or latent.stride(1) != 1 or q.shape[2] != latent.shape[1]:
         raise ValueError(f"q must be [R, Hq, dk] and latent [slots, dk] - got {tuple(q.shape)} and {tuple(latent.shape)}")
     ids = _contig(ids)
     R, Hq, dk = q.shape
-    out = torch.empty(R, Hq, value_dim, device=q.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty(R, Hq, value_dim, device=q.device, dtype=out_dtype)
+    elif out.shape != (R, Hq, value_dim) or not out.is_contiguous() or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"out must be a contiguous bfloat16 or float32 [{R}, {Hq}, {value_dim}]")
+    out_dtype = out.dtype
     lse = torch.empty(R, Hq, device=q.device, dtype=torch.float32)
     need = query("lsa_latent_attend_workspace_bytes", R, Hq, value_dim, splits)
     if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
@@ -392,7 +398,8 @@ def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, leng
     call("lsa_latent_attend", ptr(q), R, Hq, dk, value_dim, q.stride(0), q.stride(1), ptr(latent), latent.shape[0],
          latent.stride(0), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits,
          ptr(out) if out_dtype == torch.bfloat16 else None, ptr(out) if out_dtype == torch.float32 else None, ptr(lse),
-         ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
+         1 if warp_mma else 0, ptr(status), ptr(workspace),
+         workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
          launches=1 if splits == 1 else 2)
     return out, lse
 
@@ -407,7 +414,7 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
                   row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
                   out: torch.Tensor | None = None, lse: torch.Tensor | None = None,
                   workspace: torch.Tensor | None = None, warp_mma: bool = False,
-                  init_ready: torch.cuda.Event | None = None):
+                  init_ready: torch.cuda.Event | None = None, status: torch.Tensor | None = None):
     """Expansion and attention of a prefill chunk bucket by bucket: q [R, Hq, dh] bf16 over the members of each row's
     picked buckets (picked [R, top_p], members ascending in a bucket) inside [sink, position + 1 - window), cut at
     top_k, merged with the partial read `init` = (out fp32, lse). Returns (out [R, Hq, dh] bf16, lse [R, Hq]).
@@ -431,7 +438,7 @@ def bucket_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, picked: tor
          k.stride(1), ptr(picked), top_p, ptr(_contig(positions.to(torch.int64))), ptr(members), members.shape[0],
          members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(init[0]) if init else None,
          ptr(init[1]) if init else None, float(scale), ptr(out), ptr(lse), 1 if warp_mma else 0,
-         init_ready.cuda_event if init_ready is not None else None, ptr(workspace),
+         init_ready.cuda_event if init_ready is not None else None, ptr(status), ptr(workspace),
          workspace.numel() * workspace.element_size(), stream(), launches=6)
     return out, lse
 

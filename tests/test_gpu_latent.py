@@ -81,15 +81,19 @@ def _latent_case(seed, rows, heads, slots, width, ragged=True):
     return q, latent, ids, lengths
 
 
-@pytest.mark.parametrize("heads,splits", [(64, 1), (64, 4), (16, 1), (128, 3)])
-def test_latent_attend_matches_the_oracle(oracle, heads, splits):
+@pytest.mark.parametrize("heads,splits,warp_mma", [(64, 1, False), (64, 4, False), (16, 1, False), (128, 3, False),
+                                                   (64, 1, True), (128, 3, True)])
+def test_latent_attend_matches_the_oracle(oracle, heads, splits, warp_mma):
+    """Both forms of the kernel (tcgen05 with tensor-memory accumulators, the default, and warp-level MMA)."""
     from lsa_b200 import ops
 
     rows, slots, width = 12, 3000, 700
     q, latent, ids, lengths = _latent_case(heads + splits, rows, heads, slots, width)
     scale = 576 ** -0.5
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out, lse = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths), scale,
-                                 splits=splits, out_dtype=torch.float32)
+                                 splits=splits, out_dtype=torch.float32, warp_mma=warp_mma, status=status)
+    assert int(status) == 0
     want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
                                           np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
     got, got_lse = out.cpu().numpy(), lse.cpu().numpy()
@@ -103,12 +107,61 @@ def test_latent_attend_matches_the_oracle(oracle, heads, splits):
     ids_bad = ids.copy()
     ids_bad[2, : lengths[2] // 2] = slots + 5
     out16, _ = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids_bad), None, scale,
-                                 splits=splits)
+                                 splits=splits, warp_mma=warp_mma)
     keep = ids.copy()
     keep[2, : lengths[2] // 2] = -1
     want2, _ = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], keep,
                                     np.full(rows, slots, dtype=np.int64), 0, 0, scale)
     assert np.abs(out16.float().cpu().numpy() - want2[:, :, :512]).max() <= 3e-2
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_latent_attend_with_a_growing_maximum(oracle, splits):
+    """Keys whose logits grow along the list: the running maximum of the tensor-memory form jumps by far more than
+    the 2^8 it tolerates, so the accumulated output is rescaled in tensor memory, several times a row."""
+    from lsa_b200 import ops
+
+    rows, heads, slots, width = 6, 64, 4000, 1500
+    q, latent, ids, lengths = _latent_case(11, rows, heads, slots, width, ragged=False)
+    rng = np.random.default_rng(5)
+    lengths[:] = width
+    for r in range(rows):
+        ids[r] = rng.choice(slots, width, replace=False)
+    # the rows a list names late are scaled up, the same factor for every list that names them
+    gain = np.ones(slots, dtype=np.float32)
+    for r in range(rows):
+        gain[ids[r, width // 3:]] = 3.0
+        gain[ids[r, 2 * width // 3:]] = 9.0
+    latent = bf16_round(latent * gain[:, None])
+    scale = 0.15
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths), scale,
+                                 splits=splits, out_dtype=torch.float32, status=status)
+    want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
+                                          np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    assert int(status) == 0
+    gap = np.abs(out.cpu().numpy() - want[:, :, :512])
+    assert gap.max() <= 2e-2 * max(1.0, np.abs(want).max()) and gap.mean() <= 2e-3 * max(1.0, np.abs(want).mean() * 10)
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
+
+
+def test_latent_attend_long_lists_in_bf16(oracle):
+    """Lists of thousands of keys (a hundred tiles a row), ragged ends, bf16 output: the size a served row has."""
+    from lsa_b200 import ops
+
+    rows, heads, slots, width = 5, 64, 20000, 9000
+    q, latent, ids, lengths = _latent_case(3, rows, heads, slots, width, ragged=True)
+    lengths[2], lengths[3], lengths[4] = width, width - 1, 64 * 17
+    for r in (2, 3, 4):
+        ids[r, : lengths[r]] = np.random.default_rng(r).choice(slots, lengths[r], replace=False)
+    scale = 576 ** -0.5
+    out, lse = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths), scale)
+    want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
+                                          np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    gap = np.abs(out.float().cpu().numpy() - want[:, :, :512])
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (gap.max(), gap.mean())
+    held = lengths > 0
+    assert np.abs(lse.cpu().numpy()[held] - want_lse[held]).max() <= 2e-2
 
 
 def test_latent_layer_end_to_end(oracle):
