@@ -17,11 +17,14 @@
 //
 //   warps 0-3   a thread a head (lanes 0-15 of a warp; lanes 16-31 own the upper half of O): S out of tensor memory,
 //               masks, P into shared memory, the rare rescale of O, the normalised output
-//   warp 4      tensor-memory allocation; one lane issues the products
-//   warps 5-8   the gather: 16-byte asynchronous copies of the listed latent rows into the swizzled planes
+//   warp 4      tensor-memory allocation; one lane issues S = Q K^T of every tile
+//   warp 9      one lane issues O += P V of every tile (a lane of its own: the two products belong to tiles in
+//               different stages, and one lane for both makes each wait for the other's loads)
+//   warps 5-8   staging: a tile is up to 64 listed rows. 64 consecutive rows of the cache - what a bucket's pools
+//               and a window are made of - are ONE box of a tensor-map copy per plane, wherever they start;
+//               anything else is gathered with 16-byte asynchronous copies into the same swizzled planes
 //
-// The products of tile i + 1 are issued before P of tile i is needed, so the tensor cores multiply S of the next tile
-// while the softmax of this one runs. Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's
+// The two stages run as two chains (load, S, softmax, O) that fill one another's waits. Every wait on an mbarrier is bounded; a wait that gives up raises the CTA's
 // abort flag and the status word, the roles drain, the tensor memory is freed and the CTA leaves.
 #include "latent_attend.cuh"
 #include "mma.cuh"
@@ -29,7 +32,7 @@
 
 namespace lsa {
 
-constexpr int kLtThreads = 288;
+constexpr int kLtThreads = 320;
 constexpr int kLtKeys = 64;                         // gathered rows a tile
 constexpr int kLtPlanes = 9;                        // 576 dims = 9 planes of 64
 constexpr int kLtPlane = 64 * 128;                  // 64 rows x 64 dims of bf16
@@ -41,8 +44,36 @@ constexpr int kLtSmem = kLtPOff + kLtPlane + 1024;  // + room to align the base 
 constexpr int kLtTmemCols = 512;
 constexpr int kLtSCol = 256;                        // S buffers at columns 256 and 320
 constexpr int kLtChunks = 72;                       // 16-byte chunks a latent row
+constexpr int kLtMinRun = 16;                       // a shorter run of at least this many rows is a tile of its own
 constexpr float kLtRescale = 8.0f;                  // the running maximum is refreshed when it grows by 2^8
 
+constexpr uint32_t kLtSpinLimit = 1u << 20;  // polls of one wait (a tile's load or product takes microseconds)
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+#ifdef LSA_LT_TRACE
+// A clock trace of the first CTA's first 64 tiles (a tuning aid, compiled only on request): event e of tile t.
+__device__ long long lsa_lt_trace[16 * 64];
+#define LT_TRACE(cond, e, t)                                                                     \
+  do {                                                                                           \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (cond) && (t) < 64) lsa_lt_trace[(e) * 64 + (t)] = clock64(); \
+  } while (0)
+#else
+#define LT_TRACE(cond, e, t) \
+  do {                       \
+  } while (0)
+#endif
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void lt_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void lt_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -64,20 +95,24 @@ __host__ __device__ constexpr uint32_t lt_idesc(int n, bool b_mn_major) {
          ((uint32_t)(64 >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentParams p) {
+__global__ void __launch_bounds__(kLtThreads, 1)
+    latent_attend_tc_kernel(const __grid_constant__ CUtensorMap map_latent, LatentParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // k_full / k_empty: a ring stage's rows have landed / may be overwritten; s_full / s_empty: an S buffer holds a
   // product / has been read; p_full: P is in place (and O rescaled); pv_done: the second product of a tile is over;
-  // drained: every product issued has completed.
-  __shared__ __align__(8) uint64_t bars[2 * kLtStages + 2 * 2 + 3];
+  // drained: every product an issuing lane has issued is complete.
+  __shared__ __align__(8) uint64_t bars[2 * kLtStages + 2 * 2 + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
   __shared__ int32_t ids_s[kLtStages][kLtKeys];
-  __shared__ uint32_t masks_s[kLtStages][2];  // which rows of a staged tile hold a listed key of the cache
+  // what the gather tells the other roles about a staged tile: which of its 64 rows hold a listed key of the cache,
+  // and whether it is the item's last; and what its first warp tells the other three about the tile to stage
+  __shared__ volatile uint32_t info_s[kLtStages][4];
+  __shared__ volatile int32_t plan_s[1];
   enum { kFull = 0, kEmpty = kLtStages, kSFull = 2 * kLtStages, kSEmpty = 2 * kLtStages + 2 };
   auto bar = [&](int kind, int i) { return smem_u32(&bars[kind + i]); };
   const uint32_t p_full = smem_u32(&bars[2 * kLtStages + 4]), pv_done = smem_u32(&bars[2 * kLtStages + 5]),
-                 drained = smem_u32(&bars[2 * kLtStages + 6]);
+                 drained_s = smem_u32(&bars[2 * kLtStages + 6]), drained_o = smem_u32(&bars[2 * kLtStages + 7]);
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -94,7 +129,6 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
   const int64_t begin = (int64_t)split * per;
   const int64_t end = begin + per < n_total ? begin + per : n_total;
   const int n = end > begin ? (int)(end - begin) : 0;
-  const int n_tiles = (n + kLtKeys - 1) / kLtKeys;
   const int32_t *list = p.ids + r * p.list_stride + begin;
 
   // the thread's head and its half of the value dims (threads of the worker warps)
@@ -103,7 +137,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
   const int64_t out_row = (partial ? (int64_t)split * p.R + r : r) * p.Hq + head0 + row;
   const bool row_ok = warp < 4 && head0 + row < p.Hq;
 
-  if (n_tiles == 0) {  // nothing listed for this item: an empty partial
+  if (n == 0) {  // nothing listed for this item: an empty partial
     if (row_ok) {
       if (half == 0) (partial ? p.part_lse : p.lse)[out_row] = -INFINITY;
       for (int c = 0; c < 256; ++c) {
@@ -121,7 +155,7 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
 
   if (tid == 0) {
     for (int i = 0; i < kLtStages; ++i) {
-      mbar_init(bar(kFull, i), 128);
+      mbar_init(bar(kFull, i), 1);
       mbar_init(bar(kEmpty, i), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -130,7 +164,8 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
     }
     mbar_init(p_full, 128);
     mbar_init(pv_done, 1);
-    mbar_init(drained, 1);
+    mbar_init(drained_s, 1);
+    mbar_init(drained_o, 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -144,39 +179,46 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
 
-  // A wait that every lane of the warp takes together; false (and the abort flag) when it gives up or the CTA has
-  // already given up elsewhere.
+  // A wait of one thread: false (and the abort flag) when it gives up or the CTA has already given up elsewhere.
+  auto wait_one = [&](uint32_t b, uint32_t parity) {
+    bool done = false;
+    for (uint32_t spin = 0; spin < kLtSpinLimit && !done && !abort_s; ++spin) done = mbar_try(b, parity);
+    if (!done) abort_s = 1;
+    return done;
+  };
+  // The same for a warp whose lanes go on together.
   auto wait = [&](uint32_t b, uint32_t parity) {
-    const bool ok = __all_sync(0xffffffffu, !abort_s && mbar_wait(b, parity));
+    bool done = false;
+    for (uint32_t spin = 0; spin < kLtSpinLimit && !done && !abort_s; ++spin) done = mbar_try(b, parity);
+    const bool ok = __all_sync(0xffffffffu, done);
     if (!ok) abort_s = 1;
     return ok;
   };
+  // An issuing lane leaves only when its products are complete (bounded, but not cut short by the abort flag: the
+  // tensor memory must not be freed under a running product).
+  auto drain = [&](uint32_t b) {
+    umma_commit(b);
+    bool done = false;
+    for (uint32_t spin = 0; spin < kLtSpinLimit && !done; ++spin) done = mbar_try(b, 0);
+  };
 
-  if (warp >= 5) {
-    // ------------------------------------------------------------------------------------------ the gather
+  if (warp >= 5 && warp < 9) {
+    // ------------------------------------------------------------------------------------------ staging the rows
     const int ptid = tid - 5 * 32;
-    // the row's query heads: they join the first tile's copies
+    auto gather_sync = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    // the row's query heads
     for (int e = ptid; e < kLatHeads * kLtChunks; e += 128) {
       const int qr = e / kLtChunks, c = e - qr * kLtChunks;
       const bool ok = head0 + qr < p.Hq;
       const uint16_t *src = ok ? p.q + r * p.q_row_stride + (int64_t)(head0 + qr) * p.q_head_stride + c * 8 : p.q;
       cp_async_16(base + (c >> 3) * kLtPlane + qr * 128 + (((c & 7) ^ (qr & 7)) << 4), src, ok ? 16 : 0);
     }
-    int32_t id_next = ptid < kLtKeys && ptid < n ? list[ptid] : -1;
-    bool alive = true;
-    for (int j = 0; j < n_tiles && alive; ++j) {
-      const int stage = j & 1;
-      if (j >= kLtStages) alive = wait(bar(kEmpty, stage), ((j >> 1) - 1) & 1);
-      if (!alive) break;
-      if (ptid < kLtKeys) {
-        const bool ok = id_next >= 0 && id_next < p.slots;
-        ids_s[stage][ptid] = ok ? id_next : -1;
-        const uint32_t valid = __ballot_sync(0xffffffffu, ok);
-        if (lane == 0) masks_s[stage][ptid >> 5] = valid;
-        const int at = (j + 1) * kLtKeys + ptid;
-        id_next = at < n ? list[at] : -1;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the gather warps: the tile's ids are listed
+    cp_async_commit();
+    cp_async_wait<0>();
+    lt_proxy_fence();
+    gather_sync();  // the queries are in place before any tile is announced
+    // The rows of a tile that is not one box, a quarter of the copies a warp.
+    auto gather_rows = [&](int stage) {
       const uint32_t dst0 = base + kLtKOff + stage * kLtStage;
 #pragma unroll 4
       for (int i = 0; i < kLtKeys * kLtChunks / 128; ++i) {
@@ -187,40 +229,89 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
         cp_async_16(dst0 + (c >> 3) * kLtPlane + kr * 128 + (((c & 7) ^ (kr & 7)) << 4), src, id >= 0 ? 16 : 0);
       }
       cp_async_commit();
-      if (j >= 1) {  // tile j - 1 has landed while tile j is on its way
-        cp_async_wait<1>();
-        lt_proxy_fence();
-        lt_arrive(bar(kFull, (j - 1) & 1));
+      cp_async_wait<0>();
+      lt_proxy_fence();
+    };
+    if (warp == 5) {
+      // The first warp walks the list, 64 entries ahead (two a lane), and stages boxes by itself; the other three
+      // wait at the barrier for tiles that must be gathered.
+      int x = 0;
+      int32_t id_a = lane < n ? list[lane] : -1;
+      int32_t id_b = 32 + lane < n ? list[32 + lane] : -1;
+      bool alive = true;
+      for (int j = 0; x < n && alive; ++j) {
+        const int stage = j & 1;
+        // 64 consecutive rows of the cache are ONE box of a tensor-map copy per plane, wherever they start. Anything
+        // else is gathered row by row (rows that hold no key are zero-filled: a box would bring in rows nobody
+        // listed, whose bits need not be finite); a shorter run is a tile of its own, so that the tile after it
+        // starts with the next run.
+        const int remaining = min(kLtKeys, n - x);
+        const int32_t first = __shfl_sync(0xffffffffu, id_a, 0);
+        const bool ok_a = id_a >= 0 && id_a < p.slots, ok_b = id_b >= 0 && id_b < p.slots;
+        const uint32_t run_a = __ballot_sync(0xffffffffu, ok_a && id_a == first + lane);
+        const uint32_t run_b = __ballot_sync(0xffffffffu, ok_b && id_b == first + 32 + lane);
+        const int run = run_a != 0xffffffffu ? __ffs(~run_a) - 1 : 32 + (run_b != 0xffffffffu ? __ffs(~run_b) - 1 : 32);
+        const bool boxed = p.boxes && run == kLtKeys;
+        const int count = boxed ? kLtKeys : (run >= kLtMinRun ? run : remaining);
+        const int32_t keep_a = ok_a && lane < count ? id_a : -1, keep_b = ok_b && 32 + lane < count ? id_b : -1;
+        const uint32_t valid0 = __ballot_sync(0xffffffffu, keep_a >= 0), valid1 = __ballot_sync(0xffffffffu, keep_b >= 0);
+        // the box is asked into the L2 now, a tile's time before its stage is free
+        if (boxed && lane < kLtPlanes) tma_prefetch_2d(&map_latent, lane * 64, first);
+        // the entries after this tile, on their way while it is staged
+        const int at = x + count + lane;
+        id_a = at < n ? list[at] : -1;
+        id_b = at + 32 < n ? list[at + 32] : -1;
+        if (j >= kLtStages) alive = wait(bar(kEmpty, stage), ((j >> 1) - 1) & 1);
+        if (!alive) break;
+        LT_TRACE(lane == 0, 0, j);
+        if (lane == 0) info_s[stage][0] = valid0, info_s[stage][1] = valid1, info_s[stage][2] = x + count >= n;
+        const uint32_t dst0 = base + kLtKOff + stage * kLtStage;
+        if (boxed) {
+          if (lane == 0) {
+            mbar_expect_tx(bar(kFull, stage), kLtStage);
+#pragma unroll
+            for (int plane = 0; plane < kLtPlanes; ++plane)
+              tma_load_2d(dst0 + plane * kLtPlane, &map_latent, bar(kFull, stage), plane * 64, first);
+          }
+          __syncwarp();
+          LT_TRACE(lane == 0, 1, j);
+        } else {
+          ids_s[stage][lane] = keep_a;
+          ids_s[stage][32 + lane] = keep_b;
+          if (lane == 0) plan_s[0] = stage;
+          gather_sync();  // the other three warps take their quarters
+          gather_rows(stage);
+          LT_TRACE(lane == 0, 1, j);
+          gather_sync();
+          if (lane == 0) lt_arrive(bar(kFull, stage));
+        }
+        LT_TRACE(lane == 0, 2, j);
+        x += count;
+      }
+      if (lane == 0) plan_s[0] = -1;
+      gather_sync();  // the other three warps leave
+    } else {
+      for (;;) {
+        gather_sync();
+        const int stage = plan_s[0];
+        if (stage < 0) break;
+        gather_rows(stage);
+        gather_sync();
       }
     }
-    cp_async_wait<0>();
-    if (alive) {
-      lt_proxy_fence();
-      lt_arrive(bar(kFull, (n_tiles - 1) & 1));
-    }
   } else if (warp == 4) {
-    // ------------------------------------------------------------------------------------------ the products
-    auto second_product = [&](int t) {  // O += P V of tile t, then its stage and P are free
-      if (lane != 0) return;
-      const uint32_t v_s = base + kLtKOff + (t & 1) * kLtStage;
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int ks = 0; ks < kLtKeys / 16; ++ks)
-          umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
-                    smem_desc_mn_sw128(v_s + h * 4 * kLtPlane + ks * 2048, kLtPlane), lt_idesc(256, true),
-                    (t | ks) != 0);
-      umma_commit(bar(kEmpty, t & 1));
-      umma_commit(pv_done);
-    };
-    bool alive = true;
-    for (int i = 0; i < n_tiles && alive; ++i) {
-      const int sb = i & 1;
-      alive = wait(bar(kFull, sb), (i >> 1) & 1);
-      if (alive && i >= 2) alive = wait(bar(kSEmpty, sb), ((i >> 1) - 1) & 1);
-      if (!alive) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) {
+    // ------------------------------------------------------------------------------------------ S = Q K^T
+    if (lane == 0) {
+      bool alive = true;
+      for (int i = 0; alive; ++i) {
+        const int sb = i & 1;
+        alive = wait_one(bar(kFull, sb), (i >> 1) & 1);
+        if (!alive) break;
+        const bool last = info_s[sb][2] != 0;
+        if (i >= 2) alive = wait_one(bar(kSEmpty, sb), ((i >> 1) - 1) & 1);
+        if (!alive) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        LT_TRACE(true, 3, i);
         const uint32_t k_s = base + kLtKOff + sb * kLtStage;
 #pragma unroll
         for (int plane = 0; plane < kLtPlanes; ++plane)
@@ -229,64 +320,84 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
             umma_bf16(tmem_base + kLtSCol + sb * kLtKeys, smem_desc_sw128(base + plane * kLtPlane) + 2 * s,
                       smem_desc_sw128(k_s + plane * kLtPlane) + 2 * s, lt_idesc(kLtKeys, false), (plane | s) != 0);
         umma_commit(bar(kSFull, sb));
+        LT_TRACE(true, 4, i);
+        if (last) break;
       }
-      __syncwarp();
-      if (i >= 1) {
-        alive = wait(p_full, (i - 1) & 1);
+      drain(drained_s);
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------------------------------ O += P V
+    if (lane == 0) {
+      bool alive = true;
+      for (int t = 0; alive; ++t) {
+        alive = wait_one(p_full, t & 1);
         if (!alive) break;
+        const bool last = info_s[t & 1][2] != 0;  // (read before the stage is given back)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        second_product(i - 1);
-        __syncwarp();
+        LT_TRACE(true, 5, t);
+        const uint32_t v_s = base + kLtKOff + (t & 1) * kLtStage;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int ks = 0; ks < kLtKeys / 16; ++ks)
+            umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
+                      smem_desc_mn_sw128(v_s + h * 4 * kLtPlane + ks * 2048, kLtPlane), lt_idesc(256, true),
+                      (t | ks) != 0);
+        umma_commit(bar(kEmpty, t & 1));
+        umma_commit(pv_done);
+        LT_TRACE(true, 6, t);
+        if (last) break;
       }
+      drain(drained_o);
     }
-    if (alive) alive = wait(p_full, (n_tiles - 1) & 1);
-    if (alive) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      second_product(n_tiles - 1);
-      __syncwarp();
-    }
-    // whatever was issued completes before the tensor memory is given back
-    if (lane == 0) umma_commit(drained);
-    __syncwarp();
-    (void)__all_sync(0xffffffffu, mbar_wait(drained, 0));
   } else {
     // ------------------------------------------------------------------------------------------ softmax and output
     const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t p_row = base + kLtPOff + row * 128;
     float m_used = 0.0f, l_run = 0.0f;
     bool alive = true;
-    for (int i = 0; i < n_tiles && alive; ++i) {
+    int tiles = 0;
+    for (int i = 0; alive; ++i) {
       const int sb = i & 1;
       // (the stage's own barrier too: it is what publishes the tile's validity masks)
       alive = wait(bar(kFull, sb), (i >> 1) & 1) && wait(bar(kSFull, sb), (i >> 1) & 1);
       if (!alive) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t sv[2][32];
-      tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys, sv[0]);
-      tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys + 32, sv[1]);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      lt_arrive(bar(kSEmpty, sb));
-      const uint32_t valid0 = masks_s[sb][0], valid1 = masks_s[sb][1];
-      const bool whole = (valid0 & valid1) == 0xffffffffu;
+      LT_TRACE(tid == 0, 7, i);
+      // The head's 64 products sit in the lane of its first thread; its second thread (lane + 16, which owns the
+      // upper half of O) takes the last 32 of them by shuffle, so that both do half of the exponentials.
+      uint32_t sv[32];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys, lo);
+        tmem_load_32(lane_addr + kLtSCol + sb * kLtKeys + 32, hi);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        lt_arrive(bar(kSEmpty, sb));
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const uint32_t other = __shfl_sync(0xffffffffu, hi[c], lane & 15);
+          sv[c] = half ? other : lo[c];
+        }
+      }
+      const uint32_t valid = info_s[sb][half];
+      const bool last = info_s[sb][2] != 0;
+      const bool whole = (info_s[sb][0] & info_s[sb][1]) == 0xffffffffu;
       // the tile's maximum of the row (raw products: the scale is positive)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (whole) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[0][c]));
-          mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[1][c]));
-        }
+        for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
       } else {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          mx4[c & 3] = fmaxf(mx4[c & 3], (valid0 >> c) & 1u ? __uint_as_float(sv[0][c]) : -INFINITY);
-          mx4[c & 3] = fmaxf(mx4[c & 3], (valid1 >> c) & 1u ? __uint_as_float(sv[1][c]) : -INFINITY);
-        }
+        for (int c = 0; c < 32; ++c)
+          mx4[c & 3] = fmaxf(mx4[c & 3], (valid >> c) & 1u ? __uint_as_float(sv[c]) : -INFINITY);
       }
-      const float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      float m_tile = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 16));
       // The maximum the exponents subtract is refreshed only when the tile's exceeds it by 2^8: P stays below 2^8,
-      // and O, which would have to be rescaled in tensor memory, almost never is.
+      // and O, which would have to be rescaled in tensor memory, almost never is. (Both threads of a head see the
+      // same maxima, so they take the same decisions.)
       float alpha = 1.0f;
       if (i == 0) {
         m_used = m_tile == -INFINITY ? 0.0f : m_tile;
@@ -294,15 +405,13 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
         alpha = fast_exp2(m_used - m_tile);
         m_used = m_tile;
       }
-      // (lanes 16-31 hold the upper half of the same head's O: they take the head's factor from lane & 15)
-      alpha = __shfl_sync(0xffffffffu, alpha, lane & 15);
-      m_used = __shfl_sync(0xffffffffu, m_used, lane & 15);
       const bool rescale = i > 0 && __any_sync(0xffffffffu, alpha != 1.0f);
       if (i > 0) {  // the last tile's second product is over: O is at rest and P may be overwritten
         alive = wait(pv_done, (i - 1) & 1);
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       }
+      LT_TRACE(tid == 0, 8, i);
       if (rescale) {
 #pragma unroll 1
         for (int c = 0; c < 256; c += 32) {
@@ -315,37 +424,36 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-      l_run *= alpha;
+      l_run *= alpha;  // (each thread sums its own 32 keys; the two sums meet at the end)
       float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int w = 0; w < 2; ++w) {
-        const uint32_t valid = w ? valid1 : valid0;
+      for (int c8 = 0; c8 < 4; ++c8) {
+        float e[8];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          float e[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const float s = __uint_as_float(sv[w][c8 * 8 + c]);
-            const bool ok = whole || ((valid >> (c8 * 8 + c)) & 1u);
-            e[c] = fast_exp2(fmaf(ok ? s : -INFINITY, p.scale_log2, -m_used));
-            l4[c & 3] += e[c];
-          }
-          if (half == 0)  // 16-byte slot (keys / 8) ^ (row % 8) of the head's row of P
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((w * 4 + c8) ^ (row & 7)) << 4)),
-                         "r"(pack_bf16x2(e[0], e[1])), "r"(pack_bf16x2(e[2], e[3])), "r"(pack_bf16x2(e[4], e[5])),
-                         "r"(pack_bf16x2(e[6], e[7]))
-                         : "memory");
+        for (int c = 0; c < 8; ++c) {
+          const float x = __uint_as_float(sv[c8 * 8 + c]);
+          const bool ok = whole || ((valid >> (c8 * 8 + c)) & 1u);
+          e[c] = fast_exp2(fmaf(ok ? x : -INFINITY, p.scale_log2, -m_used));
+          l4[c & 3] += e[c];
         }
+        // 16-byte slot (keys / 8) ^ (row % 8) of the head's row of P
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((half * 4 + c8) ^ (row & 7)) << 4)),
+                     "r"(pack_bf16x2(e[0], e[1])), "r"(pack_bf16x2(e[2], e[3])), "r"(pack_bf16x2(e[4], e[5])),
+                     "r"(pack_bf16x2(e[6], e[7]))
+                     : "memory");
       }
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       lt_proxy_fence();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       lt_arrive(p_full);
+      LT_TRACE(tid == 0, 9, i);
+      tiles = i + 1;
+      if (last) break;
     }
-    if (alive) alive = wait(pv_done, (n_tiles - 1) & 1);
+    if (alive) alive = wait(pv_done, (tiles - 1) & 1);
     if (alive) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      l_run = __shfl_sync(0xffffffffu, l_run, lane & 15);
+      l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
       if (row_ok && half == 0)
         (partial ? p.part_lse : p.lse)[out_row] =
@@ -393,12 +501,26 @@ __global__ void __launch_bounds__(kLtThreads, 1) latent_attend_tc_kernel(LatentP
   if (tid == 0 && abort_s && p.status) atomicAdd(p.status, 1);
 }
 
-int launch_latent_attend_tc(const LatentParams &p, cudaStream_t stream) {
+#ifdef LSA_LT_TRACE
+extern "C" __attribute__((visibility("default"))) int lsa_lt_trace_read(long long *host) {
+  return (int)cudaMemcpyFromSymbol(host, lsa_lt_trace, sizeof(lsa_lt_trace));
+}
+#endif
+
+int launch_latent_attend_tc(const LatentParams &p_in, cudaStream_t stream) {
+  LatentParams p = p_in;
+  // Runs of consecutive rows are staged by tensor-map copies when the cache can be described to one (16-byte aligned
+  // base and row pitch); otherwise every tile is gathered row by row.
+  CUtensorMap map_latent = {};
+  p.boxes = ((uintptr_t)p.latent % 16) == 0 && (p.latent_row_stride * 2) % 16 == 0 && p.slots > 0 &&
+                    make_map(&map_latent, p.latent, p.slots, 576, p.latent_row_stride, kLtKeys) == LSA_OK
+                ? 1
+                : 0;
   if (cudaFuncSetAttribute(latent_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kLtSmem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
   const dim3 grid((unsigned)(p.R * p.splits), (unsigned)((p.Hq + kLatHeads - 1) / kLatHeads));
-  latent_attend_tc_kernel<<<grid, kLtThreads, kLtSmem, stream>>>(p);
+  latent_attend_tc_kernel<<<grid, kLtThreads, kLtSmem, stream>>>(map_latent, p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }

@@ -67,6 +67,7 @@ class FlatLayer:
             raise ValueError(f"the maps must both be [{kv_heads * free}, index_dim] - got {tuple(query_map.shape)} "
                              f"and {tuple(key_map.shape)}")
         self.design = design
+        self.index_dim = key_map.shape[1]
         self.query_map, self.key_map = query_map.contiguous(), key_map.contiguous()
         self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
         self.dh_off = rotary.dim if rotary.end == "prefix" else 0
@@ -155,7 +156,7 @@ class FlatLayer:
 
     def _index_buffers(self, T: int, dev, reuse_buffers: bool) -> dict:
         """The tensors an index over T keys lives in (the layer's own buffers, or fresh ones)."""
-        d, d_idx = self.design, self.key_map.shape[1]
+        d, d_idx = self.design, self.index_dim
         blocks = T // d.cluster_block_size
         P, rows = d.cluster_block_size // d.pool_size, blocks * d.block_bucket_count
         make = (lambda name, shape, dtype: self._buffer(name, shape, dtype, dev)) if reuse_buffers else \
@@ -175,20 +176,25 @@ class FlatLayer:
                                                d.cluster_block_size))
 
     def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
-        """Index keys of k [n, Hkv, dh] = the keys at positions first.., and the pools, Ward labels and bucket table of
+        """Index keys of k [n, ...] = the keys at positions first.., and the pools, Ward labels and bucket table of
         the cluster blocks they close (first is a multiple of the block size): blocks are independent, so an index
         can be built as its keys arrive."""
         d = self.design
         n = k.shape[0]
-        b0, nb = first // d.cluster_block_size, n // d.cluster_block_size
-        r0, r1 = b0 * d.block_bucket_count, (b0 + nb) * d.block_bucket_count
         with probe.region("index map"):
-            keys = self.index_keys(k, out=bufs["keys"][first:first + n])
-        if nb == 0:
+            self.index_keys(k, out=bufs["keys"][first:first + n])
+        self._cluster_blocks(first // d.cluster_block_size, n // d.cluster_block_size, bufs)
+
+    def _cluster_blocks(self, b0: int, nb: int, bufs: dict) -> None:
+        """Pools, Ward labels and the bucket table of cluster blocks b0 .. b0 + nb - 1, whose index keys are in place."""
+        d = self.design
+        if nb <= 0:
             return
+        first = b0 * d.cluster_block_size
+        r0, r1 = b0 * d.block_bucket_count, (b0 + nb) * d.block_bucket_count
+        keys = bufs["keys"][first:first + nb * d.cluster_block_size]
         with probe.region("pool"):
-            pools = ops.pool_keys(keys[: nb * d.cluster_block_size].view(nb, d.cluster_block_size, -1), d.pool_size,
-                                  out=bufs["pools"][b0:b0 + nb])
+            pools = ops.pool_keys(keys.view(nb, d.cluster_block_size, -1), d.pool_size, out=bufs["pools"][b0:b0 + nb])
         with probe.region("ward"):
             labels, _ = ops.ward_rounds(pools, float(d.pool_size), d.block_bucket_count, d.bucket_cap,
                                         labels=bufs["labels"][b0:b0 + nb], reached=bufs["reached"][b0:b0 + nb])
@@ -333,7 +339,7 @@ class FlatLayer:
         stop = start + n
         positions = torch.arange(start, stop, device=dev)
         with probe.region("index map"):
-            index_queries = self.index_queries(rows, out=self._buffer("index queries", (n, self.query_map.shape[1]),
+            index_queries = self.index_queries(rows, out=self._buffer("index queries", (n, self.index_dim),
                                                                       torch.float32, dev))
         # The window and the sinks are the same keys for neighbouring rows: one dense band serves them, and the
         # read of the selected keys starts from its partial result.

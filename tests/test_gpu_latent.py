@@ -145,6 +145,56 @@ def test_latent_attend_with_a_growing_maximum(oracle, splits):
     assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
 
 
+@pytest.mark.parametrize("splits", [1, 4])
+def test_latent_attend_over_runs_of_consecutive_rows(oracle, splits):
+    """Lists as an expansion writes them: pools of 64 consecutive rows starting anywhere, a run cut short, a long
+    window, sinks, a run that ends with the cache, and scattered ids between them. Whole runs of 64 are staged by
+    tensor-map copies and everything else row by row; both must see exactly the listed rows."""
+    from lsa_b200 import ops
+
+    rng = np.random.default_rng(21)
+    rows, heads, slots, width = 7, 64, 9000, 2600
+    q, latent, _, _ = _latent_case(9, rows, heads, slots, 8, ragged=False)
+    ids = np.full((rows, width), -1, dtype=np.int32)
+    lengths = np.zeros(rows, dtype=np.int32)
+    for r in range(rows):
+        pieces = []
+        taken = np.zeros(slots, dtype=bool)
+        for _ in range(int(rng.integers(8, 24))):
+            n = int(rng.choice([64, 64, 64, 128, 40, 17, 5, 1]))
+            first = int(rng.integers(4, slots - 700 - n))
+            if taken[first:first + n].any():
+                continue
+            taken[first:first + n] = True
+            pieces.append(np.arange(first, first + n))
+        if r % 2:
+            pieces.append(np.arange(slots - 64, slots))            # a run that ends with the cache
+        pieces.append(np.arange(slots - 700, slots - 700 + 517))   # the window
+        pieces.append(np.arange(0, 4))                             # the sinks
+        row = np.concatenate(pieces).astype(np.int32)
+        ids[r, : len(row)] = row
+        lengths[r] = len(row)
+    scale = 576 ** -0.5
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = ops.latent_attend(cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths), scale,
+                                 splits=splits, out_dtype=torch.float32, status=status)
+    want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
+                                          np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    assert int(status) == 0
+    gap = np.abs(out.cpu().numpy() - want[:, :, :512])
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (gap.max(), gap.mean())
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
+    # a cache that is a strided view (rows 1,200 bytes apart) and ids past its end
+    wide = torch.zeros(slots - 100, 600, dtype=torch.bfloat16, device="cuda")
+    wide[:, :576] = cuda(latent[: slots - 100], torch.bfloat16)
+    out2, _ = ops.latent_attend(cuda(q, torch.bfloat16), wide[:, :576], cuda(ids), cuda(lengths), scale, splits=splits,
+                                out_dtype=torch.float32)
+    keep = np.where(ids < slots - 100, ids, -1)
+    want2, _ = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], keep,
+                                    np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    assert np.abs(out2.cpu().numpy() - want2[:, :, :512]).max() <= 2e-2
+
+
 def test_latent_attend_long_lists_in_bf16(oracle):
     """Lists of thousands of keys (a hundred tiles a row), ragged ends, bf16 output: the size a served row has."""
     from lsa_b200 import ops
