@@ -75,7 +75,7 @@ int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group
 int lsa_index_map_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_row_stride, const uint16_t *Wt,
                      int d_idx, int normalize, float *out_f32, uint16_t *out_bf16, int32_t *status, void *stream);
 
-/* out = gelu(x @ Wt^T) in bf16, the hidden layer of the BASELINE-only two-layer map (no counterpart in the
+/* out = gelu(x @ Wt^T) in bf16, the hidden layer of the two-layer map (no counterpart in the
  * reference, whose maps are one linear projection); the second layer is lsa_index_map_tc over `out`.
  *   x [rows, d_in] bf16, Wt [d_out, d_in] bf16, out_bf16 [rows, d_out]; d_out a multiple of 128. */
 int lsa_gemm_gelu_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_row_stride, const uint16_t *Wt,
@@ -124,7 +124,7 @@ int lsa_bucket_table(const void *index_keys, int key_dtype, const int64_t *label
                      uint16_t *centroids_bf16, int32_t *status, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
- * Update step of the BASELINE-only k-means bucketing (the reference has no k-means: its buckets are Ward's). The
+ * Update step of the k-means bucketing (the reference has no k-means: its buckets are Ward's). The
  * assignment step is lsa_flat_select with top_p = 1 over the centroids (first maximum = lower id on a tie); this
  * replaces every non-empty cluster's centroid by the normalised sum of its pools, added in pool order.
  *   pools [n, d] fp32; order [n] int64 - the pools cluster by cluster, ascending inside a cluster;

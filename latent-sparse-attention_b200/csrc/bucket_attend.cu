@@ -144,8 +144,8 @@ __global__ void __launch_bounds__(256) bucket_segments_kernel(BucketParams p) {
 // ---------------------------------------------------------------------------------------------- attend
 
 // grid (segment bound, Hkv); blockDim = group * 32: warp w serves query head h * group + w.
-// Occupancy decides this kernel. At 96 registers and one query buffer a warp, four CTAs of five warps share an SM
-// (66 ms a step of 16 chunks); at 128 registers and two buffers three did (71 ms); uncapped, one did (125 ms).
+// Occupancy decides this kernel: at 96 registers and one query buffer a warp, four CTAs of five warps share an SM;
+// at 128 registers and two buffers three do, and uncapped one does, each markedly slower.
 template <int DH>
 __global__ void __maxnreg__(96) bucket_attend_kernel(BucketParams p) {
   constexpr int ROW_BYTES = DH * 2;

@@ -440,7 +440,7 @@ LSA_API int lsa_gather_sum(const void *src, int src_dtype, const void *index, in
 
 namespace lsa {
 
-// Update step of the BASELINE-only k-means bucketing: cluster j's new centroid is the normalised sum of the pools
+// Update step of the k-means bucketing: cluster j's new centroid is the normalised sum of the pools
 // assigned to it, added one by one in pool order (`order` lists the pools cluster by cluster, ascending within a
 // cluster; `offsets[j] .. offsets[j + 1]` is cluster j's run). An empty cluster, or one whose sum is zero, keeps its
 // centroid. One CTA a cluster; the norm is a single thread's fma chain so that it equals a CPU replay.

@@ -107,7 +107,8 @@ def build_hierarchy(index_keys: torch.Tensor, buckets: Buckets, top_level: int, 
 
 
 def growth_at(hierarchy: Hierarchy, closed_buckets: int, page_buckets: int, growth_buckets: int) -> Growth:
-    """Replay growing at every page end up to `closed_buckets`, from the counts alone (hierarchy.py:165-196)."""
+    """Replay growing at every page end up to `closed_buckets`, from the counts alone. Integer bookkeeping that must
+    match the reference count for count, so it is transcribed from it (src/lsa/core/hierarchy.py:165-196)."""
     sizes = hierarchy.node_cluster_block_sizes
     top_level, size, first_block = len(sizes), hierarchy.node_bucket_size, sizes[0]
     covered, made, closed = 0, [0] * top_level, [0] * top_level

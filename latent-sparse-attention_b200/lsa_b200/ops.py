@@ -84,7 +84,7 @@ def index_map_tc(x: torch.Tensor, weight_t: torch.Tensor, normalize: bool = True
 
 def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: torch.Tensor | None = None,
             out: torch.Tensor | None = None):
-    """The BASELINE-only two-layer map normalize(gelu(x @ W1) @ W2) on the tensor cores: x [rows, d_in] bf16,
+    """The two-layer map (no counterpart in the reference) normalize(gelu(x @ W1) @ W2) on the tensor cores: x [rows, d_in] bf16,
     w1_t [d_hidden, d_in], w2_t [d_idx, d_hidden] bf16 -> fp32 [rows, d_idx]. The hidden layer is held in bf16."""
     rows, d_in = x.shape
     d_hidden = w1_t.shape[0]
@@ -185,7 +185,7 @@ def gather_sum(src: torch.Tensor, index: torch.Tensor, index_base: int = 0) -> t
 
 
 def kmeans(pools: torch.Tensor, init_centroids: torch.Tensor, iters: int):
-    """BASELINE-only k-means bucketing (no counterpart in the reference): `iters` Lloyd iterations over pool keys
+    """k-means bucketing (no counterpart in the reference): `iters` Lloyd iterations over pool keys
     [n, d] from `init_centroids` [k, d]; returns (centroids [k, d] fp32, assignment [n] int32). Assignment is the
     exact fixed-order argmax of pool . centroid (a tie to the lower cluster)."""
     pools = _contig(pools.float())

@@ -280,3 +280,148 @@ class ShardedFlatLayer:
             partial *= weight[..., None]
             dist.all_reduce(partial, group=self.group)
         return partial.to(q.dtype)
+
+
+def exchange_rows(partial: torch.Tensor, lse: torch.Tensor, group=None) -> tuple:
+    """Every rank holds a partial result for ALL rows; rank j needs every rank's partial for ITS rows. One
+    all-to-all of the outputs and one of the log-sum-exps: ([world, R / world, ...], [world, R / world, ...]) - the
+    parts a local merge kernel reads (what a reduce-scatter of weighted outputs does in the collective, without
+    the weighting pass before it)."""
+    world = dist.get_world_size(group)
+    rows = partial.shape[0]
+    if rows % world:
+        raise ValueError(f"{rows} rows do not split over {world} ranks")
+    parts = torch.empty(world, rows // world, *partial.shape[1:], dtype=partial.dtype, device=partial.device)
+    lses = torch.empty(world, rows // world, *lse.shape[1:], dtype=lse.dtype, device=lse.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(parts, partial.contiguous(), group=group)
+        dist.all_to_all_single(lses, lse.contiguous(), group=group)
+    else:  # gloo has no all-to-all: gather everything and keep this rank's rows
+        rank, share = dist.get_rank(group), rows // world
+        parts.copy_(gather_pieces(partial, group)[:, rank * share:(rank + 1) * share])
+        lses.copy_(gather_pieces(lse, group)[:, rank * share:(rank + 1) * share])
+    return parts, lses
+
+
+class ShardedLatentLayer:
+    """`LatentLayer` over a latent cache dealt across ranks: rows in granules of 64 positions (a pool of config 4, so
+    a bucket's pools and a window stay runs of consecutive rows on every rank), cluster blocks round-robin. A step on
+    rank r: map the replicated queries, score the centroids of its own blocks, all-gather the candidates and cut them
+    with the single-GPU tie rule, expand the picks into the rows it stores, attend over them, and merge the partial
+    outputs by their log-sum-exps - after an all-to-all for a prefill chunk (each rank keeps its share of the rows),
+    after an all-gather for a decode step (every rank keeps the row)."""
+
+    def __init__(self, layer, rank: int, world: int, group=None, granule: int = GRANULE):
+        self.layer, self.rank, self.world, self.group, self.granule = layer, rank, world, group, granule
+        self.design = layer.design
+        self.index_keys = self.centroids = self.members = None
+
+    def _cluster(self, keys: torch.Tensor, first_position: int):
+        """Pools, Ward and the bucket table of whole blocks whose index keys are `keys` [blocks * block, d]."""
+        d = self.design
+        blocks = keys.shape[0] // d.cluster_block_size
+        pools = ops.pool_keys(keys.view(blocks, d.cluster_block_size, -1), d.pool_size)
+        labels, _ = ops.ward_rounds(pools, float(d.pool_size), d.block_bucket_count, d.bucket_cap)
+        members, _, _, centroids, _, _ = ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count, d.bucket_cap,
+                                                          first_position=first_position)
+        return members, centroids
+
+    def build_index(self, share: torch.Tensor, tokens: int) -> None:
+        """From this rank's dealt rows [tokens / world, latent_dim]: every index key (all-gathered), the centroids of
+        its own blocks and the global member table."""
+        d, layer, world, rank = self.design, self.layer, self.world, self.rank
+        blocks, block, per_block = tokens // d.cluster_block_size, d.cluster_block_size, d.block_bucket_count
+        if tokens % block or blocks % world or tokens % (self.granule * world):
+            raise ValueError(f"{tokens} tokens must be whole cluster blocks of {block}, a multiple of {world} of them")
+        with probe.region("index map"):
+            own_keys = layer.index_keys(share)
+        with probe.region("gather index keys"):
+            self.index_keys = undeal(gather_pieces(own_keys, self.group), self.granule)
+        del own_keys
+        mine = self.index_keys.view(blocks // world, world, block, -1)[:, rank].reshape(blocks // world * block, -1)
+        with probe.region("ward"):
+            members, self.centroids = self._cluster(mine, 0)
+            members = torch.where(members >= 0, members // block * (world * block) + rank * block + members % block,
+                                  members)
+        with probe.region("gather members"):
+            every = gather_pieces(members, self.group)
+            self.members = every.view(world, blocks // world, per_block, d.bucket_cap).transpose(0, 1).reshape(
+                blocks * per_block, d.bucket_cap).contiguous()
+
+    def extend_index(self, share: torch.Tensor, first: int, count: int) -> None:
+        """The index step of a prefill chunk at positions first .. first + count - 1: every rank maps the rows of
+        the chunk it stores, the chunk's index keys are all-gathered, and the cluster blocks that close inside
+        (first, first + count] are clustered - by every rank, a fraction of a millisecond that saves an exchange of
+        their members; a rank keeps the centroids of its own blocks only."""
+        d, layer, world, rank = self.design, self.layer, self.world, self.rank
+        block, per_block = d.cluster_block_size, d.block_bucket_count
+        if first % (self.granule * world) or count % (self.granule * world):
+            raise ValueError("a chunk must deal out in whole granules over the ranks")
+        with probe.region("index map"):
+            own = layer.index_keys(share[first // world:(first + count) // world])
+        with probe.region("gather index keys"):
+            self.index_keys[first:first + count] = undeal(gather_pieces(own, self.group), self.granule)
+        b0, b1 = first // block, (first + count) // block
+        if b1 <= b0:
+            return
+        with probe.region("ward"):
+            members, centroids = self._cluster(self.index_keys[b0 * block:b1 * block], b0 * block)
+            self.members[b0 * per_block:b1 * per_block] = members
+            for b in range(b0, b1):
+                if b % world == rank:
+                    at = (b // world) * per_block
+                    self.centroids[at:at + per_block] = centroids[(b - b0) * per_block:(b - b0 + 1) * per_block]
+
+    def select(self, rows: torch.Tensor, positions: torch.Tensor) -> tuple:
+        """This rank's share of every row's read list, as rows of its own cache: (lists, lengths). A collective call
+        (the candidates are exchanged inside). Local row l of rank r is position (l / granule * world + r) * granule
+        + l % granule."""
+        layer, d, world, rank = self.layer, self.design, self.world, self.rank
+        per_block = d.block_bucket_count
+        with probe.region("index map"):
+            index_queries = layer.index_queries(rows)
+        closed = positions // d.cluster_block_size
+        visible = (((closed - rank + world - 1) // world).clamp_min(0) * per_block).clamp_max(
+            self.centroids.shape[0]).to(torch.int32)
+        with probe.region("select"):
+            if rows.shape[0] <= 8:
+                keys, _ = ops.flat_select_decode(index_queries, self.centroids, None, visible, d.top_p, splits=4)
+            else:
+                keys, _ = ops.flat_select(index_queries, self.centroids, visible, d.top_p)
+            keys = globalise_keys(keys, per_block, rank, world)
+        with probe.region("exchange candidates"):
+            every = gather_candidates(keys, self.group)
+        with probe.region("select"):
+            _, picked = ops.merge_candidates(every)
+        with probe.region("expand"):
+            lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size,
+                                           dealt=(self.granule, world, rank))
+        return lists, lengths
+
+    def _read_rows(self, rows: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int) -> tuple:
+        layer = self.layer
+        lists, lengths = self.select(rows, positions)
+        with probe.region("attend"):
+            return ops.latent_attend(rows, share, lists, lengths, layer.scale, value_dim=layer.value_dim,
+                                     splits=splits, out_dtype=torch.float32, status=layer._attend_status)
+
+    def prefill_rows(self, rows: torch.Tensor, start: int, share: torch.Tensor, out: torch.Tensor | None = None):
+        """The read of replicated query rows [n, heads, latent_dim] at positions start.. : this rank's share of the
+        output rows, [n / world, heads, value_dim] bf16 (rows rank * n / world .. of the chunk)."""
+        positions = torch.arange(start, start + rows.shape[0], device=rows.device)
+        partial, lse = self._read_rows(rows, positions, share, 1)
+        with probe.region("merge partials"):
+            parts, lses = exchange_rows(partial, lse, self.group)
+            merged, _ = ops.lse_merge(parts, lses, out_dtype=torch.bfloat16)
+        if out is not None:
+            out.copy_(merged)
+            return out
+        return merged
+
+    def decode(self, q: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int = 32) -> torch.Tensor:
+        """One step for replicated rows [R, heads, latent_dim] at `positions`: the whole output on every rank."""
+        partial, lse = self._read_rows(q, positions.to(torch.int64), share, splits)
+        with probe.region("merge partials"):
+            merged, _ = ops.lse_merge(gather_pieces(partial, self.group), gather_pieces(lse, self.group),
+                                      out_dtype=torch.bfloat16)
+        return merged

@@ -100,3 +100,47 @@ def test_bucket_major_read_alone_under_row_budgets_and_missing_picks(oracle, war
     assert np.abs(got_lse[held] - want_lse[held]).max() <= 2e-2
     # cut lists: some row's running count must have stopped inside a bucket for the budget to have been exercised
     assert (lens.cpu().numpy()[early] == 90).any()
+
+
+@pytest.mark.parametrize("warp_mma", [False, True])
+def test_full_buckets_a_bucket_across_the_sinks_and_a_bucket_with_many_pairs(oracle, warp_mma):
+    """The edges of the bucket-major pass that clustered data seldom meets: every bucket full to the cap of 64, a
+    bucket whose members straddle the sink boundary (its first ids belong to the sinks and are not read as
+    expansion), one bucket picked by every row (far more than the 256 pairs a CTA takes, so it is cut into
+    segments), and members past the cache handed in (skipped, as the gather path skips them)."""
+    from lsa_b200 import ops
+
+    rng = np.random.default_rng(3)
+    T, Hq, Hkv, dh, cap = 4096, 10, 2, 128, 64
+    q, k, v = layer_inputs(T, Hq, Hkv, dh, 16, 13)
+    buckets_n = T // cap
+    members = np.arange(T, dtype=np.int32).reshape(buckets_n, cap)  # bucket b = positions 64 b .. 64 b + 63, all full
+    first, rows, top_p, top_k, sink, window, scale = 3000, 700, 6, 384, 4, 256, 128 ** -0.5
+    positions = np.arange(first, first + rows)
+    picked = np.empty((rows, top_p), dtype=np.int32)
+    for r in range(rows):
+        # everybody reads bucket 0 (sinks inside) and bucket 7; the rest at random among the buckets before the window
+        others = rng.choice(np.arange(1, (first - window) // cap), top_p - 2, replace=False)
+        picked[r] = np.concatenate([[7, 0], others])
+        rng.shuffle(picked[r])
+    want_lists, want_len = oracle.expand(picked, positions, members, top_k, sink, window)
+    assert (want_len == want_len[0]).all() and want_len[0] == (top_p * cap - sink) + window + sink
+    Q, K, V = (cuda(a, torch.bfloat16) for a in (q, k, v))
+    rows_q = Q[first:first + rows]
+    pos, mem, pk = cuda(positions), cuda(members), cuda(picked)
+    band = ops.band_attend(rows_q, K, V, first, window, sink, scale)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out, lse = ops.bucket_attend(rows_q, K, V, pk, pos, mem, top_k, sink, window, scale, init=band, warp_mma=warp_mma,
+                                 status=status)
+    want, want_lse = oracle.sparse_attend(q[positions], k, v, want_lists, positions, 0, 0, scale, lengths=want_len)
+    assert int(status) == 0
+    _close(out.float().cpu().numpy(), want, "oracle")
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 2e-2
+
+    # the same picks over a cache that ends before some members: those ids are skipped
+    short = 2000
+    lists, lens, _ = ops.expand(pk, pos, mem, top_k, sink, window, local=False)
+    want_s, _ = ops.sparse_attend(rows_q, K[:short], V[:short], lists, lens, scale)
+    got_s, _ = ops.bucket_attend(rows_q, K[:short], V[:short], pk, pos, mem, top_k, sink, window, scale,
+                                 warp_mma=warp_mma)
+    _close(got_s.float().cpu().numpy(), want_s.float().cpu().numpy(), "short cache")

@@ -66,7 +66,7 @@ def test_tensor_core_map_matches_the_oracle(ops, oracle, T, Hq, Hkv, dh, d_idx, 
 
 
 def test_two_layer_map_matches_its_restatement(ops, oracle):
-    """BASELINE-only variant (no reference code): the oracle restatement is the only pin."""
+    """A variant with no reference code: the oracle restatement is the only pin."""
     from scipy.special import erf
 
     rng = np.random.default_rng(3)
@@ -164,7 +164,7 @@ def test_ward_golden_and_adversarial_cases(ops, oracle):
 
 
 def test_kmeans_bucketing_matches_its_restatement(ops, oracle):
-    """BASELINE-only variant (no reference code): config 1's shapes - 1,024 pools, 256 centres, 32 dims, 10 rounds."""
+    """A variant with no reference code: config 1's shapes - 1,024 pools, 256 centres, 32 dims, 10 rounds."""
     keys = unit_rows(mixture(16384, 32, 64, 0.3, 8))
     pools = oracle.pool_keys(keys[None], 16)[0]
     rng = np.random.default_rng(0)

@@ -107,3 +107,61 @@ def test_the_rows_a_rank_keeps_partition_every_chunk():
     dealt = torch.stack([deal(rows, rank, world) for rank in range(world)])
     assert dealt[1, :64, 0].tolist() == list(range(64, 128)) and dealt[1, 64, 0] == 64 + 64 * world
     assert torch.equal(undeal(dealt), rows)
+
+
+def test_a_layer_raises_what_its_kernels_reported():
+    """`FlatLayer.check()` reads the status words the kernels raise and the per-block `reached` flags of the last
+    index builds; here they are set by hand, on the host, as a kernel would have set them."""
+    from lsa_b200.layer import FlatDesign, FlatLayer
+
+    maps = torch.randn(2 * 128, 32)
+    layer = FlatLayer(FlatDesign(pool_size=4, bucket_size=8, bucket_cap=16, cluster_block_size=64, top_p=8, top_k=64,
+                                 window_size=64), maps, maps, 4, 2, 128)
+    layer.check()  # nothing was reported
+    layer._reached.append(torch.tensor([1, 0, 1], dtype=torch.uint8))
+    with pytest.raises(ValueError, match="1 cluster blocks stopped short"):
+        layer.check()
+    layer.check()  # the report was consumed
+    layer._table_status += 2
+    with pytest.raises(ValueError, match="2 buckets overflowed"):
+        layer.check()
+    layer._attend_status += 1
+    with pytest.raises(RuntimeError, match="bounded on-chip waits gave up"):
+        layer.check()
+    layer._expand_status += 3
+    with pytest.raises(ValueError, match="3 picked bucket ids"):
+        layer.check()
+    assert not layer.status.any()
+
+
+def test_an_address_keeps_its_tensor_alive():
+    import ctypes
+    import gc
+    import weakref
+
+    from lsa_b200._lib import Address
+
+    tensor = torch.zeros(8)
+    address = Address(tensor)
+    alive = weakref.ref(tensor)
+    del tensor
+    gc.collect()
+    assert alive() is not None and int(address) == address.tensor.data_ptr()
+    assert ctypes.c_void_p.from_param(address) is not None  # ctypes takes it where it takes an int
+
+
+def test_workload_generators_are_seeded_and_shaped():
+    from lsa_b200 import workloads as W
+
+    cfg = W.cut(W.C2, 2048)
+    a, b = W.gqa_inputs(cfg), W.gqa_inputs(cfg)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    q, k, v, wq, wk = a
+    assert q.shape == (2048, 40, 128) and k.shape == (2048, 8, 128) and wq.shape == (1024, 64)
+    lengths = W.request_lengths(W.C5)
+    assert len(lengths) == 64 and lengths.min() >= 32768 and lengths.max() <= 524288 and not (lengths % 1024).any()
+    small = dict(W.C1, tokens=2048)
+    q1, k1, v1, index_map = W.c1_inputs(small)
+    assert index_map.shape == (256, 32) and torch.allclose(index_map.t() @ index_map, torch.eye(32), atol=1e-4)
+    for name, cfg in W.CONFIGS.items():
+        W.design_of(cfg)  # the sizes of every config nest and fill their top_k

@@ -90,6 +90,13 @@ def _rank_main(rank, world, port, result_dir):
         out = reduce_rows(torch.from_numpy(part) * weight[..., None])
         share = 32 // world
         np.testing.assert_allclose(out.numpy(), whole[rank * share:(rank + 1) * share], rtol=0, atol=5e-6)
+        # the all-to-all form: every rank receives all ranks' parts of ITS rows and merges them locally
+        from lsa_b200.parallel import exchange_rows
+        parts, lses = exchange_rows(torch.from_numpy(part), torch.from_numpy(lse))
+        assert parts.shape == (world, share, Hq, dh) and lses.shape == (world, share, Hq)
+        merged, merged_lse = oracle.lse_merge(parts.numpy(), lses.numpy())
+        np.testing.assert_allclose(merged, whole[rank * share:(rank + 1) * share], rtol=0, atol=5e-6)
+        np.testing.assert_allclose(merged_lse, whole_lse[rank * share:(rank + 1) * share], rtol=0, atol=2e-6)
         # a row nobody reads has weight zero everywhere, not NaN
         weight, total = merge_weight(torch.full((3, 2), float("-inf")))
         assert not weight.any() and torch.isinf(total).all()
