@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   __shared__ __align__(8) uint64_t bars[3];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
+  __shared__ uint32_t valid_s[2];  // which members of the bucket name a row of the cache
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
@@ -120,8 +121,17 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   }
   // members that name a row of the cache handed in: a key outside it is staged as zeros and masked out of the softmax,
   // as the row-by-row read skips such ids
-  const uint64_t valid_word = (uint64_t)__ballot_sync(0xffffffffu, ids_s[lane] >= 0 && ids_s[lane] < p.slots) |
-                              ((uint64_t)__ballot_sync(0xffffffffu, ids_s[lane + 32] >= 0 && ids_s[lane + 32] < p.slots) << 32);
+  // (the word stays in shared memory and only a flag in a register: every member is in the cache as a rule, and a
+  // 64-bit word held through the tile loop costs this kernel spills)
+  bool all_valid;
+  {
+    const uint32_t v_lo = __ballot_sync(0xffffffffu, ids_s[lane] >= 0 && ids_s[lane] < p.slots),
+                   v_hi = __ballot_sync(0xffffffffu, ids_s[lane + 32] >= 0 && ids_s[lane + 32] < p.slots);
+    all_valid = __popc(v_lo) + __popc(v_hi) == n_members;
+    if (tid == 0) valid_s[0] = v_lo, valid_s[1] = v_hi;
+  }
+  // which of keys c0 .. c0 + 7 name a row of the cache, a bit each
+  auto valid_byte = [&](int c0) { return all_valid ? 0xFFu : (valid_s[c0 >> 5] >> (c0 & 31)) & 0xFFu; };
   const int n_keys = max(16, (n_members + 15) & ~15);  // the N of S and the K of O: whole 16-key steps
 
   // Step k of the MMAs (warp 0; the whole warp waits so that its lanes stay together, lane 0 issues): once the k-th
@@ -236,7 +246,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
       for (int j = 0; j < 4; ++j) {
         const int c0 = (2 * j + half) * 8;
         active[j] = c0 < n_keys;
-        whole[j] = __all_sync(0xffffffffu, c0 >= lo_key && c0 + 8 <= hi_key) && ((valid_word >> c0) & 0xFFu) == 0xFFu;
+        whole[j] = __all_sync(0xffffffffu, c0 >= lo_key && c0 + 8 <= hi_key) && valid_byte(c0) == 0xFFu;
         if (go && active[j]) tmem_load_8(lane_addr + c0, sv[j]);
       }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -251,9 +261,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
 #pragma unroll
           for (int c = 0; c < 8; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[j][c]));
         } else {
+          const uint32_t vb = valid_byte(c0);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {  // (bitwise logic and selects: branches here would diverge lane by lane)
-            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((valid_word >> (c0 + c)) & 1u);
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((vb >> c) & 1u);
             mx4[c & 3] = fmaxf(mx4[c & 3], ok ? __uint_as_float(sv[j][c]) : -INFINITY);
           }
         }
@@ -276,9 +287,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
             sv[j][c] = __float_as_uint(e);
           }
         } else {
+          const uint32_t vb = valid_byte(c0);
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((valid_word >> (c0 + c)) & 1u);
+            const bool ok = (c0 + c >= lo_key) & (c0 + c < hi_key) & (bool)((vb >> c) & 1u);
             const float e = fast_exp2(fmaf(ok ? __uint_as_float(sv[j][c]) : -INFINITY, p.scale_log2, -m_row));
             l4[c & 3] += e;
             sv[j][c] = __float_as_uint(e);

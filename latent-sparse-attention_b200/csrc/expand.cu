@@ -1,5 +1,7 @@
 // Expansion: a row's picked buckets become its read list - members best bucket first, then the window, then
 // the sinks. Pure integer work, one warp a row, ballot-compacted so the order is the table's order.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace lsa {
@@ -233,6 +235,131 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
   }
 }
 
+// The same list from a CLUSTER of eight CTAs a row: a decode row of a long context lists hundreds of kilobytes of ids,
+// more than one SM moves in the time the rest of the step takes. Each CTA counts and writes an eighth of the picks;
+// the CTAs' totals cross through distributed shared memory, which is all the exchange a prefix sum over picks needs.
+constexpr int kClusterCtas = 8;
+constexpr int kClusterThreads = 512;
+
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
+    expand_cluster_kernel(ExpandParams p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  constexpr int kMine = kWideMaxPicks / kClusterCtas;  // picks a CTA takes, at most
+  __shared__ int64_t bucket_s[kMine];
+  __shared__ int count_s[kMine];
+  __shared__ int start_s[kMine];
+  __shared__ int total_s, bad_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kWarps = kClusterThreads / 32;
+  const int cta = (int)cluster.block_rank();
+  const int64_t r = blockIdx.y;
+  const int64_t pos = p.positions[r];
+  const int64_t request = p.row_request ? p.row_request[r] : 0;
+  const int32_t *table = p.page_table ? p.page_table + request * p.page_table_stride : nullptr;
+  const int row_p = p.row_top_p ? min(p.row_top_p[r], p.top_p) : p.top_p;
+  const int row_k = p.row_top_k ? min(p.row_top_k[r], p.top_k) : p.top_k;
+  const int64_t window_start = max((int64_t)0, pos + 1 - p.window);
+  int32_t *out = p.selected + r * p.width;
+  const unsigned below = (1u << lane) - 1;
+  const int share = (row_p + kClusterCtas - 1) / kClusterCtas;
+  const int first_pick = cta * share;
+  const int picks = max(0, min(share, row_p - first_pick));
+  if (tid == 0) bad_s = 0;
+  __syncthreads();
+  for (int i = tid; i < picks; i += kClusterThreads) {
+    int64_t bucket = p.picked[r * p.top_p + first_pick + i];
+    if (bucket >= 0 && p.bucket_pages) {
+      const int64_t slot = bucket / p.bucket_page_rows;
+      const int page = slot < p.bucket_max_pages ? p.bucket_pages[request * p.bucket_pages_stride + slot] : -1;
+      bucket = page >= 0 ? (int64_t)page * p.bucket_page_rows + bucket % p.bucket_page_rows : p.m;
+    }
+    if (bucket >= p.m) {
+      bucket = -1;
+      atomicAdd(&bad_s, 1);
+    }
+    bucket_s[i] = bucket;
+  }
+  __syncthreads();
+  for (int pick = warp; pick < picks; pick += kWarps) {
+    const int64_t bucket = bucket_s[pick];
+    int n = 0;
+    if (bucket >= 0)
+      for (int at0 = 0; at0 < p.cap; at0 += 128) {  // four loads in flight
+        int32_t ids[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int at = at0 + 32 * j + lane;
+          ids[j] = at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) n += __popc(__ballot_sync(0xffffffffu, ids[j] >= p.sink && ids[j] < window_start));
+      }
+    if (lane == 0) count_s[pick] = n;
+  }
+  __syncthreads();
+  if (warp == 0) {  // this CTA's picks, scanned; its total for the others
+    int carry = 0;
+    for (int base = 0; base < picks; base += 32) {
+      const int v = base + lane < picks ? count_s[base + lane] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (base + lane < picks) start_s[base + lane] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) total_s = carry;
+  }
+  cluster.sync();
+  int before = 0, all = 0;  // ids of the CTAs before this one, and of all of them
+  for (int c = 0; c < kClusterCtas; ++c) {
+    const int t = *cluster.map_shared_rank(&total_s, c);
+    if (c < cta) before += t;
+    all += t;
+  }
+  for (int pick = warp; pick < picks; pick += kWarps) {
+    const int64_t bucket = bucket_s[pick];
+    int written = before + start_s[pick];
+    if (bucket < 0) continue;
+    for (int at0 = 0; at0 < p.cap && written < row_k; at0 += 128) {
+      int32_t ids[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int at = at0 + 32 * j + lane;
+        ids[j] = at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool counts = ids[j] >= p.sink && ids[j] < window_start;
+        const unsigned votes = __ballot_sync(0xffffffffu, counts);
+        const int at = written + __popc(votes & below);
+        if (counts && at < row_k) out[at] = stored_id(p, table, ids[j]);
+        written += __popc(votes);
+      }
+    }
+  }
+  // the window, the sinks and the padding: an eighth of each a CTA
+  int total = min(all, row_k);
+  const int gtid = cta * kClusterThreads + tid, gthreads = kClusterCtas * kClusterThreads;
+  if (!(p.flags & LSA_EXPAND_NO_LOCAL)) {
+    const int in_window = (int)(pos + 1 - window_start);
+    for (int i = gtid; i < in_window; i += gthreads) out[total + i] = stored_id(p, table, window_start + i);
+    total += in_window;
+    const int sinks = (int)min((int64_t)p.sink, min(window_start, pos + 1));
+    for (int i = gtid; i < sinks; i += gthreads) out[total + i] = stored_id(p, table, i);
+    total += sinks;
+  }
+  for (int j = total + gtid; j < p.width; j += gthreads) out[j] = LSA_PAD;
+  if (tid == 0) {
+    if (cta == 0) p.lengths[r] = total;
+    if (bad_s && p.status) atomicAdd(p.status, bad_s);
+  }
+  cluster.sync();  // nobody leaves while its total may still be read
+}
+
 }  // namespace lsa
 
 LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, const int64_t *positions,
@@ -285,6 +412,13 @@ LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, cons
   p.page_size = page_size;
   p.width = top_k + window + sink;
   const bool keeps_all = owner_world <= 1 && owner_first <= 0 && owner_end == INT64_MAX;
+  if (R <= 8 && keeps_all && top_p <= lsa::kWideMaxPicks && (int64_t)top_p * bucket_cap >= 32768) {
+    // a few rows with very long lists: a cluster of CTAs a row
+    const dim3 grid(lsa::kClusterCtas, (unsigned)R);
+    lsa::expand_cluster_kernel<<<grid, lsa::kClusterThreads, 0, (cudaStream_t)stream>>>(p);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
   if (R <= 64 && keeps_all && top_p <= lsa::kWideMaxPicks && (int64_t)top_p * bucket_cap >= 4096) {
     // a decode step's long lists: one CTA a row
     lsa::expand_wide_kernel<<<(unsigned)R, lsa::kWideThreads, 0, (cudaStream_t)stream>>>(p);

@@ -120,8 +120,8 @@ def latent_cache(cfg: dict, gen: torch.Generator, world: int = 1, rank: int = 0,
     ONE cache). Returns (cache or share, the last `keep_tail` rows in full)."""
     T, dk, dv = cfg["tokens"], cfg["latent_dim"], cfg["value_dim"]
     piece = min(1 << 18, T)
-    if T % piece or piece % (granule * world) or keep_tail > piece:
-        raise ValueError(f"{T} tokens do not split into pieces of {piece} rows dealt over {world} ranks")
+    if T % (granule * world) or keep_tail > min(piece, T % piece or piece):
+        raise ValueError(f"{T} tokens do not deal out in granules of {granule} over {world} ranks")
     share = T // world
     tail = None
     cache = torch.empty(share, dk, dtype=torch.bfloat16, device="cuda")

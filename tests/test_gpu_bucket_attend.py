@@ -120,7 +120,8 @@ def test_full_buckets_a_bucket_across_the_sinks_and_a_bucket_with_many_pairs(ora
     picked = np.empty((rows, top_p), dtype=np.int32)
     for r in range(rows):
         # everybody reads bucket 0 (sinks inside) and bucket 7; the rest at random among the buckets before the window
-        others = rng.choice(np.arange(1, (first - window) // cap), top_p - 2, replace=False)
+        free = np.setdiff1d(np.arange(1, (first - window) // cap), [7])  # (a bucket is picked once a row)
+        others = rng.choice(free, top_p - 2, replace=False)
         picked[r] = np.concatenate([[7, 0], others])
         rng.shuffle(picked[r])
     want_lists, want_len = oracle.expand(picked, positions, members, top_k, sink, window)

@@ -356,6 +356,41 @@ def test_expansion_with_slots_owners_and_bad_ids(ops, oracle):
     assert int(status) == 1
 
 
+def test_expansion_of_decode_rows_by_a_cluster(ops, oracle):
+    """Eight rows or fewer whose picks hold tens of thousands of ids (a decode step over a long context) go through
+    the kernel that gives a row a cluster of CTAs; its lists are the oracle's, id for id: full picks, picks that are
+    fewer than the cluster's CTAs, a cut at top_k inside a bucket, holes in the picks, per-row budgets, a page
+    table, the window and sinks left out."""
+    rng = np.random.default_rng(4)
+    cap, buckets_n, T = 1024, 300, 300 * 1024 + 5000
+    members = np.full((buckets_n, cap), -1, dtype=np.int32)
+    for b in range(buckets_n):  # pools of 64 consecutive positions, 6 to 16 a bucket, ascending
+        pools = np.sort(rng.choice(np.arange(b * 16, b * 16 + 16), int(rng.integers(6, 17)), replace=False))
+        ids = (pools[:, None] * 64 + np.arange(64)[None]).reshape(-1)
+        members[b, : len(ids)] = ids
+    positions = np.array([T - 1, T - 700, 200000, 70, 5000], dtype=np.int64)
+    for top_p, top_k in ((40, 40 * cap), (40, 9000), (5, 5 * cap + 30000)):
+        picked = np.stack([rng.choice(buckets_n, top_p, replace=False) for _ in positions]).astype(np.int32)
+        picked[1, 3] = -1
+        picked[2, :] = np.sort(picked[2])
+        if top_p > 8:
+            picked[3, 0] = 0  # the bucket of the sinks, for a row whose window starts at 0
+        want_sel, want_len = oracle.expand(picked, positions, members, top_k, 4, 2048)
+        sel, lens, _ = ops.expand(cuda(picked), cuda(positions), cuda(members), top_k, 4, 2048)
+        assert np.array_equal(lens.cpu().numpy(), want_len), (top_p, top_k)
+        assert np.array_equal(sel.cpu().numpy(), want_sel), (top_p, top_k)
+    row_p = np.array([40, 7, 40, 1, 12], dtype=np.int32)
+    row_k = np.array([40 * cap, 3000, 100, 40 * cap, 5000], dtype=np.int32)
+    pages = rng.permutation(T // 64 + 1).astype(np.int32)
+    sel, lens, _ = ops.expand(cuda(picked), cuda(positions), cuda(members), 40 * cap, 4, 2048, cuda(row_p), cuda(row_k),
+                              page_table=cuda(pages), page_size=64, local=False)
+    one, one_len, _ = ops.expand(cuda(picked), cuda(positions), cuda(members), 40 * cap, 4, 2048, cuda(row_p),
+                                 cuda(row_k), page_table=cuda(pages), page_size=64, local=False, owner=(0, 1 << 40))
+    assert torch.equal(lens, one_len)  # (an owner range takes the one-warp kernel)
+    for r in range(len(positions)):
+        assert torch.equal(sel[r, : int(lens[r])], one[r, : int(lens[r])])
+
+
 def test_expansion_of_a_few_rows_with_long_lists(ops, oracle):
     """Up to 64 rows whose picks hold over a thousand ids go through the CTA-a-row kernel; its lists are the
     one-warp kernel's and the oracle's, id for id - cut at top_k, under per-row budgets, through a page table."""
