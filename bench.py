@@ -368,10 +368,14 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
         b_np = buckets_to_host(buckets)
         index_q = layer.index_queries(q)
         iq_np, pos_np = index_q[sample].cpu().numpy(), positions[sample].cpu().numpy()
-        attend_at = sorted({owned[-2], owned[-1], len(sample) - 1})  # two owned rows and the decode row
+        # the decode row maps its query through the few-rows kernels: one more sample row, at the last position
+        iq_np = np.concatenate([iq_np, layer.index_queries(q1).cpu().numpy()])
+        pos_np = np.concatenate([pos_np, [T - 1]])
+        q_sample = torch.cat([q[sample], q1])
+        attend_at = [owned[-1], len(sample)]  # an owned row of the chunk and the decode row
         latent_of = lambda ids: full[torch.from_numpy(ids.astype(np.int64)).cuda()].float().cpu().numpy()
         want_lists, want_lens, want_out, t_read, t_attend = c4_expected(cfg, attend_at, iq_np, pos_np, b_np, latent_of,
-                                                                       q[sample])
+                                                                       q_sample)
         if world == 1:
             same = all(int(lens_d[r]) == int(want_lens[i]) and np.array_equal(
                 lists_d[r, : int(lens_d[r])].cpu().numpy(), want_lists[i, : want_lens[i]]) for i, r in enumerate(sample))
@@ -382,10 +386,10 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
                 union = np.sort(union[union >= 0])
                 same = same and np.array_equal(union, np.sort(want_lists[i, : want_lens[i]]))
         worst, mean = 0.0, 0.0
-        for i in (owned[-2], owned[-1]):
+        for i in (owned[-1],):
             gap = np.abs(out_d[sample[i]].float().cpu().numpy() - want_out[i])
             worst, mean = max(worst, float(gap.max())), max(mean, float(gap.mean()))
-        decode_gap = float(np.abs(out1[0].float().cpu().numpy() - want_out[len(sample) - 1]).max())
+        decode_gap = float(np.abs(out1[0].float().cpu().numpy() - want_out[len(sample)]).max())
         worst = max(worst, decode_gap)
         parity = {"rows_checked": len(sample), "lists_equal": bool(same), "attention_max_abs": worst,
                   "attention_mean_abs": mean, "decode_max_abs": decode_gap, "tolerance": TOLERANCE,
@@ -402,7 +406,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
         oracle.project_mlp(rows_host, kmap[0].float().t().cpu().numpy(), kmap[1].float().t().cpu().numpy())
         oracle.project_mlp(rows_host, qmap[0].float().t().cpu().numpy(), qmap[1].float().t().cpu().numpy())
         t_map = (time.perf_counter() - t0) / n_map
-        per_token = t_map + t_read / len(sample) + t_attend / len(attend_at)
+        per_token = t_map + t_read / (len(sample) + 1) + t_attend / len(attend_at)
         cpu = {"value": 1.0 / per_token, "unit": UNIT, "cores": host_threads(), "kind": "port",
                "sample": (f"maps of {n_map} tokens, read of {len(sample)} rows, attention of {len(attend_at)} rows "
                           f"({int(want_lens[attend_at[0]])} keys a row); per-token stage times summed (map "
@@ -737,7 +741,7 @@ def run_c3(args, env: Env, cfg: dict) -> dict:
     b_np = buckets_to_host(index.buckets)
     tree_np = oracle.Hierarchy([c.cpu().numpy() for c in tree.node_centroids], [c.cpu().numpy() for c in tree.children],
                                cfg["node_bucket_size"], (cfg["node_cluster_block_size"],))
-    index_q = layer.index_queries(q).cpu().numpy()
+    index_q = layer.index_queries_rows(q).cpu().numpy()
     t0 = time.perf_counter()
     want_lists, want_len = oracle.read_hierarchy(index_q, np.array([position]), b_np, tree_np, cfg["beam_width"], None,
                                                  cfg["top_p"], cfg["top_k"], cfg["sink_size"], cfg["window_size"],

@@ -81,6 +81,19 @@ int lsa_index_map_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_ro
 int lsa_gemm_gelu_tc(const uint16_t *x, int64_t rows, int64_t d_in, int64_t x_row_stride, const uint16_t *Wt,
                      int64_t d_out, uint16_t *out_bf16, int32_t *status, void *stream);
 
+/* A linear layer over a few rows (a decode step's queries: the same maps as above when there is one row to map and
+ * a tile of 128 rows would be all padding): out[r, n] = act(sum_k xs[r, k] Wt[n, k]).
+ * Reference: the map of the decode rows, src/lsa/sglang/index/layer_index.py:906-928 (a torch matmul there).
+ *   x     [rows, heads, d_in] bf16 with element strides (x_row_stride, x_head_stride); the heads are summed first
+ *         (fp32, rounded once to bf16) - heads = 1 reads the rows as they are; rows <= 8, d_in a multiple of 8
+ *   Wt    [d_out, d_in] bf16, 16-byte aligned
+ *   flags LSA_ROWS_GELU: act = the exact GELU, else the identity; LSA_ROWS_NORMALIZE: the rows of out_f32 are
+ *         divided by their length afterwards (a second small launch), out_bf16 then holds the unit rows */
+#define LSA_ROWS_GELU 1
+#define LSA_ROWS_NORMALIZE 2
+int lsa_rows_linear(const uint16_t *x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride, int d_in,
+                    const uint16_t *Wt, int d_out, int flags, float *out_f32, uint16_t *out_bf16, void *stream);
+
 /* ---------------------------------------------------------------------------------------------------------
  * Pooling. Reference: pool_keys (src/lsa/core/ward.py:15-26).
  * pools[p, :] = sum of index_keys[p*pool_size : (p+1)*pool_size, :] added in position order, fp32.

@@ -419,7 +419,8 @@ LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, cons
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
-  if (R <= 64 && keeps_all && top_p <= lsa::kWideMaxPicks && (int64_t)top_p * bucket_cap >= 4096) {
+  if (keeps_all && top_p <= lsa::kWideMaxPicks &&
+      (int64_t)top_p * bucket_cap + window >= (R <= 8 ? 1024 : (R <= 64 ? 4096 : INT64_MAX))) {
     // a decode step's long lists: one CTA a row
     lsa::expand_wide_kernel<<<(unsigned)R, lsa::kWideThreads, 0, (cudaStream_t)stream>>>(p);
     LSA_LAUNCH_CHECK();

@@ -227,7 +227,110 @@ static int launch_index_map(const void *x, int64_t rows, int heads, int group, i
   return LSA_OK;
 }
 
+// A linear layer over a FEW rows (a decode step's queries): out[r, n] = act(sum_k xs[r, k] Wt[n, k]), xs = the row's
+// heads summed (fp32, rounded once to bf16) or the row itself. A warp owns an output column and walks its weights once
+// for all rows; eight columns a CTA, so even a single row's map spreads over N / 8 CTAs instead of one.
+constexpr int kLinThreads = 256;
+constexpr int kLinMaxRows = 8;
+
+__global__ void __launch_bounds__(kLinThreads)
+    rows_linear_kernel(const uint16_t *__restrict__ x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride,
+                       int K, const uint16_t *__restrict__ Wt, int N, int gelu, float *__restrict__ out_f32,
+                       uint16_t *__restrict__ out_bf16) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint16_t *xs = reinterpret_cast<uint16_t *>(smem_raw);  // [rows][K] bf16
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int e = tid; e < rows * K; e += kLinThreads) {
+    const int r = e / K, k = e - r * K;
+    const uint16_t *src = x + (int64_t)r * x_row_stride + k;
+    float sum = 0.0f;
+    for (int h0 = 0; h0 < heads; h0 += 8) {  // eight loads in flight, added in head order
+      uint16_t v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = h0 + j < heads ? src[(int64_t)(h0 + j) * x_head_stride] : (uint16_t)0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (h0 + j < heads) sum = __fadd_rn(sum, bf16_bits_to_float(v[j]));
+    }
+    xs[e] = heads > 1 ? float_to_bf16_bits(sum) : src[0];
+  }
+  __syncthreads();
+  const int n = blockIdx.x * (kLinThreads / 32) + warp;
+  if (n >= N) return;
+  float acc[kLinMaxRows];
+#pragma unroll
+  for (int r = 0; r < kLinMaxRows; ++r) acc[r] = 0.0f;
+  const uint16_t *w = Wt + (int64_t)n * K;
+  for (int k = lane * 8; k < K; k += 32 * 8) {  // (K is a multiple of 8 and the rows are 16-byte aligned)
+    const uint4 wv = *reinterpret_cast<const uint4 *>(w + k);
+    const uint32_t wp[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int r = 0; r < kLinMaxRows; ++r) {
+      if (r >= rows) break;
+      const uint4 xv = *reinterpret_cast<const uint4 *>(xs + r * K + k);
+      const uint32_t xp[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[r] = fmaf(__uint_as_float(xp[i] << 16), __uint_as_float(wp[i] << 16), acc[r]);
+        acc[r] = fmaf(__uint_as_float(xp[i] & 0xFFFF0000u), __uint_as_float(wp[i] & 0xFFFF0000u), acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kLinMaxRows; ++r) {
+    if (r >= rows) break;
+    float v = warp_sum(acc[r]);
+    if (gelu) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f));
+    if (lane == 0) {
+      if (out_f32) out_f32[(int64_t)r * N + n] = v;
+      if (out_bf16) out_bf16[(int64_t)r * N + n] = float_to_bf16_bits(v);
+    }
+  }
+}
+
+// rows /= their length (fp32 in place, a warp a row), with an optional bf16 copy
+__global__ void rows_unit_kernel(float *__restrict__ rows, int n_rows, int d, uint16_t *__restrict__ out_bf16) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  float ss = 0.0f;
+  for (int j = lane; j < d; j += 32) ss = fmaf(rows[(int64_t)r * d + j], rows[(int64_t)r * d + j], ss);
+  ss = warp_sum(ss);
+  const float den = fmaxf(sqrtf(ss), 1e-12f);
+  for (int j = lane; j < d; j += 32) {
+    const float v = rows[(int64_t)r * d + j] / den;
+    rows[(int64_t)r * d + j] = v;
+    if (out_bf16) out_bf16[(int64_t)r * d + j] = float_to_bf16_bits(v);
+  }
+}
+
 }  // namespace lsa
+
+LSA_API int lsa_rows_linear(const uint16_t *x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride,
+                            int d_in, const uint16_t *Wt, int d_out, int flags, float *out_f32, uint16_t *out_bf16,
+                            void *stream) {
+  LSA_REQUIRE(x && Wt && (out_f32 || out_bf16), LSA_ERR_NULL);
+  LSA_REQUIRE(rows >= 0 && rows <= lsa::kLinMaxRows && heads >= 1 && d_in >= 8 && d_in % 8 == 0 && d_out >= 1,
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(((uintptr_t)Wt % 16) == 0, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!(flags & LSA_ROWS_NORMALIZE) || out_f32, LSA_ERR_ARGUMENT);
+  const size_t smem = (size_t)rows * d_in * 2;
+  LSA_REQUIRE(smem <= 160 * 1024, LSA_ERR_UNSUPPORTED);
+  if (rows == 0) return LSA_OK;
+  if (cudaFuncSetAttribute(lsa::rows_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  const unsigned grid = (unsigned)((d_out + lsa::kLinThreads / 32 - 1) / (lsa::kLinThreads / 32));
+  const bool unit = flags & LSA_ROWS_NORMALIZE;
+  lsa::rows_linear_kernel<<<grid, lsa::kLinThreads, smem, (cudaStream_t)stream>>>(
+      x, rows, heads, x_row_stride, x_head_stride, d_in, Wt, d_out, flags & LSA_ROWS_GELU ? 1 : 0, out_f32,
+      unit ? nullptr : out_bf16);
+  LSA_LAUNCH_CHECK();
+  if (unit) {
+    lsa::rows_unit_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(out_f32, rows, d_out, out_bf16);
+    LSA_LAUNCH_CHECK();
+  }
+  return LSA_OK;
+}
 
 LSA_API int lsa_index_map(const void *x, int x_dtype, int64_t rows, int heads, int group, int dh_off, int dh_used,
                           int64_t x_row_stride, int64_t x_head_stride, const void *W, int w_dtype, int d_idx,

@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
   // k_full / k_empty: a ring stage's rows have landed / may be overwritten; s_full / s_empty: an S buffer holds a
   // product / has been read; p_full: P is in place (and O rescaled); pv_done: the second product of a tile is over;
   // drained: every product an issuing lane has issued is complete.
-  __shared__ __align__(8) uint64_t bars[2 * kLtStages + 2 * 2 + 4];
+  __shared__ __align__(8) uint64_t bars[3 * kLtStages + 2 * 2 + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int abort_s;
   __shared__ int32_t ids_s[kLtStages][kLtKeys];
@@ -109,10 +109,12 @@ __global__ void __launch_bounds__(kLtThreads, 1)
   // and whether it is the item's last; and what its first warp tells the other three about the tile to stage
   __shared__ volatile uint32_t info_s[kLtStages][4];
   __shared__ volatile int32_t plan_s[1];
-  enum { kFull = 0, kEmpty = kLtStages, kSFull = 2 * kLtStages, kSEmpty = 2 * kLtStages + 2 };
+  // (a stage is given back in two halves: planes 0-3 when the first half of O's product has read them, the rest
+  // after the second, so the next box's first planes are already on their way during the second half)
+  enum { kFull = 0, kEmpty = kLtStages, kEmptyB = 2 * kLtStages, kSFull = 3 * kLtStages, kSEmpty = 3 * kLtStages + 2 };
   auto bar = [&](int kind, int i) { return smem_u32(&bars[kind + i]); };
-  const uint32_t p_full = smem_u32(&bars[2 * kLtStages + 4]), pv_done = smem_u32(&bars[2 * kLtStages + 5]),
-                 drained_s = smem_u32(&bars[2 * kLtStages + 6]), drained_o = smem_u32(&bars[2 * kLtStages + 7]);
+  const uint32_t p_full = smem_u32(&bars[3 * kLtStages + 4]), pv_done = smem_u32(&bars[3 * kLtStages + 5]),
+                 drained_s = smem_u32(&bars[3 * kLtStages + 6]), drained_o = smem_u32(&bars[3 * kLtStages + 7]);
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -157,6 +159,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
     for (int i = 0; i < kLtStages; ++i) {
       mbar_init(bar(kFull, i), 1);
       mbar_init(bar(kEmpty, i), 1);
+      mbar_init(bar(kEmptyB, i), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(kSFull, i), 1);
@@ -267,15 +270,19 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         if (lane == 0) info_s[stage][0] = valid0, info_s[stage][1] = valid1, info_s[stage][2] = x + count >= n;
         const uint32_t dst0 = base + kLtKOff + stage * kLtStage;
         if (boxed) {
-          if (lane == 0) {
-            mbar_expect_tx(bar(kFull, stage), kLtStage);
-#pragma unroll
-            for (int plane = 0; plane < kLtPlanes; ++plane)
-              tma_load_2d(dst0 + plane * kLtPlane, &map_latent, bar(kFull, stage), plane * 64, first);
-          }
+          // a lane a plane: the copies are issued side by side, the first four planes as soon as they are free
+          if (lane == 0) mbar_expect_tx(bar(kFull, stage), kLtStage);
+          __syncwarp();
+          if (lane < 4) tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first);
+          if (j >= kLtStages) alive = wait(bar(kEmptyB, stage), ((j >> 1) - 1) & 1);
+          if (!alive) break;
+          if (lane >= 4 && lane < kLtPlanes)
+            tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first);
           __syncwarp();
           LT_TRACE(lane == 0, 1, j);
         } else {
+          if (j >= kLtStages) alive = wait(bar(kEmptyB, stage), ((j >> 1) - 1) & 1);
+          if (!alive) break;
           ids_s[stage][lane] = keep_a;
           ids_s[stage][32 + lane] = keep_b;
           if (lane == 0) plan_s[0] = stage;
@@ -337,13 +344,14 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         LT_TRACE(true, 5, t);
         const uint32_t v_s = base + kLtKOff + (t & 1) * kLtStage;
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int ks = 0; ks < kLtKeys / 16; ++ks)
             umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
                       smem_desc_mn_sw128(v_s + h * 4 * kLtPlane + ks * 2048, kLtPlane), lt_idesc(256, true),
                       (t | ks) != 0);
-        umma_commit(bar(kEmpty, t & 1));
+          umma_commit(bar(h == 0 ? kEmpty : kEmptyB, t & 1));
+        }
         umma_commit(pv_done);
         LT_TRACE(true, 6, t);
         if (last) break;

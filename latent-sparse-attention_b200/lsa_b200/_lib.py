@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -29,6 +29,7 @@ SIGNATURES = {
     "lsa_index_map": (_I, [_P, _I, _L, _I, _I, _I, _I, _L, _L, _P, _I, _I, _I, _P, _P, _P]),
     "lsa_index_map_tc": (_I, [_P, _L, _L, _L, _P, _I, _I, _P, _P, _P, _P]),
     "lsa_gemm_gelu_tc": (_I, [_P, _L, _L, _L, _P, _L, _P, _P, _P]),
+    "lsa_rows_linear": (_I, [_P, _I, _I, _L, _L, _I, _P, _I, _I, _P, _P, _P]),
     "lsa_pool_keys": (_I, [_P, _I, _L, _I, _I, _P, _P]),
     "lsa_ward_merge_workspace_bytes": (_Z, [_L, _I, _I]),
     "lsa_ward_merge": (_I, [_P, _P, _F, _L, _I, _I, _I, _F, _I, _P, _P, _P, _P, _Z, _P]),

@@ -19,7 +19,7 @@ from lsa_b200.layer import FlatLayer
 
 class TreeDecoder:
     def __init__(self, layer: FlatLayer, buckets: Buckets, hierarchy: Hierarchy, beam_width, start_nodes: int | None,
-                 page_size: int, growth_buckets: int, splits: int = 16, select_splits: int = 16):
+                 page_size: int, growth_buckets: int, splits: int = 16, select_splits: int = 8):
         self.layer, self.buckets, self.hierarchy = layer, buckets, hierarchy
         self.beam_widths = per_level(beam_width, len(hierarchy.node_cluster_block_sizes))
         self.start_nodes, self.page_size, self.growth_buckets, self.splits = start_nodes, page_size, growth_buckets, splits
@@ -40,7 +40,7 @@ class TreeDecoder:
         """q [1, Hq, dh] bf16 -> (list [1, top_k + window + sink] int32, length [1])."""
         d, plan = self.layer.design, self.plan
         with probe.region("index map"):
-            index_query = self.layer.index_queries(q)
+            index_query = self.layer.index_queries_rows(q)
         carried = None
         with probe.region("beam"):
             for level in range(plan["start"], 0, -1):

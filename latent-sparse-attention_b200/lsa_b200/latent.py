@@ -80,8 +80,18 @@ class LatentLayer(FlatLayer):
     def index_queries(self, q: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """absorbed queries [n, heads, latent_dim] bf16 -> unit index queries [n, index_dim] fp32: the heads are summed
         (fp32, rounded once to bf16) and the sum is mapped."""
+        if q.shape[0] <= 8 and out is None and q.stride(2) == 1:
+            return self.index_queries_rows(q)
         summed = ops.index_map(q, None, group=self.heads, normalize=False, out_dtype=torch.bfloat16)
         return self._map(summed, self.query_map, out)
+
+    def index_queries_rows(self, q: torch.Tensor) -> torch.Tensor:
+        """The query map for the few rows of a decode step: layers that spread one row's contraction over many CTAs
+        instead of padding it to a tile of 128 rows."""
+        if not self.two_layer:
+            return ops.rows_linear(q, self.query_map, sum_heads=True, normalize=True)
+        hidden = ops.rows_linear(q, self.query_map[0], sum_heads=True, gelu=True, out_dtype=torch.bfloat16)
+        return ops.rows_linear(hidden, self.query_map[1], normalize=True)
 
     # ---- the index
 
@@ -121,7 +131,7 @@ class LatentLayer(FlatLayer):
         return out
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, latent: torch.Tensor, index: FlatIndex,
-               splits: int = 148, select_splits: int = 64, warp_mma: bool = False) -> torch.Tensor:
+               splits: int = 148, select_splits: int = 16, warp_mma: bool = False) -> torch.Tensor:
         """One step for rows [R, heads, latent_dim] at `positions`: out [R, heads, value_dim] bf16. Fixed shapes and
         no host reads once `visible` is on the device, so a step can be captured in a CUDA graph."""
         d, b = self.design, index.buckets

@@ -139,6 +139,14 @@ class FlatLayer:
         return ops.index_map(q, self.query_map, group=self.heads // self.kv_heads, dh_off=self.dh_off,
                              dh_used=self.dh_used, out=out)
 
+    def index_queries_rows(self, q: torch.Tensor) -> torch.Tensor:
+        """The same map for the few rows of a decode step, q [R <= 8, Hq, dh] bf16: a kernel that spreads one row's
+        contraction over many CTAs (with bf16 maps; other maps take `index_queries`)."""
+        if self.tensor_cores and q.shape[0] <= 8 and q.dtype == torch.bfloat16 and q.stride(2) == 1 \
+                and q.stride(1) == q.shape[2]:
+            return ops.rows_linear(q, self.query_map_t, normalize=True)
+        return self.index_queries(q)
+
     def index_keys(self, k: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         """k [T, Hkv, dh] bf16 -> unit index keys [T, index_dim] fp32."""
         if self._takes_tensor_cores(k):

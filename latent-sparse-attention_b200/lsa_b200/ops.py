@@ -95,6 +95,33 @@ def mlp_map(x: torch.Tensor, w1_t: torch.Tensor, w2_t: torch.Tensor, hidden: tor
     return index_map_tc(hidden, _contig(w2_t), out=out)
 
 
+def rows_linear(x: torch.Tensor, weight_t: torch.Tensor, sum_heads: bool = False, gelu: bool = False,
+                normalize: bool = False, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """A linear layer over a few rows (a decode step): x [rows, d_in] or [rows, heads, d_in] bf16 (`sum_heads` adds
+    the heads first), weight_t [d_out, d_in] bf16 -> [rows, d_out] fp32 (unit rows with `normalize`) or bf16. Stands
+    in for the map of the decode rows (src/lsa/sglang/index/layer_index.py:906-928)."""
+    if x.dtype != torch.bfloat16 or weight_t.dtype != torch.bfloat16 or x.stride(-1) != 1:
+        raise ValueError("rows and map must be bfloat16 and the rows contiguous in their last dim")
+    heads = x.shape[1] if (sum_heads and x.dim() == 3) else 1
+    if x.dim() == 3 and not sum_heads:
+        if x.stride(1) != x.shape[2]:
+            raise ValueError("heads that are read side by side must be packed")
+        d_in = x.shape[1] * x.shape[2]
+    else:
+        d_in = x.shape[-1]
+    w = _contig(weight_t)
+    if w.shape[1] != d_in:
+        raise ValueError(f"the rows have {d_in} dims and the map reads {w.shape[1]}")
+    rows, d_out = x.shape[0], w.shape[0]
+    out_f32 = torch.empty(rows, d_out, device=x.device, dtype=torch.float32) \
+        if (out_dtype == torch.float32 or normalize) else None
+    out_bf16 = torch.empty(rows, d_out, device=x.device, dtype=torch.bfloat16) if out_dtype == torch.bfloat16 else None
+    call("lsa_rows_linear", ptr(x), rows, heads, x.stride(0), x.stride(1) if heads > 1 else 0, d_in, ptr(w), d_out,
+         (1 if gelu else 0) | (2 if normalize else 0), ptr(out_f32), ptr(out_bf16), stream(),
+         launches=2 if normalize else 1)
+    return out_f32 if out_dtype == torch.float32 else out_bf16
+
+
 def pool_keys(index_keys: torch.Tensor, pool_size: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """`pool_keys` (src/lsa/core/ward.py:15-26): [..., T, d] -> [..., T / pool_size, d] fp32."""
     keys = _contig(index_keys)

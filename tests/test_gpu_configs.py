@@ -144,5 +144,14 @@ def test_config_4_layer_on_a_cut_of_its_context(oracle):
                                        gathered[:, None, :], np.arange(len(ids), dtype=np.int32)[None],
                                        np.array([len(ids)]), 0, 0, W.latent_scale(cfg))
         _close(out[rows[i]].float().cpu().numpy(), want[0, :, :dv], f"row {rows[i]}")
-        if i == 4:
-            _close(out1[0].float().cpu().numpy(), want[0, :, :dv], "decode row")
+    # the decode row maps its query through the few-rows kernels: its own index vector, its own list
+    iq1 = layer.index_queries(q[-1:].contiguous())
+    assert (iq1 - index_q[-1:]).abs().max() <= 2e-3
+    list1, len1 = oracle.read(iq1.cpu().numpy(), np.array([T - 1]), buckets, cfg["top_p"], cfg["top_k"],
+                              cfg["sink_size"], cfg["window_size"])
+    ids = list1[0, : len1[0]]
+    gathered = latent[ids]
+    want, _ = oracle.sparse_attend(q[-1:].float().cpu().numpy(), gathered[:, None, :], gathered[:, None, :],
+                                   np.arange(len(ids), dtype=np.int32)[None], np.array([len(ids)]), 0, 0,
+                                   W.latent_scale(cfg))
+    _close(out1[0].float().cpu().numpy(), want[0, :, :dv], "decode row")

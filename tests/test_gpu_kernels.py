@@ -163,6 +163,33 @@ def test_ward_golden_and_adversarial_cases(ops, oracle):
     assert not reached.any() and torch.equal(labels.cpu(), torch.arange(16).expand(2, 16))
 
 
+def test_linear_layers_over_a_few_rows(ops):
+    """The decode-row maps: heads summed or read side by side, GELU or not, unit rows or not, against fp32 torch on
+    the same bf16 values (the hidden layer of the two-layer map is rounded to bf16, as the batched map rounds it)."""
+    gen = torch.Generator().manual_seed(3)
+    for rows in (1, 3, 8):
+        x = (0.5 * torch.randn(rows, 64, 576, generator=gen)).bfloat16().cuda()
+        w1 = (torch.randn(2048, 576, generator=gen) / 24).bfloat16().cuda()
+        w2 = (torch.randn(64, 2048, generator=gen) / 45).bfloat16().cuda()
+        summed = x.float().sum(1).bfloat16().float()
+        want_hidden = torch.nn.functional.gelu(summed @ w1.float().t())
+        hidden = ops.rows_linear(x, w1, sum_heads=True, gelu=True, out_dtype=torch.bfloat16)
+        assert (hidden.float() - want_hidden).abs().max() <= 2e-2 * want_hidden.abs().max()
+        want = torch.nn.functional.normalize(hidden.float() @ w2.float().t(), dim=1)
+        got = ops.rows_linear(hidden, w2, normalize=True)
+        assert (got - want).abs().max() <= 1e-5
+        # heads side by side under a widened map: [rows, 40, 128] against [64, 5120]
+        q = torch.randn(rows, 40, 128, generator=gen).bfloat16().cuda()
+        wide = (torch.randn(64, 5120, generator=gen) / 70).bfloat16().cuda()
+        got = ops.rows_linear(q, wide, normalize=True)
+        want = torch.nn.functional.normalize(q.float().reshape(rows, -1) @ wide.float().t(), dim=1)
+        assert (got - want).abs().max() <= 1e-5
+        plain = ops.rows_linear(q, wide)
+        assert (plain - q.float().reshape(rows, -1) @ wide.float().t()).abs().max() <= 1e-4
+    with pytest.raises(ValueError):
+        ops.rows_linear(torch.zeros(9, 64, device="cuda", dtype=torch.bfloat16), wide)
+
+
 def test_kmeans_bucketing_matches_its_restatement(ops, oracle):
     """A variant with no reference code: config 1's shapes - 1,024 pools, 256 centres, 32 dims, 10 rounds."""
     keys = unit_rows(mixture(16384, 32, 64, 0.3, 8))
