@@ -431,13 +431,18 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     # from pinned host memory: the chunk's queries and (this rank's share of) its latent rows in, the output back
     from lsa_b200.parallel import deal
 
-    q_h = q.cpu().pin_memory()
+    # (on several GPUs a rank copies its own rows of the chunk's queries and the ranks all-gather them over NVLink:
+    # every rank needs every row, but the host link need carry each row only once)
+    q_h = q[rank * own_rows:(rank + 1) * own_rows].cpu().pin_memory()
     tail_h = (tail if world == 1 else deal(tail, rank, world)).cpu().pin_memory()
     out_h = torch.empty(out_d.shape, dtype=out_d.dtype).pin_memory()
     q_in = torch.empty_like(q)
+    q_part = torch.empty(own_rows, Hq, dk, dtype=q.dtype, device="cuda") if world > 1 else q_in
 
     def e2e_step():
-        q_in.copy_(q_h, non_blocking=True)
+        q_part.copy_(q_h, non_blocking=True)
+        if world > 1:
+            env.dist.all_gather_into_tensor(q_in, q_part)
         share[first // world:].copy_(tail_h, non_blocking=True)
         if world == 1:
             layer.extend_index(share, first, chunk)

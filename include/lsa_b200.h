@@ -345,6 +345,12 @@ int lsa_band_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_row_
  *   splits  CTAs a row's list is divided over; > 1 needs lsa_latent_attend_workspace_bytes() of workspace
  *   flags   0: both products run on tcgen05 with a block of 64 heads as the M side, S and O in tensor memory;
  *           LSA_LATENT_WARP_MMA: the same read on warp-level mma.sync tiles
+ *   owner_granule / owner_world / owner_rank (world <= 1: off): the cache handed in is one rank's share of a
+ *           cache dealt out over owner_world ranks in granules of owner_granule positions (a multiple of 64), the
+ *           ids are POSITIONS, and the call reads only the positions its rank holds (position p is row
+ *           p / (granule * world) * granule + p % granule of the rank (p / granule) % world) - the lists of
+ *           lsa_expand with the same owner arguments hold those rows already and need none of this; tensor-memory
+ *           form only
  *   status  (may be NULL) raised if a bounded on-chip wait of the tensor-memory form gives up: the output of a
  *           call that raised it is void
  * dk = 576, dv = 512 in this build. */
@@ -353,8 +359,8 @@ size_t lsa_latent_attend_workspace_bytes(int64_t R, int Hq, int dv, int splits);
 int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int dv, int64_t q_row_stride,
                       int64_t q_head_stride, const uint16_t *latent, int64_t slots, int64_t latent_row_stride,
                       const int32_t *ids, int64_t list_stride, const int32_t *lengths, float scale, int splits,
-                      uint16_t *out_bf16, float *out_f32, float *lse, int flags, int32_t *status, void *workspace,
-                      size_t workspace_bytes, void *stream);
+                      uint16_t *out_bf16, float *out_f32, float *lse, int flags, int owner_granule, int owner_world,
+                      int owner_rank, int32_t *status, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Bucket-major attention of a prefill chunk: expansion and gather attention in one call, the loop over buckets
  * outside the loop over rows. The result is lsa_expand (LSA_EXPAND_NO_LOCAL) followed by lsa_sparse_attend with

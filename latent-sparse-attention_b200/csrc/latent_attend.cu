@@ -262,12 +262,17 @@ LSA_API int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int 
                               int64_t q_head_stride, const uint16_t *latent, int64_t slots, int64_t latent_row_stride,
                               const int32_t *ids, int64_t list_stride, const int32_t *lengths, float scale,
                               int splits, uint16_t *out_bf16, float *out_f32, float *lse, int flags,
-                              int32_t *status, void *workspace, size_t workspace_bytes, void *stream) {
+                              int owner_granule, int owner_world, int owner_rank, int32_t *status, void *workspace,
+                              size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(q && latent && ids && lse && (out_bf16 || out_f32), LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && Hq >= 1 && slots >= 0 && slots <= INT32_MAX && list_stride >= 0 && splits >= 1 &&
                   latent_row_stride >= dk,
               LSA_ERR_ARGUMENT);
   LSA_REQUIRE(dk == 576 && dv == 512, LSA_ERR_UNSUPPORTED);
+  LSA_REQUIRE(owner_world <= 1 || (owner_granule >= 64 && owner_granule % 64 == 0 && owner_rank >= 0 &&
+                                   owner_rank < owner_world),
+              LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(owner_world <= 1 || !(flags & LSA_LATENT_WARP_MMA), LSA_ERR_UNSUPPORTED);
   // 16-byte copies of latent rows and query heads need these alignments
   LSA_REQUIRE(latent_row_stride % 8 == 0 && ((uintptr_t)latent % 16) == 0 && q_row_stride % 8 == 0 &&
                   q_head_stride % 8 == 0 && ((uintptr_t)q % 16) == 0,
@@ -292,6 +297,7 @@ LSA_API int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int 
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.deal_granule = owner_granule, p.deal_world = owner_world, p.deal_rank = owner_rank;
   if (splits > 1) {
     const size_t need = lsa_latent_attend_workspace_bytes(R, Hq, dv, splits);
     LSA_REQUIRE(workspace && workspace_bytes >= need, LSA_ERR_WORKSPACE);

@@ -15,6 +15,7 @@ struct LatentParams {
   int32_t *status;  // raised when a bounded on-chip wait of the tensor-memory form gives up, or NULL
   int64_t R, slots, q_row_stride, q_head_stride, latent_row_stride, list_stride;
   int Hq, splits;
+  int deal_granule, deal_world, deal_rank;  // ids are positions of a cache dealt over ranks in granules (world <= 1: off)
   int boxes;        // set by the tensor-core launcher: runs of consecutive rows may be staged by tensor-map copies
   float scale_log2;
 };

@@ -238,46 +238,71 @@ __global__ void __launch_bounds__(kLtThreads, 1)
     if (warp == 5) {
       // The first warp walks the list, 64 entries ahead (two a lane), and stages boxes by itself; the other three
       // wait at the barrier for tiles that must be gathered.
-      int x = 0;
+      const bool dealt = p.deal_world > 1;  // ids are positions of a cache dealt over ranks: only this rank's are read
+      const int64_t deal_span = (int64_t)p.deal_granule * p.deal_world;
+      auto mine = [&](int32_t id) { return !dealt || (int)((id / p.deal_granule) % p.deal_world) == p.deal_rank; };
+      auto row_of = [&](int32_t id) {
+        return dealt ? (int32_t)(id / deal_span * p.deal_granule + id % p.deal_granule) : id;
+      };
+      int x = 0, j = 0;
       int32_t id_a = lane < n ? list[lane] : -1;
       int32_t id_b = 32 + lane < n ? list[32 + lane] : -1;
       bool alive = true;
-      for (int j = 0; x < n && alive; ++j) {
+      while ((x < n || dealt) && alive) {
         const int stage = j & 1;
+        const bool closing = x >= n;  // (a dealt list ends with an empty tile: which tile is the last is not known before)
         // 64 consecutive rows of the cache are ONE box of a tensor-map copy per plane, wherever they start. Anything
         // else is gathered row by row (rows that hold no key are zero-filled: a box would bring in rows nobody
         // listed, whose bits need not be finite); a shorter run is a tile of its own, so that the tile after it
         // starts with the next run.
-        const int remaining = min(kLtKeys, n - x);
+        const int remaining = closing ? 0 : min(kLtKeys, n - x);
         const int32_t first = __shfl_sync(0xffffffffu, id_a, 0);
-        const bool ok_a = id_a >= 0 && id_a < p.slots, ok_b = id_b >= 0 && id_b < p.slots;
-        const uint32_t run_a = __ballot_sync(0xffffffffu, ok_a && id_a == first + lane);
-        const uint32_t run_b = __ballot_sync(0xffffffffu, ok_b && id_b == first + 32 + lane);
-        const int run = run_a != 0xffffffffu ? __ffs(~run_a) - 1 : 32 + (run_b != 0xffffffffu ? __ffs(~run_b) - 1 : 32);
-        const bool boxed = p.boxes && run == kLtKeys;
-        const int count = boxed ? kLtKeys : (run >= kLtMinRun ? run : remaining);
-        const int32_t keep_a = ok_a && lane < count ? id_a : -1, keep_b = ok_b && 32 + lane < count ? id_b : -1;
+        const bool ok_a = id_a >= 0 && row_of(id_a) < p.slots && mine(id_a);
+        const bool ok_b = id_b >= 0 && row_of(id_b) < p.slots && mine(id_b);
+        const uint32_t run_a = __ballot_sync(0xffffffffu, id_a >= 0 && id_a == first + lane);
+        const uint32_t run_b = __ballot_sync(0xffffffffu, id_b >= 0 && id_b == first + 32 + lane);
+        const int run = closing ? 0 : (run_a != 0xffffffffu ? __ffs(~run_a) - 1
+                                                             : 32 + (run_b != 0xffffffffu ? __ffs(~run_b) - 1 : 32));
+        const int count = run == kLtKeys ? kLtKeys : (run >= kLtMinRun ? run : remaining);
+        const int32_t keep_a = ok_a && lane < count ? row_of(id_a) : -1;
+        const int32_t keep_b = ok_b && 32 + lane < count ? row_of(id_b) : -1;
         const uint32_t valid0 = __ballot_sync(0xffffffffu, keep_a >= 0), valid1 = __ballot_sync(0xffffffffu, keep_b >= 0);
+        // a box: 64 consecutive rows that this rank holds side by side (under dealing: inside one granule)
+        const bool boxed = p.boxes && run == kLtKeys && (valid0 & valid1) == 0xffffffffu &&
+                           (!dealt || first % p.deal_granule + kLtKeys <= p.deal_granule);
+        const int32_t first_row = __shfl_sync(0xffffffffu, keep_a, 0);
         // the box is asked into the L2 now, a tile's time before its stage is free
-        if (boxed && lane < kLtPlanes) tma_prefetch_2d(&map_latent, lane * 64, first);
+        if (boxed && lane < kLtPlanes) tma_prefetch_2d(&map_latent, lane * 64, first_row);
         // the entries after this tile, on their way while it is staged
         const int at = x + count + lane;
         id_a = at < n ? list[at] : -1;
         id_b = at + 32 < n ? list[at + 32] : -1;
+        x += count;
+        if (dealt && !closing && (valid0 | valid1) == 0u) continue;  // nothing of this tile is stored here
         if (j >= kLtStages) alive = wait(bar(kEmpty, stage), ((j >> 1) - 1) & 1);
         if (!alive) break;
         LT_TRACE(lane == 0, 0, j);
-        if (lane == 0) info_s[stage][0] = valid0, info_s[stage][1] = valid1, info_s[stage][2] = x + count >= n;
+        if (lane == 0) {
+          info_s[stage][0] = valid0, info_s[stage][1] = valid1;
+          info_s[stage][2] = dealt ? closing : x >= n;  // the last tile
+          info_s[stage][3] = closing;                   // nothing staged: the products skip it
+        }
         const uint32_t dst0 = base + kLtKOff + stage * kLtStage;
+        if (closing) {
+          if (j >= kLtStages) alive = wait(bar(kEmptyB, stage), ((j >> 1) - 1) & 1);
+          if (!alive) break;
+          if (lane == 0) lt_arrive(bar(kFull, stage));
+          break;
+        }
         if (boxed) {
           // a lane a plane: the copies are issued side by side, the first four planes as soon as they are free
           if (lane == 0) mbar_expect_tx(bar(kFull, stage), kLtStage);
           __syncwarp();
-          if (lane < 4) tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first);
+          if (lane < 4) tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first_row);
           if (j >= kLtStages) alive = wait(bar(kEmptyB, stage), ((j >> 1) - 1) & 1);
           if (!alive) break;
           if (lane >= 4 && lane < kLtPlanes)
-            tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first);
+            tma_load_2d(dst0 + lane * kLtPlane, &map_latent, bar(kFull, stage), lane * 64, first_row);
           __syncwarp();
           LT_TRACE(lane == 0, 1, j);
         } else {
@@ -293,7 +318,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
           if (lane == 0) lt_arrive(bar(kFull, stage));
         }
         LT_TRACE(lane == 0, 2, j);
-        x += count;
+        ++j;
       }
       if (lane == 0) plan_s[0] = -1;
       gather_sync();  // the other three warps leave
@@ -314,7 +339,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         const int sb = i & 1;
         alive = wait_one(bar(kFull, sb), (i >> 1) & 1);
         if (!alive) break;
-        const bool last = info_s[sb][2] != 0;
+        const bool last = info_s[sb][2] != 0, nothing = info_s[sb][3] != 0;
         if (i >= 2) alive = wait_one(bar(kSEmpty, sb), ((i >> 1) - 1) & 1);
         if (!alive) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -324,7 +349,8 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         for (int plane = 0; plane < kLtPlanes; ++plane)
 #pragma unroll
           for (int s = 0; s < 4; ++s)
-            umma_bf16(tmem_base + kLtSCol + sb * kLtKeys, smem_desc_sw128(base + plane * kLtPlane) + 2 * s,
+            if (!nothing)
+              umma_bf16(tmem_base + kLtSCol + sb * kLtKeys, smem_desc_sw128(base + plane * kLtPlane) + 2 * s,
                       smem_desc_sw128(k_s + plane * kLtPlane) + 2 * s, lt_idesc(kLtKeys, false), (plane | s) != 0);
         umma_commit(bar(kSFull, sb));
         LT_TRACE(true, 4, i);
@@ -339,7 +365,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
       for (int t = 0; alive; ++t) {
         alive = wait_one(p_full, t & 1);
         if (!alive) break;
-        const bool last = info_s[t & 1][2] != 0;  // (read before the stage is given back)
+        const bool last = info_s[t & 1][2] != 0, nothing = info_s[t & 1][3] != 0;  // (read before the stage is given back)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         LT_TRACE(true, 5, t);
         const uint32_t v_s = base + kLtKOff + (t & 1) * kLtStage;
@@ -347,7 +373,8 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int ks = 0; ks < kLtKeys / 16; ++ks)
-            umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
+            if (!nothing)
+              umma_bf16(tmem_base + ((uint32_t)(h * 16) << 16), smem_desc_sw128(base + kLtPOff) + 2 * ks,
                       smem_desc_mn_sw128(v_s + h * 4 * kLtPlane + ks * 2048, kLtPlane), lt_idesc(256, true),
                       (t | ks) != 0);
           umma_commit(bar(h == 0 ? kEmpty : kEmptyB, t & 1));
@@ -463,6 +490,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      const bool read_any = l_run > 0.0f;  // (else O may never have been written: zeros, not O x 0)
       if (row_ok && half == 0)
         (partial ? p.part_lse : p.lse)[out_row] =
             l_run > 0.0f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
@@ -472,6 +500,10 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         tmem_load_32(lane_addr + c, o);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (!row_ok) continue;
+        if (!read_any) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o[k] = 0u;
+        }
         const int64_t at = out_row * 512 + half * 256 + c;
         if (partial) {
 #pragma unroll

@@ -403,10 +403,13 @@ def sparse_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ids: torch.
 def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, lengths: torch.Tensor | None,
                   scale: float, value_dim: int = 512, splits: int = 1, out_dtype=torch.bfloat16,
                   workspace: torch.Tensor | None = None, warp_mma: bool = False,
-                  status: torch.Tensor | None = None, out: torch.Tensor | None = None):
+                  status: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                  dealt: tuple[int, int, int] | None = None):
     """The MLA read: absorbed queries q [R, Hq, dk] bf16 over the latent rows [slots, dk] bf16 each list names, a
     value being a row's first `value_dim` dims. Returns (out [R, Hq, value_dim], lse [R, Hq]). The products run
-    on tcgen05 with tensor-memory accumulators; `warp_mma` takes the warp-level MMA kernel."""
+    on tcgen05 with tensor-memory accumulators; `warp_mma` takes the warp-level MMA kernel. With `dealt` =
+    (granule, world, rank) the lists hold POSITIONS and `latent` is this rank's share of a cache dealt out in
+    granules: the call reads the positions its rank holds and skips the rest."""
     if q.dtype != torch.bfloat16 or latent.dtype != torch.bfloat16:
         raise ValueError("q and latent must be bfloat16")
     if q.dim() != 3 or latent.dim() != 2 or q.stride(2) != 1 or latent.stride(1) != 1 or q.shape[2] != latent.shape[1]:
@@ -425,7 +428,7 @@ def latent_attend(q: torch.Tensor, latent: torch.Tensor, ids: torch.Tensor, leng
     call("lsa_latent_attend", ptr(q), R, Hq, dk, value_dim, q.stride(0), q.stride(1), ptr(latent), latent.shape[0],
          latent.stride(0), ptr(ids), ids.shape[1], ptr(lengths), float(scale), splits,
          ptr(out) if out_dtype == torch.bfloat16 else None, ptr(out) if out_dtype == torch.float32 else None, ptr(lse),
-         1 if warp_mma else 0, ptr(status), ptr(workspace),
+         1 if warp_mma else 0, *(dealt if dealt is not None else (0, 1, 0)), ptr(status), ptr(workspace),
          workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
          launches=1 if splits == 1 else 2)
     return out, lse

@@ -372,10 +372,10 @@ class ShardedLatentLayer:
                     at = (b // world) * per_block
                     self.centroids[at:at + per_block] = centroids[(b - b0) * per_block:(b - b0 + 1) * per_block]
 
-    def select(self, rows: torch.Tensor, positions: torch.Tensor) -> tuple:
-        """This rank's share of every row's read list, as rows of its own cache: (lists, lengths). A collective call
-        (the candidates are exchanged inside). Local row l of rank r is position (l / granule * world + r) * granule
-        + l % granule."""
+    def pick(self, rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """Every row's top-p buckets, best first, as GLOBAL bucket ids [R, top_p] - the same on every rank. A
+        collective call: each rank scores the centroids of its own blocks, the candidates are all-gathered and cut
+        with the single-GPU tie rule."""
         layer, d, world, rank = self.layer, self.design, self.world, self.rank
         per_block = d.block_bucket_count
         with probe.region("index map"):
@@ -393,9 +393,17 @@ class ShardedLatentLayer:
             every = gather_candidates(keys, self.group)
         with probe.region("select"):
             _, picked = ops.merge_candidates(every)
+        return picked
+
+    def select(self, rows: torch.Tensor, positions: torch.Tensor) -> tuple:
+        """This rank's share of every row's read list, as rows of its own cache: (lists, lengths). A collective call
+        (the candidates are exchanged inside). Local row l of rank r is position (l / granule * world + r) * granule
+        + l % granule."""
+        d = self.design
+        picked = self.pick(rows, positions)
         with probe.region("expand"):
             lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size,
-                                           dealt=(self.granule, world, rank))
+                                           dealt=(self.granule, self.world, self.rank))
         return lists, lengths
 
     def _read_rows(self, rows: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int) -> tuple:
@@ -419,8 +427,18 @@ class ShardedLatentLayer:
         return merged
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int = 32) -> torch.Tensor:
-        """One step for replicated rows [R, heads, latent_dim] at `positions`: the whole output on every rank."""
-        partial, lse = self._read_rows(q, positions.to(torch.int64), share, splits)
+        """One step for replicated rows [R, heads, latent_dim] at `positions`: the whole output on every rank. Every
+        rank lists the WHOLE read (a few rows: the clustered expansion, which keeps every id) and its attention
+        call skips the positions it does not hold - cheaper than a dealt expansion of so few rows."""
+        layer, d = self.layer, self.design
+        positions = positions.to(torch.int64)
+        picked = self.pick(q, positions)
+        with probe.region("expand"):
+            lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size)
+        with probe.region("attend"):
+            partial, lse = ops.latent_attend(q, share, lists, lengths, layer.scale, value_dim=layer.value_dim,
+                                             splits=splits, out_dtype=torch.float32, status=layer._attend_status,
+                                             dealt=(self.granule, self.world, self.rank))
         with probe.region("merge partials"):
             merged, _ = ops.lse_merge(gather_pieces(partial, self.group), gather_pieces(lse, self.group),
                                       out_dtype=torch.bfloat16)

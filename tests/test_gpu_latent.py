@@ -195,6 +195,59 @@ def test_latent_attend_over_runs_of_consecutive_rows(oracle, splits):
     assert np.abs(out2.cpu().numpy() - want2[:, :, :512]).max() <= 2e-2
 
 
+@pytest.mark.parametrize("splits", [1, 5])
+def test_latent_attend_over_a_dealt_cache(oracle, splits):
+    """Four ranks' shares of one cache, dealt out in granules of 64 positions: every rank is handed the WHOLE list of
+    positions and reads the ones it holds; the four partial reads merged by their log-sum-exps are the read of the
+    whole cache. (One GPU plays the four ranks in turn; lists hold whole pools, cut pools and scattered ids, and one
+    row lists nothing that the last rank holds.)"""
+    from lsa_b200 import ops
+    from lsa_b200.parallel import deal
+
+    rng = np.random.default_rng(8)
+    rows, heads, slots, width, world = 5, 64, 64 * 4 * 30, 2400, 4
+    q, latent, _, _ = _latent_case(12, rows, heads, slots, 8, ragged=False)
+    ids = np.full((rows, width), -1, dtype=np.int32)
+    lengths = np.zeros(rows, dtype=np.int32)
+    for r in range(rows):
+        pieces, taken = [], np.zeros(slots, dtype=bool)
+        for _ in range(int(rng.integers(10, 25))):
+            n = int(rng.choice([64, 64, 64, 128, 40, 17, 3]))
+            first = int(rng.integers(0, slots - n)) // 64 * 64 + int(rng.choice([0, 0, 0, 5]))
+            if r == 1:
+                first = first // 256 * 256  # granules of ranks 0 only ... and their overflow into rank 1
+            if first + n > slots or taken[first:first + n].any():
+                continue
+            taken[first:first + n] = True
+            pieces.append(np.arange(first, first + n))
+        pieces.append(np.arange(slots - 600, slots - 600 + 300 + r))
+        row = np.concatenate(pieces).astype(np.int32)
+        ids[r, : len(row)] = row
+        lengths[r] = len(row)
+    scale = 576 ** -0.5
+    Q, L, I, N = cuda(q, torch.bfloat16), cuda(latent, torch.bfloat16), cuda(ids), cuda(lengths)
+    parts, lses = [], []
+    for rank in range(world):
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out, lse = ops.latent_attend(Q, deal(L, rank, world).contiguous(), I, N, scale, splits=splits,
+                                     out_dtype=torch.float32, status=status, dealt=(64, world, rank))
+        assert int(status) == 0
+        parts.append(out)
+        lses.append(lse)
+    merged, merged_lse = ops.lse_merge(torch.stack(parts), torch.stack(lses))
+    want, want_lse = oracle.sparse_attend(q, latent[:, None, :], latent[:, None, :], ids,
+                                          np.full(rows, slots, dtype=np.int64), 0, 0, scale, lengths=lengths)
+    gap = np.abs(merged.cpu().numpy() - want[:, :, :512])
+    assert gap.max() <= 2e-2 and gap.mean() <= 2e-3, (gap.max(), gap.mean())
+    assert np.abs(merged_lse.cpu().numpy() - want_lse).max() <= 2e-2
+    # a rank that holds nothing of a list returns an empty partial, not garbage
+    only0 = np.full((1, 128), -1, dtype=np.int32)
+    only0[0, :64] = np.arange(0, 64)
+    out, lse = ops.latent_attend(Q[:1], deal(L, 3, world).contiguous(), cuda(only0), None, scale, out_dtype=torch.float32,
+                                 dealt=(64, world, 3))
+    assert not out.any() and torch.isinf(lse).all()
+
+
 def test_latent_attend_long_lists_in_bf16(oracle):
     """Lists of thousands of keys (a hundred tiles a row), ragged ends, bf16 output: the size a served row has."""
     from lsa_b200 import ops

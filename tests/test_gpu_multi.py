@@ -71,6 +71,64 @@ def _rank_main(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
+def _latent_rank_main(rank, world, port, result_dir):
+    for path in (ROOT, PACKAGE_DIR, os.path.join(ROOT, "tests")):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lsa_b200 import workloads as W
+        from lsa_b200.latent import LatentLayer
+        from lsa_b200.parallel import ShardedLatentLayer, deal
+
+        # config 4's shape over 32 cluster blocks: every rank builds the whole cache and keeps its dealt share
+        cfg = W.cut(W.C4, 32 * 5120)
+        T, chunk, Hq, dk, dv = cfg["tokens"], 2048, cfg["heads"], cfg["latent_dim"], cfg["value_dim"]
+        gen = torch.Generator(device="cuda").manual_seed(2)
+        cache, tail = W.latent_cache(cfg, gen, keep_tail=chunk)
+        qmap, kmap = W.latent_maps(cfg, gen)
+        q = W.latent_queries(cfg, tail, gen)
+        first = T - chunk
+        single = LatentLayer(W.design_of(cfg), qmap, kmap, Hq, dk, dv, scale=W.latent_scale(cfg))
+        index = single.build_index(cache)
+        want = torch.empty(chunk, Hq, dv, dtype=torch.bfloat16, device="cuda")
+        single.prefill_rows(q, first, cache, index, want)
+        want1 = single.decode(q[-1:].contiguous(), torch.tensor([T - 1], device="cuda"), cache, index, splits=8)
+
+        layer = LatentLayer(W.design_of(cfg), qmap, kmap, Hq, dk, dv, scale=W.latent_scale(cfg))
+        sharded = ShardedLatentLayer(layer, rank, world)
+        share = deal(cache, rank, world).contiguous()
+        sharded.build_index(share, T)
+        # the global member table is the single-GPU one; this rank's centroids are those of its own blocks
+        assert torch.equal(sharded.members, index.buckets.bucket_members)
+        per_block, blocks = 8, T // 5120
+        mine = index.buckets.bucket_centroids.view(blocks // world, world, per_block, -1)[:, rank].reshape(-1, 64)
+        assert torch.equal(sharded.centroids, mine)
+        sharded.extend_index(share, first, chunk)  # the same keys again: the same index
+        assert torch.equal(sharded.members, index.buckets.bucket_members) and torch.equal(sharded.centroids, mine)
+        got = sharded.prefill_rows(q, first, share)
+        rows = chunk // world
+        err = (got.float() - want[rank * rows:(rank + 1) * rows].float()).abs()
+        assert got.shape == (rows, Hq, dv)
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+        got1 = sharded.decode(q[-1:].contiguous(), torch.tensor([T - 1], device="cuda"), share, splits=4)
+        assert (got1.float() - want1.float()).abs().max().item() <= 2e-2
+        layer.check()
+        open(os.path.join(result_dir, f"ok{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_latent_layer_matches_the_single_gpu_layer(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two or more GPUs")
+    mp.spawn(_latent_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert sorted(os.listdir(tmp_path)) == [f"ok{r}" for r in range(world)]
+
+
 def test_sharded_prefill_matches_the_single_gpu_layer(tmp_path):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
