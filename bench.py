@@ -426,7 +426,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     launches = (_lib.LAUNCHES - launches_before) // args.steps
     stage_ms = {name: total / args.steps for name, (total, _) in recorder.totals_ms().items()}
     probe.uninstall()
-    layer.check()
+    (sharded or layer).check()
 
     # from pinned host memory: the chunk's queries and (this rank's share of) its latent rows in, the output back
     from lsa_b200.parallel import deal

@@ -400,9 +400,11 @@ int lsa_bucket_attend(const uint16_t *q, int64_t R, int Hq, int dh, int64_t q_ro
 /* Merge of partial attention results over disjoint key sets: lse = logsumexp_p lse_p,
  * out = sum_p exp(lse_p - lse) out_p. The arithmetic of the serving engine's cp_lse_ag_out_rs_mha that the
  * reference calls at src/lsa/sglang/models/qwen3_5/backend.py:724-738.
- *   parts [n_parts, rows, dh] fp32, lses [n_parts, rows] fp32; out_bf16/out_f32 [rows, dh]; lse_out [rows] or NULL */
-int lsa_lse_merge(const float *parts, const float *lses, int n_parts, int64_t rows, int dh, uint16_t *out_bf16,
-                  float *out_f32, float *lse_out, void *stream);
+ *   parts [n_parts, rows, dh] fp32 or bf16 (parts_dtype = LSA_DTYPE_F32 / LSA_DTYPE_BF16; bf16 parts - the ranks'
+ *   partial reads of a prefill chunk, which cross NVLink at half the bytes - need n_parts < 16 and dh % 8 == 0),
+ *   lses [n_parts, rows] fp32; out_bf16/out_f32 [rows, dh]; lse_out [rows] or NULL */
+int lsa_lse_merge(const void *parts, int parts_dtype, const float *lses, int n_parts, int64_t rows, int dh,
+                  uint16_t *out_bf16, float *out_f32, float *lse_out, void *stream);
 
 #ifdef __cplusplus
 }

@@ -457,6 +457,58 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+// A few parts of many rows (the ranks' partial reads of a prefill chunk): a warp a row. The parts' weights are
+// computed once a row - lane i holds part i's - and a lane carries eight dims of the row through all parts, read 16
+// bytes at a time from bf16 or fp32 partials.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    lse_merge_few_kernel(const T *__restrict__ parts, const float *__restrict__ lses, int n_parts, int64_t rows, int dh,
+                         uint16_t *__restrict__ out_bf16, float *__restrict__ out_f32, float *__restrict__ lse_out) {
+  const int lane = lane_id();
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float mine = lane < n_parts ? lses[(int64_t)lane * rows + row] : -INFINITY;
+  float m = mine;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  const float e = m > -INFINITY ? expf(mine - m) : 0.0f;
+  const float l = warp_sum(e);
+  const float w_mine = l > 0.0f ? e / l : 0.0f;
+  for (int c0 = lane * 8; c0 < dh; c0 += 256) {
+    float acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    for (int i = 0; i < n_parts; ++i) {
+      const float w = __shfl_sync(0xffffffffu, w_mine, i);
+      const T *src = parts + ((int64_t)i * rows + row) * dh + c0;
+      float v[8];
+      if constexpr (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+        const uint32_t p4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          v[2 * k] = __uint_as_float(p4[k] << 16);
+          v[2 * k + 1] = __uint_as_float(p4[k] & 0xFFFF0000u);
+        }
+      } else {
+        const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = fmaf(w, v[k], acc[k]);
+    }
+    if (out_f32) {
+      *reinterpret_cast<float4 *>(out_f32 + row * dh + c0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4 *>(out_f32 + row * dh + c0 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    if (out_bf16)
+      *reinterpret_cast<uint4 *>(out_bf16 + row * dh + c0) =
+          make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                     pack_bf16x2(acc[6], acc[7]));
+  }
+  if (lane == 0 && lse_out) lse_out[row] = l > 0.0f ? m + logf(l) : -INFINITY;
+}
+
 }  // namespace lsa
 
 // ================================================================================================ C ABI
@@ -466,27 +518,43 @@ LSA_API size_t lsa_sparse_attend_workspace_bytes(int64_t R, int Hq, int dh, int 
   return (size_t)splits * R * Hq * (dh + 1) * sizeof(float);
 }
 
-LSA_API int lsa_lse_merge(const float *parts, const float *lses, int n_parts, int64_t rows, int dh,
+LSA_API int lsa_lse_merge(const void *parts, int parts_dtype, const float *lses, int n_parts, int64_t rows, int dh,
                           uint16_t *out_bf16, float *out_f32, float *lse_out, void *stream) {
   LSA_REQUIRE(parts && lses && (out_bf16 || out_f32), LSA_ERR_NULL);
   LSA_REQUIRE(n_parts >= 1 && rows >= 0 && dh >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(parts_dtype == LSA_DTYPE_F32 || parts_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
   if (rows == 0) return LSA_OK;
+  const bool aligned = dh % 8 == 0 && ((uintptr_t)parts % 16) == 0 && (!out_f32 || ((uintptr_t)out_f32 % 16) == 0) &&
+                       (!out_bf16 || ((uintptr_t)out_bf16 % 16) == 0);
+  if (n_parts < 16 && aligned && (parts_dtype == LSA_DTYPE_BF16 || rows >= 1024)) {
+    const unsigned grid = (unsigned)((rows + 7) / 8);
+    if (parts_dtype == LSA_DTYPE_BF16)
+      lsa::lse_merge_few_kernel<uint16_t><<<grid, 256, 0, (cudaStream_t)stream>>>(
+          (const uint16_t *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+    else
+      lsa::lse_merge_few_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(
+          (const float *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
+  LSA_REQUIRE(parts_dtype == LSA_DTYPE_F32, LSA_ERR_UNSUPPORTED);
+  const float *fparts = (const float *)parts;
   if (n_parts >= 16 && n_parts <= 1024 && dh % 128 == 0 && ((uintptr_t)parts % 16) == 0 &&
       (!out_f32 || ((uintptr_t)out_f32 % 16) == 0) && (!out_bf16 || ((uintptr_t)out_bf16 % 8) == 0)) {
     lsa::lse_merge_split_kernel<<<(unsigned)(rows * (dh / 128)), 128, 0, (cudaStream_t)stream>>>(
-        parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+        fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   if ((n_parts >= 16 || dh >= 256) && dh <= 128 * lsa::kMergeWideDims) {
-    lsa::lse_merge_wide_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(parts, lses, n_parts, rows, dh,
+    lsa::lse_merge_wide_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(fparts, lses, n_parts, rows, dh,
                                                                                   out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   const int warps = 8;
   lsa::lse_merge_kernel<<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream>>>(
-      parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+      fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -552,7 +620,7 @@ LSA_API int lsa_sparse_attend(const uint16_t *q, int64_t R, int Hq, int dh, int6
   else
     rc = group <= 8 ? lsa::launch_attend<64, 1, 9, 3>(p, s) : lsa::launch_attend<64, 2, 9, 3>(p, s);
   if (rc != LSA_OK || splits == 1) return rc;
-  return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dh, out_bf16, out_f32, lse, stream);
+  return lsa_lse_merge(p.part_out, LSA_DTYPE_F32, p.part_lse, splits, R * Hq, dh, out_bf16, out_f32, lse, stream);
 }
 
 // ================================================================================================ no-allocation entry

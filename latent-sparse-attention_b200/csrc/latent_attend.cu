@@ -317,5 +317,5 @@ LSA_API int lsa_latent_attend(const uint16_t *q, int64_t R, int Hq, int dk, int 
     LSA_LAUNCH_CHECK();
   }
   if (splits == 1) return LSA_OK;
-  return lsa_lse_merge(p.part_out, p.part_lse, splits, R * Hq, dv, out_bf16, out_f32, lse, stream);
+  return lsa_lse_merge(p.part_out, LSA_DTYPE_F32, p.part_lse, splits, R * Hq, dv, out_bf16, out_f32, lse, stream);
 }

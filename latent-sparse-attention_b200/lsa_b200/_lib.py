@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 12
+ABI_VERSION = 13
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -61,7 +61,7 @@ SIGNATURES = {
     "lsa_bucket_attend_workspace_bytes": (_Z, [_L, _I, _I, _I, _L]),
     "lsa_bucket_attend": (_I, [_P, _L, _I, _I, _L, _L, _P, _P, _L, _I, _L, _L, _P, _I, _P, _P, _L, _I, _P, _P, _I, _I, _I,
                                _P, _P, _F, _P, _P, _I, _P, _P, _P, _Z, _P]),
-    "lsa_lse_merge": (_I, [_P, _P, _I, _L, _I, _P, _P, _P, _P]),
+    "lsa_lse_merge": (_I, [_P, _I, _P, _I, _L, _I, _P, _P, _P, _P]),
 }
 
 _lib = None

@@ -494,12 +494,16 @@ def band_attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, first_positio
 
 
 def lse_merge(parts: torch.Tensor, lses: torch.Tensor, out_dtype=torch.float32):
-    """Merge [n, rows..., dh] partial outputs by their [n, rows...] log-sum-exps."""
-    parts, lses = _contig(parts.float()), _contig(lses.float())
+    """Merge [n, rows..., dh] partial outputs (fp32, or bf16 for fewer than 16 parts) by their [n, rows...]
+    log-sum-exps."""
+    if parts.dtype != torch.bfloat16 or parts.shape[0] >= 16 or parts.shape[-1] % 8:
+        parts = parts.float()
+    parts, lses = _contig(parts), _contig(lses.float())
     n, dh = parts.shape[0], parts.shape[-1]
     rows = lses.numel() // n
     out = torch.empty(parts.shape[1:], device=parts.device, dtype=out_dtype)
     lse = torch.empty(lses.shape[1:], device=parts.device, dtype=torch.float32)
-    call("lsa_lse_merge", ptr(parts), ptr(lses), n, rows, dh, ptr(out) if out_dtype == torch.bfloat16 else None,
-         ptr(out) if out_dtype == torch.float32 else None, ptr(lse), stream())
+    call("lsa_lse_merge", ptr(parts), _lib.dtype_code(parts), ptr(lses), n, rows, dh,
+         ptr(out) if out_dtype == torch.bfloat16 else None, ptr(out) if out_dtype == torch.float32 else None, ptr(lse),
+         stream())
     return out, lse

@@ -314,7 +314,37 @@ class ShardedLatentLayer:
     def __init__(self, layer, rank: int, world: int, group=None, granule: int = GRANULE):
         self.layer, self.rank, self.world, self.group, self.granule = layer, rank, world, group, granule
         self.design = layer.design
-        self.index_keys = self.centroids = self.members = None
+        self.index_keys = self.centroids = self.members = self.members_own = None
+        d = self.design
+        # A rank's own table of members: every bucket's positions that THIS rank holds (a bucket's pools are dealt
+        # round-robin, so a row is an n-th as wide as the global table's and an expansion over it an n-th of the
+        # work). Rows count toward top_k only through the global table, so it serves when the cut cannot bite.
+        # Room for twice a rank's even share of a full bucket: Ward groups pools by likeness, not by position, so a
+        # bucket's pools spread over the ranks. A bucket that does not fit is counted (`check()` raises) - and at
+        # build time, where the host may look, it simply turns the own tables off.
+        even = -(-d.bucket_cap // (d.pool_size * world)) * d.pool_size
+        self.own_cap = min(d.bucket_cap, -(-2 * even // 64) * 64)
+        self.own_tables = d.top_k >= d.top_p * d.bucket_cap and self.own_cap < d.bucket_cap
+        self.own_overflow = None
+
+    def _own_members(self, members: torch.Tensor) -> torch.Tensor:
+        """The positions of `members` [rows, cap] that this rank holds, ascending, -1 padded: [rows, own_cap]."""
+        none = torch.iinfo(torch.int32).max
+        mine = (members >= 0) & ((members // self.granule) % self.world == self.rank)
+        over = (mine.sum(1) > self.own_cap).sum().to(torch.int32).reshape(1)
+        self.own_overflow = over if self.own_overflow is None else self.own_overflow + over
+        kept, _ = torch.where(mine, members, none).sort(dim=1)
+        kept = kept[:, : self.own_cap]
+        return torch.where(kept == none, -1, kept).contiguous()
+
+    def check(self) -> None:
+        """The layer's deferred checks (`FlatLayer.check`), and that no bucket outgrew this rank's own table since
+        the index was built."""
+        self.layer.check()
+        if self.own_overflow is not None and int(self.own_overflow):
+            self.own_overflow.zero_()
+            raise ValueError(f"a bucket holds more than {self.own_cap} positions of rank {self.rank}: build the layer "
+                             "with own_tables off")
 
     def _cluster(self, keys: torch.Tensor, first_position: int):
         """Pools, Ward and the bucket table of whole blocks whose index keys are `keys` [blocks * block, d]."""
@@ -347,6 +377,10 @@ class ShardedLatentLayer:
             every = gather_pieces(members, self.group)
             self.members = every.view(world, blocks // world, per_block, d.bucket_cap).transpose(0, 1).reshape(
                 blocks * per_block, d.bucket_cap).contiguous()
+            if self.own_tables:
+                self.members_own = self._own_members(self.members)
+                if int(self.own_overflow):  # (a one-off host read at build time)
+                    self.own_tables, self.members_own, self.own_overflow = False, None, None
 
     def extend_index(self, share: torch.Tensor, first: int, count: int) -> None:
         """The index step of a prefill chunk at positions first .. first + count - 1: every rank maps the rows of
@@ -367,6 +401,8 @@ class ShardedLatentLayer:
         with probe.region("ward"):
             members, centroids = self._cluster(self.index_keys[b0 * block:b1 * block], b0 * block)
             self.members[b0 * per_block:b1 * per_block] = members
+            if self.own_tables:
+                self.members_own[b0 * per_block:b1 * per_block] = self._own_members(members)
             for b in range(b0, b1):
                 if b % world == rank:
                     at = (b // world) * per_block
@@ -402,16 +438,21 @@ class ShardedLatentLayer:
         d = self.design
         picked = self.pick(rows, positions)
         with probe.region("expand"):
-            lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size,
-                                           dealt=(self.granule, self.world, self.rank))
+            if self.own_tables:  # (the cut at top_k cannot bite: this rank's members are all there is to list)
+                lists, lengths, _ = ops.expand(picked, positions, self.members_own, d.top_p * self.own_cap, d.sink_size,
+                                               d.window_size, dealt=(self.granule, self.world, self.rank))
+            else:
+                lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size,
+                                               dealt=(self.granule, self.world, self.rank))
         return lists, lengths
 
     def _read_rows(self, rows: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int) -> tuple:
+        """This rank's partial read of every row: (out bf16, lse). (bf16 partials: they cross NVLink next.)"""
         layer = self.layer
         lists, lengths = self.select(rows, positions)
         with probe.region("attend"):
             return ops.latent_attend(rows, share, lists, lengths, layer.scale, value_dim=layer.value_dim,
-                                     splits=splits, out_dtype=torch.float32, status=layer._attend_status)
+                                     splits=splits, out_dtype=torch.bfloat16, status=layer._attend_status)
 
     def prefill_rows(self, rows: torch.Tensor, start: int, share: torch.Tensor, out: torch.Tensor | None = None):
         """The read of replicated query rows [n, heads, latent_dim] at positions start.. : this rank's share of the

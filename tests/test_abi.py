@@ -46,7 +46,7 @@ def test_arguments_are_refused_on_the_host_before_any_launch():
     # NULL pointers and bad sizes are decided before the CUDA runtime is touched
     assert lib.lsa_pool_keys(None, 0, 4, 4, 16, None, None) == -2
     assert lib.lsa_ward_merge(None, None, 4.0, 1, 64, 64, 32, 64.0, 256, None, None, None, None, 0, None) == -2
-    assert lib.lsa_lse_merge(None, None, 2, 8, 128, None, None, None, None) == -2
+    assert lib.lsa_lse_merge(None, 0, None, 2, 8, 128, None, None, None, None) == -2
     with pytest.raises(ValueError, match="NULL"):
         _lib.call("lsa_expand", None, 1, 1, None, None, 0, 1, None, None, 1, 0, 1, None, 0, 0, 1, 1, 1, 0, 0, None, None,
                   None, None)
