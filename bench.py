@@ -361,8 +361,9 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     parity, cpu = None, None
     if world > 1:  # every rank's share of the sample rows' lists, as positions
         local = lists_d[sample].to(torch.int64)
-        as_positions = torch.where(local >= 0, (local // 64 * world + rank) * 64 + local % 64, local)
-        every_lists = gather_pieces(as_positions.to(torch.int32)).cpu().numpy()
+        as_positions = torch.full((len(sample), layer.design.list_width), -1, dtype=torch.int32, device="cuda")
+        as_positions[:, : local.shape[1]] = torch.where(local >= 0, (local // 64 * world + rank) * 64 + local % 64, local)
+        every_lists = gather_pieces(as_positions).cpu().numpy()
     if rank == 0:
         oracle.set_threads(host_threads())
         b_np = buckets_to_host(buckets)
@@ -396,7 +397,17 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
                   "against": "CPU oracle on the device's own index vectors"
                              + ("; the ranks' lists are united before they are compared" if world > 1 else "")}
         if not same:
-            fail("C4 read lists differ from the oracle's")
+            detail = ""
+            if world > 1:
+                for i in range(len(sample)):
+                    union = every_lists[:, i].reshape(-1)
+                    got_set, want_set = set(union[union >= 0].tolist()), set(want_lists[i, : want_lens[i]].tolist())
+                    if got_set != want_set or len(got_set) != int((union >= 0).sum()):
+                        detail = (f" (row {sample[i]}: {int((union >= 0).sum())} listed, {len(got_set)} distinct, "
+                                  f"{len(want_set)} wanted, {len(want_set - got_set)} missing, "
+                                  f"{len(got_set - want_set)} extra)")
+                        break
+            fail("C4 read lists differ from the oracle's" + detail)
         if worst > TOLERANCE["attention_max_abs"] or mean > TOLERANCE["attention_mean_abs"]:
             fail(f"C4 attention differs from the oracle: max-abs {worst}, mean-abs {mean}")
         # the CPU baseline on the same sample: per-token stage times summed

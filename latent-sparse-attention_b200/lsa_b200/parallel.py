@@ -378,9 +378,14 @@ class ShardedLatentLayer:
             self.members = every.view(world, blocks // world, per_block, d.bucket_cap).transpose(0, 1).reshape(
                 blocks * per_block, d.bucket_cap).contiguous()
             if self.own_tables:
-                self.members_own = self._own_members(self.members)
-                if int(self.own_overflow):  # (a one-off host read at build time)
-                    self.own_tables, self.members_own, self.own_overflow = False, None, None
+                # the widest own row over ALL ranks, in whole pools and with a quarter to spare for the buckets still
+                # to come (a one-off host read at build time): every rank keeps tables of the same width
+                held = ((self.members >= 0) & ((self.members // self.granule) % world == rank)).sum(1).max().reshape(1)
+                dist.all_reduce(held, op=dist.ReduceOp.MAX, group=self.group)
+                roomy = -(-int(held) * 5 // 4 // 64) * 64
+                self.own_cap = min(d.bucket_cap, max(self.own_cap, roomy))
+                self.own_tables = self.own_cap < d.bucket_cap
+                self.members_own = self._own_members(self.members) if self.own_tables else None
 
     def extend_index(self, share: torch.Tensor, first: int, count: int) -> None:
         """The index step of a prefill chunk at positions first .. first + count - 1: every rank maps the rows of
@@ -408,10 +413,34 @@ class ShardedLatentLayer:
                     at = (b // world) * per_block
                     self.centroids[at:at + per_block] = centroids[(b - b0) * per_block:(b - b0 + 1) * per_block]
 
+    def adopt_index(self, index_keys: torch.Tensor, centroids: torch.Tensor, members: torch.Tensor) -> None:
+        """Take this rank's part of an index that exists whole (every index key, the centroids and the member table
+        of ALL buckets, block after block): what `build_index` leaves behind, without its collectives."""
+        d, world, rank = self.design, self.world, self.rank
+        per_block = d.block_bucket_count
+        blocks = members.shape[0] // per_block
+        self.index_keys, self.members = index_keys, members.contiguous()
+        self.centroids = centroids.view(blocks // world, world, per_block, -1)[:, rank].reshape(
+            blocks // world * per_block, -1).contiguous()
+        if self.own_tables:
+            self.members_own = self._own_members(self.members)
+            if int(self.own_overflow):
+                self.own_tables, self.members_own, self.own_overflow = False, None, None
+
     def pick(self, rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """Every row's top-p buckets, best first, as GLOBAL bucket ids [R, top_p] - the same on every rank. A
         collective call: each rank scores the centroids of its own blocks, the candidates are all-gathered and cut
         with the single-GPU tie rule."""
+        keys = self.local_candidates(rows, positions)
+        with probe.region("exchange candidates"):
+            every = gather_candidates(keys, self.group)
+        with probe.region("select"):
+            _, picked = ops.merge_candidates(every)
+        return picked
+
+    def local_candidates(self, rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """This rank's candidates for every row: the top-p of the buckets it clustered, as packed keys over GLOBAL
+        bucket ids [R, top_p]."""
         layer, d, world, rank = self.layer, self.design, self.world, self.rank
         per_block = d.block_bucket_count
         with probe.region("index map"):
@@ -424,19 +453,17 @@ class ShardedLatentLayer:
                 keys, _ = ops.flat_select_decode(index_queries, self.centroids, None, visible, d.top_p, splits=4)
             else:
                 keys, _ = ops.flat_select(index_queries, self.centroids, visible, d.top_p)
-            keys = globalise_keys(keys, per_block, rank, world)
-        with probe.region("exchange candidates"):
-            every = gather_candidates(keys, self.group)
-        with probe.region("select"):
-            _, picked = ops.merge_candidates(every)
-        return picked
+            return globalise_keys(keys, per_block, rank, world)
 
     def select(self, rows: torch.Tensor, positions: torch.Tensor) -> tuple:
         """This rank's share of every row's read list, as rows of its own cache: (lists, lengths). A collective call
         (the candidates are exchanged inside). Local row l of rank r is position (l / granule * world + r) * granule
         + l % granule."""
+        return self.expand_own(self.pick(rows, positions), positions)
+
+    def expand_own(self, picked: torch.Tensor, positions: torch.Tensor) -> tuple:
+        """The rows of this rank's cache that the picks (global bucket ids) list for every row: (lists, lengths)."""
         d = self.design
-        picked = self.pick(rows, positions)
         with probe.region("expand"):
             if self.own_tables:  # (the cut at top_k cannot bite: this rank's members are all there is to list)
                 lists, lengths, _ = ops.expand(picked, positions, self.members_own, d.top_p * self.own_cap, d.sink_size,

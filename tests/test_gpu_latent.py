@@ -248,6 +248,67 @@ def test_latent_attend_over_a_dealt_cache(oracle, splits):
     assert not out.any() and torch.isinf(lse).all()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_the_ranks_of_a_sharded_layer_played_on_one_gpu(world):
+    """Every step a rank of the sharded MLA layer takes except the collectives themselves, for 2, 4 and 8 ranks in
+    turn on one GPU: the candidates of the ranks' own buckets cut together are the single-GPU picks, bit for bit;
+    the rows the ranks list (through their own member tables where the layer keeps them) are, united, the
+    single-GPU list; and the ranks' partial reads merged by their log-sum-exps are the single-GPU output."""
+    from lsa_b200 import ops
+    from lsa_b200 import workloads as W
+    from lsa_b200.latent import LatentLayer
+    from lsa_b200.parallel import ShardedLatentLayer, deal
+
+    cfg = W.cut(W.C4, 64 * 5120)
+    T, chunk, Hq, dk, dv = cfg["tokens"], 256, cfg["heads"], cfg["latent_dim"], cfg["value_dim"]
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    cache, tail = W.latent_cache(cfg, gen, keep_tail=chunk)
+    qmap, kmap = W.latent_maps(cfg, gen)
+    q = W.latent_queries(cfg, tail, gen)
+    layer = LatentLayer(W.design_of(cfg), qmap, kmap, Hq, dk, dv, scale=W.latent_scale(cfg))
+    index = layer.build_index(cache)
+    positions = torch.arange(T - chunk, T, device="cuda")
+    index_q = layer.index_queries(q)
+    want_picked = layer.pick(index_q, positions, index)[0]
+    want_lists, want_lens = layer.select(index_q, positions, index)
+    want = torch.empty(chunk, Hq, dv, dtype=torch.bfloat16, device="cuda")
+    layer.prefill_rows(q, T - chunk, cache, index, want)
+
+    ranks = [ShardedLatentLayer(layer, r, world) for r in range(world)]
+    for s in ranks:
+        s.adopt_index(index.index_keys, index.buckets.bucket_centroids, index.buckets.bucket_members)
+    assert [s.own_tables for s in ranks] == [world >= 4] * world
+    every = torch.stack([s.local_candidates(q, positions) for s in ranks])
+    _, picked = ops.merge_candidates(every)
+    assert torch.equal(picked, want_picked)
+    parts, lses, union = [], [], [[] for _ in range(chunk)]
+    for r, s in enumerate(ranks):
+        lists, lens = s.expand_own(picked, positions)
+        local = lists.cpu().numpy().astype(np.int64)
+        for i in range(0, chunk, 17):
+            row = local[i, : int(lens[i])]
+            assert (row >= 0).all()
+            union[i] += ((row // 64 * world + r) * 64 + row % 64).tolist()
+        out, lse = ops.latent_attend(q, deal(cache, r, world).contiguous(), lists, lens, layer.scale,
+                                     out_dtype=torch.bfloat16)
+        parts.append(out)
+        lses.append(lse)
+    for i in range(0, chunk, 17):
+        assert sorted(union[i]) == sorted(want_lists[i, : int(want_lens[i])].tolist()), i
+    merged, _ = ops.lse_merge(torch.stack(parts), torch.stack(lses), out_dtype=torch.bfloat16)
+    gap = (merged.float() - want.float()).abs()
+    assert gap.max().item() <= 2e-2 and gap.mean().item() <= 2e-3, (gap.max().item(), gap.mean().item())
+    # the decode row: every rank is handed the whole list and reads the positions it holds
+    parts, lses = [], []
+    for r in range(world):
+        out, lse = ops.latent_attend(q[-1:], deal(cache, r, world).contiguous(), want_lists[-1:], want_lens[-1:],
+                                     layer.scale, splits=5, out_dtype=torch.float32, dealt=(64, world, r))
+        parts.append(out)
+        lses.append(lse)
+    merged, _ = ops.lse_merge(torch.stack(parts), torch.stack(lses), out_dtype=torch.bfloat16)
+    assert (merged.float() - want[-1:].float()).abs().max().item() <= 2e-2
+
+
 def test_latent_attend_long_lists_in_bf16(oracle):
     """Lists of thousands of keys (a hundred tiles a row), ragged ends, bf16 output: the size a served row has."""
     from lsa_b200 import ops
