@@ -328,7 +328,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     def decode():
         if world == 1:
             return layer.decode(q1, pos1, share, index, splits=args.decode_splits)
-        return sharded.decode(q1, pos1, share, splits=max(1, args.decode_splits // world))
+        return sharded.decode(q1, pos1, share, splits=max(16, args.decode_splits // world))
 
     # ---- parity of the timed path, before anything is timed
     step()

@@ -172,6 +172,26 @@ int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroi
                     const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
                     int64_t *keys_out, int32_t *picked_out, void *stream);
 
+/* The same search with the scan on the tensor cores: the result is lsa_flat_select's, key for key. The bf16
+ * scores of every (row, bucket) pair are made in tensor memory by tcgen05 products and never written; a row keeps
+ * the buckets at or above a threshold bisected from 512 strided samples of its own scores, less a margin that
+ * covers the bf16 rounding; the few hundred survivors are rescored with lsa_flat_select's exact fp32 dot and
+ * the best top_p kept. A row is accepted only when its worst pick is at or above the threshold (then no dropped
+ * bucket could have displaced it); any other row - and every row that sees fewer than 1,024 buckets - is scanned
+ * exactly, so the outcome never depends on the threshold being well chosen.
+ * Reference: the Blackwell bucket scan (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836), its
+ * sampled thresholds (src/lsa/core/kernels/scan_select.py:228-271) and ScanSelect's exact rescoring
+ * (src/lsa/core/kernels/scan_select.py:189-385).
+ *   centroids_bf16 [m, 64] the bf16 rounding of centroids (lsa_bucket_table's centroids_bf16); d = 64, top_p <= 512
+ *   max_visible  the host's bound on visible[] (<= 0: m) - it sets how far apart the samples lie
+ *   status       (may be NULL) raised if a bounded on-chip wait gives up; the rows it cut are scanned exactly
+ *   workspace    lsa_scan_select_workspace_bytes(R, top_p, m), 256-byte aligned */
+size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m);
+int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids, const uint16_t *centroids_bf16,
+                    int64_t m, const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                    int max_visible, int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
+                    size_t workspace_bytes, void *stream);
+
 /* Flat search, decode form: few rows, many buckets. The buckets of a row are split over `splits` CTAs whose
  * local top_p lists are merged by a second kernel. Reference: Selector.decode_flat
  * (src/lsa/sglang/index/selector.py:603-660), scan_paged (src/lsa/core/kernels/triton/paged.py:61-101),

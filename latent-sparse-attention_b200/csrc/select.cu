@@ -5,6 +5,7 @@
 // carried children beside a run of open rows). Selection is exact: a streaming top-k over 64-bit keys whose low
 // word breaks a score tie toward the lower id, so the result does not depend on the order keys were produced in.
 #include "common.cuh"
+#include "scan_select.cuh"
 
 namespace lsa {
 
@@ -490,6 +491,7 @@ constexpr int kFlatThreads = kFlatRows * 32;
 struct FlatParams {
   const float *queries, *centroids;
   const int32_t *visible, *row_keep;
+  const int32_t *row_flags;  // [R] or NULL: only rows with a nonzero flag are scanned (the others keep their output)
   int64_t *keys_out;
   int32_t *ids_out;
   int64_t R, m;
@@ -515,7 +517,7 @@ __global__ void __launch_bounds__(kFlatThreads) flat_select_kernel(FlatParams p)
   }
   if (tid < kFlatRows) {
     const int64_t r = row0 + tid;
-    int v = r < p.R ? p.visible[r] : 0;
+    int v = r < p.R && (!p.row_flags || p.row_flags[r]) ? p.visible[r] : 0;
     visible_s[tid] = v < 0 ? 0 : (v > p.m ? (int)p.m : v);
   }
   __syncthreads();
@@ -568,7 +570,7 @@ __global__ void __launch_bounds__(kFlatThreads) flat_select_kernel(FlatParams p)
     }
     __syncthreads();
   }
-  if (my_row < p.R) {
+  if (my_row < p.R && (!p.row_flags || p.row_flags[my_row])) {
     int64_t *buf = bufs + (size_t)warp * row_room;
     warp_sort_descending(buf, held);
     for (int i = lane; i < p.keep; i += 32) {
@@ -598,6 +600,222 @@ static int launch_flat(FlatParams p, cudaStream_t s) {
 }  // namespace lsa
 
 // ================================================================================================ C ABI
+
+// ------------------------------------------------------------------------------------------------ tensor-core scan
+
+namespace lsa {
+
+// Before the scan: a bf16 copy of the query rows (the M operand of the scan's products), their lengths, which rows
+// take the exact scan instead (too few visible buckets for a sampled threshold to mean anything), and the widest
+// visible count among a tile's other rows.
+__global__ void __launch_bounds__(128)
+    scan_prepare_kernel(const float *__restrict__ queries, const int32_t *__restrict__ visible, int64_t R, int64_t m,
+                        uint16_t *__restrict__ q_bf16, float *__restrict__ norms, int32_t *__restrict__ flags,
+                        int32_t *__restrict__ tile_visible) {
+  __shared__ int widest_s;
+  const int64_t row = (int64_t)blockIdx.x * 128 + threadIdx.x;
+  if (threadIdx.x == 0) widest_s = 0;
+  __syncthreads();
+  float ss = 0.0f;
+  uint32_t packed[32];
+#pragma unroll
+  for (int k = 0; k < 64; k += 4) {
+    const float4 v = row < R ? *reinterpret_cast<const float4 *>(queries + row * 64 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v.x, v.x, ss), ss = fmaf(v.y, v.y, ss), ss = fmaf(v.z, v.z, ss), ss = fmaf(v.w, v.w, ss);
+    packed[k / 2] = (uint32_t)float_to_bf16_bits(v.x) | ((uint32_t)float_to_bf16_bits(v.y) << 16);
+    packed[k / 2 + 1] = (uint32_t)float_to_bf16_bits(v.z) | ((uint32_t)float_to_bf16_bits(v.w) << 16);
+  }
+  uint4 *dst = reinterpret_cast<uint4 *>(q_bf16 + row * 64);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+  if (row < R) {
+    const int v = min(max(visible[row], 0), (int)m);
+    const bool exact = v < kScanMinVisible || !(ss > 0.0f) || !isfinite(ss);
+    norms[row] = sqrtf(ss);
+    flags[row] = exact ? 1 : 0;
+    if (!exact) atomicMax(&widest_s, v);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) tile_visible[blockIdx.x] = widest_s;
+}
+
+// After the scan: a warp a row rescores the row's survivors with the exact fixed-order fp32 dot, picks the best
+// `keep` of them, and PROVES the pick: every bucket the scan dropped scored below threshold - margin in bf16, so
+// below the threshold exactly; if the worst pick is at or above the threshold nothing dropped could have displaced
+// it. A row that cannot be proven (too few survivors, an overflowed list, a pick under the threshold) is flagged
+// for the exact scan, which then overwrites it.
+__global__ void __launch_bounds__(kSelThreads)
+    scan_pick_kernel(ScanParams p, const float *__restrict__ queries, const float *__restrict__ centroids,
+                     int32_t *__restrict__ flags, int id_base, int room, int64_t *__restrict__ keys_out,
+                     int32_t *__restrict__ ids_out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  int64_t *buf = reinterpret_cast<int64_t *>(smem_raw) + (size_t)warp * room;
+  int *hist = reinterpret_cast<int *>(reinterpret_cast<int64_t *>(smem_raw) + (size_t)kSelWarps * room) + warp * kHistBins;
+  const int64_t row = (int64_t)blockIdx.x * kSelWarps + warp;
+  if (row >= p.R || flags[row]) return;
+  const int visible = min(max(p.visible[row], 0), (int)p.m);
+  const int keep = p.row_keep ? min(p.row_keep[row], p.keep) : p.keep;
+  const int need = min(keep, visible);
+  const float *q = queries + row * 64;
+  int total = 0;
+  bool over = false;
+  for (int span = 0; span < p.spans; ++span) {
+    const int found = p.counts[row * p.spans + span];
+    over |= found > p.cap;
+    const int n = min(found, p.cap);
+    const int32_t *list = p.survivors + (row * p.spans + span) * p.cap;
+    for (int j = lane; j < n; j += 32) {
+      const int32_t id = list[j];
+      const float4 *v4 = reinterpret_cast<const float4 *>(centroids + (int64_t)id * 64);
+      float acc = 0.0f;
+#pragma unroll 4
+      for (int k4 = 0; k4 < 16; ++k4) {
+        const float4 v = __ldg(v4 + k4);
+        const float4 qv = *reinterpret_cast<const float4 *>(q + k4 * 4);
+        acc = fmaf(qv.x, v.x, acc), acc = fmaf(qv.y, v.y, acc), acc = fmaf(qv.z, v.z, acc), acc = fmaf(qv.w, v.w, acc);
+      }
+      buf[total + j] = pack_key(acc, id + id_base);
+    }
+    total += n;
+  }
+  __syncwarp();
+  bool proven = !over && total >= need;
+  if (keep == 0) total = 0;  // (a row whose budget is nothing)
+  if (proven && total > keep) {
+    const uint64_t kth = warp_kth_greatest(buf, total, keep, hist);
+    total = warp_compact(buf, 0, total, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
+  }
+  if (proven) {
+    warp_sort_descending(buf, total);
+    if (need == keep && keep > 0) {  // (a row that sees fewer buckets than it keeps holds them all already)
+      const int32_t bits = (int32_t)(buf[keep - 1] >> 32);
+      const float worst = __int_as_float(bits < 0 ? (bits ^ 0x7FFFFFFF) : bits);
+      proven = worst >= p.thresholds[row];
+    }
+  }
+  if (!proven) {
+    if (lane == 0) flags[row] = 1;
+    return;
+  }
+  for (int i = lane; i < p.keep; i += 32) {
+    const int64_t key = i < total && i < keep ? buf[i] : kEmptyKey;
+    if (keys_out) keys_out[row * p.keep + i] = key;
+    if (ids_out) ids_out[row * p.keep + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+  }
+}
+
+struct ScanWorkspace {
+  size_t q_bf16, norms, flags, tile_visible, thresholds, counts, survivors, total;
+};
+
+static int scan_spans(int64_t padded_rows, int64_t m) {
+  const int row_tiles = (int)(padded_rows / 128), tiles = (int)((m + 127) / 128);
+  // One wave of CTAs (each owns an SM's tensor memory): every span repeats the four sample tiles and the
+  // bisection, so the fewest spans that fill the machine, of at least eight tiles each.
+  int spans = 148 / row_tiles;
+  spans = max(1, min(spans, tiles / 8));
+  return min(spans, 16);
+}
+
+static int scan_cap(int top_p, int spans) {
+  const int even = (kScanFactor * top_p + spans - 1) / spans;
+  return max(64, (4 * even + 31) / 32 * 32);
+}
+
+static ScanWorkspace scan_workspace(int64_t R, int top_p, int64_t m) {
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  const int64_t padded = (R + 127) / 128 * 128;
+  const int spans = scan_spans(padded, m), cap = scan_cap(top_p, spans);
+  ScanWorkspace w;
+  size_t at = 0;
+  w.q_bf16 = at, at += up((size_t)padded * 64 * 2);
+  w.norms = at, at += up((size_t)R * 4);
+  w.flags = at, at += up((size_t)R * 4);
+  w.tile_visible = at, at += up((size_t)(padded / 128) * 4);
+  w.thresholds = at, at += up((size_t)R * 4);
+  w.counts = at, at += up((size_t)R * spans * 4);
+  w.survivors = at, at += up((size_t)R * spans * cap * 4);
+  w.total = at;
+  return w;
+}
+
+}  // namespace lsa
+
+LSA_API size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m) {
+  if (R <= 0 || top_p <= 0 || m < 0) return 0;
+  return lsa::scan_workspace(R, top_p, m).total;
+}
+
+LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids,
+                            const uint16_t *centroids_bf16, int64_t m, const int32_t *visible,
+                            const int32_t *row_top_p, int top_p, int32_t bucket_id_base, int max_visible,
+                            int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+  LSA_REQUIRE(queries && centroids && centroids_bf16 && visible && (keys_out || picked_out) && workspace, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && m >= 0 && m < INT32_MAX && top_p >= 1, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(d == 64 && top_p <= 512, LSA_ERR_UNSUPPORTED);
+  LSA_REQUIRE(((uintptr_t)queries % 16) == 0 && ((uintptr_t)centroids % 16) == 0 && ((uintptr_t)centroids_bf16 % 16) == 0 &&
+                  ((uintptr_t)workspace % 256) == 0,
+              LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  const lsa::ScanWorkspace w = lsa::scan_workspace(R, top_p, m);
+  LSA_REQUIRE(workspace_bytes >= w.total, LSA_ERR_WORKSPACE);
+  cudaStream_t s = (cudaStream_t)stream;
+  unsigned char *base = reinterpret_cast<unsigned char *>(workspace);
+  const int64_t padded = (R + 127) / 128 * 128;
+  lsa::ScanParams p = {};
+  p.queries_bf16 = reinterpret_cast<uint16_t *>(base + w.q_bf16);
+  p.centroids_bf16 = centroids_bf16;
+  p.visible = visible;
+  p.row_keep = row_top_p;
+  int32_t *flags = reinterpret_cast<int32_t *>(base + w.flags);
+  p.flags = flags;
+  p.norms = reinterpret_cast<float *>(base + w.norms);
+  p.tile_visible = reinterpret_cast<int32_t *>(base + w.tile_visible);
+  p.thresholds = reinterpret_cast<float *>(base + w.thresholds);
+  p.counts = reinterpret_cast<int32_t *>(base + w.counts);
+  p.survivors = reinterpret_cast<int32_t *>(base + w.survivors);
+  p.status = status;
+  p.R = R, p.m = m;
+  p.spans = lsa::scan_spans(padded, m);
+  p.cap = lsa::scan_cap(top_p, p.spans);
+  p.keep = top_p;
+  const int64_t widest = max_visible > 0 && max_visible < m ? max_visible : m;
+  p.sample_stride = (int)((widest + 511) / 512 > 1 ? (widest + 511) / 512 : 1);
+  lsa::scan_prepare_kernel<<<(unsigned)(padded / 128), 128, 0, s>>>(
+      queries, visible, R, m, const_cast<uint16_t *>(p.queries_bf16), const_cast<float *>(p.norms), flags,
+      const_cast<int32_t *>(p.tile_visible));
+  LSA_LAUNCH_CHECK();
+  if (m >= lsa::kScanMinVisible) {
+    int rc = lsa::launch_scan_survivors(p, padded, s);
+    if (rc != LSA_OK) return rc;
+    int room = 2;
+    while (room < p.spans * p.cap) room <<= 1;
+    const size_t smem = (size_t)lsa::kSelWarps * ((size_t)room * 8 + lsa::kHistBins * 4);
+    LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
+    if (cudaFuncSetAttribute(lsa::scan_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LSA_ERR_LAUNCH;
+    lsa::scan_pick_kernel<<<(unsigned)((R + lsa::kSelWarps - 1) / lsa::kSelWarps), lsa::kSelThreads, smem, s>>>(
+        p, queries, centroids, flags, bucket_id_base, room, keys_out, picked_out);
+    LSA_LAUNCH_CHECK();
+  }
+  // the exact scan of the rows that are flagged: too few visible buckets, or a pick the survivors could not prove
+  lsa::FlatParams f = {};
+  f.queries = queries;
+  f.centroids = centroids;
+  f.visible = visible;
+  f.row_keep = row_top_p;
+  f.row_flags = flags;
+  f.keys_out = keys_out;
+  f.ids_out = picked_out;
+  f.R = R;
+  f.m = m;
+  f.d = d;
+  f.keep = top_p;
+  f.id_base = bucket_id_base;
+  return lsa::launch_flat<64>(f, s);
+}
 
 LSA_API int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,
                             const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,

@@ -53,9 +53,7 @@ class LatentLayer(FlatLayer):
         self.scale = latent_dim ** -0.5 if scale is None else scale
         self.map_piece = map_piece
         self._buffers = {}
-        self.status = torch.zeros(4, device=device, dtype=torch.int32)
-        self._map_status, self._table_status = self.status[0:1], self.status[1:2]
-        self._expand_status, self._attend_status = self.status[2:3], self.status[3:4]
+        self._status_slots(device)
         self._reached = []
 
     # ---- the maps
@@ -124,7 +122,7 @@ class LatentLayer(FlatLayer):
         with probe.region("index map"):
             index_queries = self.index_queries(rows, out=self._buffer("index queries", (n, self.index_dim),
                                                                       torch.float32, dev))
-        lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True)
+        lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, last_position=start + n - 1)
         with probe.region("attend"):
             ops.latent_attend(rows, latent, lists, lengths, self.scale, value_dim=self.value_dim, out=out,
                               warp_mma=warp_mma, status=self._attend_status)

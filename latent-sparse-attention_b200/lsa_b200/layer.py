@@ -47,11 +47,13 @@ class FlatDesign:
 
 
 class FlatIndex:
-    """A request's index: its index keys and the buckets of its closed cluster blocks."""
+    """A request's index: its index keys and the buckets of its closed cluster blocks (and, where the tensor-core
+    scan can use it, the bf16 rounding of the centroids)."""
 
-    def __init__(self, index_keys: torch.Tensor, buckets: Buckets):
+    def __init__(self, index_keys: torch.Tensor, buckets: Buckets, centroids_bf16: torch.Tensor | None = None):
         self.index_keys = index_keys
         self.buckets = buckets
+        self.centroids_bf16 = centroids_bf16
 
 
 class FlatLayer:
@@ -76,9 +78,7 @@ class FlatLayer:
         self._buffers: dict = {}
         # What the kernels report from the device, read by `check()`: bounded waits of the map kernels that gave up,
         # buckets over their cap in the table, bad picks in the expansion, bounded waits of the attention kernels.
-        self.status = torch.zeros(4, device=query_map.device, dtype=torch.int32)
-        self._map_status, self._table_status = self.status[0:1], self.status[1:2]
-        self._expand_status, self._attend_status = self.status[2:3], self.status[3:4]
+        self._status_slots(query_map.device)
         self._reached: list = []  # per index build: whether each cluster block merged down to its bucket count
         # The bucket-major attend pass has two forms: (pair, head) rows as the M = 128 side of tcgen05 products with S
         # and O in tensor memory (the default), or warp-level MMA tiles of 16 rows.
@@ -93,6 +93,13 @@ class FlatLayer:
             self.query_map_t = ops.expand_map(self.query_map, heads, heads // kv_heads, head_dim, self.dh_off,
                                               self.dh_used)
             self.key_map_t = ops.expand_map(self.key_map, kv_heads, 1, head_dim, self.dh_off, self.dh_used)
+
+    def _status_slots(self, device) -> None:
+        """The layer's deferred-status words: index map, bucket table, expansion, attention, bucket scan."""
+        self.status = torch.zeros(5, device=device, dtype=torch.int32)
+        self._map_status, self._table_status = self.status[0:1], self.status[1:2]
+        self._expand_status, self._attend_status = self.status[2:3], self.status[3:4]
+        self._scan_status = self.status[4:5]
 
     def check(self) -> None:
         """The deferred checks of everything launched since the last call: ONE host synchronisation, so a hot path
@@ -109,9 +116,10 @@ class FlatLayer:
                              f"the cap {self.design.bucket_cap}; {counts[1]} buckets overflowed it")
         if counts[2]:
             raise ValueError(f"{counts[2]} picked bucket ids lay outside the member table")
-        if counts[0] or counts[3]:
+        if counts[0] or counts[3] or counts[4]:
             raise RuntimeError(f"bounded on-chip waits gave up ({counts[0]} in the index map, {counts[3]} in the "
-                               "attention kernels): the outputs since the last check are void")
+                               f"attention kernels, {counts[4]} in the bucket scan): the outputs since the last "
+                               "check are void")
 
     # ---- buffers
 
@@ -176,12 +184,14 @@ class FlatLayer:
                 "members": make("members", (rows, d.bucket_cap), torch.int32), "sizes": make("sizes", (rows,), torch.int32),
                 "key sums": make("key sums", (rows, d_idx), torch.float32),
                 "centroids": make("centroids", (rows, d_idx), torch.float32)}
+        if d_idx == 64:  # (the operand of the tensor-core scan)
+            bufs["centroids bf16"] = make("centroids bf16", (rows, d_idx), torch.bfloat16)
         return bufs
 
     def _index_of(self, bufs: dict) -> FlatIndex:
         d = self.design
         return FlatIndex(bufs["keys"], Buckets(bufs["centroids"], bufs["members"], bufs["sizes"], d.block_bucket_count,
-                                               d.cluster_block_size))
+                                               d.cluster_block_size), bufs.get("centroids bf16"))
 
     def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
         """Index keys of k [n, ...] = the keys at positions first.., and the pools, Ward labels and bucket table of
@@ -210,14 +220,17 @@ class FlatLayer:
                 self._reached.append(bufs["reached"][b0:b0 + nb])
         with probe.region("bucket table"):
             outs = (bufs["members"][r0:r1], bufs["sizes"][r0:r1], bufs["key sums"][r0:r1], bufs["centroids"][r0:r1],
-                    None, bufs["status"])
+                    bufs["centroids bf16"][r0:r1] if "centroids bf16" in bufs else None, bufs["status"])
             ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count, d.bucket_cap, first_position=first,
                              outs=outs)
 
+    scan_rows = 1 << 30  # from this many rows on, a pick runs its scan on the tensor cores
+
     def pick(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
-             reuse_buffers: bool = False):
+             reuse_buffers: bool = False, last_position: int | None = None):
         """The top-p buckets of every row, best first: (picked [R, top_p] int32, positions int64, and the rows' own
-        budgets under an early budget, else None)."""
+        budgets under an early budget, else None). `last_position` is the host's bound on `positions`, if it has
+        one (it places the samples of the tensor-core scan; the result does not depend on it)."""
         d, b, dev = self.design, index.buckets, index_queries.device
         R = index_queries.shape[0]
         positions = positions.to(torch.int64)
@@ -233,17 +246,26 @@ class FlatLayer:
             keys = self._buffer("keys", (R, d.top_p), torch.int64, dev)
             picked = self._buffer("picked", (R, d.top_p), torch.int32, dev)
         with probe.region("select"):
-            _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
-                                        picked=picked)
+            if index.centroids_bf16 is not None and R >= self.scan_rows and d.top_p <= 512:
+                bound = 0 if last_position is None else \
+                    last_position // d.cluster_block_size * d.block_bucket_count
+                need = ops.query("lsa_scan_select_workspace_bytes", R, d.top_p, b.bucket_centroids.shape[0])
+                work = self._buffer("scan", (need,), torch.uint8, dev)
+                _, picked = ops.scan_select(index_queries, b.bucket_centroids, index.centroids_bf16, visible, d.top_p,
+                                            row_p, max_visible=bound, keys=keys, picked=picked,
+                                            status=self._scan_status, workspace=work)
+            else:
+                _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
+                                            picked=picked)
         return picked, positions, row_p, row_k
 
     def select(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
-               reuse_buffers: bool = False, local: bool = True):
+               reuse_buffers: bool = False, local: bool = True, last_position: int | None = None):
         """Read lists [R, top_k + window + sink] int32 and their lengths for queries at `positions`; with
         `local=False` the lists hold the expansion alone (a band kernel reads the window and the sinks)."""
         d, b, dev = self.design, index.buckets, index_queries.device
         R = index_queries.shape[0]
-        picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers)
+        picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers, last_position)
         outs = None
         if reuse_buffers:
             outs = (self._buffer("lists", (R, d.list_width), torch.int32, dev),
@@ -366,7 +388,8 @@ class FlatLayer:
                 self._band_done.record(self._band_stream)
             # The rows of a chunk pick the same buckets over and over: read each bucket's keys once per 128
             # (row, pick) pairs instead of once per pair.
-            picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True)
+            picked, positions, row_p, row_k = self.pick(index_queries, positions, index, reuse_buffers=True,
+                                                        last_position=stop - 1)
             need = _lib.query("lsa_bucket_attend_workspace_bytes", n, self.design.top_p, self.heads, self.head_dim,
                               index.buckets.bucket_members.shape[0])
             with probe.region("attend"):
@@ -378,7 +401,8 @@ class FlatLayer:
                                   workspace=self._buffer("bucket workspace", (need,), torch.uint8, dev))
             return out
         init = self.band(rows, k, v, start) if banded else None
-        lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded)
+        lists, lengths = self.select(index_queries, positions, index, reuse_buffers=True, local=not banded,
+                                     last_position=stop - 1)
         self.attend(rows, k, v, lists, lengths, out=out, lse=lse, init=init)
         return out
 

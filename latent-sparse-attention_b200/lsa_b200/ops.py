@@ -246,6 +246,29 @@ def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: t
     return keys, picked
 
 
+def scan_select(index_queries: torch.Tensor, centroids: torch.Tensor, centroids_bf16: torch.Tensor,
+                visible: torch.Tensor, top_p: int, row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0,
+                max_visible: int = 0, keys: torch.Tensor | None = None, picked: torch.Tensor | None = None,
+                status: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+    """`flat_select`'s result with the scan on tcgen05: bf16 scores in tensor memory against a sampled threshold,
+    an exact fp32 rescoring of the survivors, and an exact scan of whatever row the survivors cannot prove
+    (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836, src/lsa/core/kernels/scan_select.py:189-385).
+    `max_visible` is the host's bound on `visible` (0: all of the centroids)."""
+    q, c, cb = _contig(index_queries.float()), _contig(centroids.float()), _contig(centroids_bf16)
+    R, d = q.shape
+    if cb.dtype != torch.bfloat16 or cb.shape != c.shape:
+        raise ValueError("centroids_bf16 must be the bf16 rounding of centroids")
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64) if keys is None else keys
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32) if picked is None else picked
+    need = query("lsa_scan_select_workspace_bytes", R, top_p, c.shape[0])
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
+    call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), c.shape[0], ptr(_contig(visible.to(torch.int32))),
+         ptr(row_top_p), top_p, bucket_id_base, int(max_visible), ptr(keys), ptr(picked), ptr(status), ptr(workspace),
+         workspace.numel() * workspace.element_size(), stream())
+    return keys, picked
+
+
 def flat_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, request_first: torch.Tensor | None,
                        visible: torch.Tensor, top_p: int, splits: int = 1, workspace: torch.Tensor | None = None):
     """Decode-form flat scan (src/lsa/sglang/index/selector.py:603-660): few rows, their buckets split over CTAs."""
