@@ -5,24 +5,34 @@
 
 namespace lsa {
 
-constexpr int kScanFactor = 4;               // survivors aimed at, in units of top_p
-constexpr float kScanMargin = 1.0f / 128.0f;  // bf16 operands move a score of unit vectors by less than 2^-8: twice that
-constexpr int kScanMinVisible = 1024;         // rows that see fewer buckets take the exact scan (it is cheap there)
+constexpr int kScanRoom = 2048;        // survivors a row can hold over all its lists
+constexpr int kScanMinVisible = 1024;  // rows that see fewer buckets take the exact scan (it is cheap there)
+constexpr int kScanRetry = 64;         // rows a call can hand to the split exact scan; any more take the plain one
+// With both operands rounded to bf16 and fp32 accumulation, a score of a query q against a centroid no longer than 1
+// lies within |q| * (2^-8 + 2^-16) of the fixed-order fp32 dot: kScanEps * |q| bounds that with room to spare.
+constexpr float kScanEps = 1.0f / 240.0f;
+// A list takes every bucket within kScanMargin * |q| below the row's threshold, so that the band the pick has to
+// rescore (2 * kScanEps * |q| below the top_p-th bf16 score) lies inside the lists whenever that score reaches the
+// threshold.
+constexpr float kScanMargin = 1.0f / 64.0f;
 
 struct ScanParams {
   const uint16_t *queries_bf16;    // [rows padded to 128, 64]
   const uint16_t *centroids_bf16;  // [m, 64]
   const int32_t *visible;          // [R]
   const int32_t *row_keep;         // [R] or NULL
-  const int32_t *flags;            // [R]: nonzero = the row takes the exact scan
+  int32_t *flags;                  // [R]: nonzero = the row takes the exact scan (the scan itself flags a row whose
+                                   // samples say that more buckets would reach its bar than the pick has room for)
   const float *norms;              // [R] lengths of the query rows
   const int32_t *tile_visible;     // [rows / 128] the widest visible count among a tile's unflagged rows
-  float *thresholds;               // [R]
-  int32_t *counts;                 // [R, spans] survivors found (past `cap`: the list overflowed)
-  int32_t *survivors;              // [R, spans, cap]
+  float *bars;                     // [R] the score a bucket had to reach to be listed (threshold less the margin)
+  int32_t *counts;                 // [R, lists] survivors found (past `cap`: the list overflowed)
+  int2 *survivors;                 // [R, lists, cap] (bits of the bf16-operand score, bucket); lists = 2 * spans
   int32_t *status;
   int64_t R, m;
   int spans, cap, keep, sample_stride;
+  int factor;  // survivors aimed at, in units of top_p
+  int room;    // survivors of a row the pick has room for
 };
 
 int launch_scan_survivors(const ScanParams &p, int64_t padded_rows, cudaStream_t stream);

@@ -22,8 +22,26 @@ __device__ uint64_t warp_kth_greatest(const int64_t *buf, int n, int k, int *his
   const int lane = lane_id();
   uint64_t prefix = 0, mask = 0;
   int remaining = k;
+  // The leading bytes every key shares (scores of one row lie close together) need no pass: counting them would
+  // send every key to one bin.
+  uint64_t every = ~0ull, any = 0;
+  for (int i = lane; i < n; i += 32) {
+    const uint64_t u = key_radix(buf[i]);
+    every &= u, any |= u;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    every &= __shfl_xor_sync(0xffffffffu, every, o);
+    any |= __shfl_xor_sync(0xffffffffu, any, o);
+  }
+  const uint64_t differ = every ^ any;
   for (int byte = 7; byte >= 0; --byte) {
     const int shift = byte * 8;
+    if ((differ >> shift) == 0) {  // (this byte and all above it are shared)
+      prefix |= every & ((uint64_t)0xFF << shift);
+      mask |= (uint64_t)0xFF << shift;
+      continue;
+    }
 #pragma unroll
     for (int i = 0; i < kHistBins / 32; ++i) hist[lane * (kHistBins / 32) + i] = 0;
     __syncwarp();
@@ -611,10 +629,15 @@ namespace lsa {
 __global__ void __launch_bounds__(128)
     scan_prepare_kernel(const float *__restrict__ queries, const int32_t *__restrict__ visible, int64_t R, int64_t m,
                         uint16_t *__restrict__ q_bf16, float *__restrict__ norms, int32_t *__restrict__ flags,
-                        int32_t *__restrict__ tile_visible) {
+                        int32_t *__restrict__ tile_visible, int keep, int min_visible, int32_t *__restrict__ taken,
+                        int32_t *__restrict__ retry_visible, int32_t *__restrict__ retry_keep) {
   __shared__ int widest_s;
   const int64_t row = (int64_t)blockIdx.x * 128 + threadIdx.x;
   if (threadIdx.x == 0) widest_s = 0;
+  if (blockIdx.x == 0) {  // the split exact scan's row list starts empty, its unused rows seeing nothing
+    if (threadIdx.x == 0) *taken = 0;
+    if (threadIdx.x < kScanRetry) retry_visible[threadIdx.x] = 0, retry_keep[threadIdx.x] = keep;
+  }
   __syncthreads();
   float ss = 0.0f;
   uint32_t packed[32];
@@ -630,7 +653,7 @@ __global__ void __launch_bounds__(128)
   for (int i = 0; i < 8; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
   if (row < R) {
     const int v = min(max(visible[row], 0), (int)m);
-    const bool exact = v < kScanMinVisible || !(ss > 0.0f) || !isfinite(ss);
+    const bool exact = v < min_visible || !(ss > 0.0f) || !isfinite(ss);
     norms[row] = sqrtf(ss);
     flags[row] = exact ? 1 : 0;
     if (!exact) atomicMax(&widest_s, v);
@@ -639,11 +662,13 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x == 0) tile_visible[blockIdx.x] = widest_s;
 }
 
-// After the scan: a warp a row rescores the row's survivors with the exact fixed-order fp32 dot, picks the best
-// `keep` of them, and PROVES the pick: every bucket the scan dropped scored below threshold - margin in bf16, so
-// below the threshold exactly; if the worst pick is at or above the threshold nothing dropped could have displaced
-// it. A row that cannot be proven (too few survivors, an overflowed list, a pick under the threshold) is flagged
-// for the exact scan, which then overwrites it.
+// After the scan: a warp a row. The survivors' bf16-operand scores say which of them can matter: with s the keep-th
+// greatest of them, at least `keep` buckets have a true score of s - eps or more, and a bucket whose bf16 score is
+// under s - 2 eps has a true score under s - eps, so it is not among the best `keep`. Whatever the scan dropped
+// scored under the row's bar, so if s - 2 eps reaches the bar the buckets at or above s - 2 eps are all in the lists:
+// those are rescored with the exact fixed-order fp32 dot and the best `keep` of them are the row's picks, key for
+// key what scoring every bucket would give. A row that cannot be proven - a list overflowed, fewer than `keep`
+// survivors, a band that reaches under the bar - is flagged for an exact scan, which then writes it.
 __global__ void __launch_bounds__(kSelThreads)
     scan_pick_kernel(ScanParams p, const float *__restrict__ queries, const float *__restrict__ centroids,
                      int32_t *__restrict__ flags, int id_base, int room, int64_t *__restrict__ keys_out,
@@ -654,44 +679,57 @@ __global__ void __launch_bounds__(kSelThreads)
   int *hist = reinterpret_cast<int *>(reinterpret_cast<int64_t *>(smem_raw) + (size_t)kSelWarps * room) + warp * kHistBins;
   const int64_t row = (int64_t)blockIdx.x * kSelWarps + warp;
   if (row >= p.R || flags[row]) return;
-  const int visible = min(max(p.visible[row], 0), (int)p.m);
   const int keep = p.row_keep ? min(p.row_keep[row], p.keep) : p.keep;
-  const int need = min(keep, visible);
-  const float *q = queries + row * 64;
+  const int lists = 2 * p.spans;
   int total = 0;
-  bool over = false;
-  for (int span = 0; span < p.spans; ++span) {
-    const int found = p.counts[row * p.spans + span];
-    over |= found > p.cap;
-    const int n = min(found, p.cap);
-    const int32_t *list = p.survivors + (row * p.spans + span) * p.cap;
+  bool proven = true;
+  for (int l = 0; l < lists; ++l) {
+    const int found = p.counts[row * lists + l];
+    proven &= found <= p.cap && total + found <= room;
+    const int n = proven ? found : 0;
+    const int2 *list = p.survivors + (row * lists + l) * p.cap;
     for (int j = lane; j < n; j += 32) {
-      const int32_t id = list[j];
-      const float4 *v4 = reinterpret_cast<const float4 *>(centroids + (int64_t)id * 64);
-      float acc = 0.0f;
-#pragma unroll 4
-      for (int k4 = 0; k4 < 16; ++k4) {
-        const float4 v = __ldg(v4 + k4);
-        const float4 qv = *reinterpret_cast<const float4 *>(q + k4 * 4);
-        acc = fmaf(qv.x, v.x, acc), acc = fmaf(qv.y, v.y, acc), acc = fmaf(qv.z, v.z, acc), acc = fmaf(qv.w, v.w, acc);
-      }
-      buf[total + j] = pack_key(acc, id + id_base);
+      const int2 e = list[j];
+      buf[total + j] = pack_key(__int_as_float(e.x), e.y);
     }
     total += n;
   }
   __syncwarp();
-  bool proven = !over && total >= need;
+  proven &= total >= keep;
   if (keep == 0) total = 0;  // (a row whose budget is nothing)
-  if (proven && total > keep) {
-    const uint64_t kth = warp_kth_greatest(buf, total, keep, hist);
-    total = warp_compact(buf, 0, total, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
-  }
-  if (proven) {
-    warp_sort_descending(buf, total);
-    if (need == keep && keep > 0) {  // (a row that sees fewer buckets than it keeps holds them all already)
-      const int32_t bits = (int32_t)(buf[keep - 1] >> 32);
-      const float worst = __int_as_float(bits < 0 ? (bits ^ 0x7FFFFFFF) : bits);
-      proven = worst >= p.thresholds[row];
+  if (proven && keep > 0) {
+    // the keep-th greatest bf16 score, and the band under it that has to be rescored
+    const uint64_t kth = total > keep ? warp_kth_greatest(buf, total, keep, hist) : 0;
+    int64_t least = INT64_MAX;
+    for (int j = lane; j < total; j += 32)
+      if (key_radix(buf[j]) >= kth) least = min(least, buf[j]);
+    for (int off = 16; off; off >>= 1) least = min(least, __shfl_xor_sync(0xffffffffu, least, off));
+    const int32_t bits = (int32_t)(least >> 32);
+    const float s = __int_as_float(bits < 0 ? (bits ^ 0x7FFFFFFF) : bits);
+    const float low = s - 2.0f * kScanEps * p.norms[row];
+    proven = low >= p.bars[row];
+    if (proven) {
+      const int64_t low_key = pack_key(low, 0x7FFFFFFF);  // (the least key of that score)
+      total = warp_compact(buf, 0, total, 0, [low_key](int64_t key) { return key >= low_key; });
+      const float *q = queries + row * 64;
+      for (int j = lane; j < total; j += 32) {
+        const int32_t id = key_id(buf[j]);
+        const float4 *v4 = reinterpret_cast<const float4 *>(centroids + (int64_t)id * 64);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int k4 = 0; k4 < 16; ++k4) {
+          const float4 v = __ldg(v4 + k4);
+          const float4 qv = *reinterpret_cast<const float4 *>(q + k4 * 4);
+          acc = fmaf(qv.x, v.x, acc), acc = fmaf(qv.y, v.y, acc), acc = fmaf(qv.z, v.z, acc), acc = fmaf(qv.w, v.w, acc);
+        }
+        buf[j] = pack_key(acc, id + id_base);
+      }
+      __syncwarp();
+      if (total > keep) {
+        const uint64_t cut = warp_kth_greatest(buf, total, keep, hist);
+        total = warp_compact(buf, 0, total, 0, [cut](int64_t key) { return key_radix(key) >= cut; });
+      }
+      warp_sort_descending(buf, total);
     }
   }
   if (!proven) {
@@ -705,8 +743,46 @@ __global__ void __launch_bounds__(kSelThreads)
   }
 }
 
+// The rows still flagged after the pick, gathered side by side for an exact scan that splits each row's buckets over
+// many CTAs: at most kScanRetry of them a call (those keep their flag cleared; any more stay flagged for the plain
+// exact scan).
+__global__ void __launch_bounds__(256)
+    scan_collect_kernel(const float *__restrict__ queries, const int32_t *__restrict__ visible,
+                        const int32_t *__restrict__ row_keep, int keep, int64_t R, int64_t m, int32_t *__restrict__ flags,
+                        int32_t *__restrict__ taken, float *__restrict__ q_out, int32_t *__restrict__ visible_out,
+                        int32_t *__restrict__ keep_out, int32_t *__restrict__ row_out) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= R || !flags[row]) return;
+  const int slot = atomicAdd(taken, 1);
+  if (slot >= kScanRetry) return;
+  flags[row] = 0;
+  for (int k = 0; k < 64; k += 4)
+    *reinterpret_cast<float4 *>(q_out + slot * 64 + k) = *reinterpret_cast<const float4 *>(queries + row * 64 + k);
+  visible_out[slot] = min(max(visible[row], 0), (int)m);
+  keep_out[slot] = row_keep ? min(row_keep[row], keep) : keep;
+  row_out[slot] = (int32_t)row;
+}
+
+// ... and their picks written back where they belong.
+__global__ void scan_scatter_kernel(const int64_t *__restrict__ keys_in, const int32_t *__restrict__ row_of,
+                                    const int32_t *__restrict__ keep_of, const int32_t *__restrict__ taken, int keep,
+                                    int64_t *__restrict__ keys_out, int32_t *__restrict__ ids_out) {
+  const int slot = blockIdx.x;
+  if (slot >= min(*taken, kScanRetry)) return;
+  const int64_t row = row_of[slot];
+  const int budget = keep_of[slot];  // (the merge of a row's splits knows the call's top_p, not the row's own)
+  for (int i = threadIdx.x; i < keep; i += blockDim.x) {
+    const int64_t key = i < budget ? keys_in[(int64_t)slot * keep + i] : kEmptyKey;
+    if (keys_out) keys_out[row * keep + i] = key;
+    if (ids_out) ids_out[row * keep + i] = key == kEmptyKey ? LSA_PAD : key_id(key);
+  }
+}
+
+constexpr int kScanRetrySplits = 16;
+
 struct ScanWorkspace {
-  size_t q_bf16, norms, flags, tile_visible, thresholds, counts, survivors, total;
+  size_t q_bf16, norms, flags, tile_visible, thresholds, counts, survivors;
+  size_t taken, retry_q, retry_visible, retry_keep, retry_row, retry_parts, retry_keys, total;
 };
 
 static int scan_spans(int64_t padded_rows, int64_t m) {
@@ -718,10 +794,19 @@ static int scan_spans(int64_t padded_rows, int64_t m) {
   return min(spans, 16);
 }
 
+// Three times top_p survivors are aimed at (twice, from top_p = 512 on, where more would not fit a row's room).
+static int scan_factor(int top_p) { return max(2, min(3, kScanRoom / 2 / top_p)); }
+
+// A list holds four times its even share of the survivors aimed at, so a row whose best buckets crowd into a
+// quarter of its lists still fits; all of a row's lists together stay within kScanRoom.
 static int scan_cap(int top_p, int spans) {
-  const int even = (kScanFactor * top_p + spans - 1) / spans;
-  return max(64, (4 * even + 31) / 32 * 32);
+  const int lists = 2 * spans, aimed = scan_factor(top_p) * top_p;
+  const int cap = max(32, (4 * aimed / lists + 31) / 32 * 32);
+  return min(cap, kScanRoom / lists);
 }
+
+// Survivors of a row the pick has room for: twice those aimed at (a row with more is scanned exactly).
+static int scan_room(int top_p) { return pow2_at_least(max(256, min(2 * scan_factor(top_p) * top_p, kScanRoom))); }
 
 static ScanWorkspace scan_workspace(int64_t R, int top_p, int64_t m) {
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
@@ -734,8 +819,15 @@ static ScanWorkspace scan_workspace(int64_t R, int top_p, int64_t m) {
   w.flags = at, at += up((size_t)R * 4);
   w.tile_visible = at, at += up((size_t)(padded / 128) * 4);
   w.thresholds = at, at += up((size_t)R * 4);
-  w.counts = at, at += up((size_t)R * spans * 4);
-  w.survivors = at, at += up((size_t)R * spans * cap * 4);
+  w.counts = at, at += up((size_t)R * 2 * spans * 4);
+  w.survivors = at, at += up((size_t)R * 2 * spans * cap * 8);
+  w.taken = at, at += 256;
+  w.retry_q = at, at += up((size_t)kScanRetry * 64 * 4);
+  w.retry_visible = at, at += up((size_t)kScanRetry * 4);
+  w.retry_keep = at, at += up((size_t)kScanRetry * 4);
+  w.retry_row = at, at += up((size_t)kScanRetry * 4);
+  w.retry_parts = at, at += up((size_t)kScanRetrySplits * kScanRetry * top_p * 8);
+  w.retry_keys = at, at += up((size_t)kScanRetry * top_p * 8);
   w.total = at;
   return w;
 }
@@ -773,25 +865,32 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   p.flags = flags;
   p.norms = reinterpret_cast<float *>(base + w.norms);
   p.tile_visible = reinterpret_cast<int32_t *>(base + w.tile_visible);
-  p.thresholds = reinterpret_cast<float *>(base + w.thresholds);
+  p.bars = reinterpret_cast<float *>(base + w.thresholds);
   p.counts = reinterpret_cast<int32_t *>(base + w.counts);
-  p.survivors = reinterpret_cast<int32_t *>(base + w.survivors);
+  p.survivors = reinterpret_cast<int2 *>(base + w.survivors);
   p.status = status;
   p.R = R, p.m = m;
   p.spans = lsa::scan_spans(padded, m);
   p.cap = lsa::scan_cap(top_p, p.spans);
   p.keep = top_p;
+  p.factor = lsa::scan_factor(top_p);
+  p.room = lsa::scan_room(top_p);
   const int64_t widest = max_visible > 0 && max_visible < m ? max_visible : m;
   p.sample_stride = (int)((widest + 511) / 512 > 1 ? (widest + 511) / 512 : 1);
+  // The threshold is read off 512 samples of a row's scores: where the buckets a row keeps are too small a share of
+  // those it sees for a handful of samples to reach it, the threshold would be noise, and every row is scanned exactly.
+  const bool sampled = m >= lsa::kScanMinVisible && (int64_t)p.factor * top_p * 512 >= 8 * widest;
+  int32_t *taken = reinterpret_cast<int32_t *>(base + w.taken);
+  int32_t *retry_visible = reinterpret_cast<int32_t *>(base + w.retry_visible);
   lsa::scan_prepare_kernel<<<(unsigned)(padded / 128), 128, 0, s>>>(
       queries, visible, R, m, const_cast<uint16_t *>(p.queries_bf16), const_cast<float *>(p.norms), flags,
-      const_cast<int32_t *>(p.tile_visible));
+      const_cast<int32_t *>(p.tile_visible), top_p, sampled ? lsa::kScanMinVisible : INT32_MAX, taken, retry_visible,
+      reinterpret_cast<int32_t *>(base + w.retry_keep));
   LSA_LAUNCH_CHECK();
-  if (m >= lsa::kScanMinVisible) {
+  if (sampled) {
     int rc = lsa::launch_scan_survivors(p, padded, s);
     if (rc != LSA_OK) return rc;
-    int room = 2;
-    while (room < p.spans * p.cap) room <<= 1;
+    const int room = p.room;
     const size_t smem = (size_t)lsa::kSelWarps * ((size_t)room * 8 + lsa::kHistBins * 4);
     LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
     if (cudaFuncSetAttribute(lsa::scan_pick_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -799,8 +898,39 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
     lsa::scan_pick_kernel<<<(unsigned)((R + lsa::kSelWarps - 1) / lsa::kSelWarps), lsa::kSelThreads, smem, s>>>(
         p, queries, centroids, flags, bucket_id_base, room, keys_out, picked_out);
     LSA_LAUNCH_CHECK();
+    // The rows the pick could not prove (a handful in a thousand): side by side, an exact scan with each row's
+    // buckets split over CTAs, and back.
+    float *retry_q = reinterpret_cast<float *>(base + w.retry_q);
+    int32_t *retry_keep = reinterpret_cast<int32_t *>(base + w.retry_keep);
+    int32_t *retry_row = reinterpret_cast<int32_t *>(base + w.retry_row);
+    int64_t *retry_parts = reinterpret_cast<int64_t *>(base + w.retry_parts);
+    int64_t *retry_keys = reinterpret_cast<int64_t *>(base + w.retry_keys);
+    lsa::scan_collect_kernel<<<(unsigned)((R + 255) / 256), 256, 0, s>>>(queries, visible, row_top_p, top_p, R, m, flags,
+                                                                        taken, retry_q, retry_visible, retry_keep,
+                                                                        retry_row);
+    LSA_LAUNCH_CHECK();
+    lsa::SelectParams sel = {};
+    sel.queries = retry_q;
+    sel.vectors = centroids;
+    sel.run_end = retry_visible;
+    sel.row_keep = retry_keep;
+    sel.keys_out = retry_parts;
+    sel.R = lsa::kScanRetry;
+    sel.N = INT64_MAX;
+    sel.d = 64;
+    sel.keep = top_p;
+    sel.id_base = bucket_id_base;
+    sel.run_limit = INT32_MAX;
+    rc = lsa::launch_select<1>(sel, lsa::kScanRetrySplits, s);
+    if (rc != LSA_OK) return rc;
+    rc = lsa_merge_candidates(retry_parts, lsa::kScanRetrySplits, lsa::kScanRetry, top_p, retry_keys, nullptr, stream);
+    if (rc != LSA_OK) return rc;
+    lsa::scan_scatter_kernel<<<lsa::kScanRetry, 128, 0, s>>>(retry_keys, retry_row, retry_keep, taken, top_p, keys_out,
+                                                             picked_out);
+    LSA_LAUNCH_CHECK();
   }
-  // the exact scan of the rows that are flagged: too few visible buckets, or a pick the survivors could not prove
+  // the plain exact scan of the rows that are still flagged: too few visible buckets, or more unproven rows than
+  // the split scan takes
   lsa::FlatParams f = {};
   f.queries = queries;
   f.centroids = centroids;

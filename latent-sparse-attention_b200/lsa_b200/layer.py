@@ -224,7 +224,7 @@ class FlatLayer:
             ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count, d.bucket_cap, first_position=first,
                              outs=outs)
 
-    scan_rows = 1 << 30  # from this many rows on, a pick runs its scan on the tensor cores
+    scan_rows = 1024  # from this many rows on, a pick runs its scan on the tensor cores
 
     def pick(self, index_queries: torch.Tensor, positions: torch.Tensor, index: FlatIndex,
              reuse_buffers: bool = False, last_position: int | None = None):

@@ -366,11 +366,12 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
     return selected, lengths, status
 
 
-def expand_batched(picked: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor, members: torch.Tensor,
+def expand_batched(picked: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor | None,
+                   members: torch.Tensor,
                    bucket_pages: torch.Tensor | None, bucket_page_rows: int, kv_pages: torch.Tensor | None,
                    kv_page_size: int, top_k: int, sink: int, window: int, local: bool = True):
     """Expansion for a batch of requests over one paged cache (src/lsa/core/kernels/expansion.py:16-58): row r is a
-    query of request row_request[r] at its own position; picks are the request's logical bucket ids, read through
+    query of request row_request[r] (None: request 0) at its own position; picks are the request's logical bucket ids, read through
     `bucket_pages` [requests, pages]; ids are written as KV slots through `kv_pages` [requests, pages]."""
     picked, members = _contig(picked), _contig(members)
     R, top_p = picked.shape
@@ -381,7 +382,8 @@ def expand_batched(picked: torch.Tensor, positions: torch.Tensor, row_request: t
     kv_pages = None if kv_pages is None else _contig(kv_pages.to(torch.int32))
     call("lsa_expand_batched", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
          members.shape[0], members.shape[1], None, None, top_k, sink, window, ptr(kv_pages), kv_page_size, 0,
-         _lib.INT64_MAX, 1, 1, 0, 0 if local else 1, ptr(_contig(row_request.to(torch.int32))),
+         _lib.INT64_MAX, 1, 1, 0, 0 if local else 1,
+         ptr(None if row_request is None else _contig(row_request.to(torch.int32))),
          kv_pages.shape[1] if kv_pages is not None else 0, ptr(bucket_pages),
          bucket_pages.shape[1] if bucket_pages is not None else 0,
          bucket_pages.shape[1] if bucket_pages is not None else 0, bucket_page_rows, ptr(selected), ptr(lengths),

@@ -34,20 +34,60 @@ class BucketCache:
         self.members = torch.full((rows, design.bucket_cap), -1, device=device, dtype=torch.int32)
         self.sizes = torch.zeros(rows, device=device, dtype=torch.int32)
         self.request_pages = torch.full((max_requests, max_request_pages), -1, device=device, dtype=torch.int32)
+        # Buckets each request holds, where a captured decode step can read it
+        self.bucket_counts = torch.zeros(max_requests, device=device, dtype=torch.int32)
         self.free_pages = list(range(pages - 1, -1, -1))
         self.held: dict[int, list] = {}      # request -> its pages, in order
         self.closed_keys: dict[int, int] = {}  # request -> keys of its closed cluster blocks
         self.pending: dict[int, torch.Tensor] = {}  # request -> index keys of its open block
+        self.owner: dict[int, object] = {}   # request table row -> the id of the request that holds it
 
     def buckets_of(self, request: int) -> int:
         return self.closed_keys.get(request, 0) // self.design.bucket_size
+
+    def end(self, request: int) -> int:
+        """Keys of the request the cache has taken: its closed cluster blocks and the open one."""
+        held = self.pending.get(request)
+        return self.closed_keys.get(request, 0) + (0 if held is None else held.shape[0])
 
     def release(self, request: int) -> None:
         """Give a finished request's pages back."""
         self.free_pages.extend(reversed(self.held.pop(request, [])))
         self.closed_keys.pop(request, None)
         self.pending.pop(request, None)
+        self.owner.pop(request, None)
         self.request_pages[request].fill_(-1)
+        self.bucket_counts[request] = 0
+
+    def ensure(self, request: int, rid: object) -> None:
+        """Start a row of the request table afresh when another request has taken it (bucket_cache.py:228-262)."""
+        if self.owner.get(request, rid) != rid or (request not in self.owner and self.end(request)):
+            self.release(request)
+        self.owner[request] = rid
+
+    def advance(self, request: int, end: int, index_keys_of) -> int:
+        """Bring the request up to `end` keys: the index keys of the positions the cache has not seen come from
+        `index_keys_of(first, stop)` [stop - first, index_dim] fp32 (bucket_cache.py:380-441). Returns the cluster
+        blocks closed.
+
+        Raises:
+            ValueError: The cache already holds keys past `end` (a request cut short keeps no index).
+        """
+        have = self.end(request)
+        if end < have:
+            raise ValueError(f"request {request} holds {have} keys in its index and the pool {end}")
+        return self.append(request, index_keys_of(have, end)) if end > have else 0
+
+    def rows_of(self, request: int, logical: torch.Tensor) -> torch.Tensor:
+        """Rows of the device tables that hold a request's logical buckets."""
+        return self.request_pages[request][logical // self.page_buckets].long() * self.page_buckets + \
+            logical % self.page_buckets
+
+    def gather(self, request: int, buckets: int) -> torch.Tensor:
+        """The centroids of a request's first `buckets` buckets, side by side [buckets, index_dim] fp32
+        (bucket_cache.py:560-601)."""
+        logical = torch.arange(buckets, device=self.centroids.device)
+        return self.centroids[self.rows_of(request, logical)]
 
     def _grow(self, request: int, buckets: int) -> None:
         pages = self.held.setdefault(request, [])
@@ -87,21 +127,100 @@ class BucketCache:
             labels, _ = ops.ward_rounds(pools, float(d.pool_size), per_block, d.bucket_cap)
             members, sizes, _, centroids, _, _ = ops.bucket_table(block_keys, labels, d.pool_size, per_block,
                                                                   d.bucket_cap, first_position=first_position)
-        logical = first_bucket + torch.arange(blocks * per_block, device=members.device)
-        rows = self.request_pages[request][logical // self.page_buckets].long() * self.page_buckets + \
-            logical % self.page_buckets
+        rows = self.rows_of(request, first_bucket + torch.arange(blocks * per_block, device=members.device))
         self.centroids[rows] = centroids
         self.members[rows] = members
         self.sizes[rows] = sizes
         self.closed_keys[request] = first_position + closed
+        self.bucket_counts[request] = first_bucket + blocks * per_block
         return blocks
 
 
 class Selector:
     """Routes a batch's reads over a `BucketCache` (selector.py:107-700), flat design."""
 
-    def __init__(self, cache: BucketCache, kv_page_size: int):
-        self.cache, self.kv_page_size = cache, kv_page_size
+    scan_rows = 1024  # from this many rows on, a prefill segment's scan runs on the tensor cores
+
+    def __init__(self, cache: BucketCache, kv_page_size: int = 1, slot_table=None):
+        """`slot_table()` returns the request table [requests, context / kv_page_size] int32 that maps a request's
+        positions to KV slots (an engine's `req_to_token` has pages of one token); `prefill` and `decode` read
+        through it, `decode_flat` is handed a batch's own table."""
+        self.cache, self.kv_page_size, self.slot_table = cache, kv_page_size, slot_table
+
+    def maintain(self, rids, rows, ends, index_keys_of) -> int:
+        """Bring each request's cache up to the keys already in the KV pool - eagerly, before every forward
+        (selector.py:162-197). `index_keys_of(row)` returns the row's lookup (first, stop) -> index keys. Returns
+        the cluster blocks closed."""
+        closed = 0
+        for rid, row, end in zip(rids, rows, ends, strict=True):
+            self.cache.ensure(row, rid)
+            closed += self.cache.advance(row, end, index_keys_of(row))
+        return closed
+
+    def prefill(self, row: int, index_queries: torch.Tensor, positions: torch.Tensor, index_keys: torch.Tensor,
+                query_start: int, local: bool = True) -> torch.Tensor:
+        """Read a prefill segment of one request: append its keys, select for its queries (selector.py:199-287).
+
+        The keys go into the cache in one call and every query reads the buckets its own position sees - those of
+        the cluster blocks closed before it - which is what it would have seen had the cache grown a page at a time,
+        so nothing is cut at page ends.
+
+        Args:
+            row: The request table row.
+            index_queries: The segment's index queries [S, index_dim] fp32 unit rows.
+            positions: Their positions [S], consecutive from `query_start`.
+            index_keys: The index keys the cache appends [S', index_dim] fp32, from the cache's end (S' >= S where
+                the segment's keys reach back before its first query).
+            query_start: Position of the first query, from the scheduler: no device read.
+
+        Returns:
+            KV slots [S, width] int32, -1 padded, valid entries first.
+
+        Raises:
+            ValueError: The keys do not reach the last query.
+        """
+        cache, d = self.cache, self.cache.design
+        S, dev = index_queries.shape[0], index_queries.device
+        cache.append(row, index_keys)
+        if cache.end(row) < query_start + S:
+            raise ValueError(f"request {row}'s index ends at key {cache.end(row)} and its queries at {query_start + S}")
+        if not S:
+            return torch.empty(0, d.list_width, device=dev, dtype=torch.int32)
+        last = query_start + S - 1
+        seen = min(last // d.cluster_block_size * d.block_bucket_count, cache.buckets_of(row))
+        positions = positions.to(torch.int64)
+        visible = (positions // d.cluster_block_size * d.block_bucket_count).clamp_max(seen).to(torch.int32)
+        with probe.region("index q scan"):
+            centroids = cache.gather(row, seen)
+            if S >= self.scan_rows and centroids.shape[1] == 64 and d.top_p <= 512:
+                _, picked = ops.scan_select(index_queries, centroids, centroids.bfloat16(), visible, d.top_p,
+                                            max_visible=seen)
+            else:
+                _, picked = ops.flat_select(index_queries, centroids, visible, d.top_p)
+        with probe.region("expand"):
+            table = self.slot_table()
+            lists, _, _ = ops.expand_batched(picked, positions, None, cache.members, cache.request_pages[row:row + 1],
+                                             cache.page_buckets, table[row:row + 1], self.kv_page_size, d.top_k,
+                                             d.sink_size, d.window_size, local=local)
+        return lists
+
+    def decode(self, index_queries: torch.Tensor, positions: torch.Tensor, rows: torch.Tensor, splits: int = 4,
+               local: bool = True) -> torch.Tensor:
+        """One query a request, read through the request table: KV slots [B, width] int32 (selector.py:603-700).
+        Fixed shapes and no host read, so a step can be captured in a CUDA graph."""
+        cache, d = self.cache, self.cache.design
+        rows = rows.long()
+        positions = positions.to(torch.int64)
+        visible = torch.minimum(positions // d.cluster_block_size * d.block_bucket_count,
+                                cache.bucket_counts[rows].long()).to(torch.int32)
+        with probe.region("index q scan"):
+            _, picked = ops.flat_select_paged(index_queries, cache.centroids, cache.request_pages[rows], visible,
+                                              cache.page_buckets, d.top_p, splits=splits)
+        with probe.region("expand"):
+            lists, _, _ = ops.expand_batched(picked, positions, rows.to(torch.int32), cache.members,
+                                             cache.request_pages, cache.page_buckets, self.slot_table(),
+                                             self.kv_page_size, d.top_k, d.sink_size, d.window_size, local=local)
+        return lists
 
     def visible(self, request_rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """Buckets each row sees: those of the cluster blocks closed before its own, that the cache holds."""

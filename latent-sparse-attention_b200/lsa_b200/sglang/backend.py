@@ -13,22 +13,22 @@ are the engine's own; only these attributes are read:
 from __future__ import annotations
 
 import inspect
-from dataclasses import dataclass
 from typing import Any, Callable
 
 import torch
 
 from lsa_b200 import ops
 from lsa_b200.constants import Sentinel
+from lsa_b200.sglang import index_space, weights
+from lsa_b200.sglang.layer_index import LayerIndex, Shard
+from lsa_b200.sglang.settings import DesignSettings
 
+# Every quadratic layer's indexer, built by the first backend enabled: one index a layer, however many backends read it
+ENABLED: dict = {}
 
-@dataclass(frozen=True)
-class Shard:
-    """Which KV slots a rank of a decode group owns: slot s lives on rank s % size at row s // size
-    (`src/lsa/sglang/index/layer_index.py:65-87`)."""
-
-    rank: int = 0
-    size: int = 1
+# Request table row of each request id, so a decode step finds its rows without a device read
+ROWS: dict = {}
+ROWS_KEPT = 4096
 
 
 def list_lengths(lists: torch.Tensor) -> torch.Tensor:
@@ -109,6 +109,131 @@ def group_read(backend: Any, q: torch.Tensor, layer: Any, lists: torch.Tensor, s
     return merge(out, lse).to(q.dtype).reshape(q.shape[0], -1)
 
 
+class GroupedQueryIndexer:
+    """One quadratic layer's index, built on its first use once the model and the KV pool exist
+    (`src/lsa/sglang/models/qwen3_5/backend.py:81-217`). Of the backend these are read: `req_to_token`
+    [requests, context] int32 and `token_to_kv_pool` (`size`, `page_size`, `get_key_buffer(layer_id)`); of a forward
+    batch: `forward_mode`, `positions`, `out_cache_loc`, `req_pool_indices`, `rids`, `seq_lens_cpu`,
+    `extend_seq_lens_cpu`, `extend_prefix_lens_cpu`, and `lsa_rows`, which `maintain_all` puts there."""
+
+    is_lsa = True
+
+    def __init__(self, layer_id: int, geometry: index_space.Geometry, design: DesignSettings, backend: Any,
+                 shard: Shard | None = None, heads: index_space.HeadShard | None = None,
+                 prefill_chunk: int = 8192, maps: tuple | None = None) -> None:
+        """`maps` = (query map, key map) skips the map file (tests, a server that holds the maps already)."""
+        if heads is not None or (shard is not None and shard.size > 1):
+            raise NotImplementedError("this build indexes a grouped-query layer on a rank that holds every key head "
+                                      "and every KV slot")
+        self.layer, self.geometry, self.design, self.backend = layer_id, geometry, design, backend
+        self.shard, self.heads, self.prefill_chunk, self.maps = shard or Shard(), heads, prefill_chunk, maps
+        self.index: LayerIndex | None = None
+
+    def request_table(self) -> torch.Tensor:
+        return self.backend.req_to_token
+
+    def key_buffer(self) -> torch.Tensor:
+        """This layer's key cache [slots, Hkv, dh] bf16.
+
+        Raises:
+            NotImplementedError: The KV cache is not bf16, so its keys are not the ones the maps were distilled on.
+        """
+        buffer = self.backend.token_to_kv_pool.get_key_buffer(self.layer)
+        if buffer.dtype != torch.bfloat16:
+            raise NotImplementedError(f"the key and query input reads a bf16 KV cache - this one is {buffer.dtype}, "
+                                      "serve kv_cache_dtype auto")
+        return buffer.view(-1, self.geometry.kv_head_count, self.geometry.head_dim)
+
+    def ready(self) -> LayerIndex:
+        """Build the layer's index once, and return it."""
+        if self.index is None:
+            table, pool = self.request_table(), self.backend.token_to_kv_pool
+            maps = self.maps
+            if maps is None:
+                maps = weights.read(self.design.serving.projections, self.geometry.key_dim,
+                                    self.design.indexer.index_dim, self.geometry.layers)[self.layer]
+            self.index = LayerIndex(self.design, maps, pool.size + pool.page_size, pool.size, self.request_table,
+                                    table.shape[1], self.prefill_chunk, table.device, self.shard,
+                                    key_buffer=self.key_buffer, key_slot=self.geometry.key_slot)
+            self.index.writes_pool = False  # `select_and_read` saves a forward's keys before it selects
+        return self.index
+
+    def maintain(self, forward_batch: Any) -> None:
+        """Bring each request's cache up to the tokens already in the KV pool, before every forward."""
+        rows = forward_batch.lsa_rows
+        self.ready().maintain(forward_batch.rids, rows, ends_of(forward_batch, len(rows)))
+
+    def select(self, q: torch.Tensor, k: torch.Tensor, forward_batch: Any) -> torch.Tensor:
+        """Select for every query of a forward, from the heads attention was handed: q [T, Hq * dh] or [T, Hq, dh]
+        rotated on the prefix alone, k [T, Hkv, dh] the same, already in the pool at `out_cache_loc`. Returns KV
+        slots [T, width] int32, -1 padded, valid entries first."""
+        index = self.ready()
+        inputs = index_space.key_and_query(q, k, self.geometry, self.heads)
+        positions, slots = forward_batch.positions, forward_batch.out_cache_loc.long()
+        if forward_batch.forward_mode.is_extend():
+            return index.extend(inputs, positions, slots, forward_batch.lsa_rows, forward_batch.extend_seq_lens_cpu,
+                                forward_batch.extend_prefix_lens_cpu)
+        return index.decode(inputs, positions, slots, forward_batch.req_pool_indices.long())
+
+
+def rows_of(forward_batch: Any) -> list:
+    """Request table rows of the batch: one device read a prefill, none in decode, where they are looked up by
+    request id (`src/lsa/sglang/index/registry.py:42-66`)."""
+    rids = forward_batch.rids
+    if not forward_batch.forward_mode.is_extend() and all(rid in ROWS for rid in rids):
+        return [ROWS[rid] for rid in rids]
+    rows = forward_batch.req_pool_indices.tolist()
+    ROWS.update(zip(rids, rows))
+    if len(ROWS) > 4 * len(rows) + ROWS_KEPT:  # finished requests never come back: keep the map small
+        for rid in list(ROWS)[: len(ROWS) // 2]:
+            del ROWS[rid]
+    return rows
+
+
+def ends_of(forward_batch: Any, request_count: int) -> list:
+    """Keys each real request has in the pool before this forward's own (`registry.py:69-86`); a decode batch
+    replayed in a CUDA graph is padded, so its length lists run past the requests."""
+    seq_lens = forward_batch.seq_lens_cpu.tolist()[:request_count]
+    if forward_batch.forward_mode.is_extend():
+        lengths = list(forward_batch.extend_seq_lens_cpu)[:request_count]
+    else:
+        lengths = [1] * request_count
+    return [seq_len - length for seq_len, length in zip(seq_lens, lengths, strict=True)]
+
+
+def maintain_all(backend: Any, forward_batch: Any) -> None:
+    """Put the request table rows on the batch and run every indexer's maintenance (`registry.py:89-100`).
+
+    Raises:
+        RuntimeError: The batch carries no request ids.
+    """
+    indexers = getattr(backend, "lsa_indexers", None)
+    if not indexers or getattr(forward_batch.forward_mode, "is_idle", lambda: False)():
+        return
+    if getattr(forward_batch, "rids", None) is None:
+        raise RuntimeError("LSA maintenance needs request ids on the forward batch")
+    forward_batch.lsa_rows = rows_of(forward_batch)
+    for indexer in indexers.values():
+        indexer.maintain(forward_batch)
+
+
+def enable(backend: Any, runner: Any, design: DesignSettings) -> dict:
+    """Give a grouped-query server's attention backend an indexer for every quadratic layer
+    (`models/qwen3_5/backend.py:305-347`). A backend built for another model or a draft is left as it was; a second
+    backend of the same server reads the indexers the first one built, since the pools they index are the runner's."""
+    text = runner.model_config.hf_text_config
+    if getattr(backend, "is_draft_runner", False) or not index_space.is_grouped_query(text):
+        return {}
+    if not ENABLED:
+        geometry = index_space.geometry_of(text)
+        if design.indexer.index_dim not in (16, 32, 64, 128):
+            raise NotImplementedError(f"the index kernels take an index of 16, 32, 64 or 128 dims - the design's is "
+                                      f"{design.indexer.index_dim}")
+        ENABLED.update({layer: GroupedQueryIndexer(layer, geometry, design, backend) for layer in geometry.layers})
+    backend.lsa_indexers = ENABLED
+    return ENABLED
+
+
 def bind(original: Any, *args: Any, **kwargs: Any) -> inspect.BoundArguments:
     """The arguments of a wrapped call by name, defaults filled (plugin.py:634-647)."""
     bound = inspect.signature(original).bind(*args, **kwargs)
@@ -119,7 +244,9 @@ def bind(original: Any, *args: Any, **kwargs: Any) -> inspect.BoundArguments:
 def indexer_of(backend: Any, layer: Any, forward_batch: Any):
     """The layer's indexer, or None for a layer LSA does not serve."""
     indexers = getattr(backend, "lsa_indexers", None)
-    return None if indexers is None else indexers.get(layer.layer_id)
+    if not indexers or forward_batch is None or getattr(forward_batch.forward_mode, "is_idle", lambda: False)():
+        return None
+    return indexers.get(layer.layer_id)
 
 
 def save(backend: Any, layer: Any, k: torch.Tensor, v: torch.Tensor, forward_batch: Any, shard: Shard) -> None:

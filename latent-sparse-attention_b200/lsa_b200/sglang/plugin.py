@@ -72,19 +72,32 @@ def _registry(registry=None):
 
 
 def enable(result: None, self: Any, *args: Any, **kwargs: Any) -> None:
-    """AFTER hook of an attention backend's `__init__`: give the backend its per-layer indexers."""
+    """AFTER hook of an attention backend's `__init__`: give the backend an indexer for every quadratic layer of a
+    grouped-query model, built from the design the model config named (`models/qwen3_5/backend.py:305-347`).
+
+    Raises:
+        TypeError: The backend was built without a model runner.
+    """
+    runner = kwargs.get("model_runner", args[0] if args else None)
+    if runner is None:
+        raise TypeError("the attention backend was built without a model runner")
     if not hasattr(self, "lsa_indexers"):
         self.lsa_indexers = {}
+    design = ENABLED.get("design")
+    if design is not None:
+        backend.enable(self, runner, design)
 
 
 def maintain(*args: Any, **kwargs: Any) -> None:
-    """BEFORE hook of `init_forward_metadata`: the index's host-side upkeep of a step (page allocation for keys
-    that arrived) runs here, outside any captured graph (plugin.py:491-522)."""
+    """BEFORE hook of `init_forward_metadata` and of `init_forward_metadata_out_graph`: the index's host-side upkeep
+    of a step - the clustering of blocks that closed, page allocation - runs here, before the forward and outside
+    any captured graph (plugin.py:491-522)."""
     backend_object = args[0] if args else kwargs.get("self")
-    for indexer in getattr(backend_object, "lsa_indexers", {}).values():
-        upkeep = getattr(indexer, "maintain", None)
-        if upkeep is not None:
-            upkeep(*args[1:], **kwargs)
+    forward_batch = kwargs.get("forward_batch", args[1] if len(args) > 1 else None)
+    in_capture = kwargs.get("in_capture", args[2] if len(args) > 2 else False)
+    if forward_batch is None or in_capture or not getattr(backend_object, "lsa_indexers", None):
+        return
+    backend.maintain_all(backend_object, forward_batch)
 
 
 def enable_lsa(design: DesignSettings, registry=None, targets: tuple = GROUPED_QUERY_TARGETS) -> int:

@@ -110,6 +110,64 @@ def test_select_and_read_hands_unserved_calls_back_untouched():
         backend.select_and_read(forward_decode, engine, 1, 2, 3, layer, types.SimpleNamespace(forward_mode=mode))
 
 
+def test_the_map_file_reader_refuses_what_is_not_the_models(tmp_path):
+    from lsa_b200.sglang import weights
+
+    good = {f"{layer}.{kind}": torch.randn(192, 64) for layer in (3, 7, 9) for kind in (weights.QUERY, weights.KEY)}
+    path = tmp_path / "maps.pt"
+    torch.save(good, path)
+    maps = weights.read(path, 192, 64, [3, 7])
+    assert sorted(maps) == [3, 7] and maps[3][0].dtype == torch.float32 and torch.equal(maps[7][1], good["7.W_K_idx"])
+    for bad, match in (({**good, "extra": torch.zeros(1)}, "projection file holds"),
+                       ({k: v for k, v in good.items() if k != "7.W_K_idx"}, "only one of"),
+                       ({k: v for k, v in good.items() if not k.startswith("7.")}, "missing"),
+                       ({**good, "3.W_Q_idx": torch.randn(64, 192)}, "expected"), ({}, "not a projection file")):
+        torch.save(bad, path)
+        with pytest.raises(ValueError, match=match):
+            weights.read(path, 192, 64, [3, 7])
+
+
+def test_a_grouped_query_checkpoints_geometry_and_the_heads_a_rank_holds():
+    from lsa_b200.sglang import index_space as space
+
+    published = types.SimpleNamespace(text_config=types.SimpleNamespace(
+        num_attention_heads=24, num_key_value_heads=4, head_dim=256, rope_parameters={"partial_rotary_factor": 0.25},
+        layer_types=["linear_attention"] * 3 + ["full_attention"], num_hidden_layers=4))
+    served = types.SimpleNamespace(num_attention_heads=24, num_key_value_heads=4, head_dim=256,
+                                   partial_rotary_factor=0.25, num_hidden_layers=8, full_attention_interval=4)
+    geometry = space.geometry_of(published)
+    assert (geometry.rotary_dim, geometry.key_dim, geometry.layers) == (64, 768, (3,))
+    assert space.geometry_of(served).layers == (3, 7) and space.is_grouped_query(served)
+    assert not space.is_grouped_query(types.SimpleNamespace(kv_lora_rank=512, layer_types=["full_attention"]))
+    with pytest.raises(ValueError, match="nothing is position-free"):
+        space.rotary_dim_of(types.SimpleNamespace(head_dim=128, partial_rotary_factor=1.0))
+    with pytest.raises(ValueError, match="nothing to index"):
+        space.quadratic_layers(types.SimpleNamespace(layer_types=["linear_attention"]))
+    slot = geometry.key_slot
+    assert (slot.heads, slot.offset, slot.width) == (4, 64, 192)
+    with pytest.raises(ValueError, match="does not fit"):
+        space.KeySlot(heads=1, head_dim=64, offset=32, width=48)
+    pool = torch.arange(5 * 4 * 256, dtype=torch.float32).view(5, 4, 256)
+    read = slot.read(pool, torch.tensor([1, 3]))
+    assert read.shape == (2, 768) and torch.equal(read[0, 192:384], pool[1, 1, 64:])
+    slot.write(pool, torch.tensor([0]), torch.zeros(1, 768))
+    assert not pool[0, :, 64:].any() and pool[0, :, :64].any()
+    # tensor parallel: the key heads dealt in order, a head replicated once the ranks outnumber them
+    assert space.head_shard(geometry, 1, 0) is None and space.head_shard(geometry, 4, 1, decode_size=4) is None
+    assert space.head_shard(geometry, 2, 1) == space.HeadShard(2, 2, 12, True)
+    eight = [space.head_shard(geometry, 8, rank) for rank in range(8)]
+    assert [(s.kv_first, s.counts_key) for s in eight[:4]] == [(0, True), (0, False), (1, True), (1, False)]
+    assert sum(s.counts_key for s in eight) == 4 and eight[5].dims(geometry) == (384, 576)
+    for size, decode in ((3, 1), (5, 1), (16, 1), (8, 2)):
+        with pytest.raises(NotImplementedError):
+            space.head_shard(geometry, size, 0, decode)
+    q, k = torch.randn(6, 24 * 256), torch.randn(6, 4, 256)
+    written = space.materialise(space.key_and_query(q, k, geometry), geometry)
+    assert written.key.shape == (6, 768) and written.query.shape == (6, 1, 768) and written.query.dtype == torch.float32
+    want = q.view(6, 4, 6, 256)[..., 64:].sum(2).reshape(6, 768)
+    assert torch.allclose(written.query[:, 0], want, atol=1e-5)
+
+
 def test_lists_split_over_a_decode_group_hold_every_slot_once():
     lists = torch.tensor([[5, 2, 9, 4, -1, -1], [7, -1, -1, -1, -1, -1]], dtype=torch.int32)
     assert backend.list_lengths(lists).tolist() == [4, 1]
