@@ -182,15 +182,36 @@ int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroi
  * Reference: the Blackwell bucket scan (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836), its
  * sampled thresholds (src/lsa/core/kernels/scan_select.py:228-271) and ScanSelect's exact rescoring
  * (src/lsa/core/kernels/scan_select.py:189-385).
- *   centroids_bf16 [m, 64] the bf16 rounding of centroids (lsa_bucket_table's centroids_bf16); d = 64, top_p <= 512
+ *   centroids_bf16 [m, 64] the scan's N operand: the centroids LESS A COMMON CENTRE, rounded to bf16 - a query's
+ *                score against the centre is the same for every bucket, so the ranking is the centroids' own, and
+ *                the bf16 error shrinks with the rows' length. lsa_scan_centre makes it, a run of rows at a time
+ *                as an index grows: centre [64] fp32 or NULL (none), radius [1] fp32 zeroed once by the caller and
+ *                raised to the greatest length of a row it wrote. d = 64, top_p <= 512
+ *   radius       [1] fp32 on the device, at least the length of every row of centroids less the centre; NULL = 1
+ *                (centroids no longer than 1 and no centre: the plain bf16 rounding of lsa_bucket_table)
  *   max_visible  the host's bound on visible[] (<= 0: m) - it sets how far apart the samples lie
  *   status       (may be NULL) raised if a bounded on-chip wait gives up; the rows it cut are scanned exactly
  *   workspace    lsa_scan_select_workspace_bytes(R, top_p, m), 256-byte aligned */
+int lsa_scan_centre(const float *centroids, int64_t rows, int d, const float *centre, uint16_t *out_bf16,
+                    float *radius, void *stream);
 size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m);
 int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids, const uint16_t *centroids_bf16,
-                    int64_t m, const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                    const float *radius, int64_t m, const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
                     int max_visible, int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
                     size_t workspace_bytes, void *stream);
+
+/* Every (row, bucket) score written out, each at its own column: what the reference's two-pass selection hands from
+ * its scoring to its pick (dense_keys, src/lsa/core/kernels/scan_select.py:24-58; scan_paged,
+ * src/lsa/core/kernels/triton/paged.py:61-101). The selection entry points above never write this matrix; it is here
+ * for callers written against the two-pass form.
+ *   queries [R, d] fp32; centroids [*, d] fp32; counts [R] int32 - buckets row r holds (columns past it are empty)
+ *   pages [R, max_pages] int32 or NULL - row r's logical bucket i is row i % page_rows of page pages[r, i / page_rows]
+ *         (-1 = no page: empty); NULL = bucket i is row i of centroids
+ *   scores_out [R, width] fp32 or NULL (-inf where empty); keys_out [R, width] int64 or NULL (packed with the column
+ *         + bucket_id_base, LSA_EMPTY_KEY where empty). Scores are fp32 dots added in ascending dim order. */
+int lsa_dense_scores(const float *queries, int64_t R, int d, const float *centroids, const int32_t *pages,
+                     int max_pages, int page_rows, const int32_t *counts, int64_t width, int32_t bucket_id_base,
+                     float *scores_out, int64_t *keys_out, void *stream);
 
 /* Flat search, decode form: few rows, many buckets. The buckets of a row are split over `splits` CTAs whose
  * local top_p lists are merged by a second kernel. Reference: Selector.decode_flat
@@ -253,7 +274,8 @@ int lsa_beam_step_split(const float *queries, int64_t R, int d, const float *vec
  * (src/lsa/core/reference.py:268-289), budget_at (src/lsa/budget.py:60-74); served expand_in_order
  * (src/lsa/core/kernels/expansion.py:16-58).
  *   picked     [R, top_p] int32 bucket rows, best first, -1 = none
- *   positions  [R] int64; members [m, bucket_cap] int32
+ *   positions  [R] int64; members [m, bucket_cap] int32, ASCENDING within a bucket and -1 padded at the end (as
+ *              lsa_bucket_table writes them): a bucket's row is read up to its first padding or member inside the window
  *   row_top_p / row_top_k [R] int32 or NULL - a row's own budget
  *   page_table [pages] int32 or NULL with page_size - when given every id is stored as the KV slot
  *              page_table[id / page_size] * page_size + id % page_size instead of the position

@@ -71,8 +71,9 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
   int written = 0;  // ids this owner keeps
   int bad = 0;
   // The picks are read 32 at a time, a lane a pick (so no load waits on the one before), and a bucket's member
-  // chunks four at a time: the loads of a group are in flight together, only the counting is in order.
-  const int chunks = (p.cap + 31) / 32;
+  // chunks four at a time: the loads of a group are in flight together, only the counting is in order. A bucket's
+  // members ascend and its row ends in padding, so the first chunk that holds padding or a member inside the window
+  // is the last one of the bucket that can count: the rest of its row (half of it, on average) is never read.
   for (int i0 = 0; i0 < row_p && counted < row_k; i0 += 32) {
     int64_t my_bucket = -1;
     if (i0 + lane < row_p) {
@@ -89,27 +90,31 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
       }
     }
     const int picks = min(32, row_p - i0);
-    const int segments = picks * chunks;
-    for (int s0 = 0; s0 < segments && counted < row_k; s0 += 4) {
-      int32_t ids[4];
+    for (int pick = 0; pick < picks && counted < row_k; ++pick) {
+      const int64_t bucket = __shfl_sync(0xffffffffu, my_bucket, pick);
+      if (bucket < 0) continue;
+      const int32_t *row = p.members + bucket * p.cap;
+      bool ended = false;
+      for (int at0 = 0; at0 < p.cap && !ended && counted < row_k; at0 += 128) {
+        int32_t ids[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int seg = s0 + j;
-        const int pick = seg / chunks, at = (seg - pick * chunks) * 32 + lane;
-        const int64_t bucket = __shfl_sync(0xffffffffu, my_bucket, pick & 31);
-        ids[j] = seg < segments && bucket >= 0 && at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
-      }
+        for (int j = 0; j < 4; ++j) {
+          const int at = at0 + 32 * j + lane;
+          ids[j] = at < p.cap ? row[at] : LSA_PAD;
+        }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int32_t id = ids[j];
-        const bool counts = id >= p.sink && id < window_start;
-        const unsigned votes = __ballot_sync(0xffffffffu, counts);
-        const bool inside = counts && counted + __popc(votes & below) < row_k;
-        const bool mine = inside && owned(p, id);
-        const unsigned keeps = __ballot_sync(0xffffffffu, mine);
-        if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, id);
-        written += __popc(keeps);
-        counted += __popc(votes);
+        for (int j = 0; j < 4; ++j) {
+          const int32_t id = ids[j];
+          const bool counts = id >= p.sink && id < window_start;
+          const unsigned votes = __ballot_sync(0xffffffffu, counts);
+          const bool inside = counts && counted + __popc(votes & below) < row_k;
+          const bool mine = inside && owned(p, id);
+          const unsigned keeps = __ballot_sync(0xffffffffu, mine);
+          if (mine) out[written + __popc(keeps & below)] = stored_id(p, table, id);
+          written += __popc(keeps);
+          counted += __popc(votes);
+          ended |= __any_sync(0xffffffffu, id < 0 || id >= window_start);
+        }
       }
     }
   }

@@ -240,19 +240,39 @@ __global__ void __launch_bounds__(kLinThreads)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint16_t *xs = reinterpret_cast<uint16_t *>(smem_raw);  // [rows][K] bf16
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int e = tid; e < rows * K; e += kLinThreads) {
-    const int r = e / K, k = e - r * K;
-    const uint16_t *src = x + (int64_t)r * x_row_stride + k;
-    float sum = 0.0f;
-    for (int h0 = 0; h0 < heads; h0 += 8) {  // eight loads in flight, added in head order
-      uint16_t v[8];
+  // the head sum: a thread a pair of dims, 32 heads' loads in flight at a time, added in head order
+  const bool pairs = (K % 2 == 0) && (x_row_stride % 2 == 0) && (x_head_stride % 2 == 0) && ((uintptr_t)x % 4 == 0);
+  if (pairs) {
+    for (int e = tid; e < rows * (K / 2); e += kLinThreads) {
+      const int r = e / (K / 2), k = 2 * (e - r * (K / 2));
+      const uint16_t *src = x + (int64_t)r * x_row_stride + k;
+      float lo = 0.0f, hi = 0.0f;
+      for (int h0 = 0; h0 < heads; h0 += 32) {
+        uint32_t v[32];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = h0 + j < heads ? src[(int64_t)(h0 + j) * x_head_stride] : (uint16_t)0;
+        for (int j = 0; j < 32; ++j)
+          v[j] = h0 + j < heads ? *reinterpret_cast<const uint32_t *>(src + (int64_t)(h0 + j) * x_head_stride) : 0u;
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (h0 + j < heads) sum = __fadd_rn(sum, bf16_bits_to_float(v[j]));
+        for (int j = 0; j < 32; ++j)
+          if (h0 + j < heads) {
+            lo = __fadd_rn(lo, __uint_as_float(v[j] << 16));
+            hi = __fadd_rn(hi, __uint_as_float(v[j] & 0xFFFF0000u));
+          }
+      }
+      if (heads > 1) {
+        xs[r * K + k] = float_to_bf16_bits(lo), xs[r * K + k + 1] = float_to_bf16_bits(hi);
+      } else {
+        xs[r * K + k] = src[0], xs[r * K + k + 1] = src[1];
+      }
     }
-    xs[e] = heads > 1 ? float_to_bf16_bits(sum) : src[0];
+  } else {
+    for (int e = tid; e < rows * K; e += kLinThreads) {
+      const int r = e / K, k = e - r * K;
+      const uint16_t *src = x + (int64_t)r * x_row_stride + k;
+      float sum = 0.0f;
+      for (int h = 0; h < heads; ++h) sum = __fadd_rn(sum, bf16_bits_to_float(src[(int64_t)h * x_head_stride]));
+      xs[e] = heads > 1 ? float_to_bf16_bits(sum) : src[0];
+    }
   }
   __syncthreads();
   const int n = blockIdx.x * (kLinThreads / 32) + warp;

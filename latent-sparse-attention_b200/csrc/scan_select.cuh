@@ -8,12 +8,17 @@ namespace lsa {
 constexpr int kScanRoom = 2048;        // survivors a row can hold over all its lists
 constexpr int kScanMinVisible = 1024;  // rows that see fewer buckets take the exact scan (it is cheap there)
 constexpr int kScanRetry = 64;         // rows a call can hand to the split exact scan; any more take the plain one
-// With both operands rounded to bf16 and fp32 accumulation, a score of a query q against a centroid no longer than 1
-// lies within |q| * (2^-8 + 2^-16) of the fixed-order fp32 dot: kScanEps * |q| bounds that with room to spare.
+// With both operands rounded to bf16 and fp32 accumulation, a score of a query q against a row no longer than rho
+// lies within |q| * rho * (2^-8 + 2^-16) of the real dot: kScanEps * |q| * rho bounds that with room to spare, and
+// kScanAbsolute * kScanEps * |q| more covers the rounding of the fixed-order fp32 dots the picks are ranked by.
+// The rows the scan multiplies are the centroids LESS A COMMON CENTRE (a query's score against the centre is the
+// same for every bucket, so the ranking is the same); rho is the greatest length of such a row, and where the
+// index vectors lie in a narrow cone it is a fraction of 1.
 constexpr float kScanEps = 1.0f / 240.0f;
-// A list takes every bucket within kScanMargin * |q| below the row's threshold, so that the band the pick has to
-// rescore (2 * kScanEps * |q| below the top_p-th bf16 score) lies inside the lists whenever that score reaches the
-// threshold.
+constexpr float kScanAbsolute = 0.0025f;
+// A list takes every bucket within kScanMargin * |q| * rho below the row's threshold, so that the band the pick has
+// to rescore (2 * kScanEps * |q| * rho below the top_p-th bf16 score) lies inside the lists whenever that score
+// reaches the threshold.
 constexpr float kScanMargin = 1.0f / 64.0f;
 
 struct ScanParams {
@@ -23,7 +28,7 @@ struct ScanParams {
   const int32_t *row_keep;         // [R] or NULL
   int32_t *flags;                  // [R]: nonzero = the row takes the exact scan (the scan itself flags a row whose
                                    // samples say that more buckets would reach its bar than the pick has room for)
-  const float *norms;              // [R] lengths of the query rows
+  const float *norms;              // [R] lengths of the query rows times (rho + kScanAbsolute): the scale of every margin
   const int32_t *tile_visible;     // [rows / 128] the widest visible count among a tile's unflagged rows
   float *bars;                     // [R] the score a bucket had to reach to be listed (threshold less the margin)
   int32_t *counts;                 // [R, lists] survivors found (past `cap`: the list overflowed)

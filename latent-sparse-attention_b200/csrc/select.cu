@@ -115,8 +115,36 @@ __device__ uint64_t block_kth_greatest(const int64_t *buf, int n, int k, int *hi
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint64_t prefix = 0, mask = 0;
   int remaining = k;
+  // The leading bytes every key shares need no pass (counting them would send every key to one bin, one atomic
+  // after the other): the AND and the OR of all keys, folded by the warps and then through two shared words.
+  __shared__ unsigned long long every_s, any_s;
+  if (tid == 0) every_s = ~0ull, any_s = 0ull;
+  __syncthreads();
+  {
+    uint64_t every = ~0ull, any = 0;
+    for (int i = tid; i < n; i += kSelThreads) {
+      const uint64_t u = key_radix(buf[i]);
+      every &= u, any |= u;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      every &= __shfl_xor_sync(0xffffffffu, every, o);
+      any |= __shfl_xor_sync(0xffffffffu, any, o);
+    }
+    if (lane == 0) {
+      atomicAnd(&every_s, (unsigned long long)every);
+      atomicOr(&any_s, (unsigned long long)any);
+    }
+  }
+  __syncthreads();
+  const uint64_t every = every_s, differ = every_s ^ any_s;
   for (int byte = 7; byte >= 0; --byte) {
     const int shift = byte * 8;
+    if ((differ >> shift) == 0) {  // (this byte and all above it are shared)
+      prefix |= every & ((uint64_t)0xFF << shift);
+      mask |= (uint64_t)0xFF << shift;
+      continue;
+    }
     hist[tid] = 0;  // kSelThreads == kHistBins
     __syncthreads();
     for (int i = tid; i < n; i += kSelThreads) {
@@ -629,8 +657,9 @@ namespace lsa {
 __global__ void __launch_bounds__(128)
     scan_prepare_kernel(const float *__restrict__ queries, const int32_t *__restrict__ visible, int64_t R, int64_t m,
                         uint16_t *__restrict__ q_bf16, float *__restrict__ norms, int32_t *__restrict__ flags,
-                        int32_t *__restrict__ tile_visible, int keep, int min_visible, int32_t *__restrict__ taken,
-                        int32_t *__restrict__ retry_visible, int32_t *__restrict__ retry_keep) {
+                        int32_t *__restrict__ tile_visible, int keep, int min_visible, const float *__restrict__ radius,
+                        int32_t *__restrict__ taken, int32_t *__restrict__ retry_visible,
+                        int32_t *__restrict__ retry_keep) {
   __shared__ int widest_s;
   const int64_t row = (int64_t)blockIdx.x * 128 + threadIdx.x;
   if (threadIdx.x == 0) widest_s = 0;
@@ -654,7 +683,7 @@ __global__ void __launch_bounds__(128)
   if (row < R) {
     const int v = min(max(visible[row], 0), (int)m);
     const bool exact = v < min_visible || !(ss > 0.0f) || !isfinite(ss);
-    norms[row] = sqrtf(ss);
+    norms[row] = sqrtf(ss) * ((radius ? *radius : 1.0f) + kScanAbsolute);
     flags[row] = exact ? 1 : 0;
     if (!exact) atomicMax(&widest_s, v);
   }
@@ -834,13 +863,53 @@ static ScanWorkspace scan_workspace(int64_t R, int top_p, int64_t m) {
 
 }  // namespace lsa
 
+namespace lsa {
+
+// The N operand of the tensor-core scan: the centroids less a common centre, rounded to bf16, and the greatest length
+// of such a row (kept as the bits of a non-negative float, which order as integers do).
+__global__ void __launch_bounds__(256)
+    scan_centre_kernel(const float *__restrict__ centroids, int64_t rows, const float *__restrict__ centre,
+                       uint16_t *__restrict__ out, float *__restrict__ radius) {
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 64; k += 8) {
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      const float a = centroids[row * 64 + k + j] - (centre ? centre[k + j] : 0.0f);
+      const float b = centroids[row * 64 + k + j + 1] - (centre ? centre[k + j + 1] : 0.0f);
+      ss = fmaf(a, a, ss), ss = fmaf(b, b, ss);
+      packed[j / 2] = (uint32_t)float_to_bf16_bits(a) | ((uint32_t)float_to_bf16_bits(b) << 16);
+    }
+    *reinterpret_cast<uint4 *>(out + row * 64 + k) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+  if (radius) atomicMax(reinterpret_cast<int *>(radius), __float_as_int(sqrtf(ss) * 1.000001f));
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_scan_centre(const float *centroids, int64_t rows, int d, const float *centre, uint16_t *out_bf16,
+                            float *radius, void *stream) {
+  LSA_REQUIRE(centroids && out_bf16, LSA_ERR_NULL);
+  LSA_REQUIRE(rows >= 0, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(d == 64, LSA_ERR_UNSUPPORTED);
+  LSA_REQUIRE(((uintptr_t)out_bf16 % 16) == 0, LSA_ERR_ARGUMENT);
+  if (rows == 0) return LSA_OK;
+  lsa::scan_centre_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, (cudaStream_t)stream>>>(centroids, rows, centre,
+                                                                                            out_bf16, radius);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+
 LSA_API size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m) {
   if (R <= 0 || top_p <= 0 || m < 0) return 0;
   return lsa::scan_workspace(R, top_p, m).total;
 }
 
 LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids,
-                            const uint16_t *centroids_bf16, int64_t m, const int32_t *visible,
+                            const uint16_t *centroids_bf16, const float *radius, int64_t m, const int32_t *visible,
                             const int32_t *row_top_p, int top_p, int32_t bucket_id_base, int max_visible,
                             int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
                             size_t workspace_bytes, void *stream) {
@@ -884,7 +953,8 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   int32_t *retry_visible = reinterpret_cast<int32_t *>(base + w.retry_visible);
   lsa::scan_prepare_kernel<<<(unsigned)(padded / 128), 128, 0, s>>>(
       queries, visible, R, m, const_cast<uint16_t *>(p.queries_bf16), const_cast<float *>(p.norms), flags,
-      const_cast<int32_t *>(p.tile_visible), top_p, sampled ? lsa::kScanMinVisible : INT32_MAX, taken, retry_visible,
+      const_cast<int32_t *>(p.tile_visible), top_p, sampled ? lsa::kScanMinVisible : INT32_MAX, radius, taken,
+      retry_visible,
       reinterpret_cast<int32_t *>(base + w.retry_keep));
   LSA_LAUNCH_CHECK();
   if (sampled) {
@@ -945,6 +1015,69 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   f.keep = top_p;
   f.id_base = bucket_id_base;
   return lsa::launch_flat<64>(f, s);
+}
+
+// ------------------------------------------------------------------------------------------------ dense scores
+
+namespace lsa {
+
+// Every (row, bucket) score written out, each at its own column: the two-pass selection of the reference scores
+// first and picks after, and code written against that form asks for the matrix. 8 rows a CTA share a bucket's
+// centroid; a thread a bucket, the dot added in ascending dim order.
+__global__ void __launch_bounds__(256)
+    dense_scores_kernel(const float *__restrict__ queries, const float *__restrict__ centroids,
+                        const int32_t *__restrict__ pages, int max_pages, int page_rows,
+                        const int32_t *__restrict__ counts, int64_t R, int d, int64_t width, int id_base,
+                        float *__restrict__ scores_out, int64_t *__restrict__ keys_out) {
+  extern __shared__ __align__(16) float q_s[];  // [8][d]
+  const int64_t row0 = (int64_t)blockIdx.y * 8;
+  for (int e = threadIdx.x; e < 8 * d; e += blockDim.x) {
+    const int64_t r = row0 + e / d;
+    q_s[e] = r < R ? queries[r * d + e % d] : 0.0f;
+  }
+  __syncthreads();
+  const int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= width) return;
+  for (int i = 0; i < 8 && row0 + i < R; ++i) {
+    const int64_t r = row0 + i;
+    int64_t at = col;
+    bool held = col < counts[r];
+    if (held && pages) {
+      const int page = pages[r * max_pages + col / page_rows];
+      held = page >= 0;
+      at = (int64_t)page * page_rows + col % page_rows;
+    }
+    float acc = 0.0f;
+    if (held) {
+      const float4 *c4 = reinterpret_cast<const float4 *>(centroids + at * d);
+      const float *q = q_s + i * d;
+      for (int k4 = 0; k4 < d / 4; ++k4) {
+        const float4 v = __ldg(c4 + k4);
+        acc = fmaf(q[4 * k4], v.x, acc), acc = fmaf(q[4 * k4 + 1], v.y, acc);
+        acc = fmaf(q[4 * k4 + 2], v.z, acc), acc = fmaf(q[4 * k4 + 3], v.w, acc);
+      }
+    }
+    if (scores_out) scores_out[r * width + col] = held ? acc : -INFINITY;
+    if (keys_out) keys_out[r * width + col] = held ? pack_key(acc, (int32_t)col + id_base) : kEmptyKey;
+  }
+}
+
+}  // namespace lsa
+
+LSA_API int lsa_dense_scores(const float *queries, int64_t R, int d, const float *centroids, const int32_t *pages,
+                             int max_pages, int page_rows, const int32_t *counts, int64_t width,
+                             int32_t bucket_id_base, float *scores_out, int64_t *keys_out, void *stream) {
+  LSA_REQUIRE(queries && centroids && counts && (scores_out || keys_out), LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && width >= 0 && width < INT32_MAX && d >= 4 && d % 4 == 0 && d <= 1024, LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(!pages || (max_pages >= 1 && page_rows >= 1), LSA_ERR_ARGUMENT);
+  LSA_REQUIRE(((uintptr_t)centroids % 16) == 0, LSA_ERR_ARGUMENT);
+  if (R == 0 || width == 0) return LSA_OK;
+  const dim3 grid((unsigned)((width + 255) / 256), (unsigned)((R + 7) / 8));
+  LSA_REQUIRE(grid.y <= 65535, LSA_ERR_UNSUPPORTED);
+  lsa::dense_scores_kernel<<<grid, 256, (size_t)8 * d * 4, (cudaStream_t)stream>>>(
+      queries, centroids, pages, max_pages, page_rows, counts, R, d, width, bucket_id_base, scores_out, keys_out);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
 }
 
 LSA_API int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,

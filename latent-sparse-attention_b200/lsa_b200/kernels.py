@@ -2,6 +2,9 @@
 
     pack_keys / unpack_ids / unpack_scores / ordered_int32      triton/keys.py:36-88
     ScanSelect                                                  scan_select.py:189-385
+    dense_keys / listed_keys / sample_thresholds                scan_select.py:24-143
+    scan_paged                                                  triton/paged.py:61-101
+    TopK / top_keys                                             triton/top_k.py:708-997
     DecodeSelect                                                cutedsl/decode.py:1035-1086
     expand_in_order / expand_by_threshold                       expansion.py:16-126
     cluster_ward / cluster_node_buckets                         ward.py:49-110
@@ -21,7 +24,7 @@ import torch
 
 from lsa_b200 import ops
 from lsa_b200.budget import EarlyBudget
-from lsa_b200.constants import PackedKey
+from lsa_b200.constants import PackedKey, Sentinel
 
 
 # --------------------------------------------------------------------------------------------- packed keys
@@ -88,6 +91,128 @@ class ScanSelect:
 
     def pick(self, listing: Listing) -> torch.Tensor:
         return self.out[: listing.keys.shape[0]]
+
+
+# The reference's selection is two passes - scores written out, then a pick over them - and its serving index is
+# written against the pieces of that. Here one kernel scores and picks, so these are thin: the dense forms write the
+# matrix with the exact fixed-order dot, the picks run the packed-key selection over it.
+
+SAMPLE_TARGET, SAMPLE_RANK, SCAN_MARGIN = 1.5, 64, 1e-4  # (kernels/constants.py:179-186)
+
+
+def dense_keys(index_queries, bucket_centroids, visible_counts, width=None, shapes=None, query_planes=None,
+               kernels: str = "b200") -> torch.Tensor:
+    """Every bucket a row sees scored and packed with its bucket, at its own column [R, width] int64, the empty key
+    past a row's length (scan_select.py:24-58)."""
+    if shapes is not None:
+        raise NotImplementedError("bucket shapes are not built in lsa_b200")
+    return ops.dense_scores(index_queries, bucket_centroids, visible_counts, width, keys=True)
+
+
+def scan_paged(index_queries, bucket_centroids, pages, counts, page_size: int, max_rows: int) -> torch.Tensor:
+    """Each request's buckets scored through its pages [B, max_rows] fp32, -inf past a request's count or on a page
+    it has not got (triton/paged.py:61-101)."""
+    return ops.dense_scores(index_queries, bucket_centroids, counts, max_rows, pages=pages, page_rows=page_size)
+
+
+def sample_plan(top_p: int) -> tuple:
+    """Buckets between two sampled ones, and the rank in the sample the threshold is read at
+    (triton/scan_select.py:687-698)."""
+    stride = max(1, round(SAMPLE_TARGET * top_p / SAMPLE_RANK))
+    return stride, max(1, round(SAMPLE_TARGET * top_p / stride))
+
+
+def sample_thresholds(index_queries, bucket_centroids, visible_counts, top_p: int, shapes=None, query_planes=None,
+                      kernels: str = "b200") -> torch.Tensor:
+    """Each row's score at 1.5 times its top_p, estimated from every stride-th bucket it sees [R] fp32, -inf for a
+    row that sees too few to rank (scan_select.py:110-143). The estimate here is the sampled score of that rank
+    itself, where the reference takes the lower edge of its histogram bin: both err toward more survivors."""
+    if shapes is not None:
+        raise NotImplementedError("bucket shapes are not built in lsa_b200")
+    stride, rank = sample_plan(top_p)
+    sampled = bucket_centroids[::stride]
+    counts = (visible_counts.to(torch.int64) + stride - 1) // stride
+    scores = ops.dense_scores(index_queries, sampled, counts.to(torch.int32))
+    if scores.shape[1] < rank:
+        return torch.full((scores.shape[0],), float("-inf"), device=scores.device)
+    ranked = scores.topk(rank, dim=1).values[:, rank - 1]
+    return torch.where(counts >= rank, ranked, float("-inf"))
+
+
+def listed_keys(index_queries, bucket_centroids, visible_counts, thresholds, capacity: int, shapes=None,
+                query_planes=None, kernels: str = "b200"):
+    """The buckets each row scores near its threshold, scored and packed (scan_select.py:61-107): packed keys
+    [R, capacity] int64 of the first `capacity` listed buckets in bucket order, the empty key after; buckets each row
+    listed [R] int32 (above capacity: the buffer overflowed); listed buckets at or above the threshold [R] int32."""
+    if shapes is not None:
+        raise NotImplementedError("bucket shapes are not built in lsa_b200")
+    keys = dense_keys(index_queries, bucket_centroids, visible_counts)
+    scores = unpack_scores(keys)
+    shifted = thresholds - SCAN_MARGIN * index_queries.float().norm(dim=1)
+    listed = (keys != PackedKey.EMPTY) & (scores >= shifted[:, None])
+    slot = listed.cumsum(1) - 1
+    out = torch.full((keys.shape[0], capacity + 1), PackedKey.EMPTY, device=keys.device, dtype=torch.int64)
+    out.scatter_(1, torch.where(listed & (slot < capacity), slot, capacity), keys)
+    reached = (listed & (scores >= thresholds[:, None])).sum(1, dtype=torch.int32)
+    return out[:, :capacity].contiguous(), listed.sum(1, dtype=torch.int32), reached
+
+
+class TopK:
+    """The best k columns of each row of a score matrix (triton/top_k.py:708-975). A listing here is always exact:
+    each row's best k, which is also a valid superset."""
+
+    def __init__(self, k: int, rows: int | None = None, device="cuda", exact: bool = False) -> None:
+        self.k, self.exact = k, exact
+        self.keys = torch.empty(0, 0, dtype=torch.int64)
+        self.counts = torch.empty(0, dtype=torch.int32)
+
+    def release(self) -> None:
+        self.keys = torch.empty(0, 0, dtype=torch.int64)
+        self.counts = torch.empty(0, dtype=torch.int32)
+
+    def _best(self, scores: torch.Tensor, lengths: torch.Tensor) -> torch.Tensor:
+        """Packed keys [R, k] of each row's best k columns, best first, a tie to the lower column."""
+        if scores.dtype != torch.float32:
+            raise TypeError(f"a top-k reads fp32 scores, not {scores.dtype}")
+        rows, columns = scores.shape
+        ids = torch.arange(columns, device=scores.device, dtype=torch.int32)
+        keys = torch.where(ids[None] < lengths[:, None], pack_keys(scores, ids.expand(rows, -1)), PackedKey.EMPTY)
+        parts = -(-columns // self.k)
+        padded = torch.full((rows, parts * self.k), PackedKey.EMPTY, device=scores.device, dtype=torch.int64)
+        padded[:, :columns] = keys
+        best, _ = ops.merge_candidates(padded.view(rows, parts, self.k).permute(1, 0, 2).contiguous())
+        return best
+
+    def listed(self, scores: torch.Tensor, lengths: torch.Tensor):
+        """Packed keys [R, W] of each row's best k in column order, W the lesser of k and N, and the keys each row
+        listed [R] int32."""
+        width = min(self.k, scores.shape[1])
+        best = self._best(scores, lengths)[:, :width]
+        by_column = torch.where(best != PackedKey.EMPTY, unpack_ids(best).long(), 1 << 40).argsort(dim=1)
+        self.keys = best.gather(1, by_column)
+        self.counts = torch.clamp(lengths, max=width).to(torch.int32)
+        return self.keys, self.counts
+
+    def best(self) -> torch.Tensor:
+        """The last listing's best k as packed keys [R, k], the best score first, the empty key past a row's length."""
+        rows, width = self.keys.shape
+        out = torch.full((rows, self.k), PackedKey.EMPTY, device=self.keys.device, dtype=torch.int64)
+        out[:, :width] = self.keys.sort(dim=1, descending=True).values
+        return out
+
+    def __call__(self, scores: torch.Tensor, lengths: torch.Tensor) -> torch.Tensor:
+        """The k best columns of each row [R, k] int32 in ascending column order, -1 past the last."""
+        keys, _ = self.listed(scores, lengths)
+        out = torch.full((scores.shape[0], self.k), Sentinel.PAD, device=scores.device, dtype=torch.int32)
+        out[:, :keys.shape[1]] = unpack_ids(keys)
+        return out
+
+
+def top_keys(scores: torch.Tensor, lengths: torch.Tensor, k: int) -> torch.Tensor:
+    """The best k columns of each row as packed keys [R, k], best first (triton/top_k.py:978-997)."""
+    pick = TopK(k)
+    pick.listed(scores, lengths)
+    return pick.best()
 
 
 class DecodeSelect:

@@ -48,12 +48,14 @@ class FlatDesign:
 
 class FlatIndex:
     """A request's index: its index keys and the buckets of its closed cluster blocks (and, where the tensor-core
-    scan can use it, the bf16 rounding of the centroids)."""
+    scan can use it, its operand: the centroids less a common centre in bf16, and the greatest length of one)."""
 
-    def __init__(self, index_keys: torch.Tensor, buckets: Buckets, centroids_bf16: torch.Tensor | None = None):
+    def __init__(self, index_keys: torch.Tensor, buckets: Buckets, centroids_bf16: torch.Tensor | None = None,
+                 radius: torch.Tensor | None = None):
         self.index_keys = index_keys
         self.buckets = buckets
         self.centroids_bf16 = centroids_bf16
+        self.radius = radius
 
 
 class FlatLayer:
@@ -184,14 +186,17 @@ class FlatLayer:
                 "members": make("members", (rows, d.bucket_cap), torch.int32), "sizes": make("sizes", (rows,), torch.int32),
                 "key sums": make("key sums", (rows, d_idx), torch.float32),
                 "centroids": make("centroids", (rows, d_idx), torch.float32)}
-        if d_idx == 64:  # (the operand of the tensor-core scan)
+        if d_idx == 64:  # (the operand of the tensor-core scan: centroids less the first blocks' mean, in bf16)
             bufs["centroids bf16"] = make("centroids bf16", (rows, d_idx), torch.bfloat16)
+            bufs["centre"], bufs["radius"] = make("centre", (d_idx,), torch.float32), make("radius", (1,), torch.float32)
+            bufs["radius"].zero_()
+            bufs["centred"] = [False]
         return bufs
 
     def _index_of(self, bufs: dict) -> FlatIndex:
         d = self.design
         return FlatIndex(bufs["keys"], Buckets(bufs["centroids"], bufs["members"], bufs["sizes"], d.block_bucket_count,
-                                               d.cluster_block_size), bufs.get("centroids bf16"))
+                                               d.cluster_block_size), bufs.get("centroids bf16"), bufs.get("radius"))
 
     def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
         """Index keys of k [n, ...] = the keys at positions first.., and the pools, Ward labels and bucket table of
@@ -220,9 +225,16 @@ class FlatLayer:
                 self._reached.append(bufs["reached"][b0:b0 + nb])
         with probe.region("bucket table"):
             outs = (bufs["members"][r0:r1], bufs["sizes"][r0:r1], bufs["key sums"][r0:r1], bufs["centroids"][r0:r1],
-                    bufs["centroids bf16"][r0:r1] if "centroids bf16" in bufs else None, bufs["status"])
+                    None, bufs["status"])
             ops.bucket_table(keys, labels, d.pool_size, d.block_bucket_count, d.bucket_cap, first_position=first,
                              outs=outs)
+            if "centroids bf16" in bufs:
+                # Any centre leaves the ranking as it is; the mean of the first blocks' centroids is where the cone
+                # of this layer's index vectors points, and the closer to it the rows lie, the sharper the scan.
+                if not bufs["centred"][0]:
+                    bufs["centre"].copy_(bufs["centroids"][r0:r1].mean(0))
+                    bufs["centred"][0] = True
+                ops.scan_centre(bufs["centroids"][r0:r1], bufs["centre"], bufs["centroids bf16"][r0:r1], bufs["radius"])
 
     scan_rows = 1024  # from this many rows on, a pick runs its scan on the tensor cores
 
@@ -253,7 +265,7 @@ class FlatLayer:
                 work = self._buffer("scan", (need,), torch.uint8, dev)
                 _, picked = ops.scan_select(index_queries, b.bucket_centroids, index.centroids_bf16, visible, d.top_p,
                                             row_p, max_visible=bound, keys=keys, picked=picked,
-                                            status=self._scan_status, workspace=work)
+                                            status=self._scan_status, workspace=work, radius=index.radius)
             else:
                 _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
                                             picked=picked)

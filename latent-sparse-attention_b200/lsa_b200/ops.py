@@ -246,26 +246,59 @@ def flat_select(index_queries: torch.Tensor, centroids: torch.Tensor, visible: t
     return keys, picked
 
 
+def dense_scores(index_queries: torch.Tensor, centroids: torch.Tensor, counts: torch.Tensor, width: int | None = None,
+                 pages: torch.Tensor | None = None, page_rows: int = 1, bucket_id_base: int = 0, keys: bool = False):
+    """Every (row, bucket) score at its own column [R, width] fp32 (-inf past a row's count), or with `keys` the
+    packed keys [R, width] int64 (src/lsa/core/kernels/scan_select.py:24-58, triton/paged.py:61-101); through
+    `pages` [R, max_pages] where a cache holds its buckets in pages of `page_rows`."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    width = c.shape[0] if width is None else width
+    out = torch.empty(R, width, device=q.device, dtype=torch.int64 if keys else torch.float32)
+    pages = None if pages is None else _contig(pages.to(torch.int32))
+    call("lsa_dense_scores", ptr(q), R, d, ptr(c), ptr(pages), pages.shape[1] if pages is not None else 0, page_rows,
+         ptr(_contig(counts.to(torch.int32))), width, bucket_id_base, None if keys else ptr(out),
+         ptr(out) if keys else None, stream())
+    return out
+
+
+def scan_centre(centroids: torch.Tensor, centre: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                radius: torch.Tensor | None = None):
+    """The tensor-core scan's N operand: `centroids` [rows, 64] fp32 less `centre` [64] (None: no centre), rounded to
+    bf16 into `out`, and `radius` [1] fp32 raised to the greatest length of a row written (start it at zero; a run of
+    rows at a time as an index grows). Returns (out, radius)."""
+    c = _contig(centroids.float())
+    out = torch.empty(c.shape, device=c.device, dtype=torch.bfloat16) if out is None else out
+    radius = torch.zeros(1, device=c.device, dtype=torch.float32) if radius is None else radius
+    if out.shape != c.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous bfloat16 {tuple(c.shape)}")
+    call("lsa_scan_centre", ptr(c), c.shape[0], c.shape[1], ptr(None if centre is None else _contig(centre.float())),
+         ptr(out), ptr(radius), stream())
+    return out, radius
+
+
 def scan_select(index_queries: torch.Tensor, centroids: torch.Tensor, centroids_bf16: torch.Tensor,
                 visible: torch.Tensor, top_p: int, row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0,
                 max_visible: int = 0, keys: torch.Tensor | None = None, picked: torch.Tensor | None = None,
-                status: torch.Tensor | None = None, workspace: torch.Tensor | None = None):
+                status: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                radius: torch.Tensor | None = None):
     """`flat_select`'s result with the scan on tcgen05: bf16 scores in tensor memory against a sampled threshold,
     an exact fp32 rescoring of the survivors, and an exact scan of whatever row the survivors cannot prove
     (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836, src/lsa/core/kernels/scan_select.py:189-385).
-    `max_visible` is the host's bound on `visible` (0: all of the centroids)."""
+    `centroids_bf16` and `radius` come from `scan_centre` (without a radius: the plain bf16 rounding of centroids no
+    longer than 1). `max_visible` is the host's bound on `visible` (0: all of the centroids)."""
     q, c, cb = _contig(index_queries.float()), _contig(centroids.float()), _contig(centroids_bf16)
     R, d = q.shape
     if cb.dtype != torch.bfloat16 or cb.shape != c.shape:
-        raise ValueError("centroids_bf16 must be the bf16 rounding of centroids")
+        raise ValueError("centroids_bf16 must be a bfloat16 matrix of the centroids' shape")
     keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64) if keys is None else keys
     picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32) if picked is None else picked
     need = query("lsa_scan_select_workspace_bytes", R, top_p, c.shape[0])
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         workspace = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
-    call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), c.shape[0], ptr(_contig(visible.to(torch.int32))),
-         ptr(row_top_p), top_p, bucket_id_base, int(max_visible), ptr(keys), ptr(picked), ptr(status), ptr(workspace),
-         workspace.numel() * workspace.element_size(), stream())
+    call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), ptr(radius), c.shape[0],
+         ptr(_contig(visible.to(torch.int32))), ptr(row_top_p), top_p, bucket_id_base, int(max_visible), ptr(keys),
+         ptr(picked), ptr(status), ptr(workspace), workspace.numel() * workspace.element_size(), stream())
     return keys, picked
 
 

@@ -94,3 +94,76 @@ def test_cluster_front_doors(oracle):
     sums = oracle.gather_sum(keys, buckets.bucket_members).reshape(2, 32, 32)
     pairs = kernels.cluster_node_buckets(cuda(sums))
     assert np.array_equal(pairs.cpu().numpy(), oracle.ward_rounds(sums, np.ones((2, 32), dtype=np.float32), 16, 2.0)[0])
+
+
+def test_the_two_pass_forms_dense_keys_paged_scores_and_the_top_k(oracle):
+    from lsa_b200 import kernels
+
+    rng = np.random.default_rng(8)
+    R, N, d = 37, 1500, 64
+    cents = unit_rows(rng.standard_normal((N, d), dtype=np.float32))
+    cents[40:80] = cents[40]  # ties: the lower column wins
+    queries = unit_rows(rng.standard_normal((R, d), dtype=np.float32)) * rng.uniform(0.1, 20, (R, 1)).astype(np.float32)
+    counts = rng.integers(0, N + 1, R).astype(np.int32)
+    counts[:3] = [0, 1, N]
+    want = np.full((R, N), oracle.EMPTY_KEY, dtype=np.int64)
+    scores = np.full((R, N), -np.inf, dtype=np.float32)
+    for r in range(R):
+        n = int(counts[r])
+        if n:
+            scores[r, :n] = oracle.scores(queries[r], cents[:n])
+            want[r, :n] = oracle.pack_keys(scores[r, :n], np.arange(n, dtype=np.int32))
+    keys = kernels.dense_keys(cuda(queries), cuda(cents), cuda(counts))
+    assert np.array_equal(keys.cpu().numpy(), want)
+    wide = kernels.dense_keys(cuda(queries), cuda(cents), cuda(counts), width=N + 100)
+    assert wide.shape == (R, N + 100) and (wide[:, N:] == oracle.EMPTY_KEY).all()
+
+    # through pages: the same buckets at shuffled rows of a cache, 64 to a page, one request missing a page
+    page_rows, pages_each = 64, -(-N // 64)
+    order = rng.permutation(R * pages_each + 7).astype(np.int32)
+    pages = order[: R * pages_each].reshape(R, pages_each).copy()
+    cache = np.zeros(((R * pages_each + 7) * page_rows, d), dtype=np.float32)
+    for r in range(R):
+        for i in range(pages_each):
+            rows = cents[i * page_rows:(i + 1) * page_rows]
+            cache[pages[r, i] * page_rows: pages[r, i] * page_rows + len(rows)] = rows
+    pages[5, 2] = -1
+    got = kernels.scan_paged(cuda(queries), cuda(cache), cuda(pages), cuda(counts), page_rows, N)
+    hole = scores.copy()
+    hole[5, 2 * page_rows:3 * page_rows] = -np.inf
+    assert np.array_equal(got.cpu().numpy().view(np.int32), hole.view(np.int32))
+
+    # the pick over a score matrix: best k with ties to the lower column, as keys and as columns
+    k = 48
+    pick = kernels.TopK(k, exact=True)
+    listed, listed_counts = pick.listed(cuda(scores), cuda(counts))
+    best = pick.best().cpu().numpy()
+    for r in range(R):
+        top = np.sort(want[r])[::-1][:k]
+        assert np.array_equal(best[r], top), r
+        held = min(k, int(counts[r]))
+        assert int(listed_counts[r]) == held
+        columns = kernels.unpack_ids(listed[r, :held]).cpu().numpy()
+        assert np.array_equal(columns, np.sort(oracle.unpack_ids(top[:held])))
+    columns = pick(cuda(scores), cuda(counts)).cpu().numpy()
+    assert np.array_equal(columns[2, :k], np.sort(oracle.unpack_ids(np.sort(want[2])[::-1][:k])))
+    assert (columns[0] == -1).all() and columns[1, 0] == 0 and (columns[1, 1:] == -1).all()
+    assert np.array_equal(kernels.top_keys(cuda(scores), cuda(counts), k).cpu().numpy(), best)
+
+    # thresholds from every stride-th bucket, and the listing they cut
+    top_p = 64
+    stride, rank = kernels.sample_plan(top_p)
+    assert (stride, rank) == (2, 48)
+    thresholds = kernels.sample_thresholds(cuda(queries), cuda(cents), cuda(counts), top_p).cpu().numpy()
+    for r in (2, 7, 20):
+        sampled = scores[r, : counts[r]][::stride]
+        want_t = np.sort(sampled)[::-1][rank - 1] if len(sampled) >= rank else -np.inf
+        assert thresholds[r] == want_t
+    listed_k, listed_n, reached = kernels.listed_keys(cuda(queries), cuda(cents), cuda(counts), cuda(thresholds), 256)
+    for r in (2, 7, 20):
+        if not np.isfinite(thresholds[r]):
+            continue
+        shifted = thresholds[r] - 1e-4 * np.linalg.norm(queries[r])
+        hit = np.flatnonzero(scores[r] >= np.float32(shifted))
+        assert int(listed_n[r]) == len(hit) and int(reached[r]) == int((scores[r] >= thresholds[r]).sum())
+        assert np.array_equal(listed_k[r, : min(256, len(hit))].cpu().numpy(), want[r, hit[:256]])

@@ -118,3 +118,25 @@ def test_a_chunk_of_the_long_context_shape(ops):
     got, _ = ops.scan_select(queries, cents, cents.bfloat16(), visible, 128, max_visible=m, status=status)
     want, _ = ops.flat_select(queries, cents, visible, 128)
     assert int(status) == 0 and torch.equal(got, want)
+
+
+def test_index_vectors_in_a_narrow_cone_are_told_apart_about_their_centre(ops):
+    # every centroid within 0.1 of one axis: a row's scores differ in the third digit, under what bf16 can rank - until
+    # the common centre is taken out of the operand
+    rng = np.random.default_rng(21)
+    m, R = 8192, 1500
+    axis = unit_rows(rng.standard_normal((1, 64), dtype=np.float32))
+    cents = unit_rows(axis + 0.012 * rng.standard_normal((m, 64), dtype=np.float32))
+    queries = unit_rows(axis + 0.012 * rng.standard_normal((R, 64), dtype=np.float32))
+    visible = rng.integers(1024, m + 1, R).astype(np.int32)
+    q, c, v = cuda(queries), cuda(cents), cuda(visible)
+    operand, radius = ops.scan_centre(c[:4096], c[:64].mean(0))
+    operand = torch.cat([operand, ops.scan_centre(c[4096:], c[:64].mean(0), radius=radius)[0]])  # as an index grows
+    assert 0.05 < float(radius) < 0.2
+    want, _ = ops.flat_select(q, c, v, 64)
+    got, _ = ops.scan_select(q, c, operand, v, 64, radius=radius)
+    assert torch.equal(got, want)
+    plain, unit = ops.scan_centre(c)
+    assert 0.99 < float(unit) < 1.01 and torch.equal(plain, c.bfloat16())
+    got, _ = ops.scan_select(q, c, plain, v, 64, radius=unit)  # (the rows are crowded: scanned exactly)
+    assert torch.equal(got, want)
