@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
 constexpr int kClusterCtas = 8;
 constexpr int kClusterThreads = 512;
 
-__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads, 1)
     expand_cluster_kernel(ExpandParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
@@ -286,7 +286,24 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
     bucket_s[i] = bucket;
   }
   __syncthreads();
-  for (int pick = warp; pick < picks; pick += kWarps) {
+  // A warp's first pick stays in its registers between the count and the write (a row of up to 1,280 members: forty
+  // loads a lane, all in flight at once), so the step waits for memory once a pass instead of once a group of four.
+  constexpr int kHeld = 40;
+  const bool holds = p.cap <= 32 * kHeld && warp < picks;
+  int32_t held[kHeld];
+  if (holds) {
+    const int64_t bucket = bucket_s[warp];
+    int n = 0;
+#pragma unroll
+    for (int j = 0; j < kHeld; ++j) {
+      const int at = 32 * j + lane;
+      held[j] = bucket >= 0 && at < p.cap ? p.members[bucket * p.cap + at] : LSA_PAD;
+    }
+#pragma unroll
+    for (int j = 0; j < kHeld; ++j) n += __popc(__ballot_sync(0xffffffffu, held[j] >= p.sink && held[j] < window_start));
+    if (lane == 0) count_s[warp] = n;
+  }
+  for (int pick = holds ? warp + kWarps : warp; pick < picks; pick += kWarps) {
     const int64_t bucket = bucket_s[pick];
     int n = 0;
     if (bucket >= 0)
@@ -325,7 +342,18 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
     if (c < cta) before += t;
     all += t;
   }
-  for (int pick = warp; pick < picks; pick += kWarps) {
+  if (holds) {
+    int written = before + start_s[warp];
+#pragma unroll
+    for (int j = 0; j < kHeld; ++j) {
+      const bool counts = held[j] >= p.sink && held[j] < window_start;
+      const unsigned votes = __ballot_sync(0xffffffffu, counts);
+      const int at = written + __popc(votes & below);
+      if (counts && at < row_k) out[at] = stored_id(p, table, held[j]);
+      written += __popc(votes);
+    }
+  }
+  for (int pick = holds ? warp + kWarps : warp; pick < picks; pick += kWarps) {
     const int64_t bucket = bucket_s[pick];
     int written = before + start_s[pick];
     if (bucket < 0) continue;

@@ -281,6 +281,7 @@ __global__ void __launch_bounds__(kLinThreads)
 #pragma unroll
   for (int r = 0; r < kLinMaxRows; ++r) acc[r] = 0.0f;
   const uint16_t *w = Wt + (int64_t)n * K;
+#pragma unroll 4
   for (int k = lane * 8; k < K; k += 32 * 8) {  // (K is a multiple of 8 and the rows are 16-byte aligned)
     const uint4 wv = *reinterpret_cast<const uint4 *>(w + k);
     const uint32_t wp[4] = {wv.x, wv.y, wv.z, wv.w};

@@ -344,15 +344,22 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
           if (vec_row[i] >= 0) row = vec_row[i];
         if (row >= 0) {
           const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + row * p.d);
-          for (int k4 = 0; k4 < p.d / 4; ++k4) {
-            const float4 v = __ldg(v4 + k4);
+          // sixteen dims' loads in flight at a time (a vector of 64 dims: all of it), added in dim order
+          for (int k0 = 0; k0 < p.d / 4; k0 += 4) {
+            float4 v[4];
 #pragma unroll
-            for (int i = 0; i < RB; ++i) {
-              const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
-              acc[i] = fmaf(q.x, v.x, acc[i]);
-              acc[i] = fmaf(q.y, v.y, acc[i]);
-              acc[i] = fmaf(q.z, v.z, acc[i]);
-              acc[i] = fmaf(q.w, v.w, acc[i]);
+            for (int j = 0; j < 4; ++j) v[j] = k0 + j < p.d / 4 ? __ldg(v4 + k0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (k0 + j >= p.d / 4) break;
+#pragma unroll
+              for (int i = 0; i < RB; ++i) {
+                const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + (k0 + j) * 4);
+                acc[i] = fmaf(q.x, v[j].x, acc[i]);
+                acc[i] = fmaf(q.y, v[j].y, acc[i]);
+                acc[i] = fmaf(q.z, v[j].z, acc[i]);
+                acc[i] = fmaf(q.w, v[j].w, acc[i]);
+              }
             }
           }
         }
@@ -361,13 +368,33 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
         for (int i = 0; i < RB; ++i) {
           if (vec_row[i] < 0) continue;
           const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + vec_row[i] * p.d);
-          for (int k4 = 0; k4 < p.d / 4; ++k4) {
-            const float4 v = __ldg(v4 + k4);
-            const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
-            acc[i] = fmaf(q.x, v.x, acc[i]);
-            acc[i] = fmaf(q.y, v.y, acc[i]);
-            acc[i] = fmaf(q.z, v.z, acc[i]);
-            acc[i] = fmaf(q.w, v.w, acc[i]);
+          if (p.d == 64) {  // (the served index dim: the whole vector's loads in flight at once)
+            float4 v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __ldg(v4 + j);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float4 q = *reinterpret_cast<const float4 *>(qs + i * 64 + j * 4);
+              acc[i] = fmaf(q.x, v[j].x, acc[i]);
+              acc[i] = fmaf(q.y, v[j].y, acc[i]);
+              acc[i] = fmaf(q.z, v[j].z, acc[i]);
+              acc[i] = fmaf(q.w, v[j].w, acc[i]);
+            }
+            continue;
+          }
+          for (int k0 = 0; k0 < p.d / 4; k0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = k0 + j < p.d / 4 ? __ldg(v4 + k0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (k0 + j >= p.d / 4) break;
+              const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + (k0 + j) * 4);
+              acc[i] = fmaf(q.x, v[j].x, acc[i]);
+              acc[i] = fmaf(q.y, v[j].y, acc[i]);
+              acc[i] = fmaf(q.z, v[j].z, acc[i]);
+              acc[i] = fmaf(q.w, v[j].w, acc[i]);
+            }
           }
         }
       }
@@ -949,15 +976,21 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   // The threshold is read off 512 samples of a row's scores: where the buckets a row keeps are too small a share of
   // those it sees for a handful of samples to reach it, the threshold would be noise, and every row is scanned exactly.
   const bool sampled = m >= lsa::kScanMinVisible && (int64_t)p.factor * top_p * 512 >= 8 * widest;
+  if (!sampled) {
+    lsa::FlatParams f = {};
+    f.queries = queries, f.centroids = centroids, f.visible = visible, f.row_keep = row_top_p;
+    f.keys_out = keys_out, f.ids_out = picked_out;
+    f.R = R, f.m = m, f.d = d, f.keep = top_p, f.id_base = bucket_id_base;
+    return lsa::launch_flat<64>(f, s);
+  }
   int32_t *taken = reinterpret_cast<int32_t *>(base + w.taken);
   int32_t *retry_visible = reinterpret_cast<int32_t *>(base + w.retry_visible);
   lsa::scan_prepare_kernel<<<(unsigned)(padded / 128), 128, 0, s>>>(
       queries, visible, R, m, const_cast<uint16_t *>(p.queries_bf16), const_cast<float *>(p.norms), flags,
-      const_cast<int32_t *>(p.tile_visible), top_p, sampled ? lsa::kScanMinVisible : INT32_MAX, radius, taken,
-      retry_visible,
+      const_cast<int32_t *>(p.tile_visible), top_p, lsa::kScanMinVisible, radius, taken, retry_visible,
       reinterpret_cast<int32_t *>(base + w.retry_keep));
   LSA_LAUNCH_CHECK();
-  if (sampled) {
+  {
     int rc = lsa::launch_scan_survivors(p, padded, s);
     if (rc != LSA_OK) return rc;
     const int room = p.room;

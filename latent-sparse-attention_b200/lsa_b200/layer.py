@@ -258,9 +258,12 @@ class FlatLayer:
             keys = self._buffer("keys", (R, d.top_p), torch.int64, dev)
             picked = self._buffer("picked", (R, d.top_p), torch.int32, dev)
         with probe.region("select"):
-            if index.centroids_bf16 is not None and R >= self.scan_rows and d.top_p <= 512:
-                bound = 0 if last_position is None else \
-                    last_position // d.cluster_block_size * d.block_bucket_count
+            bound = 0 if last_position is None else last_position // d.cluster_block_size * d.block_bucket_count
+            bound = min(bound or b.bucket_centroids.shape[0], b.bucket_centroids.shape[0])
+            # (the scan's threshold rests on 512 samples of a row's scores: it needs a thousand buckets in sight, and
+            # the kept ones to be a fair share of them - else the exact scan, at once)
+            if index.centroids_bf16 is not None and R >= self.scan_rows and d.top_p <= 512 and bound >= 1024 \
+                    and 3 * d.top_p * 512 >= 8 * bound:
                 need = ops.query("lsa_scan_select_workspace_bytes", R, d.top_p, b.bucket_centroids.shape[0])
                 work = self._buffer("scan", (need,), torch.uint8, dev)
                 _, picked = ops.scan_select(index_queries, b.bucket_centroids, index.centroids_bf16, visible, d.top_p,
