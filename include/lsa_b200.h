@@ -174,29 +174,31 @@ int lsa_flat_select(const float *queries, int64_t R, int d, const float *centroi
 
 /* The same search with the scan on the tensor cores: the result is lsa_flat_select's, key for key. The bf16
  * scores of every (row, bucket) pair are made in tensor memory by tcgen05 products and never written; a row keeps
- * the buckets at or above a threshold bisected from 512 strided samples of its own scores, less a margin that
- * covers the bf16 rounding; the few hundred survivors are rescored with lsa_flat_select's exact fp32 dot and
- * the best top_p kept. A row is accepted only when its worst pick is at or above the threshold (then no dropped
- * bucket could have displaced it); any other row - and every row that sees fewer than 1,024 buckets - is scanned
- * exactly, so the outcome never depends on the threshold being well chosen.
+ * the buckets whose score, plus the bucket's own bf16 error bound, reaches a threshold bisected from 512 strided
+ * samples of its scores; of the few hundred survivors those that can still be among the best top_p by their bounds
+ * are rescored with lsa_flat_select's exact fp32 dot and the best top_p kept. A row is accepted only when top_p
+ * survivors are sure to score the threshold or more (then no dropped bucket could have displaced one); any other
+ * row - and every row that sees fewer than 1,024 buckets - is scanned exactly, so the outcome never depends on the
+ * threshold being well chosen.
  * Reference: the Blackwell bucket scan (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836), its
  * sampled thresholds (src/lsa/core/kernels/scan_select.py:228-271) and ScanSelect's exact rescoring
  * (src/lsa/core/kernels/scan_select.py:189-385).
  *   centroids_bf16 [m, 64] the scan's N operand: the centroids LESS A COMMON CENTRE, rounded to bf16 - a query's
  *                score against the centre is the same for every bucket, so the ranking is the centroids' own, and
- *                the bf16 error shrinks with the rows' length. lsa_scan_centre makes it, a run of rows at a time
- *                as an index grows: centre [64] fp32 or NULL (none), radius [1] fp32 zeroed once by the caller and
- *                raised to the greatest length of a row it wrote. d = 64, top_p <= 512
- *   radius       [1] fp32 on the device, at least the length of every row of centroids less the centre; NULL = 1
- *                (centroids no longer than 1 and no centre: the plain bf16 rounding of lsa_bucket_table)
+ *                a bucket's bf16 error shrinks with the length of its row. lsa_scan_centre makes it, a run of rows
+ *                at a time as an index grows: centre [64] fp32 or NULL (none); lengths [rows] fp32 out, the length
+ *                of each row it wrote; radius [1] fp32, zeroed once by the caller and raised to the greatest of them
+ *   lengths      [m] fp32 as lsa_scan_centre wrote them (every bucket's own error bound), with radius [1] fp32 on the
+ *                device; both NULL = rows no longer than 1 (the plain bf16 rounding of lsa_bucket_table's centroids).
+ *                d = 64, top_p <= 512
  *   max_visible  the host's bound on visible[] (<= 0: m) - it sets how far apart the samples lie
  *   status       (may be NULL) raised if a bounded on-chip wait gives up; the rows it cut are scanned exactly
  *   workspace    lsa_scan_select_workspace_bytes(R, top_p, m), 256-byte aligned */
 int lsa_scan_centre(const float *centroids, int64_t rows, int d, const float *centre, uint16_t *out_bf16,
-                    float *radius, void *stream);
+                    float *lengths, float *radius, void *stream);
 size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m);
 int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids, const uint16_t *centroids_bf16,
-                    const float *radius, int64_t m, const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                    const float *lengths, const float *radius, int64_t m, const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
                     int max_visible, int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
                     size_t workspace_bytes, void *stream);
 

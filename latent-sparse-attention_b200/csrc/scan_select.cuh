@@ -7,19 +7,18 @@ namespace lsa {
 
 constexpr int kScanRoom = 2048;        // survivors a row can hold over all its lists
 constexpr int kScanMinVisible = 1024;  // rows that see fewer buckets take the exact scan (it is cheap there)
-constexpr int kScanRetry = 64;         // rows a call can hand to the split exact scan; any more take the plain one
-// With both operands rounded to bf16 and fp32 accumulation, a score of a query q against a row no longer than rho
-// lies within |q| * rho * (2^-8 + 2^-16) of the real dot: kScanEps * |q| * rho bounds that with room to spare, and
-// kScanAbsolute * kScanEps * |q| more covers the rounding of the fixed-order fp32 dots the picks are ranked by.
-// The rows the scan multiplies are the centroids LESS A COMMON CENTRE (a query's score against the centre is the
-// same for every bucket, so the ranking is the same); rho is the greatest length of such a row, and where the
-// index vectors lie in a narrow cone it is a fraction of 1.
+constexpr int kScanRetry = 128;        // rows a call can hand to the split exact scan; any more take the plain one
+// With both operands rounded to bf16 and fp32 accumulation, the score of a query q against a row of length rho lies
+// within |q| * rho * (2^-8 + 2^-16) of the real dot: |q| * (rho * kScanEps + kScanAbsolute) bounds that with room to
+// spare, the absolute part covering the rounding of the fixed-order fp32 dots the picks are ranked by. The rows the
+// scan multiplies are the centroids LESS A COMMON CENTRE (a query's score against the centre is the same for every
+// bucket, so the ranking is the same), and EVERY BUCKET CARRIES ITS OWN rho: where the index vectors lie in a narrow
+// cone most rows are short and their scores sharp, and the odd long one only widens its own interval.
 constexpr float kScanEps = 1.0f / 240.0f;
-constexpr float kScanAbsolute = 0.0025f;
-// A list takes every bucket within kScanMargin * |q| * rho below the row's threshold, so that the band the pick has
-// to rescore (2 * kScanEps * |q| * rho below the top_p-th bf16 score) lies inside the lists whenever that score
-// reaches the threshold.
-constexpr float kScanMargin = 1.0f / 64.0f;
+constexpr float kScanAbsolute = 1e-5f;
+
+// The slack of a bucket's score, per unit of |q|.
+__host__ __device__ __forceinline__ float scan_slack(float rho) { return fmaf(rho, kScanEps, kScanAbsolute); }
 
 struct ScanParams {
   const uint16_t *queries_bf16;    // [rows padded to 128, 64]
@@ -28,9 +27,11 @@ struct ScanParams {
   const int32_t *row_keep;         // [R] or NULL
   int32_t *flags;                  // [R]: nonzero = the row takes the exact scan (the scan itself flags a row whose
                                    // samples say that more buckets would reach its bar than the pick has room for)
-  const float *norms;              // [R] lengths of the query rows times (rho + kScanAbsolute): the scale of every margin
+  const float *norms;              // [R] lengths of the query rows
+  const float *lengths;            // [m] length of every row of the operand (a bucket's rho), or NULL: all `radius`
+  const float *radius;             // [1] the greatest of them, or NULL: 1
   const int32_t *tile_visible;     // [rows / 128] the widest visible count among a tile's unflagged rows
-  float *bars;                     // [R] the score a bucket had to reach to be listed (threshold less the margin)
+  float *bars;                     // [R] the row's threshold: a bucket is listed when its score plus its slack reaches it
   int32_t *counts;                 // [R, lists] survivors found (past `cap`: the list overflowed)
   int2 *survivors;                 // [R, lists, cap] (bits of the bf16-operand score, bucket); lists = 2 * spans
   int32_t *status;

@@ -179,6 +179,7 @@ __global__ void __launch_bounds__(kScanThreads, 1)
     int visible_now = visible;  // 0 once the row is handed to the exact scan
     const int keep = live ? (p.row_keep ? min(p.row_keep[row], p.keep) : p.keep) : 0;
     const float norm = live ? p.norms[row] : 0.0f;
+    const float widest_rho = p.radius ? *p.radius : 1.0f;
     // ---- the threshold: the value that `target` of the row's visible samples reach. Whatever the waits say, every
     // step below is walked by both warps of a quarter, so neither is left at their barrier.
     bool alive = true;
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(kScanThreads, 1)
     const int target = min(samples, max(1, (int)(((int64_t)p.factor * keep * samples + visible - 1) /
                                                    max(visible, 1))));
     const int mine = min(max(samples - half * 256, 0), 256);  // of this thread's 256 sample columns, those that count
-    float lo = -1.001f * norm - 1e-30f, hi = 1.001f * norm + 1e-30f;
+    float lo = -1.001f * norm * widest_rho - 1e-30f, hi = 1.001f * norm * widest_rho + 1e-30f;
 #pragma unroll 1
     for (int it = 0; it < kScanBisections; ++it) {
       const float mid = 0.5f * (lo + hi);
@@ -217,11 +218,13 @@ __global__ void __launch_bounds__(kScanThreads, 1)
     }
     SCAN_TRACE(warp == 2 && lane == 0, 5, 2);
     const float threshold = live && samples > 0 ? lo : INFINITY;
-    const float bar_score = threshold - norm * kScanMargin;  // what a bucket has to reach to be listed
+    // A bucket is listed when its score PLUS ITS OWN SLACK reaches the threshold: whatever the scan drops has a
+    // true score under the threshold.
+    const float bar_score = threshold;
     if (span == 0 && half == 0 && row < p.R) p.bars[row] = bar_score;
-    // How many buckets would be listed, by the samples: where the row's scores lie so close together that the margin
-    // takes in far more than the pick has room for (half as much again: the estimate is a noisy one), listing them is
-    // wasted work and the row is flagged here and now.
+    // How many buckets would be listed, by the samples (less a typical slack): where the row's scores lie so close
+    // together that far more reach the threshold than the pick has room for (half as much again: the estimate is a
+    // noisy one), listing them is wasted work and the row is flagged here and now.
     {
       int reach = 0;
 #pragma unroll 1
@@ -230,7 +233,7 @@ __global__ void __launch_bounds__(kScanThreads, 1)
         tmem_load_32(lane_addr + half * 256 + c, v);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int i = 0; i < 32; ++i) reach += (c + i < mine) & (__uint_as_float(v[i]) >= bar_score);
+        for (int i = 0; i < 32; ++i) reach += (c + i < mine) & (__uint_as_float(v[i]) >= bar_score - norm * scan_slack(0.5f * widest_rho));
       }
       count_s[0][half][in_tile] = reach;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
@@ -274,15 +277,21 @@ __global__ void __launch_bounds__(kScanThreads, 1)
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         // Which of the 32 scores reach the bar, as a word of bits; the scores themselves go to shared memory (a
         // column a row of 32 lanes, so no two lanes share a bank), where a hit's score can be read by its column.
+        // (lane l fetches bucket l's length; every lane then takes each bucket's by shuffle)
+        const int mine_id = id0 + c + lane;
+        const float rho_l = p.lengths ? (mine_id < p.m ? __ldg(p.lengths + mine_id) : 0.0f) : widest_rho;
+        const float slack_l = scan_slack(rho_l);
         uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           stage[(i + 0) * 32] = v[i + 0], stage[(i + 1) * 32] = v[i + 1];
           stage[(i + 2) * 32] = v[i + 2], stage[(i + 3) * 32] = v[i + 3];
-          m0 |= (__uint_as_float(v[i + 0]) >= bar_score ? 1u : 0u) << (i + 0);
-          m1 |= (__uint_as_float(v[i + 1]) >= bar_score ? 1u : 0u) << (i + 1);
-          m2 |= (__uint_as_float(v[i + 2]) >= bar_score ? 1u : 0u) << (i + 2);
-          m3 |= (__uint_as_float(v[i + 3]) >= bar_score ? 1u : 0u) << (i + 3);
+          const float s0 = __shfl_sync(0xffffffffu, slack_l, i + 0), s1 = __shfl_sync(0xffffffffu, slack_l, i + 1);
+          const float s2 = __shfl_sync(0xffffffffu, slack_l, i + 2), s3 = __shfl_sync(0xffffffffu, slack_l, i + 3);
+          m0 |= (fmaf(s0, norm, __uint_as_float(v[i + 0])) >= bar_score ? 1u : 0u) << (i + 0);
+          m1 |= (fmaf(s1, norm, __uint_as_float(v[i + 1])) >= bar_score ? 1u : 0u) << (i + 1);
+          m2 |= (fmaf(s2, norm, __uint_as_float(v[i + 2])) >= bar_score ? 1u : 0u) << (i + 2);
+          m3 |= (fmaf(s3, norm, __uint_as_float(v[i + 3])) >= bar_score ? 1u : 0u) << (i + 3);
         }
         const int seen = visible_now - (id0 + c);  // of these 32 buckets, those the row sees
         uint32_t hits = (m0 | m1) | (m2 | m3);

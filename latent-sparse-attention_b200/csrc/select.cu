@@ -115,36 +115,8 @@ __device__ uint64_t block_kth_greatest(const int64_t *buf, int n, int k, int *hi
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint64_t prefix = 0, mask = 0;
   int remaining = k;
-  // The leading bytes every key shares need no pass (counting them would send every key to one bin, one atomic
-  // after the other): the AND and the OR of all keys, folded by the warps and then through two shared words.
-  __shared__ unsigned long long every_s, any_s;
-  if (tid == 0) every_s = ~0ull, any_s = 0ull;
-  __syncthreads();
-  {
-    uint64_t every = ~0ull, any = 0;
-    for (int i = tid; i < n; i += kSelThreads) {
-      const uint64_t u = key_radix(buf[i]);
-      every &= u, any |= u;
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      every &= __shfl_xor_sync(0xffffffffu, every, o);
-      any |= __shfl_xor_sync(0xffffffffu, any, o);
-    }
-    if (lane == 0) {
-      atomicAnd(&every_s, (unsigned long long)every);
-      atomicOr(&any_s, (unsigned long long)any);
-    }
-  }
-  __syncthreads();
-  const uint64_t every = every_s, differ = every_s ^ any_s;
   for (int byte = 7; byte >= 0; --byte) {
     const int shift = byte * 8;
-    if ((differ >> shift) == 0) {  // (this byte and all above it are shared)
-      prefix |= every & ((uint64_t)0xFF << shift);
-      mask |= (uint64_t)0xFF << shift;
-      continue;
-    }
     hist[tid] = 0;  // kSelThreads == kHistBins
     __syncthreads();
     for (int i = tid; i < n; i += kSelThreads) {
@@ -344,22 +316,15 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
           if (vec_row[i] >= 0) row = vec_row[i];
         if (row >= 0) {
           const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + row * p.d);
-          // sixteen dims' loads in flight at a time (a vector of 64 dims: all of it), added in dim order
-          for (int k0 = 0; k0 < p.d / 4; k0 += 4) {
-            float4 v[4];
+          for (int k4 = 0; k4 < p.d / 4; ++k4) {
+            const float4 v = __ldg(v4 + k4);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = k0 + j < p.d / 4 ? __ldg(v4 + k0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (k0 + j >= p.d / 4) break;
-#pragma unroll
-              for (int i = 0; i < RB; ++i) {
-                const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + (k0 + j) * 4);
-                acc[i] = fmaf(q.x, v[j].x, acc[i]);
-                acc[i] = fmaf(q.y, v[j].y, acc[i]);
-                acc[i] = fmaf(q.z, v[j].z, acc[i]);
-                acc[i] = fmaf(q.w, v[j].w, acc[i]);
-              }
+            for (int i = 0; i < RB; ++i) {
+              const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
+              acc[i] = fmaf(q.x, v.x, acc[i]);
+              acc[i] = fmaf(q.y, v.y, acc[i]);
+              acc[i] = fmaf(q.z, v.z, acc[i]);
+              acc[i] = fmaf(q.w, v.w, acc[i]);
             }
           }
         }
@@ -368,33 +333,13 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
         for (int i = 0; i < RB; ++i) {
           if (vec_row[i] < 0) continue;
           const float4 *v4 = reinterpret_cast<const float4 *>(p.vectors + vec_row[i] * p.d);
-          if (p.d == 64) {  // (the served index dim: the whole vector's loads in flight at once)
-            float4 v[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __ldg(v4 + j);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float4 q = *reinterpret_cast<const float4 *>(qs + i * 64 + j * 4);
-              acc[i] = fmaf(q.x, v[j].x, acc[i]);
-              acc[i] = fmaf(q.y, v[j].y, acc[i]);
-              acc[i] = fmaf(q.z, v[j].z, acc[i]);
-              acc[i] = fmaf(q.w, v[j].w, acc[i]);
-            }
-            continue;
-          }
-          for (int k0 = 0; k0 < p.d / 4; k0 += 4) {
-            float4 v[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = k0 + j < p.d / 4 ? __ldg(v4 + k0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (k0 + j >= p.d / 4) break;
-              const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + (k0 + j) * 4);
-              acc[i] = fmaf(q.x, v[j].x, acc[i]);
-              acc[i] = fmaf(q.y, v[j].y, acc[i]);
-              acc[i] = fmaf(q.z, v[j].z, acc[i]);
-              acc[i] = fmaf(q.w, v[j].w, acc[i]);
-            }
+          for (int k4 = 0; k4 < p.d / 4; ++k4) {
+            const float4 v = __ldg(v4 + k4);
+            const float4 q = *reinterpret_cast<const float4 *>(qs + i * p.d + k4 * 4);
+            acc[i] = fmaf(q.x, v.x, acc[i]);
+            acc[i] = fmaf(q.y, v.y, acc[i]);
+            acc[i] = fmaf(q.z, v.z, acc[i]);
+            acc[i] = fmaf(q.w, v.w, acc[i]);
           }
         }
       }
@@ -684,9 +629,8 @@ namespace lsa {
 __global__ void __launch_bounds__(128)
     scan_prepare_kernel(const float *__restrict__ queries, const int32_t *__restrict__ visible, int64_t R, int64_t m,
                         uint16_t *__restrict__ q_bf16, float *__restrict__ norms, int32_t *__restrict__ flags,
-                        int32_t *__restrict__ tile_visible, int keep, int min_visible, const float *__restrict__ radius,
-                        int32_t *__restrict__ taken, int32_t *__restrict__ retry_visible,
-                        int32_t *__restrict__ retry_keep) {
+                        int32_t *__restrict__ tile_visible, int keep, int min_visible, int32_t *__restrict__ taken,
+                        int32_t *__restrict__ retry_visible, int32_t *__restrict__ retry_keep) {
   __shared__ int widest_s;
   const int64_t row = (int64_t)blockIdx.x * 128 + threadIdx.x;
   if (threadIdx.x == 0) widest_s = 0;
@@ -710,7 +654,7 @@ __global__ void __launch_bounds__(128)
   if (row < R) {
     const int v = min(max(visible[row], 0), (int)m);
     const bool exact = v < min_visible || !(ss > 0.0f) || !isfinite(ss);
-    norms[row] = sqrtf(ss) * ((radius ? *radius : 1.0f) + kScanAbsolute);
+    norms[row] = sqrtf(ss);
     flags[row] = exact ? 1 : 0;
     if (!exact) atomicMax(&widest_s, v);
   }
@@ -718,13 +662,13 @@ __global__ void __launch_bounds__(128)
   if (threadIdx.x == 0) tile_visible[blockIdx.x] = widest_s;
 }
 
-// After the scan: a warp a row. The survivors' bf16-operand scores say which of them can matter: with s the keep-th
-// greatest of them, at least `keep` buckets have a true score of s - eps or more, and a bucket whose bf16 score is
-// under s - 2 eps has a true score under s - eps, so it is not among the best `keep`. Whatever the scan dropped
-// scored under the row's bar, so if s - 2 eps reaches the bar the buckets at or above s - 2 eps are all in the lists:
-// those are rescored with the exact fixed-order fp32 dot and the best `keep` of them are the row's picks, key for
-// key what scoring every bucket would give. A row that cannot be proven - a list overflowed, fewer than `keep`
-// survivors, a band that reaches under the bar - is flagged for an exact scan, which then writes it.
+// After the scan: a warp a row. A survivor's true score lies within its slack of its bf16-operand score. With s the
+// keep-th greatest LOWER bound, at least `keep` buckets truly score s or more, so a bucket whose UPPER bound is under
+// s is not among the best `keep`; whatever the scan dropped has an upper bound under the row's threshold. So when s
+// reaches the threshold, the survivors whose upper bound reaches s are all that can matter: those are rescored with
+// the exact fixed-order fp32 dot and the best `keep` of them are the row's picks, key for key what scoring every
+// bucket would give. A row that cannot be proven - a list overflowed, fewer than `keep` survivors, s under the
+// threshold - is flagged for an exact scan, which then writes it.
 __global__ void __launch_bounds__(kSelThreads)
     scan_pick_kernel(ScanParams p, const float *__restrict__ queries, const float *__restrict__ centroids,
                      int32_t *__restrict__ flags, int id_base, int room, int64_t *__restrict__ keys_out,
@@ -739,6 +683,8 @@ __global__ void __launch_bounds__(kSelThreads)
   const int lists = 2 * p.spans;
   int total = 0;
   bool proven = true;
+  const float norm = p.norms[row];
+  const float uniform = scan_slack(p.radius ? *p.radius : 1.0f);
   for (int l = 0; l < lists; ++l) {
     const int found = p.counts[row * lists + l];
     proven &= found <= p.cap && total + found <= room;
@@ -746,7 +692,9 @@ __global__ void __launch_bounds__(kSelThreads)
     const int2 *list = p.survivors + (row * lists + l) * p.cap;
     for (int j = lane; j < n; j += 32) {
       const int2 e = list[j];
-      buf[total + j] = pack_key(__int_as_float(e.x), e.y);
+      // keyed by the LEAST its true score can be
+      const float slack = norm * (p.lengths ? scan_slack(__ldg(p.lengths + e.y)) : uniform);
+      buf[total + j] = pack_key(__int_as_float(e.x) - slack, e.y);
     }
     total += n;
   }
@@ -754,7 +702,9 @@ __global__ void __launch_bounds__(kSelThreads)
   proven &= total >= keep;
   if (keep == 0) total = 0;  // (a row whose budget is nothing)
   if (proven && keep > 0) {
-    // the keep-th greatest bf16 score, and the band under it that has to be rescored
+    // s: the keep-th greatest lower bound - at least `keep` buckets truly score s or more, so a bucket whose upper
+    // bound is under s is not among the best `keep`. Whatever the scan dropped has an upper bound under the row's
+    // threshold, so with s at or above the threshold everything that can matter is in the lists.
     const uint64_t kth = total > keep ? warp_kth_greatest(buf, total, keep, hist) : 0;
     int64_t least = INT64_MAX;
     for (int j = lane; j < total; j += 32)
@@ -762,11 +712,16 @@ __global__ void __launch_bounds__(kSelThreads)
     for (int off = 16; off; off >>= 1) least = min(least, __shfl_xor_sync(0xffffffffu, least, off));
     const int32_t bits = (int32_t)(least >> 32);
     const float s = __int_as_float(bits < 0 ? (bits ^ 0x7FFFFFFF) : bits);
-    const float low = s - 2.0f * kScanEps * p.norms[row];
-    proven = low >= p.bars[row];
+    proven = s >= p.bars[row];
     if (proven) {
-      const int64_t low_key = pack_key(low, 0x7FFFFFFF);  // (the least key of that score)
-      total = warp_compact(buf, 0, total, 0, [low_key](int64_t key) { return key >= low_key; });
+      // keep the buckets whose upper bound (the lower one plus twice the slack) reaches s
+      const float *lengths = p.lengths;
+      total = warp_compact(buf, 0, total, 0, [s, norm, uniform, lengths](int64_t key) {
+        const int32_t b = (int32_t)(key >> 32);
+        const float low = __int_as_float(b < 0 ? (b ^ 0x7FFFFFFF) : b);
+        const float slack = norm * (lengths ? scan_slack(__ldg(lengths + key_id(key))) : uniform);
+        return fmaf(2.0f, slack, low) >= s;
+      });
       const float *q = queries + row * 64;
       for (int j = lane; j < total; j += 32) {
         const int32_t id = key_id(buf[j]);
@@ -896,7 +851,7 @@ namespace lsa {
 // of such a row (kept as the bits of a non-negative float, which order as integers do).
 __global__ void __launch_bounds__(256)
     scan_centre_kernel(const float *__restrict__ centroids, int64_t rows, const float *__restrict__ centre,
-                       uint16_t *__restrict__ out, float *__restrict__ radius) {
+                       uint16_t *__restrict__ out, float *__restrict__ lengths, float *__restrict__ radius) {
   const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   float ss = 0.0f;
@@ -912,20 +867,22 @@ __global__ void __launch_bounds__(256)
     }
     *reinterpret_cast<uint4 *>(out + row * 64 + k) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   }
-  if (radius) atomicMax(reinterpret_cast<int *>(radius), __float_as_int(sqrtf(ss) * 1.000001f));
+  const float length = sqrtf(ss) * 1.000001f;
+  if (lengths) lengths[row] = length;
+  if (radius) atomicMax(reinterpret_cast<int *>(radius), __float_as_int(length));
 }
 
 }  // namespace lsa
 
 LSA_API int lsa_scan_centre(const float *centroids, int64_t rows, int d, const float *centre, uint16_t *out_bf16,
-                            float *radius, void *stream) {
+                            float *lengths, float *radius, void *stream) {
   LSA_REQUIRE(centroids && out_bf16, LSA_ERR_NULL);
   LSA_REQUIRE(rows >= 0, LSA_ERR_ARGUMENT);
   LSA_REQUIRE(d == 64, LSA_ERR_UNSUPPORTED);
   LSA_REQUIRE(((uintptr_t)out_bf16 % 16) == 0, LSA_ERR_ARGUMENT);
   if (rows == 0) return LSA_OK;
   lsa::scan_centre_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, (cudaStream_t)stream>>>(centroids, rows, centre,
-                                                                                            out_bf16, radius);
+                                                                                            out_bf16, lengths, radius);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -936,11 +893,13 @@ LSA_API size_t lsa_scan_select_workspace_bytes(int64_t R, int top_p, int64_t m) 
 }
 
 LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float *centroids,
-                            const uint16_t *centroids_bf16, const float *radius, int64_t m, const int32_t *visible,
+                            const uint16_t *centroids_bf16, const float *lengths, const float *radius, int64_t m,
+                            const int32_t *visible,
                             const int32_t *row_top_p, int top_p, int32_t bucket_id_base, int max_visible,
                             int64_t *keys_out, int32_t *picked_out, int32_t *status, void *workspace,
                             size_t workspace_bytes, void *stream) {
   LSA_REQUIRE(queries && centroids && centroids_bf16 && visible && (keys_out || picked_out) && workspace, LSA_ERR_NULL);
+  LSA_REQUIRE(!lengths || radius, LSA_ERR_NULL);
   LSA_REQUIRE(R >= 0 && m >= 0 && m < INT32_MAX && top_p >= 1, LSA_ERR_ARGUMENT);
   LSA_REQUIRE(d == 64 && top_p <= 512, LSA_ERR_UNSUPPORTED);
   LSA_REQUIRE(((uintptr_t)queries % 16) == 0 && ((uintptr_t)centroids % 16) == 0 && ((uintptr_t)centroids_bf16 % 16) == 0 &&
@@ -960,6 +919,8 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   int32_t *flags = reinterpret_cast<int32_t *>(base + w.flags);
   p.flags = flags;
   p.norms = reinterpret_cast<float *>(base + w.norms);
+  p.lengths = lengths;
+  p.radius = radius;
   p.tile_visible = reinterpret_cast<int32_t *>(base + w.tile_visible);
   p.bars = reinterpret_cast<float *>(base + w.thresholds);
   p.counts = reinterpret_cast<int32_t *>(base + w.counts);
@@ -972,7 +933,9 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   p.factor = lsa::scan_factor(top_p);
   p.room = lsa::scan_room(top_p);
   const int64_t widest = max_visible > 0 && max_visible < m ? max_visible : m;
-  p.sample_stride = (int)((widest + 511) / 512 > 1 ? (widest + 511) / 512 : 1);
+  // (an odd stride: buckets come in blocks of a power of two, and every 32nd bucket would be the same bucket of every
+  // fourth block - a sample of one kind of bucket, not of the row's scores)
+  p.sample_stride = (int)((widest + 511) / 512 > 1 ? ((widest + 511) / 512) | 1 : 1);
   // The threshold is read off 512 samples of a row's scores: where the buckets a row keeps are too small a share of
   // those it sees for a handful of samples to reach it, the threshold would be noise, and every row is scanned exactly.
   const bool sampled = m >= lsa::kScanMinVisible && (int64_t)p.factor * top_p * 512 >= 8 * widest;
@@ -987,7 +950,7 @@ LSA_API int lsa_scan_select(const float *queries, int64_t R, int d, const float 
   int32_t *retry_visible = reinterpret_cast<int32_t *>(base + w.retry_visible);
   lsa::scan_prepare_kernel<<<(unsigned)(padded / 128), 128, 0, s>>>(
       queries, visible, R, m, const_cast<uint16_t *>(p.queries_bf16), const_cast<float *>(p.norms), flags,
-      const_cast<int32_t *>(p.tile_visible), top_p, lsa::kScanMinVisible, radius, taken, retry_visible,
+      const_cast<int32_t *>(p.tile_visible), top_p, lsa::kScanMinVisible, taken, retry_visible,
       reinterpret_cast<int32_t *>(base + w.retry_keep));
   LSA_LAUNCH_CHECK();
   {

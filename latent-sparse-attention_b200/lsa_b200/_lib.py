@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -37,9 +37,9 @@ SIGNATURES = {
     "lsa_kmeans_update": (_I, [_P, _P, _P, _I, _I, _P, _P]),
     "lsa_gather_sum": (_I, [_P, _I, _P, _I, _L, _I, _I, _L, _P, _P]),
     "lsa_flat_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _I, c_int32, _P, _P, _P]),
-    "lsa_scan_centre": (_I, [_P, _L, _I, _P, _P, _P, _P]),
+    "lsa_scan_centre": (_I, [_P, _L, _I, _P, _P, _P, _P, _P]),
     "lsa_scan_select_workspace_bytes": (_Z, [_L, _I, _L]),
-    "lsa_scan_select": (_I, [_P, _L, _I, _P, _P, _P, _L, _P, _P, _I, c_int32, _I, _P, _P, _P, _P, _Z, _P]),
+    "lsa_scan_select": (_I, [_P, _L, _I, _P, _P, _P, _P, _L, _P, _P, _I, c_int32, _I, _P, _P, _P, _P, _Z, _P]),
     "lsa_dense_scores": (_I, [_P, _L, _I, _P, _P, _I, _I, _P, _L, c_int32, _P, _P, _P]),
     "lsa_flat_select_decode_workspace_bytes": (_Z, [_L, _I, _I]),
     "lsa_flat_select_decode": (_I, [_P, _L, _I, _P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),

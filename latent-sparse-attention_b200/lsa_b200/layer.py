@@ -51,11 +51,11 @@ class FlatIndex:
     scan can use it, its operand: the centroids less a common centre in bf16, and the greatest length of one)."""
 
     def __init__(self, index_keys: torch.Tensor, buckets: Buckets, centroids_bf16: torch.Tensor | None = None,
-                 radius: torch.Tensor | None = None):
+                 lengths: torch.Tensor | None = None, radius: torch.Tensor | None = None):
         self.index_keys = index_keys
         self.buckets = buckets
         self.centroids_bf16 = centroids_bf16
-        self.radius = radius
+        self.lengths, self.radius = lengths, radius
 
 
 class FlatLayer:
@@ -189,6 +189,7 @@ class FlatLayer:
         if d_idx == 64:  # (the operand of the tensor-core scan: centroids less the first blocks' mean, in bf16)
             bufs["centroids bf16"] = make("centroids bf16", (rows, d_idx), torch.bfloat16)
             bufs["centre"], bufs["radius"] = make("centre", (d_idx,), torch.float32), make("radius", (1,), torch.float32)
+            bufs["lengths"] = make("operand lengths", (rows,), torch.float32)
             bufs["radius"].zero_()
             bufs["centred"] = [False]
         return bufs
@@ -196,7 +197,8 @@ class FlatLayer:
     def _index_of(self, bufs: dict) -> FlatIndex:
         d = self.design
         return FlatIndex(bufs["keys"], Buckets(bufs["centroids"], bufs["members"], bufs["sizes"], d.block_bucket_count,
-                                               d.cluster_block_size), bufs.get("centroids bf16"), bufs.get("radius"))
+                                               d.cluster_block_size), bufs.get("centroids bf16"), bufs.get("lengths"),
+                         bufs.get("radius"))
 
     def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
         """Index keys of k [n, ...] = the keys at positions first.., and the pools, Ward labels and bucket table of
@@ -234,7 +236,8 @@ class FlatLayer:
                 if not bufs["centred"][0]:
                     bufs["centre"].copy_(bufs["centroids"][r0:r1].mean(0))
                     bufs["centred"][0] = True
-                ops.scan_centre(bufs["centroids"][r0:r1], bufs["centre"], bufs["centroids bf16"][r0:r1], bufs["radius"])
+                ops.scan_centre(bufs["centroids"][r0:r1], bufs["centre"], bufs["centroids bf16"][r0:r1],
+                                bufs["lengths"][r0:r1], bufs["radius"])
 
     scan_rows = 1024  # from this many rows on, a pick runs its scan on the tensor cores
 
@@ -268,7 +271,8 @@ class FlatLayer:
                 work = self._buffer("scan", (need,), torch.uint8, dev)
                 _, picked = ops.scan_select(index_queries, b.bucket_centroids, index.centroids_bf16, visible, d.top_p,
                                             row_p, max_visible=bound, keys=keys, picked=picked,
-                                            status=self._scan_status, workspace=work, radius=index.radius)
+                                            status=self._scan_status, workspace=work, lengths=index.lengths,
+                                            radius=index.radius)
             else:
                 _, picked = ops.flat_select(index_queries, b.bucket_centroids, visible, d.top_p, row_p, keys=keys,
                                             picked=picked)

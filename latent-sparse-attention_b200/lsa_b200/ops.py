@@ -263,30 +263,33 @@ def dense_scores(index_queries: torch.Tensor, centroids: torch.Tensor, counts: t
 
 
 def scan_centre(centroids: torch.Tensor, centre: torch.Tensor | None = None, out: torch.Tensor | None = None,
-                radius: torch.Tensor | None = None):
+                lengths: torch.Tensor | None = None, radius: torch.Tensor | None = None):
     """The tensor-core scan's N operand: `centroids` [rows, 64] fp32 less `centre` [64] (None: no centre), rounded to
-    bf16 into `out`, and `radius` [1] fp32 raised to the greatest length of a row written (start it at zero; a run of
-    rows at a time as an index grows). Returns (out, radius)."""
+    bf16 into `out`; the length of every row into `lengths` [rows] fp32, and `radius` [1] fp32 raised to the greatest
+    of them (start it at zero; a run of rows at a time as an index grows). Returns (out, lengths, radius)."""
     c = _contig(centroids.float())
     out = torch.empty(c.shape, device=c.device, dtype=torch.bfloat16) if out is None else out
+    lengths = torch.empty(c.shape[0], device=c.device, dtype=torch.float32) if lengths is None else lengths
     radius = torch.zeros(1, device=c.device, dtype=torch.float32) if radius is None else radius
     if out.shape != c.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
         raise ValueError(f"out must be a contiguous bfloat16 {tuple(c.shape)}")
+    if lengths.shape != (c.shape[0],) or lengths.dtype != torch.float32 or not lengths.is_contiguous():
+        raise ValueError(f"lengths must be a contiguous float32 [{c.shape[0]}]")
     call("lsa_scan_centre", ptr(c), c.shape[0], c.shape[1], ptr(None if centre is None else _contig(centre.float())),
-         ptr(out), ptr(radius), stream())
-    return out, radius
+         ptr(out), ptr(lengths), ptr(radius), stream())
+    return out, lengths, radius
 
 
 def scan_select(index_queries: torch.Tensor, centroids: torch.Tensor, centroids_bf16: torch.Tensor,
                 visible: torch.Tensor, top_p: int, row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0,
                 max_visible: int = 0, keys: torch.Tensor | None = None, picked: torch.Tensor | None = None,
                 status: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
-                radius: torch.Tensor | None = None):
+                lengths: torch.Tensor | None = None, radius: torch.Tensor | None = None):
     """`flat_select`'s result with the scan on tcgen05: bf16 scores in tensor memory against a sampled threshold,
     an exact fp32 rescoring of the survivors, and an exact scan of whatever row the survivors cannot prove
     (src/lsa/core/kernels/cutedsl/blackwell/bucket_scan.py:63-836, src/lsa/core/kernels/scan_select.py:189-385).
-    `centroids_bf16` and `radius` come from `scan_centre` (without a radius: the plain bf16 rounding of centroids no
-    longer than 1). `max_visible` is the host's bound on `visible` (0: all of the centroids)."""
+    `centroids_bf16`, `lengths` and `radius` come from `scan_centre` (without them: the plain bf16 rounding of
+    centroids no longer than 1). `max_visible` is the host's bound on `visible` (0: all of the centroids)."""
     q, c, cb = _contig(index_queries.float()), _contig(centroids.float()), _contig(centroids_bf16)
     R, d = q.shape
     if cb.dtype != torch.bfloat16 or cb.shape != c.shape:
@@ -296,7 +299,7 @@ def scan_select(index_queries: torch.Tensor, centroids: torch.Tensor, centroids_
     need = query("lsa_scan_select_workspace_bytes", R, top_p, c.shape[0])
     if workspace is None or workspace.numel() * workspace.element_size() < need:
         workspace = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
-    call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), ptr(radius), c.shape[0],
+    call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), ptr(lengths), ptr(radius), c.shape[0],
          ptr(_contig(visible.to(torch.int32))), ptr(row_top_p), top_p, bucket_id_base, int(max_visible), ptr(keys),
          ptr(picked), ptr(status), ptr(workspace), workspace.numel() * workspace.element_size(), stream())
     return keys, picked

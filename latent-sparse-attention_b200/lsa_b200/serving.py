@@ -193,9 +193,9 @@ class Selector:
         with probe.region("index q scan"):
             centroids = cache.gather(row, seen)
             if S >= self.scan_rows and centroids.shape[1] == 64 and d.top_p <= 512:
-                operand, radius = ops.scan_centre(centroids, centroids.mean(0))
+                operand, lengths, radius = ops.scan_centre(centroids, centroids.mean(0))
                 _, picked = ops.scan_select(index_queries, centroids, operand, visible, d.top_p, max_visible=seen,
-                                            radius=radius)
+                                            lengths=lengths, radius=radius)
             else:
                 _, picked = ops.flat_select(index_queries, centroids, visible, d.top_p)
         with probe.region("expand"):

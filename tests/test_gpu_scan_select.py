@@ -130,13 +130,17 @@ def test_index_vectors_in_a_narrow_cone_are_told_apart_about_their_centre(ops):
     queries = unit_rows(axis + 0.012 * rng.standard_normal((R, 64), dtype=np.float32))
     visible = rng.integers(1024, m + 1, R).astype(np.int32)
     q, c, v = cuda(queries), cuda(cents), cuda(visible)
-    operand, radius = ops.scan_centre(c[:4096], c[:64].mean(0))
-    operand = torch.cat([operand, ops.scan_centre(c[4096:], c[:64].mean(0), radius=radius)[0]])  # as an index grows
-    assert 0.05 < float(radius) < 0.2
+    cents[::97] = unit_rows(axis + 0.06 * rng.standard_normal((len(cents[::97]), 64), dtype=np.float32))  # a few stray far
+    c = cuda(cents)
+    operand, lengths, radius = ops.scan_centre(c[:4096], c[:64].mean(0))
+    later = ops.scan_centre(c[4096:], c[:64].mean(0), radius=radius)  # as an index grows
+    operand, lengths = torch.cat([operand, later[0]]), torch.cat([lengths, later[1]])
+    assert 0.3 < float(radius) < 0.7 and float(lengths.median()) < 0.15
+    assert torch.allclose(lengths, (c - c[:64].mean(0)).norm(dim=1), rtol=1e-4)
     want, _ = ops.flat_select(q, c, v, 64)
-    got, _ = ops.scan_select(q, c, operand, v, 64, radius=radius)
+    got, _ = ops.scan_select(q, c, operand, v, 64, lengths=lengths, radius=radius)
     assert torch.equal(got, want)
-    plain, unit = ops.scan_centre(c)
+    plain, ones, unit = ops.scan_centre(c)
     assert 0.99 < float(unit) < 1.01 and torch.equal(plain, c.bfloat16())
-    got, _ = ops.scan_select(q, c, plain, v, 64, radius=unit)  # (the rows are crowded: scanned exactly)
+    got, _ = ops.scan_select(q, c, plain, v, 64, lengths=ones, radius=unit)  # (the rows are crowded: scanned exactly)
     assert torch.equal(got, want)
