@@ -33,8 +33,17 @@ class TreeDecoder:
         starts, runs = beam_plan(self.hierarchy, self.buckets, [position], self.page_size, self.growth_buckets,
                                  self.start_nodes)
         as_tensor = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
-        self.plan = dict(start=starts[0], runs=[(as_tensor(first), as_tensor(end)) for first, end in runs],
-                         positions=torch.tensor([position], dtype=torch.int64, device=device))
+        fresh = dict(start=starts[0], runs=[(as_tensor(first), as_tensor(end)) for first, end in runs],
+                     positions=torch.tensor([position], dtype=torch.int64, device=device))
+        if self.plan is not None and self.plan["start"] == fresh["start"]:
+            # in place: a step captured in a graph reads these tensors, and follows the position (and a tree that
+            # grows in fixed-address arrays, `GrowingHierarchy`) without being captured again
+            for (first, end), (new_first, new_end) in zip(self.plan["runs"], fresh["runs"]):
+                first.copy_(new_first)
+                end.copy_(new_end)
+            self.plan["positions"].copy_(fresh["positions"])
+        else:  # (a new start level walks another number of beam steps: a graph of the step is captured again)
+            self.plan = fresh
 
     def select(self, q: torch.Tensor):
         """q [1, Hq, dh] bf16 -> (list [1, top_k + window + sink] int32, length [1])."""

@@ -106,6 +106,100 @@ def build_hierarchy(index_keys: torch.Tensor, buckets: Buckets, top_level: int, 
     return Hierarchy(node_centroids, children, node_means, bucket_means, node_bucket_size, block_sizes)
 
 
+class GrowingHierarchy:
+    """A request's hierarchy grown ONLINE, a page end at a time, in tensors whose addresses never move - so a decode
+    step captured in a CUDA graph keeps reading the same arrays while the tree grows under it. What the reference
+    does with `Hierarchy.grow` / `stage` and the `GraphTree` mirror beside it (src/lsa/sglang/index/hierarchy.py:
+    246-476, src/lsa/sglang/index/graph_tree.py:54-330); here the growing tensors are sized once for the longest
+    context, so they are their own mirror.
+
+    A growth pairs whole node cluster blocks in the order they fill, and a block's node buckets depend on nothing but
+    its own children, so after any number of page ends the levels hold exactly the first `made[level]` node buckets of
+    `build_hierarchy` over the full cache (checked in the tests), and `growth_at` counts what each `grow` made.
+    Node centroids are fp32 (the reference stores them in bf16 or fp8: not carried).
+    """
+
+    def __init__(self, index_dim: int, top_level: int, node_bucket_size: int,
+                 node_cluster_block_size: int | Sequence[int], growth_buckets: int, max_buckets: int, device="cuda"):
+        self.node_bucket_size, self.growth_buckets = node_bucket_size, growth_buckets
+        self.block_sizes = per_level(node_cluster_block_size, top_level)
+        if node_bucket_size < 2 or node_bucket_size & (node_bucket_size - 1):
+            raise ValueError(f"node_bucket_size must be a power of two from 2 - got {node_bucket_size}")
+        if any(block % node_bucket_size for block in self.block_sizes):
+            raise ValueError(f"every node_cluster_block_size must be a multiple of {node_bucket_size}")
+        self.covered, self.made, self.closed = 0, [0] * top_level, [0] * top_level
+        rooms, room = [], max_buckets
+        for _ in range(top_level):
+            room //= node_bucket_size
+            rooms.append(max(room, 1))
+        make = lambda rows, cols, dtype: torch.zeros(rows, cols, device=device, dtype=dtype)
+        self.node_centroids = [make(room, index_dim, torch.float32) for room in rooms]
+        self.node_means = [make(room, index_dim, torch.float32) for room in rooms]
+        self.children = [torch.full((room, node_bucket_size), -1, device=device, dtype=torch.int64) for room in rooms]
+        self.key_sums = [make(room, index_dim, torch.float32) for room in rooms]
+        self.key_counts = [torch.zeros(room, device=device, dtype=torch.float32) for room in rooms]
+        self.bucket_means = make(max_buckets, index_dim, torch.float32)
+        # the same counts where a captured step can read them: covered, then made and closed a level
+        self.counts_device = torch.zeros(1 + 2 * top_level, device=device, dtype=torch.int32)
+
+    def _pair(self, level: int, sums: torch.Tensor, counts: torch.Tensor, first_child: int) -> None:
+        """Pair the whole blocks of `sums` [n, d] (children first_child .. of the level below) into node buckets of
+        `level`, appended in block order."""
+        block, size = self.block_sizes[level - 1], self.node_bucket_size
+        blocks = sums.shape[0] // block
+        labels = pair_into_node_buckets(sums.view(blocks, block, -1), size)
+        kids = _rows_of(labels.contiguous(), block // size, size)
+        node_sums = ops.gather_sum(sums.contiguous(), kids)
+        node_counts = counts[kids].sum(1)
+        at, new = self.made[level - 1], kids.shape[0]
+        if at + new > self.children[level - 1].shape[0]:
+            raise RuntimeError(f"level {level} holds {self.children[level - 1].shape[0]} node buckets and {at + new} "
+                               "were made: the hierarchy was sized for a shorter context")
+        self.node_centroids[level - 1][at:at + new] = F.normalize(node_sums, dim=-1)
+        self.node_means[level - 1][at:at + new] = node_sums / node_counts.clamp_min(1)[:, None]
+        self.children[level - 1][at:at + new] = kids + first_child
+        self.key_sums[level - 1][at:at + new] = node_sums
+        self.key_counts[level - 1][at:at + new] = node_counts
+        self.made[level - 1] = at + new
+
+    def grow(self, closed_buckets: int, index_keys: torch.Tensor, buckets: Buckets) -> int:
+        """One page end: with `closed_buckets` buckets of the request closed, pair the full node cluster blocks of
+        uncovered buckets (none while fewer than `growth_buckets` wait) and whatever that fills above. Returns the
+        level-1 node buckets made."""
+        first_block = self.block_sizes[0]
+        blocks = (closed_buckets - self.covered) // first_block
+        if blocks < max(1, self.growth_buckets // first_block):
+            return 0
+        count, before = blocks * first_block, self.made[0]
+        rows = slice(self.covered, self.covered + count)
+        sums = ops.gather_sum(index_keys, buckets.bucket_members[rows])
+        counts = buckets.bucket_sizes[rows].float()
+        self.bucket_means[rows] = sums / counts.clamp_min(1)[:, None]
+        self._pair(1, sums, counts, self.covered)
+        self.covered += count
+        for level in range(2, len(self.block_sizes) + 1):
+            block = self.block_sizes[level - 1]
+            taken = (self.made[level - 2] - self.closed[level - 2]) // block * block
+            if not taken:
+                break
+            first = self.closed[level - 2]
+            self._pair(level, self.key_sums[level - 2][first:first + taken], self.key_counts[level - 2][first:first + taken],
+                       first)
+            self.closed[level - 2] = first + taken
+        self.counts_device.copy_(torch.tensor([self.covered, *self.made, *self.closed], dtype=torch.int32),
+                                 non_blocking=True)
+        return self.made[0] - before
+
+    def counts(self) -> Growth:
+        return Growth(self.covered, list(self.made), list(self.closed))
+
+    def view(self) -> Hierarchy:
+        """The levels as `read_hierarchy` and `TreeDecoder` take them: the whole fixed-address arrays (a read looks at
+        the first `made` rows of each, which `growth_at` counts for its position)."""
+        return Hierarchy(self.node_centroids, self.children, self.node_means, self.bucket_means, self.node_bucket_size,
+                         self.block_sizes)
+
+
 def growth_at(hierarchy: Hierarchy, closed_buckets: int, page_buckets: int, growth_buckets: int) -> Growth:
     """Replay growing at every page end up to `closed_buckets`, from the counts alone. Integer bookkeeping that must
     match the reference count for count, so it is transcribed from it (src/lsa/core/hierarchy.py:165-196)."""

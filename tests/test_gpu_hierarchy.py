@@ -112,3 +112,84 @@ def test_a_beam_step_split_over_ctas_keeps_what_one_cta_keeps():
         a, _ = ops.beam_step(q, buckets.bucket_centroids, want_carried, first, last, 16)
         b, _ = ops.beam_step(q, buckets.bucket_centroids, want_carried, first, last, 16, splits=splits)
         assert torch.equal(a, b)
+
+
+def test_a_tree_grown_a_page_end_at_a_time_is_the_tree_built_at_once_and_a_captured_step_follows_it(oracle):
+    """Online growth in fixed-address arrays: after every page end the levels hold the first `made` node buckets of the
+    tree built over the whole cache, `growth_at` counts them, reads through the growing tree select what reads through
+    the built one select, and a decode step captured in a CUDA graph before the tree grew reads the grown tree."""
+    from lsa_b200 import core, hierarchy
+    from lsa_b200.decode import TreeDecoder
+    from lsa_b200.layer import FlatDesign, FlatLayer
+
+    T, d = 40960, 64
+    raw = mixture(T, d, 48, 0.35, 23)
+    keys = unit_rows(raw)
+    want_buckets = oracle.build_buckets(keys, 4, 16, 32, 512)
+    buckets = core.Buckets(cuda(want_buckets.bucket_centroids), cuda(want_buckets.bucket_members),
+                           cuda(want_buckets.bucket_sizes), 32, 512)
+    m, page_size, page_buckets, growth = T // 16, 4096, 256, 512
+    blocks = (512, 32)
+    built = core.build_hierarchy(cuda(keys), buckets, 2, 4, blocks)
+    grown = hierarchy.GrowingHierarchy(d, 2, 4, blocks, growth, m)
+    addresses = [t.data_ptr() for t in (*grown.node_centroids, *grown.children)]
+    made_any = False
+    for end in range(page_buckets, m + 1, page_buckets):
+        new = grown.grow(end, cuda(keys), buckets)
+        assert grown.counts() == hierarchy.growth_at(built, end, page_buckets, growth)
+        made_any |= new > 0
+        for level in range(2):
+            n = grown.made[level]
+            assert torch.equal(grown.children[level][:n], built.children[level][:n])
+            assert torch.equal(grown.node_centroids[level][:n], built.node_centroids[level][:n])
+            assert torch.equal(grown.node_means[level][:n], built.node_means[level][:n])
+    assert made_any and grown.made[1] > 0 and grown.closed[0] > 0
+    assert addresses == [t.data_ptr() for t in (*grown.node_centroids, *grown.children)]
+    assert grown.counts_device.tolist() == [grown.covered, *grown.made, *grown.closed]
+    assert torch.equal(grown.bucket_means[: grown.covered], built.bucket_means[: grown.covered])
+    rng = np.random.default_rng(4)
+    positions = np.sort(rng.integers(0, T, 48))
+    queries = unit_rows(raw[positions] + 0.4 * rng.standard_normal((48, d), dtype=np.float32))
+    for beam, start in ((4, None), ((6, 3), 16)):
+        want = core.read_hierarchy_counted(cuda(queries), cuda(positions), buckets, built, beam, start, 24, 256, 4, 512,
+                                           page_size, growth)
+        got = core.read_hierarchy_counted(cuda(queries), cuda(positions), buckets, grown.view(), beam, start, 24, 256,
+                                          4, 512, page_size, growth)
+        assert all(torch.equal(a, b) for a, b in zip(got, want))
+
+    # a step captured while the tree covers half the cache keeps reading as the tree grows and the position moves
+    Hq, Hkv, dh = 4, 2, 64
+    gen = torch.Generator().manual_seed(0)
+    k = torch.randn(T, Hkv, dh, generator=gen).bfloat16().cuda()
+    v = torch.randn(T, Hkv, dh, generator=gen).bfloat16().cuda()
+    wq = (torch.randn(Hkv * dh, d, generator=gen) / 11).bfloat16().cuda()
+    wk = (torch.randn(Hkv * dh, d, generator=gen) / 11).bfloat16().cuda()
+    design = FlatDesign(pool_size=4, bucket_size=16, bucket_cap=32, cluster_block_size=512, top_p=24, top_k=256,
+                        sink_size=4, window_size=512)
+    layer = FlatLayer(design, wq, wk, Hq, Hkv, dh)
+    half = hierarchy.GrowingHierarchy(d, 2, 4, blocks, growth, m)
+    first_half = m // 2 // page_buckets * page_buckets
+    for end in range(page_buckets, first_half + 1, page_buckets):
+        half.grow(end, cuda(keys), buckets)
+    decoder = TreeDecoder(layer, buckets, half.view(), 6, None, page_size, growth, splits=4, select_splits=2)
+    q = torch.randn(1, Hq, dh, generator=gen).bfloat16().cuda()
+    early, late = first_half * 16 + 700, T - 5
+    decoder.prepare(early)
+    decoder.step(q, k, v)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = decoder.step(q, k, v)
+    graph.replay()
+    at_early = out.clone()
+    plain = TreeDecoder(layer, buckets, built, 6, None, page_size, growth, splits=4, select_splits=2)
+    plain.prepare(early)
+    assert torch.equal(at_early, plain.step(q, k, v))
+    for end in range(first_half + page_buckets, m + 1, page_buckets):
+        half.grow(end, cuda(keys), buckets)
+    start_before = decoder.plan["start"]
+    decoder.prepare(late)
+    assert decoder.plan["start"] == start_before  # (the same levels: the captured step is still the step)
+    graph.replay()
+    plain.prepare(late)
+    assert torch.equal(out, plain.step(q, k, v))
+    assert not torch.equal(out, at_early)
