@@ -451,16 +451,14 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     q_part = torch.empty(own_rows, Hq, dk, dtype=q.dtype, device="cuda") if world > 1 else q_in
 
     def e2e_step():
+        if world == 1:  # (the copies ride beside the work, a quarter of the chunk at a time)
+            layer.prefill_from_host(q_h, tail_h, first, share, index, out_h)
+            return
         q_part.copy_(q_h, non_blocking=True)
-        if world > 1:
-            env.dist.all_gather_into_tensor(q_in, q_part)
+        env.dist.all_gather_into_tensor(q_in, q_part)
         share[first // world:].copy_(tail_h, non_blocking=True)
-        if world == 1:
-            layer.extend_index(share, first, chunk)
-            layer.prefill_rows(q_in, first, share, index, out_d)
-        else:
-            sharded.extend_index(share, first, chunk)
-            sharded.prefill_rows(q_in, first, share, out_d)
+        sharded.extend_index(share, first, chunk)
+        sharded.prefill_rows(q_in, first, share, out_d)
         out_h.copy_(out_d, non_blocking=True)
 
     for _ in range(min(args.warmup, 3)):

@@ -55,6 +55,8 @@ class LatentLayer(FlatLayer):
         self._buffers = {}
         self._status_slots(device)
         self._reached = []
+        self._copy_in = self._copy_out = None  # the side streams of `prefill_from_host`
+        self._copy_events: list = []
 
     # ---- the maps
 
@@ -127,6 +129,45 @@ class LatentLayer(FlatLayer):
             ops.latent_attend(rows, latent, lists, lengths, self.scale, value_dim=self.value_dim, out=out,
                               warp_mma=warp_mma, status=self._attend_status)
         return out
+
+    def prefill_from_host(self, q_host: torch.Tensor, rows_host: torch.Tensor, start: int, latent: torch.Tensor,
+                          index: FlatIndex, out_host: torch.Tensor, pieces: int = 4) -> torch.Tensor:
+        """A prefill chunk whose queries [n, heads, latent_dim], own latent rows [n, latent_dim] and output
+        [n, heads, value_dim] live in PINNED host memory, the copies overlapped with the work: the latent rows cross
+        first (the chunk's index step needs them all), the queries a piece at a time on a copy stream while the piece
+        before is read, and a piece's output leaves on a second copy stream as soon as it is written. `index` is the
+        layer's own (`build_index`), which the chunk's closing blocks are added to. On return the current stream has
+        waited for the last output copy; synchronise it before reading `out_host`."""
+        dev, n = latent.device, q_host.shape[0]
+        main = torch.cuda.current_stream(dev)
+        if self._copy_in is None:
+            self._copy_in, self._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        step = -(-n // max(1, pieces))
+        spans = [(first, min(n, first + step)) for first in range(0, n, step)]
+        while len(self._copy_events) < 2 * len(spans) + 1:
+            self._copy_events.append(torch.cuda.Event())
+        rows_in, arrived, done = self._copy_events[0], self._copy_events[1::2], self._copy_events[2::2]
+        q = self._buffer("q from host", tuple(q_host.shape), q_host.dtype, dev)
+        out = self._buffer("out to host", tuple(out_host.shape), out_host.dtype, dev)
+        self._copy_in.wait_stream(main)   # the last call's reads of these buffers are over
+        self._copy_out.wait_stream(main)
+        with torch.cuda.stream(self._copy_in):
+            latent[start:start + n].copy_(rows_host, non_blocking=True)
+            rows_in.record(self._copy_in)
+            for i, (first, stop) in enumerate(spans):
+                q[first:stop].copy_(q_host[first:stop], non_blocking=True)
+                arrived[i].record(self._copy_in)
+        main.wait_event(rows_in)
+        self.extend_index(latent, start, n)
+        for i, (first, stop) in enumerate(spans):
+            main.wait_event(arrived[i])
+            self.prefill_rows(q[first:stop], start + first, latent, index, out[first:stop])
+            done[i].record(main)
+            with torch.cuda.stream(self._copy_out):
+                self._copy_out.wait_event(done[i])
+                out_host[first:stop].copy_(out[first:stop], non_blocking=True)
+        main.wait_stream(self._copy_out)
+        return out_host
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, latent: torch.Tensor, index: FlatIndex,
                splits: int = 148, select_splits: int = 16, warp_mma: bool = False) -> torch.Tensor:

@@ -155,3 +155,11 @@ def test_config_4_layer_on_a_cut_of_its_context(oracle):
                                    np.arange(len(ids), dtype=np.int32)[None], np.array([len(ids)]), 0, 0,
                                    W.latent_scale(cfg))
     _close(out1[0].float().cpu().numpy(), want[0, :, :dv], "decode row")
+    # the same chunk from pinned host buffers, a piece at a time with the copies beside the work: the same bits
+    q_h, rows_h = q.cpu().pin_memory(), cache[first:].cpu().pin_memory()
+    out_h = torch.empty(chunk, Hq, dv, dtype=torch.bfloat16).pin_memory()
+    cache[first:].zero_()
+    layer.prefill_from_host(q_h, rows_h, first, cache, index, out_h, pieces=3)
+    torch.cuda.synchronize()
+    layer.check()
+    assert torch.equal(cache[first:].cpu(), rows_h) and torch.equal(out_h, out.cpu())
