@@ -207,8 +207,9 @@ static size_t ward_smem_bytes(int P, int d) {
 
 // ------------------------------------------------------------------------------------------------ bucket table
 
-// One CTA per cluster block. Phase 1: a thread per bucket walks the pools in order and lists its positions.
-// Phase 2: a thread per (bucket, dim) adds the bucket's keys one by one in position order.
+// One CTA per cluster block. Phase 1: a warp per bucket walks the pools in order, 32 at a time, and lists their
+// positions. Phase 2: a thread per (bucket, dim) adds the bucket's keys one by one in position order, eight loads in
+// flight at a time (the order of the additions is what the results are pinned to; the loads may run ahead of it).
 template <typename T>
 __global__ void bucket_table_kernel(const T *__restrict__ index_keys, const int64_t *__restrict__ labels, int P,
                                     int pool_size, int d, int bucket_count, int bucket_cap, int64_t first_position,
@@ -221,33 +222,44 @@ __global__ void bucket_table_kernel(const T *__restrict__ index_keys, const int6
   const int64_t block_keys = (int64_t)P * pool_size;
   const int64_t row0 = block * bucket_count;
   const int64_t *lab = labels + block * P;
-  for (int b = threadIdx.x; b < bucket_count; b += blockDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int b = warp; b < bucket_count; b += warps) {
     int32_t *row = members + (row0 + b) * bucket_cap;
-    int n = 0;
-    bool overflow = false;
-    for (int p = 0; p < P; ++p) {
-      if (lab[p] != b) continue;
-      for (int j = 0; j < pool_size; ++j) {
-        if (n < bucket_cap)
-          row[n++] = (int32_t)(first_position + block * block_keys + (int64_t)p * pool_size + j);
-        else
-          overflow = true;
+    int pools = 0;  // pools of the bucket so far
+    for (int p0 = 0; p0 < P; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < P && lab[p] == b;
+      const unsigned votes = __ballot_sync(0xffffffffu, mine);
+      if (mine) {
+        const int at = (pools + __popc(votes & ((1u << lane) - 1))) * pool_size;
+        for (int j = 0; j < pool_size; ++j)
+          if (at + j < bucket_cap) row[at + j] = (int32_t)(first_position + block * block_keys + (int64_t)p * pool_size + j);
       }
+      pools += __popc(votes);
     }
-    for (int j = n; j < bucket_cap; ++j) row[j] = LSA_PAD;
-    sizes[row0 + b] = n;
-    if (overflow && status) atomicAdd(status, 1);
+    const int64_t listed = (int64_t)pools * pool_size;
+    const int n = (int)(listed < bucket_cap ? listed : bucket_cap);
+    for (int j = n + lane; j < bucket_cap; j += 32) row[j] = LSA_PAD;
+    if (lane == 0) {
+      sizes[row0 + b] = n;
+      if (listed > bucket_cap && status) atomicAdd(status, 1);
+    }
   }
   __syncthreads();
   if (!key_sums && !centroids && !centroids_bf16) return;
   for (int e = threadIdx.x; e < bucket_count * d; e += blockDim.x) {
     const int b = e / d, c = e - b * d;
     const int32_t *row = members + (row0 + b) * bucket_cap;
+    const int n = sizes[row0 + b];
     float acc = 0.0f;
-    for (int j = 0; j < bucket_cap; ++j) {
-      const int32_t pos = row[j];
-      if (pos < 0) break;
-      acc = __fadd_rn(acc, load_as_float<T>(index_keys, (int64_t)(pos - first_position) * d + c));
+    for (int j0 = 0; j0 < n; j0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = j0 + j < n ? load_as_float<T>(index_keys, (int64_t)(row[j0 + j] - first_position) * d + c) : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (j0 + j < n) acc = __fadd_rn(acc, v[j]);
     }
     sums[e] = acc;
     if (key_sums) key_sums[(row0 + b) * d + c] = acc;
