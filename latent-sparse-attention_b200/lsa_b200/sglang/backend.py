@@ -20,7 +20,7 @@ import torch
 from lsa_b200 import ops
 from lsa_b200.constants import Sentinel
 from lsa_b200.sglang import index_space, weights
-from lsa_b200.sglang.layer_index import LayerIndex, Shard
+from lsa_b200.sglang.layer_index import KeySplit, LayerIndex, Shard
 from lsa_b200.sglang.settings import DesignSettings
 
 # Every quadratic layer's indexer, built by the first backend enabled: one index a layer, however many backends read it
@@ -120,13 +120,16 @@ class GroupedQueryIndexer:
 
     def __init__(self, layer_id: int, geometry: index_space.Geometry, design: DesignSettings, backend: Any,
                  shard: Shard | None = None, heads: index_space.HeadShard | None = None,
-                 prefill_chunk: int = 8192, maps: tuple | None = None) -> None:
-        """`maps` = (query map, key map) skips the map file (tests, a server that holds the maps already)."""
-        if heads is not None or (shard is not None and shard.size > 1):
-            raise NotImplementedError("this build indexes a grouped-query layer on a rank that holds every key head "
-                                      "and every KV slot")
+                 check_index: bool = False, prefill_chunk: int = 8192, maps: tuple | None = None,
+                 sum_heads=None) -> None:
+        """`shard`: the slots this rank owns under decode context parallel; `heads`: the heads it holds under tensor
+        parallel, with `sum_heads` the sum across that group; `maps` = (query map, key map) skips the map file (tests,
+        a server that holds the maps already)."""
+        if heads is not None and sum_heads is None:
+            raise ValueError("a rank holding some of the heads needs the sum across its tensor-parallel group")
         self.layer, self.geometry, self.design, self.backend = layer_id, geometry, design, backend
         self.shard, self.heads, self.prefill_chunk, self.maps = shard or Shard(), heads, prefill_chunk, maps
+        self.check_index, self.sum_heads = check_index, sum_heads
         self.index: LayerIndex | None = None
 
     def request_table(self) -> torch.Tensor:
@@ -142,7 +145,8 @@ class GroupedQueryIndexer:
         if buffer.dtype != torch.bfloat16:
             raise NotImplementedError(f"the key and query input reads a bf16 KV cache - this one is {buffer.dtype}, "
                                       "serve kv_cache_dtype auto")
-        return buffer.view(-1, self.geometry.kv_head_count, self.geometry.head_dim)
+        held = self.geometry.kv_head_count if self.heads is None else self.heads.kv_count
+        return buffer.view(-1, held, self.geometry.head_dim)
 
     def ready(self) -> LayerIndex:
         """Build the layer's index once, and return it."""
@@ -152,9 +156,14 @@ class GroupedQueryIndexer:
             if maps is None:
                 maps = weights.read(self.design.serving.projections, self.geometry.key_dim,
                                     self.design.indexer.index_dim, self.geometry.layers)[self.layer]
+            split = None
+            if self.heads is not None:
+                start, stop = self.heads.dims(self.geometry)
+                split = KeySplit(start, stop, self.heads.counts_key, self.sum_heads)
             self.index = LayerIndex(self.design, maps, pool.size + pool.page_size, pool.size, self.request_table,
                                     table.shape[1], self.prefill_chunk, table.device, self.shard,
-                                    key_buffer=self.key_buffer, key_slot=self.geometry.key_slot)
+                                    check_index=self.check_index, key_buffer=self.key_buffer,
+                                    key_slot=self.geometry.key_slot, split=split)
             self.index.writes_pool = False  # `select_and_read` saves a forward's keys before it selects
         return self.index
 
@@ -250,7 +259,13 @@ def indexer_of(backend: Any, layer: Any, forward_batch: Any):
 
 
 def save(backend: Any, layer: Any, k: torch.Tensor, v: torch.Tensor, forward_batch: Any, shard: Shard) -> None:
-    """Write this step's keys and values into the pool at the slots the batch names (backend.py:395-424)."""
+    """Write this step's keys and values into the pool at the slots the batch names (backend.py:395-424). Under a
+    decode group a rank keeps the tokens it owns, at row slot // size, as the engine's pools place them (the pool is
+    handed the ownership mask, as the reference hands it)."""
+    if shard.size > 1:
+        loc = forward_batch.out_cache_loc
+        backend.token_to_kv_pool.set_kv_buffer(layer, loc // shard.size, k, v, dcp_kv_mask=loc % shard.size == shard.rank)
+        return
     backend.token_to_kv_pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v)
 
 

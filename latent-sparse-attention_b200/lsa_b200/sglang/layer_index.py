@@ -5,9 +5,11 @@ A model hands in its input (`KeyAndQuery`), the KV slots its tokens were given a
 lists of KV slots. The keys are in the KV pool already, so the layer keeps no copy of them: an index key is made from
 the pool's slot when the cache needs it (`PoolKeys`), and a prefill indexes its chunk from the keys in hand.
 
-What this build serves is the key-and-query input of a grouped-query or latent pool on one rank. The attention
-input `x`, a pool split over a decode group (`Shard.size > 1`), key heads split over tensor-parallel ranks (`split`)
-and prefix reuse are refused where the reference takes them.
+What this build serves is the key-and-query input of a grouped-query or latent pool: on one rank, with the pool's
+slots split over a decode group (`Shard`: a key is mapped on the rank that owns its slot and the group sums), or with
+the key heads split over tensor-parallel ranks (`KeySplit`: partial index vectors summed across the group, a token's
+index key made once and kept at its KV slot). The attention input `x` and prefix reuse are refused where the
+reference takes them.
 """
 
 from __future__ import annotations
@@ -30,10 +32,36 @@ class Shard:
 
     rank: int = 0
     size: int = 1
+    reduce: Callable[[torch.Tensor], torch.Tensor] | None = None  # sums a tensor across the group, the same on every rank
 
     def __post_init__(self) -> None:
         if not 0 <= self.rank < self.size:
             raise ValueError(f"rank {self.rank} is not in a group of {self.size}")
+
+
+@dataclass(frozen=True)
+class KeySplit:
+    """Which dims of the key and query input a tensor-parallel rank holds, and how to sum its share across the group
+    (`layer_index.py:296-304`)."""
+
+    start: int
+    stop: int
+    counts_key: bool  # whether this rank's key heads are added to the sum: one of the ranks that replicate a head is
+    reduce: Callable[[torch.Tensor], torch.Tensor]
+
+
+class KeyBuffer:
+    """A layer's index keys held at the KV slots [slots, index_dim] fp32: where a rank's pool holds only some of the
+    key heads, a token's index key is made once, as it is written (`layer_index.py:158-232`)."""
+
+    def __init__(self, slot_count: int, index_dim: int, device) -> None:
+        self.keys = torch.zeros(slot_count, index_dim, device=device, dtype=torch.float32)
+
+    def write(self, slots: torch.Tensor, keys: torch.Tensor) -> None:
+        self.keys[slots] = keys
+
+    def read(self, slots: torch.Tensor) -> torch.Tensor:
+        return self.keys[slots]
 
 
 class KeyAndQueryProjection:
@@ -45,14 +73,55 @@ class KeyAndQueryProjection:
     with one head of `key_dim` dims.
     """
 
-    def __init__(self, query_projection: torch.Tensor, key_projection: torch.Tensor, key_slot: KeySlot, device) -> None:
+    def __init__(self, query_projection: torch.Tensor, key_projection: torch.Tensor, key_slot: KeySlot, device,
+                 split: KeySplit | None = None) -> None:
+        """`key_slot` describes the WHOLE input (every key head); under `split` a rank's heads are the rows
+        [split.start, split.stop) of both maps."""
         if query_projection.shape != key_projection.shape or key_projection.shape[0] != key_slot.key_dim:
             raise ValueError(f"the pool's key input is {key_slot.key_dim} dims and the maps read "
                              f"{tuple(key_projection.shape)} and {tuple(query_projection.shape)}")
-        self.key_slot = key_slot
+        self.key_slot, self.split = key_slot, split
         self.key_dim, self.index_dim = int(key_projection.shape[0]), int(key_projection.shape[1])
         self.query_projection = query_projection.to(device=device, dtype=torch.bfloat16).contiguous()
         self.key_projection = key_projection.to(device=device, dtype=torch.bfloat16).contiguous()
+        if split is not None:
+            if not 0 <= split.start < split.stop <= self.key_dim or (split.stop - split.start) % key_slot.width:
+                raise ValueError(f"a rank's share [{split.start}, {split.stop}) must be whole heads of {key_slot.width} "
+                                 f"dims inside the input's {self.key_dim}")
+            self.share_query = self.query_projection[split.start:split.stop].contiguous()
+            self.share_key = self.key_projection[split.start:split.stop].contiguous()
+
+    def split_index(self, key: torch.Tensor, query: torch.Tensor) -> tuple:
+        """Index queries and index keys from the heads this rank holds, summed across the group (`layer_index.py:
+        355-382`): each map is applied to this rank's rows of it (both are linear before the normalise), the two
+        [index_dim] partials travel in ONE sum, and the rows are normalised after - the same on every rank. A rank
+        that replicates another's key heads adds zeros for its key.
+
+        Args:
+            key: This rank's key heads [S, held heads, head_dim] bf16 (or their input [S, share]).
+            query: This rank's query heads [S, held query heads, head_dim] bf16 (or [S, heads, share]).
+
+        Returns:
+            Index queries [S, index_dim] fp32 unit rows, index keys [S, index_dim] fp32 unit rows.
+        """
+        split, slot = self.split, self.key_slot
+        if split is None:
+            raise ValueError("a split index needs the projection's KeySplit")
+        held = (split.stop - split.start) // slot.width
+        if query.dim() == 3 and query.shape[2] == slot.head_dim and query.shape[2] != split.stop - split.start:
+            queries = ops.index_map(query, self.share_query, group=query.shape[1] // held, dh_off=slot.offset,
+                                    dh_used=slot.width, normalize=False)
+        else:
+            queries = ops.index_map(query, self.share_query, group=query.shape[1], normalize=False)
+        if not split.counts_key:
+            keys = torch.zeros_like(queries)
+        elif key.dim() == 3 and key.shape[2] == slot.head_dim:
+            keys = ops.index_map(key, self.share_key, group=1, dh_off=slot.offset, dh_used=slot.width, normalize=False)
+        else:
+            keys = ops.index_map(key.reshape(key.shape[0], 1, -1), self.share_key, normalize=False)
+        index_queries, index_keys = split.reduce(torch.cat([queries, keys], dim=1)).split(self.index_dim, dim=1)
+        unit = torch.nn.functional.normalize
+        return unit(index_queries, dim=-1).contiguous(), unit(index_keys, dim=-1).contiguous()
 
     def _heads(self, x: torch.Tensor) -> bool:
         """Whether a 3-D input is heads as attention holds them (and not [S, heads, key_dim])."""
@@ -83,12 +152,16 @@ class KeyAndQueryProjection:
 class PoolKeys:
     """A layer's index keys, made from the keys the KV pool holds when they are read (`layer_index.py:448-527`)."""
 
-    def __init__(self, key_buffer: Callable[[], torch.Tensor], projection: KeyAndQueryProjection) -> None:
-        self.key_buffer, self.projection = key_buffer, projection
+    def __init__(self, key_buffer: Callable[[], torch.Tensor], projection: KeyAndQueryProjection,
+                 shard: Shard | None = None) -> None:
+        self.key_buffer, self.projection, self.shard = key_buffer, projection, shard or Shard()
 
     def write(self, slots: torch.Tensor, key: torch.Tensor) -> None:
         """Write keys at their KV slots, which attention writes again after the indexer: the key input's dims of
-        each head, or whole heads."""
+        each head, or whole heads. Under a decode group nothing is written: attention writes each key to the rank
+        that owns it, and the batch being indexed is read from the chunk in hand."""
+        if self.shard.size > 1:
+            return
         buffer = self.key_buffer()
         if key.dim() == 3:
             buffer[slots] = key.to(buffer.dtype)
@@ -96,8 +169,17 @@ class PoolKeys:
             self.projection.key_slot.write(buffer, slots, key.to(buffer.dtype))
 
     def read(self, slots: torch.Tensor) -> torch.Tensor:
-        """The index keys at KV slots [S, index_dim] fp32."""
-        return self.projection.index_keys(self.key_buffer()[slots])
+        """The index keys at KV slots [S, index_dim] fp32, whichever rank holds them: under a decode group slot s is
+        row s // size of rank s % size's pool, a key is mapped on the rank that owns it and the group sums - each row
+        has one owner and the others add zeros; every rank calls this with the same slots (`layer_index.py:
+        497-515`)."""
+        if self.shard.size == 1:
+            return self.projection.index_keys(self.key_buffer()[slots])
+        size, rank = self.shard.size, self.shard.rank
+        owned = slots % size == rank
+        rows = torch.where(owned, slots // size, 0)  # (another rank's slot reads row 0 here and is zeroed after)
+        index_keys = self.projection.index_keys(self.key_buffer()[rows])
+        return self.shard.reduce(index_keys * owned[:, None])
 
 
 class KeyLookup:
@@ -143,23 +225,32 @@ class LayerIndex:
             NotImplementedError: A decode group, a tensor-parallel split, a cross-rank head sum or prefix reuse.
         """
         shard = shard or Shard()
-        if shard.size > 1 or split is not None or sum_heads is not None or prefix_reuse or check_index:
-            raise NotImplementedError("this build serves the key-and-query input on one rank: no decode group, no "
-                                      "split of the key heads, no prefix reuse")
-        if key_buffer is None:
+        if sum_heads is not None or prefix_reuse:
+            raise NotImplementedError("this build serves no cross-rank head sum for an MLA latent and no prefix reuse")
+        if shard.size > 1 and shard.reduce is None:
+            raise ValueError("a decode context-parallel shard needs the sum across its group")
+        if split is not None and shard.size > 1:
+            raise ValueError("a rank holding some of the key heads keeps the whole context's index keys itself - "
+                             "decode context parallel splits the slots as well")
+        if split is None and key_buffer is None:
             raise ValueError("the key and query input reads its keys from the KV pool - it needs the pool's key buffer")
         self.settings, self.shard, self.slot_table = settings, shard, slot_table
+        self.check_index = check_index and shard.size > 1
         self.index_dim = settings.indexer.index_dim
         key_slot = key_slot or KeySlot.latent(int(projections[1].shape[0]))
-        self.projection = KeyAndQueryProjection(*projections, key_slot, device)
+        self.projection = KeyAndQueryProjection(*projections, key_slot, device, split)
         if self.projection.index_dim != self.index_dim:
             raise ValueError(f"the maps write {self.projection.index_dim} dims and the design's index has {self.index_dim}")
-        self.buffer = PoolKeys(key_buffer, self.projection)
+        # Where a position's index key is found: mapped from the pool's slot when it is read, or - a rank's pool
+        # holding only some of the key heads - made once as the token is written and kept at its KV slot.
+        self.buffer = KeyBuffer(slot_count, self.index_dim, device) if split is not None else \
+            PoolKeys(key_buffer, self.projection, shard)
         design = settings.indexer.flat_design()
         requests = slot_table().shape[0]
         page_buckets = PAGE_SIZE // design.bucket_size
         request_pages = -(-max_context // PAGE_SIZE) + 1
-        pages = -(-kv_size // PAGE_SIZE) + requests  # (a request's last page is part full)
+        # (under a decode group every rank indexes each request's whole context: the cache covers `size` pools)
+        pages = -(-kv_size * shard.size // PAGE_SIZE) + requests  # (a request's last page is part full)
         cache = BucketCache(design, self.index_dim, pages, page_buckets, requests, request_pages, device)
         self.selector = Selector(cache, 1, slot_table)
         self.prefill_chunk, self.starts_checked = prefill_chunk, False
@@ -175,6 +266,10 @@ class LayerIndex:
             raise TypeError("the attention input reached an index built for the key and query")
         if inputs.key.shape[0] != slots.shape[0]:
             raise ValueError(f"the key and query input has {inputs.key.shape[0]} keys for {slots.shape[0]} slots")
+        if self.projection.split is not None:  # the keys' index keys are made once, here, and kept at their slots
+            index_queries, index_keys = self.projection.split_index(inputs.key, inputs.query)
+            self.buffer.write(slots, index_keys)
+            return index_queries, index_keys
         if self.writes_pool:
             self.buffer.write(slots, inputs.key)
         return self.projection.index_queries(inputs.query), self.projection.index_keys(inputs.key)
@@ -183,6 +278,8 @@ class LayerIndex:
         """Write new tokens' keys at their KV slots and return their index queries."""
         if inputs.key.shape[0] != slots.shape[0]:
             raise ValueError(f"the key and query input has {inputs.key.shape[0]} keys for {slots.shape[0]} slots")
+        if self.projection.split is not None:
+            return self.project(inputs, slots)[0]
         if self.writes_pool:
             self.buffer.write(slots, inputs.key)
         return self.projection.index_queries(inputs.query)
@@ -190,7 +287,10 @@ class LayerIndex:
     def write_chunk(self, inputs: KeyAndQuery, slots: torch.Tensor) -> None:
         """Write a prefill chunk's keys without selecting: a short prompt the dense path prefills. The next
         `maintain` indexes them from the pool."""
-        self.buffer.write(slots, inputs.key)
+        if self.projection.split is not None:
+            self.project(inputs, slots)
+        else:
+            self.buffer.write(slots, inputs.key)
 
     def keys_of(self, row: int, chunk: tuple | None = None) -> KeyLookup:
         return KeyLookup(self.buffer, self.slot_table, row, chunk)
@@ -199,7 +299,16 @@ class LayerIndex:
 
     def maintain(self, rids: Sequence, rows: Sequence, ends: Sequence) -> int:
         """Bring each request's cache up to the keys already in the pool, eagerly, before a forward."""
-        return self.selector.maintain(rids, rows, ends, self.keys_of)
+        closed = self.selector.maintain(rids, rows, ends, self.keys_of)
+        self.check(rows)
+        return closed
+
+    def check(self, rows: Sequence) -> None:
+        """Raise unless every rank of the decode group holds the same index for the requests, when asked to check
+        (`layer_index.py:776-784`)."""
+        if self.check_index and self.shard.reduce is not None:
+            from lsa_b200.sglang.consistency import check_same_index
+            check_same_index(self.selector.cache, rows, self.shard.reduce, self.shard.size)
 
     def extend(self, inputs: KeyAndQuery, positions: torch.Tensor, slots: torch.Tensor, rows: Sequence,
                lengths: Sequence, starts: Sequence) -> torch.Tensor:
@@ -227,6 +336,7 @@ class LayerIndex:
             lists.append(self.selector.prefill(row, index_queries[first:stop], positions[first:stop],
                                                index_keys[first:stop], start))
             first = stop
+        self.check(rows)
         return torch.cat(lists) if lists else torch.empty(0, self.settings.width, device=slots.device,
                                                           dtype=torch.int32)
 

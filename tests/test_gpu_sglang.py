@@ -220,3 +220,121 @@ def test_prefill_and_decode_through_the_hooks(oracle, monkeypatch, tmp_path):
     batch = _batch(True, [rows[1]], ["d"], np.arange(300), table[rows[1], :300], [300], [300])
     plugin.maintain(engine, batch)
     assert cache.end(rows[1]) == 0 and (cache.request_pages[rows[1]] == -1).all()
+
+
+class Fabric:
+    """The ranks of a group in one process: a first pass over the ranks records each one's term, `close` adds them in
+    rank order, and every later call returns that sum - what a collective hands each rank."""
+
+    def __init__(self):
+        self.terms, self.total = [], None
+
+    def reduce(self, term):
+        if self.total is not None:
+            return self.total
+        self.terms.append(term)
+        return term
+
+    def close(self):
+        self.total = self.terms[0]
+        for term in self.terms[1:]:
+            self.total = self.total + term
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_key_heads_split_over_a_tensor_parallel_group_give_the_index_of_one_rank(tp):
+    from lsa_b200.sglang import index_space, settings
+    from lsa_b200.sglang.layer_index import KeyAndQueryProjection, KeySplit, LayerIndex
+
+    geometry = index_space.geometry_of(TEXT)
+    rng = np.random.default_rng(tp)
+    n = 2300
+    rows, table, data, slots_total = _requests([n], rng)
+    q, k = cuda(data[0][0][:n], torch.bfloat16), cuda(data[0][1][:n], torch.bfloat16)
+    wq = torch.from_numpy(bf16_round(rng.standard_normal((geometry.key_dim, D_IDX), dtype=np.float32) / 14))
+    wk = torch.from_numpy(bf16_round(rng.standard_normal((geometry.key_dim, D_IDX), dtype=np.float32) / 14))
+    whole = KeyAndQueryProjection(wq, wk, geometry.key_slot, "cuda")
+    want_q, want_k = whole.index_queries(q), whole.index_keys(k)
+    shards = [index_space.head_shard(geometry, tp, rank) for rank in range(tp)]
+    assert sum(s.counts_key for s in shards) == HKV and sum(s.query_count for s in shards) == HQ
+
+    def inputs_of(rank):
+        s = shards[rank]
+        local_q = q[:, rank * s.query_count:(rank + 1) * s.query_count]
+        return index_space.key_and_query(local_q, k[:, s.kv_first:s.kv_first + s.kv_count], geometry, s)
+
+    fabric = Fabric()
+    projections = [KeyAndQueryProjection(wq, wk, geometry.key_slot, "cuda",
+                                         KeySplit(*s.dims(geometry), s.counts_key, fabric.reduce)) for s in shards]
+    for _ in range(2):
+        index = [p.split_index(inputs_of(r).key, inputs_of(r).query) for r, p in enumerate(projections)]
+        fabric.close()
+    for got_q, got_k in index:  # the same bits on every rank, and the unsplit vectors to rounding
+        assert torch.equal(got_q, index[0][0]) and torch.equal(got_k, index[0][1])
+    assert (index[0][0] - want_q).abs().max() <= 2e-6 and (index[0][1] - want_k).abs().max() <= 2e-6
+    # a layer on such a rank keeps each token's index key at its KV slot, and selects what one rank selects
+    design = settings.parse({**BLOCK, "serving": {"projections": "unused"}})
+    table_d = cuda(table)
+    positions = torch.arange(n, device="cuda")
+    slots = table_d[rows[0], :n].long()
+    pool = torch.zeros(slots_total, HKV, DH, device="cuda", dtype=torch.bfloat16)
+    pool[slots] = k
+    one = LayerIndex(design, (wq, wk), slots_total, slots_total, lambda: table_d, table.shape[1], 8192, "cuda",
+                     key_buffer=lambda: pool, key_slot=geometry.key_slot)
+    want = one.extend(index_space.key_and_query(q, k, geometry), positions, slots, [rows[0]], [n], [0])
+    rank = tp - 1
+    layer = LayerIndex(design, (wq, wk), slots_total, slots_total, lambda: table_d, table.shape[1], 8192, "cuda",
+                       key_slot=geometry.key_slot, split=KeySplit(*shards[rank].dims(geometry),
+                                                                  shards[rank].counts_key, fabric.reduce))
+    got = layer.extend(inputs_of(rank), positions, slots, [rows[0]], [n], [0])
+    assert torch.equal(layer.buffer.read(slots), index[0][1])
+    agree = (got == want).all(1).float().mean().item()
+    assert agree >= 0.995  # (index vectors equal to 2e-6: a near-tie may fall the other way in a row or two)
+
+
+def test_a_decode_group_reads_each_key_on_the_rank_that_owns_its_slot():
+    from lsa_b200.sglang import index_space, settings
+    from lsa_b200.sglang.layer_index import LayerIndex, Shard
+
+    geometry = index_space.geometry_of(TEXT)
+    rng = np.random.default_rng(9)
+    n, size = 2100, 2
+    rows, table, data, slots_total = _requests([n], rng)
+    slots_total += slots_total % size
+    q, k = cuda(data[0][0][: n + 1], torch.bfloat16), cuda(data[0][1][: n + 1], torch.bfloat16)
+    wq = torch.from_numpy(bf16_round(rng.standard_normal((geometry.key_dim, D_IDX), dtype=np.float32) / 14))
+    wk = torch.from_numpy(bf16_round(rng.standard_normal((geometry.key_dim, D_IDX), dtype=np.float32) / 14))
+    design = settings.parse({**BLOCK, "serving": {"projections": "unused"}})
+    table_d = cuda(table)
+    slots = table_d[rows[0], : n + 1].long()
+    pool = torch.zeros(slots_total, HKV, DH, device="cuda", dtype=torch.bfloat16)
+    pool[slots] = k
+    pools = [pool[rank::size].contiguous() for rank in range(size)]  # slot s is row s // size of rank s % size
+    one = LayerIndex(design, (wq, wk), slots_total, slots_total, lambda: table_d, table.shape[1], 8192, "cuda",
+                     key_buffer=lambda: pool, key_slot=geometry.key_slot)
+    group = [LayerIndex(design, (wq, wk), slots_total // size, slots_total // size, lambda: table_d, table.shape[1],
+                        8192, "cuda", Shard(rank, size, lambda term: term), key_buffer=lambda rank=rank: pools[rank],
+                        key_slot=geometry.key_slot) for rank in range(size)]
+
+    def read(at):  # the group's sum, every rank's owned term added in rank order
+        terms = []
+        for rank, layer in enumerate(group):
+            owned = at % size == rank
+            keys = layer.projection.index_keys(pools[rank][torch.where(owned, at // size, 0)])
+            terms.append(keys * owned[:, None])
+        return terms[0] + terms[1]
+
+    assert torch.equal(read(slots[:64]), one.buffer.read(slots[:64]))
+    for layer in group:
+        layer.buffer.read = read
+    with pytest.raises(ValueError, match="needs the sum"):
+        LayerIndex(design, (wq, wk), 8, 8, lambda: table_d, 8, 8, "cuda", Shard(1, 2), key_buffer=lambda: pool)
+    # the keys reach the pools with no indexer call (a cached prefix): every rank indexes them through the group's reads
+    step = index_space.key_and_query(q[n:], k[n:], geometry)
+    position, row = torch.tensor([n], device="cuda"), torch.tensor([rows[0]], device="cuda")
+    one.maintain(["a"], [rows[0]], [n])
+    want = one.decode(step, position, slots[n:], row)
+    for layer in group:
+        layer.maintain(["a"], [rows[0]], [n])
+        assert torch.equal(layer.decode(step, position, slots[n:], row), want)
+        assert layer.selector.cache.buckets_of(rows[0]) == n // 256 * 16

@@ -168,6 +168,61 @@ def test_a_grouped_query_checkpoints_geometry_and_the_heads_a_rank_holds():
     assert torch.allclose(written.query[:, 0], want, atol=1e-5)
 
 
+def test_a_group_whose_ranks_hold_different_indexes_is_told_so_on_every_rank():
+    from lsa_b200.sglang import consistency
+
+    a = torch.arange(12, dtype=torch.float32).view(3, 4)
+    assert int(consistency.checksum(a)) != int(consistency.checksum(a.flip(0)))  # order-sensitive
+    assert int(consistency.checksum(a)) == int(consistency.checksum(a.t().contiguous().t()))  # by value, not by stride
+
+    class Cache:  # what the check reads of a bucket cache
+        def __init__(self, seed):
+            g = torch.Generator().manual_seed(seed)
+            self.centroids, self.members = torch.randn(40, 8, generator=g), torch.randint(0, 999, (40, 6), generator=g)
+            self.sizes, self.closed_keys = torch.randint(1, 6, (40,), generator=g).int(), {2: 64, 5: 32}
+
+        def buckets_of(self, row):
+            return self.closed_keys.get(row, 0) // 8
+
+        def end(self, row):
+            return self.closed_keys.get(row, 0) + 3
+
+        def rows_of(self, row, logical):
+            return logical + 4 * row
+
+    def run(caches):
+        # each rank's two collective calls answered with the true sums of what every rank would send
+        locals_, flags = [], []
+        for cache in caches:
+            sent = []
+            try:
+                consistency.check_same_index(cache, [2, 5], lambda t: (sent.append(t.clone()), t)[1], len(caches))
+            except RuntimeError:
+                pass
+            locals_.append(sent[0])
+        total = sum(locals_[1:], locals_[0])
+        outcomes = []
+        for cache, local in zip(caches, locals_):
+            differs = (total != local * len(caches)).any().float().reshape(1)
+            flags.append(differs)
+        any_differs = sum(flags[1:], flags[0])
+        for cache in caches:
+            answers = iter([total, any_differs])
+            try:
+                consistency.check_same_index(cache, [2, 5], lambda t: next(answers), len(caches))
+                outcomes.append("same")
+            except RuntimeError as failure:
+                assert "different indexes" in str(failure)
+                outcomes.append("differ")
+        return outcomes
+
+    assert run([Cache(0), Cache(0), Cache(0)]) == ["same"] * 3
+    drifted = Cache(0)
+    drifted.members[21, 2] += 1  # one member of one bucket of request 5
+    assert run([Cache(0), drifted, Cache(0)]) == ["differ"] * 3
+    consistency.check_same_index(Cache(0), [], None, 3)  # an empty batch checks nothing
+
+
 def test_lists_split_over_a_decode_group_hold_every_slot_once():
     lists = torch.tensor([[5, 2, 9, 4, -1, -1], [7, -1, -1, -1, -1, -1]], dtype=torch.int32)
     assert backend.list_lengths(lists).tolist() == [4, 1]
