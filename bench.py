@@ -444,22 +444,19 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
 
     # (on several GPUs a rank copies its own rows of the chunk's queries and the ranks all-gather them over NVLink:
     # every rank needs every row, but the host link need carry each row only once)
-    q_h = q[rank * own_rows:(rank + 1) * own_rows].cpu().pin_memory()
+    pieces = 4
+    if world == 1:
+        q_h = q.cpu().pin_memory()
+    else:  # this rank's rows of each of the four pieces the chunk crosses the host link in
+        q_h = q.view(pieces, world, chunk // pieces // world, Hq, dk)[:, rank].reshape(own_rows, Hq, dk).cpu().pin_memory()
     tail_h = (tail if world == 1 else deal(tail, rank, world)).cpu().pin_memory()
     out_h = torch.empty(out_d.shape, dtype=out_d.dtype).pin_memory()
-    q_in = torch.empty_like(q)
-    q_part = torch.empty(own_rows, Hq, dk, dtype=q.dtype, device="cuda") if world > 1 else q_in
 
     def e2e_step():
         if world == 1:  # (the copies ride beside the work, a quarter of the chunk at a time)
             layer.prefill_from_host(q_h, tail_h, first, share, index, out_h)
             return
-        q_part.copy_(q_h, non_blocking=True)
-        env.dist.all_gather_into_tensor(q_in, q_part)
-        share[first // world:].copy_(tail_h, non_blocking=True)
-        sharded.extend_index(share, first, chunk)
-        sharded.prefill_rows(q_in, first, share, out_d)
-        out_h.copy_(out_d, non_blocking=True)
+        sharded.prefill_from_host(q_h, tail_h, first, chunk, share, out_h, pieces=pieces)
 
     for _ in range(min(args.warmup, 3)):
         e2e_step()

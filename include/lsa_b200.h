@@ -36,6 +36,7 @@ extern "C" {
 #define LSA_EMPTY_KEY INT64_MIN       /* the packed key of no bucket (src/lsa/core/kernels/constants.py:29-37) */
 /* lsa_expand flag: leave the window and the sinks out of the list (a dense band kernel reads them instead) */
 #define LSA_EXPAND_NO_LOCAL 1
+#define LSA_EXPAND_NO_PAD 2
 #define LSA_DTYPE_F32 0
 #define LSA_DTYPE_BF16 1
 
@@ -286,7 +287,9 @@ int lsa_beam_step_split(const float *queries, int64_t R, int d, const float *vec
  *              stored as its row in that rank's own cache, id / (granule*world) * granule + id % granule
  *   owner_first/owner_end - only ids in [owner_first, owner_end) are written (a rank's share of the sequence);
  *              the top_k cut still counts every id. Pass 0 and INT64_MAX for all.
- *   flags      0, or LSA_EXPAND_NO_LOCAL to write the expansion alone (the cut and the window filter stay)
+ *   flags      0, or LSA_EXPAND_NO_LOCAL to write the expansion alone (the cut and the window filter stay), and / or
+ *              LSA_EXPAND_NO_PAD to leave the entries past lengths[r] as they were (a caller that reads lists by
+ *              their lengths, as the attention entry points do, saves the write of the padding)
  *   selected   [R, top_k + window + sink] int32 out - expansion, window ascending, sinks ascending, -1 padded
  *   lengths    [R] int32 out
  * --------------------------------------------------------------------------------------------------------- */

@@ -30,15 +30,18 @@ struct ExpandParams {
 // positions round-robin over `world` ranks, in one of its granules.
 __device__ __forceinline__ bool owned(const ExpandParams &p, int64_t id) {
   if (id < p.owner_first || id >= p.owner_end) return false;
-  return p.world <= 1 || (int)((id / p.granule) % p.world) == p.rank;
+  if (p.world <= 1) return true;
+  const uint32_t u = (uint32_t)id;  // (an id fits 31 bits - the lists are int32 - and 32-bit division is the cheap one)
+  return (int)((u / (uint32_t)p.granule) % (uint32_t)p.world) == p.rank;
 }
 
 // What is written for an id: the position, its row in the rank's own cache when granules are dealt out, or its KV
 // slot through the page table.
 __device__ __forceinline__ int32_t stored_id(const ExpandParams &p, const int32_t *table, int64_t id) {
-  if (p.world > 1) id = id / ((int64_t)p.granule * p.world) * p.granule + id % p.granule;
-  if (!table) return (int32_t)id;
-  return table[id / p.page_size] * p.page_size + (int32_t)(id % p.page_size);
+  uint32_t u = (uint32_t)id;
+  if (p.world > 1) u = u / ((uint32_t)p.granule * (uint32_t)p.world) * (uint32_t)p.granule + u % (uint32_t)p.granule;
+  if (!table) return (int32_t)u;
+  return table[u / (uint32_t)p.page_size] * p.page_size + (int32_t)(u % (uint32_t)p.page_size);
 }
 
 // Append the owned ids of [first, end) to out[written..], in order; returns the new count.
@@ -124,7 +127,8 @@ __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams 
     written = append_run(p, table, out, written, window_start, pos + 1, lane);
     written = append_run(p, table, out, written, 0, min((int64_t)p.sink, min(window_start, pos + 1)), lane);
   }
-  for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
+  if (!(p.flags & LSA_EXPAND_NO_PAD))
+    for (int j = written + lane; j < p.width; j += 32) out[j] = LSA_PAD;
   if (lane == 0) {
     p.lengths[r] = written;
     if (bad && p.status) atomicAdd(p.status, bad);
@@ -233,7 +237,8 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
     for (int i = tid; i < sinks; i += kWideThreads) out[total + i] = stored_id(p, table, i);
     total += sinks;
   }
-  for (int j = total + tid; j < p.width; j += kWideThreads) out[j] = LSA_PAD;
+  if (!(p.flags & LSA_EXPAND_NO_PAD))
+    for (int j = total + tid; j < p.width; j += kWideThreads) out[j] = LSA_PAD;
   if (tid == 0) {
     p.lengths[r] = total;
     if (bad_s && p.status) atomicAdd(p.status, bad_s);
@@ -385,7 +390,8 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
     for (int i = gtid; i < sinks; i += gthreads) out[total + i] = stored_id(p, table, i);
     total += sinks;
   }
-  for (int j = total + gtid; j < p.width; j += gthreads) out[j] = LSA_PAD;
+  if (!(p.flags & LSA_EXPAND_NO_PAD))
+    for (int j = total + gtid; j < p.width; j += gthreads) out[j] = LSA_PAD;
   if (tid == 0) {
     if (cta == 0) p.lengths[r] = total;
     if (bad_s && p.status) atomicAdd(p.status, bad_s);

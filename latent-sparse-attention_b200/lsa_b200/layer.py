@@ -290,8 +290,9 @@ class FlatLayer:
             outs = (self._buffer("lists", (R, d.list_width), torch.int32, dev),
                     self._buffer("lengths", (R,), torch.int32, dev), self._expand_status)
         with probe.region("expand"):
+            # (the layer's own buffers are read by their lengths: nothing is padded there)
             lists, lengths, _ = ops.expand(picked, positions, b.bucket_members, d.top_k, d.sink_size, d.window_size,
-                                           row_p, row_k, outs=outs, local=local)
+                                           row_p, row_k, outs=outs, local=local, pad=not reuse_buffers)
         return lists, lengths
 
     def attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, lists: torch.Tensor, lengths: torch.Tensor,

@@ -382,8 +382,10 @@ def beam_step(index_queries: torch.Tensor, vectors: torch.Tensor, carried: torch
 def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor, top_k: int, sink: int, window: int,
            row_top_p: torch.Tensor | None = None, row_top_k: torch.Tensor | None = None,
            page_table: torch.Tensor | None = None, page_size: int = 0, owner: tuple[int, int] | None = None,
-           outs: tuple | None = None, dealt: tuple[int, int, int] | None = None, local: bool = True):
-    """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status)."""
+           outs: tuple | None = None, dealt: tuple[int, int, int] | None = None, local: bool = True,
+           pad: bool = True):
+    """`expand_buckets` for every row (src/lsa/core/reference.py:268-289): (lists, lengths, status). With `pad` off
+    the entries past a row's length are left as they were (a reader that goes by the lengths saves their write)."""
     picked, members = _contig(picked), _contig(members)
     R, top_p = picked.shape
     width = top_k + window + sink
@@ -398,7 +400,8 @@ def expand(picked: torch.Tensor, positions: torch.Tensor, members: torch.Tensor,
     granule, world, rank = dealt if dealt is not None else (1, 1, 0)
     call("lsa_expand", ptr(picked), R, top_p, ptr(_contig(positions.to(torch.int64))), ptr(members),
          members.shape[0], members.shape[1], ptr(row_top_p), ptr(row_top_k), top_k, sink, window, ptr(page_table),
-         page_size, first, end, granule, world, rank, 0 if local else 1, ptr(selected), ptr(lengths), ptr(status), stream())
+         page_size, first, end, granule, world, rank, (0 if local else 1) | (0 if pad else 2), ptr(selected), ptr(lengths),
+         ptr(status), stream())
     return selected, lengths, status
 
 

@@ -455,28 +455,28 @@ class ShardedLatentLayer:
                 keys, _ = ops.flat_select(index_queries, self.centroids, visible, d.top_p)
             return globalise_keys(keys, per_block, rank, world)
 
-    def select(self, rows: torch.Tensor, positions: torch.Tensor) -> tuple:
+    def select(self, rows: torch.Tensor, positions: torch.Tensor, pad: bool = True) -> tuple:
         """This rank's share of every row's read list, as rows of its own cache: (lists, lengths). A collective call
         (the candidates are exchanged inside). Local row l of rank r is position (l / granule * world + r) * granule
         + l % granule."""
-        return self.expand_own(self.pick(rows, positions), positions)
+        return self.expand_own(self.pick(rows, positions), positions, pad)
 
-    def expand_own(self, picked: torch.Tensor, positions: torch.Tensor) -> tuple:
+    def expand_own(self, picked: torch.Tensor, positions: torch.Tensor, pad: bool = True) -> tuple:
         """The rows of this rank's cache that the picks (global bucket ids) list for every row: (lists, lengths)."""
         d = self.design
         with probe.region("expand"):
             if self.own_tables:  # (the cut at top_k cannot bite: this rank's members are all there is to list)
                 lists, lengths, _ = ops.expand(picked, positions, self.members_own, d.top_p * self.own_cap, d.sink_size,
-                                               d.window_size, dealt=(self.granule, self.world, self.rank))
+                                               d.window_size, dealt=(self.granule, self.world, self.rank), pad=pad)
             else:
                 lists, lengths, _ = ops.expand(picked, positions, self.members, d.top_k, d.sink_size, d.window_size,
-                                               dealt=(self.granule, self.world, self.rank))
+                                               dealt=(self.granule, self.world, self.rank), pad=pad)
         return lists, lengths
 
     def _read_rows(self, rows: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int) -> tuple:
         """This rank's partial read of every row: (out bf16, lse). (bf16 partials: they cross NVLink next.)"""
         layer = self.layer
-        lists, lengths = self.select(rows, positions)
+        lists, lengths = self.select(rows, positions, pad=False)  # (read by their lengths just below)
         with probe.region("attend"):
             return ops.latent_attend(rows, share, lists, lengths, layer.scale, value_dim=layer.value_dim,
                                      splits=splits, out_dtype=torch.bfloat16, status=layer._attend_status)
@@ -493,6 +493,50 @@ class ShardedLatentLayer:
             out.copy_(merged)
             return out
         return merged
+
+    def prefill_from_host(self, q_host: torch.Tensor, rows_host: torch.Tensor, start: int, count: int,
+                          share: torch.Tensor, out_host: torch.Tensor, pieces: int = 4) -> torch.Tensor:
+        """A prefill chunk of `count` rows at positions start.. whose inputs and output live in PINNED host memory,
+        the copies beside the work. The host link carries every row once: the chunk is cut into `pieces`, this rank
+        brings in the `rank`-th of each piece's query rows (`q_host` [count / world, heads, latent_dim]: its rows of
+        piece 0, then of piece 1, ...), the ranks all-gather a piece over NVLink while the piece before is read, and a
+        piece's output rows of this rank (`out_host` [count / world, heads, value_dim], in the same order) leave as
+        soon as they are merged. `rows_host` holds this rank's dealt rows of the chunk's latent. A collective call; on
+        return the current stream has waited for the last output copy."""
+        layer, world, dev = self.layer, self.world, share.device
+        if count % (pieces * world):
+            raise ValueError(f"{count} rows do not cut into {pieces} pieces of {world} shares")
+        piece, own = count // pieces, count // pieces // world
+        main = torch.cuda.current_stream(dev)
+        if layer._copy_in is None:
+            layer._copy_in, layer._copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        copy_in, copy_out = layer._copy_in, layer._copy_out
+        while len(layer._copy_events) < 2 * pieces + 1:
+            layer._copy_events.append(torch.cuda.Event())
+        rows_in, arrived, done = layer._copy_events[0], layer._copy_events[1::2], layer._copy_events[2::2]
+        q_own = layer._buffer("q share from host", tuple(q_host.shape), q_host.dtype, dev)
+        q_all = layer._buffer("q pieces", (pieces, piece, *q_host.shape[1:]), q_host.dtype, dev)
+        out = layer._buffer("out share to host", tuple(out_host.shape), out_host.dtype, dev)
+        copy_in.wait_stream(main)   # the last call's reads of these buffers are over
+        copy_out.wait_stream(main)
+        with torch.cuda.stream(copy_in):
+            share[start // world:(start + count) // world].copy_(rows_host, non_blocking=True)
+            rows_in.record(copy_in)
+            for i in range(pieces):
+                q_own[i * own:(i + 1) * own].copy_(q_host[i * own:(i + 1) * own], non_blocking=True)
+                dist.all_gather_into_tensor(q_all[i].view(-1), q_own[i * own:(i + 1) * own].view(-1), group=self.group)
+                arrived[i].record(copy_in)
+        main.wait_event(rows_in)
+        self.extend_index(share, start, count)
+        for i in range(pieces):
+            main.wait_event(arrived[i])
+            self.prefill_rows(q_all[i], start + i * piece, share, out[i * own:(i + 1) * own])
+            done[i].record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(done[i])
+                out_host[i * own:(i + 1) * own].copy_(out[i * own:(i + 1) * own], non_blocking=True)
+        main.wait_stream(copy_out)
+        return out_host
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, share: torch.Tensor, splits: int = 32) -> torch.Tensor:
         """One step for replicated rows [R, heads, latent_dim] at `positions`: the whole output on every rank. Every

@@ -115,6 +115,18 @@ def _latent_rank_main(rank, world, port, result_dir):
         assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
         got1 = sharded.decode(q[-1:].contiguous(), torch.tensor([T - 1], device="cuda"), share, splits=4)
         assert (got1.float() - want1.float()).abs().max().item() <= 2e-2
+        # the same chunk from pinned host buffers, two pieces: this rank brings in and takes out its rows of each
+        pieces, own = 2, chunk // 2 // world
+        q_h = q.view(pieces, world, own, Hq, dk)[:, rank].reshape(pieces * own, Hq, dk).cpu().pin_memory()
+        rows_h = share[first // world:].cpu().pin_memory()
+        out_h = torch.empty(pieces * own, Hq, dv, dtype=torch.bfloat16).pin_memory()
+        share[first // world:].zero_()
+        sharded.prefill_from_host(q_h, rows_h, first, chunk, share, out_h, pieces=pieces)
+        torch.cuda.synchronize()
+        want_h = want.view(pieces, world, own, Hq, dv)[:, rank].reshape(pieces * own, Hq, dv)
+        err = (out_h.cuda().float() - want_h.float()).abs()
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+        assert torch.equal(share[first // world:].cpu(), rows_h)
         layer.check()
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
