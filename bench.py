@@ -70,17 +70,18 @@ def roof_ms(nbytes: float, flops: float, pk: dict) -> tuple:
     return (t_hbm, "hbm") if t_hbm >= t_tensor else (t_tensor, "tensor")
 
 
-def stage_table(work: dict, measured: dict, pk: dict, ms_per_step: float) -> dict:
-    """Per stage: algorithmic bytes and flops, the roofline time they imply, the measured time and their ratio; and
-    the stage-wise fraction = sum of the roofline times / the step time."""
+def stage_table(work: dict, measured: dict, pk: dict, ms_per_step: float, gpus: int = 1) -> dict:
+    """Per stage: algorithmic bytes and flops of the whole job, the roofline time they imply on `gpus` GPUs that share
+    them evenly, the measured time and their ratio; and the stage-wise fraction = sum of the roofline times / the step
+    time."""
     stages, total = {}, 0.0
     for name, (nbytes, flops) in work.items():
-        roof, bound = roof_ms(nbytes, flops, pk)
+        roof, bound = roof_ms(nbytes / gpus, flops / gpus, pk)
         total += roof
         got = measured.get(name)
         stages[name] = {"bytes": nbytes, "flops": flops, "roof_ms": roof, "bound": bound, "ms": got,
                         "frac": roof / got if got else None}
-    return {"stages": stages, "roof_ms": total, "frac": total / ms_per_step if ms_per_step else None}
+    return {"stages": stages, "gpus": gpus, "roof_ms": total, "frac": total / ms_per_step if ms_per_step else None}
 
 
 def host_threads() -> int:
@@ -499,7 +500,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
         "attend": (gathered_total * dk * 2 + chunk * Hq * (dk + dv) * 2 + chunk * Hq * 4.0,
                    2.0 * gathered_total * Hq * (dk + dv)),
     }
-    table = stage_table(work, stage_ms, pk, ms)
+    table = stage_table(work, stage_ms, pk, ms, world)
     attend = table["stages"]["attend"]
     attend_ms = stage_ms.get("attend")
     achieved = attend["bytes"] / world / (attend_ms * 1e-3) / 1e9 if attend_ms else None
@@ -697,7 +698,7 @@ def run_c2(args, env: Env, cfg: dict, steps: int, cpu_baseline: bool = True) -> 
             # MUST move are Q in, the band's partial in, O out and the visible K/V once a chunk
             "attend": (T * Hq * dh * (2 + 2) + T * Hq * (dh + 1) * 4 + kv_once * 1.0, 4.0 * gathered * Hq * dh),
         }
-        table = stage_table(work, stage_ms, pk, ms)
+        table = stage_table(work, stage_ms, pk, ms, world)
         attend = table["stages"]["attend"]
         calls = chunks
         result["stagewise"] = table

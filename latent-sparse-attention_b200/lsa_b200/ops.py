@@ -301,8 +301,18 @@ def scan_select(index_queries: torch.Tensor, centroids: torch.Tensor, centroids_
         workspace = torch.empty(max(need, 1), device=q.device, dtype=torch.uint8)
     call("lsa_scan_select", ptr(q), R, d, ptr(c), ptr(cb), ptr(lengths), ptr(radius), c.shape[0],
          ptr(_contig(visible.to(torch.int32))), ptr(row_top_p), top_p, bucket_id_base, int(max_visible), ptr(keys),
-         ptr(picked), ptr(status), ptr(workspace), workspace.numel() * workspace.element_size(), stream())
+         ptr(picked), ptr(status), ptr(workspace), workspace.numel() * workspace.element_size(), stream(),
+         launches=8 if _scan_samples(c.shape[0], top_p, int(max_visible)) else 1)
     return keys, picked
+
+
+def _scan_samples(m: int, top_p: int, max_visible: int) -> bool:
+    """Whether `lsa_scan_select` thresholds its rows by sampling (eight launches: operands, scan, pick, the rows left
+    over collected, scanned in splits, merged and scattered, the exact scan of the rest) or scans all of them exactly
+    (one launch): the gate of csrc/select.cu, restated for the launch count."""
+    widest = max_visible if 0 < max_visible < m else m
+    factor = max(2, min(3, 1024 // max(top_p, 1)))
+    return m >= 1024 and factor * top_p * 512 >= 8 * widest
 
 
 def flat_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, request_first: torch.Tensor | None,
