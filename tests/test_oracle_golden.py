@@ -237,3 +237,49 @@ def test_miniature_config_end_to_end(oracle):
     out, _ = oracle.sparse_attend(q[rows], k, v, g["selected"][rows], rows, 128, 4, q.shape[2] ** -0.5,
                                   lengths=g["lengths"][rows])
     np.testing.assert_allclose(out, g["out"], rtol=0, atol=5e-6)
+
+
+@pytest.mark.parametrize("width", [32, 64])
+def test_bucket_shapes_match_the_reference(oracle, width):
+    # (the reference's own cases: tests/unit/core/test_shape.py:40-94)
+    g = golden("shapes")
+    tag = f"w{width}_"
+    keys, centroids, members, queries = g[tag + "keys"], g[tag + "centroids"], g[tag + "members"], g[tag + "queries"]
+    if width == 32:
+        np.testing.assert_allclose(oracle.covariances(keys, centroids, members)[0], g[tag + "covariances"], atol=1e-7)
+    for rank in (0, 1, 2, 4, width):
+        want = oracle.Shapes(g[f"{tag}r{rank}_basis"], g[f"{tag}r{rank}_variances"], g[f"{tag}r{rank}_floor"])
+        # the reference's shapes through the oracle's scoring: the spread in double, the scores in the fixed fp32 order
+        np.testing.assert_allclose(oracle.spread(queries, want), g[f"{tag}r{rank}_spread"], rtol=0, atol=2e-7)
+        np.testing.assert_allclose(oracle.shaped_scores(queries, centroids, want, 2.0), g[f"{tag}r{rank}_scores"],
+                                   rtol=0, atol=5e-7)
+        assert np.array_equal(oracle.pack_shape_basis(oracle.unpack_shape_basis(want.basis)), want.basis)
+        # the oracle's own build
+        got = oracle.build_shapes(keys, centroids, members, rank)
+        np.testing.assert_allclose(got.variances, want.variances, rtol=1e-5, atol=1e-7)
+        np.testing.assert_allclose(got.floor, want.floor, rtol=1e-5, atol=1e-7)
+        kept = got.variances.sum(1) + got.floor * (width - rank)
+        np.testing.assert_allclose(kept, np.trace(oracle.covariances(keys, centroids, members)[0], axis1=1, axis2=2),
+                                   rtol=1e-4, atol=1e-6)  # a shape keeps the trace whatever its rank
+        if rank <= 2:  # a direction is its negation too; past the keys a bucket holds the directions are anyone's
+            same = (got.basis == want.basis).all(-1) | (got.basis == ~want.basis).all(-1)
+            assert same[members[:, rank].reshape(-1) >= 0].all()
+            np.testing.assert_allclose(oracle.spread(queries, got), g[f"{tag}r{rank}_spread"], rtol=0, atol=2e-7)
+
+
+def test_a_shaped_read_matches_the_reference(oracle):
+    g = golden("shapes")
+    buckets = oracle.Buckets(g["read_centroids"], g["read_members"], (g["read_members"] >= 0).sum(1).astype(np.int32),
+                             8, 64)
+    shapes = oracle.Shapes(g["read_basis"], g["read_variances"], g["read_floor"])
+    plain, plain_lengths = oracle.read(g["read_queries"], g["read_positions"], buckets, 4, 16, 2, 24)
+    for z in (0, 2):
+        selected, lengths = oracle.read(g["read_queries"], g["read_positions"], buckets, 4, 16, 2, 24, shapes=shapes,
+                                        deviations=float(z))
+        assert np.array_equal(lengths, g[f"read_z{z}_lengths"])
+        assert np.array_equal(selected, g[f"read_z{z}_selected"])
+    assert np.array_equal(g["read_z0_selected"], plain) and not np.array_equal(g["read_z2_selected"], plain)
+    with pytest.raises(ValueError, match="rank must be from 0 to the keys' width 32 - got 33"):
+        oracle.shape_buckets(g["read_keys"], buckets, 33)
+    built = oracle.shape_buckets(g["read_keys"], buckets, 2)
+    np.testing.assert_allclose(built.variances, shapes.variances, rtol=1e-5, atol=1e-8)
