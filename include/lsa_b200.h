@@ -246,6 +246,49 @@ int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p
                          int32_t *picked_out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
+ * Bucket shapes: a bucket's spread about its centroid - the covariance of its index keys kept as `rank` leading
+ * directions, each rounded to one sign bit a dimension (+-1/sqrt(d)), their variances, and a floor: the rest of the
+ * trace spread evenly over the directions left out. A shaped bucket scores as its estimated best key,
+ *     q . c + deviations * sqrt( sum_j variance_j (q . s_j)^2 + floor (1 - sum_j (q . s_j)^2) ).
+ * Reference: Shapes, build_shapes, spread, shaped_scores, pack_shape_basis (src/lsa/core/shape.py:25-170),
+ * shape_buckets and the shaped read (src/lsa/core/reference.py:147-164,229-230), the served builders and scans
+ * (src/lsa/core/kernels/triton/shape.py:281-343,659-717,849-886), BucketCache.shape_buckets
+ * (src/lsa/sglang/index/bucket_cache.py:603-627).
+ *   basis     [rows, rank, d / 8] uint8 - bit b of byte i = dimension 8 i + b, set where the sign is positive;
+ *             4-byte aligned (read as words)
+ *   variances [rows, rank] fp32 descending;  floors [rows] fp32;  rank 0..d (0: an even spread, basis may be NULL)
+ * Every shaped entry point scores in one fixed fp32 order (q . s_j over ascending dimensions with the sign as a
+ * factor, scaled once, the directions folded in order), so a bucket scores alike whichever kernel reads it.
+ *
+ * lsa_shape_build: the shapes of m buckets from the keys they hold, exactly (a CTA a bucket: the [d, d] covariance
+ * summed in member order, diagonalised by Jacobi rotations). d = 32 or 64.
+ *   index_keys [key_rows, d] fp32 - row i is the key at position key_base + i; members [m, cap] int32 positions,
+ *   -1 padded (a position outside the rows given adds nothing); centroids [m, d] fp32 */
+int lsa_shape_build(const float *index_keys, int64_t key_base, int64_t key_rows, const float *centroids,
+                    const int32_t *members, int64_t m, int cap, int d, int rank, uint8_t *basis_out,
+                    float *variances_out, float *floors_out, void *stream);
+
+/* lsa_flat_select over shaped buckets: the same lists, a bucket scored by its estimated best key. */
+int lsa_shaped_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,
+                      const uint8_t *basis, const float *variances, const float *floors, int rank, float deviations,
+                      const int32_t *visible, const int32_t *row_top_p, int top_p, int32_t bucket_id_base,
+                      int64_t *keys_out, int32_t *picked_out, void *stream);
+
+/* lsa_flat_select_decode over shaped buckets (the shape table is indexed like `centroids`: request_first[r] + id). */
+int lsa_shaped_select_decode(const float *queries, int64_t R, int d, const float *centroids, const uint8_t *basis,
+                             const float *variances, const float *floors, int rank, float deviations,
+                             const int64_t *request_first, const int32_t *visible, int top_p, int splits,
+                             int64_t *keys_out, int32_t *picked_out, void *workspace, size_t workspace_bytes,
+                             void *stream);
+
+/* Shaped scores written out: row r against the table rows rows[r, :] (int32, -1 = none: -inf), or against table
+ * rows 0..width when rows is NULL (score_shaped_rows, add_planes_spread, scan_paged_shaped of the reference).
+ *   scores_out [R, width] fp32 */
+int lsa_shaped_scores(const float *queries, int64_t R, int d, const float *centroids, int64_t m, const uint8_t *basis,
+                      const float *variances, const float *floors, int rank, float deviations, const int32_t *rows,
+                      int64_t width, float *scores_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
  * Tree search, one beam step: score the candidate rows of a level (open node buckets first_open..made and the
  * children carried from the level above), keep the best `keep`, a tie to the lower row.
  * Reference: beam_pick / best (src/lsa/core/hierarchy.py:402-451); served Hierarchy.beam_search, pick_buckets

@@ -6,6 +6,7 @@
 // word breaks a score tie toward the lower id, so the result does not depend on the order keys were produced in.
 #include "common.cuh"
 #include "scan_select.cuh"
+#include "shape.cuh"
 
 namespace lsa {
 
@@ -228,10 +229,11 @@ struct SelectParams {
   int64_t R, N;
   const int32_t *pages;         // [R, max_pages] page of every page_rows ids of a row (-1 = none), or NULL
   int d, n_carried, keep, fanout, id_base, chunk, run_limit, max_pages, page_rows;
+  ShapeTable shape;             // the vectors' shapes, row for row (floors NULL: none)
 };
 
 // RB rows a CTA. Shared memory: queries [RB][d], per-row key buffers [RB][keep_pow2 + chunk], histograms.
-template <int RB>
+template <int RB, bool SHAPED>
 __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int keep_room = 2;  // even, so the float4 reads of the queries behind the buffers stay 16-byte aligned
@@ -342,6 +344,11 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
             acc[i] = fmaf(q.w, v.w, acc[i]);
           }
         }
+      }
+      if constexpr (SHAPED) {
+#pragma unroll
+        for (int i = 0; i < RB; ++i)
+          if (vec_row[i] >= 0) acc[i] = shaped_score(acc[i], qs + i * p.d, p.d, p.shape, vec_row[i]);
       }
 #pragma unroll
       for (int i = 0; i < RB; ++i)
@@ -489,10 +496,19 @@ static int launch_select(SelectParams p, int splits, cudaStream_t s) {
   size_t smem = 0;
   p.chunk = select_chunk(RB, p.keep, p.d, &smem);
   if (p.chunk == 0) return LSA_ERR_UNSUPPORTED;
-  if (cudaFuncSetAttribute(select_kernel<RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return LSA_ERR_LAUNCH;
   dim3 grid((unsigned)((p.R + RB - 1) / RB), (unsigned)splits);
-  select_kernel<RB><<<grid, kSelThreads, smem, s>>>(p);
+  if (p.shape.floors) {
+    if (cudaFuncSetAttribute(select_kernel<RB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return LSA_ERR_LAUNCH;
+    select_kernel<RB, true><<<grid, kSelThreads, smem, s>>>(p);
+    LSA_LAUNCH_CHECK();
+    return LSA_OK;
+  }
+  if (cudaFuncSetAttribute(select_kernel<RB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  select_kernel<RB, false><<<grid, kSelThreads, smem, s>>>(p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -514,9 +530,10 @@ struct FlatParams {
   int32_t *ids_out;
   int64_t R, m;
   int d, keep, id_base, chunk;
+  ShapeTable shape;  // the centroids' shapes, row for row (floors NULL: none)
 };
 
-template <int D>
+template <int D, bool SHAPED>
 __global__ void __launch_bounds__(kFlatThreads) flat_select_kernel(FlatParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int keep_room = 2;
@@ -568,6 +585,44 @@ __global__ void __launch_bounds__(kFlatThreads) flat_select_kernel(FlatParams p)
           acc[i] = fmaf(q.w, v.w, acc[i]);
         }
       }
+      if constexpr (SHAPED) {
+        // The spread of this thread's bucket under each of the CTA's rows: a sign is read off its word once and
+        // meets all sixteen rows.
+        float variance[kFlatRows], inside[kFlatRows];
+#pragma unroll
+        for (int i = 0; i < kFlatRows; ++i) variance[i] = 0.0f, inside[i] = 0.0f;
+        const int64_t bucket = base + c;
+        for (int j = 0; j < p.shape.rank; ++j) {
+          float along[kFlatRows];
+#pragma unroll
+          for (int i = 0; i < kFlatRows; ++i) along[i] = 0.0f;
+          const uint32_t *bits = p.shape.basis + (bucket * p.shape.rank + j) * (D / 32);
+#pragma unroll
+          for (int w = 0; w < D / 32; ++w) {
+            const uint32_t word = __ldg(bits + w);
+#pragma unroll 2
+            for (int b4 = 0; b4 < 8; ++b4) {
+              const float s0 = shape_sign(word, b4 * 4), s1 = shape_sign(word, b4 * 4 + 1);
+              const float s2 = shape_sign(word, b4 * 4 + 2), s3 = shape_sign(word, b4 * 4 + 3);
+#pragma unroll
+              for (int i = 0; i < kFlatRows; ++i) {
+                const float4 q = *reinterpret_cast<const float4 *>(qs + i * D + w * 32 + b4 * 4);
+                along[i] = __fmaf_rn(q.x, s0, along[i]);
+                along[i] = __fmaf_rn(q.y, s1, along[i]);
+                along[i] = __fmaf_rn(q.z, s2, along[i]);
+                along[i] = __fmaf_rn(q.w, s3, along[i]);
+              }
+            }
+          }
+          const float variance_j = __ldg(p.shape.variances + bucket * p.shape.rank + j);
+#pragma unroll
+          for (int i = 0; i < kFlatRows; ++i) shape_fold(along[i], p.shape.scale, variance_j, variance[i], inside[i]);
+        }
+        const float floor_ = __ldg(p.shape.floors + bucket);
+#pragma unroll
+        for (int i = 0; i < kFlatRows; ++i)
+          acc[i] = shape_finish(acc[i], variance[i], inside[i], floor_, p.shape.deviations);
+      }
 #pragma unroll
       for (int i = 0; i < kFlatRows; ++i)
         bufs[(size_t)i * row_room + keep_room + c] =
@@ -608,9 +663,18 @@ static int launch_flat(FlatParams p, cudaStream_t s) {
   while (p.chunk > 256 && fixed + (size_t)kFlatRows * p.chunk * 8 > 200 * 1024) p.chunk -= 256;
   const size_t smem = fixed + (size_t)kFlatRows * p.chunk * 8;
   if (smem > 200 * 1024) return LSA_ERR_UNSUPPORTED;
-  if (cudaFuncSetAttribute(flat_select_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return LSA_ERR_LAUNCH;
-  flat_select_kernel<D><<<(unsigned)((p.R + kFlatRows - 1) / kFlatRows), kFlatThreads, smem, s>>>(p);
+  const unsigned grid = (unsigned)((p.R + kFlatRows - 1) / kFlatRows);
+  if (p.shape.floors) {
+    if (cudaFuncSetAttribute(flat_select_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return LSA_ERR_LAUNCH;
+    flat_select_kernel<D, true><<<grid, kFlatThreads, smem, s>>>(p);
+  } else {
+    if (cudaFuncSetAttribute(flat_select_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return LSA_ERR_LAUNCH;
+    flat_select_kernel<D, false><<<grid, kFlatThreads, smem, s>>>(p);
+  }
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -1113,6 +1177,48 @@ LSA_API int lsa_flat_select(const float *queries, int64_t R, int d, const float 
   return lsa::launch_select<8>(p, 1, (cudaStream_t)stream);
 }
 
+// ------------------------------------------------------------------------------------------------ shaped buckets
+
+namespace lsa {
+static bool shape_table(ShapeTable *t, const uint8_t *basis, const float *variances, const float *floors, int rank,
+                        float deviations, int d) {
+  if (!floors || rank < 0 || rank > d || d % 32 != 0) return false;
+  if (rank > 0 && (!basis || !variances || ((uintptr_t)basis % 4) != 0)) return false;
+  t->basis = reinterpret_cast<const uint32_t *>(basis);
+  t->variances = variances;
+  t->floors = floors;
+  t->rank = rank;
+  t->deviations = deviations;
+  t->scale = 1.0f / sqrtf((float)d);
+  return true;
+}
+}  // namespace lsa
+
+LSA_API int lsa_shaped_select(const float *queries, int64_t R, int d, const float *centroids, int64_t m,
+                              const uint8_t *basis, const float *variances, const float *floors, int rank,
+                              float deviations, const int32_t *visible, const int32_t *row_top_p, int top_p,
+                              int32_t bucket_id_base, int64_t *keys_out, int32_t *picked_out, void *stream) {
+  LSA_REQUIRE(queries && centroids && visible && (keys_out || picked_out), LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && m >= 0 && top_p >= 1 && m < INT32_MAX, LSA_ERR_ARGUMENT);
+  lsa::ShapeTable table;
+  LSA_REQUIRE(lsa::shape_table(&table, basis, variances, floors, rank, deviations, d), LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  if ((d == 64 || d == 32) && top_p <= 512) {
+    lsa::FlatParams f = {};
+    f.queries = queries, f.centroids = centroids, f.visible = visible, f.row_keep = row_top_p;
+    f.keys_out = keys_out, f.ids_out = picked_out;
+    f.R = R, f.m = m, f.d = d, f.keep = top_p, f.id_base = bucket_id_base;
+    f.shape = table;
+    return d == 64 ? lsa::launch_flat<64>(f, (cudaStream_t)stream) : lsa::launch_flat<32>(f, (cudaStream_t)stream);
+  }
+  lsa::SelectParams p = {};
+  p.queries = queries, p.vectors = centroids, p.run_end = visible, p.row_keep = row_top_p;
+  p.keys_out = keys_out, p.ids_out = picked_out;
+  p.R = R, p.N = m, p.d = d, p.keep = top_p, p.id_base = bucket_id_base, p.run_limit = (int)m;
+  p.shape = table;
+  return lsa::launch_select<8>(p, 1, (cudaStream_t)stream);
+}
+
 LSA_API size_t lsa_flat_select_decode_workspace_bytes(int64_t R, int top_p, int splits) {
   if (R <= 0 || top_p <= 0 || splits <= 1) return 0;
   return (size_t)R * top_p * splits * sizeof(int64_t);
@@ -1160,6 +1266,34 @@ LSA_API int lsa_flat_select_decode(const float *queries, int64_t R, int d, const
   if (splits == 1) {
     p.keys_out = keys_out;
     p.ids_out = picked_out;
+    return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+  }
+  p.keys_out = (int64_t *)workspace;
+  int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
+  if (rc != LSA_OK) return rc;
+  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+}
+
+LSA_API int lsa_shaped_select_decode(const float *queries, int64_t R, int d, const float *centroids,
+                                     const uint8_t *basis, const float *variances, const float *floors, int rank,
+                                     float deviations, const int64_t *request_first, const int32_t *visible,
+                                     int top_p, int splits, int64_t *keys_out, int32_t *picked_out, void *workspace,
+                                     size_t workspace_bytes, void *stream) {
+  LSA_REQUIRE(queries && centroids && visible && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && top_p >= 1 && splits >= 1 && splits <= 1024, LSA_ERR_ARGUMENT);
+  lsa::ShapeTable table;
+  LSA_REQUIRE(lsa::shape_table(&table, basis, variances, floors, rank, deviations, d), LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  if (splits > 1) {
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= lsa_flat_select_decode_workspace_bytes(R, top_p, splits), LSA_ERR_WORKSPACE);
+  }
+  lsa::SelectParams p = {};
+  p.queries = queries, p.vectors = centroids, p.vector_base = request_first, p.run_end = visible;
+  p.R = R, p.N = INT64_MAX, p.d = d, p.keep = top_p, p.run_limit = INT32_MAX;
+  p.shape = table;
+  if (splits == 1) {
+    p.keys_out = keys_out, p.ids_out = picked_out;
     return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
   }
   p.keys_out = (int64_t *)workspace;

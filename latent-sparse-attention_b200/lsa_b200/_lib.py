@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 16
+ABI_VERSION = 17
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -45,6 +45,10 @@ SIGNATURES = {
     "lsa_flat_select_decode": (_I, [_P, _L, _I, _P, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
     "lsa_flat_select_paged": (_I, [_P, _L, _I, _P, _L, _P, _I, _I, _P, _I, _I, _P, _P, _P, _Z, _P]),
     "lsa_merge_candidates": (_I, [_P, _I, _L, _I, _P, _P, _P]),
+    "lsa_shape_build": (_I, [_P, _L, _L, _P, _P, _L, _I, _I, _I, _P, _P, _P, _P]),
+    "lsa_shaped_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _P, _I, _F, _P, _P, _I, c_int32, _P, _P, _P]),
+    "lsa_shaped_select_decode": (_I, [_P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
+    "lsa_shaped_scores": (_I, [_P, _L, _I, _P, _L, _P, _P, _P, _I, _F, _P, _L, _P, _P]),
     "lsa_beam_step": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P]),
     "lsa_beam_step_workspace_bytes": (_Z, [_L, _I, _I]),
     "lsa_beam_step_split": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _Z, _P]),

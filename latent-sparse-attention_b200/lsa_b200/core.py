@@ -5,11 +5,11 @@ specification (`src/lsa/core/__init__.py:36-56`), with CUDA tensors in and out:
 
     regroup / regroup_partial / rownorm / project / project_partial / position_free   index_space.py
     pool_keys / ward_rounds / ward_merge / members_from_labels                        ward.py
-    Buckets / build_buckets / read                                                    reference.py
+    Buckets / build_buckets / shape_buckets / read                                    reference.py
     topk_attention                                                                    attention.py
 
-Every function raises `ValueError` naming what arrived where the reference does. Bucket shapes (`shapes=`) are
-not built; passing them raises `NotImplementedError`.
+Every function raises `ValueError` naming what arrived where the reference does. Bucket shapes live in
+`lsa_b200.shape` (the reference's `lsa.core.shape`); `read` given `shapes` scores a bucket by its estimated best key.
 """
 
 from __future__ import annotations
@@ -296,6 +296,17 @@ def build_buckets(index_keys: torch.Tensor, pool_size: int, bucket_size: int, bu
     return Buckets(centroids, members, sizes, per_block, cluster_block_size)
 
 
+def shape_buckets(index_keys: torch.Tensor, buckets: Buckets, rank: int):
+    """Give every bucket its shape: its keys' spread about its centroid, kept as `rank` sign directions
+    (reference.py:147-164). Returns `shape.Shapes`, row for row with the buckets."""
+    from lsa_b200 import shape
+
+    check_unit_rows("index_keys", index_keys)
+    if not 0 <= rank <= index_keys.shape[1]:
+        raise ValueError(f"rank must be from 0 to the keys' width {index_keys.shape[1]} - got {rank}")
+    return shape.build_shapes(index_keys, buckets.bucket_centroids, buckets.bucket_members, rank)
+
+
 def check_read_arguments(index_queries, positions, buckets, top_p, top_k, sink_size, window_size,
                          early_budget=None) -> None:
     """The refusals of `read` (reference.py:209-224): unit rows of the buckets' dim, one non-negative integer
@@ -322,8 +333,6 @@ def read(index_queries: torch.Tensor, positions: torch.Tensor, buckets: Buckets,
 
     Returns selected ids [Tq, top_k + window + sink] int32 (-1 padded; expansion, window, sinks) and lengths [Tq].
     """
-    if shapes is not None:
-        raise NotImplementedError("bucket shapes are not built in lsa_b200")
     check_read_arguments(index_queries, positions, buckets, top_p, top_k, sink_size, window_size, early_budget)
     positions = positions.to(torch.int64)
     visible = (positions // buckets.cluster_block_size * buckets.block_bucket_count).clamp_max(
@@ -333,7 +342,16 @@ def read(index_queries: torch.Tensor, positions: torch.Tensor, buckets: Buckets,
         early = positions < early_budget.position
         row_p = torch.where(early, early_budget.top_p, top_p).to(torch.int32)
         row_k = torch.where(early, early_budget.top_k, top_k).to(torch.int32)
-    _, picked = ops.flat_select(index_queries, buckets.bucket_centroids, visible, top_p, row_p)
+    if shapes is not None:  # a bucket scores as its estimated best key (reference.py:229-230)
+        from lsa_b200 import shape
+
+        if shapes.floor.shape[0] != buckets.bucket_centroids.shape[0]:
+            raise ValueError(f"shapes hold {shapes.floor.shape[0]} buckets and the table "
+                             f"{buckets.bucket_centroids.shape[0]}")
+        _, picked = ops.shaped_select(index_queries, buckets.bucket_centroids, shape.table(shapes, deviations),
+                                      visible, top_p, row_p)
+    else:
+        _, picked = ops.flat_select(index_queries, buckets.bucket_centroids, visible, top_p, row_p)
     selected, lengths, _ = ops.expand(picked, positions, buckets.bucket_members, top_k, sink_size, window_size,
                                       row_p, row_k)
     return selected, lengths

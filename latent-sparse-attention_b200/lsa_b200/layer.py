@@ -14,6 +14,7 @@ import torch
 from lsa_b200 import _lib, ops, probe
 from lsa_b200.budget import EarlyBudget
 from lsa_b200.core import Buckets, RotaryLayout, check_sizes
+from lsa_b200.shape import Shape
 
 
 @dataclass(frozen=True)
@@ -29,9 +30,14 @@ class FlatDesign:
     sink_size: int = 4
     window_size: int = 512
     early_budget: EarlyBudget | None = None
+    bucket_shape: Shape | None = None  # buckets keep their spread and score as their estimated best key
 
     def __post_init__(self) -> None:
         check_sizes(self.pool_size, self.bucket_size, self.bucket_cap, self.cluster_block_size)
+        object.__setattr__(self, "bucket_shape", Shape.read("bucket_shape", self.bucket_shape))
+        if self.bucket_shape is not None and self.bucket_shape.rank > self.bucket_cap:
+            raise ValueError(f"bucket_shape keeps at most bucket_cap {self.bucket_cap} directions - got rank "
+                             f"{self.bucket_shape.rank}")
         if min(self.top_p, self.top_k, self.window_size) < 1 or self.sink_size < 0:
             raise ValueError("top_p, top_k and window_size must be positive and sink_size non-negative")
         if self.top_p * self.bucket_cap < self.top_k:
@@ -51,11 +57,13 @@ class FlatIndex:
     scan can use it, its operand: the centroids less a common centre in bf16, and the greatest length of one)."""
 
     def __init__(self, index_keys: torch.Tensor, buckets: Buckets, centroids_bf16: torch.Tensor | None = None,
-                 lengths: torch.Tensor | None = None, radius: torch.Tensor | None = None):
+                 lengths: torch.Tensor | None = None, radius: torch.Tensor | None = None,
+                 shapes: ops.ShapeTable | None = None):
         self.index_keys = index_keys
         self.buckets = buckets
         self.centroids_bf16 = centroids_bf16
         self.lengths, self.radius = lengths, radius
+        self.shapes = shapes  # the buckets' shapes, row for row, under a design with `bucket_shape`
 
 
 class FlatLayer:
@@ -192,13 +200,20 @@ class FlatLayer:
             bufs["lengths"] = make("operand lengths", (rows,), torch.float32)
             bufs["radius"].zero_()
             bufs["centred"] = [False]
+        if d.bucket_shape is not None:
+            if d_idx not in (32, 64):
+                raise ValueError(f"bucket shapes are built over index keys of 32 or 64 dims - got {d_idx}")
+            rank = d.bucket_shape.rank
+            bufs["shapes"] = ops.ShapeTable(make("shape basis", (rows, rank, d_idx // 8), torch.uint8),
+                                            make("shape variances", (rows, rank), torch.float32),
+                                            make("shape floor", (rows,), torch.float32), d.bucket_shape.deviations)
         return bufs
 
     def _index_of(self, bufs: dict) -> FlatIndex:
         d = self.design
         return FlatIndex(bufs["keys"], Buckets(bufs["centroids"], bufs["members"], bufs["sizes"], d.block_bucket_count,
                                                d.cluster_block_size), bufs.get("centroids bf16"), bufs.get("lengths"),
-                         bufs.get("radius"))
+                         bufs.get("radius"), bufs.get("shapes"))
 
     def _build_blocks(self, k: torch.Tensor, first: int, bufs: dict) -> None:
         """Index keys of k [n, ...] = the keys at positions first.., and the pools, Ward labels and bucket table of
@@ -238,6 +253,10 @@ class FlatLayer:
                     bufs["centred"][0] = True
                 ops.scan_centre(bufs["centroids"][r0:r1], bufs["centre"], bufs["centroids bf16"][r0:r1],
                                 bufs["lengths"][r0:r1], bufs["radius"])
+        if "shapes" in bufs:  # (members are positions: the keys of these blocks start at `first`)
+            with probe.region("bucket shapes"):
+                ops.shape_build(keys, bufs["centroids"][r0:r1], bufs["members"][r0:r1], d.bucket_shape.rank,
+                                key_base=first, out=bufs["shapes"].rows(slice(r0, r1)))
 
     scan_rows = 1024  # from this many rows on, a pick runs its scan on the tensor cores
 
@@ -265,7 +284,10 @@ class FlatLayer:
             bound = min(bound or b.bucket_centroids.shape[0], b.bucket_centroids.shape[0])
             # (the scan's threshold rests on 512 samples of a row's scores: it needs a thousand buckets in sight, and
             # the kept ones to be a fair share of them - else the exact scan, at once)
-            if index.centroids_bf16 is not None and R >= self.scan_rows and d.top_p <= 512 and bound >= 1024 \
+            if index.shapes is not None:  # a bucket scores as its estimated best key: the exact scan, shaped
+                _, picked = ops.shaped_select(index_queries, b.bucket_centroids, index.shapes, visible, d.top_p, row_p,
+                                              keys=keys, picked=picked)
+            elif index.centroids_bf16 is not None and R >= self.scan_rows and d.top_p <= 512 and bound >= 1024 \
                     and 3 * d.top_p * 512 >= 8 * bound:
                 need = ops.query("lsa_scan_select_workspace_bytes", R, d.top_p, b.bucket_centroids.shape[0])
                 work = self._buffer("scan", (need,), torch.uint8, dev)

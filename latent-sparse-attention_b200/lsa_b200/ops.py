@@ -4,6 +4,8 @@ launch on the current CUDA stream. Each names the reference function it stands i
 
 from __future__ import annotations
 
+from typing import NamedTuple
+
 import torch
 
 from lsa_b200 import _lib
@@ -350,6 +352,104 @@ def flat_select_paged(index_queries: torch.Tensor, centroids: torch.Tensor, page
          workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
          launches=1 if splits == 1 else 2)
     return keys, picked
+
+
+class ShapeTable(NamedTuple):
+    """The shapes of a table of buckets, row for row with their centroids, and the deviations they score with
+    (src/lsa/core/kernels/triton/shape.py:42-61)."""
+
+    basis: torch.Tensor  # [m, rank, d / 8] uint8: one sign bit a dimension, bit b of byte i = dimension 8 i + b
+    variances: torch.Tensor  # [m, rank] fp32, descending
+    floor: torch.Tensor  # [m] fp32
+    deviations: float  # z
+
+    def rows(self, rows) -> "ShapeTable":
+        """The shapes of some rows (an index tensor or a slice), aligned with them."""
+        return ShapeTable(self.basis[rows], self.variances[rows], self.floor[rows], self.deviations)
+
+    @property
+    def rank(self) -> int:
+        return self.basis.shape[1]
+
+
+def _shape_args(shapes: ShapeTable, d: int):
+    basis, variances, floor = _contig(shapes.basis), _contig(shapes.variances.float()), _contig(shapes.floor.float())
+    if basis.dtype != torch.uint8 or basis.dim() != 3 or basis.shape[2] * 8 != d:
+        raise ValueError(f"a shape basis is [buckets, rank, {d // 8}] uint8 - got {tuple(basis.shape)} {basis.dtype}")
+    if variances.shape != basis.shape[:2] or floor.shape != basis.shape[:1]:
+        raise ValueError("a shape's variances are [buckets, rank] and its floor [buckets]")
+    return basis, variances, floor
+
+
+def shape_build(index_keys: torch.Tensor, centroids: torch.Tensor, members: torch.Tensor, rank: int,
+                key_base: int = 0, out: ShapeTable | None = None, deviations: float = 0.0) -> ShapeTable:
+    """The shapes of buckets from the keys they hold (src/lsa/core/shape.py:88-106; the served builder
+    src/lsa/core/kernels/triton/shape.py:849-886): each bucket's covariance about its centroid, diagonalised exactly,
+    kept as `rank` packed sign directions, their variances and a floor. `index_keys` [rows, d] fp32 holds the keys at
+    positions key_base.. ; `members` [m, cap] are positions, -1 padded. `out`: a table's rows to write into."""
+    keys, c, mem = _contig(index_keys.float()), _contig(centroids.float()), _contig(members.to(torch.int32))
+    m, d = c.shape
+    if out is None:
+        out = ShapeTable(torch.empty(m, rank, d // 8, device=c.device, dtype=torch.uint8),
+                         torch.empty(m, rank, device=c.device), torch.empty(m, device=c.device), deviations)
+    basis, variances, floor = out.basis, out.variances, out.floor
+    if not (basis.is_contiguous() and variances.is_contiguous() and floor.is_contiguous()):
+        raise ValueError("shapes are written into contiguous rows")
+    if basis.shape != (m, rank, d // 8) or variances.shape != (m, rank) or floor.shape != (m,):
+        raise ValueError(f"out holds {tuple(basis.shape)} - expected the shapes of {m} buckets of rank {rank}")
+    call("lsa_shape_build", ptr(keys), key_base, keys.shape[0], ptr(c), ptr(mem), m, mem.shape[1], d, rank, ptr(basis),
+         ptr(variances), ptr(floor), stream())
+    return out
+
+
+def shaped_select(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: ShapeTable, visible: torch.Tensor,
+                  top_p: int, row_top_p: torch.Tensor | None = None, bucket_id_base: int = 0,
+                  keys: torch.Tensor | None = None, picked: torch.Tensor | None = None):
+    """`flat_select` over shaped buckets: a bucket scores as its estimated best key
+    (src/lsa/core/reference.py:229-230, src/lsa/core/shape.py:123-137)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    basis, variances, floor = _shape_args(shapes, d)
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64) if keys is None else keys
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32) if picked is None else picked
+    call("lsa_shaped_select", ptr(q), R, d, ptr(c), c.shape[0], ptr(basis), ptr(variances), ptr(floor),
+         basis.shape[1], float(shapes.deviations), ptr(_contig(visible.to(torch.int32))), ptr(row_top_p), top_p,
+         bucket_id_base, ptr(keys), ptr(picked), stream())
+    return keys, picked
+
+
+def shaped_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: ShapeTable,
+                         request_first: torch.Tensor | None, visible: torch.Tensor, top_p: int, splits: int = 1,
+                         workspace: torch.Tensor | None = None):
+    """`flat_select_decode` over shaped buckets (src/lsa/core/kernels/triton/shape.py:659-717)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    basis, variances, floor = _shape_args(shapes, d)
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    need = query("lsa_flat_select_decode_workspace_bytes", R, top_p, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_shaped_select_decode", ptr(q), R, d, ptr(c), ptr(basis), ptr(variances), ptr(floor), basis.shape[1],
+         float(shapes.deviations), ptr(request_first), ptr(_contig(visible.to(torch.int32))), top_p, splits, ptr(keys),
+         ptr(picked), ptr(workspace), workspace.numel() * workspace.element_size() if workspace is not None else 0,
+         stream(), launches=1 if splits == 1 else 2)
+    return keys, picked
+
+
+def shaped_scores(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: ShapeTable,
+                  rows: torch.Tensor | None = None, width: int | None = None) -> torch.Tensor:
+    """Shaped scores written out [R, width] fp32: row r against the table rows `rows[r]` (-1: -inf), or against the
+    first `width` table rows (src/lsa/core/kernels/triton/shape.py:281-343,407-450)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    R, d = q.shape
+    basis, variances, floor = _shape_args(shapes, d)
+    rows = None if rows is None else _contig(rows.to(torch.int32))
+    width = (c.shape[0] if width is None else width) if rows is None else rows.shape[1]
+    out = torch.empty(R, width, device=q.device, dtype=torch.float32)
+    call("lsa_shaped_scores", ptr(q), R, d, ptr(c), c.shape[0], ptr(basis), ptr(variances), ptr(floor), basis.shape[1],
+         float(shapes.deviations), ptr(rows), width, ptr(out), stream())
+    return out
 
 
 def merge_candidates(keys_in: torch.Tensor):
