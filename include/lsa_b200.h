@@ -281,12 +281,36 @@ int lsa_shaped_select_decode(const float *queries, int64_t R, int d, const float
                              int64_t *keys_out, int32_t *picked_out, void *workspace, size_t workspace_bytes,
                              void *stream);
 
+/* lsa_flat_select_paged over shaped buckets: the shape table lies row for row beside `centroids` (the pages of a
+ * serving cache hold a bucket's shape where they hold its centroid). */
+int lsa_shaped_select_paged(const float *queries, int64_t R, int d, const float *centroids, int64_t rows,
+                            const uint8_t *basis, const float *variances, const float *floors, int rank,
+                            float deviations, const int32_t *pages, int max_pages, int page_rows,
+                            const int32_t *counts, int top_p, int splits, int64_t *keys_out, int32_t *picked_out,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
 /* Shaped scores written out: row r against the table rows rows[r, :] (int32, -1 = none: -inf), or against table
  * rows 0..width when rows is NULL (score_shaped_rows, add_planes_spread, scan_paged_shaped of the reference).
  *   scores_out [R, width] fp32 */
 int lsa_shaped_scores(const float *queries, int64_t R, int d, const float *centroids, int64_t m, const uint8_t *basis,
                       const float *variances, const float *floors, int rank, float deviations, const int32_t *rows,
                       int64_t width, float *scores_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------------------
+ * Prefix reuse: a fingerprint of each page of what a rank stores for a request's keys, by which a request that
+ * arrives with a cached prefix takes the index pages another request built from the same bits. Reference:
+ * page_fingerprints, fingerprint_weights (src/lsa/sglang/index/layer_index.py:89-122), KeyLookup.fingerprints
+ * (layer_index.py:586-610), BucketCache.adopt / fingerprint (src/lsa/sglang/index/bucket_cache.py:257-331).
+ * A row's bits are read as int64 words w; out[p] = sum_r position_weights[r] * sum_w word_weights[w] * row(p, r)[w],
+ * wrapping as int64 sums do: exact and independent of the order of addition.
+ *   stored   the pool's rows: row i at byte i * row_stride_bytes, row_bytes read of each (both multiples of 8)
+ *   slots    [pages * page_rows] int64 or NULL - the row of `stored` that holds each position of the pages (a
+ *            request table's KV slots; < 0 or >= slot_count adds nothing); NULL = the rows are the positions
+ *   owned    [pages * page_rows] uint8 or NULL - 0 where another rank of a decode group owns the slot (adds nothing)
+ *   word_weights [>= row_bytes / 8] int64, position_weights [page_rows] int64 (odd);  out [pages] int64 */
+int lsa_page_fingerprints(const void *stored, int64_t row_stride_bytes, int row_bytes, const int64_t *slots,
+                          int64_t slot_count, int64_t pages, int page_rows, const uint8_t *owned,
+                          const int64_t *word_weights, const int64_t *position_weights, int64_t *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------------------------
  * Tree search, one beam step: score the candidate rows of a level (open node buckets first_open..made and the

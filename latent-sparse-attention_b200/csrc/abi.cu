@@ -16,4 +16,4 @@ LSA_API const char *lsa_error_string(int code) {
   }
 }
 
-LSA_API int lsa_abi_version(void) { return 17; }
+LSA_API int lsa_abi_version(void) { return 18; }

@@ -1370,6 +1370,36 @@ LSA_API int lsa_flat_select_paged(const float *queries, int64_t R, int d, const 
   return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
 }
 
+LSA_API int lsa_shaped_select_paged(const float *queries, int64_t R, int d, const float *centroids, int64_t rows,
+                                    const uint8_t *basis, const float *variances, const float *floors, int rank,
+                                    float deviations, const int32_t *pages, int max_pages, int page_rows,
+                                    const int32_t *counts, int top_p, int splits, int64_t *keys_out,
+                                    int32_t *picked_out, void *workspace, size_t workspace_bytes, void *stream) {
+  LSA_REQUIRE(queries && centroids && pages && counts && keys_out, LSA_ERR_NULL);
+  LSA_REQUIRE(R >= 0 && rows >= 0 && max_pages >= 1 && page_rows >= 1 && top_p >= 1 && splits >= 1 && splits <= 1024,
+              LSA_ERR_ARGUMENT);
+  lsa::ShapeTable table;
+  LSA_REQUIRE(lsa::shape_table(&table, basis, variances, floors, rank, deviations, d), LSA_ERR_ARGUMENT);
+  if (R == 0) return LSA_OK;
+  if (splits > 1) {
+    LSA_REQUIRE(workspace, LSA_ERR_NULL);
+    LSA_REQUIRE(workspace_bytes >= lsa_flat_select_decode_workspace_bytes(R, top_p, splits), LSA_ERR_WORKSPACE);
+  }
+  lsa::SelectParams p = {};
+  p.queries = queries, p.vectors = centroids, p.run_end = counts;
+  p.pages = pages, p.max_pages = max_pages, p.page_rows = page_rows;
+  p.R = R, p.N = rows, p.d = d, p.keep = top_p, p.run_limit = INT32_MAX;
+  p.shape = table;
+  if (splits == 1) {
+    p.keys_out = keys_out, p.ids_out = picked_out;
+    return lsa::launch_select<1>(p, 1, (cudaStream_t)stream);
+  }
+  p.keys_out = (int64_t *)workspace;
+  int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
+  if (rc != LSA_OK) return rc;
+  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+}
+
 LSA_API size_t lsa_beam_step_workspace_bytes(int64_t R, int keep, int splits) {
   return lsa_flat_select_decode_workspace_bytes(R, keep, splits);
 }

@@ -13,7 +13,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liblsa_b200.so")
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 PAD = -1
@@ -48,7 +48,10 @@ SIGNATURES = {
     "lsa_shape_build": (_I, [_P, _L, _L, _P, _P, _L, _I, _I, _I, _P, _P, _P, _P]),
     "lsa_shaped_select": (_I, [_P, _L, _I, _P, _L, _P, _P, _P, _I, _F, _P, _P, _I, c_int32, _P, _P, _P]),
     "lsa_shaped_select_decode": (_I, [_P, _L, _I, _P, _P, _P, _P, _I, _F, _P, _P, _I, _I, _P, _P, _P, _Z, _P]),
+    "lsa_shaped_select_paged": (_I, [_P, _L, _I, _P, _L, _P, _P, _P, _I, _F, _P, _I, _I, _P, _I, _I, _P, _P, _P, _Z,
+                                     _P]),
     "lsa_shaped_scores": (_I, [_P, _L, _I, _P, _L, _P, _P, _P, _I, _F, _P, _L, _P, _P]),
+    "lsa_page_fingerprints": (_I, [_P, _L, _I, _P, _L, _L, _I, _P, _P, _P, _P, _P]),
     "lsa_beam_step": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _P, _P, _P, _P]),
     "lsa_beam_step_workspace_bytes": (_Z, [_L, _I, _I]),
     "lsa_beam_step_split": (_I, [_P, _L, _I, _P, _L, _P, _I, _P, _P, _I, _P, _I, _I, _P, _P, _P, _P, _Z, _P]),

@@ -4,6 +4,8 @@
     ScanSelect                                                  scan_select.py:189-385
     dense_keys / listed_keys / sample_thresholds                scan_select.py:24-143
     scan_paged                                                  triton/paged.py:61-101
+    ShapeTable / build_shapes / build_bucket_shapes / score_shaped_rows / add_spread / add_planes_spread /
+    scan_paged_shaped                                           triton/shape.py:42-886
     TopK / top_keys                                             triton/top_k.py:708-997
     DecodeSelect                                                cutedsl/decode.py:1035-1086
     expand_in_order / expand_by_threshold                       expansion.py:16-126
@@ -75,11 +77,13 @@ class ScanSelect:
         return self.pick(self.listed(index_queries, bucket_centroids, visible_counts, shapes))
 
     def listed(self, index_queries, bucket_centroids, visible_counts, shapes=None) -> Listing:
-        if shapes is not None:
-            raise NotImplementedError("bucket shapes are not built in lsa_b200")
         rows = index_queries.shape[0]
-        ops.flat_select(index_queries, bucket_centroids, visible_counts, self.top_p, keys=self.keys[:rows],
-                        picked=self.out[:rows])
+        if shapes is not None:  # (an `ops.ShapeTable`, row for row with the centroids)
+            ops.shaped_select(index_queries, bucket_centroids, shapes, visible_counts, self.top_p,
+                              keys=self.keys[:rows], picked=self.out[:rows])
+        else:
+            ops.flat_select(index_queries, bucket_centroids, visible_counts, self.top_p, keys=self.keys[:rows],
+                            picked=self.out[:rows])
         return Listing(self.keys[:rows], visible_counts)
 
     def holds_top_p(self, listing: Listing) -> bool:
@@ -100,19 +104,90 @@ class ScanSelect:
 SAMPLE_TARGET, SAMPLE_RANK, SCAN_MARGIN = 1.5, 64, 1e-4  # (kernels/constants.py:179-186)
 
 
+def _dense_scores(index_queries, bucket_centroids, visible_counts, width=None, shapes=None) -> torch.Tensor:
+    """Every bucket a row sees scored at its own column [R, width] fp32, -inf past a row's count: by its centroid, or
+    with `shapes` (an `ops.ShapeTable`) by its estimated best key."""
+    if shapes is None:
+        return ops.dense_scores(index_queries, bucket_centroids, visible_counts, width)
+    scores = ops.shaped_scores(index_queries, bucket_centroids, shapes, width=width)
+    columns = torch.arange(scores.shape[1], device=scores.device)
+    return torch.where(columns[None] < visible_counts.to(torch.int64)[:, None], scores, float("-inf"))
+
+
 def dense_keys(index_queries, bucket_centroids, visible_counts, width=None, shapes=None, query_planes=None,
                kernels: str = "b200") -> torch.Tensor:
     """Every bucket a row sees scored and packed with its bucket, at its own column [R, width] int64, the empty key
-    past a row's length (scan_select.py:24-58)."""
-    if shapes is not None:
-        raise NotImplementedError("bucket shapes are not built in lsa_b200")
-    return ops.dense_scores(index_queries, bucket_centroids, visible_counts, width, keys=True)
+    past a row's length (scan_select.py:24-58). `shapes`: the buckets' `ShapeTable`; the reference scores a shaped
+    bucket against the bit-planes of the query (`query_planes`), here the query itself is read and none are needed."""
+    if shapes is None:
+        return ops.dense_scores(index_queries, bucket_centroids, visible_counts, width, keys=True)
+    scores = _dense_scores(index_queries, bucket_centroids, visible_counts, width, shapes)
+    ids = torch.arange(scores.shape[1], device=scores.device, dtype=torch.int32)[None].expand_as(scores)
+    return torch.where(scores > float("-inf"), pack_keys(scores, ids), PackedKey.EMPTY)
 
 
 def scan_paged(index_queries, bucket_centroids, pages, counts, page_size: int, max_rows: int) -> torch.Tensor:
     """Each request's buckets scored through its pages [B, max_rows] fp32, -inf past a request's count or on a page
     it has not got (triton/paged.py:61-101)."""
     return ops.dense_scores(index_queries, bucket_centroids, counts, max_rows, pages=pages, page_rows=page_size)
+
+
+# --------------------------------------------------------------------------------------------- bucket shapes
+
+ShapeTable = ops.ShapeTable  # (triton/shape.py:42-61)
+
+
+def build_shapes(index_keys, centroids, members, rank: int):
+    """Shape each bucket over every key under it (triton/shape.py:798-846): (packed sign basis [N, rank, d / 8] uint8,
+    variances [N, rank] fp32 descending, floor [N] fp32). `index_keys` maps positions [M] int64 to their index keys
+    [M, d], as the reference's callers pass it, or is the key matrix itself."""
+    if callable(index_keys):
+        held = members >= 0
+        if not bool(held.any()):
+            keys, first = torch.zeros(1, centroids.shape[1], device=centroids.device), 0
+        else:
+            first, last = int(members[held].min()), int(members[held].max())
+            keys = index_keys(torch.arange(first, last + 1, device=members.device))
+    else:
+        keys, first = index_keys, 0
+    built = ops.shape_build(keys, centroids, members, rank, key_base=first)
+    return built.basis, built.variances, built.floor
+
+
+def build_bucket_shapes(index_keys, centroids, members, rank: int):
+    """Shape buckets of at most a cap of keys exactly (triton/shape.py:849-886). The device build is exact for any
+    bucket, so this is `build_shapes`."""
+    return build_shapes(index_keys, centroids, members, rank)
+
+
+def score_shaped_rows(index_queries, centroids, basis, variances, floor, rows, deviations: float) -> torch.Tensor:
+    """Each query against the table rows it names by their estimated best key [S, width] fp32, -inf where a row is
+    -1 (triton/shape.py:281-343)."""
+    return ops.shaped_scores(index_queries, centroids, ShapeTable(basis, variances, floor, deviations), rows=rows)
+
+
+def add_spread(scores, index_queries, basis, variances, floor, deviations: float) -> torch.Tensor:
+    """`scores` [S, m] plus `deviations` times each bucket's spread under each query (triton/shape.py:523-570)."""
+    zero = torch.zeros(floor.shape[0], index_queries.shape[1], device=scores.device)
+    return scores + ops.shaped_scores(index_queries, zero, ShapeTable(basis, variances, floor, deviations),
+                                      width=scores.shape[1])
+
+
+def add_planes_spread(scores, index_queries, shapes: ShapeTable) -> torch.Tensor:
+    """The same from a table (triton/shape.py:407-450; the reference reads the query's bit-planes there and the bf16
+    query in `add_spread`, here both read the fp32 query and agree bit for bit)."""
+    return add_spread(scores, index_queries, shapes.basis, shapes.variances, shapes.floor, shapes.deviations)
+
+
+def scan_paged_shaped(index_queries, bucket_centroids, shapes: ShapeTable, pages, counts, page_size: int,
+                      max_rows: int) -> torch.Tensor:
+    """Each request's buckets scored by their estimated best key through its pages [B, max_rows] fp32, -inf past a
+    request's count or on a page it has not got (triton/shape.py:659-717)."""
+    logical = torch.arange(max_rows, device=pages.device)
+    page = pages.long()[:, (logical // page_size).clamp_max(pages.shape[1] - 1)]
+    held = (logical[None] < counts.to(torch.int64)[:, None]) & (page >= 0) & (logical[None] // page_size < pages.shape[1])
+    rows = torch.where(held, page * page_size + logical[None] % page_size, -1).to(torch.int32)
+    return ops.shaped_scores(index_queries, bucket_centroids, shapes, rows=rows)
 
 
 def sample_plan(top_p: int) -> tuple:
@@ -127,12 +202,11 @@ def sample_thresholds(index_queries, bucket_centroids, visible_counts, top_p: in
     """Each row's score at 1.5 times its top_p, estimated from every stride-th bucket it sees [R] fp32, -inf for a
     row that sees too few to rank (scan_select.py:110-143). The estimate here is the sampled score of that rank
     itself, where the reference takes the lower edge of its histogram bin: both err toward more survivors."""
-    if shapes is not None:
-        raise NotImplementedError("bucket shapes are not built in lsa_b200")
     stride, rank = sample_plan(top_p)
     sampled = bucket_centroids[::stride]
     counts = (visible_counts.to(torch.int64) + stride - 1) // stride
-    scores = ops.dense_scores(index_queries, sampled, counts.to(torch.int32))
+    scores = _dense_scores(index_queries, sampled, counts.to(torch.int32),
+                           shapes=None if shapes is None else shapes.rows(slice(None, None, stride)))
     if scores.shape[1] < rank:
         return torch.full((scores.shape[0],), float("-inf"), device=scores.device)
     ranked = scores.topk(rank, dim=1).values[:, rank - 1]
@@ -144,9 +218,7 @@ def listed_keys(index_queries, bucket_centroids, visible_counts, thresholds, cap
     """The buckets each row scores near its threshold, scored and packed (scan_select.py:61-107): packed keys
     [R, capacity] int64 of the first `capacity` listed buckets in bucket order, the empty key after; buckets each row
     listed [R] int32 (above capacity: the buffer overflowed); listed buckets at or above the threshold [R] int32."""
-    if shapes is not None:
-        raise NotImplementedError("bucket shapes are not built in lsa_b200")
-    keys = dense_keys(index_queries, bucket_centroids, visible_counts)
+    keys = dense_keys(index_queries, bucket_centroids, visible_counts, shapes=shapes)
     scores = unpack_scores(keys)
     shifted = thresholds - SCAN_MARGIN * index_queries.float().norm(dim=1)
     listed = (keys != PackedKey.EMPTY) & (scores >= shifted[:, None])

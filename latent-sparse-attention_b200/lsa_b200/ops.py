@@ -437,6 +437,28 @@ def shaped_select_decode(index_queries: torch.Tensor, centroids: torch.Tensor, s
     return keys, picked
 
 
+def shaped_select_paged(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: ShapeTable, pages: torch.Tensor,
+                        counts: torch.Tensor, page_rows: int, top_p: int, splits: int = 1,
+                        workspace: torch.Tensor | None = None):
+    """`flat_select_paged` over shaped buckets, the shapes paged as the centroids are
+    (src/lsa/core/kernels/triton/shape.py:573-717). Returns (keys, logical ids)."""
+    q, c = _contig(index_queries.float()), _contig(centroids.float())
+    pages = _contig(pages.to(torch.int32))
+    R, d = q.shape
+    basis, variances, floor = _shape_args(shapes, d)
+    keys = torch.empty(R, top_p, device=q.device, dtype=torch.int64)
+    picked = torch.empty(R, top_p, device=q.device, dtype=torch.int32)
+    need = query("lsa_flat_select_decode_workspace_bytes", R, top_p, splits)
+    if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, device=q.device, dtype=torch.uint8)
+    call("lsa_shaped_select_paged", ptr(q), R, d, ptr(c), c.shape[0], ptr(basis), ptr(variances), ptr(floor),
+         basis.shape[1], float(shapes.deviations), ptr(pages), pages.shape[1], page_rows,
+         ptr(_contig(counts.to(torch.int32))), top_p, splits, ptr(keys), ptr(picked), ptr(workspace),
+         workspace.numel() * workspace.element_size() if workspace is not None else 0, stream(),
+         launches=1 if splits == 1 else 2)
+    return keys, picked
+
+
 def shaped_scores(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: ShapeTable,
                   rows: torch.Tensor | None = None, width: int | None = None) -> torch.Tensor:
     """Shaped scores written out [R, width] fp32: row r against the table rows `rows[r]` (-1: -inf), or against the
@@ -449,6 +471,30 @@ def shaped_scores(index_queries: torch.Tensor, centroids: torch.Tensor, shapes: 
     out = torch.empty(R, width, device=q.device, dtype=torch.float32)
     call("lsa_shaped_scores", ptr(q), R, d, ptr(c), c.shape[0], ptr(basis), ptr(variances), ptr(floor), basis.shape[1],
          float(shapes.deviations), ptr(rows), width, ptr(out), stream())
+    return out
+
+
+def page_fingerprints(stored: torch.Tensor, page_rows: int, word_weights: torch.Tensor,
+                      position_weights: torch.Tensor, slots: torch.Tensor | None = None,
+                      owned: torch.Tensor | None = None) -> torch.Tensor:
+    """A fingerprint of each page of the bits a pool stores for a run of whole pages [pages] int64
+    (src/lsa/sglang/index/layer_index.py:106-122): `stored` [rows, dim] with contiguous rows of a multiple of 8 bytes
+    (any stride between rows), read at `slots` [pages * page_rows] int64 (None: rows 0.. in order); `owned`
+    [pages * page_rows] bool marks the slots this rank owns (the others add nothing)."""
+    if stored.dim() != 2 or stored.stride(1) != 1:
+        raise ValueError("stored rows must be contiguous [rows, dim]")
+    size = stored.element_size()
+    count = stored.shape[0] if slots is None else slots.shape[0]
+    if count % page_rows:
+        raise ValueError(f"{count} rows are not whole pages of {page_rows}")
+    if position_weights.shape[0] != page_rows or word_weights.shape[0] * 8 < stored.shape[1] * size:
+        raise ValueError("the weights cover a page's positions and a row's words")
+    slots = None if slots is None else _contig(slots.to(torch.int64))
+    owned = None if owned is None else _contig(owned.to(torch.uint8))
+    out = torch.empty(count // page_rows, device=stored.device, dtype=torch.int64)
+    call("lsa_page_fingerprints", ptr(stored), stored.stride(0) * size, stored.shape[1] * size, ptr(slots),
+         stored.shape[0], count // page_rows, page_rows, ptr(owned), ptr(_contig(word_weights)),
+         ptr(_contig(position_weights)), ptr(out), stream())
     return out
 
 

@@ -17,18 +17,55 @@ each request's index keys as they arrive and its page tables, and takes back lis
 
 from __future__ import annotations
 
+from dataclasses import dataclass
+
 import torch
 
 from lsa_b200 import ops, probe
 from lsa_b200.layer import FlatDesign
 
 
+@dataclass
+class Retained:
+    """A finished request's leading full pages and their fingerprints, kept for a request that shares them
+    (bucket_cache.py:60-67)."""
+
+    pages: list
+    prints: list
+    seen: int
+
+
+def fingerprints_of(lookup, first: int, count: int) -> list:
+    """The fingerprints of a request's pages [first, first + count), by the lookup's own read (bucket_cache.py:43-57).
+
+    Raises:
+        TypeError: The lookup reads no fingerprints, which prefix reuse needs.
+    """
+    fingerprints = getattr(lookup, "fingerprints", None)
+    if fingerprints is None:
+        raise TypeError("prefix reuse fingerprints pages from the pool, and this lookup reads none")
+    return fingerprints(first, count) if count > 0 else []
+
+
 class BucketCache:
-    """Paged store of every request's buckets (bucket_cache.py:70-140)."""
+    """Paged store of every request's buckets (bucket_cache.py:70-140).
+
+    Under `reuse` - the server's prefix cache on - a request that arrives with a cached prefix takes the index pages of
+    that prefix instead of building them again (bucket_cache.py:11-19): a full page's buckets are its own keys' alone
+    and never change once full, so a page is shared between requests by a count of its holders. A request fingerprints
+    each of its full pages from the pool once its keys are all there; when its row goes to another request, its leading
+    fingerprinted pages are kept as a `Retained` prefix rather than freed. A new request fingerprints its own leading
+    pages and takes the longest run that matches, from a retained prefix or a running request. Retained prefixes go
+    first when pages run short."""
 
     def __init__(self, design: FlatDesign, index_dim: int, pages: int, page_buckets: int, max_requests: int,
-                 max_request_pages: int, device="cuda"):
+                 max_request_pages: int, device="cuda", reuse: bool = False):
         self.design, self.page_buckets = design, page_buckets
+        self.reuse = reuse
+        self.holders = [0] * pages          # requests and retained prefixes that hold each page
+        self.prints: dict[int, list] = {}   # request -> fingerprints of its leading full pages
+        self.retained: list[Retained] = []
+        self.clock = 0                      # ticks once a release, to tell which retained prefix is the oldest
         rows = pages * page_buckets
         self.centroids = torch.zeros(rows, index_dim, device=device, dtype=torch.float32)
         self.members = torch.full((rows, design.bucket_cap), -1, device=device, dtype=torch.int32)
@@ -36,6 +73,15 @@ class BucketCache:
         self.request_pages = torch.full((max_requests, max_request_pages), -1, device=device, dtype=torch.int32)
         # Buckets each request holds, where a captured decode step can read it
         self.bucket_counts = torch.zeros(max_requests, device=device, dtype=torch.int32)
+        # Under `bucket_shape` each bucket also keeps its shape, built as its cluster block closes, in the row that
+        # holds its centroid (bucket_cache.py:8-10,108-116)
+        self.bucket_shapes: ops.ShapeTable | None = None
+        if design.bucket_shape is not None:
+            rank = design.bucket_shape.rank
+            self.bucket_shapes = ops.ShapeTable(
+                torch.zeros(rows, rank, index_dim // 8, device=device, dtype=torch.uint8),
+                torch.zeros(rows, rank, device=device), torch.zeros(rows, device=device),
+                design.bucket_shape.deviations)
         self.free_pages = list(range(pages - 1, -1, -1))
         self.held: dict[int, list] = {}      # request -> its pages, in order
         self.closed_keys: dict[int, int] = {}  # request -> keys of its closed cluster blocks
@@ -50,9 +96,30 @@ class BucketCache:
         held = self.pending.get(request)
         return self.closed_keys.get(request, 0) + (0 if held is None else held.shape[0])
 
-    def release(self, request: int) -> None:
-        """Give a finished request's pages back."""
-        self.free_pages.extend(reversed(self.held.pop(request, [])))
+    @property
+    def page_keys(self) -> int:
+        """Keys whose buckets fill a page."""
+        return self.page_buckets * self.design.bucket_size
+
+    def let_go(self, pages: list) -> None:
+        """Drop one holder of each page, freeing those no one holds any longer (bucket_cache.py:237-250)."""
+        freed = []
+        for page in pages:
+            self.holders[page] -= 1
+            if not self.holders[page]:
+                freed.append(page)
+        self.free_pages.extend(reversed(freed))
+
+    def release(self, request: int, retain: bool = True) -> None:
+        """Give a finished request's pages back - but for its leading fingerprinted pages, under `reuse`, which stay
+        as a retained prefix for a request that shares them (bucket_cache.py:196-235)."""
+        pages = self.held.pop(request, [])
+        prints = self.prints.pop(request, [])
+        self.clock += 1
+        if self.reuse and retain and prints:
+            self.retained.append(Retained(pages[:len(prints)], prints, self.clock))  # (the holder's count goes along)
+            pages = pages[len(prints):]
+        self.let_go(pages)
         self.closed_keys.pop(request, None)
         self.pending.pop(request, None)
         self.owner.pop(request, None)
@@ -78,6 +145,73 @@ class BucketCache:
             raise ValueError(f"request {request} holds {have} keys in its index and the pool {end}")
         return self.append(request, index_keys_of(have, end)) if end > have else 0
 
+    def adopt(self, request: int, end: int, lookup) -> int:
+        """Take the longest run of leading pages another request indexed from the same keys, under `reuse`
+        (bucket_cache.py:257-316). Only a request that holds nothing yet takes one - one just admitted with a cached
+        prefix of a page or more. The candidates are the retained prefixes and the requests holding fingerprinted
+        pages; a page matches when its fingerprint does, every page before it having matched. `lookup.fingerprints(
+        first, count)` reads the request's own pages from the pool. Returns the pages taken.
+
+        Raises:
+            TypeError: The lookup reads no fingerprints.
+        """
+        page_keys = self.page_keys
+        if not self.reuse or self.end(request) or end < page_keys:
+            return 0
+        donors = [(entry.pages, entry.prints) for entry in self.retained] + \
+            [(self.held[other][:len(found)], found) for other, found in self.prints.items() if other != request and found]
+        if not donors:
+            return 0
+        prints = fingerprints_of(lookup, 0, 1)
+        donors = [donor for donor in donors if donor[1][0] == prints[0]]
+        if not donors:
+            return 0
+        longest = min(end // page_keys, max(len(donor[1]) for donor in donors))
+        prints += fingerprints_of(lookup, 1, longest - 1)
+
+        def matched(theirs: list) -> int:
+            count = 0
+            while count < min(len(theirs), longest) and theirs[count] == prints[count]:
+                count += 1
+            return count
+
+        pages, theirs = max(donors, key=lambda donor: matched(donor[1]))
+        count = matched(theirs)
+        if count > self.request_pages.shape[1]:
+            raise RuntimeError(f"request {request} needs {count} index pages and a request holds at most "
+                               f"{self.request_pages.shape[1]}")
+        pages = list(pages[:count])
+        for page in pages:
+            self.holders[page] += 1
+        self.held[request] = pages
+        self.prints[request] = prints[:count]
+        self.request_pages[request, :count] = torch.tensor(pages, dtype=torch.int32, device=self.request_pages.device)
+        self.closed_keys[request] = count * page_keys
+        self.bucket_counts[request] = count * self.page_buckets
+        return count
+
+    def fingerprint(self, request: int, end: int, lookup) -> None:
+        """Fingerprint the request's full pages whose keys have all reached the pool, under `reuse`
+        (bucket_cache.py:318-331)."""
+        if not self.reuse:
+            return
+        full = min(self.closed_keys.get(request, 0), end) // self.page_keys
+        taken = self.prints.setdefault(request, [])
+        if full > len(taken):
+            taken += fingerprints_of(lookup, len(taken), full - len(taken))
+
+    def reclaim(self) -> None:
+        """Drop retained prefixes, oldest first, until a page is free (bucket_cache.py:252-255,355-378).
+
+        Raises:
+            RuntimeError: Every page belongs to a request.
+        """
+        while self.retained and not self.free_pages:
+            oldest = min(range(len(self.retained)), key=lambda index: self.retained[index].seen)
+            self.let_go(self.retained.pop(oldest).pages)
+        if not self.free_pages:
+            raise RuntimeError("the bucket cache is out of pages")  # bucket_cache.py:375-378
+
     def rows_of(self, request: int, logical: torch.Tensor) -> torch.Tensor:
         """Rows of the device tables that hold a request's logical buckets."""
         return self.request_pages[request][logical // self.page_buckets].long() * self.page_buckets + \
@@ -89,6 +223,14 @@ class BucketCache:
         logical = torch.arange(buckets, device=self.centroids.device)
         return self.centroids[self.rows_of(request, logical)]
 
+    def gather_shapes(self, request: int, buckets: int) -> ops.ShapeTable | None:
+        """The shapes of the buckets `gather` returns, row for row, or None when buckets are not shaped
+        (bucket_cache.py:455-466)."""
+        if self.bucket_shapes is None:
+            return None
+        logical = torch.arange(buckets, device=self.centroids.device)
+        return self.bucket_shapes.rows(self.rows_of(request, logical))
+
     def _grow(self, request: int, buckets: int) -> None:
         pages = self.held.setdefault(request, [])
         need = -(-buckets // self.page_buckets)
@@ -98,8 +240,9 @@ class BucketCache:
         fresh = []
         while len(pages) < need:
             if not self.free_pages:
-                raise RuntimeError("the bucket cache is out of pages")  # bucket_cache.py:375-378
+                self.reclaim()
             fresh.append(self.free_pages.pop())
+            self.holders[fresh[-1]] = 1
             pages.append(fresh[-1])
         if fresh:
             first = len(pages) - len(fresh)
@@ -131,6 +274,12 @@ class BucketCache:
         self.centroids[rows] = centroids
         self.members[rows] = members
         self.sizes[rows] = sizes
+        if self.bucket_shapes is not None:  # (bucket_cache.py:603-627; members are positions from `first_position`)
+            with probe.region("bucket shapes"):
+                built = ops.shape_build(block_keys, centroids, members, d.bucket_shape.rank, key_base=first_position)
+            self.bucket_shapes.basis[rows] = built.basis
+            self.bucket_shapes.variances[rows] = built.variances
+            self.bucket_shapes.floor[rows] = built.floor
         self.closed_keys[request] = first_position + closed
         self.bucket_counts[request] = first_bucket + blocks * per_block
         return blocks
@@ -154,7 +303,10 @@ class Selector:
         closed = 0
         for rid, row, end in zip(rids, rows, ends, strict=True):
             self.cache.ensure(row, rid)
-            closed += self.cache.advance(row, end, index_keys_of(row))
+            lookup = index_keys_of(row)
+            self.cache.adopt(row, end, lookup)
+            closed += self.cache.advance(row, end, lookup)
+            self.cache.fingerprint(row, end, lookup)
         return closed
 
     def prefill(self, row: int, index_queries: torch.Tensor, positions: torch.Tensor, index_keys: torch.Tensor,
@@ -192,7 +344,10 @@ class Selector:
         visible = (positions // d.cluster_block_size * d.block_bucket_count).clamp_max(seen).to(torch.int32)
         with probe.region("index q scan"):
             centroids = cache.gather(row, seen)
-            if S >= self.scan_rows and centroids.shape[1] == 64 and d.top_p <= 512:
+            if cache.bucket_shapes is not None:
+                _, picked = ops.shaped_select(index_queries, centroids, cache.gather_shapes(row, seen), visible,
+                                              d.top_p)
+            elif S >= self.scan_rows and centroids.shape[1] == 64 and d.top_p <= 512:
                 operand, lengths, radius = ops.scan_centre(centroids, centroids.mean(0))
                 _, picked = ops.scan_select(index_queries, centroids, operand, visible, d.top_p, max_visible=seen,
                                             lengths=lengths, radius=radius)
@@ -215,13 +370,22 @@ class Selector:
         visible = torch.minimum(positions // d.cluster_block_size * d.block_bucket_count,
                                 cache.bucket_counts[rows].long()).to(torch.int32)
         with probe.region("index q scan"):
-            _, picked = ops.flat_select_paged(index_queries, cache.centroids, cache.request_pages[rows], visible,
-                                              cache.page_buckets, d.top_p, splits=splits)
+            _, picked = self._scan_paged(index_queries, cache.request_pages[rows], visible, splits)
         with probe.region("expand"):
             lists, _, _ = ops.expand_batched(picked, positions, rows.to(torch.int32), cache.members,
                                              cache.request_pages, cache.page_buckets, self.slot_table(),
                                              self.kv_page_size, d.top_k, d.sink_size, d.window_size, local=local)
         return lists
+
+    def _scan_paged(self, index_queries: torch.Tensor, pages: torch.Tensor, visible: torch.Tensor, splits: int):
+        """A decode step's scan through the requests' page tables: by centroid, or under `bucket_shape` by each
+        bucket's estimated best key (selector.py:603-660)."""
+        cache = self.cache
+        if cache.bucket_shapes is not None:
+            return ops.shaped_select_paged(index_queries, cache.centroids, cache.bucket_shapes, pages, visible,
+                                           cache.page_buckets, cache.design.top_p, splits=splits)
+        return ops.flat_select_paged(index_queries, cache.centroids, pages, visible, cache.page_buckets,
+                                     cache.design.top_p, splits=splits)
 
     def visible(self, request_rows: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """Buckets each row sees: those of the cluster blocks closed before its own, that the cache holds."""
@@ -238,8 +402,7 @@ class Selector:
         visible = self.visible(request_rows, positions) if visible is None else visible
         pages = cache.request_pages[request_rows.long()]
         with probe.region("index q scan"):
-            _, picked = ops.flat_select_paged(index_queries, cache.centroids, pages, visible, cache.page_buckets,
-                                              d.top_p, splits=splits)
+            _, picked = self._scan_paged(index_queries, pages, visible, splits)
         with probe.region("expand"):
             rows = torch.arange(request_rows.shape[0], device=picked.device, dtype=torch.int32)
             lists, lengths, _ = ops.expand_batched(picked, positions, rows, cache.members, pages, cache.page_buckets,

@@ -8,8 +8,9 @@ the pool's slot when the cache needs it (`PoolKeys`), and a prefill indexes its 
 What this build serves is the key-and-query input of a grouped-query or latent pool: on one rank, with the pool's
 slots split over a decode group (`Shard`: a key is mapped on the rank that owns its slot and the group sums), or with
 the key heads split over tensor-parallel ranks (`KeySplit`: partial index vectors summed across the group, a token's
-index key made once and kept at its KV slot). The attention input `x` and prefix reuse are refused where the
-reference takes them.
+index key made once and kept at its KV slot). Under `prefix_reuse` a request that arrives with a cached prefix takes
+the index pages another request built from the same pool bits (page fingerprints). The attention input `x` is
+refused where the reference takes it.
 """
 
 from __future__ import annotations
@@ -23,6 +24,45 @@ from lsa_b200 import ops
 from lsa_b200.serving import BucketCache, Selector
 from lsa_b200.sglang.index_space import KeyAndQuery, KeySlot
 from lsa_b200.sglang.settings import PAGE_SIZE, DesignSettings
+
+
+# Pages fingerprinted a call, which bounds the slots a call reads (`layer_index.py:56`)
+FINGERPRINT_PAGES = 8
+# Bits a piece of a fingerprint holds while a group sums it: a collective that adds in fp32 is exact on such pieces
+FINGERPRINT_PIECE_BITS = 16
+FINGERPRINT_SEED = 20261007
+FINGERPRINT_WORDS = 4096
+_FINGERPRINT_WEIGHTS: dict = {}
+
+
+def fingerprint_weights(device) -> tuple:
+    """The fingerprint's odd int64 weights - one a word of a key's stored bits, one a position of a page - drawn as
+    the reference draws them, so a page's fingerprint is the same number (`layer_index.py:89-103`)."""
+    key = str(device)
+    if key not in _FINGERPRINT_WEIGHTS:
+        generator = torch.Generator().manual_seed(FINGERPRINT_SEED)
+        words, positions = (torch.randint(-(1 << 62), 1 << 62, (count,), generator=generator) | 1
+                            for count in (FINGERPRINT_WORDS, PAGE_SIZE))
+        _FINGERPRINT_WEIGHTS[key] = (words.to(device), positions.to(device))
+    return _FINGERPRINT_WEIGHTS[key]
+
+
+def page_fingerprints(stored: torch.Tensor, owned: torch.Tensor | None, slots: torch.Tensor | None = None) -> torch.Tensor:
+    """A fingerprint of each page of what a rank stores for its keys [pages] int64 (`layer_index.py:106-122`): a
+    weighted sum of the bits that wraps instead of rounding, so it is exact, the order it adds in does not change it,
+    and pages that differ in any bit match by chance alone. A slot another rank owns adds nothing, so a group's sum is
+    the fingerprint of the whole page. `stored` [rows, dim] is read at `slots` (None: its rows are a run of whole
+    pages in order)."""
+    words, positions = fingerprint_weights(stored.device)
+    return ops.page_fingerprints(stored, PAGE_SIZE, words, positions, slots=slots, owned=owned)
+
+
+def exact_group_sum(values: torch.Tensor, reduce: Callable[[torch.Tensor], torch.Tensor]) -> torch.Tensor:
+    """int64 values summed across a group exactly, wrapping as an int64 sum does, whatever dtype the collective adds
+    in: 16-bit pieces as floats, put back together (`layer_index.py:125-137`)."""
+    shifts = FINGERPRINT_PIECE_BITS * torch.arange(64 // FINGERPRINT_PIECE_BITS, device=values.device)
+    pieces = ((values[:, None] >> shifts) & ((1 << FINGERPRINT_PIECE_BITS) - 1)).float()
+    return (reduce(pieces).long() << shifts).sum(1)
 
 
 @dataclass(frozen=True)
@@ -62,6 +102,11 @@ class KeyBuffer:
 
     def read(self, slots: torch.Tensor) -> torch.Tensor:
         return self.keys[slots]
+
+    def stored(self, slots: torch.Tensor) -> tuple:
+        """What this rank stores for KV slots - their index keys - as (table, rows of it, ownership or None), for a
+        fingerprint to read in place (`layer_index.py:221-232`)."""
+        return self.keys, slots, None
 
 
 class KeyAndQueryProjection:
@@ -182,6 +227,21 @@ class PoolKeys:
         return self.shard.reduce(index_keys * owned[:, None])
 
 
+    def stored(self, slots: torch.Tensor) -> tuple:
+        """What this rank's pool stores for KV slots - their key input - as (table [pool rows, dims], rows of it,
+        ownership or None), for a fingerprint to read in place (`layer_index.py:515-527`): the pool's own bits, not
+        index keys - a projection rounds by the size of its batch, the pool does not."""
+        size, slot = self.shard.size, self.projection.key_slot
+        owned = None if size == 1 else slots % size == self.shard.rank
+        rows = slots if size == 1 else torch.where(owned, slots // size, 0)
+        buffer = self.key_buffer()
+        bytes_ = buffer.element_size()
+        if slot.heads == 1 and (slot.offset * bytes_) % 8 == 0 and (slot.width * bytes_) % 8 == 0 \
+                and (buffer.stride(0) * bytes_) % 8 == 0:
+            return buffer[:, 0, slot.offset:slot.offset + slot.width], rows, owned  # (a view: nothing is copied)
+        return slot.read(buffer, rows), None, owned
+
+
 class KeyLookup:
     """One request's positions to their index keys: the pool's, and a chunk's own where the chunk is in hand
     (`layer_index.py:530-611`)."""
@@ -197,6 +257,24 @@ class KeyLookup:
             start, keys = self.chunk
             return keys[first - start:stop - start]
         return self.buffer.read(table[self.row, first:stop].long())
+
+    def fingerprints(self, first: int, count: int) -> list:
+        """The fingerprints of the request's pages [first, first + count), read from the pool
+        (`layer_index.py:586-610`). Under a decode group every rank fingerprints the slots it owns and the group sums
+        them, so every rank holds the same numbers."""
+        shard = getattr(self.buffer, "shard", None)
+        prints = []
+        for start in range(first, first + count, FINGERPRINT_PAGES):
+            stop = min(first + count, start + FINGERPRINT_PAGES)
+            slots = self.slot_table()[self.row, start * PAGE_SIZE:stop * PAGE_SIZE].long()
+            stored, rows, owned = self.buffer.stored(slots)
+            prints.append(page_fingerprints(stored, owned, rows))
+        if not prints:
+            return []
+        total = torch.cat(prints)
+        if shard is not None and shard.reduce is not None:
+            total = exact_group_sum(total, shard.reduce)
+        return total.tolist()
 
 
 class LayerIndex:
@@ -222,11 +300,11 @@ class LayerIndex:
 
         Raises:
             ValueError: No way to the KV pool's keys.
-            NotImplementedError: A decode group, a tensor-parallel split, a cross-rank head sum or prefix reuse.
+            NotImplementedError: A cross-rank head sum.
         """
         shard = shard or Shard()
-        if sum_heads is not None or prefix_reuse:
-            raise NotImplementedError("this build serves no cross-rank head sum for an MLA latent and no prefix reuse")
+        if sum_heads is not None:
+            raise NotImplementedError("this build serves no cross-rank head sum for an MLA latent")
         if shard.size > 1 and shard.reduce is None:
             raise ValueError("a decode context-parallel shard needs the sum across its group")
         if split is not None and shard.size > 1:
@@ -251,7 +329,8 @@ class LayerIndex:
         request_pages = -(-max_context // PAGE_SIZE) + 1
         # (under a decode group every rank indexes each request's whole context: the cache covers `size` pools)
         pages = -(-kv_size * shard.size // PAGE_SIZE) + requests  # (a request's last page is part full)
-        cache = BucketCache(design, self.index_dim, pages, page_buckets, requests, request_pages, device)
+        cache = BucketCache(design, self.index_dim, pages, page_buckets, requests, request_pages, device,
+                            reuse=prefix_reuse)
         self.selector = Selector(cache, 1, slot_table)
         self.prefill_chunk, self.starts_checked = prefill_chunk, False
         # An attention backend that saves a forward's keys before it selects turns the layer's own write off

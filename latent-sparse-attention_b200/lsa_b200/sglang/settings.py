@@ -10,6 +10,7 @@ from typing import Any
 
 from lsa_b200.budget import EarlyBudget
 from lsa_b200.layer import FlatDesign
+from lsa_b200.shape import Shape
 
 BLOCK = "lsa"
 PAGE_SIZE = 8192  # keys a page of the bucket cache holds: where a prefill segment is cut and a tree grows
@@ -36,6 +37,8 @@ class IndexerConfig:
     beam_width: int | None = None
     start_nodes: int | None = None
     early_budget: EarlyBudget | None = None
+    bucket_shape: Shape | None = None  # buckets keep their spread and score as their estimated best key
+    node_bucket_shape: Shape | None = None  # the same for the node buckets of a tree
 
     def __post_init__(self) -> None:
         pool = self.pool_size or 1
@@ -61,11 +64,37 @@ class IndexerConfig:
                 (self.top_level < 1 and any(value is not None for value in tree)):
             raise ValueError("node_bucket_size, node_cluster_block_size and beam_width are set exactly when "
                              "top_level is 1 or more")
+        self.check_shapes()
         if self.early_budget is not None:
             if self.top_level:
                 raise ValueError("an early budget is flat only")
             if self.early_budget.top_p > self.top_p or self.early_budget.top_k > self.top_k:
                 raise ValueError("the early budget is at most the design's top_p and top_k")
+
+    def check_shapes(self) -> None:
+        """Build the shape knobs from their mappings and refuse a shape the design cannot hold (design.py:317-345).
+
+        Raises:
+            ValueError: A shape is refused, keeps more directions than `index_dim` (or than `bucket_cap`, the most
+                keys a bucket holds), `index_dim` is not a multiple of 32 (a basis is read a word at a time), or
+                `node_bucket_shape` is set: node buckets are not shaped here.
+        """
+        for name in ("bucket_shape", "node_bucket_shape"):
+            shape = Shape.read(name, getattr(self, name))
+            object.__setattr__(self, name, shape)
+            if shape is None:
+                continue
+            if shape.rank > self.index_dim:
+                raise ValueError(f"{name} keeps at most index_dim {self.index_dim} directions - got rank {shape.rank}")
+            if self.index_dim % 32:
+                raise ValueError(f"a shaped design needs index_dim a multiple of 32 - got {self.index_dim}")
+        if self.bucket_shape is not None and self.bucket_shape.rank > self.bucket_cap:
+            raise ValueError(f"bucket_shape keeps at most bucket_cap {self.bucket_cap} directions - got rank "
+                             f"{self.bucket_shape.rank}")
+        if self.node_bucket_shape is not None:
+            if self.top_level < 1:
+                raise ValueError("node_bucket_shape is set with top_level 0, where there are no node buckets")
+            raise ValueError("node_bucket_shape is not served: this build shapes the buckets of a flat design only")
 
     @property
     def width(self) -> int:
@@ -75,7 +104,8 @@ class IndexerConfig:
     def flat_design(self) -> FlatDesign:
         return FlatDesign(pool_size=self.pool_size or 1, bucket_size=self.bucket_size, bucket_cap=self.bucket_cap,
                           cluster_block_size=self.window_size, top_p=self.top_p, top_k=self.top_k,
-                          sink_size=self.sink_size, window_size=self.window_size, early_budget=self.early_budget)
+                          sink_size=self.sink_size, window_size=self.window_size, early_budget=self.early_budget,
+                          bucket_shape=self.bucket_shape)
 
 
 @dataclass(frozen=True)

@@ -234,3 +234,106 @@ def test_a_layer_of_a_shaped_design_reads_by_estimated_best_keys(oracle):
     with pytest.raises(ValueError, match="bucket_shape keeps at most bucket_cap 4 directions - got rank 5"):
         FlatDesign(pool_size=1, bucket_size=2, bucket_cap=4, cluster_block_size=64, top_p=64, top_k=64,
                    bucket_shape={"rank": 5})
+
+
+def test_a_serving_cache_pages_the_shapes_with_the_centroids(oracle):
+    from lsa_b200.layer import FlatDesign
+    from lsa_b200.serving import BucketCache, Selector
+
+    design = FlatDesign(pool_size=4, bucket_size=16, bucket_cap=32, cluster_block_size=256, top_p=6, top_k=150,
+                        sink_size=4, window_size=256, bucket_shape={"rank": 2, "deviations": 2.0})
+    d_idx, page_buckets = 32, 32
+    lengths = [700, 2048, 3000]
+    rng = np.random.default_rng(0)
+    cache = BucketCache(design, d_idx, pages=16, page_buckets=page_buckets, max_requests=4, max_request_pages=8)
+    slots = rng.permutation(4 * 3072).astype(np.int32).reshape(4, 3072)  # a request table of one-token pages
+    selector = Selector(cache, 1, slot_table=lambda: cuda(slots))
+    raws = [mixture(n, d_idx, 10, 0.3, 100 + r) for r, n in enumerate(lengths)]
+    keys = [unit_rows(raw) for raw in raws]
+    for r, n in enumerate(lengths):  # in pieces, the requests interleaved: their pages interleave too
+        cache.append(r, cuda(keys[r][: n // 3]))
+    for r, n in enumerate(lengths):
+        cache.append(r, cuda(keys[r][n // 3:]))
+    positions = np.array([n - 1 for n in lengths])
+    queries = np.stack([unit_rows(raws[r][positions[r]] + 0.3 * rng.standard_normal(d_idx).astype(np.float32))
+                        for r in range(len(lengths))])
+
+    def own_shapes(r):
+        held = cache.gather_shapes(r, cache.buckets_of(r))
+        return oracle.Shapes(held.basis.cpu().numpy(), held.variances.cpu().numpy(), held.floor.cpu().numpy())
+
+    for r in range(len(lengths)):  # what the cache built page by page is the oracle's build of the whole request
+        buckets = oracle.build_buckets(keys[r], 4, 16, 32, 256)
+        want = oracle.shape_buckets(keys[r], buckets, 2)
+        np.testing.assert_allclose(own_shapes(r).variances, want.variances, rtol=1e-3, atol=1e-6)
+        np.testing.assert_allclose(own_shapes(r).floor, want.floor, rtol=1e-3, atol=1e-6)
+    rows = torch.arange(len(lengths)).cuda()
+    for splits in (1, 3):
+        lists = selector.decode(cuda(queries), cuda(positions), rows, splits=splits)
+        for r in range(len(lengths)):
+            buckets = oracle.build_buckets(keys[r], 4, 16, 32, 256)
+            want, want_len = oracle.read(queries[r:r + 1], positions[r:r + 1], buckets, 6, 150, 4, 256,
+                                         shapes=own_shapes(r), deviations=2.0)
+            ids = want[0, : want_len[0]]
+            assert np.array_equal(lists[r, : int(want_len[0])].cpu().numpy(), slots[r][ids]), (r, splits)
+            assert (lists[r, int(want_len[0]):] == -1).all()
+    # a prefill segment of a fourth request: keys appended, every query reads the blocks closed before it, shaped
+    raw = mixture(1500, d_idx, 10, 0.3, 7)
+    seg_keys, seg_q = unit_rows(raw), unit_rows(raw + 0.3 * rng.standard_normal(raw.shape).astype(np.float32))
+    got = selector.prefill(3, cuda(seg_q), cuda(np.arange(1500)), cuda(seg_keys), 0)
+    buckets = oracle.build_buckets(seg_keys, 4, 16, 32, 256)
+    want, want_len = oracle.read(seg_q, np.arange(1500), buckets, 6, 150, 4, 256, shapes=own_shapes(3), deviations=2.0)
+    for r in (0, 255, 256, 700, 1499):
+        ids = want[r, : want_len[r]]
+        assert np.array_equal(got[r, : int(want_len[r])].cpu().numpy(), slots[3][ids]), r
+
+
+def test_the_front_doors_by_the_references_names(ops, oracle):
+    # (tests/unit/core/test_shape_kernels.py:116-164: rows scored, the dense spread, the decode scan through pages)
+    from lsa_b200 import kernels
+
+    keys, centroids, members = anisotropic_buckets(512, 16, 64, 2)
+    basis, variances, floor = kernels.build_bucket_shapes(lambda positions: cuda(keys)[positions], cuda(centroids),
+                                                          cuda(members), 2)
+    again = kernels.build_shapes(cuda(keys), cuda(centroids), cuda(members), 2)
+    assert torch.equal(basis, again[0]) and torch.equal(variances, again[1]) and torch.equal(floor, again[2])
+    table = kernels.ShapeTable(basis, variances, floor, 2.0)
+    mine = oracle.Shapes(basis.cpu().numpy(), variances.cpu().numpy(), floor.cpu().numpy())
+    rng = np.random.default_rng(3)
+    queries = unit_rows(rng.standard_normal((32, 64), dtype=np.float32))
+    want = oracle.shaped_scores(queries, centroids, mine, 2.0)
+    rows = rng.integers(-1, 512, (32, 200)).astype(np.int32)
+    got = kernels.score_shaped_rows(cuda(queries), cuda(centroids), basis, variances, floor, cuda(rows), 2.0)
+    expect = np.where(rows >= 0, np.take_along_axis(want, np.maximum(rows, 0), 1), -np.inf).astype(np.float32)
+    assert np.array_equal(got.cpu().numpy().view(np.int32), expect.view(np.int32))
+    # the dense spread and the row scoring agree on the spread bit for bit
+    zero = torch.zeros(512, 64, device="cuda")
+    every = torch.arange(512, device="cuda", dtype=torch.int32).expand(32, -1).contiguous()
+    from_rows = kernels.score_shaped_rows(cuda(queries), zero, basis, variances, floor, every, 2.0)
+    dense = kernels.add_planes_spread(torch.zeros(32, 512, device="cuda"), cuda(queries), table)
+    assert torch.equal(dense, from_rows)
+    assert torch.equal(kernels.add_spread(torch.zeros(32, 512, device="cuda"), cuda(queries), basis, variances, floor,
+                                          2.0), dense)
+    np.testing.assert_allclose(dense.cpu().numpy(), 2.0 * oracle.spread(queries, mine), atol=2e-6)
+    # the decode scan scores each page row as the row scoring does
+    page_size = 128
+    page_table = torch.tensor([[2, 0, 3, -1], [1, 3, -1, -1]], device="cuda", dtype=torch.int32)
+    counts = torch.tensor([3 * page_size - 7, page_size + 5], device="cuda", dtype=torch.int32)
+    scores = kernels.scan_paged_shaped(cuda(queries[:2]), cuda(centroids), table, page_table, counts, page_size,
+                                       4 * page_size)
+    logical = torch.arange(4 * page_size, device="cuda")
+    for request in range(2):
+        page = page_table[request, logical // page_size]
+        held = (logical < counts[request]) & (page >= 0)
+        at = torch.where(held, page * page_size + logical % page_size, -1).int()[None]
+        expect = kernels.score_shaped_rows(cuda(queries[request:request + 1]), cuda(centroids), basis, variances, floor,
+                                           at, 2.0)
+        assert torch.equal(scores[request:request + 1], expect)
+    # the two-pass selection over shaped buckets: dense keys, then the front door's pick
+    visible = cuda(rng.integers(0, 513, 32).astype(np.int32))
+    dense_keys = kernels.dense_keys(cuda(queries), cuda(centroids), visible, shapes=table)
+    select = kernels.ScanSelect(32, 16)
+    picked = select(cuda(queries), cuda(centroids), visible, shapes=table)
+    top = dense_keys.sort(dim=1, descending=True).values[:, :16]
+    assert torch.equal(select.keys, top)
+    assert torch.equal(picked, kernels.unpack_ids(top).to(torch.int32))

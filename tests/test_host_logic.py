@@ -165,3 +165,66 @@ def test_workload_generators_are_seeded_and_shaped():
     assert index_map.shape == (256, 32) and torch.allclose(index_map.t() @ index_map, torch.eye(32), atol=1e-4)
     for name, cfg in W.CONFIGS.items():
         W.design_of(cfg)  # the sizes of every config nest and fill their top_k
+
+
+class _Lookup:
+    """A request's pages as a list of fingerprints: what `KeyLookup.fingerprints` would read from the pool."""
+
+    def __init__(self, prints):
+        self.prints, self.reads = prints, 0
+
+    def fingerprints(self, first, count):
+        self.reads += count
+        return self.prints[first:first + count]
+
+
+def test_prefix_reuse_shares_full_pages_by_fingerprint_and_keeps_a_finished_prefix():
+    from lsa_b200.serving import BucketCache
+
+    design = FlatDesign(pool_size=1, bucket_size=2, bucket_cap=4, cluster_block_size=8, top_p=8, top_k=16)
+    cache = BucketCache(design, 32, pages=6, page_buckets=4, max_requests=4, max_request_pages=4, device="cpu",
+                        reuse=True)
+    page = cache.page_keys
+    assert page == 8
+
+    def filled(request, pages):  # (what `append` leaves once `pages` pages of keys were clustered)
+        cache._grow(request, pages * cache.page_buckets)
+        cache.closed_keys[request] = pages * page
+        cache.bucket_counts[request] = pages * cache.page_buckets
+
+    filled(0, 3)
+    cache.fingerprint(0, 3 * page, _Lookup([11, 12, 13]))
+    assert cache.prints[0] == [11, 12, 13] and cache.adopt(0, 3 * page, _Lookup([11, 12, 13])) == 0  # (it holds keys)
+    # a request sharing two pages takes them by reference; a third print it has not got keys for is never read
+    second = _Lookup([11, 12, 99])
+    assert cache.adopt(1, 2 * page + 3, second) == 2 and second.reads == 2
+    assert cache.held[1] == cache.held[0][:2] and cache.end(1) == 2 * page and int(cache.bucket_counts[1]) == 8
+    assert cache.request_pages[1, :2].tolist() == cache.held[0][:2] and cache.request_pages[1, 2] == -1
+    assert [cache.holders[p] for p in cache.held[0]] == [2, 2, 1] and len(cache.free_pages) == 3
+    assert cache.adopt(2, page - 1, _Lookup([11])) == 0            # less than a page in the pool
+    assert cache.adopt(2, 3 * page, _Lookup([77, 12, 13])) == 0     # the first page differs: nothing after it counts
+    # the first request ends: its fingerprinted pages stay as a retained prefix, nothing is freed
+    kept = list(cache.held[0])
+    cache.release(0)
+    assert len(cache.retained) == 1 and cache.retained[0].pages == kept and len(cache.free_pages) == 3
+    assert cache.adopt(2, 3 * page + 1, _Lookup([11, 12, 13, 14])) == 3 and cache.held[2] == kept
+    assert [cache.holders[p] for p in kept] == [3, 3, 2]
+    # a request that holds shared pages and ends keeps the prefix alive: each holder is counted
+    cache.release(2, retain=False)
+    cache.release(1, retain=False)
+    assert [cache.holders[p] for p in kept] == [1, 1, 1] and len(cache.free_pages) == 3
+    # pages run short: the retained prefix goes first, and its pages come back as no one else holds them
+    filled(3, 3)
+    assert not cache.free_pages
+    cache._grow(2, cache.page_buckets)
+    assert not cache.retained and len(cache.free_pages) == 2 and cache.holders[cache.held[2][0]] == 1
+    with pytest.raises(RuntimeError, match="out of pages"):
+        cache._grow(1, 3 * cache.page_buckets)
+    for request in (1, 2, 3):
+        cache.release(request, retain=False)
+    assert sorted(cache.free_pages) == list(range(6)) and not any(cache.holders)
+    with pytest.raises(TypeError, match="this lookup reads none"):
+        filled(0, 1)
+        cache.fingerprint(0, page, object())
+    plain = BucketCache(design, 32, pages=2, page_buckets=4, max_requests=2, max_request_pages=2, device="cpu")
+    assert plain.adopt(0, 4 * page, object()) == 0 and plain.fingerprint(0, page, object()) is None

@@ -283,3 +283,29 @@ def test_a_shaped_read_matches_the_reference(oracle):
         oracle.shape_buckets(g["read_keys"], buckets, 33)
     built = oracle.shape_buckets(g["read_keys"], buckets, 2)
     np.testing.assert_allclose(built.variances, shapes.variances, rtol=1e-5, atol=1e-8)
+
+
+def _fingerprint_pattern(rows, dim):
+    i, j = np.arange(rows, dtype=np.int64)[:, None], np.arange(dim, dtype=np.int64)[None]
+    return ((i * 40503 + j * 1201 + (i * j) % 251 + 7) & 0xFFFF).astype(np.uint16)
+
+
+def test_page_fingerprints_match_the_reference(oracle):
+    g = golden("fingerprints")
+    page = int(g["page_size"])
+    words, positions = oracle.fingerprint_weights(page)
+    assert len(words) == int(g["words_count"]) and (words & 1).all() and (positions & 1).all()
+    assert np.array_equal(words[:16], g["words_head"]) and np.array_equal(positions[:16], g["positions_head"])
+    assert words.sum() == g["words_sum"] and positions.sum() == g["positions_sum"]
+    for dim in (16, 64, 512):
+        stored = _fingerprint_pattern(3 * page, dim)
+        every = np.ones(3 * page, bool)
+        assert np.array_equal(oracle.page_fingerprints(stored, every, words, positions), g[f"d{dim}_all"])
+        parts = [oracle.page_fingerprints(stored, np.arange(3 * page) % 3 == rank, words, positions) for rank in range(3)]
+        for rank in range(3):
+            assert np.array_equal(parts[rank], g[f"d{dim}_rank{rank}"])
+        assert np.array_equal(oracle.exact_group_sum(parts), g[f"d{dim}_all"])  # the group's sum is the whole page's
+    changed = _fingerprint_pattern(3 * page, 64)
+    changed[page + 5, 3] ^= 1  # one bit of one key: that page's fingerprint alone moves
+    moved = oracle.page_fingerprints(changed, np.ones(3 * page, bool), words, positions) != g["d64_all"]
+    assert moved.tolist() == [False, True, False]

@@ -40,6 +40,17 @@ def test_settings_block_is_parsed_and_unknown_keys_are_refused():
     assert settings.parse({}).indexer.top_p == 1024  # the reference's defaults
     early = settings.parse({"indexer": {"early_budget": {"position": 4096, "top_k": 512, "top_p": 64}}})
     assert early.early_width == 512 + 512 + 4
+    shaped = settings.parse({"indexer": {"bucket_shape": {"rank": 2, "deviations": 1.5}}})
+    assert shaped.indexer.bucket_shape.rank == 2 and shaped.indexer.flat_design().bucket_shape.deviations == 1.5
+    assert settings.parse({"indexer": {"bucket_shape": {}}}).indexer.bucket_shape.deviations == 2.0  # (the defaults)
+    for refused, why in (({"bucket_shape": {"rank": 9}}, "at most 8 directions"),
+                         ({"bucket_shape": {"rank": 2, "deviations": 0}}, "deviations must be positive"),
+                         ({"bucket_shape": {"spread": 1}}, "rank and deviations"),
+                         ({"bucket_shape": 2}, "a mapping of rank and deviations"),
+                         ({"bucket_shape": {"rank": 2}, "index_dim": 48}, "multiple of 32"),
+                         ({"node_bucket_shape": {"rank": 1}}, "top_level 0")):
+        with pytest.raises(ValueError, match=why):
+            settings.parse({"indexer": refused})
     for bad in ({"indexer": {"windows": 3}}, {"serving": {"kernels": "triton"}}, {"extra": 1},
                 {"indexer": {"bucket_cap": 8}}, {"indexer": {"window_size": 500}}, {"indexer": {"top_level": 1}},
                 {"serving": {"decode": "descend"}}, {"indexer": {"top_p": 4096}},
