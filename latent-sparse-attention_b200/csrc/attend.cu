@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(W * 32, 1) sparse_attend_kernel(AttendParams p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int64_t item = (int64_t)blockIdx.x * W + warp;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   if (item >= p.R * p.splits * p.Hkv) return;
   const int h = (int)(item % p.Hkv);
   const int64_t rs = item / p.Hkv;
@@ -299,6 +301,8 @@ __global__ void lse_merge_kernel(const float *__restrict__ parts, const float *_
                                  float *__restrict__ lse_out) {
   const int lane = lane_id();
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  dependents_may_launch();
+  wait_for_earlier_grids();
   if (row >= rows) return;
   float m = -INFINITY;
   for (int i = 0; i < n_parts; ++i) m = fmaxf(m, lses[(int64_t)i * rows + row]);
@@ -334,6 +338,8 @@ __global__ void __launch_bounds__(128)
   __shared__ float red_s[4];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row = blockIdx.x;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   float m = -INFINITY;
   for (int i = tid; i < n_parts; i += 128) m = fmaxf(m, lses[(int64_t)i * rows + row]);
 #pragma unroll
@@ -389,7 +395,7 @@ static int launch_attend(const AttendParams &p, cudaStream_t s) {
   const int64_t items = p.R * p.splits * p.Hkv;
   const int64_t grid = (items + W - 1) / W;
   if (grid > INT32_MAX) return LSA_ERR_ARGUMENT;
-  sparse_attend_kernel<DH, NT, W, STAGES><<<(unsigned)grid, W * 32, smem, s>>>(p);
+  launch(p.R <= kChainedRows, sparse_attend_kernel<DH, NT, W, STAGES>, dim3((unsigned)grid), dim3(W * 32), smem, s, p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -406,6 +412,8 @@ __global__ void __launch_bounds__(128)
   __shared__ float4 sum_s[4][32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunks = dh / 128;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   const int64_t row = blockIdx.x / chunks;
   const int col = (int)(blockIdx.x % chunks) * 128 + lane * 4;
   float m = -INFINITY;
@@ -466,6 +474,8 @@ __global__ void __launch_bounds__(256)
                          uint16_t *__restrict__ out_bf16, float *__restrict__ out_f32, float *__restrict__ lse_out) {
   const int lane = lane_id();
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  dependents_may_launch();
+  wait_for_earlier_grids();
   if (row >= rows) return;
   const float mine = lane < n_parts ? lses[(int64_t)lane * rows + row] : -INFINITY;
   float m = mine;
@@ -524,16 +534,18 @@ LSA_API int lsa_lse_merge(const void *parts, int parts_dtype, const float *lses,
   LSA_REQUIRE(n_parts >= 1 && rows >= 0 && dh >= 1, LSA_ERR_ARGUMENT);
   LSA_REQUIRE(parts_dtype == LSA_DTYPE_F32 || parts_dtype == LSA_DTYPE_BF16, LSA_ERR_ARGUMENT);
   if (rows == 0) return LSA_OK;
+  // (rows here are (row, head) pairs: a decode step's few query rows of up to 128 heads)
+  const bool chained = rows <= lsa::kChainedRows * 128;
   const bool aligned = dh % 8 == 0 && ((uintptr_t)parts % 16) == 0 && (!out_f32 || ((uintptr_t)out_f32 % 16) == 0) &&
                        (!out_bf16 || ((uintptr_t)out_bf16 % 16) == 0);
   if (n_parts < 16 && aligned && (parts_dtype == LSA_DTYPE_BF16 || rows >= 1024)) {
     const unsigned grid = (unsigned)((rows + 7) / 8);
     if (parts_dtype == LSA_DTYPE_BF16)
-      lsa::lse_merge_few_kernel<uint16_t><<<grid, 256, 0, (cudaStream_t)stream>>>(
-          (const uint16_t *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+      lsa::launch(chained, lsa::lse_merge_few_kernel<uint16_t>, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
+                  (const uint16_t *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     else
-      lsa::lse_merge_few_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(
-          (const float *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+      lsa::launch(chained, lsa::lse_merge_few_kernel<float>, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
+                  (const float *)parts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
@@ -541,20 +553,20 @@ LSA_API int lsa_lse_merge(const void *parts, int parts_dtype, const float *lses,
   const float *fparts = (const float *)parts;
   if (n_parts >= 16 && n_parts <= 1024 && dh % 128 == 0 && ((uintptr_t)parts % 16) == 0 &&
       (!out_f32 || ((uintptr_t)out_f32 % 16) == 0) && (!out_bf16 || ((uintptr_t)out_bf16 % 8) == 0)) {
-    lsa::lse_merge_split_kernel<<<(unsigned)(rows * (dh / 128)), 128, 0, (cudaStream_t)stream>>>(
-        fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+    lsa::launch(chained, lsa::lse_merge_split_kernel, dim3((unsigned)(rows * (dh / 128))), dim3(128), 0,
+                (cudaStream_t)stream, fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   if ((n_parts >= 16 || dh >= 256) && dh <= 128 * lsa::kMergeWideDims) {
-    lsa::lse_merge_wide_kernel<<<(unsigned)rows, 128, 0, (cudaStream_t)stream>>>(fparts, lses, n_parts, rows, dh,
-                                                                                  out_bf16, out_f32, lse_out);
+    lsa::launch(chained, lsa::lse_merge_wide_kernel, dim3((unsigned)rows), dim3(128), 0, (cudaStream_t)stream, fparts,
+                lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   const int warps = 8;
-  lsa::lse_merge_kernel<<<(unsigned)((rows + warps - 1) / warps), warps * 32, 0, (cudaStream_t)stream>>>(
-      fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
+  lsa::launch(chained, lsa::lse_merge_kernel, dim3((unsigned)((rows + warps - 1) / warps)), dim3(warps * 32), 0,
+              (cudaStream_t)stream, fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }

@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "lsa_b200.h"
 
@@ -76,6 +77,44 @@ __device__ __forceinline__ int warp_sum_int(int x) {
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// ---- chained launches of a decode step
+// A decode step is a chain of small kernels, each waiting for the one before. Launched as programmatic dependents
+// (the attribute below), a kernel's CTAs are placed on the SMs while the kernel before it is still running, do what
+// does not depend on it, and wait at `wait_for_earlier_grids()`; the gap between two launches goes. Every kernel that
+// may be launched this way calls the wait on every path before it touches memory an earlier kernel wrote (the wait
+// ends when the earlier grids have completed and their writes are visible; in a kernel launched the plain way both
+// calls do nothing).
+__device__ __forceinline__ void dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void wait_for_earlier_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+constexpr int64_t kChainedRows = 8;  // calls of at most this many rows are a decode step's: their launches are chained
+
+// Off unless LSA_CHAINED_LAUNCH=1 (read once): a step replayed from a CUDA graph, whose launches are already a
+// microsecond apart, measured slower with its whole chain resident and waiting (153 against 130 us for the MLA flat
+// step, 84 against 78 for the tree step); only a step launched eagerly from the host gained (196 against 203 us).
+inline bool chained_launches() {
+  static const bool on = [] {
+    const char *set = getenv("LSA_CHAINED_LAUNCH");
+    return set && set[0] == '1';
+  }();
+  return on;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...), as a programmatic dependent of the stream's last kernel when
+// `chained`. The error, if any, is left for LSA_LAUNCH_CHECK.
+template <typename... Params, typename... Args>
+inline void launch(bool chained, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                   Args &&...args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid, config.blockDim = block, config.dynamicSmemBytes = smem, config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = chained && chained_launches() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
 
 inline int sm_count() {
   int dev = 0, n = 148;

@@ -61,6 +61,8 @@ __device__ __forceinline__ int append_run(const ExpandParams &p, const int32_t *
 __global__ void __launch_bounds__(kExpandWarps * 32) expand_kernel(ExpandParams p) {
   const int lane = lane_id();
   const int64_t r = (int64_t)blockIdx.x * kExpandWarps + (threadIdx.x >> 5);
+  dependents_may_launch();
+  wait_for_earlier_grids();
   if (r >= p.R) return;
   const int64_t pos = p.positions[r];
   const int64_t request = p.row_request ? p.row_request[r] : 0;
@@ -150,6 +152,8 @@ __global__ void __launch_bounds__(kWideThreads) expand_wide_kernel(ExpandParams 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kWarps = kWideThreads / 32;
   const int64_t r = blockIdx.x;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   const int64_t pos = p.positions[r];
   const int64_t request = p.row_request ? p.row_request[r] : 0;
   const int32_t *table = p.page_table ? p.page_table + request * p.page_table_stride : nullptr;
@@ -264,6 +268,8 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
   constexpr int kWarps = kClusterThreads / 32;
   const int cta = (int)cluster.block_rank();
   const int64_t r = blockIdx.y;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   const int64_t pos = p.positions[r];
   const int64_t request = p.row_request ? p.row_request[r] : 0;
   const int32_t *table = p.page_table ? p.page_table + request * p.page_table_stride : nullptr;
@@ -454,19 +460,21 @@ LSA_API int lsa_expand_batched(const int32_t *picked, int64_t R, int top_p, cons
   if (R <= 8 && keeps_all && top_p <= lsa::kWideMaxPicks && (int64_t)top_p * bucket_cap >= 32768) {
     // a few rows with very long lists: a cluster of CTAs a row
     const dim3 grid(lsa::kClusterCtas, (unsigned)R);
-    lsa::expand_cluster_kernel<<<grid, lsa::kClusterThreads, 0, (cudaStream_t)stream>>>(p);
+    lsa::launch(true, lsa::expand_cluster_kernel, grid, dim3(lsa::kClusterThreads), 0, (cudaStream_t)stream, p);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   if (keeps_all && top_p <= lsa::kWideMaxPicks &&
       (int64_t)top_p * bucket_cap + window >= (R <= 8 ? 1024 : (R <= 64 ? 4096 : INT64_MAX))) {
     // a decode step's long lists: one CTA a row
-    lsa::expand_wide_kernel<<<(unsigned)R, lsa::kWideThreads, 0, (cudaStream_t)stream>>>(p);
+    lsa::launch(R <= lsa::kChainedRows, lsa::expand_wide_kernel, dim3((unsigned)R), dim3(lsa::kWideThreads), 0,
+                (cudaStream_t)stream, p);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   const unsigned grid = (unsigned)((R + lsa::kExpandWarps - 1) / lsa::kExpandWarps);
-  lsa::expand_kernel<<<grid, lsa::kExpandWarps * 32, 0, (cudaStream_t)stream>>>(p);
+  lsa::launch(R <= lsa::kChainedRows, lsa::expand_kernel, dim3(grid), dim3(lsa::kExpandWarps * 32), 0,
+              (cudaStream_t)stream, p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }

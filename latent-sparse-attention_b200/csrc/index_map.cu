@@ -232,6 +232,7 @@ static int launch_index_map(const void *x, int64_t rows, int heads, int group, i
 // for all rows; eight columns a CTA, so even a single row's map spreads over N / 8 CTAs instead of one.
 constexpr int kLinThreads = 256;
 constexpr int kLinMaxRows = 8;
+constexpr int kLinHeld = 8;  // 16-byte runs of a column's weights a lane takes before it waits for the kernel before
 
 __global__ void __launch_bounds__(kLinThreads)
     rows_linear_kernel(const uint16_t *__restrict__ x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride,
@@ -240,6 +241,17 @@ __global__ void __launch_bounds__(kLinThreads)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint16_t *xs = reinterpret_cast<uint16_t *>(smem_raw);  // [rows][K] bf16
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  dependents_may_launch();
+  // The weights of this warp's column do not depend on the kernel before: up to 2,048 of them are taken first, while
+  // that kernel may still be running.
+  const int n = blockIdx.x * (kLinThreads / 32) + warp;
+  uint4 held[kLinHeld];
+#pragma unroll
+  for (int i = 0; i < kLinHeld; ++i) {
+    const int k = lane * 8 + i * 256;
+    held[i] = n < N && k < K ? *reinterpret_cast<const uint4 *>(Wt + (int64_t)n * K + k) : make_uint4(0, 0, 0, 0);
+  }
+  wait_for_earlier_grids();
   // the head sum: a thread a pair of dims, 32 heads' loads in flight at a time, added in head order
   const bool pairs = (K % 2 == 0) && (x_row_stride % 2 == 0) && (x_head_stride % 2 == 0) && ((uintptr_t)x % 4 == 0);
   if (pairs) {
@@ -275,15 +287,13 @@ __global__ void __launch_bounds__(kLinThreads)
     }
   }
   __syncthreads();
-  const int n = blockIdx.x * (kLinThreads / 32) + warp;
   if (n >= N) return;
   float acc[kLinMaxRows];
 #pragma unroll
   for (int r = 0; r < kLinMaxRows; ++r) acc[r] = 0.0f;
   const uint16_t *w = Wt + (int64_t)n * K;
-#pragma unroll 4
-  for (int k = lane * 8; k < K; k += 32 * 8) {  // (K is a multiple of 8 and the rows are 16-byte aligned)
-    const uint4 wv = *reinterpret_cast<const uint4 *>(w + k);
+  // (K is a multiple of 8 and the rows are 16-byte aligned; a lane walks its weights in ascending order either way)
+  auto fold = [&](const uint4 wv, int k) {
     const uint32_t wp[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
     for (int r = 0; r < kLinMaxRows; ++r) {
@@ -296,7 +306,14 @@ __global__ void __launch_bounds__(kLinThreads)
         acc[r] = fmaf(__uint_as_float(xp[i] & 0xFFFF0000u), __uint_as_float(wp[i] & 0xFFFF0000u), acc[r]);
       }
     }
+  };
+#pragma unroll
+  for (int i = 0; i < kLinHeld; ++i) {
+    const int k = lane * 8 + i * 256;
+    if (k < K) fold(held[i], k);
   }
+#pragma unroll 4
+  for (int k = lane * 8 + kLinHeld * 256; k < K; k += 32 * 8) fold(*reinterpret_cast<const uint4 *>(w + k), k);
 #pragma unroll
   for (int r = 0; r < kLinMaxRows; ++r) {
     if (r >= rows) break;
@@ -311,6 +328,8 @@ __global__ void __launch_bounds__(kLinThreads)
 
 // rows /= their length (fp32 in place, a warp a row), with an optional bf16 copy
 __global__ void rows_unit_kernel(float *__restrict__ rows, int n_rows, int d, uint16_t *__restrict__ out_bf16) {
+  dependents_may_launch();
+  wait_for_earlier_grids();
   const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (r >= n_rows) return;
   float ss = 0.0f;
@@ -342,12 +361,13 @@ LSA_API int lsa_rows_linear(const uint16_t *x, int rows, int heads, int64_t x_ro
     return LSA_ERR_LAUNCH;
   const unsigned grid = (unsigned)((d_out + lsa::kLinThreads / 32 - 1) / (lsa::kLinThreads / 32));
   const bool unit = flags & LSA_ROWS_NORMALIZE;
-  lsa::rows_linear_kernel<<<grid, lsa::kLinThreads, smem, (cudaStream_t)stream>>>(
-      x, rows, heads, x_row_stride, x_head_stride, d_in, Wt, d_out, flags & LSA_ROWS_GELU ? 1 : 0, out_f32,
-      unit ? nullptr : out_bf16);
+  lsa::launch(true, lsa::rows_linear_kernel, dim3(grid), dim3(lsa::kLinThreads), smem, (cudaStream_t)stream, x, rows,
+              heads, x_row_stride, x_head_stride, d_in, Wt, d_out, flags & LSA_ROWS_GELU ? 1 : 0, out_f32,
+              unit ? nullptr : out_bf16);
   LSA_LAUNCH_CHECK();
   if (unit) {
-    lsa::rows_unit_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(out_f32, rows, d_out, out_bf16);
+    lsa::launch(true, lsa::rows_unit_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, (cudaStream_t)stream,
+                out_f32, rows, d_out, out_bf16);
     LSA_LAUNCH_CHECK();
   }
   return LSA_OK;

@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(kLtThreads, 1)
   const int64_t r = blockIdx.x / p.splits;
   const int head0 = blockIdx.y * kLatHeads;
   const bool partial = p.splits > 1;
+  dependents_may_launch();
+  wait_for_earlier_grids();
 
   int64_t n_total = p.lengths ? p.lengths[r] : p.list_stride;
   if (n_total > p.list_stride) n_total = p.list_stride;
@@ -560,7 +562,7 @@ int launch_latent_attend_tc(const LatentParams &p_in, cudaStream_t stream) {
       cudaSuccess)
     return LSA_ERR_LAUNCH;
   const dim3 grid((unsigned)(p.R * p.splits), (unsigned)((p.Hq + kLatHeads - 1) / kLatHeads));
-  latent_attend_tc_kernel<<<grid, kLtThreads, kLtSmem, stream>>>(map_latent, p);
+  launch(p.R <= kChainedRows, latent_attend_tc_kernel, grid, dim3(kLtThreads), kLtSmem, stream, map_latent, p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }

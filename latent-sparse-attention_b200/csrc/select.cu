@@ -247,6 +247,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t row0 = (int64_t)blockIdx.x * RB;
   const int splits = gridDim.y, split = blockIdx.y;
+  dependents_may_launch();
+  wait_for_earlier_grids();
 
   for (int e = tid; e < RB * p.d; e += kSelThreads) {
     const int64_t r = row0 + e / p.d;
@@ -423,6 +425,8 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
   int *hist = reinterpret_cast<int *>(buf + room);        // [256]
   const int lane = lane_id();
   const int64_t r = blockIdx.x;
+  dependents_may_launch();
+  wait_for_earlier_grids();
   int n = 0;
   if (blockDim.x == kSelThreads) {
     // many candidates (a row split over dozens of CTAs): the whole CTA cuts them to `keep`, warp 0 sorts and writes
@@ -501,14 +505,14 @@ static int launch_select(SelectParams p, int splits, cudaStream_t s) {
     if (cudaFuncSetAttribute(select_kernel<RB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return LSA_ERR_LAUNCH;
-    select_kernel<RB, true><<<grid, kSelThreads, smem, s>>>(p);
+    launch(p.R <= kChainedRows, select_kernel<RB, true>, grid, dim3(kSelThreads), smem, s, p);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
   }
   if (cudaFuncSetAttribute(select_kernel<RB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  select_kernel<RB, false><<<grid, kSelThreads, smem, s>>>(p);
+  launch(p.R <= kChainedRows, select_kernel<RB, false>, grid, dim3(kSelThreads), smem, s, p);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -1235,9 +1239,9 @@ LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, i
   if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  lsa::merge_candidates_kernel<<<(unsigned)R, lsa::merge_threads(parts, top_p), smem, (cudaStream_t)stream>>>(keys_in, parts, R, top_p, room,
-                                                                                keys_out, picked_out, nullptr, 0,
-                                                                                nullptr);
+  lsa::launch(R <= lsa::kChainedRows, lsa::merge_candidates_kernel, dim3((unsigned)R),
+              dim3(lsa::merge_threads(parts, top_p)), smem, (cudaStream_t)stream, keys_in, parts, R, top_p, room,
+              keys_out, picked_out, nullptr, 0, nullptr);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
@@ -1443,8 +1447,9 @@ LSA_API int lsa_beam_step_split(const float *queries, int64_t R, int d, const fl
   if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return LSA_ERR_LAUNCH;
-  lsa::merge_candidates_kernel<<<(unsigned)R, lsa::merge_threads(splits, keep), smem, (cudaStream_t)stream>>>(
-      (const int64_t *)workspace, splits, R, keep, room, keys_out, kept_out, children, fanout, carried_out);
+  lsa::launch(R <= lsa::kChainedRows, lsa::merge_candidates_kernel, dim3((unsigned)R),
+              dim3(lsa::merge_threads(splits, keep)), smem, (cudaStream_t)stream, (const int64_t *)workspace, splits, R,
+              keep, room, keys_out, kept_out, children, fanout, carried_out);
   LSA_LAUNCH_CHECK();
   return LSA_OK;
 }
