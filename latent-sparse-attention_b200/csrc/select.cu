@@ -212,6 +212,86 @@ __device__ void warp_sort_descending(int64_t *buf, int n) {
   }
 }
 
+// ---------------------------------------------------------------------------------------- top 128 in registers
+
+// A decode row's candidates are a thousand or two: cutting them by radix passes costs a dozen barriers and shared
+// histograms a pass. Here a warp holds 128 keys in registers, four a lane (key e at register e / 32 of lane e % 32),
+// sorts them with a bitonic network whose exchanges are shuffles or register moves - no barrier at all - and the
+// warps' lists are folded pairwise: the greater of A[e] and B[127 - e] is the best 128 of both as a bitonic run,
+// which seven more stages sort. Keys are distinct (an id in the low word), so the result is the exact top 128.
+constexpr int kTopLane = 4;
+constexpr int kTopWarp = kTopLane * 32;
+
+// One stage of the network over a warp's 128 keys: exchanges `stride` apart, descending where (e & span) == 0.
+__device__ __forceinline__ void warp_exchange(int64_t (&k)[kTopLane], int lane, int span, int stride) {
+  if (stride == 64) {  // registers 0-2 and 1-3 of a lane (span is 128 here: descending throughout)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t a = k[j], b = k[j + 2];
+      k[j] = a < b ? b : a, k[j + 2] = a < b ? a : b;
+    }
+  } else if (stride == 32) {  // registers 0-1 and 2-3
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) {
+      const bool descending = ((j * 32) & span) == 0;
+      const int64_t a = k[j], b = k[j + 1];
+      const bool swap = (a < b) == descending;
+      k[j] = swap ? b : a, k[j + 1] = swap ? a : b;
+    }
+  } else {  // another lane's same register
+    const bool lower = (lane & stride) == 0;
+#pragma unroll
+    for (int j = 0; j < kTopLane; ++j) {
+      const bool descending = ((j * 32 + lane) & span) == 0;
+      const int64_t mine = k[j], other = __shfl_xor_sync(0xffffffffu, mine, stride);
+      const bool greater = lower == descending;  // the lower place of a descending run keeps the greater key
+      k[j] = (mine < other) == greater ? other : mine;
+    }
+  }
+}
+
+__device__ __forceinline__ void warp_sort128(int64_t (&k)[kTopLane], int lane) {
+  for (int span = 2; span <= kTopWarp; span <<= 1)
+    for (int stride = span >> 1; stride > 0; stride >>= 1) warp_exchange(k, lane, span, stride);
+}
+
+// A bitonic run of 128 sorted descending.
+__device__ __forceinline__ void warp_merge128(int64_t (&k)[kTopLane], int lane) {
+  for (int stride = kTopWarp >> 1; stride > 0; stride >>= 1) warp_exchange(k, lane, kTopWarp, stride);
+}
+
+// The best 128 of this warp's sorted keys and another sorted list `t` of the same warp, left sorted in k.
+__device__ __forceinline__ void warp_fold128(int64_t (&k)[kTopLane], const int64_t (&t)[kTopLane], int lane) {
+#pragma unroll
+  for (int j = 0; j < kTopLane; ++j) {
+    const int64_t other = __shfl_sync(0xffffffffu, t[kTopLane - 1 - j], 31 - lane);  // t[127 - e]
+    k[j] = k[j] < other ? other : k[j];
+  }
+  warp_merge128(k, lane);
+}
+
+// The best 128 of what the first `warps` warps of a CTA hold (128 sorted keys each; `warps` a power of two), left
+// sorted in warp 0's registers. Every thread of the CTA calls this; `slots` is shared memory for warps / 2 lists that
+// nobody reads or writes otherwise from the first barrier here on.
+__device__ void block_top128(int64_t (&k)[kTopLane], int64_t *slots, int warps, int warp, int lane) {
+  for (int half = warps >> 1; half >= 1; half >>= 1) {
+    __syncthreads();
+    if (warp >= half && warp < 2 * half) {
+#pragma unroll
+      for (int j = 0; j < kTopLane; ++j) slots[(warp - half) * kTopWarp + j * 32 + lane] = k[j];
+    }
+    __syncthreads();
+    if (warp < half) {
+#pragma unroll
+      for (int j = 0; j < kTopLane; ++j) {
+        const int64_t other = slots[warp * kTopWarp + kTopWarp - 1 - (j * 32 + lane)];
+        k[j] = k[j] < other ? other : k[j];
+      }
+      warp_merge128(k, lane);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------- the kernel
 
 struct SelectParams {
@@ -284,6 +364,11 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   // (a single row: every thread of the CTA carries the row's state, which stays the same in all of them)
   const int my_keep_all = (RB == 1 && row0 < p.R) ? (p.row_keep ? min(p.row_keep[row0], p.keep) : p.keep) : 0;
   __shared__ int block_counter, block_pick[3];
+  // A single row whose share of the candidates is one chunk of at most 1,024, cut to at most 128: sorted in registers.
+  const bool in_registers = RB == 1 && cand_end - cand_begin <= kSelWarps * kTopWarp && cand_end > cand_begin &&
+                            cand_end - cand_begin <= p.chunk && p.keep <= kTopWarp &&
+                            p.chunk >= kSelWarps / 2 * kTopWarp;  // (the chunk's room holds the lists being folded)
+  bool sorted = false;
 
   for (int chunk_base = cand_begin; chunk_base < cand_end; chunk_base += p.chunk) {
     const int chunk_n = min(p.chunk, cand_end - chunk_base);
@@ -357,6 +442,30 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
         bufs[(size_t)i * row_room + keep_room + t] = ids[i] >= 0 ? pack_key(acc[i], ids[i] + p.id_base) : kEmptyKey;
     }
     __syncthreads();
+    if (RB == 1 && in_registers) {
+      // ---- select: every warp sorts 128 of the chunk's keys, the warps' lists are folded into warp 0's
+      int64_t *chunk = bufs + keep_room;
+      int64_t k[kTopLane];
+#pragma unroll
+      for (int j = 0; j < kTopLane; ++j) {
+        const int at = warp * kTopWarp + j * 32 + lane;
+        k[j] = at < chunk_n ? chunk[at] : kEmptyKey;
+      }
+      warp_sort128(k, lane);
+      block_top128(k, chunk, kSelWarps, warp, lane);
+      if (warp == 0) {
+        int valid = 0;
+#pragma unroll
+        for (int j = 0; j < kTopLane; ++j) {
+          bufs[j * 32 + lane] = k[j];
+          valid += k[j] != kEmptyKey;
+        }
+        held = min(warp_sum_int(valid), my_keep_all);
+        __syncwarp();
+      }
+      sorted = true;
+      continue;
+    }
     // ---- select: a row that has the CTA to itself is folded by all of its threads (the keys are distinct and the
     // final sort orders them, so the order they are kept in does not matter)
     if (RB == 1 && row_room <= kBlockCompactPerThread * kSelThreads) {
@@ -394,7 +503,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
 
   if (warp < RB && my_row < p.R) {
     int64_t *buf = bufs + (size_t)warp * row_room;
-    warp_sort_descending(buf, held);
+    if (!sorted) warp_sort_descending(buf, held);
     const int64_t out_row = ((int64_t)split * p.R + my_row) * p.keep;
     for (int i = lane; i < p.keep; i += 32) {
       const int64_t key = i < held ? buf[i] : kEmptyKey;
@@ -428,7 +537,39 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
   dependents_may_launch();
   wait_for_earlier_grids();
   int n = 0;
-  if (blockDim.x == kSelThreads) {
+  bool sorted = false;
+  if (keep <= kTopWarp && parts * keep > 256) {
+    // lists of at most 128 keys (a decode row split over CTAs, the ranks' candidates): a warp takes a list into its
+    // registers, sorts it (the lists need not arrive sorted), folds in the lists a stride of warps further on, and
+    // the warps' results are folded into warp 0's
+    const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    int64_t k[kTopLane];
+    auto take = [&](int64_t (&into)[kTopLane], int part) {
+#pragma unroll
+      for (int j = 0; j < kTopLane; ++j) {
+        const int e = j * 32 + lane;
+        into[j] = part < parts && e < keep ? keys_in[((int64_t)part * R + r) * keep + e] : kEmptyKey;
+      }
+      warp_sort128(into, lane);
+    };
+    take(k, warp);
+    for (int part = warp + warps; part < parts; part += warps) {  // (the same trips for every lane of a warp)
+      int64_t t[kTopLane];
+      take(t, part);
+      warp_fold128(k, t, lane);
+    }
+    block_top128(k, buf, warps, warp, lane);
+    if (warp > 0) return;
+#pragma unroll
+    for (int j = 0; j < kTopLane; ++j) {
+      buf[j * 32 + lane] = k[j];
+      n += k[j] != kEmptyKey;
+    }
+    n = warp_sum_int(n);
+    if (n > keep) n = keep;
+    __syncwarp();
+    sorted = true;
+  } else if (blockDim.x == kSelThreads) {
     // many candidates (a row split over dozens of CTAs): the whole CTA cuts them to `keep`, warp 0 sorts and writes
     __shared__ int counter, pick[3];
     const int total = parts * keep;
@@ -457,7 +598,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
       n = warp_compact(buf, 0, n, 0, [kth](int64_t key) { return key_radix(key) >= kth; });
     }
   }
-  warp_sort_descending(buf, n);
+  if (!sorted) warp_sort_descending(buf, n);
   for (int i = lane; i < keep; i += 32) {
     const int64_t key = i < n ? buf[i] : kEmptyKey;
     if (keys_out) keys_out[r * keep + i] = key;
@@ -475,6 +616,11 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
 // Threads of a candidate merge: a warp for a few hundred candidates, the whole CTA for what its registers can hold.
 static int merge_threads(int parts, int keep) {
   const int64_t total = (int64_t)parts * keep;
+  if (keep <= kTopWarp && total > 256) {  // a warp a list (or several), a power of two of warps
+    int warps = 1;
+    while (warps < kSelWarps && warps < parts) warps <<= 1;
+    return warps * 32;
+  }
   return total > 256 && total <= kBlockCompactPerThread * kSelThreads ? kSelThreads : 32;
 }
 
