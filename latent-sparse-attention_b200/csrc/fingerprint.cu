@@ -6,7 +6,8 @@
 // that wraps instead of rounding - exact whatever order it is added in, so the lanes, warps and ranks may add in any.
 // A slot another rank owns adds nothing, and a group's sum of its ranks' fingerprints is the whole page's.
 //
-// Byte work bound by HBM: a page is read once, a warp a row with the lanes side by side over its words.
+// Byte work bound by HBM: a page is read once, a warp a row with the lanes side by side over its words, a page's rows
+// dealt over as many CTAs as fill the SMs.
 #include "common.cuh"
 
 namespace lsa {
@@ -22,24 +23,25 @@ __global__ void __launch_bounds__(kPrintThreads)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t page = blockIdx.x;
   uint64_t total = 0;
-  for (int r = warp; r < page_rows; r += kPrintThreads / 32) {
+  // (a page's rows are dealt over the CTAs of its grid row: a wrapping sum does not mind who adds what)
+  for (int r = blockIdx.y * (kPrintThreads / 32) + warp; r < page_rows; r += gridDim.y * (kPrintThreads / 32)) {
     const int64_t at = page * page_rows + r;
     if (owned && !owned[at]) continue;
     const int64_t row = slots ? slots[at] : at;
     if (row < 0 || (slots && row >= slot_count)) continue;
     const uint64_t *words = stored + row * row_stride_words;
-    uint64_t sum = 0;
+    uint64_t sum = 0;  // (this lane's words of the row; the lanes' shares meet once, at the end)
     for (int w = lane; w < row_words; w += 32) sum += __ldg(words + w) * __ldg(word_weights + w);
-#pragma unroll
-    for (int offset = 16; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
     total += sum * __ldg(position_weights + r);
   }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) total += __shfl_xor_sync(0xffffffffu, total, offset);
   if (lane == 0) warp_sums[warp] = total;
   __syncthreads();
   if (threadIdx.x == 0) {
     uint64_t sum = 0;
     for (int w = 0; w < kPrintThreads / 32; ++w) sum += warp_sums[w];
-    out[page] = (int64_t)sum;
+    atomicAdd(reinterpret_cast<unsigned long long *>(out + page), (unsigned long long)sum);
   }
 }
 
@@ -55,7 +57,12 @@ LSA_API int lsa_page_fingerprints(const void *stored, int64_t row_stride_bytes, 
               LSA_ERR_ARGUMENT);
   if (pages == 0) return LSA_OK;
   LSA_REQUIRE(pages <= 0x7fffffff, LSA_ERR_UNSUPPORTED);
-  lsa::page_fingerprints_kernel<<<(unsigned)pages, lsa::kPrintThreads, 0, (cudaStream_t)stream>>>(
+  // enough CTAs to fill the SMs a few times over, whatever the count of pages: each adds its share into the page's sum
+  int shares = (int)((4 * (int64_t)lsa::sm_count() + pages - 1) / pages);
+  const int most = (page_rows + lsa::kPrintThreads / 32 - 1) / (lsa::kPrintThreads / 32);
+  shares = shares < 1 ? 1 : (shares > most ? most : shares);
+  if (cudaMemsetAsync(out, 0, (size_t)pages * sizeof(int64_t), (cudaStream_t)stream) != cudaSuccess) return LSA_ERR_LAUNCH;
+  lsa::page_fingerprints_kernel<<<dim3((unsigned)pages, (unsigned)shares), lsa::kPrintThreads, 0, (cudaStream_t)stream>>>(
       (const uint64_t *)stored, slots, slot_count, page_rows, row_bytes / 8, row_stride_bytes / 8, owned,
       (const uint64_t *)word_weights, (const uint64_t *)position_weights, out);
   LSA_LAUNCH_CHECK();

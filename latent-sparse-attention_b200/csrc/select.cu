@@ -10,6 +10,19 @@
 
 namespace lsa {
 
+#ifdef LSA_SELECT_TRACE
+// Clock stamps of thread 0 of one CTA of a decode row's scan (row 0) and of its merge (row 1), for a build that asks.
+__device__ long long lsa_select_trace[2][16];
+#define LSA_STAMP(row, at)                                                         \
+  do {                                                                             \
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) lsa_select_trace[row][at] = clock64(); \
+  } while (0)
+#else
+#define LSA_STAMP(row, at) \
+  do {                     \
+  } while (0)
+#endif
+
 constexpr int kSelThreads = 256;
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kHistBins = 256;
@@ -294,6 +307,44 @@ __device__ void block_top128(int64_t (&k)[kTopLane], int64_t *slots, int warps, 
 
 // ---------------------------------------------------------------------------------------- the kernel
 
+// Dims whose vectors a single-row scan stages through shared memory: 8 or 16 columns of 16 bytes.
+__host__ __device__ inline bool select_stages(int d) { return d == 32 || d == 64; }
+
+// A tile of up to kSelThreads candidate vectors of NV 16-byte columns through shared memory, and this thread's own
+// candidate's score out of it (every thread of the CTA calls this). The loads of a thread are all issued before any
+// of them is stored: 16 of them wait together, not one after another.
+template <int NV>
+__device__ __forceinline__ float tile_score(const float *__restrict__ vectors, const int64_t *rowof_s, float4 *tile_s,
+                                            const float *qs, int tile_n, int tid, bool scores) {
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int e = tid + i * kSelThreads, cand = e / NV, c4 = e % NV;
+    const int64_t row = cand < tile_n ? rowof_s[cand] : -1;
+    v[i] = row >= 0 ? __ldg(reinterpret_cast<const float4 *>(vectors + row * (NV * 4)) + c4)
+                    : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int e = tid + i * kSelThreads, cand = e / NV, c4 = e % NV;
+    tile_s[cand * NV + (c4 ^ (cand & (NV - 1)))] = v[i];
+  }
+  __syncthreads();
+  float acc = 0.0f;
+  if (scores) {
+#pragma unroll
+    for (int k4 = 0; k4 < NV; ++k4) {
+      const float4 w = tile_s[tid * NV + (k4 ^ (tid & (NV - 1)))];
+      const float4 q = *reinterpret_cast<const float4 *>(qs + k4 * 4);
+      acc = fmaf(q.x, w.x, acc);
+      acc = fmaf(q.y, w.y, acc);
+      acc = fmaf(q.z, w.z, acc);
+      acc = fmaf(q.w, w.w, acc);
+    }
+  }
+  return acc;
+}
+
 struct SelectParams {
   const float *queries;         // [R, d]
   const float *vectors;         // [N, d]
@@ -322,6 +373,10 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   int64_t *bufs = reinterpret_cast<int64_t *>(smem_raw);               // [RB][row_room]
   float *qs = reinterpret_cast<float *>(bufs + (size_t)RB * row_room);  // [RB][d]
   int *hists = reinterpret_cast<int *>(qs + RB * p.d);                  // [RB][256]
+  // (a single row of 32 or 64 dims: a tile of candidate vectors staged for the scoring, and the rows they came from)
+  float4 *tile_s = reinterpret_cast<float4 *>(hists + RB * kHistBins);  // [kSelThreads][d / 4], columns swizzled
+  int64_t *rowof_s = reinterpret_cast<int64_t *>(tile_s + kSelThreads * (p.d >> 2));  // [kSelThreads]
+  const bool staged = RB == 1 && select_stages(p.d);  // (d = 64: 16 columns, d = 32: 8)
   __shared__ int total_s[RB], first_s[RB], end_s[RB];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -329,6 +384,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
   const int splits = gridDim.y, split = blockIdx.y;
   dependents_may_launch();
   wait_for_earlier_grids();
+  LSA_STAMP(0, 0);
 
   for (int e = tid; e < RB * p.d; e += kSelThreads) {
     const int64_t r = row0 + e / p.d;
@@ -348,6 +404,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
     total_s[tid] = r < p.R ? p.n_carried + (end - first) : 0;
   }
   __syncthreads();
+  LSA_STAMP(0, 1);
   int max_total = 0;
 #pragma unroll
   for (int i = 0; i < RB; ++i) max_total = max(max_total, total_s[i]);
@@ -372,8 +429,39 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
 
   for (int chunk_base = cand_begin; chunk_base < cand_end; chunk_base += p.chunk) {
     const int chunk_n = min(p.chunk, cand_end - chunk_base);
+    // ---- score, a single row: a tile of candidates at a time. A thread a candidate reading its own vector straight
+    // from memory makes every load instruction of a warp touch 32 lines (a vector is 128 or 256 bytes): the loads of
+    // a 1,024-candidate share then cost more than everything else the CTA does. Here the tile's vectors come in with
+    // every half warp on one vector's 256 contiguous bytes, land in shared memory with their 16-byte columns
+    // swizzled by the candidate, and each thread reads its own back without a bank conflict, in the same order.
+    for (int t0 = 0; staged && t0 < chunk_n; t0 += kSelThreads) {
+      const int t = t0 + tid, c = chunk_base + t;
+      int32_t id = -1;
+      int64_t vec_row = -1;
+      if (t < chunk_n && row0 < p.R && c < total_s[0]) {
+        id = c < p.n_carried ? p.carried[row0 * p.n_carried + c] : first_s[0] + (c - p.n_carried);
+        vec_row = id >= 0 ? (p.vector_base ? p.vector_base[row0] : 0) + id : -1;
+        if (p.pages && id >= 0) {
+          const int page = id / p.page_rows < p.max_pages ? p.pages[row0 * p.max_pages + id / p.page_rows] : -1;
+          vec_row = page >= 0 ? (int64_t)page * p.page_rows + id % p.page_rows : -1;
+          if (page < 0) id = -1;
+        }
+        if (vec_row >= p.N) vec_row = -1, id = -1;
+      }
+      rowof_s[tid] = vec_row;
+      __syncthreads();
+      const int tile_n = min(kSelThreads, chunk_n - t0);
+      float acc = p.d == 64 ? tile_score<16>(p.vectors, rowof_s, tile_s, qs, tile_n, tid, vec_row >= 0)
+                            : tile_score<8>(p.vectors, rowof_s, tile_s, qs, tile_n, tid, vec_row >= 0);
+      if (t < chunk_n) {
+        if constexpr (SHAPED) {
+          if (vec_row >= 0) acc = shaped_score(acc, qs, p.d, p.shape, vec_row);
+        }
+        bufs[keep_room + t] = id >= 0 ? pack_key(acc, id + p.id_base) : kEmptyKey;
+      }
+    }
     // ---- score: a thread a candidate, every row of the CTA against it
-    for (int t = tid; t < chunk_n; t += kSelThreads) {
+    for (int t = tid; !staged && t < chunk_n; t += kSelThreads) {
       const int c = chunk_base + t;
       float acc[RB];
       int64_t vec_row[RB];
@@ -441,7 +529,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
       for (int i = 0; i < RB; ++i)
         bufs[(size_t)i * row_room + keep_room + t] = ids[i] >= 0 ? pack_key(acc[i], ids[i] + p.id_base) : kEmptyKey;
     }
+    LSA_STAMP(0, 2);
     __syncthreads();
+    LSA_STAMP(0, 3);
     if (RB == 1 && in_registers) {
       // ---- select: every warp sorts 128 of the chunk's keys, the warps' lists are folded into warp 0's
       int64_t *chunk = bufs + keep_room;
@@ -452,7 +542,9 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
         k[j] = at < chunk_n ? chunk[at] : kEmptyKey;
       }
       warp_sort128(k, lane);
+      LSA_STAMP(0, 4);
       block_top128(k, chunk, kSelWarps, warp, lane);
+      LSA_STAMP(0, 5);
       if (warp == 0) {
         int valid = 0;
 #pragma unroll
@@ -520,6 +612,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectParams p) {
       }
     }
   }
+  LSA_STAMP(0, 6);
 }
 
 // Global top-k of `parts` lists of packed keys, a warp a row.
@@ -528,7 +621,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
                                                               int64_t *__restrict__ keys_out,
                                                               int32_t *__restrict__ ids_out,
                                                               const int64_t *__restrict__ children, int fanout,
-                                                              int32_t *__restrict__ carried_out) {
+                                                              int32_t *__restrict__ carried_out, int lists_sorted) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   int64_t *buf = reinterpret_cast<int64_t *>(smem_raw);  // [room]
   int *hist = reinterpret_cast<int *>(buf + room);        // [256]
@@ -536,12 +629,13 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
   const int64_t r = blockIdx.x;
   dependents_may_launch();
   wait_for_earlier_grids();
+  LSA_STAMP(1, 0);
   int n = 0;
   bool sorted = false;
   if (keep <= kTopWarp && parts * keep > 256) {
     // lists of at most 128 keys (a decode row split over CTAs, the ranks' candidates): a warp takes a list into its
-    // registers, sorts it (the lists need not arrive sorted), folds in the lists a stride of warps further on, and
-    // the warps' results are folded into warp 0's
+    // registers, sorts it unless the caller made it and knows it sorted (best first, empty keys last), folds in the
+    // lists a stride of warps further on, and the warps' results are folded into warp 0's
     const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     int64_t k[kTopLane];
     auto take = [&](int64_t (&into)[kTopLane], int part) {
@@ -550,15 +644,18 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
         const int e = j * 32 + lane;
         into[j] = part < parts && e < keep ? keys_in[((int64_t)part * R + r) * keep + e] : kEmptyKey;
       }
-      warp_sort128(into, lane);
+      if (!lists_sorted) warp_sort128(into, lane);
     };
     take(k, warp);
+    LSA_STAMP(1, 1);
     for (int part = warp + warps; part < parts; part += warps) {  // (the same trips for every lane of a warp)
       int64_t t[kTopLane];
       take(t, part);
       warp_fold128(k, t, lane);
     }
+    LSA_STAMP(1, 2);
     block_top128(k, buf, warps, warp, lane);
+    LSA_STAMP(1, 3);
     if (warp > 0) return;
 #pragma unroll
     for (int j = 0; j < kTopLane; ++j) {
@@ -611,6 +708,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
       carried_out[r * keep * fanout + e] = i < n ? (int32_t)children[(int64_t)key_id(buf[i]) * fanout + c] : LSA_PAD;
     }
   }
+  LSA_STAMP(1, 4);
 }
 
 // Threads of a candidate merge: a warp for a few hundred candidates, the whole CTA for what its registers can hold.
@@ -633,7 +731,8 @@ static int pow2_at_least(int n) {
 // Chunk of candidates a pass scores: as many as shared memory holds beside the held keys, at most 2048.
 static int select_chunk(int rb, int keep, int d, size_t *smem_out) {
   const size_t budget = 200 * 1024;
-  const size_t fixed = (size_t)rb * (pow2_at_least(keep) * 8 + d * 4 + kHistBins * 4);
+  const size_t tile = rb == 1 && select_stages(d) ? (size_t)kSelThreads * (d * 4 + 8) : 0;
+  const size_t fixed = (size_t)rb * (pow2_at_least(keep) * 8 + d * 4 + kHistBins * 4) + tile;
   int chunk = 2048;
   while (chunk > 256 && fixed + (size_t)rb * chunk * 8 > budget) chunk -= 256;
   if (fixed + (size_t)rb * chunk * 8 > budget) return 0;
@@ -830,6 +929,12 @@ static int launch_flat(FlatParams p, cudaStream_t s) {
 }
 
 }  // namespace lsa
+
+#ifdef LSA_SELECT_TRACE
+extern "C" __attribute__((visibility("default"))) int lsa_select_trace_read(long long *host) {
+  return (int)cudaMemcpyFromSymbol(host, lsa::lsa_select_trace, sizeof(lsa::lsa_select_trace));
+}
+#endif
 
 // ================================================================================================ C ABI
 
@@ -1374,22 +1479,31 @@ LSA_API size_t lsa_flat_select_decode_workspace_bytes(int64_t R, int top_p, int 
   return (size_t)R * top_p * splits * sizeof(int64_t);
 }
 
+namespace lsa {
+// The global top_p of `parts` lists a row; `sorted`: every list arrives best first with its empty keys last (the
+// lists this file's own scans write).
+static int merge_lists(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out, int32_t *picked_out,
+                       const int64_t *children, int fanout, int32_t *carried_out, bool sorted, cudaStream_t stream) {
+  const int room = pow2_at_least(parts * top_p);
+  const size_t smem = (size_t)room * 8 + kHistBins * 4;
+  LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
+  if (cudaFuncSetAttribute(merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
+    return LSA_ERR_LAUNCH;
+  launch(R <= kChainedRows, merge_candidates_kernel, dim3((unsigned)R), dim3(merge_threads(parts, top_p)), smem, stream,
+         keys_in, parts, R, top_p, room, keys_out, picked_out, children, fanout, carried_out, sorted ? 1 : 0);
+  LSA_LAUNCH_CHECK();
+  return LSA_OK;
+}
+}  // namespace lsa
+
 LSA_API int lsa_merge_candidates(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out,
                                  int32_t *picked_out, void *stream) {
   LSA_REQUIRE(keys_in && (keys_out || picked_out), LSA_ERR_NULL);
   LSA_REQUIRE(parts >= 1 && R >= 0 && top_p >= 1, LSA_ERR_ARGUMENT);
   if (R == 0) return LSA_OK;
-  const int room = lsa::pow2_at_least(parts * top_p);
-  const size_t smem = (size_t)room * 8 + lsa::kHistBins * 4;
-  LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
-  if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
-    return LSA_ERR_LAUNCH;
-  lsa::launch(R <= lsa::kChainedRows, lsa::merge_candidates_kernel, dim3((unsigned)R),
-              dim3(lsa::merge_threads(parts, top_p)), smem, (cudaStream_t)stream, keys_in, parts, R, top_p, room,
-              keys_out, picked_out, nullptr, 0, nullptr);
-  LSA_LAUNCH_CHECK();
-  return LSA_OK;
+  return lsa::merge_lists(keys_in, parts, R, top_p, keys_out, picked_out, nullptr, 0, nullptr, false,
+                          (cudaStream_t)stream);
 }
 
 LSA_API int lsa_flat_select_decode(const float *queries, int64_t R, int d, const float *centroids,
@@ -1421,7 +1535,8 @@ LSA_API int lsa_flat_select_decode(const float *queries, int64_t R, int d, const
   p.keys_out = (int64_t *)workspace;
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
-  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+  return lsa::merge_lists((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, nullptr, 0, nullptr, true,
+                          (cudaStream_t)stream);
 }
 
 LSA_API int lsa_shaped_select_decode(const float *queries, int64_t R, int d, const float *centroids,
@@ -1449,7 +1564,8 @@ LSA_API int lsa_shaped_select_decode(const float *queries, int64_t R, int d, con
   p.keys_out = (int64_t *)workspace;
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
-  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+  return lsa::merge_lists((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, nullptr, 0, nullptr, true,
+                          (cudaStream_t)stream);
 }
 
 LSA_API int lsa_beam_step(const float *queries, int64_t R, int d, const float *vectors, int64_t N,
@@ -1517,7 +1633,8 @@ LSA_API int lsa_flat_select_paged(const float *queries, int64_t R, int d, const 
   p.keys_out = (int64_t *)workspace;
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
-  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+  return lsa::merge_lists((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, nullptr, 0, nullptr, true,
+                          (cudaStream_t)stream);
 }
 
 LSA_API int lsa_shaped_select_paged(const float *queries, int64_t R, int d, const float *centroids, int64_t rows,
@@ -1547,7 +1664,8 @@ LSA_API int lsa_shaped_select_paged(const float *queries, int64_t R, int d, cons
   p.keys_out = (int64_t *)workspace;
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
-  return lsa_merge_candidates((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, stream);
+  return lsa::merge_lists((const int64_t *)workspace, splits, R, top_p, keys_out, picked_out, nullptr, 0, nullptr, true,
+                          (cudaStream_t)stream);
 }
 
 LSA_API size_t lsa_beam_step_workspace_bytes(int64_t R, int keep, int splits) {
@@ -1587,15 +1705,6 @@ LSA_API int lsa_beam_step_split(const float *queries, int64_t R, int d, const fl
   p.run_limit = (int)N;
   int rc = lsa::launch_select<1>(p, splits, (cudaStream_t)stream);
   if (rc != LSA_OK) return rc;
-  const int room = lsa::pow2_at_least(splits * keep);
-  const size_t smem = (size_t)room * 8 + lsa::kHistBins * 4;
-  LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
-  if (cudaFuncSetAttribute(lsa::merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
-    return LSA_ERR_LAUNCH;
-  lsa::launch(R <= lsa::kChainedRows, lsa::merge_candidates_kernel, dim3((unsigned)R),
-              dim3(lsa::merge_threads(splits, keep)), smem, (cudaStream_t)stream, (const int64_t *)workspace, splits, R,
-              keep, room, keys_out, kept_out, children, fanout, carried_out);
-  LSA_LAUNCH_CHECK();
-  return LSA_OK;
+  return lsa::merge_lists((const int64_t *)workspace, splits, R, keep, keys_out, kept_out, children, fanout, carried_out,
+                          true, (cudaStream_t)stream);
 }

@@ -170,7 +170,7 @@ class LatentLayer(FlatLayer):
         return out_host
 
     def decode(self, q: torch.Tensor, positions: torch.Tensor, latent: torch.Tensor, index: FlatIndex,
-               splits: int = 148, select_splits: int = 16, warp_mma: bool = False) -> torch.Tensor:
+               splits: int = 148, select_splits: int = 32, warp_mma: bool = False) -> torch.Tensor:
         """One step for rows [R, heads, latent_dim] at `positions`: out [R, heads, value_dim] bf16. Fixed shapes and
         no host reads once `visible` is on the device, so a step can be captured in a CUDA graph."""
         d, b = self.design, index.buckets
