@@ -75,8 +75,11 @@ __global__ void __launch_bounds__(kShapeThreads)
   }
   __syncthreads();
   // A plane whose off-diagonal entry is this small against the spread of the whole bucket is left alone: turning it
-  // would move a direction by less than fp32 holds.
+  // would move a direction by less than fp32 holds. So is a plane of two directions that both carry next to nothing
+  // (a bucket of n keys spreads along n - 1 directions at most: the rest is rounding noise that would keep the sweeps
+  // going for nothing).
   const float tiny = fmaxf(trace_s, 1e-30f) * (1e-7f / D);
+  const float nothing = fmaxf(trace_s, 1e-30f) * 1e-7f;
 
   // ---- cyclic Jacobi: a round rotates d / 2 disjoint (p, q) planes at once (the circle method's pairing)
   for (int sweep = 0; sweep < kShapeSweeps && rank > 0; ++sweep) {
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(kShapeThreads)
         }
         const float apq = a_s[p][q];
         float c = 1.0f, s = 0.0f;
-        if (fabsf(apq) > tiny) {
+        if (fabsf(apq) > tiny && fmaxf(fabsf(a_s[p][p]), fabsf(a_s[q][q])) > nothing) {
           const float theta = (a_s[q][q] - a_s[p][p]) / (2.0f * apq);
           const float t = (theta >= 0.0f ? 1.0f : -1.0f) / (fabsf(theta) + sqrtf(theta * theta + 1.0f));
           c = 1.0f / sqrtf(t * t + 1.0f);
@@ -111,6 +114,7 @@ __global__ void __launch_bounds__(kShapeThreads)
         const int i = e / (D / 2), k = e % (D / 2);
         const int p = p_s[k], q = q_s[k];
         const float c = cos_s[k], s = sin_s[k];
+        if (s == 0.0f) continue;  // (a plane left alone)
         const float aip = a_s[i][p], aiq = a_s[i][q];
         a_s[i][p] = c * aip - s * aiq;
         a_s[i][q] = s * aip + c * aiq;
@@ -124,6 +128,7 @@ __global__ void __launch_bounds__(kShapeThreads)
         const int j = e % D, k = e / D;
         const int p = p_s[k], q = q_s[k];
         const float c = cos_s[k], s = sin_s[k];
+        if (s == 0.0f) continue;
         const float apj = a_s[p][j], aqj = a_s[q][j];
         a_s[p][j] = c * apj - s * aqj;
         a_s[q][j] = s * apj + c * aqj;
