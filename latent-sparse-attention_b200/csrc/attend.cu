@@ -400,54 +400,86 @@ static int launch_attend(const AttendParams &p, cudaStream_t s) {
   return LSA_OK;
 }
 
-// Many parts of wide rows (a decode step split over every SM): a CTA owns (row, 128 dims). Its four warps take the
-// parts in turn, a lane four dims of a part (one 16-byte load, eight in flight), and the warps' sums meet in shared
+// Many parts of wide rows (a decode step split over every SM): a CTA owns (row, 128 dims). Its sixteen warps take
+// the parts in turn, a lane four dims of a part (one 16-byte load, ten in flight), and the warps' sums meet in shared
 // memory: the partials of a split read are some tens of MB that one pass at the copy bandwidth can merge.
-__global__ void __launch_bounds__(128)
+constexpr int kSplitWarps = 16;
+constexpr int kSplitThreads = kSplitWarps * 32;
+constexpr int kSplitBatch = 10;  // parts a warp asks for at once: 160 parts (a decode row split over every SM) in one go
+
+__global__ void __launch_bounds__(kSplitThreads)
     lse_merge_split_kernel(const float *__restrict__ parts, const float *__restrict__ lses, int n_parts, int64_t rows,
                            int dh, uint16_t *__restrict__ out_bf16, float *__restrict__ out_f32,
                            float *__restrict__ lse_out) {
   __shared__ float w_s[1024];
-  __shared__ float red_s[4];
-  __shared__ float4 sum_s[4][32];
+  __shared__ float max_s[kSplitWarps], sum_l_s[kSplitWarps];
+  __shared__ float4 sum_s[kSplitWarps][32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunks = dh / 128;
   dependents_may_launch();
   wait_for_earlier_grids();
   const int64_t row = blockIdx.x / chunks;
   const int col = (int)(blockIdx.x % chunks) * 128 + lane * 4;
-  float m = -INFINITY;
-  for (int i = tid; i < n_parts; i += 128) m = fmaxf(m, lses[(int64_t)i * rows + row]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (lane == 0) red_s[warp] = m;
-  __syncthreads();
-  m = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
-  __syncthreads();
-  float l = 0.0f;
-  for (int i = tid; i < n_parts; i += 128) {
-    const float e = m > -INFINITY ? expf(lses[(int64_t)i * rows + row] - m) : 0.0f;
-    w_s[i] = e;
-    l += e;
-  }
-  l = warp_sum(l);
-  if (lane == 0) red_s[warp] = l;
-  __syncthreads();
-  const float denom = red_s[0] + red_s[1] + red_s[2] + red_s[3];
-  const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
-  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   const float *src = parts + row * dh + col;
   const int64_t stride = rows * dh;
-  for (int i0 = warp; i0 < n_parts; i0 += 32) {
-    float4 v[8];
+  // A step is a chain of waits on memory, so everything that can be asked for at once is: this warp's first parts
+  // (they do not depend on the weights) and this thread's log-sum-exps, before any of them is used.
+  float4 v[kSplitBatch];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = i0 + 4 * j;
+  for (int j = 0; j < kSplitBatch; ++j) {
+    const int i = warp + kSplitWarps * j;
+    v[j] = i < n_parts ? *reinterpret_cast<const float4 *>(src + (int64_t)i * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float mine[1024 / kSplitThreads];
+#pragma unroll
+  for (int j = 0; j < 1024 / kSplitThreads; ++j) {
+    const int i = tid + j * kSplitThreads;
+    mine[j] = i < n_parts ? lses[(int64_t)i * rows + row] : -INFINITY;
+  }
+  float m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 1024 / kSplitThreads; ++j) m = fmaxf(m, mine[j]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) max_s[warp] = m;
+  __syncthreads();
+  m = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kSplitWarps; ++w) m = fmaxf(m, max_s[w]);
+  float l = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 1024 / kSplitThreads; ++j) {
+    const int i = tid + j * kSplitThreads;
+    if (i < n_parts) {
+      const float e = m > -INFINITY ? expf(mine[j] - m) : 0.0f;
+      w_s[i] = e;
+      l += e;
+    }
+  }
+  l = warp_sum(l);
+  if (lane == 0) sum_l_s[warp] = l;
+  __syncthreads();
+  float denom = 0.0f;
+#pragma unroll
+  for (int w = 0; w < kSplitWarps; ++w) denom += sum_l_s[w];
+  const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+  float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+  for (int j = 0; j < kSplitBatch; ++j) {
+    const int i = warp + kSplitWarps * j;
+    const float w = i < n_parts ? w_s[i] : 0.0f;
+    acc.x = fmaf(w, v[j].x, acc.x), acc.y = fmaf(w, v[j].y, acc.y);
+    acc.z = fmaf(w, v[j].z, acc.z), acc.w = fmaf(w, v[j].w, acc.w);
+  }
+  for (int i0 = warp + kSplitWarps * kSplitBatch; i0 < n_parts; i0 += kSplitWarps * kSplitBatch) {
+#pragma unroll
+    for (int j = 0; j < kSplitBatch; ++j) {
+      const int i = i0 + kSplitWarps * j;
       v[j] = i < n_parts ? *reinterpret_cast<const float4 *>(src + (int64_t)i * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = i0 + 4 * j;
+    for (int j = 0; j < kSplitBatch; ++j) {
+      const int i = i0 + kSplitWarps * j;
       const float w = i < n_parts ? w_s[i] : 0.0f;
       acc.x = fmaf(w, v[j].x, acc.x), acc.y = fmaf(w, v[j].y, acc.y);
       acc.z = fmaf(w, v[j].z, acc.z), acc.w = fmaf(w, v[j].w, acc.w);
@@ -456,9 +488,13 @@ __global__ void __launch_bounds__(128)
   sum_s[warp][lane] = acc;
   __syncthreads();
   if (warp == 0) {
-    float4 a = sum_s[0][lane], b = sum_s[1][lane], c = sum_s[2][lane], d = sum_s[3][lane];
-    const float x = (a.x + b.x + c.x + d.x) * inv, y = (a.y + b.y + c.y + d.y) * inv;
-    const float z = (a.z + b.z + c.z + d.z) * inv, w = (a.w + b.w + c.w + d.w) * inv;
+    float x = 0.0f, y = 0.0f, z = 0.0f, w = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kSplitWarps; ++k) {
+      const float4 a = sum_s[k][lane];
+      x += a.x, y += a.y, z += a.z, w += a.w;
+    }
+    x *= inv, y *= inv, z *= inv, w *= inv;
     if (out_f32) *reinterpret_cast<float4 *>(out_f32 + row * dh + col) = make_float4(x, y, z, w);
     if (out_bf16) *reinterpret_cast<uint2 *>(out_bf16 + row * dh + col) = make_uint2(pack_bf16x2(x, y), pack_bf16x2(z, w));
     if (lane == 0 && lse_out && blockIdx.x % chunks == 0) lse_out[row] = denom > 0.0f ? m + logf(denom) : -INFINITY;
@@ -553,7 +589,7 @@ LSA_API int lsa_lse_merge(const void *parts, int parts_dtype, const float *lses,
   const float *fparts = (const float *)parts;
   if (n_parts >= 16 && n_parts <= 1024 && dh % 128 == 0 && ((uintptr_t)parts % 16) == 0 &&
       (!out_f32 || ((uintptr_t)out_f32 % 16) == 0) && (!out_bf16 || ((uintptr_t)out_bf16 % 8) == 0)) {
-    lsa::launch(chained, lsa::lse_merge_split_kernel, dim3((unsigned)(rows * (dh / 128))), dim3(128), 0,
+    lsa::launch(chained, lsa::lse_merge_split_kernel, dim3((unsigned)(rows * (dh / 128))), dim3(lsa::kSplitThreads), 0,
                 (cudaStream_t)stream, fparts, lses, n_parts, rows, dh, out_bf16, out_f32, lse_out);
     LSA_LAUNCH_CHECK();
     return LSA_OK;
