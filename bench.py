@@ -667,6 +667,25 @@ def run_c2(args, env: Env, cfg: dict, steps: int, cpu_baseline: bool = True) -> 
         e2e_step()
     e2e_ms = env.timed(e2e_step, steps)
     base.check()
+    arms = None
+    if world > 1:
+        # the other way to part the same prefill over the ranks, timed for the record beside the one the line reports
+        other_rows = not by_rows
+        q_other = (layer.rows_of(host[0], chunk * world) if other_rows else host[0]).cuda()
+
+        def other_step():
+            if other_rows:
+                layer.prefill_by_rows(q_other, k, v, T, chunk=chunk * world, out=out_d)
+            else:
+                layer.prefill(q_other, k, v, chunk=chunk, out=out_d)
+
+        other_step()
+        other_ms = env.timed(other_step, max(1, min(steps, 2)))
+        base.check()
+        rows_ms, context_ms = (ms, other_ms) if by_rows else (other_ms, ms)
+        arms = {"rows split, cache all-gathered": {"value": T / (rows_ms * 1e-3), "ms_per_step": rows_ms},
+                "context parallel over the dealt cache": {"value": T / (context_ms * 1e-3), "ms_per_step": context_ms}}
+        del q_other
 
     result = {"metric": "LSA layer prefill tokens/s (flat, GQA, 128k tokens from position 0)", "value": T / (ms * 1e-3),
               "unit": UNIT, "n_gpus": world, "steps": steps, "ms_per_step": ms,
@@ -681,6 +700,8 @@ def run_c2(args, env: Env, cfg: dict, steps: int, cpu_baseline: bool = True) -> 
                       "d2h_bytes_per_step": out_h.numel() * world * 2},
               "gpu_launches": launches, "clocks": clocks.summary(), "parity": parity,
               "stages_ms_per_step": stage_ms}
+    if arms is not None:
+        result["arms"] = arms
     if world == 1:
         d_idx, d_in = cfg["index_dim"], Hkv * dh
         row = Hkv * dh * 2 * 2
