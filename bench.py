@@ -284,7 +284,7 @@ def _latent_scale(cfg):
 
 def run_c4(args, env: Env, cfg: dict) -> dict:
     import oracle
-    from lsa_b200 import _lib, probe
+    from lsa_b200 import _lib, ops, probe
     from lsa_b200 import workloads as W
     from lsa_b200.core import Buckets
     from lsa_b200.latent import LatentLayer
@@ -440,6 +440,31 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     probe.uninstall()
     (sharded or layer).check()
 
+    # What a kernel that does nothing but read the same rows reaches: the lists of 148 neighbouring query rows (what
+    # the attention launch has in flight at once, a row an SM), walked 64 ids at a time across the rows as the
+    # launch walks them, through the page-fingerprint kernel (a warp a 1,152-byte row, a wrapping sum of its words).
+    gather_probe = None
+    if world == 1:
+        group, tile, mid = 148, 64, chunk // 2
+        walked = int(lens_d[mid:mid + group].min()) // tile * tile
+        ids = lists_d[mid:mid + group, :walked].reshape(group, walked // tile, tile).permute(1, 0, 2).reshape(-1)
+        ids = ids.to(torch.int64)
+        probe_gen = torch.Generator(device="cuda").manual_seed(1)
+        by_word = torch.randint(-(1 << 62), 1 << 62, (dk * 2 // 8,), generator=probe_gen, device="cuda") | 1
+        by_row = torch.randint(-(1 << 62), 1 << 62, (tile,), generator=probe_gen, device="cuda") | 1
+        rows_2d = share.view(share.shape[0], -1)
+
+        def read_rows():
+            ops.page_fingerprints(rows_2d, tile, by_word, by_row, slots=ids)
+
+        read_rows()
+        probe_ms = env.timed(read_rows, 3)
+        gather_probe = {"GB/s": ids.numel() * dk * 2 / (probe_ms * 1e-3) / 1e9, "rows_read": int(ids.numel()),
+                        "ms": probe_ms,
+                        "note": "lsa_page_fingerprints over the listed rows of 148 neighbouring query rows in the "
+                                "attention launch's own order: a read-only gather of the same 1,152-byte rows"}
+        del ids
+
     # from pinned host memory: the chunk's queries and (this rank's share of) its latent rows in, the output back
     from lsa_b200.parallel import deal
 
@@ -537,7 +562,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
                      "useful_tflops": attend["flops"] / world / (attend_ms * 1e-3) / 1e12 if attend_ms else None,
                      "tensor_frac": attend["flops"] / world / (attend_ms * 1e-3) / 1e12 / pk["tensor_tflops"]
                      if attend_ms else None,
-                     "ms_per_launch": attend_ms,
+                     "ms_per_launch": attend_ms, "gather_probe": gather_probe,
                      "note": "algorithmic bytes = every listed latent row once per query row (1,152 bytes) + Q in + "
                              "O out, per GPU; achieved = those bytes over the launch's CUDA-event time"},
         "stagewise": table,
