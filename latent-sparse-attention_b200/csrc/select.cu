@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
   LSA_STAMP(1, 0);
   int n = 0;
   bool sorted = false;
-  if (keep <= kTopWarp && parts * keep > 256) {
+  if (keep <= kTopWarp && parts > 1) {
     // lists of at most 128 keys (a decode row split over CTAs, the ranks' candidates): a warp takes a list into its
     // registers, sorts it unless the caller made it and knows it sorted (best first, empty keys last), folds in the
     // lists a stride of warps further on, and the warps' results are folded into warp 0's
@@ -714,7 +714,7 @@ __global__ void __launch_bounds__(kSelThreads) merge_candidates_kernel(const int
 // Threads of a candidate merge: a warp for a few hundred candidates, the whole CTA for what its registers can hold.
 static int merge_threads(int parts, int keep) {
   const int64_t total = (int64_t)parts * keep;
-  if (keep <= kTopWarp && total > 256) {  // a warp a list (or several), a power of two of warps
+  if (keep <= kTopWarp && parts > 1) {  // a warp a list (or several), a power of two of warps
     int warps = 1;
     while (warps < kSelWarps && warps < parts) warps <<= 1;
     return warps * 32;
@@ -1484,7 +1484,8 @@ namespace lsa {
 // lists this file's own scans write).
 static int merge_lists(const int64_t *keys_in, int parts, int64_t R, int top_p, int64_t *keys_out, int32_t *picked_out,
                        const int64_t *children, int fanout, int32_t *carried_out, bool sorted, cudaStream_t stream) {
-  const int room = pow2_at_least(parts * top_p);
+  // (the lists folded in registers pass through kSelWarps / 2 slots of 128 keys, whatever they hold themselves)
+  const int room = max(pow2_at_least(parts * top_p), kSelWarps / 2 * kTopWarp);
   const size_t smem = (size_t)room * 8 + kHistBins * 4;
   LSA_REQUIRE(smem <= 200 * 1024, LSA_ERR_UNSUPPORTED);
   if (cudaFuncSetAttribute(merge_candidates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
