@@ -232,7 +232,7 @@ static int launch_index_map(const void *x, int64_t rows, int heads, int group, i
 // for all rows; eight columns a CTA, so even a single row's map spreads over N / 8 CTAs instead of one.
 constexpr int kLinThreads = 256;
 constexpr int kLinMaxRows = 8;
-constexpr int kLinHeld = 8;  // 16-byte runs of a column's weights a lane takes before it waits for the kernel before
+constexpr int kLinHeld = 20;  // 16-byte runs of a column's weights a lane takes before anything else (5,120 weights a column)
 
 __global__ void __launch_bounds__(kLinThreads)
     rows_linear_kernel(const uint16_t *__restrict__ x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride,
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kLinThreads)
   uint16_t *xs = reinterpret_cast<uint16_t *>(smem_raw);  // [rows][K] bf16
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   dependents_may_launch();
-  // The weights of this warp's column do not depend on the kernel before: up to 2,048 of them are taken first, while
+  // The weights of this warp's column do not depend on the kernel before: up to 5,120 of them are taken first, while
   // that kernel may still be running.
   const int n = blockIdx.x * (kLinThreads / 32) + warp;
   uint4 held[kLinHeld];
@@ -254,7 +254,23 @@ __global__ void __launch_bounds__(kLinThreads)
   wait_for_earlier_grids();
   // the head sum: a thread a pair of dims, 32 heads' loads in flight at a time, added in head order
   const bool pairs = (K % 2 == 0) && (x_row_stride % 2 == 0) && (x_head_stride % 2 == 0) && ((uintptr_t)x % 4 == 0);
-  if (pairs) {
+  if (heads == 1 && x_row_stride % 8 == 0 && ((uintptr_t)x % 16) == 0) {
+    // nothing to sum: the rows are copied 16 bytes a thread, four loads in flight (K is a multiple of 8)
+    const int per_row = K / 8, total = rows * per_row;
+    for (int e0 = tid; e0 < total; e0 += 4 * kLinThreads) {
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * kLinThreads, r = e / per_row, c = e - r * per_row;
+        if (e < total) v[j] = *reinterpret_cast<const uint4 *>(x + (int64_t)r * x_row_stride + c * 8);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * kLinThreads;
+        if (e < total) reinterpret_cast<uint4 *>(xs)[e] = v[j];
+      }
+    }
+  } else if (pairs) {
     for (int e = tid; e < rows * (K / 2); e += kLinThreads) {
       const int r = e / (K / 2), k = 2 * (e - r * (K / 2));
       const uint16_t *src = x + (int64_t)r * x_row_stride + k;
