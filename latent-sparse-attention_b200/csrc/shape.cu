@@ -2,10 +2,12 @@
 // estimated best key (src/lsa/core/shape.py:36-137; the served builders: src/lsa/core/kernels/triton/shape.py:720-886).
 //
 // A shape is built exactly: a CTA a bucket sums the [d, d] covariance of its keys about the centroid in shared
-// memory (members in stored order), diagonalises it with cyclic Jacobi rotations (d / 2 disjoint rotations a round,
-// d - 1 rounds a sweep) and keeps the `rank` leading directions as sign bits with their variances; the rest of the
-// trace is the floor. A bucket's few keys spread nearly alike along several directions, where a power iteration
-// stops short; the rotations find every direction to fp32 rounding whatever the gaps.
+// memory (members in stored order) - or, for a bucket of at most 32 keys and fewer than d, the [n, n] Gram matrix of
+// the residuals, which carries the same variances and is the smaller matrix (the reference's route for buckets,
+// src/lsa/core/kernels/triton/shape.py:849-886) - diagonalises it with cyclic Jacobi rotations and keeps the `rank`
+// leading directions as sign bits with their variances; the rest of the trace is the floor. A bucket's few keys
+// spread nearly alike along several directions, where a power iteration stops short; the rotations find every
+// direction to fp32 rounding whatever the gaps.
 #include "common.cuh"
 #include "shape.cuh"
 
@@ -13,7 +15,78 @@ namespace lsa {
 
 constexpr int kShapeThreads = 128;
 constexpr int kShapeSweeps = 16;
-constexpr int kShapeBatch = 8;  // members staged a round of the covariance sum
+constexpr int kShapeBatch = 8;   // members staged a round of the covariance sum
+constexpr int kShapeGram = 32;   // a bucket of at most this many keys goes through its Gram matrix
+
+// Cyclic Jacobi on a symmetric M x M matrix A (row pitch `ld`), M even: a round rotates M / 2 disjoint (p, q) planes
+// at once (the circle method's pairing), M - 1 rounds a sweep, until a sweep turns nothing. V (same pitch, the
+// identity on entry) collects the rotations: column k = direction k, A's diagonal its variance. Every thread of the
+// CTA calls this.
+__device__ void jacobi_sweeps(float *A, float *V, int M, int ld, float trace, float *cos_s, float *sin_s, int *p_s,
+                              int *q_s, int *moved_s) {
+  const int tid = threadIdx.x, half = M >> 1;
+  // A plane whose off-diagonal entry is this small against the spread of the whole bucket is left alone: turning it
+  // would move a direction by less than fp32 holds. So is a plane of two directions that both carry next to nothing
+  // (n keys spread along n - 1 directions at most: the rest is rounding noise that would keep the sweeps going).
+  const float tiny = fmaxf(trace, 1e-30f) * (1e-7f / M);
+  const float nothing = fmaxf(trace, 1e-30f) * 1e-7f;
+  for (int sweep = 0; sweep < kShapeSweeps; ++sweep) {
+    if (tid == 0) *moved_s = 0;
+    __syncthreads();
+    for (int round = 0; round < M - 1; ++round) {
+      if (tid < half) {
+        int p, q;
+        if (tid == 0) {
+          p = M - 1, q = round;
+        } else {
+          p = (round + tid) % (M - 1), q = (round - tid + (M - 1)) % (M - 1);
+        }
+        if (p > q) {
+          const int t = p;
+          p = q, q = t;
+        }
+        const float apq = A[p * ld + q], app = A[p * ld + p], aqq = A[q * ld + q];
+        float c = 1.0f, s = 0.0f;
+        if (fabsf(apq) > tiny && fmaxf(fabsf(app), fabsf(aqq)) > nothing) {
+          const float theta = (aqq - app) / (2.0f * apq);
+          const float t = (theta >= 0.0f ? 1.0f : -1.0f) / (fabsf(theta) + sqrtf(theta * theta + 1.0f));
+          c = 1.0f / sqrtf(t * t + 1.0f);
+          s = t * c;
+          *moved_s = 1;
+        }
+        p_s[tid] = p, q_s[tid] = q, cos_s[tid] = c, sin_s[tid] = s;
+      }
+      __syncthreads();
+      // columns: A <- A J, V <- V J
+      for (int e = tid; e < M * half; e += kShapeThreads) {
+        const int i = e / half, k = e - i * half;
+        const float c = cos_s[k], s = sin_s[k];
+        if (s == 0.0f) continue;  // (a plane left alone)
+        const int p = p_s[k], q = q_s[k];
+        const float aip = A[i * ld + p], aiq = A[i * ld + q];
+        A[i * ld + p] = c * aip - s * aiq;
+        A[i * ld + q] = s * aip + c * aiq;
+        const float vip = V[i * ld + p], viq = V[i * ld + q];
+        V[i * ld + p] = c * vip - s * viq;
+        V[i * ld + q] = s * vip + c * viq;
+      }
+      __syncthreads();
+      // rows: A <- J^T A
+      for (int e = tid; e < M * half; e += kShapeThreads) {
+        const int k = e / M, j = e - k * M;
+        const float c = cos_s[k], s = sin_s[k];
+        if (s == 0.0f) continue;
+        const int p = p_s[k], q = q_s[k];
+        const float apj = A[p * ld + j], aqj = A[q * ld + j];
+        A[p * ld + j] = c * apj - s * aqj;
+        A[q * ld + j] = s * apj + c * aqj;
+      }
+      __syncthreads();
+    }
+    if (!*moved_s) break;  // (read after the round's last barrier, by every thread alike)
+    __syncthreads();
+  }
+}
 
 template <int D>
 __global__ void __launch_bounds__(kShapeThreads)
@@ -21,24 +94,23 @@ __global__ void __launch_bounds__(kShapeThreads)
                        const float *__restrict__ centroids, const int32_t *__restrict__ members, int64_t m, int cap,
                        int rank, uint8_t *__restrict__ basis_out, float *__restrict__ variances_out,
                        float *__restrict__ floors_out) {
-  __shared__ float a_s[D][D + 1];  // the covariance, then its rotated form
-  __shared__ float v_s[D][D + 1];  // the rotations applied so far: column k = direction k
+  constexpr int LD = D + 1;
+  constexpr int kSmall = kShapeGram * (kShapeGram + 1);  // a Gram matrix, and as much again for its rotations
+  __shared__ float mat_s[D * LD > 2 * kSmall ? D * LD : 2 * kSmall];  // the matrix that is diagonalised
+  __shared__ float vec_s[D * LD];  // the rotations of the covariance, or the residuals a Gram matrix is made of
   __shared__ float res_s[kShapeBatch][D];
   __shared__ float cos_s[D / 2], sin_s[D / 2];
   __shared__ int p_s[D / 2], q_s[D / 2];
   __shared__ float centre_s[D];
   __shared__ float diag_s[D];
   __shared__ int order_s[D];
+  __shared__ int32_t held_s[kShapeGram];
   __shared__ int size_s, moved_s;
   __shared__ float trace_s;
 
   const int tid = threadIdx.x;
   const int64_t bucket = blockIdx.x;
   if (bucket >= m) return;
-  for (int e = tid; e < D * D; e += kShapeThreads) {
-    a_s[e / D][e % D] = 0.0f;
-    v_s[e / D][e % D] = e / D == e % D ? 1.0f : 0.0f;
-  }
   if (tid < D) centre_s[tid] = centroids[bucket * D + tid];
   int mine = 0;
   for (int s = tid; s < cap; s += kShapeThreads) mine += members[bucket * cap + s] >= 0;
@@ -46,123 +118,116 @@ __global__ void __launch_bounds__(kShapeThreads)
   __syncthreads();
   if (mine) atomicAdd(&size_s, mine);
   __syncthreads();
+  const int n = size_s;
+  // Fewer keys than dims: the [n, n] Gram matrix of the residuals has the covariance's nonzero variances (times n)
+  // and is the smaller matrix to diagonalise; its direction w gives the covariance's as R^T w.
+  const bool gram = n <= kShapeGram && n < D;
+  const int M = gram ? max(2, (n + 1) & ~1) : D;
+  const int ld = gram ? M + 1 : LD;
+  float *A = mat_s, *V = gram ? mat_s + kSmall : vec_s;
 
-  // ---- covariance: residuals of a few members at a time, every thread adds them into its own entries in slot order
-  for (int s0 = 0; s0 < cap; s0 += kShapeBatch) {
-    for (int e = tid; e < kShapeBatch * D; e += kShapeThreads) {
-      const int s = s0 + e / D;
-      const int64_t id = s < cap ? members[bucket * cap + s] : -1;
-      const int64_t at = id - key_base;
-      res_s[e / D][e % D] = id >= 0 && at >= 0 && at < key_rows ? index_keys[at * D + e % D] - centre_s[e % D] : 0.0f;
+  if (gram) {
+    // ---- the held members in stored order (a bucket's row may hold padding anywhere), their residuals, the Gram matrix
+    if (tid == 0) {
+      int at = 0;
+      for (int s = 0; s < cap && at < n; ++s) {
+        const int32_t id = members[bucket * cap + s];
+        if (id >= 0) held_s[at++] = id;
+      }
     }
     __syncthreads();
+    for (int e = tid; e < M * D; e += kShapeThreads) {
+      const int s = e / D, i = e - s * D;
+      float r = 0.0f;
+      if (s < n) {
+        const int64_t at = (int64_t)held_s[s] - key_base;
+        if (at >= 0 && at < key_rows) r = index_keys[at * D + i] - centre_s[i];
+      }
+      vec_s[s * LD + i] = r;
+    }
+    __syncthreads();
+    for (int e = tid; e < M * M; e += kShapeThreads) {
+      const int a = e / M, b = e - a * M;
+      float acc = 0.0f;
+#pragma unroll 8
+      for (int i = 0; i < D; ++i) acc = fmaf(vec_s[a * LD + i], vec_s[b * LD + i], acc);
+      A[a * ld + b] = acc;
+      V[a * ld + b] = a == b ? 1.0f : 0.0f;
+    }
+  } else {
     for (int e = tid; e < D * D; e += kShapeThreads) {
-      const int i = e / D, j = e % D;
-      float acc = a_s[i][j];
-#pragma unroll
-      for (int b = 0; b < kShapeBatch; ++b) acc = fmaf(res_s[b][i], res_s[b][j], acc);
-      a_s[i][j] = acc;
+      A[(e / D) * LD + e % D] = 0.0f;
+      V[(e / D) * LD + e % D] = e / D == e % D ? 1.0f : 0.0f;
     }
     __syncthreads();
+    // ---- covariance: residuals of a few members at a time, every thread adds them into its own entries in slot order
+    for (int s0 = 0; s0 < cap; s0 += kShapeBatch) {
+      for (int e = tid; e < kShapeBatch * D; e += kShapeThreads) {
+        const int s = s0 + e / D;
+        const int64_t id = s < cap ? members[bucket * cap + s] : -1;
+        const int64_t at = id - key_base;
+        res_s[e / D][e % D] = id >= 0 && at >= 0 && at < key_rows ? index_keys[at * D + e % D] - centre_s[e % D] : 0.0f;
+      }
+      __syncthreads();
+      for (int e = tid; e < D * D; e += kShapeThreads) {
+        const int i = e / D, j = e % D;
+        float acc = A[i * LD + j];
+#pragma unroll
+        for (int b = 0; b < kShapeBatch; ++b) acc = fmaf(res_s[b][i], res_s[b][j], acc);
+        A[i * LD + j] = acc;
+      }
+      __syncthreads();
+    }
   }
-  const float inv_size = 1.0f / (float)max(size_s, 1);
-  for (int e = tid; e < D * D; e += kShapeThreads) a_s[e / D][e % D] *= inv_size;
   __syncthreads();
+  // (both matrices are sums over the keys: the variances come out times n, and are divided at the end)
   if (tid == 0) {
     float trace = 0.0f;
-    for (int i = 0; i < D; ++i) trace += a_s[i][i];
+    for (int i = 0; i < M; ++i) trace += A[i * ld + i];
     trace_s = trace;
   }
   __syncthreads();
-  // A plane whose off-diagonal entry is this small against the spread of the whole bucket is left alone: turning it
-  // would move a direction by less than fp32 holds. So is a plane of two directions that both carry next to nothing
-  // (a bucket of n keys spreads along n - 1 directions at most: the rest is rounding noise that would keep the sweeps
-  // going for nothing).
-  const float tiny = fmaxf(trace_s, 1e-30f) * (1e-7f / D);
-  const float nothing = fmaxf(trace_s, 1e-30f) * 1e-7f;
-
-  // ---- cyclic Jacobi: a round rotates d / 2 disjoint (p, q) planes at once (the circle method's pairing)
-  for (int sweep = 0; sweep < kShapeSweeps && rank > 0; ++sweep) {
-    if (tid == 0) moved_s = 0;
-    __syncthreads();
-    for (int round = 0; round < D - 1; ++round) {
-      if (tid < D / 2) {
-        int p, q;
-        if (tid == 0) {
-          p = D - 1, q = round;
-        } else {
-          p = (round + tid) % (D - 1), q = (round - tid + (D - 1)) % (D - 1);
-        }
-        if (p > q) {
-          const int t = p;
-          p = q, q = t;
-        }
-        const float apq = a_s[p][q];
-        float c = 1.0f, s = 0.0f;
-        if (fabsf(apq) > tiny && fmaxf(fabsf(a_s[p][p]), fabsf(a_s[q][q])) > nothing) {
-          const float theta = (a_s[q][q] - a_s[p][p]) / (2.0f * apq);
-          const float t = (theta >= 0.0f ? 1.0f : -1.0f) / (fabsf(theta) + sqrtf(theta * theta + 1.0f));
-          c = 1.0f / sqrtf(t * t + 1.0f);
-          s = t * c;
-          moved_s = 1;
-        }
-        p_s[tid] = p, q_s[tid] = q, cos_s[tid] = c, sin_s[tid] = s;
-      }
-      __syncthreads();
-      // columns: A <- A J, V <- V J
-      for (int e = tid; e < D * (D / 2); e += kShapeThreads) {
-        const int i = e / (D / 2), k = e % (D / 2);
-        const int p = p_s[k], q = q_s[k];
-        const float c = cos_s[k], s = sin_s[k];
-        if (s == 0.0f) continue;  // (a plane left alone)
-        const float aip = a_s[i][p], aiq = a_s[i][q];
-        a_s[i][p] = c * aip - s * aiq;
-        a_s[i][q] = s * aip + c * aiq;
-        const float vip = v_s[i][p], viq = v_s[i][q];
-        v_s[i][p] = c * vip - s * viq;
-        v_s[i][q] = s * vip + c * viq;
-      }
-      __syncthreads();
-      // rows: A <- J^T A
-      for (int e = tid; e < D * (D / 2); e += kShapeThreads) {
-        const int j = e % D, k = e / D;
-        const int p = p_s[k], q = q_s[k];
-        const float c = cos_s[k], s = sin_s[k];
-        if (s == 0.0f) continue;
-        const float apj = a_s[p][j], aqj = a_s[q][j];
-        a_s[p][j] = c * apj - s * aqj;
-        a_s[q][j] = s * apj + c * aqj;
-      }
-      __syncthreads();
-    }
-    if (!moved_s) break;  // (read after the round's last barrier, by every thread alike)
-    __syncthreads();
-  }
+  if (rank > 0) jacobi_sweeps(A, V, M, ld, trace_s, cos_s, sin_s, p_s, q_s, &moved_s);
+  __syncthreads();
 
   // ---- the leading directions: variances descending, an equal pair by the lower column
-  if (tid < D) diag_s[tid] = a_s[tid][tid];
+  if (tid < M) diag_s[tid] = A[tid * ld + tid];
   __syncthreads();
-  if (tid < D) {
-    const float mine = diag_s[tid];
+  if (tid < M) {
+    const float own = diag_s[tid];
     int before = 0;
-    for (int k = 0; k < D; ++k) before += diag_s[k] > mine || (diag_s[k] == mine && k < tid);
+    for (int k = 0; k < M; ++k) before += diag_s[k] > own || (diag_s[k] == own && k < tid);
     order_s[before] = tid;
   }
   __syncthreads();
   for (int e = tid; e < rank * (D / 8); e += kShapeThreads) {
-    const int j = e / (D / 8), byte = e % (D / 8), column = order_s[j];
+    const int j = e / (D / 8), byte = e % (D / 8);
     unsigned bits = 0;
-    for (int b = 0; b < 8; ++b) bits |= (v_s[byte * 8 + b][column] > 0.0f ? 1u : 0u) << b;
+    if (j < M) {
+      const int column = order_s[j];
+      for (int b = 0; b < 8; ++b) {
+        const int i = byte * 8 + b;
+        float along;
+        if (gram) {  // the covariance's direction is R^T w (a positive multiple of it: only the signs are kept)
+          along = 0.0f;
+          for (int s = 0; s < n; ++s) along = fmaf(vec_s[s * LD + i], V[s * ld + column], along);
+        } else {
+          along = V[i * ld + column];
+        }
+        bits |= (along > 0.0f ? 1u : 0u) << b;
+      }
+    }
     basis_out[(bucket * rank + j) * (D / 8) + byte] = (uint8_t)bits;
   }
   if (tid == 0) {
+    const float over = 1.0f / (float)max(n, 1);
     float kept = 0.0f;
     for (int j = 0; j < rank; ++j) {
-      const float variance = fmaxf(diag_s[order_s[j]], 0.0f);
+      const float variance = j < M ? fmaxf(diag_s[order_s[j]], 0.0f) * over : 0.0f;
       variances_out[bucket * rank + j] = variance;
       kept += variance;
     }
-    floors_out[bucket] = fmaxf((trace_s - kept) / (float)max(D - rank, 1), 0.0f);
+    floors_out[bucket] = fmaxf((trace_s * over - kept) / (float)max(D - rank, 1), 0.0f);
   }
 }
 

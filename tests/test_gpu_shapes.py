@@ -19,6 +19,23 @@ def ops():
     return module
 
 
+@pytest.mark.parametrize("width,size,rank", [(64, 48, 2), (64, 96, 3), (32, 40, 2), (64, 33, 1), (64, 32, 4)])
+def test_buckets_of_more_keys_than_a_gram_matrix_takes_go_through_the_covariance(ops, oracle, width, size, rank):
+    # (at most 32 keys and fewer than the dims: the Gram matrix; above: the [d, d] covariance - the same shapes)
+    keys, centroids, members = anisotropic_buckets(96, size, width, size + rank)
+    want = oracle.build_shapes(keys, centroids, members, rank)
+    got = ops.shape_build(cuda(keys), cuda(centroids), cuda(members), rank)
+    np.testing.assert_allclose(got.variances.cpu().numpy(), want.variances, rtol=1e-3, atol=1e-6)
+    np.testing.assert_allclose(got.floor.cpu().numpy(), want.floor, rtol=1e-3, atol=1e-6)
+    queries = unit_rows(np.random.default_rng(2).standard_normal((64, width), dtype=np.float32))
+    built = oracle.Shapes(got.basis.cpu().numpy(), got.variances.cpu().numpy(), got.floor.cpu().numpy())
+    near = np.isclose(oracle.spread(queries, built), oracle.spread(queries, want), rtol=1e-3, atol=1e-5)
+    assert near.mean() > 0.99
+    full = (members >= 0).sum(1) >= 8
+    mine, theirs = got.basis.cpu().numpy()[full, 0], want.basis[full, 0]
+    assert ((mine == theirs).all(-1) | (mine == ~theirs).all(-1)).mean() > 0.97
+
+
 def anisotropic_buckets(count, size, width, seed):
     """Buckets of `size` unit keys spread along two directions of their own (the reference's construction), ragged."""
     rng = np.random.default_rng(seed)
