@@ -73,8 +73,9 @@ __global__ void __launch_bounds__(kTcThreads, 2) bucket_attend_tc_kernel(BucketP
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.y;
   const int seg = blockIdx.x;
-  if (seg >= p.seg_offsets[p.m]) return;
+  // (the table holds a slot for every CTA of the grid: the segment is asked for beside the count, not after it)
   const int4 info = p.segments[seg];
+  if (seg >= p.seg_offsets[p.m]) return;
   const int64_t bucket = info.x;
   const int first = info.y, n_pairs = info.z;
   const int n_rows = n_pairs * p.group;
