@@ -100,6 +100,22 @@ def _rank_main(rank, world, port, result_dir):
         # a row nobody reads has weight zero everywhere, not NaN
         weight, total = merge_weight(torch.full((3, 2), float("-inf")))
         assert not weight.any() and torch.isinf(total).all()
+        # page fingerprints of a decode group: each rank prints the slots it owns (slot s lives on rank s % world),
+        # the group adds the 16-bit pieces with a float all-reduce, and every rank holds the whole page's number
+        from lsa_b200.sglang.layer_index import exact_group_sum
+        page_rows, pages = 64, 3
+        bits = rng.integers(0, 1 << 16, (pages * page_rows, 32), dtype=np.uint16)
+        words, places = oracle.fingerprint_weights(page_rows)
+        slots = np.arange(pages * page_rows)
+        own = oracle.page_fingerprints(bits, slots % world == rank, words, places)
+
+        def group_sum(pieces):
+            dist.all_reduce(pieces)
+            return pieces
+
+        total = exact_group_sum(torch.from_numpy(own), group_sum)
+        whole_pages = oracle.page_fingerprints(bits, np.ones(len(slots), bool), words, places)
+        assert np.array_equal(total.numpy(), whole_pages), "the group's sum is not the whole page's fingerprint"
         open(os.path.join(result_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
