@@ -44,6 +44,7 @@ constexpr int kLtSmem = kLtPOff + kLtPlane + 1024;  // + room to align the base 
 constexpr int kLtTmemCols = 512;
 constexpr int kLtSCol = 256;                        // S buffers at columns 256 and 320
 constexpr int kLtChunks = 72;                       // 16-byte chunks a latent row
+constexpr int kLtOutPitch = 516;                    // floats between staged output rows: 16-byte aligned, 4 banks on
 constexpr int kLtMinRun = 16;                       // a shorter run of at least this many rows is a tile of its own
 constexpr float kLtRescale = 8.0f;                  // the running maximum is refreshed when it grows by 2^8
 
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
   const bool partial = p.splits > 1;
   dependents_may_launch();
   wait_for_earlier_grids();
+  LT_TRACE(tid == 0, 10, 0);
 
   int64_t n_total = p.lengths ? p.lengths[r] : p.list_stride;
   if (n_total > p.list_stride) n_total = p.list_stride;
@@ -183,6 +185,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
+  LT_TRACE(tid == 0, 10, 1);
 
   // A wait of one thread: false (and the abort flag) when it gives up or the CTA has already given up elsewhere.
   auto wait_one = [&](uint32_t b, uint32_t parity) {
@@ -211,6 +214,13 @@ __global__ void __launch_bounds__(kLtThreads, 1)
     // ------------------------------------------------------------------------------------------ staging the rows
     const int ptid = tid - 5 * 32;
     auto gather_sync = [] { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+    // (the first entries of the list are asked for before the queries, which they do not depend on: a decode step's
+    // CTA lives for a few tiles and cannot afford one wait on memory after another)
+    int32_t head_a = -1, head_b = -1;
+    if (warp == 5) {
+      head_a = lane < n ? list[lane] : -1;
+      head_b = 32 + lane < n ? list[32 + lane] : -1;
+    }
     // the row's query heads
     for (int e = ptid; e < kLatHeads * kLtChunks; e += 128) {
       const int qr = e / kLtChunks, c = e - qr * kLtChunks;
@@ -247,8 +257,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
         return dealt ? (int32_t)(id / deal_span * p.deal_granule + id % p.deal_granule) : id;
       };
       int x = 0, j = 0;
-      int32_t id_a = lane < n ? list[lane] : -1;
-      int32_t id_b = 32 + lane < n ? list[32 + lane] : -1;
+      int32_t id_a = head_a, id_b = head_b;
       bool alive = true;
       while ((x < n || dealt) && alive) {
         const int stage = j & 1;
@@ -488,6 +497,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
       if (last) break;
     }
     if (alive) alive = wait(pv_done, (tiles - 1) & 1);
+    LT_TRACE(tid == 0, 10, 2);
     if (alive) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
@@ -496,24 +506,35 @@ __global__ void __launch_bounds__(kLtThreads, 1)
       if (row_ok && half == 0)
         (partial ? p.part_lse : p.lse)[out_row] =
             l_run > 0.0f ? (m_used + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      // A split's partial output goes out through shared memory (the ring is free by now): a thread holds 128 bytes
+      // of ITS head's row, so stores straight from the registers touch 32 lines an instruction; staged, the warp
+      // writes its sixteen rows - one contiguous block of the partial outputs - in whole lines. (A decode step, whose
+      // CTAs live for a few tiles, spent a quarter of its time in these stores.)
+      float *o_s = reinterpret_cast<float *>(smem_raw + (base - smem_u32(smem_raw)) + kLtKOff) +
+                   (warp & 3) * (16 * kLtOutPitch);
 #pragma unroll 1
       for (int c = 0; c < 256; c += 32) {
         uint32_t o[32];
         tmem_load_32(lane_addr + c, o);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (partial) {
+          float *mine = o_s + (lane & 15) * kLtOutPitch + half * 256 + c;
+          const float by = read_any ? inv : 0.0f;
+#pragma unroll
+          for (int k = 0; k < 32; k += 4)
+            *reinterpret_cast<float4 *>(mine + k) =
+                read_any ? make_float4(__uint_as_float(o[k]) * by, __uint_as_float(o[k + 1]) * by,
+                                       __uint_as_float(o[k + 2]) * by, __uint_as_float(o[k + 3]) * by)
+                         : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          continue;
+        }
         if (!row_ok) continue;
         if (!read_any) {
 #pragma unroll
           for (int k = 0; k < 32; ++k) o[k] = 0u;
         }
         const int64_t at = out_row * 512 + half * 256 + c;
-        if (partial) {
-#pragma unroll
-          for (int k = 0; k < 32; k += 4)
-            *reinterpret_cast<float4 *>(p.part_out + at + k) =
-                make_float4(__uint_as_float(o[k]) * inv, __uint_as_float(o[k + 1]) * inv,
-                            __uint_as_float(o[k + 2]) * inv, __uint_as_float(o[k + 3]) * inv);
-        } else {
+        {
           if (p.out_f32) {
 #pragma unroll
             for (int k = 0; k < 32; k += 4)
@@ -532,6 +553,17 @@ __global__ void __launch_bounds__(kLtThreads, 1)
           }
         }
       }
+      if (partial) {
+        __syncwarp();
+        const int first_head = head0 + (warp & 3) * 16;
+        float *block = p.part_out + (out_row - (lane & 15)) * 512;  // (the warp's first row)
+        for (int i = lane; i < 16 * 128; i += 32) {
+          const int local = i >> 7, c4 = i & 127;
+          if (first_head + local < p.Hq)
+            *reinterpret_cast<float4 *>(block + (int64_t)local * 512 + c4 * 4) =
+                *reinterpret_cast<const float4 *>(o_s + local * kLtOutPitch + c4 * 4);
+        }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -541,6 +573,7 @@ __global__ void __launch_bounds__(kLtThreads, 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kLtTmemCols));
   }
   if (tid == 0 && abort_s && p.status) atomicAdd(p.status, 1);
+  LT_TRACE(tid == 0, 10, 3);
 }
 
 #ifdef LSA_LT_TRACE
