@@ -232,8 +232,10 @@ static int launch_index_map(const void *x, int64_t rows, int heads, int group, i
 // for all rows; eight columns a CTA, so even a single row's map spreads over N / 8 CTAs instead of one.
 constexpr int kLinThreads = 256;
 constexpr int kLinMaxRows = 8;
-constexpr int kLinHeld = 20;  // 16-byte runs of a column's weights a lane takes before anything else (5,120 weights a column)
+// 16-byte runs of a column's weights a lane takes before anything else: 8 (2,048 weights a column), or 20 (5,120) for
+// the widest maps - the kernel is built for both, so that a narrow map does not carry the registers of a wide one.
 
+template <int kLinHeld>
 __global__ void __launch_bounds__(kLinThreads)
     rows_linear_kernel(const uint16_t *__restrict__ x, int rows, int heads, int64_t x_row_stride, int64_t x_head_stride,
                        int K, const uint16_t *__restrict__ Wt, int N, int gelu, float *__restrict__ out_f32,
@@ -372,12 +374,12 @@ LSA_API int lsa_rows_linear(const uint16_t *x, int rows, int heads, int64_t x_ro
   const size_t smem = (size_t)rows * d_in * 2;
   LSA_REQUIRE(smem <= 160 * 1024, LSA_ERR_UNSUPPORTED);
   if (rows == 0) return LSA_OK;
-  if (cudaFuncSetAttribute(lsa::rows_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
+  auto kernel = d_in <= 2048 ? lsa::rows_linear_kernel<8> : lsa::rows_linear_kernel<20>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return LSA_ERR_LAUNCH;
   const unsigned grid = (unsigned)((d_out + lsa::kLinThreads / 32 - 1) / (lsa::kLinThreads / 32));
   const bool unit = flags & LSA_ROWS_NORMALIZE;
-  lsa::launch(true, lsa::rows_linear_kernel, dim3(grid), dim3(lsa::kLinThreads), smem, (cudaStream_t)stream, x, rows,
+  lsa::launch(true, kernel, dim3(grid), dim3(lsa::kLinThreads), smem, (cudaStream_t)stream, x, rows,
               heads, x_row_stride, x_head_stride, d_in, Wt, d_out, flags & LSA_ROWS_GELU ? 1 : 0, out_f32,
               unit ? nullptr : out_bf16);
   LSA_LAUNCH_CHECK();
