@@ -368,14 +368,31 @@ class Selector:
         rows = rows.long()
         positions = positions.to(torch.int64)
         visible = torch.minimum(positions // d.cluster_block_size * d.block_bucket_count,
-                                cache.bucket_counts[rows].long()).to(torch.int32)
+                                cache.bucket_counts[rows].long())
+        pages = cache.request_pages[rows]
+        limit = self.captured_limit()
+        if limit is not None and -(-limit // cache.page_keys) < pages.shape[1]:
+            # A graph captured for contexts up to `limit`: no request of it has a bucket past the range's pages, and
+            # a padded row of the graph may name a longer one, so its count is cut to the range (selector.py:620-627)
+            held = -(-limit // cache.page_keys)
+            pages = pages[:, :held]
+            visible = visible.clamp(max=held * cache.page_buckets)
+        visible = visible.to(torch.int32)
         with probe.region("index q scan"):
-            _, picked = self._scan_paged(index_queries, cache.request_pages[rows], visible, splits)
+            _, picked = self._scan_paged(index_queries, pages, visible, splits)
         with probe.region("expand"):
             lists, _, _ = ops.expand_batched(picked, positions, rows.to(torch.int32), cache.members,
                                              cache.request_pages, cache.page_buckets, self.slot_table(),
                                              self.kv_page_size, d.top_k, d.sink_size, d.window_size, local=local)
         return lists
+
+    @staticmethod
+    def captured_limit() -> int | None:
+        """The longest context of the decode graph being captured, when an engine captures one graph a context range
+        (`lsa_b200.sglang.context_buckets`); None otherwise."""
+        from lsa_b200.sglang import context_buckets
+
+        return context_buckets.captured_limit()
 
     def _scan_paged(self, index_queries: torch.Tensor, pages: torch.Tensor, visible: torch.Tensor, splits: int):
         """A decode step's scan through the requests' page tables: by centroid, or under `bucket_shape` by each

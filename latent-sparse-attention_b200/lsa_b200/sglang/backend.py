@@ -163,7 +163,9 @@ class GroupedQueryIndexer:
             self.index = LayerIndex(self.design, maps, pool.size + pool.page_size, pool.size, self.request_table,
                                     table.shape[1], self.prefill_chunk, table.device, self.shard,
                                     check_index=self.check_index, key_buffer=self.key_buffer,
-                                    key_slot=self.geometry.key_slot, split=split)
+                                    key_slot=self.geometry.key_slot, split=split,
+                                    prefix_reuse=self.design.serving.prefix_reuse,
+                                    spare_contexts=self.design.serving.spare_contexts)
             self.index.writes_pool = False  # `select_and_read` saves a forward's keys before it selects
         return self.index
 

@@ -284,7 +284,8 @@ class LayerIndex:
                  slot_table: Callable[[], torch.Tensor], max_context: int, prefill_chunk: int, device,
                  shard: Shard | None = None, check_index: bool = False,
                  key_buffer: Callable[[], torch.Tensor] | None = None, sum_heads=None,
-                 key_slot: KeySlot | None = None, prefix_reuse: bool = False, split=None) -> None:
+                 key_slot: KeySlot | None = None, prefix_reuse: bool = False, split=None,
+                 spare_contexts: int = 0) -> None:
         """Hold the maps and build the selector.
 
         Args:
@@ -329,6 +330,9 @@ class LayerIndex:
         request_pages = -(-max_context // PAGE_SIZE) + 1
         # (under a decode group every rank indexes each request's whole context: the cache covers `size` pools)
         pages = -(-kv_size * shard.size // PAGE_SIZE) + requests  # (a request's last page is part full)
+        # (requests that share a cached prefix hold it once in the KV pool and once each here, unless pages are shared
+        # by `prefix_reuse`: `spare_contexts` full contexts of pages on top of what the pool calls for)
+        pages += spare_contexts * (request_pages - 1)
         cache = BucketCache(design, self.index_dim, pages, page_buckets, requests, request_pages, device,
                             reuse=prefix_reuse)
         self.selector = Selector(cache, 1, slot_table)

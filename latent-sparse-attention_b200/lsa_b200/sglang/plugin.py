@@ -37,6 +37,12 @@ GROUPED_QUERY_METHODS = ("__init__", "init_forward_metadata", "init_forward_meta
 GROUPED_QUERY_TARGETS = tuple(f"{attention}.{method}" for attention in GROUPED_QUERY_BACKENDS
                               for method in GROUPED_QUERY_METHODS)
 HOOK_REGISTRY = "sglang.srt.plugins.hook_registry"
+# Where a decode runner captures its graphs, and the getter that says which attention variant is being captured: both
+# must be there for a graph a context range (plugin.py:138-143); a runner without them keeps its one decode graph
+CONTEXT_GRAPH_TARGETS = (
+    "sglang.srt.model_executor.runner.decode_cuda_graph_runner.DecodeCudaGraphRunner._capture_one_stream",
+    "sglang.srt.model_executor.runner_utils.capture_mode.get_capture_attention_variant",
+)
 
 # The design a process serves, once a model config named one
 ENABLED: dict = {}
@@ -100,7 +106,36 @@ def maintain(*args: Any, **kwargs: Any) -> None:
     backend.maintain_all(backend_object, forward_batch)
 
 
-def enable_lsa(design: DesignSettings, registry=None, targets: tuple = GROUPED_QUERY_TARGETS) -> int:
+def capture_context_graphs(original: Any, self: Any, *args: Any, **kwargs: Any) -> Any:
+    """AROUND hook of the decode runner's graph capture: hand it one graph a context range of the design, unless the
+    runner already captures variants of its own or the step is not a flat decode (plugin.py:600-631). What a graph
+    computes is the same; a range trims the page-table columns no request of it can fill."""
+    from lsa_b200.sglang import context_buckets
+
+    design = ENABLED.get("design")
+    flat_decode = design is not None and design.serving.decode == "flat" and self.capture_forward_mode.is_decode()
+    if flat_decode and getattr(self, "attention_graph_variants", None) is None:
+        longest = self.model_runner.model_config.context_len
+        ranges = context_buckets.ContextBuckets.under(design.serving.decode_context_limits, longest)
+        if ranges is not None:
+            logger.info("lsa: decode graphs for contexts up to %s and %d", ranges.limits, longest)
+            self.attention_graph_variants = ranges
+    return original(self, *args, **kwargs)
+
+
+def context_graphs(hook_registry, kinds, targets: tuple = CONTEXT_GRAPH_TARGETS) -> bool:
+    """Register the capture hook where this sglang keys decode graphs by an attention variant; elsewhere the server
+    keeps one decode graph, which serves every context (plugin.py:680-702)."""
+    missing = unresolved(targets)
+    if missing:
+        logger.info("lsa: one decode graph, no context ranges - %s", "; ".join(missing))
+        return False
+    hook_registry.register(targets[0], capture_context_graphs, kinds.AROUND)
+    return True
+
+
+def enable_lsa(design: DesignSettings, registry=None, targets: tuple = GROUPED_QUERY_TARGETS,
+               graph_targets: tuple = CONTEXT_GRAPH_TARGETS) -> int:
     """Enable the design on this process; returns the hooks registered.
 
     Raises:
@@ -123,12 +158,13 @@ def enable_lsa(design: DesignSettings, registry=None, targets: tuple = GROUPED_Q
     hooks = [(target, *by_method[target.rpartition(".")[2]]) for target in targets]
     for target, hook, kind in hooks:
         hook_registry.register(target, hook, kind)
+    ranged = bool(design.serving.decode_context_limits) and context_graphs(hook_registry, kinds, graph_targets)
     hook_registry.apply_hooks()
     ENABLED["design"] = design
     print(f"{BANNER_READY} lsa-top_level{design.indexer.top_level}-decode_{design.serving.decode} width {design.width} "
           f"map {design.serving.projections} kernels {design.serving.kernels}", flush=True)
-    logger.info("lsa: %d hooks registered", len(hooks))
-    return len(hooks)
+    logger.info("lsa: %d hooks registered", len(hooks) + ranged)
+    return len(hooks) + ranged
 
 
 def configure(result: None, self: Any, *args: Any, registry=None, **kwargs: Any) -> None:

@@ -16,6 +16,10 @@ BLOCK = "lsa"
 PAGE_SIZE = 8192  # keys a page of the bucket cache holds: where a prefill segment is cut and a tree grows
 TOPK_LIMIT = 2048
 KERNELS = ("b200",)
+# Longest contexts a decode CUDA graph is captured for, ascending: a batch replays the graph of the first limit its
+# longest request fits under, and the full-context graph beyond the last (design.py:46-52: 18 pages times a power of
+# two, so that a request at a power of two plus its answer sits high in its range)
+DECODE_CONTEXT_LIMITS = tuple(18 * PAGE_SIZE * 2 ** i for i in range(7))
 DECODES = ("flat", "descend")
 
 
@@ -115,12 +119,31 @@ class ServingChoices:
     projections: str | None = None  # the map file: `<layer>.W_Q_idx` / `<layer>.W_K_idx` tensors
     decode: str = "flat"
     kernels: str = "b200"
+    # Contexts a flat decode captures a CUDA graph for besides the server's own, ascending - empty captures one
+    decode_context_limits: tuple = DECODE_CONTEXT_LIMITS
+    # Take a cached prefix's index where the server caches prefixes, rather than build it again - opt-in
+    prefix_reuse: bool = False
+    # Full contexts the bucket cache holds beyond the KV pool's pages: requests that share a cached prefix in the pool
+    # and not in the index are not bounded by the pool's size
+    spare_contexts: int = 0
 
     def __post_init__(self) -> None:
         if self.decode not in DECODES:
             raise ValueError(f"decode must be one of {DECODES} - got {self.decode!r}")
         if self.kernels not in KERNELS:
             raise ValueError(f"kernels must be one of {KERNELS} - got {self.kernels!r}")
+        limits = tuple(self.decode_context_limits)
+        object.__setattr__(self, "decode_context_limits", limits)
+        for limit in limits:
+            if isinstance(limit, bool) or not isinstance(limit, int) or limit < PAGE_SIZE:
+                raise ValueError(f"decode_context_limits are integers of at least a page of {PAGE_SIZE} keys - got "
+                                 f"{limit!r}")
+        if list(limits) != sorted(set(limits)):
+            raise ValueError(f"decode_context_limits must be ascending and distinct - got {list(limits)}")
+        if not isinstance(self.prefix_reuse, bool):
+            raise ValueError(f"prefix_reuse is true or false - got {self.prefix_reuse!r}")
+        if isinstance(self.spare_contexts, bool) or not isinstance(self.spare_contexts, int) or self.spare_contexts < 0:
+            raise ValueError(f"spare_contexts must be a whole number - got {self.spare_contexts!r}")
 
 
 @dataclass(frozen=True)

@@ -80,3 +80,48 @@ def test_batched_decode_over_paged_buckets_and_kv(oracle):
     with pytest.raises(RuntimeError, match="out of pages"):
         for r in (6, 7):
             cache.append(r, cuda(keys[2]))
+
+
+def test_a_decode_graph_captured_for_a_context_range_reads_the_same_lists(oracle, monkeypatch):
+    # (an engine that captures one decode graph a context range says which through its capture module; the selector
+    # then reads no page past the range and cuts the counts to it - for requests inside the range, nothing changes)
+    import sys
+    import types
+
+    from lsa_b200.layer import FlatDesign
+    from lsa_b200.serving import BucketCache, Selector
+    from lsa_b200.sglang import context_buckets
+
+    design = FlatDesign(pool_size=4, bucket_size=16, bucket_cap=32, cluster_block_size=256, top_p=6, top_k=150,
+                        sink_size=4, window_size=256)
+    d_idx, page_buckets = 32, 32
+    lengths = [700, 2048, 3000]
+    rng = np.random.default_rng(1)
+    cache = BucketCache(design, d_idx, pages=16, page_buckets=page_buckets, max_requests=4, max_request_pages=8)
+    slots = rng.permutation(4 * 3072).astype(np.int32).reshape(4, 3072)
+    selector = Selector(cache, 1, slot_table=lambda: cuda(slots))
+    raws = [mixture(n, d_idx, 10, 0.3, 200 + r) for r, n in enumerate(lengths)]
+    for r, n in enumerate(lengths):
+        cache.append(r, cuda(unit_rows(raws[r])))
+    positions = np.array([n - 1 for n in lengths])
+    queries = np.stack([unit_rows(raws[r][positions[r]] + 0.3 * rng.standard_normal(d_idx).astype(np.float32))
+                        for r in range(len(lengths))])
+    rows = torch.arange(len(lengths)).cuda()
+    want = selector.decode(cuda(queries), cuda(positions), rows)
+    for r, n in enumerate(lengths):  # (and the oracle's read, as slots)
+        buckets = oracle.build_buckets(unit_rows(raws[r]), 4, 16, 32, 256)
+        lists, lens = oracle.read(queries[r:r + 1], positions[r:r + 1], buckets, 6, 150, 4, 256)
+        assert np.array_equal(want[r, : int(lens[0])].cpu().numpy(), slots[r][lists[0, : int(lens[0])]])
+    capture = types.ModuleType(context_buckets.CAPTURE_MODE)
+    label = {"now": None}
+    capture.get_capture_attention_variant = lambda: label["now"]
+    monkeypatch.setitem(sys.modules, context_buckets.CAPTURE_MODE, capture)
+    page_keys = cache.page_keys
+    assert page_keys == 512
+    for limit in (6 * page_keys, 7 * page_keys, 64 * page_keys):  # ranges that hold every request here
+        label["now"] = f"context_{limit}"
+        assert torch.equal(selector.decode(cuda(queries), cuda(positions), rows), want)
+    # a range shorter than a request cuts what that padded row may count to the range's pages; the others are as before
+    label["now"] = f"context_{4 * page_keys}"
+    cut = selector.decode(cuda(queries), cuda(positions), rows)
+    assert torch.equal(cut[:2], want[:2]) and not torch.equal(cut[2], want[2])

@@ -308,3 +308,78 @@ def test_a_read_attends_over_exactly_the_slots_a_list_names(oracle):
     got = backend.select_and_read(forward_decode, engine, cuda(q, torch.bfloat16).view(T, Hq * dh), step_k, step_v, layer,
                                   batch)
     assert len(pool.saved) == 1 and np.abs(got.float().cpu().numpy().reshape(T, Hq, dh) - want).max() <= 2e-2
+
+
+def test_decode_graphs_are_keyed_by_context_ranges(monkeypatch):
+    import sys
+
+    import torch
+
+    from lsa_b200.sglang import context_buckets
+
+    page = settings.PAGE_SIZE
+    # the knobs: ascending whole pages, and the reference's default ranges
+    defaults = settings.parse({}).serving
+    assert defaults.decode_context_limits == tuple(18 * page * 2 ** i for i in range(7))
+    assert defaults.prefix_reuse is False and defaults.spare_contexts == 0
+    chosen = settings.parse({"serving": {"decode_context_limits": [2 * page, 8 * page], "prefix_reuse": True,
+                                         "spare_contexts": 2}}).serving
+    assert chosen.decode_context_limits == (2 * page, 8 * page) and chosen.prefix_reuse and chosen.spare_contexts == 2
+    for refused in ({"decode_context_limits": [page - 1]}, {"decode_context_limits": [4 * page, 2 * page]},
+                    {"decode_context_limits": [2 * page, 2 * page]}, {"prefix_reuse": "yes"}, {"spare_contexts": -1}):
+        with pytest.raises(ValueError):
+            settings.parse({"serving": refused})
+    # the ranges narrower than the server's context; the widest graph is captured first
+    ranges = context_buckets.ContextBuckets.under(chosen.decode_context_limits + (64 * page,), 32 * page)
+    assert ranges.limits == (2 * page, 8 * page)
+    assert ranges.capture_labels == ("context_full", f"context_{8 * page}", f"context_{2 * page}")
+    assert context_buckets.ContextBuckets.under((8 * page,), 4 * page) is None
+
+    def batch(*lengths):
+        return types.SimpleNamespace(seq_lens_cpu=torch.tensor(lengths))
+
+    assert ranges.select(batch(5, 2 * page)) == f"context_{2 * page}"          # the longest request decides
+    assert ranges.select(batch(2 * page + 1, 9)) == f"context_{8 * page}"
+    assert ranges.select(batch(8 * page + 1)) == "context_full"
+    assert ranges.select(types.SimpleNamespace()) == "context_full"           # lengths not on the host
+    assert ranges.select(types.SimpleNamespace(seq_lens_cpu=torch.tensor([], dtype=torch.int64))) == "context_full"
+    assert context_buckets.pages_of(page) == 1 and context_buckets.pages_of(page + 1) == 2
+    # the label being captured, where an engine's capture module says one
+    assert context_buckets.captured_limit() is None
+    capture = types.ModuleType(context_buckets.CAPTURE_MODE)
+    label = {"now": None}
+    capture.get_capture_attention_variant = lambda: label["now"]
+    monkeypatch.setitem(sys.modules, context_buckets.CAPTURE_MODE, capture)
+    for said, limit in ((None, None), ("context_full", None), (f"context_{2 * page}", 2 * page), ("other", None)):
+        label["now"] = said
+        assert context_buckets.captured_limit() == limit
+    # the capture hook hands a decode runner the ranges once, and leaves a runner with variants of its own alone
+    design = settings.parse({"serving": {"projections": "m", "decode_context_limits": [2 * page, 8 * page]}})
+    monkeypatch.setattr(plugin, "ENABLED", {"design": design})
+    seen = []
+
+    def capture_one_stream(self, *args):
+        seen.append(self.attention_graph_variants)
+        return "captured"
+
+    def runner(variants=None, decode=True):
+        config = types.SimpleNamespace(context_len=32 * page)
+        return types.SimpleNamespace(attention_graph_variants=variants, model_runner=types.SimpleNamespace(model_config=config),
+                                     capture_forward_mode=types.SimpleNamespace(is_decode=lambda: decode))
+
+    assert plugin.capture_context_graphs(capture_one_stream, runner()) == "captured"
+    assert seen[-1].limits == (2 * page, 8 * page)
+    plugin.capture_context_graphs(capture_one_stream, runner(variants="theirs"))
+    plugin.capture_context_graphs(capture_one_stream, runner(decode=False))
+    assert seen[-2] == "theirs" and seen[-1] is None
+    # the hook is registered only where both the capture and the getter resolve
+    registry = FakeRegistry()
+    assert not plugin.context_graphs(registry, registry.HookType) and not registry.hooks
+    fake = types.ModuleType("fake_runner")
+    fake.Runner = type("Runner", (), {"_capture_one_stream": capture_one_stream})
+    fake.get_capture_attention_variant = capture.get_capture_attention_variant
+    monkeypatch.setitem(sys.modules, "fake_runner", fake)
+    targets = ("fake_runner.Runner._capture_one_stream", "fake_runner.get_capture_attention_variant")
+    assert plugin.context_graphs(registry, registry.HookType, targets)
+    assert [(t, h.__name__, k) for t, h, k in registry.hooks] == [(targets[0], "capture_context_graphs",
+                                                                   FakeRegistry.HookType.AROUND)]
