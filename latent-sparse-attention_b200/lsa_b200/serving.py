@@ -65,7 +65,9 @@ class BucketCache:
         self.holders = [0] * pages          # requests and retained prefixes that hold each page
         self.prints: dict[int, list] = {}   # request -> fingerprints of its leading full pages
         self.retained: list[Retained] = []
-        self.clock = 0                      # ticks once a release, to tell which retained prefix is the oldest
+        self.clock = 0                      # ticks once a release or a batch: which prefix, which request is oldest
+        self.seen: dict[int, int] = {}      # request -> the tick of the last batch that named it
+        self.active: set = set()            # the requests of the running batch, whose pages are never reclaimed
         rows = pages * page_buckets
         self.centroids = torch.zeros(rows, index_dim, device=device, dtype=torch.float32)
         self.members = torch.full((rows, design.bucket_cap), -1, device=device, dtype=torch.int32)
@@ -120,6 +122,7 @@ class BucketCache:
             self.retained.append(Retained(pages[:len(prints)], prints, self.clock))  # (the holder's count goes along)
             pages = pages[len(prints):]
         self.let_go(pages)
+        self.seen.pop(request, None)
         self.closed_keys.pop(request, None)
         self.pending.pop(request, None)
         self.owner.pop(request, None)
@@ -131,6 +134,13 @@ class BucketCache:
         if self.owner.get(request, rid) != rid or (request not in self.owner and self.end(request)):
             self.release(request)
         self.owner[request] = rid
+        self.seen[request] = self.clock
+
+    def running(self, requests) -> None:
+        """Name the requests of the batch about to run: finished requests keep their pages until their row is given
+        to another or pages run short, and a running one is never the one to give them up (bucket_cache.py:333-378)."""
+        self.clock += 1
+        self.active = set(int(request) for request in requests)
 
     def advance(self, request: int, end: int, index_keys_of) -> int:
         """Bring the request up to `end` keys: the index keys of the positions the cache has not seen come from
@@ -200,17 +210,24 @@ class BucketCache:
         if full > len(taken):
             taken += fingerprints_of(lookup, len(taken), full - len(taken))
 
-    def reclaim(self) -> None:
-        """Drop retained prefixes, oldest first, until a page is free (bucket_cache.py:252-255,355-378).
+    def reclaim(self, asking: int | None = None) -> None:
+        """Drop retained prefixes, oldest first, then release the idle requests seen longest ago, until a page is
+        free (bucket_cache.py:252-255,355-378). `asking` is the request that needs the page.
 
         Raises:
-            RuntimeError: Every page belongs to a request.
+            RuntimeError: Every page belongs to a running request.
         """
         while self.retained and not self.free_pages:
             oldest = min(range(len(self.retained)), key=lambda index: self.retained[index].seen)
             self.let_go(self.retained.pop(oldest).pages)
+        idle = [request for request, pages in self.held.items()
+                if pages and request != asking and request not in self.active]
+        for request in sorted(idle, key=lambda request: self.seen.get(request, 0)):
+            if self.free_pages:
+                break
+            self.release(request, retain=False)
         if not self.free_pages:
-            raise RuntimeError("the bucket cache is out of pages")  # bucket_cache.py:375-378
+            raise RuntimeError("the bucket cache is out of pages - every page belongs to a running request")
 
     def rows_of(self, request: int, logical: torch.Tensor) -> torch.Tensor:
         """Rows of the device tables that hold a request's logical buckets."""
@@ -240,7 +257,7 @@ class BucketCache:
         fresh = []
         while len(pages) < need:
             if not self.free_pages:
-                self.reclaim()
+                self.reclaim(request)
             fresh.append(self.free_pages.pop())
             self.holders[fresh[-1]] = 1
             pages.append(fresh[-1])
@@ -301,6 +318,7 @@ class Selector:
         (selector.py:162-197). `index_keys_of(row)` returns the row's lookup (first, stop) -> index keys. Returns
         the cluster blocks closed."""
         closed = 0
+        self.cache.running(rows)
         for rid, row, end in zip(rids, rows, ends, strict=True):
             self.cache.ensure(row, rid)
             lookup = index_keys_of(row)

@@ -218,9 +218,27 @@ def test_prefix_reuse_shares_full_pages_by_fingerprint_and_keeps_a_finished_pref
     assert not cache.free_pages
     cache._grow(2, cache.page_buckets)
     assert not cache.retained and len(cache.free_pages) == 2 and cache.holders[cache.held[2][0]] == 1
+    cache.running([1, 2, 3])
     with pytest.raises(RuntimeError, match="out of pages"):
         cache._grow(1, 3 * cache.page_buckets)
     for request in (1, 2, 3):
+        cache.release(request, retain=False)
+    assert sorted(cache.free_pages) == list(range(6)) and not any(cache.holders)
+    # idle requests give their pages up, the one seen longest ago first; a request of the running batch never does
+    for request, rid in ((0, "a"), (1, "b"), (2, "c")):
+        cache.running([request])
+        cache.ensure(request, rid)
+        filled(request, 2)
+    assert not cache.free_pages
+    cache.running([1, 3])
+    cache.ensure(3, "d")
+    filled(3, 1)                      # request 0, seen first, goes; its pages come back
+    assert 0 not in cache.held and cache.held[1] and cache.held[2] and len(cache.free_pages) == 1
+    filled(3, 3)                      # one free page, then request 2 goes (1 is running)
+    assert 2 not in cache.held and len(cache.held[1]) == 2 and len(cache.held[3]) == 3 and len(cache.free_pages) == 1
+    with pytest.raises(RuntimeError, match="every page belongs to a running request"):
+        filled(3, 4), filled(1, 4)
+    for request in (1, 3):
         cache.release(request, retain=False)
     assert sorted(cache.free_pages) == list(range(6)) and not any(cache.holders)
     with pytest.raises(TypeError, match="this lookup reads none"):
