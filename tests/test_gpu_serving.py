@@ -77,9 +77,17 @@ def test_batched_decode_over_paged_buckets_and_kv(oracle):
     assert len(cache.free_pages) > free_before and (cache.request_pages[2] == -1).all()
     cache.append(5, cuda(keys[1]))
     assert cache.buckets_of(5) == 2048 // 16
+    # pages run short: a request of the running batch never gives its pages up ...
+    cache.running(range(8))
     with pytest.raises(RuntimeError, match="out of pages"):
         for r in (6, 7):
             cache.append(r, cuda(keys[2]))
+    # ... an idle one does, and the cache goes on
+    cache.running([6, 7])
+    for r in (6, 7):
+        cache.release(r, retain=False)
+        cache.append(r, cuda(keys[2]))
+    assert cache.buckets_of(6) == cache.buckets_of(7) == 5000 // 256 * 256 // 16
 
 
 def test_a_decode_graph_captured_for_a_context_range_reads_the_same_lists(oracle, monkeypatch):
