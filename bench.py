@@ -445,7 +445,8 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
     # launch walks them, through the page-fingerprint kernel (a warp a 1,152-byte row, a wrapping sum of its words).
     gather_probe = None
     if world == 1:
-        group, tile, mid = 148, 64, chunk // 2
+        tile, mid = 64, chunk // 2
+        group = min(148, chunk - mid)
         walked = int(lens_d[mid:mid + group].min()) // tile * tile
         ids = lists_d[mid:mid + group, :walked].reshape(group, walked // tile, tile).permute(1, 0, 2).reshape(-1)
         ids = ids.to(torch.int64)
@@ -458,7 +459,7 @@ def run_c4(args, env: Env, cfg: dict) -> dict:
             ops.page_fingerprints(rows_2d, tile, by_word, by_row, slots=ids)
 
         read_rows()
-        probe_ms = env.timed(read_rows, 3)
+        probe_ms = max(env.timed(read_rows, 3), 1e-6)
         gather_probe = {"GB/s": ids.numel() * dk * 2 / (probe_ms * 1e-3) / 1e9, "rows_read": int(ids.numel()),
                         "ms": probe_ms,
                         "note": "lsa_page_fingerprints over the listed rows of 148 neighbouring query rows in the "
